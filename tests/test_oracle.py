@@ -1,0 +1,273 @@
+"""Pins the C++ oracle against independent Python big-integer arithmetic.
+
+The reference holds no known-answer vectors for this path (its arithmetic lives
+in an absent third-party library), so the pins are: algebraic identities,
+direct big-integer recomputation, and the committed fixtures under
+tests/golden (produced by tests/golden/make_golden.py from Python ints).
+"""
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+
+import oracle_lib as ora
+import pyref
+from pyref import R, P, fr_array, fr_ints
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_field_ops_match_python_ints():
+    rng = random.Random(1)
+    edge = [0, 1, 2, R - 1, R - 2, (1 << 255) % R, (1 << 64) - 1, 1 << 64]
+    a = edge + pyref.rand_fr(rng, 64)
+    b = list(reversed(edge)) + pyref.rand_fr(rng, 64)
+    A, B = fr_array(a), fr_array(b)
+    assert fr_ints(ora.fr_binop(0, A, B)) == [(x + y) % R for x, y in zip(a, b)]
+    assert fr_ints(ora.fr_binop(1, A, B)) == [(x - y) % R for x, y in zip(a, b)]
+    assert fr_ints(ora.fr_binop(2, A, B)) == [(x * y) % R for x, y in zip(a, b)]
+    nz = [x for x in a if x]
+    assert fr_ints(ora.fr_inv(fr_array(nz))) == [pow(x, -1, R) for x in nz]
+    with pytest.raises(RuntimeError, match="invert zero"):
+        ora.fr_inv(fr_array([0]))
+
+
+def test_fp_ops_match_python_ints():
+    rng = random.Random(2)
+    a = [0, 1, P - 1] + [rng.randrange(P) for _ in range(32)]
+    b = [P - 1, P - 2, P - 1] + [rng.randrange(P) for _ in range(32)]
+    enc = lambda v: np.frombuffer(b"".join(x.to_bytes(48, "little") for x in v), dtype=np.uint8).reshape(-1, 48)
+    dec = lambda arr: [int.from_bytes(arr[i].tobytes(), "little") for i in range(arr.shape[0])]
+    assert dec(ora.fp_binop(0, enc(a), enc(b))) == [(x + y) % P for x, y in zip(a, b)]
+    assert dec(ora.fp_binop(1, enc(a), enc(b))) == [(x - y) % P for x, y in zip(a, b)]
+    assert dec(ora.fp_binop(2, enc(a), enc(b))) == [(x * y) % P for x, y in zip(a, b)]
+
+
+def test_signed_and_decimal():
+    vals = [0, 1, -1, 17, -(1 << 62), (1 << 62), -123456789]
+    assert fr_ints(ora.fr_from_i64(vals)) == [v % R for v in vals]
+    for v in [0, 1, R - 1, 1234567890123456789012345678901234567890]:
+        assert ora.fr_to_decimal(fr_array([v])) == str(v % R)
+
+
+def test_root_of_unity_rule():
+    for log2n in [0, 1, 4, 15, 22, 32]:
+        n = 1 << log2n
+        w = fr_ints(ora.root_of_unity(n))[0]
+        assert w == pyref.root_of_unity(n)
+        assert pow(w, n, R) == 1
+        if n > 1:
+            assert pow(w, n // 2, R) == R - 1
+    with pytest.raises(RuntimeError):
+        ora.root_of_unity(12)
+
+
+def test_batch_invert():
+    rng = random.Random(3)
+    a = pyref.rand_fr(rng, 33)
+    assert fr_ints(ora.batch_invert(fr_array(a))) == [pow(x, -1, R) for x in a]
+    with pytest.raises(RuntimeError, match="zero"):
+        ora.batch_invert(fr_array([5, 0, 7]))
+
+
+@pytest.mark.parametrize("n", [1, 2, 16, 256])
+def test_bary_weights(n):
+    rng = random.Random(4 + n)
+    x = rng.randrange(1 << 64)
+    w = fr_ints(ora.bary_weights(fr_array([x]), n))
+    assert w == pyref.bary_weights(x, n)
+    assert sum(w) % R == 1  # the Lagrange basis sums to one
+
+
+def test_eval_rotations_and_commit():
+    rng = random.Random(5)
+    n, k = 64, 5
+    cols = [pyref.rand_fr(rng, n) for _ in range(k)]
+    w = pyref.rand_fr(rng, n)
+    C = np.stack([fr_array(c) for c in cols])
+    out = ora.eval_rotations(C, fr_array(w), [0, 1, 7])
+    for p, rot in enumerate([0, 1, 7]):
+        want = [sum(w[c] * col[(c + rot) % n] for c in range(n)) % R for col in cols]
+        assert fr_ints(out[p]) == want
+    valid = 40
+    out = ora.commit_tau_eval(C[:, :valid].copy(), fr_array(w[:valid]))
+    assert fr_ints(out) == [sum(w[c] * col[c] for c in range(valid)) % R for col in cols]
+    # threaded chunking gives the same values
+    n2 = 2048
+    cols2 = np.stack([fr_array(pyref.rand_fr(rng, n2)) for _ in range(3)])
+    w2 = fr_array(pyref.rand_fr(rng, n2))
+    assert np.array_equal(ora.eval_rotations(cols2, w2, [0, 1], threads=4), ora.eval_rotations(cols2, w2, [0, 1]))
+    assert np.array_equal(ora.commit_tau_eval(cols2, w2, threads=4), ora.commit_tau_eval(cols2, w2))
+
+
+def test_barycentric_equals_horner_of_interpolant():
+    # evaluating a column through weights equals evaluating its interpolating
+    # polynomial: ties a2/a3/a12 together and to the inverse NTT.
+    rng = random.Random(6)
+    n = 32
+    vals = pyref.rand_fr(rng, n)
+    x = rng.randrange(1 << 64)
+    w = ora.bary_weights(fr_array([x]), n)
+    by_weights = fr_ints(ora.commit_tau_eval(fr_array(vals)[None], w))[0]
+    coeffs = ora.ntt(fr_array(vals), inverse=True)
+    assert fr_ints(ora.horner(coeffs, fr_array([x])))[0] == by_weights
+    assert fr_ints(ora.poly_evaluate_barycentric(fr_array(vals), n, fr_array([x])))[0] == by_weights
+    # direct hit on a domain point
+    om = pyref.root_of_unity(n)
+    assert fr_ints(ora.poly_evaluate_barycentric(fr_array(vals), n, fr_array([pow(om, 5, R)])))[0] == vals[5]
+
+
+def test_matrix_and_bindings():
+    rng = random.Random(7)
+    rows, cols = 9, 5
+    M = [[rng.randrange(R) for _ in range(cols)] for _ in range(rows)]
+    Mb = np.stack([fr_array(r) for r in M])
+    x = rng.randrange(1 << 64)
+    flat = [v for r in M for v in r]
+    want = sum(c * pow(x, i, R) for i, c in enumerate(flat)) % R
+    assert fr_ints(ora.matrix_row_major_eval(Mb, fr_array([x])))[0] == want
+    w = pyref.rand_fr(rng, rows)
+    got = fr_ints(ora.weighted_column_sum(Mb, fr_array(w), 7))
+    assert got == [sum(w[r] * M[r][c] for r in range(7)) % R for c in range(cols)]
+    pw = fr_ints(ora.powers(fr_array([x]), cols))
+    assert pw == [pow(x, j, R) for j in range(cols)]
+    got = fr_ints(ora.linear_form_by_powers(Mb, fr_array(pw)))
+    assert got == [sum(M[i][j] * pw[j] for j in range(cols)) % R for i in range(rows)]
+    a, b = pyref.rand_fr(rng, 6), pyref.rand_fr(rng, 6)
+    acc, mu = ora.zkmap_accumulator(fr_array(a), fr_array(b), 16)
+    run, want_acc = 0, [0]
+    for i in range(6):
+        run = (run + a[i] * b[i]) % R
+        want_acc.append(run)
+    want_acc += [run] * (16 - 7)
+    assert fr_ints(acc) == want_acc and fr_ints(mu)[0] == run
+
+
+def test_logup_and_routes():
+    rng = random.Random(8)
+    n = 16
+    table, query, mult = (pyref.rand_fr(rng, n) for _ in range(3))
+    qt = [1] * 10 + [0] * 6
+    qq = [1] * 12 + [0] * 4
+    beta = rng.randrange(1 << 64)
+    active = ora.active_transition_count(fr_array(qt), fr_array(qq))
+    assert active == 12
+    got = fr_ints(ora.logup_accumulator(*(fr_array(v) for v in (table, query, mult, qt, qq)), fr_array([beta]), active))
+    run, want = 0, [0]
+    for i in range(active):
+        run = (run + qt[i] * mult[i] * pow(table[i] + beta, -1, R) - qq[i] * pow(query[i] + beta, -1, R)) % R
+        want.append(run)
+    want += [run] * (n - len(want))
+    assert got == want
+    got = fr_ints(ora.route_node_accumulator(fr_array(table), fr_array(mult), 9, fr_array([beta])))
+    run, want = 0, [0]
+    for i in range(9):
+        run = (run + mult[i] * pow(table[i] + beta, -1, R)) % R
+        want.append(run)
+    want += [run] * (n - len(want))
+    assert got == want
+    got = fr_ints(ora.route_edge_accumulator(fr_array(query), 9, fr_array([beta])))
+    run, want = 0, [0]
+    for i in range(9):
+        run = (run + pow(query[i] + beta, -1, R)) % R
+        want.append(run)
+    want += [run] * (n - len(want))
+    assert got == want
+    assert fr_ints(ora.route_edge_accumulator(fr_array(query), 0, fr_array([beta]))) == [0] * n
+
+
+def test_segmented_states():
+    rng = random.Random(9)
+    n = 20
+    v = pyref.rand_fr(rng, n)
+    q = [1 if i in (0, 3, 4, 11) else 0 for i in range(n)]
+    got = fr_ints(ora.group_prefix_state(fr_array(v), fr_array(q)))
+    want = [v[0]]
+    for i in range(1, n):
+        want.append(v[i] if q[i] else (want[-1] + v[i]) % R)
+    assert got == want
+    delta = [5, 0, 0, 7, 0, 1, 2, 3]
+    got = fr_ints(ora.first_zero_marker(fr_array(delta), [0, 3, 5], [3, 5, 8], 8))
+    assert got == [0, 1, 0, 0, 1, 0, 0, 0]
+
+
+def test_witness_leaves():
+    vals = np.array([0.0, 0.03124, 0.03125, -0.03125, 1.5, -2.71828, 100.99])
+    want = [int(v * 16 + 0.5) if v >= 0 else -int(-v * 16 + 0.5) for v in vals]
+    assert ora.quantize(vals).tolist() == want
+    rng = random.Random(10)
+    nodes = pyref.rand_fr(rng, 5)
+    idx = [4, 0, 0, 3, 2, 2]
+    got = fr_ints(ora.broadcast_node_values(fr_array(nodes), idx, 8))
+    assert got == [nodes[i] for i in idx] + [0, 0]
+    assert fr_ints(ora.multiplicity_from_indices([1, 1, 3, 0, 1], 4)) == [1, 3, 0, 1]
+    l, r_ = pyref.rand_fr(rng, 4), pyref.rand_fr(rng, 4)
+    lam = rng.randrange(R)
+    assert fr_ints(ora.weighted_sum(fr_array(l), fr_array([lam]), fr_array(r_), 6)) == [(a + lam * b) % R for a, b in zip(l, r_)] + [0, 0]
+    rows, width = 3, 4
+    feats = [[rng.randrange(100) for _ in range(width)] for _ in range(rows)]
+    ei, ev = rng.randrange(R), rng.randrange(R)
+    got = fr_ints(ora.feature_lookup_rows(fr_array(range(rows)), fr_array(range(width)), np.stack([fr_array(f) for f in feats]), fr_array([ei]), fr_array([ev])))
+    assert got == [(r0 + ei * c + ev * feats[r0][c]) % R for r0 in range(rows) for c in range(width)]
+
+
+def test_g1_against_affine_python():
+    G = (pyref.GX, pyref.GY)
+    Gb = np.frombuffer(pyref.g1_bytes(G), dtype=np.uint8)
+    assert ora.g1_on_curve(Gb)
+    rng = random.Random(11)
+    scalars = [0, 1, 2, R - 1, 17 + 11] + pyref.rand_fr(rng, 3)
+    out = ora.g1_mul_same_base(Gb, fr_array(scalars))
+    for i, s in enumerate(scalars):
+        assert bytes(out[i]) == pyref.g1_bytes(pyref.g1_mul(s, G))
+    a, b = pyref.g1_mul(5, G), pyref.g1_mul(R - 5, G)
+    assert bytes(ora.g1_add(np.frombuffer(pyref.g1_bytes(a), np.uint8), np.frombuffer(pyref.g1_bytes(b), np.uint8))) == bytes(96)
+    assert bytes(ora.g1_add(np.frombuffer(pyref.g1_bytes(a), np.uint8), np.frombuffer(pyref.g1_bytes(a), np.uint8))) == pyref.g1_bytes(pyref.g1_mul(10, G))
+    pts = [pyref.g1_mul(k, G) for k in (3, 9, 27)]
+    sc = pyref.rand_fr(rng, 3)
+    want = pyref.g1_mul(sum(k * s for k, s in zip((3, 9, 27), sc)) % R, G)
+    got = ora.g1_msm_naive(np.frombuffer(b"".join(pyref.g1_bytes(p) for p in pts), np.uint8), fr_array(sc))
+    assert bytes(got) == pyref.g1_bytes(want)
+
+
+def test_ntt_and_fold():
+    rng = random.Random(12)
+    for n in (1, 2, 8, 64):
+        a = pyref.rand_fr(rng, n)
+        w = pyref.root_of_unity(n)
+        want = [sum(a[i] * pow(w, i * j, R) for i in range(n)) % R for j in range(n)]
+        assert fr_ints(ora.ntt(fr_array(a))) == want
+        assert fr_ints(ora.dft_naive(fr_array(a))) == want
+        assert fr_ints(ora.ntt(ora.ntt(fr_array(a)), inverse=True)) == a
+        want_coset = [sum(a[i] * pow(5 * pow(w, j, R), i, R) for i in range(n)) % R for j in range(n)]
+        assert fr_ints(ora.ntt(fr_array(a), coset_shift=fr_array([5]))) == want_coset
+        assert fr_ints(ora.ntt(ora.ntt(fr_array(a), coset_shift=fr_array([5])), inverse=True, coset_shift=fr_array([5]))) == a
+    t = pyref.rand_fr(rng, 16)
+    r_ = rng.randrange(R)
+    assert fr_ints(ora.fold(fr_array(t), fr_array([r_]))) == [(t[2 * i] + r_ * (t[2 * i + 1] - t[2 * i])) % R for i in range(8)]
+
+
+def test_transcript_hash():
+    for s in [b"", b"gatzk", b"|alpha=123|0"]:
+        assert ora.fnv1a(s) == pyref.fnv1a(s)
+
+
+def test_golden_fixtures():
+    with open(os.path.join(GOLDEN, "hotpath_small.json")) as f:
+        g = json.load(f)
+    hx = lambda s: np.frombuffer(bytes.fromhex(s), dtype=np.uint8)
+    assert bytes(ora.root_of_unity(g["omega"]["n"])).hex() == g["omega"]["value"]
+    bw = g["bary"]
+    assert bytes(ora.bary_weights(hx(bw["x"]), bw["n"]).tobytes()).hex() == bw["weights"]
+    ev = g["eval"]
+    cols = hx(ev["columns"]).reshape(ev["k"], ev["n"], 32)
+    out = ora.eval_rotations(cols, hx(ev["weights"]).reshape(-1, 32), ev["rotations"])
+    assert out.tobytes().hex() == ev["out"]
+    g1 = g["g1_same_base"]
+    out = ora.g1_mul_same_base(hx(g1["base"]), hx(g1["scalars"]).reshape(-1, 32))
+    assert out.tobytes().hex() == g1["points"]
+    lg = g["logup"]
+    out = ora.logup_accumulator(*(hx(lg[k]).reshape(-1, 32) for k in ("table", "query", "mult", "q_table", "q_query")), hx(lg["beta"]), lg["active"])
+    assert out.tobytes().hex() == lg["out"]
