@@ -1,0 +1,104 @@
+/* gatzk_b200.h — C ABI of libgatzk_b200.so, the B200 (sm_100a) compute backend for
+ * the data-parallel core of the GAT-ZKML prover.
+ *
+ * Conventions
+ *  - every function returns 0 on success and a non-zero GZK_E_* code otherwise;
+ *    gzk_last_error() gives the message of the last failure on the context.  No
+ *    exception crosses this boundary.
+ *  - Fr values cross the boundary as 32-byte little-endian canonical integers, the
+ *    format of FieldElement::write_little_endian / from_little_endian_mod
+ *    (include/gatzk/algebra/field.hpp:79-84, 193-201).
+ *  - G1 points cross the boundary affine, x || y, 2 x 48 bytes little-endian
+ *    canonical; 96 zero bytes are the point at infinity.
+ *  - `gzk_buf` handles name device-resident arrays.  A buffer has a kind: FR
+ *    (canonical 32-byte elements, the upload format), FR_MONT (Montgomery form,
+ *    what kernels of this library produce), I64 / U32 (small-integer columns that
+ *    are widened to Fr inside the kernels, as FieldElement::from_signed does,
+ *    field.hpp:71-76).
+ *  - one context per GPU and per host thread that issues work; calls on one
+ *    context are ordered on the context's CUDA stream.
+ *  - there is no CPU fallback: every entry point fails with GZK_E_CUDA when no
+ *    sm_100 device is usable.
+ */
+#ifndef GATZK_B200_H
+#define GATZK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define GZK_OK 0
+#define GZK_E_INVALID 1   /* bad argument: the reference would have thrown std::runtime_error */
+#define GZK_E_CUDA 2      /* CUDA runtime failure or no usable device */
+#define GZK_E_DOMAIN 3    /* evaluation point lies on the domain / zero denominator in a batch inversion */
+#define GZK_E_TIMEOUT 4   /* a bounded device-side wait gave up */
+
+#define GZK_KIND_FR 0
+#define GZK_KIND_FR_MONT 1
+#define GZK_KIND_I64 2
+#define GZK_KIND_U32 3
+
+typedef struct gzk_ctx gzk_ctx;
+typedef struct gzk_buf gzk_buf;
+
+/* ---- context ------------------------------------------------------------------
+ * Replaces the runtime probe `cuda_backend_runtime_available()`
+ * (src/algebra/cuda_backend.cu:10-14, used by src/main.cpp:134-142) and owns what
+ * the reference keeps in process-wide caches: domain tables
+ * (RootOfUnityDomain::create, src/algebra/polynomial.cpp:37-91). */
+int gzk_ctx_create(int device, gzk_ctx** out);
+void gzk_ctx_destroy(gzk_ctx* ctx);
+const char* gzk_last_error(const gzk_ctx* ctx);
+int gzk_ctx_synchronize(gzk_ctx* ctx);
+/* the CUDA stream (cudaStream_t) all work of this context is issued on */
+void* gzk_ctx_stream(gzk_ctx* ctx);
+
+/* ---- device buffers -----------------------------------------------------------
+ * Replace the host std::vector<FieldElement> column storage of
+ * Polynomial::from_evaluations (src/algebra/polynomial.cpp:364-379) and the
+ * interleaved copy of the PackedEvaluationBackend constructor
+ * (src/algebra/eval_backend.cpp:61-87): columns stay column-major in HBM. */
+int gzk_buf_alloc(gzk_ctx* ctx, int kind, size_t count, gzk_buf** out);
+int gzk_buf_free(gzk_ctx* ctx, gzk_buf* buf);
+int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
+/* downloads always deliver the wire format: FR_MONT buffers are converted to
+ * canonical on the device first */
+int gzk_buf_download(gzk_ctx* ctx, const gzk_buf* buf, size_t offset, void* host, size_t count);
+size_t gzk_buf_count(const gzk_buf* buf);
+int gzk_buf_kind(const gzk_buf* buf);
+void* gzk_buf_device_ptr(gzk_buf* buf);
+
+/* ---- a1: field helpers ---------------------------------------------------------
+ * omega_n = 5^((r-1)/n): FieldElement::root_of_unity (field.hpp:87-101). */
+int gzk_root_of_unity(gzk_ctx* ctx, uint64_t size, uint8_t out[32]);
+
+/* ---- a2: barycentric weights ----------------------------------------------------
+ * w_i(x) = (x^n - 1) * omega^i / n / (x - omega^i), i < n = 2^log2n.
+ * Replaces RootOfUnityDomain::barycentric_weights_native
+ * (src/algebra/polynomial.cpp:131-316) and cached_barycentric_weights_native
+ * (src/protocol/trace.cpp:181-201).  `out` must be FR_MONT with count >= n.
+ * GZK_E_DOMAIN when x is a domain point (the reference then takes the
+ * direct-index branch of build_domain_evaluation_weights,
+ * include/gatzk/algebra/domain_evaluation.hpp:40-71, which the caller handles). */
+int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf* out);
+
+/* ---- a3 / a4: packed evaluation and commit inner products ------------------------
+ * out[p][k] = sum_{c < len} col_k[c] * w[(c - rot_p) mod n]
+ *           = sum_c w[c] * col_k[(c + rot_p) mod n]   (columns are zero beyond len).
+ * Replaces PackedEvaluationBackend::evaluate_with_native_weights and
+ * ::evaluate_with_native_weight_rotations (src/algebra/eval_backend.cpp:191-292,
+ * 309-444), evaluate_polynomials_with_shared_domain_weights
+ * (src/crypto/kzg.cpp:161-282; valid prefix = len, one rotation 0) and
+ * dot_product_native_weights (src/algebra/vector_ops.cpp:168-219).
+ * cols: K buffers of kind FR / FR_MONT / I64 / U32 with count >= len;
+ * weights: FR_MONT with count >= n; out_host: P*K*32 bytes, [p][k]. */
+int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
+                   const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,254 @@
+// Barycentric weight vector of a root-of-unity domain at a point x:
+//   w_i = (x^n - 1)/n * omega^i / (x - omega^i).
+// The n field inversions are one batch inversion, organised for the GPU as
+//   pass 1  per-CTA product of its 1024 denominators,
+//   pass 2  one CTA inverts all CTA products (scan of products + ONE Fermat
+//           inversion for the whole vector),
+//   pass 3  per-CTA: in-CTA exclusive prefix/suffix products turn the CTA inverse
+//           into the 1024 element inverses; the weight is written once, coalesced.
+// Denominators are regenerated from two small omega tables in pass 3 instead of
+// being stored, so HBM traffic is the 32 n bytes of the output only.
+#include "common.cuh"
+
+namespace gzk
+{
+    namespace
+    {
+        constexpr int kThreads = 256;
+        constexpr int kElems = 4;
+        constexpr int kChunk = kThreads * kElems;
+
+        struct BaryArgs
+        {
+            const Fr* lo;
+            const Fr* hi;
+            unsigned lo_bits;
+            uint64_t n;
+            Fr x;       // Montgomery
+            Fr scale;   // (x^n - 1)/n, Montgomery
+        };
+
+        __device__ __forceinline__ Fr shfl_fr(const Fr& v, int src_lane)
+        {
+            Fr o;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o.l[i] = __shfl_sync(0xffffffffu, v.l[i], src_lane);
+            return o;
+        }
+
+        __global__ void __launch_bounds__(kThreads) bary_products_kernel(BaryArgs a, Fr* block_products, int* status)
+        {
+            __shared__ Fr warp_products[kThreads / 32];
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk;
+            Fr prod = Fr::one();
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
+                if (e < a.n)
+                {
+                    const Fr d = sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, e));
+                    if (d.is_zero()) atomicExch(status, 1);
+                    prod = mul(prod, d);
+                }
+            }
+            const int lane = threadIdx.x & 31;
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                const Fr other = shfl_fr(prod, (lane + offset) & 31);
+                if (lane < offset) prod = mul(prod, other);
+            }
+            if (lane == 0) warp_products[threadIdx.x >> 5] = prod;
+            __syncthreads();
+            if (threadIdx.x == 0)
+            {
+                Fr total = warp_products[0];
+#pragma unroll
+                for (int w = 1; w < kThreads / 32; ++w) total = mul(total, warp_products[w]);
+                store_fr(block_products + blockIdx.x, total);
+            }
+        }
+
+        // In-place batch inversion of `count` non-zero values by ONE CTA (values are
+        // Montgomery).  Each thread owns a contiguous run; run products are combined
+        // with shared-memory exclusive prefix/suffix product scans.
+        constexpr int kInvThreads = 512;
+        __global__ void __launch_bounds__(kInvThreads) batch_invert_single_cta_kernel(Fr* values, Fr* prefix_tmp, uint32_t count)
+        {
+            __shared__ Fr pre[kInvThreads];
+            __shared__ Fr suf[kInvThreads];
+            __shared__ Fr total_inv;
+            const uint32_t t = threadIdx.x;
+            const uint32_t run = (count + kInvThreads - 1) / kInvThreads;
+            const uint32_t begin = t * run < count ? t * run : count;
+            const uint32_t end = begin + run < count ? begin + run : count;
+            Fr acc = Fr::one();
+            for (uint32_t i = begin; i < end; ++i)
+            {
+                store_fr(prefix_tmp + i, acc);
+                acc = mul(acc, load_fr_plain(values + i));
+            }
+            pre[t] = acc;
+            suf[t] = acc;
+            __syncthreads();
+            // inclusive scans (Hillis-Steele): pre = prod_{t' <= t}, suf = prod_{t' >= t}
+            for (uint32_t offset = 1; offset < kInvThreads; offset <<= 1)
+            {
+                Fr p = pre[t], s = suf[t];
+                const bool has_p = t >= offset, has_s = t + offset < kInvThreads;
+                Fr po, so;
+                if (has_p) po = pre[t - offset];
+                if (has_s) so = suf[t + offset];
+                __syncthreads();
+                if (has_p) pre[t] = mul(p, po);
+                if (has_s) suf[t] = mul(s, so);
+                __syncthreads();
+            }
+            if (t == 0) total_inv = inv(pre[kInvThreads - 1]);
+            __syncthreads();
+            // 1 / (own run product) = total_inv * prod_{t' < t} * prod_{t' > t}
+            Fr outer = total_inv;
+            if (t > 0) outer = mul(outer, pre[t - 1]);
+            if (t + 1 < kInvThreads) outer = mul(outer, suf[t + 1]);
+            for (uint32_t i = end; i-- > begin;)
+            {
+                const Fr v = load_fr_plain(values + i);
+                store_fr(values + i, mul(outer, load_fr_plain(prefix_tmp + i)));
+                outer = mul(outer, v);
+            }
+        }
+
+        __global__ void __launch_bounds__(kThreads) bary_finish_kernel(BaryArgs a, const Fr* block_inverses, Fr* out)
+        {
+            __shared__ Fr warp_incl[kThreads / 32];
+            __shared__ Fr warp_pre[kThreads / 32];
+            __shared__ Fr warp_suf[kThreads / 32];
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk;
+            const int lane = threadIdx.x & 31;
+            const int warp = threadIdx.x >> 5;
+
+            Fr d[kElems];
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
+                d[j] = e < a.n ? sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, e)) : Fr::one();
+            }
+            // thread-local exclusive prefixes; `mine` = product of the thread's elements
+            Fr pre[kElems];
+            Fr mine = Fr::one();
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                pre[j] = mine;
+                mine = mul(mine, d[j]);
+            }
+            // warp inclusive prefix and suffix products of `mine`
+            Fr incl = mine, sufx = mine;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1)
+            {
+                const Fr up = shfl_fr(incl, (lane - offset) & 31);
+                const Fr down = shfl_fr(sufx, (lane + offset) & 31);
+                if (lane >= offset) incl = mul(incl, up);
+                if (lane + offset < 32) sufx = mul(sufx, down);
+            }
+            Fr left = shfl_fr(incl, (lane - 1) & 31);   // exclusive prefix within the warp
+            Fr right = shfl_fr(sufx, (lane + 1) & 31);  // exclusive suffix within the warp
+            if (lane == 0) left = Fr::one();
+            if (lane == 31) right = Fr::one();
+            if (lane == 31) warp_incl[warp] = incl;
+            __syncthreads();
+            if (threadIdx.x == 0)
+            {
+                Fr run = Fr::one();
+#pragma unroll
+                for (int w = 0; w < kThreads / 32; ++w)
+                {
+                    warp_pre[w] = run;
+                    run = mul(run, warp_incl[w]);
+                }
+                run = Fr::one();
+#pragma unroll
+                for (int w = kThreads / 32 - 1; w >= 0; --w)
+                {
+                    warp_suf[w] = run;
+                    run = mul(run, warp_incl[w]);
+                }
+            }
+            __syncthreads();
+            // outer = 1 / (product of this thread's elements)
+            Fr outer = mul(load_fr(block_inverses + blockIdx.x), mul(mul(left, warp_pre[warp]), mul(right, warp_suf[warp])));
+            // walk the thread's elements backwards: inverse_j = outer * suffix_j * pre_j
+            Fr suffix = Fr::one();
+#pragma unroll
+            for (int j = kElems - 1; j >= 0; --j)
+            {
+                const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
+                const Fr inverse = mul(outer, mul(pre[j], suffix));
+                // omega^e = x - d_e: cheaper to rebuild than to keep in registers
+                if (e < a.n) store_fr(out + e, mul(mul(a.scale, sub(a.x, d[j])), inverse));
+                suffix = mul(suffix, d[j]);
+            }
+        }
+    }
+
+    // Shared with other translation units: in-place batch inversion of a device
+    // array of Montgomery values by one CTA; `tmp` must hold `count` elements.
+    int launch_batch_invert_single_cta(gzk_ctx* ctx, Fr* values, Fr* tmp, uint32_t count)
+    {
+        if (count == 0) return GZK_OK;
+        batch_invert_single_cta_kernel<<<1, kInvThreads, 0, ctx->stream>>>(values, tmp, count);
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        return GZK_OK;
+    }
+}
+
+using namespace gzk;
+
+extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], gzk_buf* out)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (x_bytes == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "bary_weights: null argument");
+    if (log2n > 30) return fail(ctx, GZK_E_INVALID, "bary_weights: domain too large");
+    const uint64_t n = 1ULL << log2n;
+    if (out->kind != GZK_KIND_FR_MONT || out->count < n)
+        return fail(ctx, GZK_E_INVALID, "bary_weights: output must be a Montgomery buffer of the domain size");
+    bool canonical = false;
+    const Fr x_plain = host_fr_from_bytes(x_bytes, &canonical);
+    if (!canonical) return fail(ctx, GZK_E_INVALID, "bary_weights: x is not a canonical field element");
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const DomainTables* dom = nullptr;
+    int rc = get_domain(ctx, log2n, &dom);
+    if (rc != GZK_OK) return rc;
+
+    BaryArgs args;
+    args.lo = dom->lo;
+    args.hi = dom->hi;
+    args.lo_bits = dom->lo_bits;
+    args.n = n;
+    args.x = to_mont(x_plain);
+    Fr xn = args.x;
+    for (unsigned s = 0; s < log2n; ++s) xn = sqr(xn);
+    const Fr zero_eval = sub(xn, Fr::one());
+    if (zero_eval.is_zero()) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
+    args.scale = mul(zero_eval, dom->inv_size);
+
+    const uint32_t blocks = static_cast<uint32_t>((n + kChunk - 1) / kChunk);
+    void* scratch = nullptr;
+    if ((rc = ensure_scratch(ctx, 2, static_cast<size_t>(blocks) * 2 * sizeof(Fr), &scratch)) != GZK_OK) return rc;
+    Fr* products = static_cast<Fr*>(scratch);
+    Fr* tmp = products + blocks;
+    GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+    bary_products_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, ctx->d_status);
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    if ((rc = launch_batch_invert_single_cta(ctx, products, tmp, blocks)) != GZK_OK) return rc;
+    bary_finish_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, static_cast<Fr*>(out->dptr));
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    int status = 0;
+    GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (status != 0) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
+    return GZK_OK;
+}

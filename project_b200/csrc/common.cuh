@@ -1,0 +1,119 @@
+// Internal declarations shared by the translation units of libgatzk_b200.so:
+// the context and buffer objects behind the opaque C handles, error plumbing and
+// the global-memory access helpers for 32-byte field elements.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/gatzk_b200.h"
+#include "field.cuh"
+
+struct gzk_buf
+{
+    void* dptr = nullptr;
+    size_t count = 0;
+    int kind = GZK_KIND_FR;
+    size_t elem_bytes = 32;
+};
+
+namespace gzk
+{
+    // omega powers of one domain as two small tables: omega^i = hi[i >> LO] * lo[i & mask].
+    struct DomainTables
+    {
+        unsigned log2n = 0;
+        unsigned lo_bits = 0;
+        Fr* lo = nullptr;       // omega^j, j < 2^lo_bits (Montgomery)
+        Fr* hi = nullptr;       // omega^(j << lo_bits), j < 2^(log2n - lo_bits)
+        Fr* lo_inv = nullptr;   // omega^-j
+        Fr* hi_inv = nullptr;   // omega^-(j << lo_bits)
+        Fr omega;               // Montgomery
+        Fr inv_size;            // 1/n, Montgomery
+    };
+
+    // Grow-only device scratch owned by the context (reused across calls, never
+    // shrinks; freed with the context).
+    struct Scratch
+    {
+        void* ptr = nullptr;
+        size_t bytes = 0;
+    };
+}
+
+struct gzk_ctx
+{
+    int device = 0;
+    int sm_count = 0;
+    cudaStream_t stream = nullptr;
+    std::string last_error;
+    std::unordered_map<unsigned, gzk::DomainTables> domains;
+    gzk::Scratch scratch[4];
+    void* pinned = nullptr;  // small pinned staging area for results
+    size_t pinned_bytes = 0;
+    int* d_status = nullptr;  // device-side status word (zero-denominator flags etc.)
+};
+
+namespace gzk
+{
+    int fail(gzk_ctx* ctx, int code, const std::string& message);
+    int cuda_fail(gzk_ctx* ctx, cudaError_t err, const char* what);
+    int ensure_scratch(gzk_ctx* ctx, int slot, size_t bytes, void** out);
+    int ensure_pinned(gzk_ctx* ctx, size_t bytes, void** out);
+    int get_domain(gzk_ctx* ctx, unsigned log2n, const DomainTables** out);
+
+    // Host-side scalar helpers (same arithmetic, emulated carry flag).
+    Fr host_fr_from_bytes(const uint8_t* bytes, bool* canonical_ok);
+    void host_fr_to_bytes(const Fr& canonical, uint8_t* bytes);
+    Fr host_root_of_unity(unsigned log2n);  // Montgomery form
+
+#define GZK_CUDA_TRY(ctx, expr)                                         \
+    do                                                                  \
+    {                                                                   \
+        cudaError_t gzk_err_ = (expr);                                  \
+        if (gzk_err_ != cudaSuccess) return gzk::cuda_fail(ctx, gzk_err_, #expr); \
+    } while (0)
+
+#if defined(__CUDACC__)
+    // 32-byte element access as two 128-bit transactions.
+    __device__ __forceinline__ Fr load_fr(const Fr* p)
+    {
+        const uint4* q = reinterpret_cast<const uint4*>(p);
+        const uint4 a = __ldg(q);
+        const uint4 b = __ldg(q + 1);
+        Fr o;
+        o.l[0] = a.x; o.l[1] = a.y; o.l[2] = a.z; o.l[3] = a.w;
+        o.l[4] = b.x; o.l[5] = b.y; o.l[6] = b.z; o.l[7] = b.w;
+        return o;
+    }
+    __device__ __forceinline__ Fr load_fr_plain(const Fr* p)
+    {
+        const uint4* q = reinterpret_cast<const uint4*>(p);
+        const uint4 a = q[0];
+        const uint4 b = q[1];
+        Fr o;
+        o.l[0] = a.x; o.l[1] = a.y; o.l[2] = a.z; o.l[3] = a.w;
+        o.l[4] = b.x; o.l[5] = b.y; o.l[6] = b.z; o.l[7] = b.w;
+        return o;
+    }
+    __device__ __forceinline__ void store_fr(Fr* p, const Fr& v)
+    {
+        uint4* q = reinterpret_cast<uint4*>(p);
+        q[0] = make_uint4(v.l[0], v.l[1], v.l[2], v.l[3]);
+        q[1] = make_uint4(v.l[4], v.l[5], v.l[6], v.l[7]);
+    }
+    // omega^i from the two-level tables.
+    __device__ __forceinline__ Fr domain_point(const Fr* lo, const Fr* hi, unsigned lo_bits, uint64_t i)
+    {
+        const Fr a = load_fr(hi + (i >> lo_bits));
+        const uint64_t j = i & ((1ULL << lo_bits) - 1ULL);
+        if (j == 0) return a;
+        return mul(a, load_fr(lo + j));
+    }
+#endif
+}

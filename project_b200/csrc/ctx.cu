@@ -1,0 +1,337 @@
+// Context, device buffers and domain tables of libgatzk_b200.so.
+#include <cstring>
+#include <new>
+
+#include "common.cuh"
+
+namespace gzk
+{
+    int fail(gzk_ctx* ctx, int code, const std::string& message)
+    {
+        if (ctx != nullptr) ctx->last_error = message;
+        return code;
+    }
+
+    int cuda_fail(gzk_ctx* ctx, cudaError_t err, const char* what)
+    {
+        return fail(ctx, GZK_E_CUDA, std::string("CUDA error: ") + cudaGetErrorString(err) + " in " + what);
+    }
+
+    int ensure_scratch(gzk_ctx* ctx, int slot, size_t bytes, void** out)
+    {
+        Scratch& s = ctx->scratch[slot];
+        if (s.bytes < bytes)
+        {
+            if (s.ptr != nullptr)
+            {
+                GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                GZK_CUDA_TRY(ctx, cudaFree(s.ptr));
+                s.ptr = nullptr;
+                s.bytes = 0;
+            }
+            const size_t rounded = (bytes + (1u << 20) - 1) & ~static_cast<size_t>((1u << 20) - 1);
+            GZK_CUDA_TRY(ctx, cudaMalloc(&s.ptr, rounded));
+            s.bytes = rounded;
+        }
+        *out = s.ptr;
+        return GZK_OK;
+    }
+
+    int ensure_pinned(gzk_ctx* ctx, size_t bytes, void** out)
+    {
+        if (ctx->pinned_bytes < bytes)
+        {
+            if (ctx->pinned != nullptr)
+            {
+                GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                GZK_CUDA_TRY(ctx, cudaFreeHost(ctx->pinned));
+                ctx->pinned = nullptr;
+                ctx->pinned_bytes = 0;
+            }
+            const size_t rounded = (bytes + 65535) & ~static_cast<size_t>(65535);
+            GZK_CUDA_TRY(ctx, cudaMallocHost(&ctx->pinned, rounded));
+            ctx->pinned_bytes = rounded;
+        }
+        *out = ctx->pinned;
+        return GZK_OK;
+    }
+
+    Fr host_fr_from_bytes(const uint8_t* bytes, bool* canonical_ok)
+    {
+        Fr v;
+        std::memcpy(v.l, bytes, 32);
+        // canonical <=> v < r
+        bool less = false;
+        for (int i = 7; i >= 0; --i)
+        {
+            if (v.l[i] != FrCfg::mod(i))
+            {
+                less = v.l[i] < FrCfg::mod(i);
+                break;
+            }
+        }
+        if (canonical_ok != nullptr) *canonical_ok = less;
+        return v;
+    }
+
+    void host_fr_to_bytes(const Fr& canonical, uint8_t* bytes) { std::memcpy(bytes, canonical.l, 32); }
+
+    Fr host_root_of_unity(unsigned log2n)
+    {
+        // exponent = (r - 1) >> log2n, as FieldElement::root_of_unity divides (r-1) by n
+        uint32_t e[8];
+        for (int i = 0; i < 8; ++i) e[i] = FrCfg::mod(i);
+        e[0] -= 1;
+        for (unsigned s = 0; s < log2n; ++s)
+        {
+            for (int i = 0; i < 8; ++i)
+            {
+                e[i] >>= 1;
+                if (i + 1 < 8) e[i] |= e[i + 1] << 31;
+            }
+        }
+        Fr five = Fr::zero();
+        five.l[0] = 5;
+        const Fr base = to_mont(five);
+        Fr out = Fr::one();
+        bool started = false;
+        for (int limb = 7; limb >= 0; --limb)
+        {
+            for (int bit = 31; bit >= 0; --bit)
+            {
+                if (started) out = sqr(out);
+                if ((e[limb] >> bit) & 1U)
+                {
+                    out = started ? mul(out, base) : base;
+                    started = true;
+                }
+            }
+        }
+        return out;
+    }
+
+    int get_domain(gzk_ctx* ctx, unsigned log2n, const DomainTables** out)
+    {
+        if (log2n > 32) return fail(ctx, GZK_E_INVALID, "domain size exceeds the 2-adicity of Fr");
+        auto it = ctx->domains.find(log2n);
+        if (it != ctx->domains.end())
+        {
+            *out = &it->second;
+            return GZK_OK;
+        }
+        DomainTables t;
+        t.log2n = log2n;
+        t.lo_bits = log2n < 12 ? log2n : (log2n + 1) / 2 > 12 ? (log2n + 1) / 2 : 12;
+        if (t.lo_bits > log2n) t.lo_bits = log2n;
+        const size_t lo_count = static_cast<size_t>(1) << t.lo_bits;
+        const size_t hi_count = static_cast<size_t>(1) << (log2n - t.lo_bits);
+        t.omega = host_root_of_unity(log2n);
+        const Fr omega_inv = inv(t.omega);
+        {
+            Fr n_plain = Fr::zero();
+            const uint64_t n = 1ULL << log2n;
+            n_plain.l[0] = static_cast<uint32_t>(n);
+            n_plain.l[1] = static_cast<uint32_t>(n >> 32);
+            t.inv_size = inv(to_mont(n_plain));
+        }
+        std::vector<Fr> host(lo_count > hi_count ? lo_count : hi_count);
+        auto build = [&](const Fr& step, size_t count, Fr** dptr) -> int {
+            Fr cur = Fr::one();
+            for (size_t j = 0; j < count; ++j)
+            {
+                host[j] = cur;
+                cur = mul(cur, step);
+            }
+            GZK_CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void**>(dptr), count * sizeof(Fr)));
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(*dptr, host.data(), count * sizeof(Fr), cudaMemcpyHostToDevice, ctx->stream));
+            GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            return GZK_OK;
+        };
+        Fr hi_step = t.omega, hi_step_inv = omega_inv;
+        for (unsigned s = 0; s < t.lo_bits; ++s)
+        {
+            hi_step = sqr(hi_step);
+            hi_step_inv = sqr(hi_step_inv);
+        }
+        int rc;
+        if ((rc = build(t.omega, lo_count, &t.lo)) != GZK_OK) return rc;
+        if ((rc = build(hi_step, hi_count, &t.hi)) != GZK_OK) return rc;
+        if ((rc = build(omega_inv, lo_count, &t.lo_inv)) != GZK_OK) return rc;
+        if ((rc = build(hi_step_inv, hi_count, &t.hi_inv)) != GZK_OK) return rc;
+        auto ins = ctx->domains.emplace(log2n, t);
+        *out = &ins.first->second;
+        return GZK_OK;
+    }
+
+    __global__ void convert_kernel(const Fr* in, Fr* out, size_t count, int to_montgomery)
+    {
+        const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+        for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < count; i += stride)
+        {
+            const Fr v = load_fr(in + i);
+            store_fr(out + i, to_montgomery ? to_mont(v) : from_mont(v));
+        }
+    }
+}
+
+using namespace gzk;
+
+extern "C"
+{
+    int gzk_ctx_create(int device, gzk_ctx** out)
+    {
+        if (out == nullptr) return GZK_E_INVALID;
+        *out = nullptr;
+        int count = 0;
+        if (cudaGetDeviceCount(&count) != cudaSuccess || count <= 0 || device < 0 || device >= count) return GZK_E_CUDA;
+        cudaDeviceProp prop;
+        if (cudaGetDeviceProperties(&prop, device) != cudaSuccess) return GZK_E_CUDA;
+        if (prop.major != 10) return GZK_E_CUDA;  // built for sm_100a only
+        if (cudaSetDevice(device) != cudaSuccess) return GZK_E_CUDA;
+        gzk_ctx* ctx = new (std::nothrow) gzk_ctx();
+        if (ctx == nullptr) return GZK_E_INVALID;
+        ctx->device = device;
+        ctx->sm_count = prop.multiProcessorCount;
+        if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 64) != cudaSuccess ||
+            cudaMemset(ctx->d_status, 0, 64) != cudaSuccess)
+        {
+            delete ctx;
+            return GZK_E_CUDA;
+        }
+        *out = ctx;
+        return GZK_OK;
+    }
+
+    void gzk_ctx_destroy(gzk_ctx* ctx)
+    {
+        if (ctx == nullptr) return;
+        cudaSetDevice(ctx->device);
+        cudaStreamSynchronize(ctx->stream);
+        for (auto& kv : ctx->domains)
+        {
+            cudaFree(kv.second.lo);
+            cudaFree(kv.second.hi);
+            cudaFree(kv.second.lo_inv);
+            cudaFree(kv.second.hi_inv);
+        }
+        for (auto& s : ctx->scratch)
+            if (s.ptr != nullptr) cudaFree(s.ptr);
+        if (ctx->pinned != nullptr) cudaFreeHost(ctx->pinned);
+        if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
+        cudaStreamDestroy(ctx->stream);
+        delete ctx;
+    }
+
+    const char* gzk_last_error(const gzk_ctx* ctx) { return ctx == nullptr ? "no context" : ctx->last_error.c_str(); }
+
+    int gzk_ctx_synchronize(gzk_ctx* ctx)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    void* gzk_ctx_stream(gzk_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
+
+    int gzk_buf_alloc(gzk_ctx* ctx, int kind, size_t count, gzk_buf** out)
+    {
+        if (ctx == nullptr || out == nullptr) return GZK_E_INVALID;
+        size_t elem = 0;
+        switch (kind)
+        {
+        case GZK_KIND_FR:
+        case GZK_KIND_FR_MONT: elem = 32; break;
+        case GZK_KIND_I64: elem = 8; break;
+        case GZK_KIND_U32: elem = 4; break;
+        default: return fail(ctx, GZK_E_INVALID, "unknown buffer kind");
+        }
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        gzk_buf* b = new (std::nothrow) gzk_buf();
+        if (b == nullptr) return fail(ctx, GZK_E_INVALID, "out of host memory");
+        b->count = count;
+        b->kind = kind;
+        b->elem_bytes = elem;
+        const size_t bytes = count * elem > 0 ? count * elem : 32;
+        const cudaError_t err = cudaMalloc(&b->dptr, bytes);
+        if (err != cudaSuccess)
+        {
+            delete b;
+            return cuda_fail(ctx, err, "cudaMalloc(buffer)");
+        }
+        *out = b;
+        return GZK_OK;
+    }
+
+    int gzk_buf_free(gzk_ctx* ctx, gzk_buf* buf)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (buf == nullptr) return GZK_OK;
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaFree(buf->dptr));
+        delete buf;
+        return GZK_OK;
+    }
+
+    int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count)
+    {
+        if (ctx == nullptr || buf == nullptr || (host == nullptr && count != 0)) return GZK_E_INVALID;
+        if (offset + count > buf->count) return fail(ctx, GZK_E_INVALID, "upload exceeds the buffer");
+        if (count == 0) return GZK_OK;
+        char* dst = static_cast<char*>(buf->dptr) + offset * buf->elem_bytes;
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(dst, host, count * buf->elem_bytes, cudaMemcpyHostToDevice, ctx->stream));
+        if (buf->kind == GZK_KIND_FR_MONT)
+        {
+            Fr* p = reinterpret_cast<Fr*>(dst);
+            const unsigned blocks = static_cast<unsigned>((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+            convert_kernel<<<blocks, 256, 0, ctx->stream>>>(p, p, count, 1);
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+        }
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_buf_download(gzk_ctx* ctx, const gzk_buf* buf, size_t offset, void* host, size_t count)
+    {
+        if (ctx == nullptr || buf == nullptr || (host == nullptr && count != 0)) return GZK_E_INVALID;
+        if (offset + count > buf->count) return fail(ctx, GZK_E_INVALID, "download exceeds the buffer");
+        if (count == 0) return GZK_OK;
+        const char* src = static_cast<const char*>(buf->dptr) + offset * buf->elem_bytes;
+        if (buf->kind == GZK_KIND_FR_MONT)
+        {
+            // convert in chunks through context scratch so that the buffer itself stays Montgomery
+            const size_t chunk = static_cast<size_t>(1) << 20;
+            void* tmp = nullptr;
+            int rc = ensure_scratch(ctx, 3, (count < chunk ? count : chunk) * 32, &tmp);
+            if (rc != GZK_OK) return rc;
+            for (size_t done = 0; done < count; done += chunk)
+            {
+                const size_t cur = count - done < chunk ? count - done : chunk;
+                const unsigned blocks = static_cast<unsigned>((cur + 255) / 256 < 4096 ? (cur + 255) / 256 : 4096);
+                convert_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const Fr*>(src) + done, static_cast<Fr*>(tmp), cur, 0);
+                GZK_CUDA_TRY(ctx, cudaGetLastError());
+                GZK_CUDA_TRY(ctx, cudaMemcpyAsync(static_cast<char*>(host) + done * 32, tmp, cur * 32, cudaMemcpyDeviceToHost, ctx->stream));
+                GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            }
+            return GZK_OK;
+        }
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(host, src, count * buf->elem_bytes, cudaMemcpyDeviceToHost, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    size_t gzk_buf_count(const gzk_buf* buf) { return buf == nullptr ? 0 : buf->count; }
+    int gzk_buf_kind(const gzk_buf* buf) { return buf == nullptr ? -1 : buf->kind; }
+    void* gzk_buf_device_ptr(gzk_buf* buf) { return buf == nullptr ? nullptr : buf->dptr; }
+
+    int gzk_root_of_unity(gzk_ctx* ctx, uint64_t size, uint8_t out[32])
+    {
+        if (ctx == nullptr || out == nullptr) return GZK_E_INVALID;
+        if (size == 0 || (size & (size - 1)) != 0) return fail(ctx, GZK_E_INVALID, "domain size must be a non-zero power of two");
+        unsigned log2n = 0;
+        while ((1ULL << log2n) < size) ++log2n;
+        if (log2n > 32) return fail(ctx, GZK_E_INVALID, "domain size exceeds the 2-adicity of Fr");
+        host_fr_to_bytes(from_mont(host_root_of_unity(log2n)), out);
+        return GZK_OK;
+    }
+}

@@ -1,0 +1,496 @@
+// Montgomery prime fields on 32-bit limbs for sm_100a: BLS12-381 Fr (8 limbs)
+// and Fp (12 limbs), the fields the reference prover works in
+// (include/gatzk/algebra/field.hpp:19-25 initialises mcl for BLS12_381).
+//
+// Multiplication keeps two accumulators, one for products that land on even
+// limb boundaries and one for products that land on odd boundaries, so that
+// each row of the schoolbook product is a single mad.lo.cc / madc.hi.cc carry
+// chain with no carry conflicts between neighbouring products.  After every
+// row the value is divided by 2^32 by swapping the roles of the two
+// accumulators (the odd-aligned one becomes even-aligned).
+#pragma once
+
+#include "mp.cuh"
+
+namespace gzk
+{
+    struct FrCfg
+    {
+        static constexpr int N = 8;
+        static constexpr uint32_t INV = 0xffffffffu;  // -r^-1 mod 2^32
+        GZK_HD static constexpr uint32_t mod(int i)
+        {
+            constexpr uint32_t m[8] = {0x00000001u, 0xffffffffu, 0xfffe5bfeu, 0x53bda402u,
+                                       0x09a1d805u, 0x3339d808u, 0x299d7d48u, 0x73eda753u};
+            return m[i];
+        }
+        GZK_HD static constexpr uint32_t r1(int i)  // 2^256 mod r
+        {
+            constexpr uint32_t m[8] = {0xfffffffeu, 0x00000001u, 0x00034802u, 0x5884b7fau,
+                                       0xecbc4ff5u, 0x998c4fefu, 0xacc5056fu, 0x1824b159u};
+            return m[i];
+        }
+        GZK_HD static constexpr uint32_t r2(int i)  // 2^512 mod r
+        {
+            constexpr uint32_t m[8] = {0xf3f29c6du, 0xc999e990u, 0x87925c23u, 0x2b6cedcbu,
+                                       0x7254398fu, 0x05d31496u, 0x9f59ff11u, 0x0748d9d9u};
+            return m[i];
+        }
+    };
+
+    struct FpCfg
+    {
+        static constexpr int N = 12;
+        static constexpr uint32_t INV = 0xfffcfffdu;  // -p^-1 mod 2^32
+        GZK_HD static constexpr uint32_t mod(int i)
+        {
+            constexpr uint32_t m[12] = {0xffffaaabu, 0xb9feffffu, 0xb153ffffu, 0x1eabfffeu, 0xf6b0f624u, 0x6730d2a0u,
+                                        0xf38512bfu, 0x64774b84u, 0x434bacd7u, 0x4b1ba7b6u, 0x397fe69au, 0x1a0111eau};
+            return m[i];
+        }
+        GZK_HD static constexpr uint32_t r1(int i)  // 2^384 mod p
+        {
+            constexpr uint32_t m[12] = {0x0002fffdu, 0x76090000u, 0xc40c0002u, 0xebf4000bu, 0x53c758bau, 0x5f489857u,
+                                        0x70525745u, 0x77ce5853u, 0xa256ec6du, 0x5c071a97u, 0xfa80e493u, 0x15f65ec3u};
+            return m[i];
+        }
+        GZK_HD static constexpr uint32_t r2(int i)  // 2^768 mod p
+        {
+            constexpr uint32_t m[12] = {0x1c341746u, 0xf4df1f34u, 0x09d104f1u, 0x0a76e6a6u, 0x4c95b6d5u, 0x8de5476cu,
+                                        0x939d83c0u, 0x67eb88a9u, 0xb519952du, 0x9a793e85u, 0x92cae3aau, 0x11988fe5u};
+            return m[i];
+        }
+    };
+
+    template <typename Cfg>
+    struct Fe
+    {
+        static constexpr int N = Cfg::N;
+        uint32_t l[N];
+
+        GZK_HD static Fe zero()
+        {
+            Fe o;
+#pragma unroll
+            for (int i = 0; i < N; ++i) o.l[i] = 0;
+            return o;
+        }
+        // Montgomery form of 1.
+        GZK_HD static Fe one()
+        {
+            Fe o;
+#pragma unroll
+            for (int i = 0; i < N; ++i) o.l[i] = Cfg::r1(i);
+            return o;
+        }
+        GZK_HD static Fe r2()
+        {
+            Fe o;
+#pragma unroll
+            for (int i = 0; i < N; ++i) o.l[i] = Cfg::r2(i);
+            return o;
+        }
+        GZK_HD static Fe modulus()
+        {
+            Fe o;
+#pragma unroll
+            for (int i = 0; i < N; ++i) o.l[i] = Cfg::mod(i);
+            return o;
+        }
+        GZK_HD bool is_zero() const
+        {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc |= l[i];
+            return acc == 0;
+        }
+        GZK_HD bool operator==(const Fe& o) const
+        {
+            uint32_t acc = 0;
+#pragma unroll
+            for (int i = 0; i < N; ++i) acc |= l[i] ^ o.l[i];
+            return acc == 0;
+        }
+        GZK_HD bool operator!=(const Fe& o) const { return !(*this == o); }
+    };
+
+    // r = a - modulus if a >= modulus else a  (input < 2*modulus, N limbs).
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> reduce_once(const Fe<Cfg>& a)
+    {
+        constexpr int N = Cfg::N;
+        Fe<Cfg> t;
+        t.l[0] = mp::sub_cc(a.l[0], Cfg::mod(0));
+#pragma unroll
+        for (int i = 1; i < N; ++i) t.l[i] = mp::subc_cc(a.l[i], Cfg::mod(i));
+        const uint32_t borrow = mp::subc(0, 0);  // 0 or 0xffffffff
+        Fe<Cfg> o;
+#pragma unroll
+        for (int i = 0; i < N; ++i) o.l[i] = borrow ? a.l[i] : t.l[i];
+        return o;
+    }
+
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> add(const Fe<Cfg>& a, const Fe<Cfg>& b)
+    {
+        constexpr int N = Cfg::N;
+        // Both moduli leave the top bit of the top limb free, so a+b fits N limbs.
+        Fe<Cfg> s;
+        s.l[0] = mp::add_cc(a.l[0], b.l[0]);
+#pragma unroll
+        for (int i = 1; i < N - 1; ++i) s.l[i] = mp::addc_cc(a.l[i], b.l[i]);
+        s.l[N - 1] = mp::addc(a.l[N - 1], b.l[N - 1]);
+        return reduce_once(s);
+    }
+
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> sub(const Fe<Cfg>& a, const Fe<Cfg>& b)
+    {
+        constexpr int N = Cfg::N;
+        Fe<Cfg> d;
+        d.l[0] = mp::sub_cc(a.l[0], b.l[0]);
+#pragma unroll
+        for (int i = 1; i < N; ++i) d.l[i] = mp::subc_cc(a.l[i], b.l[i]);
+        const uint32_t borrow = mp::subc(0, 0);
+        Fe<Cfg> o;
+        o.l[0] = mp::add_cc(d.l[0], borrow & Cfg::mod(0));
+#pragma unroll
+        for (int i = 1; i < N - 1; ++i) o.l[i] = mp::addc_cc(d.l[i], borrow & Cfg::mod(i));
+        o.l[N - 1] = mp::addc(d.l[N - 1], borrow & Cfg::mod(N - 1));
+        return o;
+    }
+
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> neg(const Fe<Cfg>& a)
+    {
+        return sub(Fe<Cfg>::zero(), a);
+    }
+
+    namespace detail
+    {
+        // P (N+1 limbs, even-aligned) += sum over even j of x[j] * y * 2^(32 j);
+        // the carry out of the chain is added to P[N].
+        template <typename Cfg, typename X>
+        GZK_HD void mad_even(uint32_t* P, X x, uint32_t y)
+        {
+            constexpr int N = Cfg::N;
+            P[0] = mp::mad_lo_cc(x(0), y, P[0]);
+            P[1] = mp::madc_hi_cc(x(0), y, P[1]);
+#pragma unroll
+            for (int j = 2; j < N; j += 2)
+            {
+                P[j] = mp::madc_lo_cc(x(j), y, P[j]);
+                P[j + 1] = mp::madc_hi_cc(x(j), y, P[j + 1]);
+            }
+            P[N] = mp::addc(P[N], 0);
+        }
+        // Q (N limbs, odd-aligned) += sum over odd j of x[j] * y * 2^(32 (j-1));
+        // the caller guarantees that the sum fits N limbs.
+        template <typename Cfg, typename X>
+        GZK_HD void mad_odd(uint32_t* Q, X x, uint32_t y)
+        {
+            constexpr int N = Cfg::N;
+            Q[0] = mp::mad_lo_cc(x(1), y, Q[0]);
+            Q[1] = mp::madc_hi_cc(x(1), y, Q[1]);
+#pragma unroll
+            for (int j = 3; j < N - 1; j += 2)
+            {
+                Q[j - 1] = mp::madc_lo_cc(x(j), y, Q[j - 1]);
+                Q[j] = mp::madc_hi_cc(x(j), y, Q[j]);
+            }
+            Q[N - 2] = mp::madc_lo_cc(x(N - 1), y, Q[N - 2]);
+            Q[N - 1] = mp::madc_hi(x(N - 1), y, Q[N - 1]);
+        }
+
+        template <typename Cfg>
+        struct ModLimb
+        {
+            GZK_HD constexpr uint32_t operator()(int i) const { return Cfg::mod(i); }
+        };
+        struct ArrLimb
+        {
+            const uint32_t* p;
+            GZK_HD uint32_t operator()(int i) const { return p[i]; }
+        };
+
+        // One Montgomery row: on entry `P` holds the previous odd-aligned
+        // accumulator (N limbs) and `Q` the previous even-aligned one (N+1
+        // limbs, limb 0 already zero).  The running value is divided by 2^32 by
+        // swapping roles, then a*bi and m*modulus are added.
+        template <typename Cfg>
+        GZK_HD void mont_row(uint32_t* P, uint32_t* Q, const uint32_t* a, uint32_t bi)
+        {
+            constexpr int N = Cfg::N;
+            // value/2^32 = (Q >> 32) + P: limb Q[1] joins P[0]; the carry of that
+            // addition has weight 2^32, which is exactly limb 0 of the new
+            // odd-aligned accumulator, so it feeds the next chain.
+            P[0] = mp::add_cc(P[0], Q[1]);
+            // new odd-aligned accumulator = (Q >> 64) + odd limbs of a times bi
+#pragma unroll
+            for (int j = 1; j < N - 1; j += 2)
+            {
+                Q[j - 1] = mp::madc_lo_cc(a[j], bi, Q[j + 1]);
+                Q[j] = mp::madc_hi_cc(a[j], bi, Q[j + 2]);
+            }
+            Q[N - 2] = mp::madc_lo_cc(a[N - 1], bi, Q[N]);
+            Q[N - 1] = mp::madc_hi(a[N - 1], bi, 0);
+            Q[N] = 0;
+            P[N] = 0;
+            mad_even<Cfg>(P, ArrLimb{a}, bi);
+            const uint32_t m = mp::mul_lo(P[0], Cfg::INV);
+            mad_odd<Cfg>(Q, ModLimb<Cfg>{}, m);
+            mad_even<Cfg>(P, ModLimb<Cfg>{}, m);
+        }
+    }
+
+    // Montgomery product a*b*2^(-32N) mod modulus, fully reduced.
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> mul(const Fe<Cfg>& a, const Fe<Cfg>& b)
+    {
+        constexpr int N = Cfg::N;
+        static_assert(N % 2 == 0, "limb count must be even");
+        uint32_t X[N + 1], Y[N + 1];
+        // first row: plain products, no accumulation
+#pragma unroll
+        for (int j = 0; j < N; j += 2)
+        {
+            X[j] = mp::mul_lo(a.l[j], b.l[0]);
+            X[j + 1] = mp::mul_hi(a.l[j], b.l[0]);
+            Y[j] = mp::mul_lo(a.l[j + 1], b.l[0]);
+            Y[j + 1] = mp::mul_hi(a.l[j + 1], b.l[0]);
+        }
+        X[N] = 0;
+        Y[N] = 0;
+        {
+            const uint32_t m = mp::mul_lo(X[0], Cfg::INV);
+            detail::mad_odd<Cfg>(Y, detail::ModLimb<Cfg>{}, m);
+            detail::mad_even<Cfg>(X, detail::ModLimb<Cfg>{}, m);
+        }
+#pragma unroll
+        for (int i = 1; i < N; i += 2)
+        {
+            detail::mont_row<Cfg>(Y, X, a.l, b.l[i]);
+            if (i + 1 < N) detail::mont_row<Cfg>(X, Y, a.l, b.l[i + 1]);
+        }
+        // after an odd number of role swaps Y is even-aligned (limb 0 zero) and X
+        // odd-aligned: result = (Y >> 32) + X < 2*modulus.
+        Fe<Cfg> s;
+        s.l[0] = mp::add_cc(Y[1], X[0]);
+#pragma unroll
+        for (int k = 1; k < N - 1; ++k) s.l[k] = mp::addc_cc(Y[k + 1], X[k]);
+        s.l[N - 1] = mp::addc(Y[N], X[N - 1]);
+        return reduce_once(s);
+    }
+
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> sqr(const Fe<Cfg>& a)
+    {
+        return mul(a, a);
+    }
+
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> to_mont(const Fe<Cfg>& canonical)
+    {
+        return mul(canonical, Fe<Cfg>::r2());
+    }
+
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> from_mont(const Fe<Cfg>& a)
+    {
+        Fe<Cfg> one_plain = Fe<Cfg>::zero();
+        one_plain.l[0] = 1;
+        return mul(a, one_plain);
+    }
+
+    // a^e for a 64-bit exponent (Montgomery in, Montgomery out).
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> pow_u64(const Fe<Cfg>& a, uint64_t e)
+    {
+        Fe<Cfg> out = Fe<Cfg>::one();
+        bool started = false;
+        for (int i = 63; i >= 0; --i)
+        {
+            if (started) out = sqr(out);
+            if ((e >> i) & 1ULL)
+            {
+                out = started ? mul(out, a) : a;
+                started = true;
+            }
+        }
+        return out;
+    }
+
+    // Fermat inverse a^(modulus-2); a must be non-zero (0 maps to 0).
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> inv(const Fe<Cfg>& a)
+    {
+        constexpr int N = Cfg::N;
+        Fe<Cfg> out = Fe<Cfg>::one();
+        bool started = false;
+        uint32_t exponent[N];
+        {
+            // modulus - 2 with borrow propagation
+            uint32_t borrow = 2;
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+            {
+                const uint32_t m = Cfg::mod(i);
+                exponent[i] = m - borrow;
+                borrow = m < borrow ? 1u : 0u;
+            }
+        }
+        for (int limb = N - 1; limb >= 0; --limb)
+        {
+            const uint32_t e = exponent[limb];
+            for (int bit = 31; bit >= 0; --bit)
+            {
+                if (started) out = sqr(out);
+                if ((e >> bit) & 1U)
+                {
+                    out = started ? mul(out, a) : a;
+                    started = true;
+                }
+            }
+        }
+        return out;
+    }
+
+    // Full 2N-limb product of two N-limb integers (no reduction).  Products whose
+    // low half lands on an even limb go to E, the others to O (O is offset by one
+    // limb); every carry out of a row chain lands in a limb no earlier row has
+    // touched, so a single addc captures it.
+    template <int N>
+    GZK_HD void mul_wide(const uint32_t* a, const uint32_t* b, uint32_t* out)
+    {
+        static_assert(N % 2 == 0, "limb count must be even");
+        uint32_t E[2 * N], O[2 * N];
+#pragma unroll
+        for (int k = 0; k < 2 * N; ++k)
+        {
+            E[k] = 0;
+            O[k] = 0;
+        }
+#pragma unroll
+        for (int j = 0; j < N; j += 2)
+        {
+            E[j] = mp::mul_lo(a[j], b[0]);
+            E[j + 1] = mp::mul_hi(a[j], b[0]);
+            O[j] = mp::mul_lo(a[j + 1], b[0]);
+            O[j + 1] = mp::mul_hi(a[j + 1], b[0]);
+        }
+#pragma unroll
+        for (int i = 1; i < N; ++i)
+        {
+            if (i & 1)
+            {
+                // odd j -> even column: E[i+j], E[i+j+1]; top pair is fresh
+                E[i + 1] = mp::mad_lo_cc(a[1], b[i], E[i + 1]);
+                E[i + 2] = mp::madc_hi_cc(a[1], b[i], E[i + 2]);
+#pragma unroll
+                for (int j = 3; j < N; j += 2)
+                {
+                    E[i + j] = mp::madc_lo_cc(a[j], b[i], E[i + j]);
+                    E[i + j + 1] = mp::madc_hi_cc(a[j], b[i], E[i + j + 1]);
+                }
+                // even j -> odd column: O[i+j-1], O[i+j]; carry lands in O[i+N-1]
+                O[i - 1] = mp::mad_lo_cc(a[0], b[i], O[i - 1]);
+                O[i] = mp::madc_hi_cc(a[0], b[i], O[i]);
+#pragma unroll
+                for (int j = 2; j < N; j += 2)
+                {
+                    O[i + j - 1] = mp::madc_lo_cc(a[j], b[i], O[i + j - 1]);
+                    O[i + j] = mp::madc_hi_cc(a[j], b[i], O[i + j]);
+                }
+                O[i + N - 1] = mp::addc(O[i + N - 1], 0);
+            }
+            else
+            {
+                // even j -> even column: E[i+j], E[i+j+1]; carry lands in E[i+N]
+                E[i] = mp::mad_lo_cc(a[0], b[i], E[i]);
+                E[i + 1] = mp::madc_hi_cc(a[0], b[i], E[i + 1]);
+#pragma unroll
+                for (int j = 2; j < N; j += 2)
+                {
+                    E[i + j] = mp::madc_lo_cc(a[j], b[i], E[i + j]);
+                    E[i + j + 1] = mp::madc_hi_cc(a[j], b[i], E[i + j + 1]);
+                }
+                E[i + N] = mp::addc(E[i + N], 0);
+                // odd j -> odd column: O[i+j-1], O[i+j]; top pair is fresh
+                O[i] = mp::mad_lo_cc(a[1], b[i], O[i]);
+                O[i + 1] = mp::madc_hi_cc(a[1], b[i], O[i + 1]);
+#pragma unroll
+                for (int j = 3; j < N; j += 2)
+                {
+                    O[i + j - 1] = mp::madc_lo_cc(a[j], b[i], O[i + j - 1]);
+                    O[i + j] = mp::madc_hi_cc(a[j], b[i], O[i + j]);
+                }
+            }
+        }
+        out[0] = E[0];
+        out[1] = mp::add_cc(E[1], O[0]);
+#pragma unroll
+        for (int k = 2; k < 2 * N - 1; ++k) out[k] = mp::addc_cc(E[k], O[k - 1]);
+        out[2 * N - 1] = mp::addc(E[2 * N - 1], O[2 * N - 2]);
+    }
+
+    // acc (L limbs) += x (M limbs, M <= L), carries rippled to the top of acc.
+    template <int L, int M>
+    GZK_HD void acc_add(uint32_t* acc, const uint32_t* x)
+    {
+        acc[0] = mp::add_cc(acc[0], x[0]);
+#pragma unroll
+        for (int k = 1; k < M; ++k) acc[k] = mp::addc_cc(acc[k], x[k]);
+#pragma unroll
+        for (int k = M; k < L; ++k) acc[k] = mp::addc_cc(acc[k], 0);
+    }
+
+    // Montgomery reduction of a wide integer T (N + ROWS limbs, T < modulus *
+    // 2^(32*ROWS)): returns T * 2^(-32*ROWS) mod modulus, fully reduced.  Used
+    // once per accumulated inner product, so it favours clarity over speed.
+    template <typename Cfg, int ROWS>
+    GZK_HD Fe<Cfg> redc_wide(const uint32_t* T_in)
+    {
+        constexpr int N = Cfg::N;
+        constexpr int L = N + ROWS + 1;
+        uint32_t T[L];
+#pragma unroll
+        for (int k = 0; k < L - 1; ++k) T[k] = T_in[k];
+        T[L - 1] = 0;
+#pragma unroll
+        for (int i = 0; i < ROWS; ++i)
+        {
+            const uint32_t m = mp::mul_lo(T[i], Cfg::INV);
+            // low halves
+            T[i] = mp::mad_lo_cc(m, Cfg::mod(0), T[i]);
+#pragma unroll
+            for (int j = 1; j < N; ++j) T[i + j] = mp::madc_lo_cc(m, Cfg::mod(j), T[i + j]);
+#pragma unroll
+            for (int k = i + N; k < L; ++k) T[k] = mp::addc_cc(T[k], 0);
+            // high halves
+            T[i + 1] = mp::mad_hi_cc(m, Cfg::mod(0), T[i + 1]);
+#pragma unroll
+            for (int j = 1; j < N; ++j) T[i + j + 1] = mp::madc_hi_cc(m, Cfg::mod(j), T[i + j + 1]);
+#pragma unroll
+            for (int k = i + N + 1; k < L; ++k) T[k] = mp::addc_cc(T[k], 0);
+        }
+        Fe<Cfg> s;
+#pragma unroll
+        for (int k = 0; k < N; ++k) s.l[k] = T[ROWS + k];
+        return reduce_once(s);
+    }
+
+    using Fr = Fe<FrCfg>;
+    using Fp = Fe<FpCfg>;
+
+    // 2^544 mod r: turns redc_wide<FrCfg, 9>(sum of Montgomery * canonical
+    // products) back into the Montgomery form of the true sum.
+    GZK_HD Fr fr_const_2_544()
+    {
+        constexpr uint32_t c[8] = {0xefe9ec32u, 0x0408b03au, 0x122df55fu, 0xc98a431eu,
+                                   0x8277a7beu, 0xdd74d8f7u, 0x9163e436u, 0x1ef2c2b1u};
+        Fr o;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o.l[i] = c[i];
+        return o;
+    }
+}

@@ -1,0 +1,142 @@
+"""ctypes binding of libgatzk_b200.so (include/gatzk_b200.h).
+
+There is no fallback: if the shared library is absent or no sm_100 GPU is
+usable, construction raises.
+"""
+import ctypes
+import os
+
+import numpy as np
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libgatzk_b200.so")
+
+KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32 = 0, 1, 2, 3
+_KIND_DTYPE = {KIND_FR: (np.uint8, 32), KIND_FR_MONT: (np.uint8, 32), KIND_I64: (np.int64, 1), KIND_U32: (np.uint32, 1)}
+
+_lib = None
+
+
+class GzkError(RuntimeError):
+    def __init__(self, code, message):
+        super().__init__(f"gatzk_b200 error {code}: {message}")
+        self.code = code
+
+
+def load_library():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise RuntimeError(
+                f"{LIB_PATH} is missing: build it with `python -m project_b200.build` (needs nvcc); there is no CPU fallback"
+            )
+        _lib = ctypes.CDLL(LIB_PATH)
+        _lib.gzk_last_error.restype = ctypes.c_char_p
+        _lib.gzk_last_error.argtypes = [ctypes.c_void_p]
+        _lib.gzk_buf_count.restype = ctypes.c_size_t
+        _lib.gzk_buf_count.argtypes = [ctypes.c_void_p]
+        _lib.gzk_buf_kind.argtypes = [ctypes.c_void_p]
+        _lib.gzk_buf_device_ptr.restype = ctypes.c_void_p
+        _lib.gzk_buf_device_ptr.argtypes = [ctypes.c_void_p]
+        _lib.gzk_ctx_stream.restype = ctypes.c_void_p
+        _lib.gzk_ctx_stream.argtypes = [ctypes.c_void_p]
+        _lib.gzk_ctx_destroy.restype = None
+        _lib.gzk_ctx_destroy.argtypes = [ctypes.c_void_p]
+    return _lib
+
+
+def _ptr(a):
+    return None if a is None else a.ctypes.data_as(ctypes.c_void_p)
+
+
+def _sz(v):
+    return ctypes.c_size_t(int(v))
+
+
+def _fr(x):
+    a = np.ascontiguousarray(x, dtype=np.uint8).reshape(-1)
+    assert a.size == 32, "expected one 32-byte field element"
+    return a
+
+
+class Buffer:
+    def __init__(self, backend, handle, kind, count):
+        self.backend, self.handle, self.kind, self.count = backend, handle, kind, count
+
+    def upload(self, host, offset=0):
+        dtype, width = _KIND_DTYPE[self.kind]
+        a = np.ascontiguousarray(host, dtype=dtype)
+        count = a.size // width
+        self.backend._check(self.backend.lib.gzk_buf_upload(self.backend.ctx, self.handle, _sz(offset), _ptr(a), _sz(count)))
+        return self
+
+    def download(self, offset=0, count=None):
+        dtype, width = _KIND_DTYPE[self.kind]
+        count = self.count - offset if count is None else count
+        out = np.zeros((count, width) if width > 1 else (count,), dtype=dtype)
+        self.backend._check(self.backend.lib.gzk_buf_download(self.backend.ctx, self.handle, _sz(offset), _ptr(out), _sz(count)))
+        return out
+
+    @property
+    def device_ptr(self):
+        return self.backend.lib.gzk_buf_device_ptr(self.handle)
+
+    def free(self):
+        if self.handle is not None:
+            self.backend._check(self.backend.lib.gzk_buf_free(self.backend.ctx, self.handle))
+            self.handle = None
+
+
+class Backend:
+    """One context on one GPU; thin, argument-for-argument view of the C ABI."""
+
+    def __init__(self, device=0):
+        self.lib = load_library()
+        ctx = ctypes.c_void_p()
+        rc = self.lib.gzk_ctx_create(int(device), ctypes.byref(ctx))
+        if rc != 0:
+            raise GzkError(rc, "gzk_ctx_create failed: no usable sm_100 CUDA device (there is no CPU fallback)")
+        self.ctx = ctx
+
+    def close(self):
+        if self.ctx:
+            self.lib.gzk_ctx_destroy(self.ctx)
+            self.ctx = None
+
+    def _check(self, rc):
+        if rc != 0:
+            raise GzkError(rc, self.lib.gzk_last_error(self.ctx).decode())
+
+    def synchronize(self):
+        self._check(self.lib.gzk_ctx_synchronize(self.ctx))
+
+    @property
+    def stream(self):
+        return self.lib.gzk_ctx_stream(self.ctx)
+
+    def alloc(self, kind, count):
+        h = ctypes.c_void_p()
+        self._check(self.lib.gzk_buf_alloc(self.ctx, int(kind), _sz(count), ctypes.byref(h)))
+        return Buffer(self, h, kind, count)
+
+    def upload(self, host, kind=KIND_FR):
+        dtype, width = _KIND_DTYPE[kind]
+        a = np.ascontiguousarray(host, dtype=dtype)
+        return self.alloc(kind, a.size // width).upload(a)
+
+    def root_of_unity(self, size):
+        out = np.zeros(32, dtype=np.uint8)
+        self._check(self.lib.gzk_root_of_unity(self.ctx, ctypes.c_uint64(size), _ptr(out)))
+        return out
+
+    def bary_weights(self, log2n, x, out=None):
+        out = out or self.alloc(KIND_FR_MONT, 1 << log2n)
+        self._check(self.lib.gzk_bary_weights(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), out.handle))
+        return out
+
+    def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
+        handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
+        rot = np.ascontiguousarray(rotations, dtype=np.uint64)
+        out = np.zeros((rot.size, len(cols), 32), dtype=np.uint8)
+        self._check(self.lib.gzk_eval_batch(self.ctx, handles, _sz(len(cols)), _sz(length), ctypes.c_uint(log2n), weights.handle, _ptr(rot), _sz(rot.size), _ptr(out)))
+        return out
