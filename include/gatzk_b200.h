@@ -56,6 +56,16 @@ int gzk_ctx_synchronize(gzk_ctx* ctx);
 /* the CUDA stream (cudaStream_t) all work of this context is issued on */
 void* gzk_ctx_stream(gzk_ctx* ctx);
 
+/* ---- measurement ---------------------------------------------------------------
+ * Per kernel family: number of launches since the last reset and, while timing is
+ * enabled, the summed CUDA-event duration on the context stream.  Replaces the
+ * steady_clock stage metrics of RunMetrics (include/gatzk/protocol/proof.hpp:119-272)
+ * for device work. */
+int gzk_timing_enable(gzk_ctx* ctx, int on);
+int gzk_timing_reset(gzk_ctx* ctx);
+int gzk_timing_family_count(gzk_ctx* ctx);
+int gzk_timing_get(gzk_ctx* ctx, int index, const char** name, uint64_t* launches, double* total_ms);
+
 /* ---- device buffers -----------------------------------------------------------
  * Replace the host std::vector<FieldElement> column storage of
  * Polynomial::from_evaluations (src/algebra/polynomial.cpp:364-379) and the

@@ -12,6 +12,7 @@
 // thrown (message retrievable with ora_last_error).
 
 #include <algorithm>
+#include <chrono>
 #include <cmath>
 #include <cstdint>
 #include <cstring>
@@ -774,6 +775,119 @@ extern "C"
                 const Fr hi = Fr::from_le_bytes(table + 32 * (2 * i + 1));
                 (lo + r * (hi - lo)).to_le_bytes(out + 32 * i);
             }
+        });
+    }
+
+    // ---- CPU baseline timing ---------------------------------------------------------
+    // Times the reference's loops on values held in native (Montgomery) form, as
+    // mcl::Fr holds them, so that no wire-format conversion is charged to the CPU:
+    //  - packed evaluation: eval_backend.cpp:309-444 (K columns x n rows x P
+    //    rotations, chunked over `threads` like its std::async fan-out);
+    //  - barycentric weights: polynomial.cpp:179-315 (chunk-parallel batch inversion).
+    // Inputs are seeded pseudo-random field elements generated before the clock starts.
+    int ora_bench_eval(std::size_t k_count, std::size_t n, std::size_t p_count, std::size_t threads,
+                       std::uint64_t seed, double* seconds, Bytes* checksum_out)
+    {
+        return guarded([&] {
+            if (n == 0 || (n & (n - 1)) != 0) throw std::runtime_error("domain size must be a non-zero power of two");
+            std::vector<Fr> values(k_count * n), w(n);
+            std::uint64_t state = seed * 0x9E3779B97F4A7C15ULL + 1;
+            auto next = [&]() {
+                state ^= state << 13;
+                state ^= state >> 7;
+                state ^= state << 17;
+                return state;
+            };
+            auto rnd = [&]() {
+                Fr f;
+                for (auto& limb : f.v.w) limb = next();
+                f.v.w[3] >>= 2;  // < 2^254 < r: a valid residue
+                return f;
+            };
+            for (auto& v : values) v = rnd();  // interleaved [c*K + k], as the reference packs them
+            for (auto& v : w) v = rnd();
+            const std::size_t mask = n - 1;
+            const std::size_t used = std::max<std::size_t>(1, std::min(threads, n / 512 == 0 ? 1 : n / 512));
+            std::vector<std::vector<Fr>> partials(used, std::vector<Fr>(p_count * k_count, Fr::zero()));
+            const auto t0 = std::chrono::steady_clock::now();
+            parallel_chunks(n, used, [&](std::size_t t, std::size_t begin, std::size_t end) {
+                auto& partial = partials[t];
+                for (std::size_t column = begin; column < end; ++column)
+                {
+                    const Fr& weight = w[column];
+                    for (std::size_t p = 0; p < p_count; ++p)
+                    {
+                        const std::size_t rotated = (column + p) & mask;
+                        const Fr* row = &values[rotated * k_count];
+                        Fr* out_row = &partial[p * k_count];
+                        for (std::size_t k = 0; k < k_count; ++k) out_row[k] += row[k] * weight;
+                    }
+                }
+            });
+            std::vector<Fr> total(p_count * k_count, Fr::zero());
+            for (const auto& partial : partials)
+                for (std::size_t i = 0; i < total.size(); ++i) total[i] += partial[i];
+            const auto t1 = std::chrono::steady_clock::now();
+            *seconds = std::chrono::duration<double>(t1 - t0).count();
+            Fr sum = Fr::zero();
+            for (const auto& v : total) sum += v;
+            if (checksum_out != nullptr) sum.to_le_bytes(checksum_out);
+        });
+    }
+
+    int ora_bench_bary(std::size_t n, std::size_t threads, std::uint64_t seed, double* seconds, Bytes* checksum_out)
+    {
+        return guarded([&] {
+            const Fr x = Fr::from_u64(seed * 2654435761ULL + 12345);
+            const Fr omega = root_of_unity(n);
+            const Fr inv_size = Fr::from_u64(n).inv();
+            std::vector<Fr> points(n);
+            {
+                Fr p = Fr::one();
+                for (std::size_t i = 0; i < n; ++i)
+                {
+                    points[i] = p;
+                    p *= omega;
+                }
+            }
+            const auto t0 = std::chrono::steady_clock::now();
+            const std::size_t tasks = std::max<std::size_t>(1, std::min<std::size_t>(threads, (n + (1ULL << 20) - 1) >> 20));
+            std::vector<Fr> denominators(n), prefix(n), weights(n), chunk_products(tasks, Fr::one());
+            const Fr zero_eval = x.pow(static_cast<u64>(n)) - Fr::one();
+            parallel_chunks(n, tasks, [&](std::size_t t, std::size_t begin, std::size_t end) {
+                Fr acc = Fr::one();
+                for (std::size_t i = begin; i < end; ++i)
+                {
+                    denominators[i] = x - points[i];
+                    prefix[i] = acc;
+                    acc *= denominators[i];
+                }
+                chunk_products[t] = acc;
+            });
+            std::vector<Fr> cross_prefix(tasks + 1, Fr::one());
+            for (std::size_t c = 0; c < tasks; ++c) cross_prefix[c + 1] = cross_prefix[c] * chunk_products[c];
+            const Fr global_inv = cross_prefix[tasks].inv();
+            std::vector<Fr> outer(tasks);
+            Fr cross_suffix = Fr::one();
+            for (std::size_t c = tasks; c-- > 0;)
+            {
+                outer[c] = global_inv * cross_prefix[c] * cross_suffix;
+                cross_suffix *= chunk_products[c];
+            }
+            parallel_chunks(n, tasks, [&](std::size_t t, std::size_t begin, std::size_t end) {
+                Fr running = Fr::one();
+                for (std::size_t i = end; i-- > begin;)
+                {
+                    const Fr inv_d = outer[t] * prefix[i] * running;
+                    weights[i] = zero_eval * (points[i] * inv_size) * inv_d;
+                    running *= denominators[i];
+                }
+            });
+            const auto t1 = std::chrono::steady_clock::now();
+            *seconds = std::chrono::duration<double>(t1 - t0).count();
+            Fr sum = Fr::zero();
+            for (const auto& v : weights) sum += v;
+            if (checksum_out != nullptr) sum.to_le_bytes(checksum_out);
         });
     }
 

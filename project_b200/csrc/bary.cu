@@ -199,6 +199,7 @@ namespace gzk
     int launch_batch_invert_single_cta(gzk_ctx* ctx, Fr* values, Fr* tmp, uint32_t count)
     {
         if (count == 0) return GZK_OK;
+        LaunchScope scope(ctx, "batch_invert_cta");
         batch_invert_single_cta_kernel<<<1, kInvThreads, 0, ctx->stream>>>(values, tmp, count);
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return GZK_OK;
@@ -241,10 +242,16 @@ extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_by
     Fr* products = static_cast<Fr*>(scratch);
     Fr* tmp = products + blocks;
     GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
-    bary_products_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, ctx->d_status);
+    {
+        LaunchScope scope(ctx, "bary_products");
+        bary_products_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, ctx->d_status);
+    }
     GZK_CUDA_TRY(ctx, cudaGetLastError());
     if ((rc = launch_batch_invert_single_cta(ctx, products, tmp, blocks)) != GZK_OK) return rc;
-    bary_finish_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, static_cast<Fr*>(out->dptr));
+    {
+        LaunchScope scope(ctx, "bary_finish");
+        bary_finish_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, static_cast<Fr*>(out->dptr));
+    }
     GZK_CUDA_TRY(ctx, cudaGetLastError());
     int status = 0;
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));

@@ -46,6 +46,22 @@ namespace gzk
     };
 }
 
+namespace gzk
+{
+    // CUDA-event timing of kernel families, switched on by gzk_timing_enable.
+    struct TimedLaunch
+    {
+        int family;
+        cudaEvent_t start, stop;
+    };
+    struct FamilyStat
+    {
+        std::string name;
+        uint64_t launches = 0;
+        double total_ms = 0.0;
+    };
+}
+
 struct gzk_ctx
 {
     int device = 0;
@@ -57,6 +73,10 @@ struct gzk_ctx
     void* pinned = nullptr;  // small pinned staging area for results
     size_t pinned_bytes = 0;
     int* d_status = nullptr;  // device-side status word (zero-denominator flags etc.)
+    bool timing = false;
+    std::vector<gzk::FamilyStat> families;
+    std::vector<gzk::TimedLaunch> pending;
+    std::vector<cudaEvent_t> event_pool;
 };
 
 namespace gzk
@@ -66,6 +86,24 @@ namespace gzk
     int ensure_scratch(gzk_ctx* ctx, int slot, size_t bytes, void** out);
     int ensure_pinned(gzk_ctx* ctx, size_t bytes, void** out);
     int get_domain(gzk_ctx* ctx, unsigned log2n, const DomainTables** out);
+
+    // Brackets the kernel launches issued during its lifetime with CUDA events on
+    // the context stream when timing is on; every launch site uses one, so the
+    // per-family launch counts are maintained even when timing is off.
+    class LaunchScope
+    {
+    public:
+        LaunchScope(gzk_ctx* ctx, const char* family, unsigned launches = 1);
+        ~LaunchScope();
+        LaunchScope(const LaunchScope&) = delete;
+        LaunchScope& operator=(const LaunchScope&) = delete;
+
+    private:
+        gzk_ctx* ctx_;
+        int family_;
+        cudaEvent_t start_ = nullptr;
+    };
+    void timing_collect(gzk_ctx* ctx);
 
     // Host-side scalar helpers (same arithmetic, emulated carry flag).
     Fr host_fr_from_bytes(const uint8_t* bytes, bool* canonical_ok);

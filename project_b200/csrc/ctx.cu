@@ -56,6 +56,66 @@ namespace gzk
         return GZK_OK;
     }
 
+    static int family_index(gzk_ctx* ctx, const char* family)
+    {
+        for (size_t i = 0; i < ctx->families.size(); ++i)
+            if (ctx->families[i].name == family) return static_cast<int>(i);
+        FamilyStat st;
+        st.name = family;
+        ctx->families.push_back(st);
+        return static_cast<int>(ctx->families.size() - 1);
+    }
+
+    static cudaEvent_t take_event(gzk_ctx* ctx)
+    {
+        if (!ctx->event_pool.empty())
+        {
+            cudaEvent_t e = ctx->event_pool.back();
+            ctx->event_pool.pop_back();
+            return e;
+        }
+        cudaEvent_t e = nullptr;
+        cudaEventCreate(&e);
+        return e;
+    }
+
+    LaunchScope::LaunchScope(gzk_ctx* ctx, const char* family, unsigned launches) : ctx_(ctx), family_(family_index(ctx, family))
+    {
+        ctx_->families[family_].launches += launches;
+        if (ctx_->timing)
+        {
+            start_ = take_event(ctx_);
+            cudaEventRecord(start_, ctx_->stream);
+        }
+    }
+
+    LaunchScope::~LaunchScope()
+    {
+        if (start_ != nullptr)
+        {
+            TimedLaunch t;
+            t.family = family_;
+            t.start = start_;
+            t.stop = take_event(ctx_);
+            cudaEventRecord(t.stop, ctx_->stream);
+            ctx_->pending.push_back(t);
+        }
+    }
+
+    void timing_collect(gzk_ctx* ctx)
+    {
+        if (ctx->pending.empty()) return;
+        cudaStreamSynchronize(ctx->stream);
+        for (auto& t : ctx->pending)
+        {
+            float ms = 0.f;
+            if (cudaEventElapsedTime(&ms, t.start, t.stop) == cudaSuccess) ctx->families[t.family].total_ms += ms;
+            ctx->event_pool.push_back(t.start);
+            ctx->event_pool.push_back(t.stop);
+        }
+        ctx->pending.clear();
+    }
+
     Fr host_fr_from_bytes(const uint8_t* bytes, bool* canonical_ok)
     {
         Fr v;
@@ -219,6 +279,8 @@ extern "C"
             if (s.ptr != nullptr) cudaFree(s.ptr);
         if (ctx->pinned != nullptr) cudaFreeHost(ctx->pinned);
         if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
+        timing_collect(ctx);
+        for (auto e : ctx->event_pool) cudaEventDestroy(e);
         cudaStreamDestroy(ctx->stream);
         delete ctx;
     }
@@ -233,6 +295,39 @@ extern "C"
     }
 
     void* gzk_ctx_stream(gzk_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
+
+    int gzk_timing_enable(gzk_ctx* ctx, int on)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        timing_collect(ctx);
+        ctx->timing = on != 0;
+        return GZK_OK;
+    }
+
+    int gzk_timing_reset(gzk_ctx* ctx)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        timing_collect(ctx);
+        for (auto& f : ctx->families)
+        {
+            f.launches = 0;
+            f.total_ms = 0.0;
+        }
+        return GZK_OK;
+    }
+
+    int gzk_timing_family_count(gzk_ctx* ctx) { return ctx == nullptr ? 0 : static_cast<int>(ctx->families.size()); }
+
+    int gzk_timing_get(gzk_ctx* ctx, int index, const char** name, uint64_t* launches, double* total_ms)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        timing_collect(ctx);
+        if (index < 0 || index >= static_cast<int>(ctx->families.size())) return fail(ctx, GZK_E_INVALID, "timing: no such family");
+        if (name != nullptr) *name = ctx->families[index].name.c_str();
+        if (launches != nullptr) *launches = ctx->families[index].launches;
+        if (total_ms != nullptr) *total_ms = ctx->families[index].total_ms;
+        return GZK_OK;
+    }
 
     int gzk_buf_alloc(gzk_ctx* ctx, int kind, size_t count, gzk_buf** out)
     {
@@ -284,6 +379,7 @@ extern "C"
         {
             Fr* p = reinterpret_cast<Fr*>(dst);
             const unsigned blocks = static_cast<unsigned>((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+            LaunchScope scope(ctx, "convert");
             convert_kernel<<<blocks, 256, 0, ctx->stream>>>(p, p, count, 1);
             GZK_CUDA_TRY(ctx, cudaGetLastError());
         }
@@ -308,7 +404,10 @@ extern "C"
             {
                 const size_t cur = count - done < chunk ? count - done : chunk;
                 const unsigned blocks = static_cast<unsigned>((cur + 255) / 256 < 4096 ? (cur + 255) / 256 : 4096);
-                convert_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const Fr*>(src) + done, static_cast<Fr*>(tmp), cur, 0);
+                {
+                    LaunchScope scope(ctx, "convert");
+                    convert_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const Fr*>(src) + done, static_cast<Fr*>(tmp), cur, 0);
+                }
                 GZK_CUDA_TRY(ctx, cudaGetLastError());
                 GZK_CUDA_TRY(ctx, cudaMemcpyAsync(static_cast<char*>(host) + done * 32, tmp, cur * 32, cudaMemcpyDeviceToHost, ctx->stream));
                 GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));

@@ -241,14 +241,20 @@ extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count
         uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
         const uint64_t max_blocks = static_cast<uint64_t>(ctx->sm_count) * 2;
         if (blocks > max_blocks) blocks = max_blocks;
-        if (p_now == 2)
-            eval_partial_kernel<2><<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(args);
-        else
-            eval_partial_kernel<1><<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(args);
+        {
+            LaunchScope scope(ctx, p_now == 2 ? "eval_partial_p2" : "eval_partial_p1");
+            if (p_now == 2)
+                eval_partial_kernel<2><<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(args);
+            else
+                eval_partial_kernel<1><<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(args);
+        }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         const uint32_t outs = p_now * static_cast<uint32_t>(k_count);
-        eval_finish_kernel<<<(outs + 127) / 128, 128, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
-                                                                       static_cast<uint32_t>(k_count), d_out + p0 * k_count);
+        {
+            LaunchScope scope(ctx, "eval_finish");
+            eval_finish_kernel<<<(outs + 127) / 128, 128, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
+                                                                           static_cast<uint32_t>(k_count), d_out + p0 * k_count);
+        }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
     }
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, d_out, p_count * k_count * 32, cudaMemcpyDeviceToHost, ctx->stream));

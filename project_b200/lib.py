@@ -42,6 +42,7 @@ def load_library():
         _lib.gzk_ctx_stream.argtypes = [ctypes.c_void_p]
         _lib.gzk_ctx_destroy.restype = None
         _lib.gzk_ctx_destroy.argtypes = [ctypes.c_void_p]
+        _lib.gzk_timing_family_count.argtypes = [ctypes.c_void_p]
     return _lib
 
 
@@ -109,6 +110,23 @@ class Backend:
 
     def synchronize(self):
         self._check(self.lib.gzk_ctx_synchronize(self.ctx))
+
+    def timing_enable(self, on=True):
+        self._check(self.lib.gzk_timing_enable(self.ctx, int(bool(on))))
+
+    def timing_reset(self):
+        self._check(self.lib.gzk_timing_reset(self.ctx))
+
+    def timing_report(self):
+        """{family: (launches, total_ms)} since the last reset."""
+        out = {}
+        for i in range(self.lib.gzk_timing_family_count(self.ctx)):
+            name = ctypes.c_char_p()
+            launches = ctypes.c_uint64()
+            ms = ctypes.c_double()
+            self._check(self.lib.gzk_timing_get(self.ctx, i, ctypes.byref(name), ctypes.byref(launches), ctypes.byref(ms)))
+            out[name.value.decode()] = (int(launches.value), float(ms.value))
+        return out
 
     @property
     def stream(self):

@@ -319,3 +319,18 @@ def fold(table, challenge):
 
 def fnv1a(data: bytes):
     return int(lib().ora_fnv1a(data, _sz(len(data))))
+
+
+def bench_eval(k, n, p_count, threads, seed=1):
+    """Seconds the reference's packed-evaluation loop takes on native-form values."""
+    sec = ctypes.c_double()
+    chk = np.zeros(32, dtype=np.uint8)
+    _check(lib().ora_bench_eval(_sz(k), _sz(n), _sz(p_count), _sz(threads), ctypes.c_uint64(seed), ctypes.byref(sec), _p(chk)))
+    return sec.value, chk
+
+
+def bench_bary(n, threads, seed=1):
+    sec = ctypes.c_double()
+    chk = np.zeros(32, dtype=np.uint8)
+    _check(lib().ora_bench_bary(_sz(n), _sz(threads), ctypes.c_uint64(seed), ctypes.byref(sec), _p(chk)))
+    return sec.value, chk
