@@ -108,6 +108,33 @@ int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf*
 int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                    const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host);
 
+/* ---- packed evaluation without any allocation ------------------------------------
+ * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that
+ * cannot call cudaMalloc while they run: a prover host that has already given all
+ * HBM to its own column pool (an allocation would fail), or one that cannot accept
+ * the device-wide synchronisation an allocation implies in the middle of a proof.
+ * Nothing is allocated or freed here, by CUDA or by any library: the work area is a
+ * fixed ~2.1 MiB array inside the library image, resident on every GPU that loads
+ * the library until the process exits.
+ *  - limits: k_count <= 256 columns and p_count <= 2 rotations per call; larger
+ *    requests are rejected with GZK_E_INVALID and a message in `err`.
+ *  - col_ptrs / col_kinds: HOST arrays of k_count DEVICE pointers and their
+ *    GZK_KIND_*; weights_mont: device pointer to n Montgomery-form weights (what
+ *    gzk_bary_weights writes); out_device: device pointer to p_count*k_count*32
+ *    bytes, receives canonical Fr values [p][k].  Work is queued on `stream`
+ *    (a cudaStream_t; NULL = default stream) on `device`, which is made current;
+ *    the results are complete once the caller has synchronised that stream.
+ *  - the first call on each device also looks up the device address of the array
+ *    and the SM count; make that first call before starting any stream capture.
+ *  - all calls on a device share the one array, which keeps whatever the previous
+ *    call left in it.  Every slot a call reads it has written itself first, so
+ *    nothing needs clearing, but two calls that overlap on the GPU (different
+ *    streams, or different host threads) race on the array: serialise them.
+ *  - err / err_cap: optional buffer for a failure message. */
+int gzk_eval_batch_static(int device, void* stream, const void* const* col_ptrs, const int* col_kinds, size_t k_count,
+                          size_t len, unsigned log2n, const void* weights_mont, const uint64_t* rotations,
+                          size_t p_count, void* out_device, char* err, size_t err_cap);
+
 #ifdef __cplusplus
 }
 #endif

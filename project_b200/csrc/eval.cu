@@ -262,3 +262,133 @@ extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count
     std::memcpy(out_host, h_out, p_count * k_count * 32);
     return GZK_OK;
 }
+
+
+// ---------------------------------------------------------------------------------
+// Packed evaluation for callers that must not allocate.
+//
+// gzk_eval_batch obtains its work area (the per-tile partial sums and the column
+// pointer table) from the context, which grows it with cudaMalloc on demand.  Some
+// users of this library cannot tolerate that: a prover host that has handed all of
+// the GPU's memory to its own column pool has nothing left for cudaMalloc to give,
+// and a cudaMalloc in the middle of a proof synchronises the whole device and
+// stalls the other streams of the process.  For them this one entry point keeps
+// its work area in a fixed array that is part of the loaded library image.
+namespace
+{
+    constexpr size_t kStaticMaxColumns = 256;
+    constexpr size_t kStaticMaxRotations = 2;
+    constexpr size_t kStaticMaxTiles = 64;
+    constexpr size_t kStaticTableBytes = kStaticMaxColumns * (sizeof(void*) + sizeof(int));  // 3 KiB
+    constexpr size_t kStaticPartialOffset = 4096;
+    constexpr size_t kStaticPartialBytes = kStaticMaxTiles * kStaticMaxRotations * kStaticMaxColumns * gzk::kAccLimbs * sizeof(uint32_t);
+    constexpr size_t kStaticBytes = kStaticPartialOffset + kStaticPartialBytes;  // about 2.1 MiB per GPU
+    static_assert(kStaticTableBytes <= kStaticPartialOffset, "pointer table must fit before the partial sums");
+
+    // Held by every GPU that loads the library, until the process exits.
+    static __device__ __align__(256) unsigned char g_eval_static_scratch[kStaticBytes];
+
+    // In host code `g_eval_static_scratch` is only a handle for the runtime, not an
+    // address a kernel can use; the device address is looked up once per device.
+    constexpr int kMaxDevices = 64;
+    void* g_static_addr[kMaxDevices] = {};
+    int g_static_sms[kMaxDevices] = {};
+
+    int static_fail(char* err, size_t cap, int code, const char* message)
+    {
+        if (err != nullptr && cap > 0)
+        {
+            std::strncpy(err, message, cap - 1);
+            err[cap - 1] = '\0';
+        }
+        return code;
+    }
+}
+
+extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const* col_ptrs, const int* col_kinds,
+                                     size_t k_count, size_t len, unsigned log2n, const void* weights_mont,
+                                     const uint64_t* rotations, size_t p_count, void* out_device, char* err,
+                                     size_t err_cap)
+{
+    if (k_count == 0 || p_count == 0) return GZK_OK;
+    if (col_ptrs == nullptr || col_kinds == nullptr || weights_mont == nullptr || rotations == nullptr || out_device == nullptr)
+        return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: null argument");
+    if (device < 0 || device >= kMaxDevices) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: device index out of range");
+    if (k_count > kStaticMaxColumns)
+        return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: more than 256 columns; split the batch or use gzk_eval_batch");
+    if (p_count > kStaticMaxRotations)
+        return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: more than 2 rotations; split the call or use gzk_eval_batch");
+    if (log2n > 32) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: domain too large");
+    const uint64_t n = 1ULL << log2n;
+    if (len > n) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: len exceeds the domain size");
+    for (size_t p = 0; p < p_count; ++p)
+        if (rotations[p] >= n) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: rotation out of range");
+    for (size_t k = 0; k < k_count; ++k)
+    {
+        if (col_ptrs[k] == nullptr) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: null column pointer");
+        if (col_kinds[k] < GZK_KIND_FR || col_kinds[k] > GZK_KIND_U32)
+            return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: unknown column kind");
+    }
+    if (cudaSetDevice(device) != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: cudaSetDevice failed");
+    if (g_static_addr[device] == nullptr)
+    {
+        // one-time set-up for this device, with the device current
+        void* addr = nullptr;
+        if (cudaGetSymbolAddress(&addr, g_eval_static_scratch) != cudaSuccess || addr == nullptr)
+            return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: cudaGetSymbolAddress failed");
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+            return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: cannot query the SM count");
+        g_static_sms[device] = sms;
+        g_static_addr[device] = addr;
+    }
+    unsigned char* scratch = static_cast<unsigned char*>(g_static_addr[device]);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+
+    // same tile plan as gzk_eval_batch, capped so the partial sums fit the array
+    const uint64_t warps_total = static_cast<uint64_t>(g_static_sms[device]) * 2 * (kThreads / 32);
+    uint64_t want_tiles = (8 * warps_total + k_count - 1) / k_count;
+    uint64_t max_tiles = (len + 255) / 256;
+    if (max_tiles == 0) max_tiles = 1;
+    if (want_tiles > kStaticMaxTiles) want_tiles = kStaticMaxTiles;
+    if (want_tiles > max_tiles) want_tiles = max_tiles;
+    if (want_tiles == 0) want_tiles = 1;
+    uint64_t tile_rows = (len + want_tiles - 1) / want_tiles;
+    tile_rows = (tile_rows + 31) & ~31ULL;
+    if (tile_rows == 0) tile_rows = 32;
+    const uint32_t tiles = len == 0 ? 1 : static_cast<uint32_t>((len + tile_rows - 1) / tile_rows);
+
+    // pointer table: built on the stack, copied into the head of the array
+    unsigned char table[kStaticTableBytes];
+    std::memcpy(table, col_ptrs, k_count * sizeof(void*));
+    std::memcpy(table + kStaticMaxColumns * sizeof(void*), col_kinds, k_count * sizeof(int));
+    if (cudaMemcpyAsync(scratch, table, kStaticTableBytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
+        return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: copying the column table failed");
+
+    EvalArgs args;
+    args.cols = reinterpret_cast<const void* const*>(scratch);
+    args.kinds = reinterpret_cast<const int*>(scratch + kStaticMaxColumns * sizeof(void*));
+    args.weights = static_cast<const Fr*>(weights_mont);
+    args.len = len;
+    args.mask = n - 1;
+    args.tile_rows = tile_rows;
+    args.tiles = tiles;
+    args.k_count = static_cast<uint32_t>(k_count);
+    args.rot[0] = rotations[0];
+    args.rot[1] = p_count == 2 ? rotations[1] : 0;
+    args.partial = reinterpret_cast<uint32_t*>(scratch + kStaticPartialOffset);
+    const uint64_t units = static_cast<uint64_t>(tiles) * k_count;
+    uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
+    const uint64_t max_blocks = static_cast<uint64_t>(g_static_sms[device]) * 2;
+    if (blocks > max_blocks) blocks = max_blocks;
+    if (p_count == 2)
+        eval_partial_kernel<2><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(args);
+    else
+        eval_partial_kernel<1><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(args);
+    if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
+    const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
+    eval_finish_kernel<<<(outs + 127) / 128, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
+                                                         static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device));
+    if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
+    return GZK_OK;
+}

@@ -158,3 +158,19 @@ class Backend:
         out = np.zeros((rot.size, len(cols), 32), dtype=np.uint8)
         self._check(self.lib.gzk_eval_batch(self.ctx, handles, _sz(len(cols)), _sz(length), ctypes.c_uint(log2n), weights.handle, _ptr(rot), _sz(rot.size), _ptr(out)))
         return out
+
+
+def eval_batch_static(device, stream, col_ptrs, col_kinds, length, log2n, weights_ptr, rotations, out_ptr):
+    """gzk_eval_batch_static: the allocation-free variant of packed evaluation.  All
+    pointers are raw device addresses (ints); results land in `out_ptr` once the
+    caller has synchronised `stream`.  Raises GzkError with the library's message."""
+    lib = load_library()
+    k = len(col_ptrs)
+    ptrs = (ctypes.c_void_p * k)(*col_ptrs)
+    kinds = (ctypes.c_int * k)(*col_kinds)
+    rot = np.ascontiguousarray(rotations, dtype=np.uint64)
+    err = ctypes.create_string_buffer(256)
+    rc = lib.gzk_eval_batch_static(int(device), ctypes.c_void_p(stream), ptrs, kinds, _sz(k), _sz(length), ctypes.c_uint(log2n),
+                                   ctypes.c_void_p(weights_ptr), _ptr(rot), _sz(rot.size), ctypes.c_void_p(out_ptr), err, _sz(256))
+    if rc != 0:
+        raise GzkError(rc, err.value.decode())
