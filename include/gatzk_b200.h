@@ -66,6 +66,11 @@ int gzk_timing_reset(gzk_ctx* ctx);
 int gzk_timing_family_count(gzk_ctx* ctx);
 int gzk_timing_get(gzk_ctx* ctx, int index, const char** name, uint64_t* launches, double* total_ms);
 
+/* Integer-pipe ceiling for the roofline of the inner-product kernels: 8x8-limb
+ * multiply-accumulates per second over the whole GPU on register operands, with
+ * 1 or 2 independent accumulators per lane.  No reference counterpart. */
+int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, double* products_per_second);
+
 /* ---- device buffers -----------------------------------------------------------
  * Replace the host std::vector<FieldElement> column storage of
  * Polynomial::from_evaluations (src/algebra/polynomial.cpp:364-379) and the

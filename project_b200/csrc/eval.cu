@@ -25,7 +25,7 @@ namespace gzk
     namespace
     {
         constexpr int kAccLimbs = 17;
-        constexpr int kThreads = 256;
+        constexpr int kThreads = 128;
 
         struct EvalArgs
         {
@@ -39,35 +39,93 @@ namespace gzk
             uint32_t k_count;
             uint64_t rot[2];
             uint32_t* partial;        // [tile][p][k][17]
+            int* status;              // raised when a bounded wait gives up
         };
 
-        __device__ __forceinline__ Fr load_column_value(const void* col, int kind, uint64_t c)
+        // ---- per-warp TMA ring -------------------------------------------------------
+        // Column values are read exactly once, so they bypass L1 entirely: lane 0 of
+        // each warp streams 4 KiB chunks (128 rows) of the column into a private
+        // shared-memory ring with cp.async.bulk, kStages chunks ahead of the
+        // arithmetic, and the warp waits on the chunk's mbarrier.  That keeps
+        // kStages x 4 KiB per warp in flight towards HBM at no register cost.  Every
+        // wait is bounded; a wait that gives up raises the status word and the
+        // kernel returns.
+        constexpr int kStages = 4;
+        constexpr int kChunkRows = 128;
+        constexpr int kChunkBytes = kChunkRows * 32;
+        constexpr int kWarps = kThreads / 32;
+        constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kStages * kChunkBytes;
+        constexpr size_t kSmemBytes = kRingBytes + static_cast<size_t>(kWarps) * kStages * sizeof(uint64_t);
+        constexpr uint32_t kWaitLimit = 1u << 22;
+
+        __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+        __device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
         {
-            if (kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT) return load_fr(static_cast<const Fr*>(col) + c);
-            Fr f = Fr::zero();
-            if (kind == GZK_KIND_U32)
-            {
-                f.l[0] = __ldg(static_cast<const uint32_t*>(col) + c);
-                return f;
-            }
-            // I64: FieldElement::from_signed — negative values are r - |v|
-            const long long v = __ldg(static_cast<const long long*>(col) + c);
-            const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
-            f.l[0] = static_cast<uint32_t>(mag);
-            f.l[1] = static_cast<uint32_t>(mag >> 32);
-            return v < 0 ? sub(Fr::zero(), f) : f;
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+        }
+        __device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+        {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+        }
+        __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar)
+        {
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                         "l"(src), "r"(bytes), "r"(bar)
+                         : "memory");
+        }
+        __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
+        {
+            uint32_t done;
+            asm volatile(
+                "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                : "=r"(done)
+                : "r"(bar), "r"(parity)
+                : "memory");
+            return done != 0;
+        }
+        // Bounded wait: false when the limit ran out.
+        __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+        {
+            for (uint32_t spin = 0; spin < kWaitLimit; ++spin)
+                if (mbar_try_wait(bar, parity)) return true;
+            return false;
+        }
+        __device__ __forceinline__ Fr load_fr_shared(const unsigned char* p)
+        {
+            const uint4* q = reinterpret_cast<const uint4*>(p);
+            const uint4 a = q[0];
+            const uint4 b = q[1];
+            Fr o;
+            o.l[0] = a.x; o.l[1] = a.y; o.l[2] = a.z; o.l[3] = a.w;
+            o.l[4] = b.x; o.l[5] = b.y; o.l[6] = b.z; o.l[7] = b.w;
+            return o;
         }
 
         template <int P>
         __global__ void __launch_bounds__(kThreads) eval_partial_kernel(EvalArgs a)
         {
+            extern __shared__ __align__(128) unsigned char smem[];
             const uint32_t lane = threadIdx.x & 31;
+            const uint32_t warp_in_cta = threadIdx.x >> 5;
+            unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * kStages * kChunkBytes;
+            uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRingBytes) + warp_in_cta * kStages;
+            if (lane == 0)
+            {
+#pragma unroll
+                for (int st = 0; st < kStages; ++st) mbar_init(smem_u32(bars + st), 1);
+                asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
+            __syncwarp();
+
             const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
             const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
             const uint64_t units = static_cast<uint64_t>(a.tiles) * a.k_count;
             const uint64_t per_warp = (units + warps - 1) / warps;
             const uint64_t u_begin = warp * per_warp;
             const uint64_t u_end = u_begin + per_warp < units ? u_begin + per_warp : units;
+            uint32_t ring_pos = 0;  // chunks this warp has pushed through the ring so far
 
             for (uint64_t u = u_begin; u < u_end; ++u)
             {
@@ -78,44 +136,160 @@ namespace gzk
                 const uint64_t c_begin = static_cast<uint64_t>(tile) * a.tile_rows;
                 const uint64_t c_end = c_begin + a.tile_rows < a.len ? c_begin + a.tile_rows : a.len;
 
-                uint32_t acc[P][kAccLimbs];
+                WideAcc acc[P];
 #pragma unroll
-                for (int p = 0; p < P; ++p)
-#pragma unroll
-                    for (int i = 0; i < kAccLimbs; ++i) acc[p][i] = 0;
+                for (int p = 0; p < P; ++p) acc[p].clear();
 
-                for (uint64_t c = c_begin + lane; c < c_end; c += 32)
+                if (kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT)
                 {
-                    const Fr f = load_column_value(col, kind, c);
-#pragma unroll
-                    for (int p = 0; p < P; ++p)
+                    const unsigned char* base = static_cast<const unsigned char*>(col) + c_begin * 32;
+                    const uint64_t rows = c_end > c_begin ? c_end - c_begin : 0;
+                    const uint32_t chunks = static_cast<uint32_t>((rows + kChunkRows - 1) / kChunkRows);
+                    auto issue = [&](uint32_t j) {
+                        // chunk j of this unit goes to ring slot (ring_pos + j) % kStages
+                        const uint32_t slot = (ring_pos + j) % kStages;
+                        const uint64_t row0 = static_cast<uint64_t>(j) * kChunkRows;
+                        const uint32_t bytes = static_cast<uint32_t>((rows - row0 < kChunkRows ? rows - row0 : kChunkRows) * 32);
+                        const uint32_t bar = smem_u32(bars + slot);
+                        mbar_expect_tx(bar, bytes);
+                        bulk_load(smem_u32(ring + static_cast<size_t>(slot) * kChunkBytes), base + row0 * 32, bytes, bar);
+                    };
+                    uint32_t issued = 0;
+                    if (lane == 0)
+                        for (; issued < kStages - 1 && issued < chunks; ++issued) issue(issued);
+                    issued = __shfl_sync(0xffffffffu, issued, 0);
+                    bool ok = true;
+                    for (uint32_t ch = 0; ch < chunks; ++ch)
                     {
-                        const Fr w = load_fr(a.weights + ((c - a.rot[p]) & a.mask));
-                        uint32_t prod[16];
-                        mul_wide<8>(w.l, f.l, prod);
-                        acc_add<kAccLimbs, 16>(acc[p], prod);
+                        if (issued < chunks)
+                        {
+                            if (lane == 0) issue(issued);
+                            ++issued;
+                        }
+                        const uint32_t slot = (ring_pos + ch) % kStages;
+                        const uint32_t parity = ((ring_pos + ch) / kStages) & 1u;
+                        ok = mbar_wait(smem_u32(bars + slot), parity);
+                        if (!__all_sync(0xffffffffu, ok))
+                        {
+                            ok = false;
+                            break;
+                        }
+                        const unsigned char* stage = ring + static_cast<size_t>(slot) * kChunkBytes;
+                        const uint64_t row0 = static_cast<uint64_t>(ch) * kChunkRows;
+                        const uint32_t rows_here = static_cast<uint32_t>(rows - row0 < kChunkRows ? rows - row0 : kChunkRows);
+#pragma unroll 1
+                        for (uint32_t r = lane; r < rows_here; r += 32)
+                        {
+                            const Fr f = load_fr_shared(stage + r * 32);
+                            const uint64_t c = c_begin + row0 + r;
+#pragma unroll
+                            for (int p = 0; p < P; ++p)
+                            {
+                                const Fr w = load_fr(a.weights + ((c - a.rot[p]) & a.mask));
+                                acc[p].template mac<8>(w.l, f.l);
+                            }
+                        }
+                        __syncwarp();  // the slot may be refilled from the next iteration on
+                    }
+                    if (!ok)
+                    {
+                        // a copy never completed: flag it, give the copies still in flight a
+                        // bounded chance to land, and leave
+                        if (lane == 0) atomicExch(a.status, GZK_E_TIMEOUT);
+                        for (uint32_t j = 0; j < issued && j < chunks; ++j)
+                            mbar_wait(smem_u32(bars + (ring_pos + j) % kStages), ((ring_pos + j) / kStages) & 1u);
+                        return;
+                    }
+                    ring_pos += chunks;
+                }
+                else if (kind == GZK_KIND_U32)
+                {
+                    const uint32_t* values = static_cast<const uint32_t*>(col);
+                    for (uint64_t c = c_begin + lane; c < c_end; c += 32)
+                    {
+                        const uint32_t f = __ldcs(values + c);
+#pragma unroll
+                        for (int p = 0; p < P; ++p)
+                        {
+                            const Fr w = load_fr(a.weights + ((c - a.rot[p]) & a.mask));
+                            acc[p].template mac<1>(w.l, &f);
+                        }
+                    }
+                }
+                else
+                {
+                    // I64, FieldElement::from_signed: v < 0 stands for r - |v|.  w * (r - |v|)
+                    // is congruent to (r - w) * |v|, which keeps the product 8 x 2 limbs.
+                    const long long* values = static_cast<const long long*>(col);
+                    for (uint64_t c = c_begin + lane; c < c_end; c += 32)
+                    {
+                        const long long v = __ldcs(values + c);
+                        const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
+                        const uint32_t f[2] = {static_cast<uint32_t>(mag), static_cast<uint32_t>(mag >> 32)};
+#pragma unroll
+                        for (int p = 0; p < P; ++p)
+                        {
+                            Fr w = load_fr(a.weights + ((c - a.rot[p]) & a.mask));
+                            if (v < 0) w = sub(Fr::zero(), w);
+                            acc[p].template mac<2>(w.l, f);
+                        }
                     }
                 }
                 // exact integer sum across the warp
 #pragma unroll
                 for (int p = 0; p < P; ++p)
                 {
+                    uint32_t sum[kAccLimbs];
+                    acc[p].fold(sum);
 #pragma unroll
                     for (int offset = 16; offset > 0; offset >>= 1)
                     {
                         uint32_t other[kAccLimbs];
 #pragma unroll
-                        for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, acc[p][i], offset);
-                        acc_add<kAccLimbs, kAccLimbs>(acc[p], other);
+                        for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, sum[i], offset);
+                        acc_add<kAccLimbs, kAccLimbs>(sum, other);
                     }
                     if (lane == 0)
                     {
                         uint32_t* dst = a.partial + ((static_cast<uint64_t>(tile) * P + p) * a.k_count + k) * kAccLimbs;
 #pragma unroll
-                        for (int i = 0; i < kAccLimbs; ++i) dst[i] = acc[p][i];
+                        for (int i = 0; i < kAccLimbs; ++i) dst[i] = sum[i];
                     }
                 }
             }
+        }
+
+        // Resident CTAs per SM of the two kernel variants (queried once; also opts the
+        // kernels into their dynamic shared-memory size).  Allocates nothing.
+        int blocks_per_sm(int p)
+        {
+            static int cached[3] = {0, 0, 0};
+            if (cached[p] == 0)
+            {
+                int nb = 0;
+                cudaError_t err;
+                if (p == 2)
+                {
+                    cudaFuncSetAttribute(eval_partial_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<2>, kThreads, kSmemBytes);
+                }
+                else
+                {
+                    cudaFuncSetAttribute(eval_partial_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
+                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<1>, kThreads, kSmemBytes);
+                }
+                cached[p] = (err == cudaSuccess && nb > 0) ? nb : 1;
+            }
+            return cached[p];
+        }
+
+        void launch_eval_partial(cudaStream_t stream, const EvalArgs& args, int p, unsigned blocks)
+        {
+            blocks_per_sm(p);  // makes sure the shared-memory opt-in has happened
+            if (p == 2)
+                eval_partial_kernel<2><<<blocks, kThreads, kSmemBytes, stream>>>(args);
+            else
+                eval_partial_kernel<1><<<blocks, kThreads, kSmemBytes, stream>>>(args);
         }
 
         // Sums the per-tile partials of one (rotation, column) pair, reduces once and
@@ -161,7 +335,82 @@ namespace gzk
     }
 }
 
+namespace gzk
+{
+    namespace
+    {
+        // Integer-pipe ceiling of the inner product arithmetic: every lane runs the
+        // 8x8-limb multiply-accumulate on register operands, no memory traffic.
+        template <int CHAINS>
+        __global__ void __launch_bounds__(kThreads) mac_peak_kernel(uint32_t iters, uint32_t* sink)
+        {
+            WideAcc acc[CHAINS];
+            Fr w, f;
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+            {
+                w.l[i] = threadIdx.x * 2654435761u + i * 40503u + blockIdx.x;
+                f.l[i] = threadIdx.x * 2246822519u + i * 3266489917u + 17u;
+            }
+#pragma unroll
+            for (int c = 0; c < CHAINS; ++c) acc[c].clear();
+            for (uint32_t it = 0; it < iters; ++it)
+            {
+#pragma unroll
+                for (int c = 0; c < CHAINS; ++c) acc[c].template mac<8>(w.l, f.l);
+                w.l[0] += it;  // keep the operands loop-variant
+                f.l[7] ^= it;
+            }
+            uint32_t sum[kAccLimbs];
+            uint32_t x = 0;
+#pragma unroll
+            for (int c = 0; c < CHAINS; ++c)
+            {
+                acc[c].fold(sum);
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) x ^= sum[i];
+            }
+            if (x == 0x12345678u) sink[0] = x;  // practically never: defeats dead-code elimination
+        }
+    }
+}
+
 using namespace gzk;
+
+// Measures the multiply-accumulate ceiling (8x8-limb products per second over the
+// whole GPU) with `chains` independent accumulators per lane (1 or 2).
+extern "C" int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, double* products_per_second)
+{
+    if (ctx == nullptr || products_per_second == nullptr) return GZK_E_INVALID;
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int nb = 0;
+    if (chains == 2)
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, mac_peak_kernel<2>, kThreads, 0);
+    else
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, mac_peak_kernel<1>, kThreads, 0);
+    if (nb <= 0) nb = 1;
+    const unsigned blocks = static_cast<unsigned>(ctx->sm_count * nb);
+    cudaEvent_t e0, e1;
+    GZK_CUDA_TRY(ctx, cudaEventCreate(&e0));
+    GZK_CUDA_TRY(ctx, cudaEventCreate(&e1));
+    for (int rep = 0; rep < 2; ++rep)
+    {
+        GZK_CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
+        if (chains == 2)
+            mac_peak_kernel<2><<<blocks, kThreads, 0, ctx->stream>>>(iters, reinterpret_cast<uint32_t*>(ctx->d_status) + 8);
+        else
+            mac_peak_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(iters, reinterpret_cast<uint32_t*>(ctx->d_status) + 8);
+        GZK_CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    float ms = 0.f;
+    GZK_CUDA_TRY(ctx, cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    const double products = static_cast<double>(blocks) * kThreads * static_cast<double>(iters) * (chains == 2 ? 2 : 1);
+    *products_per_second = products / (ms * 1e-3);
+    return GZK_OK;
+}
 
 extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                               const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host)
@@ -186,23 +435,24 @@ extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count
 
     // tile plan: enough (tile, column) units to keep every warp of the machine busy
     // several times over, but at most 256 tiles so the partial buffer stays small.
-    const uint64_t warps_total = static_cast<uint64_t>(ctx->sm_count) * 2 * (kThreads / 32);
-    uint64_t want_tiles = (8 * warps_total + k_count - 1) / k_count;
+    const uint64_t resident_blocks = static_cast<uint64_t>(ctx->sm_count) * blocks_per_sm(p_count >= 2 ? 2 : 1);
+    const uint64_t warps_total = resident_blocks * (kThreads / 32);
+    uint64_t want_tiles = (6 * warps_total + k_count - 1) / k_count;
     uint64_t max_tiles = (len + 255) / 256;
     if (max_tiles == 0) max_tiles = 1;
     if (want_tiles > 256) want_tiles = 256;
     if (want_tiles > max_tiles) want_tiles = max_tiles;
     if (want_tiles == 0) want_tiles = 1;
     uint64_t tile_rows = (len + want_tiles - 1) / want_tiles;
-    tile_rows = (tile_rows + 31) & ~31ULL;
-    if (tile_rows == 0) tile_rows = 32;
+    tile_rows = (tile_rows + kChunkRows - 1) / kChunkRows * kChunkRows;
+    if (tile_rows == 0) tile_rows = kChunkRows;
     const uint32_t tiles = len == 0 ? 1 : static_cast<uint32_t>((len + tile_rows - 1) / tile_rows);
 
     // device-side tables and scratch
     const size_t table_bytes = k_count * (sizeof(void*) + sizeof(int));
     const size_t table_padded = (table_bytes + 31) & ~static_cast<size_t>(31);
     void* h_table = nullptr;
-    int rc = ensure_pinned(ctx, table_padded + p_count * k_count * 32, &h_table);
+    int rc = ensure_pinned(ctx, table_padded + p_count * k_count * 32 + 64, &h_table);
     if (rc != GZK_OK) return rc;
     void* d_table = nullptr;
     if ((rc = ensure_scratch(ctx, 0, table_padded + p_count * k_count * 32, &d_table)) != GZK_OK) return rc;
@@ -237,16 +487,14 @@ extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count
         args.rot[0] = rotations[p0];
         args.rot[1] = p_now == 2 ? rotations[p0 + 1] : 0;
         args.partial = static_cast<uint32_t*>(d_partial);
+        args.status = ctx->d_status;
         const uint64_t units = static_cast<uint64_t>(tiles) * k_count;
         uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
-        const uint64_t max_blocks = static_cast<uint64_t>(ctx->sm_count) * 2;
+        const uint64_t max_blocks = static_cast<uint64_t>(ctx->sm_count) * blocks_per_sm(p_now);
         if (blocks > max_blocks) blocks = max_blocks;
         {
             LaunchScope scope(ctx, p_now == 2 ? "eval_partial_p2" : "eval_partial_p1");
-            if (p_now == 2)
-                eval_partial_kernel<2><<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(args);
-            else
-                eval_partial_kernel<1><<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(args);
+            launch_eval_partial(ctx->stream, args, static_cast<int>(p_now), static_cast<unsigned>(blocks));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         const uint32_t outs = p_now * static_cast<uint32_t>(k_count);
@@ -258,7 +506,14 @@ extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count
         GZK_CUDA_TRY(ctx, cudaGetLastError());
     }
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, d_out, p_count * k_count * 32, cudaMemcpyDeviceToHost, ctx->stream));
+    int* h_status = reinterpret_cast<int*>(h_out + p_count * k_count * 32);
+    GZK_CUDA_TRY(ctx, cudaMemcpyAsync(h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+    if (*h_status != 0)
+    {
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        return fail(ctx, GZK_E_TIMEOUT, "eval_batch: a bounded wait on a bulk copy gave up");
+    }
     std::memcpy(out_host, h_out, p_count * k_count * 32);
     return GZK_OK;
 }
@@ -280,10 +535,11 @@ namespace
     constexpr size_t kStaticMaxRotations = 2;
     constexpr size_t kStaticMaxTiles = 64;
     constexpr size_t kStaticTableBytes = kStaticMaxColumns * (sizeof(void*) + sizeof(int));  // 3 KiB
+    constexpr size_t kStaticStatusOffset = 3584;  // one status word between the table and the partial sums
     constexpr size_t kStaticPartialOffset = 4096;
     constexpr size_t kStaticPartialBytes = kStaticMaxTiles * kStaticMaxRotations * kStaticMaxColumns * gzk::kAccLimbs * sizeof(uint32_t);
     constexpr size_t kStaticBytes = kStaticPartialOffset + kStaticPartialBytes;  // about 2.1 MiB per GPU
-    static_assert(kStaticTableBytes <= kStaticPartialOffset, "pointer table must fit before the partial sums");
+    static_assert(kStaticTableBytes <= kStaticStatusOffset, "pointer table must fit before the status word");
 
     // Held by every GPU that loads the library, until the process exits.
     static __device__ __align__(256) unsigned char g_eval_static_scratch[kStaticBytes];
@@ -354,8 +610,8 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     if (want_tiles > max_tiles) want_tiles = max_tiles;
     if (want_tiles == 0) want_tiles = 1;
     uint64_t tile_rows = (len + want_tiles - 1) / want_tiles;
-    tile_rows = (tile_rows + 31) & ~31ULL;
-    if (tile_rows == 0) tile_rows = 32;
+    tile_rows = (tile_rows + kChunkRows - 1) / kChunkRows * kChunkRows;
+    if (tile_rows == 0) tile_rows = kChunkRows;
     const uint32_t tiles = len == 0 ? 1 : static_cast<uint32_t>((len + tile_rows - 1) / tile_rows);
 
     // pointer table: built on the stack, copied into the head of the array
@@ -377,14 +633,12 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     args.rot[0] = rotations[0];
     args.rot[1] = p_count == 2 ? rotations[1] : 0;
     args.partial = reinterpret_cast<uint32_t*>(scratch + kStaticPartialOffset);
+    args.status = reinterpret_cast<int*>(scratch + kStaticStatusOffset);
     const uint64_t units = static_cast<uint64_t>(tiles) * k_count;
     uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
     const uint64_t max_blocks = static_cast<uint64_t>(g_static_sms[device]) * 2;
     if (blocks > max_blocks) blocks = max_blocks;
-    if (p_count == 2)
-        eval_partial_kernel<2><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(args);
-    else
-        eval_partial_kernel<1><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(args);
+    launch_eval_partial(s, args, static_cast<int>(p_count), static_cast<unsigned>(blocks));
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
     eval_finish_kernel<<<(outs + 127) / 128, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),

@@ -479,6 +479,121 @@ namespace gzk
         return reduce_once(s);
     }
 
+    // Unreduced accumulator for sums of 8x8-limb products (inner products of Fr
+    // vectors).  Products whose low half lands on an even limb are added into E,
+    // the others into O (O is offset by one limb), each row of a product as one
+    // carry chain straight into the accumulator.  The carry out of a chain is not
+    // rippled: it is counted in a small counter for the limb position it belongs
+    // to (five positions for E, four for O).  A term therefore costs 64 wide
+    // multiply-adds plus 16 carry captures and no temporaries; the pieces are
+    // merged once, in fold().  Exact for up to 2^31 terms.
+    struct WideAcc
+    {
+        uint32_t E[16];
+        uint32_t O[14];
+        uint32_t cE[5];  // carries into E positions 8,10,12,14,16
+        uint32_t cO[4];  // carries into O positions 8,10,12,14
+
+        GZK_HD void clear()
+        {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) E[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 14; ++i) O[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 5; ++i) cE[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cO[i] = 0;
+        }
+
+        template <int I>
+        GZK_HD void row(const uint32_t* a, uint32_t bi)
+        {
+            if (I % 2 == 0)
+            {
+                E[I] = mp::mad_lo_cc(a[0], bi, E[I]);
+                E[I + 1] = mp::madc_hi_cc(a[0], bi, E[I + 1]);
+#pragma unroll
+                for (int j = 2; j < 8; j += 2)
+                {
+                    E[I + j] = mp::madc_lo_cc(a[j], bi, E[I + j]);
+                    E[I + j + 1] = mp::madc_hi_cc(a[j], bi, E[I + j + 1]);
+                }
+                cE[I / 2] = mp::addc(cE[I / 2], 0);
+                O[I] = mp::mad_lo_cc(a[1], bi, O[I]);
+                O[I + 1] = mp::madc_hi_cc(a[1], bi, O[I + 1]);
+#pragma unroll
+                for (int j = 3; j < 8; j += 2)
+                {
+                    O[I + j - 1] = mp::madc_lo_cc(a[j], bi, O[I + j - 1]);
+                    O[I + j] = mp::madc_hi_cc(a[j], bi, O[I + j]);
+                }
+                cO[I / 2] = mp::addc(cO[I / 2], 0);
+            }
+            else
+            {
+                E[I + 1] = mp::mad_lo_cc(a[1], bi, E[I + 1]);
+                E[I + 2] = mp::madc_hi_cc(a[1], bi, E[I + 2]);
+#pragma unroll
+                for (int j = 3; j < 8; j += 2)
+                {
+                    E[I + j] = mp::madc_lo_cc(a[j], bi, E[I + j]);
+                    E[I + j + 1] = mp::madc_hi_cc(a[j], bi, E[I + j + 1]);
+                }
+                cE[(I + 1) / 2] = mp::addc(cE[(I + 1) / 2], 0);
+                O[I - 1] = mp::mad_lo_cc(a[0], bi, O[I - 1]);
+                O[I] = mp::madc_hi_cc(a[0], bi, O[I]);
+#pragma unroll
+                for (int j = 2; j < 8; j += 2)
+                {
+                    O[I + j - 1] = mp::madc_lo_cc(a[j], bi, O[I + j - 1]);
+                    O[I + j] = mp::madc_hi_cc(a[j], bi, O[I + j]);
+                }
+                cO[(I - 1) / 2] = mp::addc(cO[(I - 1) / 2], 0);
+            }
+        }
+
+        // acc += a * b for 8-limb a and the low ROWS limbs of b (higher limbs of b
+        // are known to be zero: small-integer columns).
+        template <int ROWS>
+        GZK_HD void mac(const uint32_t* a, const uint32_t* b)
+        {
+            row<0>(a, b[0]);
+            if (ROWS > 1) row<1>(a, b[1]);
+            if (ROWS > 2) row<2>(a, b[2]);
+            if (ROWS > 3) row<3>(a, b[3]);
+            if (ROWS > 4) row<4>(a, b[4]);
+            if (ROWS > 5) row<5>(a, b[5]);
+            if (ROWS > 6) row<6>(a, b[6]);
+            if (ROWS > 7) row<7>(a, b[7]);
+        }
+
+        // Merge into one 17-limb integer.
+        GZK_HD void fold(uint32_t* out) const
+        {
+            uint32_t t[17];
+#pragma unroll
+            for (int k = 0; k < 16; ++k) out[k] = E[k];
+            out[16] = 0;
+#pragma unroll
+            for (int k = 0; k < 17; ++k) t[k] = 0;
+#pragma unroll
+            for (int i = 0; i < 5; ++i) t[8 + 2 * i] = cE[i];
+            acc_add<17, 17>(out, t);
+            t[0] = 0;
+#pragma unroll
+            for (int k = 0; k < 14; ++k) t[k + 1] = O[k];
+            t[15] = 0;
+            t[16] = 0;
+            acc_add<17, 17>(out, t);
+#pragma unroll
+            for (int k = 0; k < 17; ++k) t[k] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) t[9 + 2 * i] = cO[i];
+            acc_add<17, 17>(out, t);
+        }
+    };
+
     using Fr = Fe<FrCfg>;
     using Fp = Fe<FpCfg>;
 

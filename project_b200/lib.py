@@ -128,6 +128,11 @@ class Backend:
             out[name.value.decode()] = (int(launches.value), float(ms.value))
         return out
 
+    def measure_mac_peak(self, chains=1, iters=20000):
+        out = ctypes.c_double()
+        self._check(self.lib.gzk_measure_mac_peak(self.ctx, int(chains), ctypes.c_uint32(iters), ctypes.byref(out)))
+        return out.value
+
     @property
     def stream(self):
         return self.lib.gzk_ctx_stream(self.ctx)

@@ -69,11 +69,13 @@ int check_wide(std::mt19937_64& rng)
     // reduced once: must equal the Montgomery form of the true field sum.
     using namespace gzk;
     int failures = 0;
-    for (int trial = 0; trial < 200; ++trial)
+    for (int trial = 0; trial < 600; ++trial)
     {
         uint32_t acc[17] = {};
+        gzk::WideAcc wacc;
+        wacc.clear();
         oracle::Fr want = oracle::Fr::zero();
-        const int terms = 1 + static_cast<int>(rng() % 40);
+        const int terms = 1 + static_cast<int>(rng() % (trial % 50 == 0 ? 5000 : 40));
         for (int t = 0; t < terms; ++t)
         {
             oracle::BigInt<4> cw, cf;
@@ -119,6 +121,12 @@ int check_wide(std::mt19937_64& rng)
                 if (std::memcmp(ref, prod, 64) != 0) { ++failures; std::printf("mul_wide mismatch\n"); }
             }
             acc_add<17, 16>(acc, prod);
+            wacc.mac<8>(wl, fl);
+        }
+        {
+            uint32_t folded[17];
+            wacc.fold(folded);
+            if (std::memcmp(folded, acc, sizeof(acc)) != 0) { ++failures; std::printf("WideAcc mismatch\n"); }
         }
         const Fr reduced = mul(redc_wide<FrCfg, 9>(acc), fr_const_2_544());
         if (std::memcmp(reduced.l, want.v.w.data(), 32) != 0) { ++failures; std::printf("redc_wide mismatch\n"); }

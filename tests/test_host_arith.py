@@ -1,0 +1,17 @@
+"""Carry-chain field arithmetic of the CUDA kernels, compiled for the host (emulated
+carry flag) and compared with the oracle's 64-bit implementation.  No GPU needed."""
+import os
+import subprocess
+import tempfile
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_device_arithmetic_matches_oracle_on_host():
+    src = os.path.join(ROOT, "tests", "host", "mp_host_check.cpp")
+    with tempfile.TemporaryDirectory() as tmp:
+        exe = os.path.join(tmp, "mp_host_check")
+        subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, src], check=True)
+        out = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stdout + out.stderr
+    assert out.stdout.strip().endswith("OK")
