@@ -113,6 +113,39 @@ int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf*
 int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                    const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host);
 
+/* ---- a7: LogUp and route running sums ----------------------------------------------
+ * Input columns may be of any kind; `out` is FR_MONT with count >= n.  One batch
+ * inversion per call; GZK_E_DOMAIN ("batch_invert encountered zero") when a
+ * denominator is zero, as the reference throws.
+ * gzk_logup_accumulator: R_0 = 0, R_{i+1} = R_i + q_table_i*m_i/(T_i+beta) - q_query_i/(Q_i+beta)
+ * for i < active_count (clamped to n-1), tail filled with the last value.  Replaces
+ * build_logup_accumulator_with_active_count (src/protocol/lookup.cpp:100-157).
+ * gzk_route_node_accumulator / gzk_route_edge_accumulator: running sums of
+ * m_i/(T_i+beta) resp. 1/(Q_i+beta) over the first valid_length rows (must be <
+ * domain_size).  Replace build_route_node_accumulator / build_route_edge_accumulator
+ * (src/protocol/trace.cpp:298-361). */
+int gzk_logup_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* query, const gzk_buf* multiplicity,
+                          const gzk_buf* q_table, const gzk_buf* q_query, size_t n, const uint8_t beta[32],
+                          size_t active_count, gzk_buf* out);
+int gzk_route_node_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* multiplicity, size_t valid_length,
+                               size_t domain_size, const uint8_t beta[32], gzk_buf* out);
+int gzk_route_edge_accumulator(gzk_ctx* ctx, const gzk_buf* query, size_t valid_length, size_t domain_size,
+                               const uint8_t beta[32], gzk_buf* out);
+
+/* ---- a8: segmented prefix states over the dst-sorted edge list ------------------------
+ * out[0] = v[0]; out[i] = q_new[i] ? v[i] : out[i-1] + v[i].  q_new must hold only
+ * 0 and 1 (the reference's selector; other values give GZK_E_INVALID).  Replaces
+ * build_group_prefix_state and build_max_counter_state (src/protocol/psq.cpp:7-39). */
+int gzk_group_prefix_state(gzk_ctx* ctx, const gzk_buf* values, const gzk_buf* q_new, size_t n, gzk_buf* out);
+
+/* ---- a9: inner-product accumulator ------------------------------------------------------
+ * acc[0] = 0, acc[i+1] = acc[i] + a[i]*b[i] for i < count, tail filled with the
+ * total, which is also returned in mu_out.  Replaces build_zkmap_trace
+ * (src/protocol/zkmap.cpp:7-32) and the accumulator of build_binding_trace
+ * (src/protocol/trace.cpp:1595-1621). */
+int gzk_zkmap_accumulator(gzk_ctx* ctx, const gzk_buf* a, const gzk_buf* b, size_t count, size_t domain_size,
+                          gzk_buf* out_acc, uint8_t mu_out[32]);
+
 /* ---- packed evaluation without any allocation ------------------------------------
  * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that
  * cannot call cudaMalloc while they run: a prover host that has already given all

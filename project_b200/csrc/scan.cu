@@ -1,0 +1,447 @@
+// Running-sum column builders: LogUp accumulators, route accumulators, the
+// inner-product (zkMaP / binding) accumulator and the segmented prefix states over
+// the dst-sorted edge list.  All are "out = prefix sums of per-row terms"; the
+// terms of the lookup arguments need one field inversion per row, done as one
+// batch inversion for the whole column.
+//
+// Passes (no inter-CTA waiting anywhere, so nothing can spin):
+//   1. (inverting ops) per-CTA product of the 1024 denominators of its rows
+//   2. (inverting ops) one CTA inverts all CTA products: a single Fermat inversion
+//   3. per-CTA: rebuild denominators, recover each inverse from in-CTA
+//      prefix/suffix products, form the terms, scan them locally, write the local
+//      running sums and the CTA aggregate
+//   4. one CTA turns the aggregates into exclusive CTA offsets and the grand total
+//   5. elementwise fix-up: add the CTA offset, fill the tail with the total
+#include <cstring>
+
+#include "block.cuh"
+
+namespace gzk
+{
+    int launch_batch_invert_single_cta(gzk_ctx* ctx, Fr* values, Fr* tmp, uint32_t count);
+
+    namespace
+    {
+        constexpr int kThreads = 256;
+        constexpr int kElems = 4;
+        constexpr int kChunk = kThreads * kElems;
+        constexpr int kWarps = kThreads / 32;
+
+        enum ScanOp
+        {
+            kLogup = 0,      // term = q_table*mult/(table+beta) - q_query/(query+beta)
+            kRouteNode = 1,  // term = mult/(table+beta)
+            kRouteEdge = 2,  // term = 1/(query+beta)
+            kProduct = 3,    // term = a*b
+            kSegmented = 4,  // term = value, running sum restarts where q_new = 1
+        };
+
+        struct ScanArgs
+        {
+            ColRef c0, c1, c2, c3, c4;
+            uint64_t count;  // rows that carry a term
+            uint64_t n;      // length of the output column
+            Fr beta;
+            Fr* out;
+            Fr* cta_products;     // pass 1 -> 2 -> 3
+            Fr* agg_value;        // per-CTA aggregate / exclusive offset
+            uint32_t* agg_flag;
+            uint32_t* agg_first;  // first row (CTA-relative) that starts a segment, kChunk if none
+            Fr* total;            // grand total (Montgomery)
+            int* status;
+        };
+
+        template <int OP>
+        __device__ __forceinline__ Fr denominator(const ScanArgs& a, uint64_t e)
+        {
+            if (OP == kLogup) return mul(add(col_load_mont(a.c0, e), a.beta), add(col_load_mont(a.c1, e), a.beta));
+            return add(col_load_mont(a.c0, e), a.beta);
+        }
+
+        template <int OP>
+        __global__ void __launch_bounds__(kThreads) scan_products_kernel(ScanArgs a)
+        {
+            __shared__ Fr slots[kWarps];
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk + static_cast<uint64_t>(threadIdx.x) * kElems;
+            Fr prod = Fr::one();
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                const uint64_t e = base + j;
+                if (e < a.count)
+                {
+                    const Fr d = denominator<OP>(a, e);
+                    if (d.is_zero()) atomicExch(a.status, GZK_E_DOMAIN);
+                    prod = mul(prod, d);
+                }
+            }
+            const Fr total = block_product<kThreads>(prod, slots);
+            if (threadIdx.x == 0) store_fr(a.cta_products + blockIdx.x, total);
+        }
+
+        template <int OP>
+        __global__ void __launch_bounds__(kThreads) scan_main_kernel(ScanArgs a)
+        {
+            __shared__ Fr slots[3 * kWarps];
+            __shared__ SegVal seg_slots[kWarps];
+            __shared__ uint32_t first_flag;
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk + static_cast<uint64_t>(threadIdx.x) * kElems;
+            if (threadIdx.x == 0) first_flag = kChunk;
+            __syncthreads();
+
+            Fr term[kElems];
+            uint32_t flag[kElems];
+#pragma unroll
+            for (int j = 0; j < kElems; ++j) flag[j] = 0;
+
+            if (OP == kLogup || OP == kRouteNode || OP == kRouteEdge)
+            {
+                Fr d[kElems], pre[kElems];
+                Fr mine = Fr::one();
+#pragma unroll
+                for (int j = 0; j < kElems; ++j)
+                {
+                    const uint64_t e = base + j;
+                    d[j] = e < a.count ? denominator<OP>(a, e) : Fr::one();
+                    pre[j] = mine;
+                    mine = mul(mine, d[j]);
+                }
+                const Fr outer = block_invert_products<kThreads>(mine, load_fr(a.cta_products + blockIdx.x), slots);
+                Fr suffix = Fr::one();
+#pragma unroll
+                for (int j = kElems - 1; j >= 0; --j)
+                {
+                    const uint64_t e = base + j;
+                    const Fr inverse = mul(outer, mul(pre[j], suffix));
+                    suffix = mul(suffix, d[j]);
+                    if (e >= a.count)
+                    {
+                        term[j] = Fr::zero();
+                    }
+                    else if (OP == kLogup)
+                    {
+                        // inverse = 1/((T+b)(Q+b)): 1/(T+b) = inverse*(Q+b), 1/(Q+b) = inverse*(T+b)
+                        const Fr tb = add(col_load_mont(a.c0, e), a.beta);
+                        const Fr qb = add(col_load_mont(a.c1, e), a.beta);
+                        const Fr table_term = mul(mul(col_load_mont(a.c3, e), col_load_mont(a.c2, e)), mul(inverse, qb));
+                        const Fr query_term = mul(col_load_mont(a.c4, e), mul(inverse, tb));
+                        term[j] = sub(table_term, query_term);
+                    }
+                    else if (OP == kRouteNode)
+                    {
+                        term[j] = mul(col_load_mont(a.c1, e), inverse);
+                    }
+                    else
+                    {
+                        term[j] = inverse;
+                    }
+                }
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < kElems; ++j)
+                {
+                    const uint64_t e = base + j;
+                    if (e >= a.count)
+                    {
+                        term[j] = Fr::zero();
+                    }
+                    else if (OP == kProduct)
+                    {
+                        term[j] = mul(col_load_mont(a.c0, e), col_load_mont(a.c1, e));
+                    }
+                    else
+                    {
+                        term[j] = col_load_mont(a.c0, e);
+                        const Fr q = col_load_mont(a.c1, e);
+                        if (!q.is_zero())
+                        {
+                            if (q != Fr::one()) atomicExch(a.status, GZK_E_INVALID);
+                            flag[j] = 1;
+                            atomicMin(&first_flag, static_cast<uint32_t>(threadIdx.x * kElems + j));
+                        }
+                    }
+                }
+            }
+
+            // thread-local inclusive segmented scan
+            SegVal local[kElems];
+            SegVal run;
+            run.v = Fr::zero();
+            run.flag = 0;
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                SegVal cur;
+                cur.v = term[j];
+                cur.flag = flag[j];
+                run = seg_combine(run, cur);
+                local[j] = run;
+            }
+            SegVal aggregate;
+            const SegVal prefix = block_seg_exclusive_scan<kThreads>(run, seg_slots, &aggregate);
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                const uint64_t e = base + j;
+                const Fr value = seg_combine(prefix, local[j]).v;
+                if (OP == kSegmented)
+                {
+                    if (e < a.n) store_fr(a.out + e, value);
+                }
+                else
+                {
+                    if (e < a.count && e + 1 < a.n) store_fr(a.out + e + 1, value);
+                }
+            }
+            if (threadIdx.x == 0)
+            {
+                store_fr(a.agg_value + blockIdx.x, aggregate.v);
+                a.agg_flag[blockIdx.x] = aggregate.flag;
+                a.agg_first[blockIdx.x] = first_flag;
+            }
+        }
+
+        // Exclusive segmented scan of the CTA aggregates (in place) by one CTA.
+        __global__ void __launch_bounds__(kThreads) scan_offsets_kernel(Fr* agg_value, uint32_t* agg_flag, uint32_t ctas, Fr* total_out)
+        {
+            __shared__ SegVal seg_slots[kWarps];
+            const uint32_t run_len = (ctas + kThreads - 1) / kThreads;
+            const uint32_t begin = threadIdx.x * run_len < ctas ? threadIdx.x * run_len : ctas;
+            const uint32_t end = begin + run_len < ctas ? begin + run_len : ctas;
+            SegVal run;
+            run.v = Fr::zero();
+            run.flag = 0;
+            for (uint32_t i = begin; i < end; ++i)
+            {
+                SegVal cur;
+                cur.v = load_fr_plain(agg_value + i);
+                cur.flag = agg_flag[i];
+                run = seg_combine(run, cur);
+            }
+            SegVal total;
+            SegVal prefix = block_seg_exclusive_scan<kThreads>(run, seg_slots, &total);
+            for (uint32_t i = begin; i < end; ++i)
+            {
+                SegVal cur;
+                cur.v = load_fr_plain(agg_value + i);
+                cur.flag = agg_flag[i];
+                store_fr(agg_value + i, prefix.v);
+                agg_flag[i] = prefix.flag;
+                prefix = seg_combine(prefix, cur);
+            }
+            if (threadIdx.x == 0) store_fr(total_out, total.v);
+        }
+
+        template <int OP>
+        __global__ void __launch_bounds__(kThreads) scan_fixup_kernel(ScanArgs a)
+        {
+            const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (idx >= a.n) return;
+            if (OP == kSegmented)
+            {
+                const uint64_t cta = idx / kChunk;
+                if (cta == 0) return;
+                if (static_cast<uint32_t>(idx - cta * kChunk) < a.agg_first[cta])
+                    store_fr(a.out + idx, add(load_fr_plain(a.out + idx), load_fr(a.agg_value + cta)));
+                return;
+            }
+            if (idx == 0)
+            {
+                store_fr(a.out, Fr::zero());
+            }
+            else if (idx <= a.count)
+            {
+                const uint64_t cta = (idx - 1) / kChunk;
+                if (cta != 0) store_fr(a.out + idx, add(load_fr_plain(a.out + idx), load_fr(a.agg_value + cta)));
+            }
+            else
+            {
+                store_fr(a.out + idx, load_fr(a.total));
+            }
+        }
+
+        template <int OP>
+        int run_scan(gzk_ctx* ctx, ScanArgs& args, bool inverting, uint8_t* total_out_host)
+        {
+            GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+            const uint64_t span = OP == kSegmented ? args.n : args.count;
+            const uint32_t ctas = static_cast<uint32_t>((span + kChunk - 1) / kChunk > 0 ? (span + kChunk - 1) / kChunk : 1);
+            void* scratch = nullptr;
+            const size_t bytes = static_cast<size_t>(ctas) * (3 * sizeof(Fr) + 2 * sizeof(uint32_t)) + 2 * sizeof(Fr);
+            int rc = ensure_scratch(ctx, 2, bytes, &scratch);
+            if (rc != GZK_OK) return rc;
+            Fr* base = static_cast<Fr*>(scratch);
+            args.cta_products = base;
+            Fr* tmp = base + ctas;
+            args.agg_value = base + 2 * static_cast<size_t>(ctas);
+            args.total = base + 3 * static_cast<size_t>(ctas);
+            args.agg_flag = reinterpret_cast<uint32_t*>(base + 3 * static_cast<size_t>(ctas) + 2);
+            args.agg_first = args.agg_flag + ctas;
+            args.status = ctx->d_status;
+            GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+            if (inverting)
+            {
+                {
+                    LaunchScope scope(ctx, "scan_products");
+                    scan_products_kernel<OP><<<ctas, kThreads, 0, ctx->stream>>>(args);
+                }
+                GZK_CUDA_TRY(ctx, cudaGetLastError());
+                if ((rc = launch_batch_invert_single_cta(ctx, args.cta_products, tmp, ctas)) != GZK_OK) return rc;
+            }
+            {
+                LaunchScope scope(ctx, "scan_main");
+                scan_main_kernel<OP><<<ctas, kThreads, 0, ctx->stream>>>(args);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            {
+                LaunchScope scope(ctx, "scan_offsets");
+                scan_offsets_kernel<<<1, kThreads, 0, ctx->stream>>>(args.agg_value, args.agg_flag, ctas, args.total);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            if (args.n > 0)
+            {
+                LaunchScope scope(ctx, "scan_fixup");
+                scan_fixup_kernel<OP><<<static_cast<unsigned>((args.n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(args);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            struct
+            {
+                Fr total;
+                int status;
+            } host;
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&host.total, args.total, sizeof(Fr), cudaMemcpyDeviceToHost, ctx->stream));
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&host.status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+            GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            if (host.status == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "batch_invert encountered zero");
+            if (host.status == GZK_E_INVALID) return fail(ctx, GZK_E_INVALID, "q_new must hold only 0 and 1");
+            if (total_out_host != nullptr) host_fr_to_bytes(from_mont(host.total), total_out_host);
+            return GZK_OK;
+        }
+
+        bool col_ok(const gzk_buf* b, uint64_t need) { return b != nullptr && b->count >= need; }
+        ColRef ref(const gzk_buf* b)
+        {
+            ColRef r;
+            r.ptr = b->dptr;
+            r.kind = b->kind;
+            return r;
+        }
+        int load_scalar(gzk_ctx* ctx, const uint8_t* bytes, Fr* out_mont)
+        {
+            bool canonical = false;
+            const Fr v = host_fr_from_bytes(bytes, &canonical);
+            if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
+            *out_mont = to_mont(v);
+            return GZK_OK;
+        }
+        bool out_ok(const gzk_buf* out, uint64_t n) { return out != nullptr && out->kind == GZK_KIND_FR_MONT && out->count >= n; }
+    }
+}
+
+using namespace gzk;
+
+extern "C"
+{
+    int gzk_logup_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* query, const gzk_buf* multiplicity,
+                              const gzk_buf* q_table, const gzk_buf* q_query, size_t n, const uint8_t beta[32],
+                              size_t active_count, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (beta == nullptr || !out_ok(out, n)) return fail(ctx, GZK_E_INVALID, "logup: output must be a Montgomery buffer of n elements");
+        if (n > 0 && active_count > n - 1) active_count = n - 1;  // lookup.cpp:117
+        if (n == 0) return GZK_OK;
+        if (!col_ok(table, active_count) || !col_ok(query, active_count) || !col_ok(multiplicity, active_count) ||
+            !col_ok(q_table, active_count) || !col_ok(q_query, active_count))
+            return fail(ctx, GZK_E_INVALID, "lookup accumulator input size mismatch");
+        ScanArgs args{};
+        args.c0 = ref(table);
+        args.c1 = ref(query);
+        args.c2 = ref(multiplicity);
+        args.c3 = ref(q_table);
+        args.c4 = ref(q_query);
+        args.count = active_count;
+        args.n = n;
+        args.out = static_cast<Fr*>(out->dptr);
+        int rc = load_scalar(ctx, beta, &args.beta);
+        if (rc != GZK_OK) return rc;
+        return run_scan<kLogup>(ctx, args, true, nullptr);
+    }
+
+    int gzk_route_node_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* multiplicity, size_t valid_length,
+                                   size_t domain_size, const uint8_t beta[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (beta == nullptr || !out_ok(out, domain_size)) return fail(ctx, GZK_E_INVALID, "route node: bad output buffer");
+        if (domain_size == 0) return GZK_OK;
+        if (valid_length >= domain_size) return fail(ctx, GZK_E_INVALID, "route accumulator needs valid_length < domain_size");
+        if (!col_ok(table, valid_length) || !col_ok(multiplicity, valid_length))
+            return fail(ctx, GZK_E_INVALID, "route node accumulator input size mismatch");
+        ScanArgs args{};
+        args.c0 = ref(table);
+        args.c1 = ref(multiplicity);
+        args.count = valid_length;
+        args.n = domain_size;
+        args.out = static_cast<Fr*>(out->dptr);
+        int rc = load_scalar(ctx, beta, &args.beta);
+        if (rc != GZK_OK) return rc;
+        return run_scan<kRouteNode>(ctx, args, true, nullptr);
+    }
+
+    int gzk_route_edge_accumulator(gzk_ctx* ctx, const gzk_buf* query, size_t valid_length, size_t domain_size,
+                                   const uint8_t beta[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (beta == nullptr || !out_ok(out, domain_size)) return fail(ctx, GZK_E_INVALID, "route edge: bad output buffer");
+        if (domain_size == 0) return GZK_OK;
+        if (valid_length >= domain_size) return fail(ctx, GZK_E_INVALID, "route accumulator needs valid_length < domain_size");
+        if (!col_ok(query, valid_length)) return fail(ctx, GZK_E_INVALID, "route edge accumulator input size mismatch");
+        ScanArgs args{};
+        args.c0 = ref(query);
+        args.count = valid_length;
+        args.n = domain_size;
+        args.out = static_cast<Fr*>(out->dptr);
+        int rc = load_scalar(ctx, beta, &args.beta);
+        if (rc != GZK_OK) return rc;
+        return run_scan<kRouteEdge>(ctx, args, true, nullptr);
+    }
+
+    int gzk_zkmap_accumulator(gzk_ctx* ctx, const gzk_buf* a, const gzk_buf* b, size_t count, size_t domain_size,
+                              gzk_buf* out_acc, uint8_t mu_out[32])
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (!out_ok(out_acc, domain_size)) return fail(ctx, GZK_E_INVALID, "zkmap: bad output buffer");
+        if (count != 0 && count + 1 > domain_size) return fail(ctx, GZK_E_INVALID, "zkMaP accumulator exceeds its domain");
+        if (!col_ok(a, count) || !col_ok(b, count)) return fail(ctx, GZK_E_INVALID, "zkMaP input size mismatch");
+        if (domain_size == 0)
+        {
+            if (mu_out != nullptr) std::memset(mu_out, 0, 32);
+            return GZK_OK;
+        }
+        ScanArgs args{};
+        args.c0 = ref(a);
+        args.c1 = ref(b);
+        args.count = count;
+        args.n = domain_size;
+        args.beta = Fr::zero();
+        args.out = static_cast<Fr*>(out_acc->dptr);
+        return run_scan<kProduct>(ctx, args, false, mu_out);
+    }
+
+    int gzk_group_prefix_state(gzk_ctx* ctx, const gzk_buf* values, const gzk_buf* q_new, size_t n, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (!out_ok(out, n)) return fail(ctx, GZK_E_INVALID, "prefix state: bad output buffer");
+        if (!col_ok(values, n) || !col_ok(q_new, n)) return fail(ctx, GZK_E_INVALID, "prefix state input size mismatch");
+        if (n == 0) return GZK_OK;
+        ScanArgs args{};
+        args.c0 = ref(values);
+        args.c1 = ref(q_new);
+        args.count = n;
+        args.n = n;
+        args.beta = Fr::zero();
+        args.out = static_cast<Fr*>(out->dptr);
+        return run_scan<kSegmented>(ctx, args, false, nullptr);
+    }
+}

@@ -157,6 +157,34 @@ class Backend:
         self._check(self.lib.gzk_bary_weights(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), out.handle))
         return out
 
+    def logup_accumulator(self, table, query, mult, q_table, q_query, n, beta, active_count):
+        out = self.alloc(KIND_FR_MONT, n)
+        self._check(self.lib.gzk_logup_accumulator(self.ctx, table.handle, query.handle, mult.handle, q_table.handle, q_query.handle,
+                                                   _sz(n), _ptr(_fr(beta)), _sz(active_count), out.handle))
+        return out
+
+    def route_node_accumulator(self, table, mult, valid_length, domain_size, beta):
+        out = self.alloc(KIND_FR_MONT, domain_size)
+        self._check(self.lib.gzk_route_node_accumulator(self.ctx, table.handle, mult.handle, _sz(valid_length), _sz(domain_size),
+                                                        _ptr(_fr(beta)), out.handle))
+        return out
+
+    def route_edge_accumulator(self, query, valid_length, domain_size, beta):
+        out = self.alloc(KIND_FR_MONT, domain_size)
+        self._check(self.lib.gzk_route_edge_accumulator(self.ctx, query.handle, _sz(valid_length), _sz(domain_size), _ptr(_fr(beta)), out.handle))
+        return out
+
+    def group_prefix_state(self, values, q_new, n):
+        out = self.alloc(KIND_FR_MONT, n)
+        self._check(self.lib.gzk_group_prefix_state(self.ctx, values.handle, q_new.handle, _sz(n), out.handle))
+        return out
+
+    def zkmap_accumulator(self, a, b, count, domain_size):
+        out = self.alloc(KIND_FR_MONT, domain_size)
+        mu = np.zeros(32, dtype=np.uint8)
+        self._check(self.lib.gzk_zkmap_accumulator(self.ctx, a.handle, b.handle, _sz(count), _sz(domain_size), out.handle, _ptr(mu)))
+        return out, mu
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)
