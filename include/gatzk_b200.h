@@ -40,6 +40,7 @@ extern "C" {
 #define GZK_KIND_FR_MONT 1
 #define GZK_KIND_I64 2
 #define GZK_KIND_U32 3
+#define GZK_KIND_F64 4   /* IEEE doubles: input of gzk_quantize only */
 
 typedef struct gzk_ctx gzk_ctx;
 typedef struct gzk_buf gzk_buf;
@@ -145,6 +146,51 @@ int gzk_group_prefix_state(gzk_ctx* ctx, const gzk_buf* values, const gzk_buf* q
  * (src/protocol/trace.cpp:1595-1621). */
 int gzk_zkmap_accumulator(gzk_ctx* ctx, const gzk_buf* a, const gzk_buf* b, size_t count, size_t domain_size,
                           gzk_buf* out_acc, uint8_t mu_out[32]);
+
+/* ---- a6 / a9 / a12: matrices and coefficient polynomials ----------------------------------
+ * gzk_matrix_horner: the rows x cols row-major matrix read as one coefficient
+ * polynomial sum_{i,j} M[i][j] x^(i*cols+j).  Replaces matrix_row_major_evaluation /
+ * row_polynomial_at_point (src/protocol/trace.cpp:508-573, twin at
+ * src/protocol/prover.cpp:414-440) and, with rows = 1, horner / the coefficient
+ * branch of Polynomial::evaluate (src/algebra/polynomial.cpp:415-421, 499-508).
+ * gzk_fold_rows: out[c] = sum_{row < row_count} w[row] * M[row][c]; `out` is an FR
+ * buffer (canonical).  Replaces weighted_column_sum_native (trace.cpp:203-271).
+ * gzk_linear_form_rows: out[row] = sum_c M[row][c] * powers[c]; out FR_MONT.  Replaces
+ * linear_form_by_powers / compress_rows_with_challenge (trace.cpp:273-296, 1358-1364).
+ * gzk_powers: 1, c, c^2, ... (the `powers` helper those callers use). */
+int gzk_matrix_horner(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const uint8_t x[32], uint8_t out[32]);
+int gzk_fold_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* row_weights, size_t row_count,
+                  gzk_buf* out);
+int gzk_linear_form_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* column_powers, gzk_buf* out);
+int gzk_powers(gzk_ctx* ctx, const uint8_t challenge[32], size_t count, gzk_buf* out);
+
+/* ---- a10: witness-column leaves ---------------------------------------------------------------
+ * gzk_weighted_sum: out[i] = left[i] + lambda*right[i], i < count, zero tail
+ *   (build_weighted_sum and the query pack of build_pair_lookup_artifacts,
+ *   src/protocol/trace.cpp:2073, 2098-2108).
+ * gzk_feature_lookup_rows: out[row*width+c] = row_id[row] + eta_i*feature_index[c]
+ *   + eta_v*features[row*width+c] (fill_feature_lookup_rows, trace.cpp:579-607).
+ * gzk_broadcast_node_values: out[e] = node_values[index[e]], e < edge_count, zero tail;
+ *   index is a U32 or I64 buffer, out has the kind of node_values
+ *   (broadcast_node_values and the gathers of quantize_*_witness_cpu,
+ *   trace.cpp:1366-1381, 1143-1279).
+ * gzk_histogram: out[b] = #{i : indices[i] = b}, out is a U32 column
+ *   (multiplicity_from_indices, trace.cpp:1916-1933, and lookup_histogram_indices_cuda,
+ *   src/algebra/cuda_backend.cu:21-102).
+ * gzk_quantize: F64 -> I64, round half away from zero at scale 16 (quantize_float,
+ *   trace.cpp:973-976).
+ * gzk_first_zero_marker: out[k] = 1 for the first row k of every [begin,end) group
+ *   with delta[k] = 0, else 0; out is a U32 column (s_max, trace.cpp:2610-2618). */
+int gzk_weighted_sum(gzk_ctx* ctx, const gzk_buf* left, const uint8_t lambda[32], const gzk_buf* right, size_t count,
+                     size_t domain_size, gzk_buf* out);
+int gzk_feature_lookup_rows(gzk_ctx* ctx, const gzk_buf* row_ids, const gzk_buf* feature_indices, const gzk_buf* features,
+                            size_t rows, size_t width, const uint8_t eta_index[32], const uint8_t eta_value[32], gzk_buf* out);
+int gzk_broadcast_node_values(gzk_ctx* ctx, const gzk_buf* node_values, size_t node_count, const gzk_buf* index, size_t edge_count,
+                              size_t domain_size, gzk_buf* out);
+int gzk_histogram(gzk_ctx* ctx, const gzk_buf* indices, size_t count, size_t domain_size, gzk_buf* out);
+int gzk_quantize(gzk_ctx* ctx, const gzk_buf* values, size_t count, gzk_buf* out);
+int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
+                          size_t domain_size, gzk_buf* out);
 
 /* ---- packed evaluation without any allocation ------------------------------------
  * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that

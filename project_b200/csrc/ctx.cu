@@ -337,7 +337,8 @@ extern "C"
         {
         case GZK_KIND_FR:
         case GZK_KIND_FR_MONT: elem = 32; break;
-        case GZK_KIND_I64: elem = 8; break;
+        case GZK_KIND_I64:
+        case GZK_KIND_F64: elem = 8; break;
         case GZK_KIND_U32: elem = 4; break;
         default: return fail(ctx, GZK_E_INVALID, "unknown buffer kind");
         }

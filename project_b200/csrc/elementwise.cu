@@ -1,0 +1,290 @@
+// Elementwise / gather / histogram leaves of witness-column construction.  All are
+// HBM-bound: one coalesced pass over the inputs, one over the output.
+#include <cstring>
+
+#include "block.cuh"
+
+namespace gzk
+{
+    namespace
+    {
+        constexpr int kThreads = 256;
+
+        __device__ __forceinline__ uint64_t grid_stride() { return static_cast<uint64_t>(gridDim.x) * blockDim.x; }
+        __device__ __forceinline__ uint64_t grid_index() { return static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; }
+
+        // out[i] = left[i] + lambda * right[i] for i < count, zero tail.
+        __global__ void weighted_sum_kernel(ColRef left, ColRef right, Fr lambda, uint64_t count, uint64_t n, Fr* out)
+        {
+            for (uint64_t i = grid_index(); i < n; i += grid_stride())
+                store_fr(out + i, i < count ? add(col_load_mont(left, i), mul(lambda, col_load_mont(right, i))) : Fr::zero());
+        }
+
+        // out[row*width + c] = row_id[row] + eta_i * feature_index[c] + eta_v * features[row*width + c]
+        __global__ void feature_rows_kernel(ColRef row_ids, ColRef feature_indices, ColRef features, uint64_t rows, uint32_t width,
+                                            Fr eta_index, Fr eta_value, Fr* out)
+        {
+            const uint64_t total = rows * width;
+            for (uint64_t i = grid_index(); i < total; i += grid_stride())
+            {
+                const uint64_t row = i / width;
+                const uint32_t c = static_cast<uint32_t>(i - row * width);
+                const Fr v = add(add(col_load_mont(row_ids, row), mul(eta_index, col_load_mont(feature_indices, c))),
+                                 mul(eta_value, col_load_mont(features, i)));
+                store_fr(out + i, v);
+            }
+        }
+
+        __device__ __forceinline__ uint64_t index_at(const ColRef& idx, uint64_t i)
+        {
+            if (idx.kind == GZK_KIND_U32) return __ldg(static_cast<const uint32_t*>(idx.ptr) + i);
+            return static_cast<uint64_t>(__ldg(static_cast<const long long*>(idx.ptr) + i));
+        }
+
+        // out[e] = node_values[index[e]] for e < edge_count, zero tail; element size 4, 8 or 32 bytes.
+        template <typename T>
+        __global__ void gather_kernel(const T* node_values, uint64_t node_count, ColRef index, uint64_t edge_count, uint64_t n, T* out,
+                                      int* status)
+        {
+            for (uint64_t e = grid_index(); e < n; e += grid_stride())
+            {
+                T v{};
+                if (e < edge_count)
+                {
+                    const uint64_t src = index_at(index, e);
+                    if (src < node_count)
+                        v = node_values[src];
+                    else
+                        atomicExch(status, GZK_E_INVALID);
+                }
+                out[e] = v;
+            }
+        }
+
+        __global__ void histogram_kernel(ColRef index, uint64_t count, uint64_t domain_size, uint32_t* out, int* status)
+        {
+            for (uint64_t i = grid_index(); i < count; i += grid_stride())
+            {
+                const uint64_t b = index_at(index, i);
+                if (b < domain_size)
+                    atomicAdd(out + b, 1u);
+                else
+                    atomicExch(status, GZK_E_INVALID);
+            }
+        }
+
+        // trace.cpp:973-976: (int64)(v >= 0 ? v*16 + 0.5 : v*16 - 0.5), no fused multiply-add
+        __global__ void quantize_kernel(const double* values, uint64_t count, long long* out)
+        {
+            for (uint64_t i = grid_index(); i < count; i += grid_stride())
+            {
+                const double v = values[i];
+                const double scaled = __dmul_rn(v, 16.0);
+                const double shifted = v >= 0.0 ? __dadd_rn(scaled, 0.5) : __dadd_rn(scaled, -0.5);
+                out[i] = static_cast<long long>(shifted);
+            }
+        }
+
+        // one thread per destination group: mark the first row whose delta is zero
+        __global__ void first_zero_kernel(ColRef delta, ColRef group_begin, ColRef group_end, uint64_t groups, uint64_t n, uint32_t* out,
+                                          int* status)
+        {
+            for (uint64_t g = grid_index(); g < groups; g += grid_stride())
+            {
+                const uint64_t b = index_at(group_begin, g), e = index_at(group_end, g);
+                if (e > n || b > e)
+                {
+                    atomicExch(status, GZK_E_INVALID);
+                    continue;
+                }
+                for (uint64_t k = b; k < e; ++k)
+                {
+                    bool zero;
+                    if (delta.kind == GZK_KIND_I64)
+                        zero = __ldg(static_cast<const long long*>(delta.ptr) + k) == 0;
+                    else if (delta.kind == GZK_KIND_U32)
+                        zero = __ldg(static_cast<const uint32_t*>(delta.ptr) + k) == 0;
+                    else
+                        zero = load_fr(static_cast<const Fr*>(delta.ptr) + k).is_zero();
+                    if (zero)
+                    {
+                        out[k] = 1;
+                        break;
+                    }
+                }
+            }
+        }
+
+        unsigned blocks_for(gzk_ctx* ctx, uint64_t n)
+        {
+            uint64_t b = (n + kThreads - 1) / kThreads;
+            const uint64_t cap = static_cast<uint64_t>(ctx->sm_count) * 16;
+            if (b > cap) b = cap;
+            return b == 0 ? 1u : static_cast<unsigned>(b);
+        }
+        ColRef ref(const gzk_buf* b)
+        {
+            ColRef r;
+            r.ptr = b->dptr;
+            r.kind = b->kind;
+            return r;
+        }
+        int scalar_mont(gzk_ctx* ctx, const uint8_t* bytes, Fr* out)
+        {
+            bool canonical = false;
+            const Fr v = host_fr_from_bytes(bytes, &canonical);
+            if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
+            *out = to_mont(v);
+            return GZK_OK;
+        }
+        int finish_with_status(gzk_ctx* ctx, const char* message)
+        {
+            int status = 0;
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+            GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            if (status != 0) return fail(ctx, GZK_E_INVALID, message);
+            return GZK_OK;
+        }
+        bool index_kind_ok(const gzk_buf* b) { return b != nullptr && (b->kind == GZK_KIND_U32 || b->kind == GZK_KIND_I64); }
+    }
+}
+
+using namespace gzk;
+
+extern "C"
+{
+    int gzk_weighted_sum(gzk_ctx* ctx, const gzk_buf* left, const uint8_t lambda[32], const gzk_buf* right, size_t count,
+                         size_t domain_size, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (domain_size == 0) return GZK_OK;
+        if (left == nullptr || right == nullptr || lambda == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "weighted_sum: null argument");
+        if (count > domain_size || left->count < count || right->count < count) return fail(ctx, GZK_E_INVALID, "weighted_sum: input size mismatch");
+        if (out->kind != GZK_KIND_FR_MONT || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "weighted_sum: output must be a Montgomery buffer");
+        Fr l;
+        int rc = scalar_mont(ctx, lambda, &l);
+        if (rc != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "weighted_sum");
+            weighted_sum_kernel<<<blocks_for(ctx, domain_size), kThreads, 0, ctx->stream>>>(ref(left), ref(right), l, count, domain_size,
+                                                                                             static_cast<Fr*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_feature_lookup_rows(gzk_ctx* ctx, const gzk_buf* row_ids, const gzk_buf* feature_indices, const gzk_buf* features,
+                                size_t rows, size_t width, const uint8_t eta_index[32], const uint8_t eta_value[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (rows == 0 || width == 0) return GZK_OK;
+        if (row_ids == nullptr || feature_indices == nullptr || features == nullptr || out == nullptr || eta_index == nullptr || eta_value == nullptr)
+            return fail(ctx, GZK_E_INVALID, "feature_lookup_rows: null argument");
+        const uint64_t total = static_cast<uint64_t>(rows) * width;
+        if (row_ids->count < rows || feature_indices->count < width || features->count < total || width > 0xffffffffu)
+            return fail(ctx, GZK_E_INVALID, "feature_lookup_rows: input size mismatch");
+        if (out->kind != GZK_KIND_FR_MONT || out->count < total) return fail(ctx, GZK_E_INVALID, "feature_lookup_rows: output must be a Montgomery buffer");
+        Fr ei, ev;
+        int rc = scalar_mont(ctx, eta_index, &ei);
+        if (rc != GZK_OK) return rc;
+        if ((rc = scalar_mont(ctx, eta_value, &ev)) != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "feature_rows");
+            feature_rows_kernel<<<blocks_for(ctx, total), kThreads, 0, ctx->stream>>>(ref(row_ids), ref(feature_indices), ref(features), rows,
+                                                                                       static_cast<uint32_t>(width), ei, ev,
+                                                                                       static_cast<Fr*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_broadcast_node_values(gzk_ctx* ctx, const gzk_buf* node_values, size_t node_count, const gzk_buf* index, size_t edge_count,
+                                  size_t domain_size, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (domain_size == 0) return GZK_OK;
+        if (node_values == nullptr || out == nullptr || !index_kind_ok(index)) return fail(ctx, GZK_E_INVALID, "broadcast: index must be a U32 or I64 buffer");
+        if (node_values->count < node_count || index->count < edge_count || edge_count > domain_size)
+            return fail(ctx, GZK_E_INVALID, "broadcast: input size mismatch");
+        if (out->kind != node_values->kind || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "broadcast: output must have the kind of the node values");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        {
+            LaunchScope scope(ctx, "gather");
+            const unsigned blocks = blocks_for(ctx, domain_size);
+            if (node_values->elem_bytes == 32)
+                gather_kernel<ulonglong4><<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const ulonglong4*>(node_values->dptr), node_count, ref(index),
+                                                                                 edge_count, domain_size, static_cast<ulonglong4*>(out->dptr), ctx->d_status);
+            else if (node_values->elem_bytes == 8)
+                gather_kernel<unsigned long long><<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const unsigned long long*>(node_values->dptr), node_count,
+                                                                                         ref(index), edge_count, domain_size,
+                                                                                         static_cast<unsigned long long*>(out->dptr), ctx->d_status);
+            else
+                gather_kernel<uint32_t><<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint32_t*>(node_values->dptr), node_count, ref(index),
+                                                                               edge_count, domain_size, static_cast<uint32_t*>(out->dptr), ctx->d_status);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        return finish_with_status(ctx, "edge endpoint out of range");
+    }
+
+    int gzk_histogram(gzk_ctx* ctx, const gzk_buf* indices, size_t count, size_t domain_size, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (out == nullptr || out->kind != GZK_KIND_U32 || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "histogram: output must be a U32 buffer of the domain size");
+        if (count != 0 && (!index_kind_ok(indices) || indices->count < count)) return fail(ctx, GZK_E_INVALID, "histogram: indices must be a U32 or I64 buffer");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(out->dptr, 0, domain_size * sizeof(uint32_t), ctx->stream));
+        if (count != 0)
+        {
+            LaunchScope scope(ctx, "histogram");
+            histogram_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(ref(indices), count, domain_size, static_cast<uint32_t*>(out->dptr),
+                                                                                    ctx->d_status);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        return finish_with_status(ctx, "lookup index out of range");
+    }
+
+    int gzk_quantize(gzk_ctx* ctx, const gzk_buf* values, size_t count, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (count == 0) return GZK_OK;
+        if (values == nullptr || values->kind != GZK_KIND_F64 || values->count < count) return fail(ctx, GZK_E_INVALID, "quantize: input must be an F64 buffer");
+        if (out == nullptr || out->kind != GZK_KIND_I64 || out->count < count) return fail(ctx, GZK_E_INVALID, "quantize: output must be an I64 buffer");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "quantize");
+            quantize_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(static_cast<const double*>(values->dptr), count,
+                                                                                   static_cast<long long*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
+                              size_t domain_size, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (out == nullptr || out->kind != GZK_KIND_U32 || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "first_zero_marker: output must be a U32 buffer of the domain size");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(out->dptr, 0, domain_size * sizeof(uint32_t), ctx->stream));
+        if (groups != 0)
+        {
+            if (delta == nullptr || delta->kind == GZK_KIND_F64 || !index_kind_ok(group_begin) ||
+                !index_kind_ok(group_end) || group_begin->count < groups || group_end->count < groups)
+                return fail(ctx, GZK_E_INVALID, "first_zero_marker: input size mismatch");
+            LaunchScope scope(ctx, "first_zero");
+            first_zero_kernel<<<blocks_for(ctx, groups), kThreads, 0, ctx->stream>>>(ref(delta), ref(group_begin), ref(group_end), groups,
+                                                                                     delta->count < domain_size ? delta->count : domain_size,
+                                                                                     static_cast<uint32_t*>(out->dptr), ctx->d_status);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        return finish_with_status(ctx, "first_zero_marker: group bounds out of range");
+    }
+}

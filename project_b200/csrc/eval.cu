@@ -295,7 +295,7 @@ namespace gzk
         // Sums the per-tile partials of one (rotation, column) pair, reduces once and
         // writes the canonical result.
         __global__ void eval_finish_kernel(const uint32_t* partial, const int* kinds, uint32_t tiles, uint32_t p_count,
-                                           uint32_t k_count, Fr* out_canonical)
+                                           uint32_t k_count, Fr* out_canonical, int uniform_kind = -1, int out_montgomery = 0)
         {
             const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
             if (idx >= p_count * k_count) return;
@@ -318,7 +318,7 @@ namespace gzk
             // reduced = S * 2^-32 (canonical columns) -> times 2^288 via Montgomery
             // product with 2^544;  S * 2^224 (Montgomery columns) -> times 2^32 via 2^288.
             Fr fix;
-            if (kinds[k] == GZK_KIND_FR_MONT)
+            if ((kinds != nullptr ? kinds[k] : uniform_kind) == GZK_KIND_FR_MONT)
             {
                 constexpr uint32_t c288[8] = {0xcaaf6b13u, 0x355094eau, 0x69a568efu, 0xf6b10cb3u,
                                               0x40cc3869u, 0xe2c926a6u, 0xed269aadu, 0x736a6d3bu};
@@ -330,7 +330,7 @@ namespace gzk
                 fix = fr_const_2_544();
             }
             const Fr mont = mul(reduced, fix);  // Montgomery form of S
-            store_fr(out_canonical + idx, from_mont(mont));
+            store_fr(out_canonical + idx, out_montgomery ? mont : from_mont(mont));
         }
     }
 }
@@ -372,6 +372,21 @@ namespace gzk
             }
             if (x == 0x12345678u) sink[0] = x;  // practically never: defeats dead-code elimination
         }
+    }
+}
+
+namespace gzk
+{
+    // For the other inner-product kernels of the library, which produce partial sums
+    // in the same [tile][p][k][17] layout: sum over tiles, reduce once, write results.
+    int launch_eval_finish(gzk_ctx* ctx, const uint32_t* partial, int uniform_kind, uint32_t tiles, uint32_t k_count,
+                           Fr* out, bool out_montgomery)
+    {
+        LaunchScope scope(ctx, "eval_finish");
+        eval_finish_kernel<<<(k_count + 127) / 128, 128, 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
+                                                                          out_montgomery ? 1 : 0);
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        return GZK_OK;
     }
 }
 

@@ -1,0 +1,320 @@
+// Row-major matrix kernels of the binding / commitment path:
+//   matrix_horner      the matrix read as ONE coefficient polynomial (row-major
+//                      flattening) evaluated at a point;
+//   fold_rows          out[c] = sum_row w[row] * M[row][c];
+//   linear_form_rows   out[row] = sum_c M[row][c] * p[c];
+//   powers             1, c, c^2, ...
+#include <cstring>
+
+#include "block.cuh"
+
+namespace gzk
+{
+    int launch_eval_finish(gzk_ctx* ctx, const uint32_t* partial, int uniform_kind, uint32_t tiles, uint32_t k_count,
+                           Fr* out, bool out_montgomery);
+
+    namespace
+    {
+        constexpr int kThreads = 256;
+        constexpr int kAccLimbs = 17;
+
+        // ---- Horner ------------------------------------------------------------------
+        // CTA b owns coefficients [b*span, (b+1)*span).  Thread t runs Horner in x^T over
+        // the coefficients s+t, s+t+T, ... (coalesced across the CTA), scales by x^t; the
+        // CTA sum is scaled by x^s.  One Montgomery multiplication per coefficient.
+        __global__ void __launch_bounds__(kThreads) horner_kernel(ColRef coeffs, uint64_t total, uint64_t span, Fr x, Fr x_stride,
+                                                                  Fr* partial)
+        {
+            __shared__ Fr warp_sum[kThreads / 32];
+            const uint64_t s = static_cast<uint64_t>(blockIdx.x) * span;
+            const uint64_t e_end = s + span < total ? s + span : total;
+            Fr acc = Fr::zero();
+            if (s + threadIdx.x < e_end)
+            {
+                const uint64_t steps = (e_end - s - threadIdx.x - 1) / kThreads;  // last index = s + t + steps*T
+                for (uint64_t j = steps + 1; j-- > 0;)
+                {
+                    acc = mul(acc, x_stride);
+                    acc = add(acc, col_load_mont(coeffs, s + threadIdx.x + j * kThreads));
+                }
+                acc = mul(acc, pow_u64(x, threadIdx.x));
+            }
+            const int lane = threadIdx.x & 31;
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                const Fr other = shfl_fr_idx(acc, (lane + offset) & 31);
+                if (lane < offset) acc = add(acc, other);
+            }
+            if (lane == 0) warp_sum[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            if (threadIdx.x == 0)
+            {
+                Fr sum = warp_sum[0];
+#pragma unroll
+                for (int w = 1; w < kThreads / 32; ++w) sum = add(sum, warp_sum[w]);
+                store_fr(partial + blockIdx.x, mul(sum, pow_u64(x, s)));
+            }
+        }
+
+        __global__ void sum_partials_kernel(const Fr* partial, uint32_t count, Fr* out_canonical)
+        {
+            if (threadIdx.x != 0 || blockIdx.x != 0) return;
+            Fr sum = Fr::zero();
+            for (uint32_t i = 0; i < count; ++i) sum = add(sum, load_fr_plain(partial + i));
+            store_fr(out_canonical, from_mont(sum));
+        }
+
+        // ---- fold rows ----------------------------------------------------------------
+        // Raw limbs of a matrix entry for the unreduced accumulator: FR and FR_MONT
+        // entries are used as stored (the final reduction accounts for the form),
+        // small-integer kinds are widened to Montgomery form first.
+        __device__ __forceinline__ Fr entry_raw(const ColRef& m, uint64_t i)
+        {
+            if (m.kind == GZK_KIND_FR || m.kind == GZK_KIND_FR_MONT) return load_fr(static_cast<const Fr*>(m.ptr) + i);
+            return col_load_mont(m, i);
+        }
+
+        // CTA (tile, column chunk): threads are laid out as (row lane, column); each
+        // thread accumulates w[row] * M[row][c] unreduced over the rows of the tile that
+        // fall on its row lane; row lanes are then summed through shared memory.
+        __global__ void __launch_bounds__(kThreads) fold_rows_kernel(ColRef matrix, const Fr* weights, uint64_t row_count, uint32_t cols,
+                                                                     uint64_t tile_rows, uint32_t col_chunks, uint32_t* partial)
+        {
+            extern __shared__ uint32_t lanes_sum[];  // [kThreads][17]
+            const uint32_t tile = blockIdx.x / col_chunks;
+            const uint32_t chunk = blockIdx.x - tile * col_chunks;
+            const uint32_t width = cols < kThreads ? cols : kThreads;   // columns handled by this CTA
+            const uint32_t row_lanes = kThreads / width;
+            const uint32_t c_local = threadIdx.x % width;
+            const uint32_t row_lane = threadIdx.x / width;
+            const uint32_t c = chunk * kThreads + c_local;
+            const uint64_t r_begin = static_cast<uint64_t>(tile) * tile_rows;
+            const uint64_t r_end = r_begin + tile_rows < row_count ? r_begin + tile_rows : row_count;
+            WideAcc acc;
+            acc.clear();
+            if (row_lane < row_lanes && c < cols)
+            {
+                for (uint64_t row = r_begin + row_lane; row < r_end; row += row_lanes)
+                {
+                    const Fr w = load_fr(weights + row);
+                    const Fr v = entry_raw(matrix, row * cols + c);
+                    acc.mac<8>(w.l, v.l);
+                }
+            }
+            uint32_t sum[kAccLimbs];
+            acc.fold(sum);
+#pragma unroll
+            for (int i = 0; i < kAccLimbs; ++i) lanes_sum[threadIdx.x * kAccLimbs + i] = sum[i];
+            __syncthreads();
+            if (row_lane == 0 && c < cols)
+            {
+                for (uint32_t rl = 1; rl < row_lanes; ++rl)
+                {
+                    uint32_t other[kAccLimbs];
+#pragma unroll
+                    for (int i = 0; i < kAccLimbs; ++i) other[i] = lanes_sum[(rl * width + c_local) * kAccLimbs + i];
+                    acc_add<kAccLimbs, kAccLimbs>(sum, other);
+                }
+                uint32_t* dst = partial + (static_cast<uint64_t>(tile) * cols + c) * kAccLimbs;
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) dst[i] = sum[i];
+            }
+        }
+
+        // ---- linear form over rows -------------------------------------------------------
+        // One warp per row: lanes stride over the columns, exact warp sum, one reduction.
+        __global__ void __launch_bounds__(kThreads) linear_form_kernel(ColRef matrix, const Fr* powers, uint64_t rows, uint32_t cols, Fr* out)
+        {
+            const uint32_t lane = threadIdx.x & 31;
+            const uint64_t row = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+            if (row >= rows) return;
+            WideAcc acc;
+            acc.clear();
+            for (uint32_t j = lane; j < cols; j += 32)
+            {
+                const Fr p = load_fr(powers + j);
+                const Fr v = entry_raw(matrix, row * cols + j);
+                acc.mac<8>(p.l, v.l);
+            }
+            uint32_t sum[kAccLimbs];
+            acc.fold(sum);
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                uint32_t other[kAccLimbs];
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, sum[i], offset);
+                acc_add<kAccLimbs, kAccLimbs>(sum, other);
+            }
+            if (lane == 0)
+            {
+                const Fr reduced = redc_wide<FrCfg, 9>(sum);
+                Fr fix;
+                if (matrix.kind == GZK_KIND_FR)
+                {
+                    fix = fr_const_2_544();
+                }
+                else
+                {
+                    constexpr uint32_t c288[8] = {0xcaaf6b13u, 0x355094eau, 0x69a568efu, 0xf6b10cb3u,
+                                                  0x40cc3869u, 0xe2c926a6u, 0xed269aadu, 0x736a6d3bu};
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) fix.l[i] = c288[i];
+                }
+                store_fr(out + row, mul(reduced, fix));
+            }
+        }
+
+        __global__ void powers_kernel(Fr c, uint64_t count, Fr* out)
+        {
+            const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            if (i < count) store_fr(out + i, pow_u64(c, i));
+        }
+
+        int scalar_mont(gzk_ctx* ctx, const uint8_t* bytes, Fr* out)
+        {
+            bool canonical = false;
+            const Fr v = host_fr_from_bytes(bytes, &canonical);
+            if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
+            *out = to_mont(v);
+            return GZK_OK;
+        }
+    }
+}
+
+using namespace gzk;
+
+extern "C"
+{
+    int gzk_matrix_horner(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const uint8_t x_bytes[32], uint8_t out[32])
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (x_bytes == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "matrix_horner: null argument");
+        const uint64_t total = static_cast<uint64_t>(rows) * cols;
+        if (total == 0)
+        {
+            std::memset(out, 0, 32);  // matrix_row_major_evaluation returns zero for an empty matrix
+            return GZK_OK;
+        }
+        if (matrix == nullptr || matrix->count < total) return fail(ctx, GZK_E_INVALID, "matrix_horner: matrix buffer too small");
+        Fr x;
+        int rc = scalar_mont(ctx, x_bytes, &x);
+        if (rc != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        uint64_t ctas = (total + static_cast<uint64_t>(kThreads) * 8 - 1) / (static_cast<uint64_t>(kThreads) * 8);
+        const uint64_t max_ctas = static_cast<uint64_t>(ctx->sm_count) * 8;
+        if (ctas > max_ctas) ctas = max_ctas;
+        uint64_t span = (total + ctas - 1) / ctas;
+        span = (span + kThreads - 1) / kThreads * kThreads;
+        ctas = (total + span - 1) / span;
+        void* scratch = nullptr;
+        if ((rc = ensure_scratch(ctx, 2, (ctas + 1) * sizeof(Fr), &scratch)) != GZK_OK) return rc;
+        Fr* partial = static_cast<Fr*>(scratch);
+        ColRef m;
+        m.ptr = matrix->dptr;
+        m.kind = matrix->kind;
+        {
+            LaunchScope scope(ctx, "horner");
+            horner_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, total, span, x, pow_u64(x, kThreads), partial);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            LaunchScope scope(ctx, "horner_sum");
+            sum_partials_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(ctas), partial + ctas);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out, partial + ctas, 32, cudaMemcpyDeviceToHost, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_fold_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* row_weights, size_t row_count,
+                      gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (cols == 0 || rows == 0) return GZK_OK;  // weighted_column_sum_native returns {} for an empty matrix
+        if (matrix == nullptr || row_weights == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "fold_rows: null argument");
+        if (row_count > rows || row_count > row_weights->count || matrix->count < static_cast<uint64_t>(rows) * cols)
+            return fail(ctx, GZK_E_INVALID, "weighted column sum native input size mismatch");
+        if (row_weights->kind != GZK_KIND_FR_MONT) return fail(ctx, GZK_E_INVALID, "fold_rows: weights must be a Montgomery buffer");
+        if (out->kind != GZK_KIND_FR || out->count < cols) return fail(ctx, GZK_E_INVALID, "fold_rows: output must be an FR buffer of cols elements");
+        if (cols > (1u << 24)) return fail(ctx, GZK_E_INVALID, "fold_rows: too many columns");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        const uint32_t col_chunks = static_cast<uint32_t>((cols + kThreads - 1) / kThreads);
+        const uint32_t width = cols < kThreads ? static_cast<uint32_t>(cols) : kThreads;
+        const uint32_t row_lanes = kThreads / width;
+        // enough tiles to fill the machine, each tile at least 8 rows per row lane
+        uint64_t tiles = static_cast<uint64_t>(ctx->sm_count) * 4 / col_chunks;
+        const uint64_t max_tiles = (row_count + 8ull * row_lanes - 1) / (8ull * row_lanes);
+        if (tiles > max_tiles) tiles = max_tiles;
+        if (tiles > 1024) tiles = 1024;
+        if (tiles == 0) tiles = 1;
+        const uint64_t tile_rows = (row_count + tiles - 1) / tiles > 0 ? (row_count + tiles - 1) / tiles : 1;
+        tiles = row_count == 0 ? 1 : (row_count + tile_rows - 1) / tile_rows;
+        void* scratch = nullptr;
+        int rc = ensure_scratch(ctx, 1, tiles * cols * kAccLimbs * sizeof(uint32_t), &scratch);
+        if (rc != GZK_OK) return rc;
+        ColRef m;
+        m.ptr = matrix->dptr;
+        m.kind = matrix->kind;
+        const size_t smem = static_cast<size_t>(kThreads) * kAccLimbs * sizeof(uint32_t);
+        {
+            LaunchScope scope(ctx, "fold_rows");
+            fold_rows_kernel<<<static_cast<unsigned>(tiles * col_chunks), kThreads, smem, ctx->stream>>>(
+                m, static_cast<const Fr*>(row_weights->dptr), row_count, static_cast<uint32_t>(cols), tile_rows, col_chunks,
+                static_cast<uint32_t*>(scratch));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        const int form = matrix->kind == GZK_KIND_FR ? GZK_KIND_FR : GZK_KIND_FR_MONT;
+        if ((rc = launch_eval_finish(ctx, static_cast<const uint32_t*>(scratch), form, static_cast<uint32_t>(tiles),
+                                     static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr), false)) != GZK_OK)
+            return rc;
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_linear_form_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* column_powers, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (rows == 0) return GZK_OK;
+        if (matrix == nullptr || column_powers == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "linear_form_rows: null argument");
+        if (matrix->count < static_cast<uint64_t>(rows) * cols || column_powers->count < cols)
+            return fail(ctx, GZK_E_INVALID, "linear_form_rows: input size mismatch");
+        if (column_powers->kind != GZK_KIND_FR_MONT) return fail(ctx, GZK_E_INVALID, "linear_form_rows: powers must be a Montgomery buffer");
+        if (out->kind != GZK_KIND_FR_MONT || out->count < rows) return fail(ctx, GZK_E_INVALID, "linear_form_rows: output must be a Montgomery buffer of rows elements");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        ColRef m;
+        m.ptr = matrix->dptr;
+        m.kind = matrix->kind;
+        const uint64_t warps_per_cta = kThreads / 32;
+        const uint64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
+        {
+            LaunchScope scope(ctx, "linear_form");
+            linear_form_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, static_cast<const Fr*>(column_powers->dptr), rows,
+                                                                                         static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_powers(gzk_ctx* ctx, const uint8_t challenge[32], size_t count, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (count == 0) return GZK_OK;
+        if (challenge == nullptr || out == nullptr || out->kind != GZK_KIND_FR_MONT || out->count < count)
+            return fail(ctx, GZK_E_INVALID, "powers: output must be a Montgomery buffer of count elements");
+        Fr c;
+        int rc = scalar_mont(ctx, challenge, &c);
+        if (rc != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "powers");
+            powers_kernel<<<static_cast<unsigned>((count + 127) / 128), 128, 0, ctx->stream>>>(c, count, static_cast<Fr*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+}

@@ -11,8 +11,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libgatzk_b200.so")
 
-KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32 = 0, 1, 2, 3
-_KIND_DTYPE = {KIND_FR: (np.uint8, 32), KIND_FR_MONT: (np.uint8, 32), KIND_I64: (np.int64, 1), KIND_U32: (np.uint32, 1)}
+KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, KIND_F64 = 0, 1, 2, 3, 4
+_KIND_DTYPE = {KIND_FR: (np.uint8, 32), KIND_FR_MONT: (np.uint8, 32), KIND_I64: (np.int64, 1), KIND_U32: (np.uint32, 1), KIND_F64: (np.float64, 1)}
 
 _lib = None
 
@@ -184,6 +184,57 @@ class Backend:
         mu = np.zeros(32, dtype=np.uint8)
         self._check(self.lib.gzk_zkmap_accumulator(self.ctx, a.handle, b.handle, _sz(count), _sz(domain_size), out.handle, _ptr(mu)))
         return out, mu
+
+    def matrix_horner(self, matrix, rows, cols, x):
+        out = np.zeros(32, dtype=np.uint8)
+        self._check(self.lib.gzk_matrix_horner(self.ctx, matrix.handle, _sz(rows), _sz(cols), _ptr(_fr(x)), _ptr(out)))
+        return out
+
+    def fold_rows(self, matrix, rows, cols, weights, row_count):
+        out = self.alloc(KIND_FR, cols)
+        self._check(self.lib.gzk_fold_rows(self.ctx, matrix.handle, _sz(rows), _sz(cols), weights.handle, _sz(row_count), out.handle))
+        return out
+
+    def linear_form_rows(self, matrix, rows, cols, powers):
+        out = self.alloc(KIND_FR_MONT, rows)
+        self._check(self.lib.gzk_linear_form_rows(self.ctx, matrix.handle, _sz(rows), _sz(cols), powers.handle, out.handle))
+        return out
+
+    def powers(self, challenge, count):
+        out = self.alloc(KIND_FR_MONT, count)
+        self._check(self.lib.gzk_powers(self.ctx, _ptr(_fr(challenge)), _sz(count), out.handle))
+        return out
+
+    def weighted_sum(self, left, lam, right, count, domain_size):
+        out = self.alloc(KIND_FR_MONT, domain_size)
+        self._check(self.lib.gzk_weighted_sum(self.ctx, left.handle, _ptr(_fr(lam)), right.handle, _sz(count), _sz(domain_size), out.handle))
+        return out
+
+    def feature_lookup_rows(self, row_ids, feature_indices, features, rows, width, eta_index, eta_value):
+        out = self.alloc(KIND_FR_MONT, rows * width)
+        self._check(self.lib.gzk_feature_lookup_rows(self.ctx, row_ids.handle, feature_indices.handle, features.handle, _sz(rows), _sz(width),
+                                                     _ptr(_fr(eta_index)), _ptr(_fr(eta_value)), out.handle))
+        return out
+
+    def broadcast_node_values(self, node_values, node_count, index, edge_count, domain_size):
+        out = self.alloc(node_values.kind, domain_size)
+        self._check(self.lib.gzk_broadcast_node_values(self.ctx, node_values.handle, _sz(node_count), index.handle, _sz(edge_count), _sz(domain_size), out.handle))
+        return out
+
+    def histogram(self, indices, count, domain_size):
+        out = self.alloc(KIND_U32, domain_size)
+        self._check(self.lib.gzk_histogram(self.ctx, indices.handle, _sz(count), _sz(domain_size), out.handle))
+        return out
+
+    def quantize(self, values, count):
+        out = self.alloc(KIND_I64, count)
+        self._check(self.lib.gzk_quantize(self.ctx, values.handle, _sz(count), out.handle))
+        return out
+
+    def first_zero_marker(self, delta, group_begin, group_end, groups, domain_size):
+        out = self.alloc(KIND_U32, domain_size)
+        self._check(self.lib.gzk_first_zero_marker(self.ctx, delta.handle, group_begin.handle, group_end.handle, _sz(groups), _sz(domain_size), out.handle))
+        return out
 
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])

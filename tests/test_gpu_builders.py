@@ -113,3 +113,102 @@ def test_zkmap_accumulator(be, count, domain):
     assert np.array_equal(mu, want_mu)
     with pytest.raises(GzkError):
         be.zkmap_accumulator(be.upload(a, KIND_FR), be.upload(b, KIND_FR), domain, domain)
+
+
+@pytest.mark.parametrize("rows,cols", [(1, 1), (9, 5), (1, 3000), (300, 64), (2500, 8), (70, 300)])
+def test_matrix_horner(be, rows, cols):
+    from project_b200 import KIND_FR
+
+    rng = np.random.default_rng(rows * 1000 + cols)
+    m = rand_fr(rng, rows * cols).reshape(rows, cols, 32)
+    x = fr_array([int(rng.integers(2, 1 << 62))])
+    got = be.matrix_horner(be.upload(m, KIND_FR), rows, cols, x)
+    assert np.array_equal(got, ora.matrix_row_major_eval(m, x))
+    if rows == 1:
+        assert np.array_equal(got, ora.horner(m[0], x))
+
+
+def test_matrix_horner_empty_and_small_ints(be):
+    from project_b200 import KIND_FR, KIND_I64
+
+    x = fr_array([77])
+    empty = be.upload(np.zeros((1, 32), dtype=np.uint8), KIND_FR)
+    assert not be.matrix_horner(empty, 0, 5, x).any()
+    rng = np.random.default_rng(3)
+    vals = rng.integers(-4096, 4096, size=(40, 16), dtype=np.int64)
+    got = be.matrix_horner(be.upload(vals, KIND_I64), 40, 16, x)
+    assert np.array_equal(got, ora.matrix_row_major_eval(ora.fr_from_i64(vals.reshape(-1)).reshape(40, 16, 32), x))
+
+
+@pytest.mark.parametrize("rows,cols,row_count", [(9, 5, 7), (300, 8, 300), (5000, 64, 4321), (700, 256, 700), (130, 300, 100)])
+def test_fold_rows_and_linear_form(be, rows, cols, row_count):
+    from project_b200 import KIND_FR, KIND_FR_MONT
+
+    rng = np.random.default_rng(rows + cols)
+    m = rand_fr(rng, rows * cols).reshape(rows, cols, 32)
+    w = rand_fr(rng, rows)
+    mb = be.upload(m, KIND_FR)
+    got = be.fold_rows(mb, rows, cols, be.upload(w, KIND_FR_MONT), row_count).download()
+    assert np.array_equal(got, ora.weighted_column_sum(m, w, row_count))
+    # Montgomery-form matrix gives the same values
+    got = be.fold_rows(be.upload(m, KIND_FR_MONT), rows, cols, be.upload(w, KIND_FR_MONT), row_count).download()
+    assert np.array_equal(got, ora.weighted_column_sum(m, w, row_count))
+    c = fr_array([int(rng.integers(2, 1 << 62))])
+    pw = be.powers(c, cols)
+    assert np.array_equal(pw.download(), ora.powers(c, cols))
+    got = be.linear_form_rows(mb, rows, cols, pw).download()
+    assert np.array_equal(got, ora.linear_form_by_powers(m, ora.powers(c, cols)))
+
+
+def test_elementwise_leaves(be):
+    from project_b200 import KIND_FR, KIND_F64, KIND_I64, KIND_U32, GzkError
+
+    rng = np.random.default_rng(11)
+    n, count = 5000, 4100
+    left, right = rand_fr(rng, count), rand_fr(rng, count)
+    lam = rand_fr(rng, 1)[0]
+    got = be.weighted_sum(be.upload(left, KIND_FR), lam, be.upload(right, KIND_FR), count, n).download()
+    assert np.array_equal(got, ora.weighted_sum(left, lam, right, n))
+
+    rows, width = 37, 50
+    feats = rng.integers(0, 16, size=(rows, width), dtype=np.int64)
+    row_ids = np.arange(rows, dtype=np.uint32)
+    fidx = np.arange(width, dtype=np.uint32)
+    ei, ev = rand_fr(rng, 1)[0], rand_fr(rng, 1)[0]
+    got = be.feature_lookup_rows(be.upload(row_ids, KIND_U32), be.upload(fidx, KIND_U32), be.upload(feats, KIND_I64), rows, width, ei, ev).download()
+    want = ora.feature_lookup_rows(fr_array(range(rows)), fr_array(range(width)), ora.fr_from_i64(feats.reshape(-1)).reshape(rows, width, 32), ei, ev)
+    assert np.array_equal(got, want)
+
+    nodes, edges, domain = 300, 2000, 2048
+    node_vals = rand_fr(rng, nodes)
+    idx = rng.integers(0, nodes, size=edges, dtype=np.int64)
+    got = be.broadcast_node_values(be.upload(node_vals, KIND_FR), nodes, be.upload(idx, KIND_I64), edges, domain).download()
+    assert np.array_equal(got, ora.broadcast_node_values(node_vals, idx, domain))
+    node_i = rng.integers(-4000, 4000, size=nodes, dtype=np.int64)
+    got = be.broadcast_node_values(be.upload(node_i, KIND_I64), nodes, be.upload(idx.astype(np.uint32), KIND_U32), edges, domain).download()
+    assert np.array_equal(got[:edges], node_i[idx]) and not got[edges:].any()
+    bad = idx.copy()
+    bad[5] = nodes
+    with pytest.raises(GzkError, match="out of range"):
+        be.broadcast_node_values(be.upload(node_i, KIND_I64), nodes, be.upload(bad, KIND_I64), edges, domain)
+
+    table = 4096
+    hits = rng.integers(0, table, size=50000, dtype=np.int64)
+    got = be.histogram(be.upload(hits, KIND_I64), hits.size, table).download()
+    want = ora.multiplicity_from_indices(hits, table)
+    assert np.array_equal(fr_array([int(v) for v in got]), want)
+    with pytest.raises(GzkError, match="out of range"):
+        be.histogram(be.upload(np.array([table], dtype=np.int64), KIND_I64), 1, table)
+
+    vals = np.concatenate([rng.normal(0, 20, size=20000), np.array([0.0, 0.03125, -0.03125, 0.031249999, 1e-300, -1e-300, 255.96875, -255.96875]),
+                           (rng.integers(-8000, 8000, size=4000) + 0.5) / 16.0])
+    got = be.quantize(be.upload(vals, KIND_F64), vals.size).download()
+    assert np.array_equal(got, ora.quantize(vals))
+
+    delta = rng.integers(0, 3, size=1000, dtype=np.int64)
+    cuts = np.sort(rng.choice(np.arange(1, 1000), size=120, replace=False))
+    gb = np.concatenate([[0], cuts]).astype(np.int64)
+    ge = np.concatenate([cuts, [1000]]).astype(np.int64)
+    got = be.first_zero_marker(be.upload(delta, KIND_I64), be.upload(gb, KIND_I64), be.upload(ge, KIND_I64), gb.size, 1024).download()
+    want = ora.first_zero_marker(ora.fr_from_i64(np.concatenate([delta, np.ones(24, dtype=np.int64)])), gb, ge, 1024)
+    assert np.array_equal(fr_array([int(v) for v in got]), want)
