@@ -41,6 +41,7 @@ extern "C" {
 #define GZK_KIND_I64 2
 #define GZK_KIND_U32 3
 #define GZK_KIND_F64 4   /* IEEE doubles: input of gzk_quantize only */
+#define GZK_KIND_G1 5    /* affine G1 points, 96 bytes; wire format on upload/download, Montgomery on the device */
 
 typedef struct gzk_ctx gzk_ctx;
 typedef struct gzk_buf gzk_buf;
@@ -191,6 +192,31 @@ int gzk_histogram(gzk_ctx* ctx, const gzk_buf* indices, size_t count, size_t dom
 int gzk_quantize(gzk_ctx* ctx, const gzk_buf* values, size_t count, gzk_buf* out);
 int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
                           size_t domain_size, gzk_buf* out);
+
+/* ---- a5: G1 -----------------------------------------------------------------------------------
+ * gzk_g1_mul_same_base: points[k] = [scalars[k]] base for K host scalars (32-byte
+ * canonical) -> K affine points (96 bytes each).  Replaces g1_mul_same_base_batch /
+ * mcl::G1::mulEach (src/crypto/curve.cpp:138-238) and batch_quotient_commitments
+ * (src/protocol/prover.cpp:2220-2247).  A window table of the base is built on first
+ * use and stays resident on the context.  The base is an argument because the
+ * reference derives its generator with mcl's hashAndMapToG1 (src/crypto/kzg.cpp:383).
+ * gzk_g1_fixed_base_mul: same for a device scalar buffer (FR or FR_MONT) into a G1 buffer.
+ * gzk_commit_batch: tau-evaluations (gzk_eval_batch, rotation 0, valid prefix len) followed
+ * by the same-base multiplication: KZG::commit_batch (src/crypto/kzg.cpp:458-542);
+ * returns both the scalars p_k(tau) (Commitment::tau_evaluation) and the points. */
+int gzk_g1_mul_same_base(gzk_ctx* ctx, const uint8_t base[96], const uint8_t* scalars_host, size_t count, uint8_t* points_out_host);
+int gzk_g1_fixed_base_mul(gzk_ctx* ctx, const uint8_t base[96], const gzk_buf* scalars, size_t count, gzk_buf* out);
+int gzk_commit_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n, const gzk_buf* weights_tau,
+                     const uint8_t base[96], uint8_t* tau_evals_out, uint8_t* points_out);
+
+/* ---- MSM (kernel sweep; honest-prover commitment) ----------------------------------------------
+ * gzk_msm: out = sum_i [scalars[i]] points[i]; scalars FR or FR_MONT, points a G1
+ * buffer.  Pippenger with signed-digit windows and XYZZ buckets.  No reference caller:
+ * the reference commits with the trapdoor (src/crypto/kzg.cpp:402-419); against the
+ * Lagrange SRS of gzk_srs_lagrange the MSM of a column equals that commitment.
+ * gzk_srs_lagrange: out_points[i] = [L_i(tau)] base over the 2^log2n domain. */
+int gzk_msm(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, size_t n, uint8_t out[96]);
+int gzk_srs_lagrange(gzk_ctx* ctx, unsigned log2n, const uint8_t base[96], const uint8_t tau[32], gzk_buf* out_points);
 
 /* ---- packed evaluation without any allocation ------------------------------------
  * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that

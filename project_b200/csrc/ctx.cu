@@ -6,6 +6,9 @@
 
 namespace gzk
 {
+    int launch_convert_fp(gzk_ctx* ctx, const void* in, void* out, size_t fp_count, bool to_montgomery);
+    void g1_release_tables(gzk_ctx* ctx);
+
     int fail(gzk_ctx* ctx, int code, const std::string& message)
     {
         if (ctx != nullptr) ctx->last_error = message;
@@ -280,6 +283,7 @@ extern "C"
         if (ctx->pinned != nullptr) cudaFreeHost(ctx->pinned);
         if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
         timing_collect(ctx);
+        g1_release_tables(ctx);
         for (auto e : ctx->event_pool) cudaEventDestroy(e);
         cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -340,6 +344,7 @@ extern "C"
         case GZK_KIND_I64:
         case GZK_KIND_F64: elem = 8; break;
         case GZK_KIND_U32: elem = 4; break;
+        case GZK_KIND_G1: elem = 96; break;
         default: return fail(ctx, GZK_E_INVALID, "unknown buffer kind");
         }
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
@@ -384,6 +389,11 @@ extern "C"
             convert_kernel<<<blocks, 256, 0, ctx->stream>>>(p, p, count, 1);
             GZK_CUDA_TRY(ctx, cudaGetLastError());
         }
+        if (buf->kind == GZK_KIND_G1)
+        {
+            const int rc = launch_convert_fp(ctx, dst, dst, count * 2, true);
+            if (rc != GZK_OK) return rc;
+        }
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return GZK_OK;
     }
@@ -411,6 +421,21 @@ extern "C"
                 }
                 GZK_CUDA_TRY(ctx, cudaGetLastError());
                 GZK_CUDA_TRY(ctx, cudaMemcpyAsync(static_cast<char*>(host) + done * 32, tmp, cur * 32, cudaMemcpyDeviceToHost, ctx->stream));
+                GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+            }
+            return GZK_OK;
+        }
+        if (buf->kind == GZK_KIND_G1)
+        {
+            const size_t chunk = static_cast<size_t>(1) << 18;
+            void* tmp = nullptr;
+            int rc = ensure_scratch(ctx, 3, (count < chunk ? count : chunk) * 96, &tmp);
+            if (rc != GZK_OK) return rc;
+            for (size_t done = 0; done < count; done += chunk)
+            {
+                const size_t cur = count - done < chunk ? count - done : chunk;
+                if ((rc = launch_convert_fp(ctx, src + done * 96, tmp, cur * 2, false)) != GZK_OK) return rc;
+                GZK_CUDA_TRY(ctx, cudaMemcpyAsync(static_cast<char*>(host) + done * 96, tmp, cur * 96, cudaMemcpyDeviceToHost, ctx->stream));
                 GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
             }
             return GZK_OK;

@@ -1,0 +1,306 @@
+// G1 multi-scalar multiplication sum_i [s_i] P_i by the bucket (Pippenger) method
+// with signed-digit windows and XYZZ bucket accumulators.
+//
+//   1. digits     every scalar is cut into W signed c-bit digits; per (window, |digit|)
+//                 bucket the number of hits is counted
+//   2. offsets    exclusive scan of the bucket counts (one CTA)
+//   3. scatter    (point index, sign) pairs are written bucket by bucket
+//   4. buckets    one thread per bucket adds its points (mixed XYZZ additions)
+//   5. bits       sum_j j*B_j is split by the bits of j: for every (window, bit) one
+//                 CTA sums the buckets whose multiplier has that bit set
+//   6. finish     per window Horner over the bits, shift by 2^(c*w), sum, to affine
+//
+// Signed digits halve the bucket count (2^(c-1) per window): a negative digit adds
+// the negated point.  Group sums do not depend on the order of additions, so the
+// atomics of steps 1 and 3 leave the result bit-identical from run to run.
+#include <cstring>
+
+#include "block.cuh"
+#include "g1.cuh"
+
+namespace gzk
+{
+    namespace
+    {
+        constexpr int kThreads = 128;
+        constexpr int kMaxWindows = 32;
+
+        struct MsmPlan
+        {
+            uint32_t c;        // window bits
+            uint32_t windows;  // ceil(256 / c)
+            uint32_t half;     // 2^(c-1) buckets per window
+        };
+
+        // code[w*n + i] = 0 for a zero digit, else ((|d|-1) << 1 | negative) + 1
+        __global__ void __launch_bounds__(kThreads) msm_digits_kernel(ColRef scalars, uint64_t n, MsmPlan plan, uint32_t* code,
+                                                                     uint32_t* bucket_count)
+        {
+            const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            if (i >= n) return;
+            Fr s = load_fr(static_cast<const Fr*>(scalars.ptr) + i);
+            if (scalars.kind == GZK_KIND_FR_MONT) s = from_mont(s);
+            uint32_t carry = 0;
+            for (uint32_t w = 0; w < plan.windows; ++w)
+            {
+                const uint32_t bit = w * plan.c;
+                uint32_t raw = 0;
+                if (bit < 256)
+                {
+                    const uint32_t limb = bit >> 5, shift = bit & 31;
+                    uint64_t two = s.l[limb];
+                    if (limb + 1 < 8) two |= static_cast<uint64_t>(s.l[limb + 1]) << 32;
+                    raw = static_cast<uint32_t>(two >> shift) & ((1u << plan.c) - 1u);
+                }
+                uint32_t d = raw + carry;
+                uint32_t negative = 0;
+                carry = 0;
+                if (d > plan.half)
+                {
+                    d = (1u << plan.c) - d;
+                    negative = 1;
+                    carry = 1;
+                }
+                uint32_t out = 0;
+                if (d != 0)
+                {
+                    out = (((d - 1) << 1) | negative) + 1;
+                    atomicAdd(bucket_count + static_cast<uint64_t>(w) * plan.half + (d - 1), 1u);
+                }
+                code[static_cast<uint64_t>(w) * n + i] = out;
+            }
+        }
+
+        // exclusive scan of `count` uint32 values by one CTA (in place); also zeroes `cursor`
+        __global__ void __launch_bounds__(1024) msm_offsets_kernel(uint32_t* values, uint32_t* cursor, uint32_t count)
+        {
+            __shared__ uint32_t warp_totals[32];
+            __shared__ uint32_t carry_in;
+            const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            if (threadIdx.x == 0) carry_in = 0;
+            __syncthreads();
+            for (uint32_t base = 0; base < count; base += 1024)
+            {
+                const uint32_t idx = base + threadIdx.x;
+                const uint32_t v = idx < count ? values[idx] : 0;
+                uint32_t incl = v;
+#pragma unroll
+                for (int offset = 1; offset < 32; offset <<= 1)
+                {
+                    const uint32_t up = __shfl_up_sync(0xffffffffu, incl, offset);
+                    if (lane >= static_cast<uint32_t>(offset)) incl += up;
+                }
+                if (lane == 31) warp_totals[warp] = incl;
+                __syncthreads();
+                uint32_t warp_offset = 0;
+                for (uint32_t w2 = 0; w2 < warp; ++w2) warp_offset += warp_totals[w2];
+                const uint32_t start = carry_in;
+                if (idx < count)
+                {
+                    values[idx] = start + warp_offset + incl - v;
+                    cursor[idx] = 0;
+                }
+                __syncthreads();
+                if (threadIdx.x == 1023) carry_in = start + warp_offset + incl;
+                __syncthreads();
+            }
+        }
+
+        __global__ void __launch_bounds__(kThreads) msm_scatter_kernel(const uint32_t* code, uint64_t n, MsmPlan plan,
+                                                                      const uint32_t* bucket_start, uint32_t* cursor, uint32_t* entries)
+        {
+            const uint64_t total = n * plan.windows;
+            const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+            for (uint64_t t = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < total; t += stride)
+            {
+                const uint32_t v = code[t];
+                if (v == 0) continue;
+                const uint64_t w = t / n;
+                const uint64_t i = t - w * n;
+                const uint32_t payload = v - 1;
+                const uint64_t bucket = w * plan.half + (payload >> 1);
+                const uint32_t pos = atomicAdd(cursor + bucket, 1u);
+                entries[bucket_start[bucket] + pos] = (static_cast<uint32_t>(i) << 1) | (payload & 1u);
+            }
+        }
+
+        __global__ void __launch_bounds__(kThreads) msm_buckets_kernel(const G1Affine* points, const uint32_t* bucket_start,
+                                                                      const uint32_t* bucket_size, const uint32_t* entries,
+                                                                      uint32_t buckets, G1Xyzz* out)
+        {
+            const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+            if (b >= buckets) return;
+            const uint32_t start = bucket_start[b], size = bucket_size[b];
+            G1Xyzz acc = G1Xyzz::infinity();
+#pragma unroll 1
+            for (uint32_t k = 0; k < size; ++k)
+            {
+                const uint32_t e = entries[start + k];
+                acc = g1_add_mixed(acc, load_affine(points + (e >> 1)), (e & 1u) != 0);
+            }
+            store_xyzz(out + b, acc);
+        }
+
+        // CTA (window w, bit b): sum of the buckets j (multiplier j+1) with bit b of (j+1) set
+        __global__ void __launch_bounds__(kThreads) msm_bits_kernel(const G1Xyzz* buckets, MsmPlan plan, G1Xyzz* bit_sums)
+        {
+            __shared__ G1Xyzz slots[kThreads];
+            const uint32_t w = blockIdx.x / plan.c, bit = blockIdx.x % plan.c;
+            G1Xyzz acc = G1Xyzz::infinity();
+            for (uint32_t j = threadIdx.x; j < plan.half; j += kThreads)
+                if (((j + 1) >> bit) & 1u) acc = g1_add(acc, load_xyzz(buckets + static_cast<uint64_t>(w) * plan.half + j));
+            slots[threadIdx.x] = acc;
+            __syncthreads();
+            for (uint32_t offset = kThreads / 2; offset > 0; offset >>= 1)
+            {
+                if (threadIdx.x < offset) slots[threadIdx.x] = g1_add(slots[threadIdx.x], slots[threadIdx.x + offset]);
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) store_xyzz(bit_sums + blockIdx.x, slots[0]);
+        }
+
+        // one thread per window, then a tree over the windows; thread 0 converts to affine
+        __global__ void __launch_bounds__(kMaxWindows) msm_finish_kernel(const G1Xyzz* bit_sums, MsmPlan plan, G1Xyzz* out_xyzz,
+                                                                        G1Affine* out_canonical)
+        {
+            __shared__ G1Xyzz slots[kMaxWindows];
+            const uint32_t w = threadIdx.x;
+            G1Xyzz acc = G1Xyzz::infinity();
+            if (w < plan.windows)
+            {
+                for (int bit = static_cast<int>(plan.c) - 1; bit >= 0; --bit)
+                {
+                    acc = g1_double(acc);
+                    acc = g1_add(acc, load_xyzz(bit_sums + w * plan.c + bit));
+                }
+                for (uint32_t k = 0; k < w * plan.c; ++k) acc = g1_double(acc);
+            }
+            slots[w] = acc;
+            __syncthreads();
+            for (uint32_t offset = kMaxWindows / 2; offset > 0; offset >>= 1)
+            {
+                if (w < offset) slots[w] = g1_add(slots[w], slots[w + offset]);
+                __syncthreads();
+            }
+            if (w == 0)
+            {
+                store_xyzz(out_xyzz, slots[0]);
+                G1Affine a = g1_to_affine(slots[0]);
+                a.x = from_mont(a.x);
+                a.y = from_mont(a.y);
+                store_affine(out_canonical, a);
+            }
+        }
+
+        MsmPlan make_plan(uint64_t n)
+        {
+            uint32_t log2n = 0;
+            while ((1ULL << (log2n + 1)) <= n) ++log2n;
+            int c = static_cast<int>(log2n) - 4;
+            if (c < 8) c = 8;
+            if (c > 16) c = 16;
+            MsmPlan p;
+            p.c = static_cast<uint32_t>(c);
+            p.windows = (256 + p.c - 1) / p.c;
+            p.half = 1u << (p.c - 1);
+            return p;
+        }
+    }
+
+    // MSM over device-resident scalars and points; the XYZZ result is left in
+    // `out_xyzz` (device, optional use by multi-GPU combiners) and the canonical
+    // affine result is copied to `out_host`.
+    int msm_run(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, uint64_t n, uint8_t out_host[96])
+    {
+        const MsmPlan plan = make_plan(n);
+        const uint64_t buckets = static_cast<uint64_t>(plan.windows) * plan.half;
+        const size_t code_bytes = static_cast<size_t>(n) * plan.windows * sizeof(uint32_t);
+        const size_t bucket_u32 = buckets * sizeof(uint32_t);
+        const size_t total = 2 * code_bytes + 3 * bucket_u32 + buckets * sizeof(G1Xyzz) + static_cast<size_t>(plan.windows) * plan.c * sizeof(G1Xyzz) +
+                             sizeof(G1Xyzz) + sizeof(G1Affine) + 4096;
+        void* scratch = nullptr;
+        int rc = ensure_scratch(ctx, 1, total, &scratch);
+        if (rc != GZK_OK) return rc;
+        char* cur = static_cast<char*>(scratch);
+        auto take = [&](size_t bytes) {
+            char* p = cur;
+            cur += (bytes + 255) & ~static_cast<size_t>(255);
+            return p;
+        };
+        G1Xyzz* bucket_points = reinterpret_cast<G1Xyzz*>(take(buckets * sizeof(G1Xyzz)));
+        G1Xyzz* bit_sums = reinterpret_cast<G1Xyzz*>(take(static_cast<size_t>(plan.windows) * plan.c * sizeof(G1Xyzz)));
+        G1Xyzz* result_xyzz = reinterpret_cast<G1Xyzz*>(take(sizeof(G1Xyzz)));
+        G1Affine* result_affine = reinterpret_cast<G1Affine*>(take(sizeof(G1Affine)));
+        uint32_t* code = reinterpret_cast<uint32_t*>(take(code_bytes));
+        uint32_t* entries = reinterpret_cast<uint32_t*>(take(code_bytes));
+        uint32_t* bucket_size = reinterpret_cast<uint32_t*>(take(bucket_u32));
+        uint32_t* bucket_start = reinterpret_cast<uint32_t*>(take(bucket_u32));
+        uint32_t* cursor = reinterpret_cast<uint32_t*>(take(bucket_u32));
+        if (static_cast<size_t>(cur - static_cast<char*>(scratch)) > ctx->scratch[1].bytes)
+            return fail(ctx, GZK_E_INVALID, "msm: internal scratch accounting error");
+
+        ColRef s;
+        s.ptr = scalars->dptr;
+        s.kind = scalars->kind;
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(bucket_size, 0, bucket_u32, ctx->stream));
+        {
+            LaunchScope scope(ctx, "msm_digits");
+            msm_digits_kernel<<<static_cast<unsigned>((n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(s, n, plan, code, bucket_size);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(bucket_start, bucket_size, bucket_u32, cudaMemcpyDeviceToDevice, ctx->stream));
+        {
+            LaunchScope scope(ctx, "msm_offsets");
+            msm_offsets_kernel<<<1, 1024, 0, ctx->stream>>>(bucket_start, cursor, static_cast<uint32_t>(buckets));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            LaunchScope scope(ctx, "msm_scatter");
+            const uint64_t work = n * plan.windows;
+            uint64_t blocks = (work + kThreads - 1) / kThreads;
+            const uint64_t cap = static_cast<uint64_t>(ctx->sm_count) * 32;
+            if (blocks > cap) blocks = cap;
+            msm_scatter_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(code, n, plan, bucket_start, cursor, entries);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            LaunchScope scope(ctx, "msm_buckets");
+            msm_buckets_kernel<<<static_cast<unsigned>((buckets + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
+                static_cast<const G1Affine*>(points->dptr), bucket_start, bucket_size, entries, static_cast<uint32_t>(buckets), bucket_points);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            LaunchScope scope(ctx, "msm_bits");
+            msm_bits_kernel<<<plan.windows * plan.c, kThreads, 0, ctx->stream>>>(bucket_points, plan, bit_sums);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            LaunchScope scope(ctx, "msm_finish");
+            msm_finish_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan, result_xyzz, result_affine);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, result_affine, 96, cudaMemcpyDeviceToHost, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+}
+
+using namespace gzk;
+
+extern "C" int gzk_msm(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, size_t n, uint8_t out[96])
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (out == nullptr) return fail(ctx, GZK_E_INVALID, "msm: null output");
+    if (n == 0)
+    {
+        std::memset(out, 0, 96);
+        return GZK_OK;
+    }
+    if (scalars == nullptr || points == nullptr) return fail(ctx, GZK_E_INVALID, "msm: null argument");
+    if ((scalars->kind != GZK_KIND_FR && scalars->kind != GZK_KIND_FR_MONT) || scalars->count < n)
+        return fail(ctx, GZK_E_INVALID, "msm: scalars must be an FR or FR_MONT buffer of n elements");
+    if (points->kind != GZK_KIND_G1 || points->count < n) return fail(ctx, GZK_E_INVALID, "msm: points must be a G1 buffer of n elements");
+    if (n >= (1ULL << 31)) return fail(ctx, GZK_E_INVALID, "msm: at most 2^31 - 1 points per call");
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return msm_run(ctx, scalars, points, n, out);
+}

@@ -11,8 +11,8 @@ import numpy as np
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libgatzk_b200.so")
 
-KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, KIND_F64 = 0, 1, 2, 3, 4
-_KIND_DTYPE = {KIND_FR: (np.uint8, 32), KIND_FR_MONT: (np.uint8, 32), KIND_I64: (np.int64, 1), KIND_U32: (np.uint32, 1), KIND_F64: (np.float64, 1)}
+KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, KIND_F64, KIND_G1 = 0, 1, 2, 3, 4, 5
+_KIND_DTYPE = {KIND_FR: (np.uint8, 32), KIND_FR_MONT: (np.uint8, 32), KIND_I64: (np.int64, 1), KIND_U32: (np.uint32, 1), KIND_F64: (np.float64, 1), KIND_G1: (np.uint8, 96)}
 
 _lib = None
 
@@ -234,6 +234,39 @@ class Backend:
     def first_zero_marker(self, delta, group_begin, group_end, groups, domain_size):
         out = self.alloc(KIND_U32, domain_size)
         self._check(self.lib.gzk_first_zero_marker(self.ctx, delta.handle, group_begin.handle, group_end.handle, _sz(groups), _sz(domain_size), out.handle))
+        return out
+
+    def g1_mul_same_base(self, base, scalars):
+        base = np.ascontiguousarray(base, dtype=np.uint8).reshape(-1)
+        sc = np.ascontiguousarray(scalars, dtype=np.uint8).reshape(-1, 32)
+        out = np.zeros((sc.shape[0], 96), dtype=np.uint8)
+        self._check(self.lib.gzk_g1_mul_same_base(self.ctx, _ptr(base), _ptr(sc), _sz(sc.shape[0]), _ptr(out)))
+        return out
+
+    def g1_fixed_base_mul(self, base, scalars, count):
+        base = np.ascontiguousarray(base, dtype=np.uint8).reshape(-1)
+        out = self.alloc(KIND_G1, count)
+        self._check(self.lib.gzk_g1_fixed_base_mul(self.ctx, _ptr(base), scalars.handle, _sz(count), out.handle))
+        return out
+
+    def commit_batch(self, cols, length, log2n, weights_tau, base):
+        base = np.ascontiguousarray(base, dtype=np.uint8).reshape(-1)
+        handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
+        evals = np.zeros((len(cols), 32), dtype=np.uint8)
+        points = np.zeros((len(cols), 96), dtype=np.uint8)
+        self._check(self.lib.gzk_commit_batch(self.ctx, handles, _sz(len(cols)), _sz(length), ctypes.c_uint(log2n), weights_tau.handle,
+                                              _ptr(base), _ptr(evals), _ptr(points)))
+        return evals, points
+
+    def msm(self, scalars, points, n):
+        out = np.zeros(96, dtype=np.uint8)
+        self._check(self.lib.gzk_msm(self.ctx, scalars.handle, points.handle, _sz(n), _ptr(out)))
+        return out
+
+    def srs_lagrange(self, log2n, base, tau):
+        base = np.ascontiguousarray(base, dtype=np.uint8).reshape(-1)
+        out = self.alloc(KIND_G1, 1 << log2n)
+        self._check(self.lib.gzk_srs_lagrange(self.ctx, ctypes.c_uint(log2n), _ptr(base), _ptr(_fr(tau)), out.handle))
         return out
 
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):

@@ -7,8 +7,15 @@ import tempfile
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+def test_point_formulas_match_oracle_on_host():
+    _run(os.path.join(ROOT, "tests", "host", "g1_host_check.cpp"))
+
+
 def test_device_arithmetic_matches_oracle_on_host():
-    src = os.path.join(ROOT, "tests", "host", "mp_host_check.cpp")
+    _run(os.path.join(ROOT, "tests", "host", "mp_host_check.cpp"))
+
+
+def _run(src):
     with tempfile.TemporaryDirectory() as tmp:
         exe = os.path.join(tmp, "mp_host_check")
         subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, src], check=True)
