@@ -218,6 +218,20 @@ int gzk_commit_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t 
 int gzk_msm(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, size_t n, uint8_t out[96]);
 int gzk_srs_lagrange(gzk_ctx* ctx, unsigned log2n, const uint8_t base[96], const uint8_t tau[32], gzk_buf* out_points);
 
+/* ---- NTT / coset LDE / multilinear fold (kernel sweep) -------------------------------------------
+ * No reference caller: the reference evaluates by barycentric weights and never
+ * builds quotient polynomials (src/algebra/polynomial.cpp:131-316, 415-508).  The
+ * domain is the reference's: omega_n = 5^((r-1)/n) (field.hpp:87-101).
+ * gzk_ntt: out[b][j] = sum_i in[b][i] * (shift*omega^j)^i (forward) or its inverse;
+ * natural order in and out, `batch` vectors stored back to back; coset_shift may
+ * be NULL (shift 1).  `out` is FR_MONT and must differ from `in`.
+ * gzk_coset_lde: evaluations on the 2^log2n domain -> evaluations on shift * the
+ * 2^(log2n+log2_blowup) domain.
+ * gzk_fold: out[i] = t[2i] + r*(t[2i+1] - t[2i]), i < n/2 (one sumcheck round). */
+int gzk_ntt(gzk_ctx* ctx, const gzk_buf* in, gzk_buf* out, unsigned log2n, size_t batch, int inverse, const uint8_t* coset_shift);
+int gzk_coset_lde(gzk_ctx* ctx, const gzk_buf* in, unsigned log2n, unsigned log2_blowup, const uint8_t shift[32], gzk_buf* out);
+int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out);
+
 /* ---- packed evaluation without any allocation ------------------------------------
  * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that
  * cannot call cudaMalloc while they run: a prover host that has already given all

@@ -1,0 +1,300 @@
+// Stand-alone Fr NTT / inverse NTT / coset variants and the multilinear fold
+// (kernel sweep; the reference has no transform on its proving path).
+//
+// Natural order in, natural order out.  The log2(n) radix-2 stages are grouped into
+// passes of up to 10 stages; each pass loads a 1024-element tile into shared
+// memory (limb-planar, conflict-free), runs its stages there and writes the tile
+// back, so a 2^24-point transform touches HBM in 4 passes instead of 24.  Pass 0
+// gathers its tile through the bit-reversal permutation; later passes take tiles
+// of 2^G strided rows by 2^L contiguous elements.  Twiddles come from the two-level
+// omega tables of the domain (a lookup, plus one multiplication where the exponent
+// has low bits).
+#include <cstring>
+
+#include "block.cuh"
+
+namespace gzk
+{
+    namespace
+    {
+        constexpr int kThreads = 256;
+        constexpr int kTileBits = 10;
+        constexpr int kTile = 1 << kTileBits;
+
+        struct NttArgs
+        {
+            ColRef in;          // pass 0 only
+            Fr* data;           // output / in-place working vector (Montgomery)
+            const Fr* lo;       // omega^j or omega^-j
+            const Fr* hi;
+            unsigned lo_bits;
+            unsigned log2n;
+            unsigned s0;        // first stage of this pass
+            unsigned stages;    // stages in this pass
+            unsigned low_bits;  // contiguous low bits in the tile (L)
+            int last;           // last pass: apply the output scaling
+            int scale_mode;     // 0 none, 1 multiply by `scale` (1/n), 2 also by shift^-i
+            Fr scale;
+            const Fr* shift_lo; // powers of the coset shift (forward: applied on load; inverse: on store)
+            const Fr* shift_hi;
+            unsigned shift_lo_bits;
+            int pre_shift;      // pass 0: multiply input i by shift^i
+        };
+
+        __device__ __forceinline__ void smem_store(uint32_t* tile, uint32_t e, const Fr& v)
+        {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) tile[i * kTile + e] = v.l[i];
+        }
+        __device__ __forceinline__ Fr smem_load(const uint32_t* tile, uint32_t e)
+        {
+            Fr v;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v.l[i] = tile[i * kTile + e];
+            return v;
+        }
+        __device__ __forceinline__ uint64_t bit_reverse(uint64_t x, unsigned bits)
+        {
+            return bits == 0 ? 0 : (__brevll(x) >> (64 - bits));
+        }
+
+        // global index of tile element e: [high | mid (stages bits) | lowbase | l (low_bits)]
+        __device__ __forceinline__ uint64_t tile_index(const NttArgs& a, uint64_t tile_id, uint32_t e)
+        {
+            const uint32_t l = e & ((1u << a.low_bits) - 1u);
+            const uint32_t mid = e >> a.low_bits;
+            const uint64_t lows_per_group = 1ULL << (a.s0 - a.low_bits);  // lowbase values
+            const uint64_t lowbase = tile_id % lows_per_group;
+            const uint64_t high = tile_id / lows_per_group;
+            return (high << (a.s0 + a.stages)) | (static_cast<uint64_t>(mid) << a.s0) | (lowbase << a.low_bits) | l;
+        }
+
+        __global__ void __launch_bounds__(kThreads) ntt_pass_kernel(NttArgs a)
+        {
+            extern __shared__ uint32_t tile[];  // [8][kTile]
+            const uint64_t n = 1ULL << a.log2n;
+            const uint32_t tile_elems = 1u << (a.stages + a.low_bits);
+            const uint64_t vec_offset = static_cast<uint64_t>(blockIdx.y) * n;
+            const uint64_t tile_id = blockIdx.x;
+
+            for (uint32_t e = threadIdx.x; e < tile_elems; e += kThreads)
+            {
+                const uint64_t gi = tile_index(a, tile_id, e);
+                Fr v;
+                if (a.s0 == 0)
+                {
+                    const uint64_t src = bit_reverse(gi, a.log2n);
+                    ColRef in = a.in;
+                    v = col_load_mont(in, vec_offset + src);
+                    if (a.pre_shift) v = mul(v, domain_point(a.shift_lo, a.shift_hi, a.shift_lo_bits, src));
+                }
+                else
+                {
+                    v = load_fr_plain(a.data + vec_offset + gi);
+                }
+                smem_store(tile, e, v);
+            }
+            __syncthreads();
+
+            for (unsigned t = 0; t < a.stages; ++t)
+            {
+                const unsigned s = a.s0 + t;  // butterflies pair rows whose `mid` differs in bit t
+                for (uint32_t b = threadIdx.x; b < tile_elems / 2; b += kThreads)
+                {
+                    // insert a zero at bit (t + low_bits) of b
+                    const uint32_t pos = t + a.low_bits;
+                    const uint32_t lower = b & ((1u << pos) - 1u);
+                    const uint32_t e0 = ((b >> pos) << (pos + 1)) | lower;
+                    const uint32_t e1 = e0 | (1u << pos);
+                    const uint64_t gi = tile_index(a, tile_id, e0);
+                    const uint64_t j = gi & ((1ULL << s) - 1ULL);
+                    const uint64_t k = j << (a.log2n - s - 1);  // exponent of omega_n
+                    const Fr u = smem_load(tile, e0);
+                    Fr v = smem_load(tile, e1);
+                    if (k != 0) v = mul(v, domain_point(a.lo, a.hi, a.lo_bits, k));
+                    smem_store(tile, e0, add(u, v));
+                    smem_store(tile, e1, sub(u, v));
+                }
+                __syncthreads();
+            }
+
+            for (uint32_t e = threadIdx.x; e < tile_elems; e += kThreads)
+            {
+                const uint64_t gi = tile_index(a, tile_id, e);
+                Fr v = smem_load(tile, e);
+                if (a.last && a.scale_mode >= 1) v = mul(v, a.scale);
+                if (a.last && a.scale_mode == 2) v = mul(v, domain_point(a.shift_lo, a.shift_hi, a.shift_lo_bits, gi));
+                store_fr(a.data + vec_offset + gi, v);
+            }
+        }
+
+        // powers table: out[j] = base^(j << shift_bits)
+        __global__ void power_table_kernel(Fr base, unsigned shift_bits, uint32_t count, Fr* out)
+        {
+            const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
+            if (j < count) store_fr(out + j, pow_u64(base, static_cast<uint64_t>(j) << shift_bits));
+        }
+
+        __global__ void fold_kernel(ColRef table, Fr r, uint64_t half, Fr* out)
+        {
+            const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+            for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < half; i += stride)
+            {
+                const Fr lo = col_load_mont(table, 2 * i);
+                const Fr hi = col_load_mont(table, 2 * i + 1);
+                store_fr(out + i, add(lo, mul(r, sub(hi, lo))));
+            }
+        }
+
+        int scalar_mont(gzk_ctx* ctx, const uint8_t* bytes, Fr* out)
+        {
+            bool canonical = false;
+            const Fr v = host_fr_from_bytes(bytes, &canonical);
+            if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
+            *out = to_mont(v);
+            return GZK_OK;
+        }
+    }
+}
+
+using namespace gzk;
+
+extern "C"
+{
+    int gzk_ntt(gzk_ctx* ctx, const gzk_buf* in, gzk_buf* out, unsigned log2n, size_t batch, int inverse, const uint8_t* coset_shift)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (batch == 0) return GZK_OK;
+        if (in == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "ntt: null argument");
+        if (log2n > 30) return fail(ctx, GZK_E_INVALID, "ntt: domain too large");
+        const uint64_t n = 1ULL << log2n;
+        if (in->kind == GZK_KIND_F64 || in->kind == GZK_KIND_G1 || in->count < n * batch) return fail(ctx, GZK_E_INVALID, "ntt: input buffer too small or of the wrong kind");
+        if (out->kind != GZK_KIND_FR_MONT || out->count < n * batch) return fail(ctx, GZK_E_INVALID, "ntt: output must be a Montgomery buffer of n*batch elements");
+        if (out->dptr == in->dptr) return fail(ctx, GZK_E_INVALID, "ntt: input and output must be different buffers");
+        if (batch > 65535) return fail(ctx, GZK_E_INVALID, "ntt: batch too large");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        const DomainTables* dom = nullptr;
+        int rc = get_domain(ctx, log2n, &dom);
+        if (rc != GZK_OK) return rc;
+
+        NttArgs args{};
+        args.in.ptr = in->dptr;
+        args.in.kind = in->kind;
+        args.data = static_cast<Fr*>(out->dptr);
+        args.lo = inverse ? dom->lo_inv : dom->lo;
+        args.hi = inverse ? dom->hi_inv : dom->hi;
+        args.lo_bits = dom->lo_bits;
+        args.log2n = log2n;
+        args.scale = dom->inv_size;
+        args.scale_mode = inverse ? 1 : 0;
+
+        if (coset_shift != nullptr)
+        {
+            Fr g;
+            if ((rc = scalar_mont(ctx, coset_shift, &g)) != GZK_OK) return rc;
+            if (g.is_zero()) return fail(ctx, GZK_E_INVALID, "ntt: coset shift must be non-zero");
+            if (inverse) g = inv(g);
+            // two-level table of powers of the shift (or its inverse)
+            const unsigned lo_bits = (log2n + 1) / 2;
+            const uint32_t lo_count = 1u << lo_bits, hi_count = 1u << (log2n - lo_bits);
+            void* scratch = nullptr;
+            if ((rc = ensure_scratch(ctx, 2, static_cast<size_t>(lo_count + hi_count) * sizeof(Fr), &scratch)) != GZK_OK) return rc;
+            Fr* t_lo = static_cast<Fr*>(scratch);
+            Fr* t_hi = t_lo + lo_count;
+            {
+                LaunchScope scope(ctx, "ntt_shift_table", 2);
+                power_table_kernel<<<(lo_count + 127) / 128, 128, 0, ctx->stream>>>(g, 0, lo_count, t_lo);
+                power_table_kernel<<<(hi_count + 127) / 128, 128, 0, ctx->stream>>>(g, lo_bits, hi_count, t_hi);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            args.shift_lo = t_lo;
+            args.shift_hi = t_hi;
+            args.shift_lo_bits = lo_bits;
+            args.pre_shift = inverse ? 0 : 1;
+            if (inverse) args.scale_mode = 2;
+        }
+
+        const size_t smem = 8 * kTile * sizeof(uint32_t);
+        unsigned s0 = 0;
+        do
+        {
+            const unsigned remaining = log2n - s0;
+            unsigned low_bits = 0, stages = 0;
+            if (s0 == 0)
+            {
+                stages = remaining < static_cast<unsigned>(kTileBits) ? remaining : kTileBits;
+            }
+            else
+            {
+                low_bits = s0 < 4 ? s0 : 4;
+                stages = remaining < kTileBits - low_bits ? remaining : kTileBits - low_bits;
+            }
+            args.s0 = s0;
+            args.stages = stages;
+            args.low_bits = low_bits;
+            args.last = (s0 + stages == log2n) ? 1 : 0;
+            const uint64_t tiles = n >> (stages + low_bits);
+            dim3 grid(static_cast<unsigned>(tiles), static_cast<unsigned>(batch));
+            {
+                LaunchScope scope(ctx, "ntt_pass");
+                ntt_pass_kernel<<<grid, kThreads, smem, ctx->stream>>>(args);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            s0 += stages;
+        } while (s0 < log2n);
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (n < 2) return GZK_OK;
+        if (table == nullptr || out == nullptr || challenge == nullptr) return fail(ctx, GZK_E_INVALID, "fold: null argument");
+        if (table->kind == GZK_KIND_F64 || table->kind == GZK_KIND_G1 || table->count < n) return fail(ctx, GZK_E_INVALID, "fold: table buffer too small or of the wrong kind");
+        if (out->kind != GZK_KIND_FR_MONT || out->count < n / 2) return fail(ctx, GZK_E_INVALID, "fold: output must be a Montgomery buffer of n/2 elements");
+        Fr r;
+        int rc = scalar_mont(ctx, challenge, &r);
+        if (rc != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        ColRef t;
+        t.ptr = table->dptr;
+        t.kind = table->kind;
+        const uint64_t half = n / 2;
+        uint64_t blocks = (half + kThreads - 1) / kThreads;
+        const uint64_t cap = static_cast<uint64_t>(ctx->sm_count) * 16;
+        if (blocks > cap) blocks = cap;
+        {
+            LaunchScope scope(ctx, "fold");
+            fold_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(t, r, half, static_cast<Fr*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    // Coset low-degree extension: evaluations on the 2^log2n domain -> evaluations of the
+    // same polynomial on shift * (2^(log2n+log2_blowup) domain).
+    int gzk_coset_lde(gzk_ctx* ctx, const gzk_buf* in, unsigned log2n, unsigned log2_blowup, const uint8_t shift[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (in == nullptr || out == nullptr || shift == nullptr) return fail(ctx, GZK_E_INVALID, "coset_lde: null argument");
+        if (log2n + log2_blowup > 30) return fail(ctx, GZK_E_INVALID, "coset_lde: extended domain too large");
+        const size_t n = static_cast<size_t>(1) << log2n, big = n << log2_blowup;
+        if (out->kind != GZK_KIND_FR_MONT || out->count < big) return fail(ctx, GZK_E_INVALID, "coset_lde: output must be a Montgomery buffer of the extended size");
+        gzk_buf* coeffs = nullptr;
+        int rc = gzk_buf_alloc(ctx, GZK_KIND_FR_MONT, big, &coeffs);
+        if (rc != GZK_OK) return rc;
+        rc = gzk_ntt(ctx, in, coeffs, log2n, 1, 1, nullptr);
+        if (rc == GZK_OK && big > n)
+        {
+            const cudaError_t err = cudaMemsetAsync(static_cast<char*>(coeffs->dptr) + n * 32, 0, (big - n) * 32, ctx->stream);
+            if (err != cudaSuccess) rc = cuda_fail(ctx, err, "cudaMemsetAsync(lde padding)");
+        }
+        if (rc == GZK_OK) rc = gzk_ntt(ctx, coeffs, out, log2n + log2_blowup, 1, 0, shift);
+        const std::string message = ctx->last_error;
+        gzk_buf_free(ctx, coeffs);
+        if (rc != GZK_OK) ctx->last_error = message;
+        return rc;
+    }
+}

@@ -269,6 +269,22 @@ class Backend:
         self._check(self.lib.gzk_srs_lagrange(self.ctx, ctypes.c_uint(log2n), _ptr(base), _ptr(_fr(tau)), out.handle))
         return out
 
+    def ntt(self, inp, log2n, batch=1, inverse=False, coset_shift=None):
+        out = self.alloc(KIND_FR_MONT, (1 << log2n) * batch)
+        shift = None if coset_shift is None else _ptr(_fr(coset_shift))
+        self._check(self.lib.gzk_ntt(self.ctx, inp.handle, out.handle, ctypes.c_uint(log2n), _sz(batch), int(bool(inverse)), shift))
+        return out
+
+    def coset_lde(self, inp, log2n, log2_blowup, shift):
+        out = self.alloc(KIND_FR_MONT, 1 << (log2n + log2_blowup))
+        self._check(self.lib.gzk_coset_lde(self.ctx, inp.handle, ctypes.c_uint(log2n), ctypes.c_uint(log2_blowup), _ptr(_fr(shift)), out.handle))
+        return out
+
+    def fold(self, table, n, challenge):
+        out = self.alloc(KIND_FR_MONT, n // 2)
+        self._check(self.lib.gzk_fold(self.ctx, table.handle, _sz(n), _ptr(_fr(challenge)), out.handle))
+        return out
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)
