@@ -193,6 +193,16 @@ int gzk_quantize(gzk_ctx* ctx, const gzk_buf* values, size_t count, gzk_buf* out
 int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
                           size_t domain_size, gzk_buf* out);
 
+/* ---- a11: public feature-domain columns that are never materialised ---------------------------
+ * out[0..4] = sum_{i < rows*feature_count} w[i] * {1, i / fc, i % fc, abs_ids[i / fc],
+ * features[i]} (32 bytes each; abs_ids / features may be NULL, their slot is then
+ * zero).  Replaces evaluate_truncated_domain_polynomial and
+ * evaluate_lazy_large_fh_public_group(_points) (src/protocol/prover.cpp:224-276,
+ * 1205-1675), which stream the same generated columns on the CPU for n_FH >= 2^24.
+ * Weights at the wanted point come from gzk_bary_weights. */
+int gzk_fh_public_eval(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
+                       const gzk_buf* weights, uint8_t out[5 * 32]);
+
 /* ---- a5: G1 -----------------------------------------------------------------------------------
  * gzk_g1_mul_same_base: points[k] = [scalars[k]] base for K host scalars (32-byte
  * canonical) -> K affine points (96 bytes each).  Replaces g1_mul_same_base_batch /

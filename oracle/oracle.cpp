@@ -653,6 +653,32 @@ extern "C"
         });
     }
 
+    // ---- a11: lazily evaluated public feature-domain columns ---------------------------
+    // src/protocol/prover.cpp:224-276 (evaluate_truncated_domain_polynomial) and
+    // :1341-1675 (evaluate_lazy_large_fh_public_group_points): dot products of the
+    // weight vector with the generated columns 1, index / feature_count,
+    // index % feature_count, absolute_ids[row], features[row][column] over the first
+    // rows*feature_count entries.  out = {ones, row, col, abs, feature}.
+    int ora_fh_public_eval(const Bytes* features, std::size_t rows, std::size_t feature_count, const std::uint64_t* abs_ids,
+                           const Bytes* weights, Bytes* out)
+    {
+        return guarded([&] {
+            Fr sums[5] = {Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero(), Fr::zero()};
+            const std::size_t valid = rows * feature_count;
+            for (std::size_t index = 0; index < valid; ++index)
+            {
+                const Fr w = Fr::from_le_bytes(weights + 32 * index);
+                const std::size_t row = index / feature_count;
+                sums[0] += w;
+                sums[1] += w * Fr::from_u64(row);
+                sums[2] += w * Fr::from_u64(index % feature_count);
+                if (abs_ids != nullptr) sums[3] += w * Fr::from_u64(abs_ids[row]);
+                if (features != nullptr) sums[4] += w * Fr::from_le_bytes(features + 32 * index);
+            }
+            for (int i = 0; i < 5; ++i) sums[i].to_le_bytes(out + 32 * i);
+        });
+    }
+
     // ---- a5: same-base batch and group helpers (curve.cpp:81-238) -------------------
     int ora_g1_mul_same_base(const Bytes* base, const Bytes* scalars, std::size_t count, Bytes* out)
     {

@@ -285,6 +285,12 @@ class Backend:
         self._check(self.lib.gzk_fold(self.ctx, table.handle, _sz(n), _ptr(_fr(challenge)), out.handle))
         return out
 
+    def fh_public_eval(self, features, rows, feature_count, abs_ids, weights):
+        out = np.zeros((5, 32), dtype=np.uint8)
+        self._check(self.lib.gzk_fh_public_eval(self.ctx, features.handle if features is not None else None, _sz(rows), _sz(feature_count),
+                                                abs_ids.handle if abs_ids is not None else None, weights.handle, _ptr(out)))
+        return out
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)

@@ -334,3 +334,12 @@ def bench_bary(n, threads, seed=1):
     chk = np.zeros(32, dtype=np.uint8)
     _check(lib().ora_bench_bary(_sz(n), _sz(threads), ctypes.c_uint64(seed), ctypes.byref(sec), _p(chk)))
     return sec.value, chk
+
+
+def fh_public_eval(features, rows, feature_count, abs_ids, weights):
+    features = _u8(features) if features is not None else None
+    ids = np.ascontiguousarray(abs_ids, dtype=np.uint64) if abs_ids is not None else None
+    weights = _u8(weights)
+    out = np.zeros((5, 32), dtype=np.uint8)
+    _check(lib().ora_fh_public_eval(_p(features), _sz(rows), _sz(feature_count), _p(ids), _p(weights), _p(out)))
+    return out

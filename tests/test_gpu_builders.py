@@ -212,3 +212,26 @@ def test_elementwise_leaves(be):
     got = be.first_zero_marker(be.upload(delta, KIND_I64), be.upload(gb, KIND_I64), be.upload(ge, KIND_I64), gb.size, 1024).download()
     want = ora.first_zero_marker(ora.fr_from_i64(np.concatenate([delta, np.ones(24, dtype=np.int64)])), gb, ge, 1024)
     assert np.array_equal(fr_array([int(v) for v in got]), want)
+
+
+@pytest.mark.parametrize("rows,fc,log2n,kind", [(37, 50, 11, "fr"), (300, 128, 16, "i64"), (1000, 16, 14, "u32")])
+def test_fh_public_eval(be, rows, fc, log2n, kind):
+    from project_b200 import KIND_FR, KIND_I64, KIND_U32
+
+    rng = np.random.default_rng(rows)
+    x = fr_array([int(rng.integers(2, 1 << 62))])
+    w = be.bary_weights(log2n, x)
+    w_host = w.download()
+    abs_ids = rng.permutation(rows).astype(np.int64)
+    if kind == "fr":
+        feats = rand_fr(rng, rows * fc)
+        fbuf, fhost = be.upload(feats, KIND_FR), feats
+    elif kind == "i64":
+        vals = rng.integers(-300, 300, size=rows * fc, dtype=np.int64)
+        fbuf, fhost = be.upload(vals, KIND_I64), ora.fr_from_i64(vals)
+    else:
+        vals = rng.integers(0, 17, size=rows * fc, dtype=np.uint32)
+        fbuf, fhost = be.upload(vals, KIND_U32), ora.fr_from_i64(vals.astype(np.int64))
+    got = be.fh_public_eval(fbuf, rows, fc, be.upload(abs_ids, KIND_I64), w)
+    want = ora.fh_public_eval(fhost, rows, fc, abs_ids, w_host)
+    assert np.array_equal(got, want)
