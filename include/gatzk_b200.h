@@ -242,6 +242,25 @@ int gzk_ntt(gzk_ctx* ctx, const gzk_buf* in, gzk_buf* out, unsigned log2n, size_
 int gzk_coset_lde(gzk_ctx* ctx, const gzk_buf* in, unsigned log2n, unsigned log2_blowup, const uint8_t shift[32], gzk_buf* out);
 int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out);
 
+/* ---- sharding across GPUs (one context per GPU, one process per GPU) ---------------------------
+ * The reference is a single process; these entry points let the rows of a domain be
+ * split over GPUs with only tiny exchanges, which the host performs (NCCL / MPI
+ * all-gather of the partial results below):
+ * gzk_bary_weights_range: the slice w[first .. first+count) (indices modulo n) of the
+ *   barycentric weight vector; no exchange needed, the batch inversion is per slice.
+ * gzk_eval_batch_range: partial sums of gzk_eval_batch over the local rows
+ *   [row_offset, row_offset+len) given a weight slice starting at weights_first that
+ *   covers row_offset-rot .. row_offset+len-1-rot for every rotation.
+ * gzk_fr_sum: out[i] = sum_g values[g][i] over `groups` GPUs (host arithmetic).
+ * gzk_g1_sum: sum of `count` affine points (host arithmetic): the per-GPU results of an
+ *   MSM whose point range was split over the GPUs. */
+int gzk_bary_weights_range(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], uint64_t first, uint64_t count, gzk_buf* out);
+int gzk_eval_batch_range(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, uint64_t row_offset, unsigned log2n,
+                         const gzk_buf* weights, uint64_t weights_first, const uint64_t* rotations, size_t p_count,
+                         uint8_t* out_host);
+int gzk_fr_sum(const uint8_t* values, size_t groups, size_t count, uint8_t* out);
+int gzk_g1_sum(const uint8_t* points, size_t count, uint8_t out[96]);
+
 /* ---- packed evaluation without any allocation ------------------------------------
  * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that
  * cannot call cudaMalloc while they run: a prover host that has already given all

@@ -23,7 +23,9 @@ namespace gzk
             const Fr* lo;
             const Fr* hi;
             unsigned lo_bits;
-            uint64_t n;
+            uint64_t n;      // number of weights produced by this call
+            uint64_t first;  // domain index of the first one (ranges wrap around the domain)
+            uint64_t mask;   // domain size - 1
             Fr x;       // Montgomery
             Fr scale;   // (x^n - 1)/n, Montgomery
         };
@@ -47,7 +49,7 @@ namespace gzk
                 const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
                 if (e < a.n)
                 {
-                    const Fr d = sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, e));
+                    const Fr d = sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, (a.first + e) & a.mask));
                     if (d.is_zero()) atomicExch(status, 1);
                     prod = mul(prod, d);
                 }
@@ -133,7 +135,7 @@ namespace gzk
             for (int j = 0; j < kElems; ++j)
             {
                 const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
-                d[j] = e < a.n ? sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, e)) : Fr::one();
+                d[j] = e < a.n ? sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, (a.first + e) & a.mask)) : Fr::one();
             }
             // thread-local exclusive prefixes; `mine` = product of the thread's elements
             Fr pre[kElems];
@@ -208,14 +210,15 @@ namespace gzk
 
 using namespace gzk;
 
-extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], gzk_buf* out)
+static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], uint64_t first, uint64_t count, gzk_buf* out)
 {
     if (ctx == nullptr) return GZK_E_INVALID;
     if (x_bytes == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "bary_weights: null argument");
     if (log2n > 30) return fail(ctx, GZK_E_INVALID, "bary_weights: domain too large");
     const uint64_t n = 1ULL << log2n;
-    if (out->kind != GZK_KIND_FR_MONT || out->count < n)
-        return fail(ctx, GZK_E_INVALID, "bary_weights: output must be a Montgomery buffer of the domain size");
+    if (count > n || first >= n) return fail(ctx, GZK_E_INVALID, "bary_weights: range exceeds the domain");
+    if (out->kind != GZK_KIND_FR_MONT || out->count < count)
+        return fail(ctx, GZK_E_INVALID, "bary_weights: output must be a Montgomery buffer of the requested size");
     bool canonical = false;
     const Fr x_plain = host_fr_from_bytes(x_bytes, &canonical);
     if (!canonical) return fail(ctx, GZK_E_INVALID, "bary_weights: x is not a canonical field element");
@@ -228,15 +231,18 @@ extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_by
     args.lo = dom->lo;
     args.hi = dom->hi;
     args.lo_bits = dom->lo_bits;
-    args.n = n;
+    args.n = count;
+    args.first = first;
+    args.mask = n - 1;
     args.x = to_mont(x_plain);
     Fr xn = args.x;
     for (unsigned s = 0; s < log2n; ++s) xn = sqr(xn);
     const Fr zero_eval = sub(xn, Fr::one());
     if (zero_eval.is_zero()) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
     args.scale = mul(zero_eval, dom->inv_size);
+    if (count == 0) return GZK_OK;
 
-    const uint32_t blocks = static_cast<uint32_t>((n + kChunk - 1) / kChunk);
+    const uint32_t blocks = static_cast<uint32_t>((count + kChunk - 1) / kChunk);
     void* scratch = nullptr;
     if ((rc = ensure_scratch(ctx, 2, static_cast<size_t>(blocks) * 2 * sizeof(Fr), &scratch)) != GZK_OK) return rc;
     Fr* products = static_cast<Fr*>(scratch);
@@ -258,4 +264,17 @@ extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_by
     GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
     if (status != 0) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
     return GZK_OK;
+}
+
+extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], gzk_buf* out)
+{
+    return bary_impl(ctx, log2n, x_bytes, 0, log2n <= 30 ? (1ULL << log2n) : 0, out);
+}
+
+// Weights first, first+1, ..., first+count-1 (indices modulo the domain size): the
+// slice of the vector one GPU needs when the rows of a domain are sharded.  The
+// batch inversion runs over the slice only, so no exchange between GPUs is needed.
+extern "C" int gzk_bary_weights_range(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], uint64_t first, uint64_t count, gzk_buf* out)
+{
+    return bary_impl(ctx, log2n, x_bytes, first, count, out);
 }

@@ -427,18 +427,12 @@ extern "C" int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, do
     return GZK_OK;
 }
 
-extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
-                              const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host)
+// Shared body of gzk_eval_batch and gzk_eval_batch_range.  `rotations` are already the
+// effective ones: row c of a column meets weights[(c - rotation) mod n] of the buffer.
+static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
+                           const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host)
 {
-    if (ctx == nullptr) return GZK_E_INVALID;
-    if (k_count == 0 || p_count == 0) return GZK_OK;
-    if (cols == nullptr || weights == nullptr || rotations == nullptr || out_host == nullptr)
-        return fail(ctx, GZK_E_INVALID, "eval_batch: null argument");
-    if (log2n > 32) return fail(ctx, GZK_E_INVALID, "eval_batch: domain too large");
     const uint64_t n = 1ULL << log2n;
-    if (len > n) return fail(ctx, GZK_E_INVALID, "domain evaluation backend weight size mismatch");
-    if (weights->kind != GZK_KIND_FR_MONT || weights->count < n)
-        return fail(ctx, GZK_E_INVALID, "eval_batch: weights must be a Montgomery buffer of the domain size");
     if (k_count > (1u << 20)) return fail(ctx, GZK_E_INVALID, "eval_batch: too many columns");
     for (size_t k = 0; k < k_count; ++k)
     {
@@ -659,5 +653,71 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     eval_finish_kernel<<<(outs + 127) / 128, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
                                                          static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device));
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
+    return GZK_OK;
+}
+
+extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
+                              const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (k_count == 0 || p_count == 0) return GZK_OK;
+    if (cols == nullptr || weights == nullptr || rotations == nullptr || out_host == nullptr)
+        return fail(ctx, GZK_E_INVALID, "eval_batch: null argument");
+    if (log2n > 32) return fail(ctx, GZK_E_INVALID, "eval_batch: domain too large");
+    const uint64_t n = 1ULL << log2n;
+    if (len > n) return fail(ctx, GZK_E_INVALID, "domain evaluation backend weight size mismatch");
+    if (weights->kind != GZK_KIND_FR_MONT || weights->count < n)
+        return fail(ctx, GZK_E_INVALID, "eval_batch: weights must be a Montgomery buffer of the domain size");
+    return eval_batch_impl(ctx, cols, k_count, len, log2n, weights, rotations, p_count, out_host);
+}
+
+// Row-sharded form: this GPU holds rows [row_offset, row_offset + len) of every column
+// (cols[k][0] is row row_offset) and the weights w[weights_first .. weights_first +
+// weights->count) of the domain (indices modulo n, e.g. from gzk_bary_weights_range).
+// Returns the PARTIAL sums over the local rows; the partials of all GPUs add up
+// (gzk_fr_sum) to what gzk_eval_batch returns on the whole columns.
+extern "C" int gzk_eval_batch_range(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, uint64_t row_offset, unsigned log2n,
+                                    const gzk_buf* weights, uint64_t weights_first, const uint64_t* rotations, size_t p_count,
+                                    uint8_t* out_host)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (k_count == 0 || p_count == 0) return GZK_OK;
+    if (cols == nullptr || weights == nullptr || rotations == nullptr || out_host == nullptr)
+        return fail(ctx, GZK_E_INVALID, "eval_batch_range: null argument");
+    if (log2n > 32) return fail(ctx, GZK_E_INVALID, "eval_batch_range: domain too large");
+    const uint64_t n = 1ULL << log2n;
+    if (len > n || row_offset >= n || weights_first >= n) return fail(ctx, GZK_E_INVALID, "eval_batch_range: range exceeds the domain");
+    if (weights->kind != GZK_KIND_FR_MONT) return fail(ctx, GZK_E_INVALID, "eval_batch_range: weights must be a Montgomery buffer");
+    if (p_count > 16) return fail(ctx, GZK_E_INVALID, "eval_batch_range: too many rotations");
+    uint64_t effective[16];
+    for (size_t p = 0; p < p_count; ++p)
+    {
+        if (rotations[p] >= n) return fail(ctx, GZK_E_INVALID, "eval_batch_range: rotation out of range");
+        // local row c is global row row_offset + c and needs w[(row_offset + c - rot) mod n],
+        // stored at buffer index (row_offset + c - rot - weights_first) mod n
+        const uint64_t first_needed = (row_offset + n - rotations[p] + n - weights_first) & (n - 1);
+        if (len != 0 && first_needed + len > weights->count)
+            return fail(ctx, GZK_E_INVALID, "eval_batch_range: the weight slice does not cover the rows at this rotation");
+        effective[p] = (n - first_needed) & (n - 1);
+    }
+    return eval_batch_impl(ctx, cols, k_count, len, log2n, weights, effective, p_count, out_host);
+}
+
+// Host-side combination of per-GPU partial results: out[i] = sum_g values[g][i] (mod r).
+extern "C" int gzk_fr_sum(const uint8_t* values, size_t groups, size_t count, uint8_t* out)
+{
+    if (values == nullptr || out == nullptr) return GZK_E_INVALID;
+    for (size_t i = 0; i < count; ++i)
+    {
+        Fr acc = Fr::zero();
+        for (size_t g = 0; g < groups; ++g)
+        {
+            bool canonical = false;
+            const Fr v = host_fr_from_bytes(values + (g * count + i) * 32, &canonical);
+            if (!canonical) return GZK_E_INVALID;
+            acc = add(acc, v);  // canonical residues add like Montgomery ones
+        }
+        host_fr_to_bytes(acc, out + i * 32);
+    }
     return GZK_OK;
 }

@@ -321,4 +321,32 @@ extern "C"
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return GZK_OK;
     }
+
+    // Host-side sum of a few affine points (wire format): combines the per-GPU results of
+    // a point-range-sharded MSM.  Runs on the CPU; `count` is the number of GPUs.
+    int gzk_g1_sum(const uint8_t* points, size_t count, uint8_t out[96])
+    {
+        if (points == nullptr || out == nullptr) return GZK_E_INVALID;
+        G1Xyzz acc = G1Xyzz::infinity();
+        for (size_t i = 0; i < count; ++i)
+        {
+            const uint8_t* p = points + 96 * i;
+            bool is_inf = true;
+            for (int b = 0; b < 96; ++b) is_inf = is_inf && p[b] == 0;
+            if (is_inf) continue;
+            if (!fp_canonical(p) || !fp_canonical(p + 48)) return GZK_E_INVALID;
+            G1Affine a;
+            std::memcpy(a.x.l, p, 48);
+            std::memcpy(a.y.l, p + 48, 48);
+            a.x = to_mont(a.x);
+            a.y = to_mont(a.y);
+            acc = g1_add_mixed(acc, a);
+        }
+        G1Affine r = g1_to_affine(acc);
+        r.x = from_mont(r.x);
+        r.y = from_mont(r.y);
+        std::memcpy(out, r.x.l, 48);
+        std::memcpy(out + 48, r.y.l, 48);
+        return GZK_OK;
+    }
 }

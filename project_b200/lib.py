@@ -291,6 +291,19 @@ class Backend:
                                                 abs_ids.handle if abs_ids is not None else None, weights.handle, _ptr(out)))
         return out
 
+    def bary_weights_range(self, log2n, x, first, count):
+        out = self.alloc(KIND_FR_MONT, max(count, 1))
+        self._check(self.lib.gzk_bary_weights_range(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), ctypes.c_uint64(first), ctypes.c_uint64(count), out.handle))
+        return out
+
+    def eval_batch_range(self, cols, length, row_offset, log2n, weights, weights_first, rotations=(0,)):
+        handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
+        rot = np.ascontiguousarray(rotations, dtype=np.uint64)
+        out = np.zeros((rot.size, len(cols), 32), dtype=np.uint8)
+        self._check(self.lib.gzk_eval_batch_range(self.ctx, handles, _sz(len(cols)), _sz(length), ctypes.c_uint64(row_offset), ctypes.c_uint(log2n),
+                                                  weights.handle, ctypes.c_uint64(weights_first), _ptr(rot), _sz(rot.size), _ptr(out)))
+        return out
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)
@@ -313,3 +326,34 @@ def eval_batch_static(device, stream, col_ptrs, col_kinds, length, log2n, weight
                                    ctypes.c_void_p(weights_ptr), _ptr(rot), _sz(rot.size), ctypes.c_void_p(out_ptr), err, _sz(256))
     if rc != 0:
         raise GzkError(rc, err.value.decode())
+
+
+def fr_sum(values):
+    """Host combine of per-GPU partial results: values [groups, ..., 32] -> [..., 32]."""
+    lib = load_library()
+    v = np.ascontiguousarray(values, dtype=np.uint8)
+    groups = v.shape[0]
+    count = v[0].size // 32
+    out = np.zeros(v.shape[1:], dtype=np.uint8)
+    rc = lib.gzk_fr_sum(_ptr(v), _sz(groups), _sz(count), _ptr(out))
+    if rc != 0:
+        raise GzkError(rc, "gzk_fr_sum: non-canonical input")
+    return out
+
+
+def g1_sum(points):
+    lib = load_library()
+    v = np.ascontiguousarray(points, dtype=np.uint8).reshape(-1, 96)
+    out = np.zeros(96, dtype=np.uint8)
+    rc = lib.gzk_g1_sum(_ptr(v), _sz(v.shape[0]), _ptr(out))
+    if rc != 0:
+        raise GzkError(rc, "gzk_g1_sum: non-canonical input")
+    return out
+
+
+def shard_rows(n_rows, world, rank, align=1):
+    """Contiguous row range [begin, end) of `rank` when n_rows rows are split over `world` GPUs."""
+    per = -(-n_rows // world)
+    per = -(-per // align) * align
+    begin = min(n_rows, rank * per)
+    return begin, min(n_rows, begin + per)

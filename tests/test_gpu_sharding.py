@@ -1,0 +1,69 @@
+"""Row-range sharding of the packed evaluation and point-range sharding of the MSM:
+the per-shard partial results, combined by the host helpers, must equal the
+single-GPU result bit for bit.  The shards run one after the other on one GPU here
+(ranks that wait on each other never share a GPU; these do not wait)."""
+import numpy as np
+import pytest
+
+import oracle_lib as ora
+import pyref
+from pyref import fr_array
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def be():
+    from project_b200 import Backend
+
+    b = Backend(0)
+    yield b
+    b.close()
+
+
+@pytest.mark.parametrize("world", [2, 3, 8])
+def test_sharded_eval_equals_whole(be, world):
+    from project_b200 import KIND_FR, fr_sum, shard_rows
+
+    rng = np.random.default_rng(world)
+    log2n, n, k, length = 12, 4096, 6, 3900
+    cols = rng.integers(0, 256, size=(k, n, 32), dtype=np.uint8)
+    cols[:, :, 31] &= 0x3F
+    cols[:, length:] = 0
+    x = fr_array([int(rng.integers(2, 1 << 62))])
+    rots = (0, 1, 7)
+    w_full = be.bary_weights(log2n, x)
+    whole = be.eval_batch([be.upload(cols[i, :length], KIND_FR) for i in range(k)], length, log2n, w_full, rots)
+    partials = []
+    for rank in range(world):
+        begin, end = shard_rows(length, world, rank, align=32)
+        halo = max(rots)
+        first = (begin - halo) % n
+        w_slice = be.bary_weights_range(log2n, x, first, (end - begin) + halo)
+        assert np.array_equal(w_slice.download()[: (end - begin) + halo], np.roll(w_full.download(), -first, axis=0)[: (end - begin) + halo])
+        bufs = [be.upload(cols[i, begin:end] if end > begin else np.zeros((1, 32), np.uint8), KIND_FR) for i in range(k)]
+        partials.append(be.eval_batch_range(bufs, end - begin, begin % n, log2n, w_slice, first, rots))
+    assert np.array_equal(fr_sum(np.stack(partials)), whole)
+    assert np.array_equal(whole, ora.eval_rotations(cols, w_full.download(), rots))
+
+
+def test_sharded_msm_equals_whole(be):
+    from project_b200 import KIND_FR, g1_sum, shard_rows
+
+    G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8).copy()
+    rng = np.random.default_rng(9)
+    n, world = 5000, 4
+    kb = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    sb = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    kb[:, 31] &= 0x3F
+    sb[:, 31] &= 0x3F
+    pts = be.g1_fixed_base_mul(G, be.upload(kb, KIND_FR), n)
+    whole = be.msm(be.upload(sb, KIND_FR), pts, n)
+    host_pts = pts.download()
+    from project_b200 import KIND_G1
+
+    parts = []
+    for rank in range(world):
+        begin, end = shard_rows(n, world, rank)
+        parts.append(be.msm(be.upload(sb[begin:end], KIND_FR), be.upload(host_pts[begin:end], KIND_G1), end - begin))
+    assert np.array_equal(g1_sum(np.stack(parts)), whole)
