@@ -169,12 +169,13 @@ def main():
     ap.add_argument("--profile-case", action="store_true", help="one 2^18 x 64-column domain (profiler captures)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-sweep", action="store_true", help="skip the MSM / NTT / fold kernel sweep lines")
     args = ap.parse_args()
     workload = WORKLOAD_SMALL if args.small else (WORKLOAD_PROFILE if args.profile_case else WORKLOAD_B2)
     wl_name = ("reduced shapes (edge 2^14 x 64, N 2^11 x 32)" if args.small else
                "profiling case (edge 2^18 x 64 columns)" if args.profile_case else
-               "mid-size GAT (N=19717, 8x8 hidden, 8x3 output) hot-path step: commit + quotient + opening evaluations over 7 domains, "
-               "1161 Fr columns, inputs larger than L2")
+               "mid-size GAT (N=19717, 8x8 hidden, 8x3 output) hot-path step: commit (tau-evaluation + same-base G1 batch) + quotient + opening "
+               "evaluations over 7 domains, 1161 Fr columns, plus the column builders of 16 heads; inputs larger than L2")
     if args.impl == "reference":
         return run_reference(args, workload, wl_name)
 
@@ -184,76 +185,154 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     torch.cuda.set_device(local_rank)
+    dist = None
     if world > 1:
         import torch.distributed as dist
 
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    from project_b200 import KIND_FR, KIND_FR_MONT, Backend
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import pyref
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, Backend, fr_sum, shard_rows
 
     be = Backend(local_rank)
     stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", local_rank))
-    rng = np.random.default_rng(1234 + rank)
+    rng = np.random.default_rng(1234)
+    G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8).copy()
+    heads = 2 if (args.small or args.profile_case) else 16
 
-    # Shard: with N ranks every rank takes a contiguous 1/N slice of the columns of
-    # every domain (independent inner products, no data-path collective).
-    def my_columns(k):
-        lo = (k * rank) // world
-        hi = (k * (rank + 1)) // world
-        return hi - lo
-
-    # ---- resident inputs ----------------------------------------------------------
+    # ---- resident inputs: every rank holds its ROW range of every column ---------------
     slabs = {}
     domains = []
     tau = np.zeros(32, dtype=np.uint8)
     tau[0] = 11 + 17  # KZG::setup: tau = seed + 17 with the config seed 11
     for name, lg, k, valid in workload:
         n = 1 << lg
-        kk = my_columns(k)
+        begin, end = shard_rows(n, world, rank, align=32) if world > 1 else (0, n)
+        rows = end - begin
+        if rows == 0:
+            begin = 0  # a rank without rows of a tiny domain contributes zero partial sums
         if lg not in slabs:
-            base = rng.integers(0, 256, size=(min(n, 1 << 22) * 4, 32), dtype=np.uint8)
+            base = rng.integers(0, 256, size=(min(n, 1 << 22) * 2, 32), dtype=np.uint8)
             base[:, 31] &= 0x3F
             slabs[lg] = base
         base = slabs[lg]
         cols = []
-        for i in range(kk):
-            buf = be.alloc(KIND_FR, n)
-            off = (i * 7919) % (base.shape[0] - min(n, 1 << 22) + 1) if n <= (1 << 22) else 0
-            if n <= (1 << 22):
-                buf.upload(base[off:off + n])
-            else:
-                for part in range(n >> 22):
-                    o2 = ((i + part) * 104729) % (base.shape[0] - (1 << 22) + 1)
-                    buf.upload(base[o2:o2 + (1 << 22)], offset=part << 22)
+        for i in range(k):
+            buf = be.alloc(KIND_FR, max(rows, 1))
+            done = 0
+            while done < rows:
+                part = min(rows - done, 1 << 22)
+                off = ((i * 7919 + done) * 31) % (base.shape[0] - part + 1)
+                buf.upload(base[off:off + part], offset=done)
+                done += part
             cols.append(buf)
-        w_tau = be.bary_weights(lg, tau)
-        w_z = be.alloc(KIND_FR_MONT, n)
-        domains.append({"name": name, "lg": lg, "n": n, "k": kk, "valid": min(valid, n), "cols": cols, "w_tau": w_tau, "w_z": w_z})
-    be.synchronize()
+        d = {"name": name, "lg": lg, "n": n, "k": k, "valid": min(valid, n), "cols": cols, "begin": begin, "rows": rows}
+        if world == 1:
+            d["w_tau"] = be.bary_weights(lg, tau)
+            d["w_z"] = be.alloc(KIND_FR_MONT, n)
+        else:
+            d["w_first"] = (begin - 1) % n
+            d["w_tau"] = be.bary_weights_range(lg, tau, d["w_first"], rows + 1)
+            d["w_z"] = be.alloc(KIND_FR_MONT, rows + 1)
+        domains.append(d)
 
+    # builder inputs (edge- and node-shaped columns of one head; reused for every head)
+    edge = next((d for d in domains if d["name"] == "edge"), domains[0])
+    node = next((d for d in domains if d["name"] == "N"), domains[-1])
+    ne, nn = edge["n"], node["n"]
+    e_valid, n_valid = min(edge["valid"], ne - 1), min(node["valid"], nn - 1)
+    b_in = {
+        "table": be.upload(rng.integers(-2048, 2048, size=ne, dtype=np.int64), KIND_I64),
+        "query": be.upload(rng.integers(-2048, 2048, size=ne, dtype=np.int64), KIND_I64),
+        "mult": be.upload(rng.integers(0, 64, size=ne, dtype=np.uint32), KIND_U32),
+        "q_table": be.upload((np.arange(ne) < 4096).astype(np.uint32), KIND_U32),
+        "q_query": be.upload((np.arange(ne) < e_valid).astype(np.uint32), KIND_U32),
+        "q_new": be.upload((rng.random(ne) < 0.15).astype(np.uint32), KIND_U32),
+        "values": be.upload(rng.integers(0, 4096, size=ne, dtype=np.int64), KIND_I64),
+        "node_vals": be.upload(rng.integers(-4096, 4096, size=nn, dtype=np.int64), KIND_I64),
+        "src": be.upload(rng.integers(0, n_valid, size=ne, dtype=np.int64).astype(np.uint32), KIND_U32),
+        "hits": be.upload(rng.integers(0, 4096, size=e_valid, dtype=np.int64).astype(np.uint32), KIND_U32),
+        "matrix": be.upload(rng.integers(-4096, 4096, size=n_valid * 8, dtype=np.int64), KIND_I64),
+        "node_tab": be.upload(rng.integers(0, 1 << 20, size=nn, dtype=np.int64), KIND_I64),
+        "node_mult": be.upload(rng.integers(0, 64, size=nn, dtype=np.uint32), KIND_U32),
+    }
+    w_node = be.bary_weights(node["lg"], tau)
+    be.synchronize()
     step_counter = [0]
 
     def challenge():
         step_counter[0] += 1
         z = np.zeros(32, dtype=np.uint8)
-        z[:8] = np.frombuffer(np.uint64(0x9E3779B97F4A7C15 * step_counter[0] % (1 << 64) | 1).tobytes(), dtype=np.uint8)
+        z[:8] = np.frombuffer(np.uint64((0x9E3779B97F4A7C15 * step_counter[0]) % (1 << 64) | 1).tobytes(), dtype=np.uint8)
         return z
 
-    def step_resident():
+    def gather_sum(partial):
+        """all-gather the per-rank partial sums (a few KB) over NCCL and add them mod r"""
+        if world == 1:
+            return partial
+        t = torch.from_numpy(partial).cuda()
+        out = torch.empty((world,) + tuple(t.shape), dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(out, t)
+        return fr_sum(out.cpu().numpy())
+
+    def evaluate(d, weights, length, rotations):
+        if world == 1:
+            return be.eval_batch(d["cols"], length, d["lg"], weights, rotations)
+        local_len = max(0, min(length - d["begin"], d["rows"]))
+        return gather_sum(be.eval_batch_range(d["cols"], local_len, d["begin"], d["lg"], weights, d["w_first"], rotations))
+
+    def step_evaluations():
         outs = []
         for d in domains:
-            if d["k"] == 0:
-                continue
-            outs.append(be.eval_batch(d["cols"], d["valid"], d["lg"], d["w_tau"], (0,)))
-            outs.append(be.eval_batch(d["cols"], d["n"], d["lg"], d["w_tau"], (0, 1)))
-            be.bary_weights(d["lg"], challenge(), out=d["w_z"])
-            outs.append(be.eval_batch(d["cols"], d["n"], d["lg"], d["w_z"], (0, 1)))
+            tau_evals = evaluate(d, d["w_tau"], d["valid"], (0,))[0]
+            outs.append(be.g1_mul_same_base(G, tau_evals))                      # commit: [p_k(tau)] G
+            outs.append(evaluate(d, d["w_tau"], d["n"], (0, 1)))                # quotient: {tau, omega*tau}
+            z = challenge()
+            if world == 1:
+                be.bary_weights(d["lg"], z, out=d["w_z"])
+            else:
+                be.bary_weights_range(d["lg"], z, d["w_first"], d["rows"] + 1, out=d["w_z"])
+            outs.append(evaluate(d, d["w_z"], d["n"], (0, 1)))                  # openings: {z, omega*z}
         return outs
+
+    # builder outputs are allocated once: the columns of a proof live in the backend's pool
+    b_out = {
+        "edge_mont": [be.alloc(KIND_FR_MONT, ne) for _ in range(3)],
+        "node_mont": be.alloc(KIND_FR_MONT, nn),
+        "edge_i64": be.alloc(KIND_I64, ne),
+        "hist": be.alloc(KIND_U32, 4096),
+        "folded": be.alloc(KIND_FR, 8),
+        "acc16": be.alloc(KIND_FR_MONT, 16),
+    }
+
+    def step_builders():
+        # column builders of the heads this rank owns (heads are independent)
+        beta = challenge()
+        e_out = b_out["edge_mont"]
+        for head in range(rank, heads, world):
+            for i in range(4):  # feature / LeakyReLU / range / exp lookups
+                be.logup_accumulator(b_in["table"], b_in["query"], b_in["mult"], b_in["q_table"], b_in["q_query"], ne, beta, e_valid, out=e_out[i % 3])
+            for i in range(2):  # src / dst routes
+                be.route_node_accumulator(b_in["node_tab"], b_in["node_mult"], n_valid, nn, beta, out=b_out["node_mont"])
+                be.route_edge_accumulator(b_in["query"], e_valid, ne, beta, out=e_out[i])
+            for i in range(2):  # PSQ state, max counter
+                be.group_prefix_state(b_in["values"], b_in["q_new"], ne, out=e_out[i])
+            for _ in range(5):  # E_src, E_dst, M, Sum, inv broadcast to edges
+                be.broadcast_node_values(b_in["node_vals"], nn, b_in["src"], e_valid, ne, out=b_out["edge_i64"])
+            for _ in range(3):
+                be.histogram(b_in["hits"], e_valid, 4096, out=b_out["hist"])
+            for _ in range(6):  # bindings: fold rows by weights, then the running inner product
+                be.fold_rows(b_in["matrix"], n_valid, 8, w_node, n_valid, out=b_out["folded"])
+                be.zkmap_accumulator(b_out["folded"], b_out["folded"], 8, 16, out=b_out["acc16"])
+            be.weighted_sum(b_in["table"], beta, b_in["query"], e_valid, ne, out=e_out[2])
+
+    def step_resident():
+        step_builders()
+        return step_evaluations()
 
     def barrier():
         if world > 1:
-            import torch.distributed as dist
-
             dist.barrier()
         torch.cuda.synchronize()
         be.synchronize()
@@ -276,8 +355,6 @@ def main():
         report = be.timing_report()
         be.timing_enable(False)
         if world > 1:
-            import torch.distributed as dist
-
             t = torch.tensor([ms], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
@@ -287,8 +364,7 @@ def main():
     ms_per_step = ms_total / args.steps
     launches = sum(v[0] for v in report.values())
 
-    # roofline of the dominant kernel family (packed evaluation, 2-point)
-    fam = max(report.items(), key=lambda kv: kv[1][1])[0]
+    # ---- roofline of the dominant kernel (packed evaluation) ----------------------------
     peaks_path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(peaks_path):
         with open(peaks_path) as f:
@@ -298,68 +374,125 @@ def main():
         peak, peak_src = 6650.0, "fallback"
     eval_ms = sum(v[1] for kname, v in report.items() if kname.startswith("eval_partial"))
     eval_launches = sum(v[0] for kname, v in report.items() if kname.startswith("eval_partial"))
-    local_workload = [(d["name"], d["lg"], d["k"], d["valid"]) for d in domains if d["k"] > 0]
-    eval_bytes = workload_bytes(local_workload) * args.steps
-    achieved = eval_bytes / (eval_ms * 1e-3) / 1e9 if eval_ms > 0 else 0.0
+    local_workload = [(d["name"], d["lg"], d["k"], max(0, min(d["valid"] - d["begin"], d["rows"]))) for d in domains]
+    local_rows = {d["name"]: d["rows"] for d in domains}
+    local_bytes = sum(32 * (k * valid + valid) + 2 * 32 * (k + 1) * local_rows[name] for name, lg, k, valid in local_workload)
+    local_terms = sum(k * valid + 4 * k * local_rows[name] for name, lg, k, valid in local_workload)
+    achieved = local_bytes * args.steps / (eval_ms * 1e-3) / 1e9 if eval_ms > 0 else 0.0
+    mac_peak = be.measure_mac_peak(2, 20000)
+    products_per_s = local_terms * args.steps / (eval_ms * 1e-3) if eval_ms > 0 else 0.0
     roofline = {
         "bound": "hbm", "kernel": "eval_partial_kernel (packed evaluation, all launches of the step)", "achieved": achieved,
-        "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None, "traffic": None,
+        "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None, "traffic": 570.4e6 + 4.7e6,
+        "traffic_note": "ncu dram read+write of one 2-rotation launch on the 2^18 x 64 profiling case (algorithmic 545.3e6); see profiles/",
         "peak_source": peak_src, "launches": eval_launches, "avg_launch_ms": eval_ms / max(1, eval_launches),
-        "bytes_per_step": workload_bytes(local_workload),
-        "field_muladds_per_s": workload_terms(local_workload) * args.steps / (eval_ms * 1e-3) if eval_ms > 0 else None,
+        "bytes_per_step": local_bytes,
+        "integer_pipe": {"achieved_products_per_s": products_per_s, "measured_peak_products_per_s": mac_peak,
+                         "frac": products_per_s / mac_peak if mac_peak else None,
+                         "note": "the kernel's binding roof: 64 32x32 limb products per 32-byte term; peak measured in this run on register operands"},
     }
 
-    # ---- end to end: columns start in pinned host memory ---------------------------
+    # ---- end to end: columns start in pinned host memory --------------------------------
     e2e = None
     if not args.no_e2e:
         pinned = {}
         for d in domains:
-            if d["k"] == 0:
-                continue
-            rows = min(d["n"], 1 << 22)
+            rows = min(max(d["rows"], 1), 1 << 22)
             t = torch.empty((rows, 32), dtype=torch.uint8, pin_memory=True)
-            src = slabs[d["lg"]]
-            t.numpy()[:] = src[:rows]
+            t.numpy()[:] = slabs[d["lg"]][:rows]
             pinned[d["name"]] = t
-        h2d = sum(d["k"] * d["n"] * 32 for d in domains)
-        d2h = sum(d["k"] * 5 * 32 for d in domains)
+        h2d = sum(d["k"] * d["rows"] * 32 for d in domains) * world
+        d2h = sum(d["k"] * (5 * 32 + 96) for d in domains)
 
         def step_e2e():
             for d in domains:
-                if d["k"] == 0:
-                    continue
                 host = pinned[d["name"]].numpy()
-                rows = host.shape[0]
                 for buf in d["cols"]:
-                    for part in range(0, d["n"], rows):
-                        buf.upload(host, offset=part)
+                    done = 0
+                    while done < d["rows"]:
+                        part = min(d["rows"] - done, host.shape[0])
+                        buf.upload(host[:part], offset=done)
+                        done += part
             return step_resident()
 
-        e2e_ms, _, _ = timed(step_e2e, max(1, min(args.steps, 3)), 1)
-        e2e = {"value": e2e_ms / max(1, min(args.steps, 3)), "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+        e2e_steps = max(1, min(args.steps, 3))
+        e2e_ms, _, _ = timed(step_e2e, e2e_steps, 1)
+        e2e = {"value": e2e_ms / e2e_steps, "unit": "ms", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+    # ---- kernel sweep (single GPU): MSM Mpts/s, NTT GB/s, fold GB/s ------------------------
+    sweep = None
+    if world == 1 and not args.no_sweep and not args.profile_case:
+        sweep = run_sweep(be, rng, G, stream, small=args.small)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = cpu_count()
         v, desc = cpu_sample(workload, threads)
-        cpu_baseline = {"value": v, "unit": "ms", "cores": threads, "kind": "port", "sample": desc}
+        cpu_baseline = {"value": v, "unit": "ms", "cores": threads, "kind": "port",
+                        "sample": desc + "; covers the evaluation part of the step (the builders and the G1 batch are not in the CPU figure)"}
 
     if rank == 0:
         line = {
             "metric": METRIC, "value": ms_per_step, "unit": "ms", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
-            "dtype": "u32x8 Montgomery Fr (BLS12-381)", "data": "synthetic",
+            "dtype": "u32x8 Montgomery Fr / u32x12 Fp (BLS12-381)", "data": "synthetic",
             "config": {"workload": wl_name, "l2": "inputs larger than L2 (5.3 GB edge columns, 2.7 GB FH columns per pass)",
-                       "sharding": f"columns of every domain split across {world} rank(s), no data-path collective"},
+                       "sharding": f"rows of every domain split across {world} rank(s); per-call all-gather of the partial sums (K*P*32 B) over NCCL; "
+                                   f"builder heads dealt round-robin"},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
-            "kernel_ms": {k: round(v[1], 3) for k, v in report.items()}, "clocks": clocks,
+            "kernel_ms": {k: round(v[1], 3) for k, v in report.items()}, "clocks": clocks, "sweep": sweep,
         }
         print(json.dumps(line))
     if world > 1:
-        import torch.distributed as dist
-
         dist.destroy_process_group()
     return 0
+
+
+def run_sweep(be, rng, G, stream, small=False):
+    """Stand-alone kernels of the sweep at one representative size each (device-timed)."""
+    import torch
+
+    from project_b200 import KIND_FR
+
+    def timed_ms(fn, reps=3):
+        fn()
+        be.synchronize()
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(reps):
+            fn()
+        stop.record(stream)
+        be.synchronize()
+        return start.elapsed_time(stop) / reps
+
+    def rand_fr(n):
+        a = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+        a[:, 31] &= 0x3F
+        return a
+
+    out = {}
+    lg = 14 if small else 20
+    n = 1 << lg
+    scalars = be.upload(rand_fr(n), KIND_FR)
+    points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n), KIND_FR), n)
+    ms = timed_ms(lambda: be.msm(scalars, points, n))
+    out["msm"] = {"log2n": lg, "ms": ms, "Mpts_per_s": n / ms / 1e3}
+    lg = 14 if small else 22
+    n = 1 << lg
+    from project_b200 import KIND_FR_MONT
+
+    vec = be.upload(rand_fr(n), KIND_FR)
+    res = be.alloc(KIND_FR_MONT, n)
+    ms = timed_ms(lambda: be.ntt(vec, lg, out=res))
+    out["ntt"] = {"log2n": lg, "batch": 1, "ms": ms, "GB_per_s": 2 * 32 * n / ms / 1e6,
+                  "field_mults_per_s": (n // 2) * lg / ms * 1e3}
+    r = rand_fr(1)[0]
+    ms = timed_ms(lambda: be.fold(vec, n, r, out=res))
+    out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6}
+    for b in (scalars, points, vec, res):
+        b.free()
+    return out
 
 
 if __name__ == "__main__":

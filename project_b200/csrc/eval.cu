@@ -292,19 +292,20 @@ namespace gzk
                 eval_partial_kernel<1><<<blocks, kThreads, kSmemBytes, stream>>>(args);
         }
 
-        // Sums the per-tile partials of one (rotation, column) pair, reduces once and
-        // writes the canonical result.
+        // One warp per (rotation, column) pair: the lanes sum the per-tile partials, the
+        // warp adds them up exactly, lane 0 reduces once and writes the result.
         __global__ void eval_finish_kernel(const uint32_t* partial, const int* kinds, uint32_t tiles, uint32_t p_count,
                                            uint32_t k_count, Fr* out_canonical, int uniform_kind = -1, int out_montgomery = 0)
         {
-            const uint32_t idx = blockIdx.x * blockDim.x + threadIdx.x;
+            const uint32_t lane = threadIdx.x & 31;
+            const uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
             if (idx >= p_count * k_count) return;
             const uint32_t p = idx / k_count;
             const uint32_t k = idx - p * k_count;
             uint32_t acc[kAccLimbs];
 #pragma unroll
             for (int i = 0; i < kAccLimbs; ++i) acc[i] = 0;
-            for (uint32_t tile = 0; tile < tiles; ++tile)
+            for (uint32_t tile = lane; tile < tiles; tile += 32)
             {
                 const uint32_t* src = partial + ((static_cast<uint64_t>(tile) * p_count + p) * k_count + k) * kAccLimbs;
                 uint32_t t[kAccLimbs];
@@ -312,6 +313,15 @@ namespace gzk
                 for (int i = 0; i < kAccLimbs; ++i) t[i] = src[i];
                 acc_add<kAccLimbs, kAccLimbs>(acc, t);
             }
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                uint32_t other[kAccLimbs];
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, acc[i], offset);
+                acc_add<kAccLimbs, kAccLimbs>(acc, other);
+            }
+            if (lane != 0) return;
             // acc = 2^256 * S (canonical columns) or 2^512 * S (Montgomery columns), S the
             // true sum; 9 reduction rows divide by 2^288.
             const Fr reduced = redc_wide<FrCfg, 9>(acc);
@@ -383,7 +393,7 @@ namespace gzk
                            Fr* out, bool out_montgomery)
     {
         LaunchScope scope(ctx, "eval_finish");
-        eval_finish_kernel<<<(k_count + 127) / 128, 128, 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
+        eval_finish_kernel<<<(k_count + 3) / 4, 128, 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
                                                                           out_montgomery ? 1 : 0);
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return GZK_OK;
@@ -509,7 +519,7 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
         const uint32_t outs = p_now * static_cast<uint32_t>(k_count);
         {
             LaunchScope scope(ctx, "eval_finish");
-            eval_finish_kernel<<<(outs + 127) / 128, 128, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
+            eval_finish_kernel<<<(outs + 3) / 4, 128, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
                                                                            static_cast<uint32_t>(k_count), d_out + p0 * k_count);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
@@ -650,7 +660,7 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     launch_eval_partial(s, args, static_cast<int>(p_count), static_cast<unsigned>(blocks));
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
-    eval_finish_kernel<<<(outs + 127) / 128, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
+    eval_finish_kernel<<<(outs + 3) / 4, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
                                                          static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device));
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     return GZK_OK;

@@ -320,9 +320,10 @@ namespace gzk
         return out;
     }
 
-    // Fermat inverse a^(modulus-2); a must be non-zero (0 maps to 0).
+    // Fermat inverse a^(modulus-2); a must be non-zero (0 maps to 0).  Kept as the
+    // cross-check of the binary algorithm below.
     template <typename Cfg>
-    GZK_HD Fe<Cfg> inv(const Fe<Cfg>& a)
+    GZK_HD Fe<Cfg> inv_fermat(const Fe<Cfg>& a)
     {
         constexpr int N = Cfg::N;
         Fe<Cfg> out = Fe<Cfg>::one();
@@ -353,6 +354,128 @@ namespace gzk
             }
         }
         return out;
+    }
+
+    namespace detail
+    {
+        template <int N>
+        GZK_HD bool limbs_even(const uint32_t* a) { return (a[0] & 1u) == 0; }
+        template <int N>
+        GZK_HD bool limbs_is_one(const uint32_t* a)
+        {
+            uint32_t acc = a[0] ^ 1u;
+#pragma unroll
+            for (int i = 1; i < N; ++i) acc |= a[i];
+            return acc == 0;
+        }
+        template <int N>
+        GZK_HD void limbs_shr1(uint32_t* a)
+        {
+#pragma unroll
+            for (int i = 0; i < N - 1; ++i) a[i] = (a[i] >> 1) | (a[i + 1] << 31);
+            a[N - 1] >>= 1;
+        }
+        // a >= b ?
+        template <int N>
+        GZK_HD bool limbs_geq(const uint32_t* a, const uint32_t* b)
+        {
+            mp::sub_cc(a[0], b[0]);
+#pragma unroll
+            for (int i = 1; i < N; ++i) mp::subc_cc(a[i], b[i]);
+            return mp::subc(0, 0) == 0;  // no borrow
+        }
+        template <int N>
+        GZK_HD void limbs_sub(uint32_t* a, const uint32_t* b)
+        {
+            a[0] = mp::sub_cc(a[0], b[0]);
+#pragma unroll
+            for (int i = 1; i < N - 1; ++i) a[i] = mp::subc_cc(a[i], b[i]);
+            a[N - 1] = mp::subc(a[N - 1], b[N - 1]);
+        }
+        // x = x / 2 mod modulus (x < modulus; modulus odd with a spare top bit)
+        template <typename Cfg>
+        GZK_HD void halve_mod(uint32_t* x)
+        {
+            constexpr int N = Cfg::N;
+            if (x[0] & 1u)
+            {
+                x[0] = mp::add_cc(x[0], Cfg::mod(0));
+#pragma unroll
+                for (int i = 1; i < N - 1; ++i) x[i] = mp::addc_cc(x[i], Cfg::mod(i));
+                x[N - 1] = mp::addc(x[N - 1], Cfg::mod(N - 1));
+            }
+            limbs_shr1<N>(x);
+        }
+    }
+
+    // Inverse by the binary extended Euclidean algorithm (shifts and subtractions on
+    // N limbs, about 2*bits short iterations) followed by one Montgomery product that
+    // restores the Montgomery form.  Roughly five times shorter than the Fermat power
+    // as a dependent chain, which matters because every batch inversion of the library
+    // ends in exactly one serial inversion.  a must be non-zero (0 maps to 0).
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> inv(const Fe<Cfg>& a)
+    {
+        constexpr int N = Cfg::N;
+        if (a.is_zero()) return a;
+        uint32_t u[N], v[N], x1[N], x2[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+        {
+            u[i] = a.l[i];
+            v[i] = Cfg::mod(i);
+            x1[i] = 0;
+            x2[i] = 0;
+        }
+        x1[0] = 1;
+        // every pass removes at least one bit from u or v: 2 * 32 * N passes suffice
+        for (int guard = 0; guard < 64 * N + 8; ++guard)
+        {
+            if (detail::limbs_is_one<N>(u) || detail::limbs_is_one<N>(v)) break;
+            while (detail::limbs_even<N>(u))
+            {
+                detail::limbs_shr1<N>(u);
+                detail::halve_mod<Cfg>(x1);
+            }
+            while (detail::limbs_even<N>(v))
+            {
+                detail::limbs_shr1<N>(v);
+                detail::halve_mod<Cfg>(x2);
+            }
+            if (detail::limbs_geq<N>(u, v))
+            {
+                detail::limbs_sub<N>(u, v);
+                // x1 = x1 - x2 mod modulus
+                if (!detail::limbs_geq<N>(x1, x2))
+                {
+                    x1[0] = mp::add_cc(x1[0], Cfg::mod(0));
+#pragma unroll
+                    for (int i = 1; i < N - 1; ++i) x1[i] = mp::addc_cc(x1[i], Cfg::mod(i));
+                    x1[N - 1] = mp::addc(x1[N - 1], Cfg::mod(N - 1));
+                }
+                detail::limbs_sub<N>(x1, x2);
+            }
+            else
+            {
+                detail::limbs_sub<N>(v, u);
+                if (!detail::limbs_geq<N>(x2, x1))
+                {
+                    x2[0] = mp::add_cc(x2[0], Cfg::mod(0));
+#pragma unroll
+                    for (int i = 1; i < N - 1; ++i) x2[i] = mp::addc_cc(x2[i], Cfg::mod(i));
+                    x2[N - 1] = mp::addc(x2[N - 1], Cfg::mod(N - 1));
+                }
+                detail::limbs_sub<N>(x2, x1);
+            }
+        }
+        Fe<Cfg> plain;  // (a as an integer)^-1 mod modulus
+        const bool from_u = detail::limbs_is_one<N>(u);
+#pragma unroll
+        for (int i = 0; i < N; ++i) plain.l[i] = from_u ? x1[i] : x2[i];
+        // a = A*R  =>  plain = A^-1 R^-1; Montgomery form of A^-1 is A^-1 R = plain * R^2,
+        // i.e. the Montgomery product of plain with R^3.
+        const Fe<Cfg> r3 = mul(Fe<Cfg>::r2(), Fe<Cfg>::r2());
+        return mul(plain, r3);
     }
 
     // Full 2N-limb product of two N-limb integers (no reduction).  Products whose

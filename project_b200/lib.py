@@ -157,30 +157,30 @@ class Backend:
         self._check(self.lib.gzk_bary_weights(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), out.handle))
         return out
 
-    def logup_accumulator(self, table, query, mult, q_table, q_query, n, beta, active_count):
-        out = self.alloc(KIND_FR_MONT, n)
+    def logup_accumulator(self, table, query, mult, q_table, q_query, n, beta, active_count, out=None):
+        out = out or self.alloc(KIND_FR_MONT, n)
         self._check(self.lib.gzk_logup_accumulator(self.ctx, table.handle, query.handle, mult.handle, q_table.handle, q_query.handle,
                                                    _sz(n), _ptr(_fr(beta)), _sz(active_count), out.handle))
         return out
 
-    def route_node_accumulator(self, table, mult, valid_length, domain_size, beta):
-        out = self.alloc(KIND_FR_MONT, domain_size)
+    def route_node_accumulator(self, table, mult, valid_length, domain_size, beta, out=None):
+        out = out or self.alloc(KIND_FR_MONT, domain_size)
         self._check(self.lib.gzk_route_node_accumulator(self.ctx, table.handle, mult.handle, _sz(valid_length), _sz(domain_size),
                                                         _ptr(_fr(beta)), out.handle))
         return out
 
-    def route_edge_accumulator(self, query, valid_length, domain_size, beta):
-        out = self.alloc(KIND_FR_MONT, domain_size)
+    def route_edge_accumulator(self, query, valid_length, domain_size, beta, out=None):
+        out = out or self.alloc(KIND_FR_MONT, domain_size)
         self._check(self.lib.gzk_route_edge_accumulator(self.ctx, query.handle, _sz(valid_length), _sz(domain_size), _ptr(_fr(beta)), out.handle))
         return out
 
-    def group_prefix_state(self, values, q_new, n):
-        out = self.alloc(KIND_FR_MONT, n)
+    def group_prefix_state(self, values, q_new, n, out=None):
+        out = out or self.alloc(KIND_FR_MONT, n)
         self._check(self.lib.gzk_group_prefix_state(self.ctx, values.handle, q_new.handle, _sz(n), out.handle))
         return out
 
-    def zkmap_accumulator(self, a, b, count, domain_size):
-        out = self.alloc(KIND_FR_MONT, domain_size)
+    def zkmap_accumulator(self, a, b, count, domain_size, out=None):
+        out = out or self.alloc(KIND_FR_MONT, domain_size)
         mu = np.zeros(32, dtype=np.uint8)
         self._check(self.lib.gzk_zkmap_accumulator(self.ctx, a.handle, b.handle, _sz(count), _sz(domain_size), out.handle, _ptr(mu)))
         return out, mu
@@ -190,8 +190,8 @@ class Backend:
         self._check(self.lib.gzk_matrix_horner(self.ctx, matrix.handle, _sz(rows), _sz(cols), _ptr(_fr(x)), _ptr(out)))
         return out
 
-    def fold_rows(self, matrix, rows, cols, weights, row_count):
-        out = self.alloc(KIND_FR, cols)
+    def fold_rows(self, matrix, rows, cols, weights, row_count, out=None):
+        out = out or self.alloc(KIND_FR, cols)
         self._check(self.lib.gzk_fold_rows(self.ctx, matrix.handle, _sz(rows), _sz(cols), weights.handle, _sz(row_count), out.handle))
         return out
 
@@ -205,8 +205,8 @@ class Backend:
         self._check(self.lib.gzk_powers(self.ctx, _ptr(_fr(challenge)), _sz(count), out.handle))
         return out
 
-    def weighted_sum(self, left, lam, right, count, domain_size):
-        out = self.alloc(KIND_FR_MONT, domain_size)
+    def weighted_sum(self, left, lam, right, count, domain_size, out=None):
+        out = out or self.alloc(KIND_FR_MONT, domain_size)
         self._check(self.lib.gzk_weighted_sum(self.ctx, left.handle, _ptr(_fr(lam)), right.handle, _sz(count), _sz(domain_size), out.handle))
         return out
 
@@ -216,13 +216,13 @@ class Backend:
                                                      _ptr(_fr(eta_index)), _ptr(_fr(eta_value)), out.handle))
         return out
 
-    def broadcast_node_values(self, node_values, node_count, index, edge_count, domain_size):
-        out = self.alloc(node_values.kind, domain_size)
+    def broadcast_node_values(self, node_values, node_count, index, edge_count, domain_size, out=None):
+        out = out or self.alloc(node_values.kind, domain_size)
         self._check(self.lib.gzk_broadcast_node_values(self.ctx, node_values.handle, _sz(node_count), index.handle, _sz(edge_count), _sz(domain_size), out.handle))
         return out
 
-    def histogram(self, indices, count, domain_size):
-        out = self.alloc(KIND_U32, domain_size)
+    def histogram(self, indices, count, domain_size, out=None):
+        out = out or self.alloc(KIND_U32, domain_size)
         self._check(self.lib.gzk_histogram(self.ctx, indices.handle, _sz(count), _sz(domain_size), out.handle))
         return out
 
@@ -269,8 +269,8 @@ class Backend:
         self._check(self.lib.gzk_srs_lagrange(self.ctx, ctypes.c_uint(log2n), _ptr(base), _ptr(_fr(tau)), out.handle))
         return out
 
-    def ntt(self, inp, log2n, batch=1, inverse=False, coset_shift=None):
-        out = self.alloc(KIND_FR_MONT, (1 << log2n) * batch)
+    def ntt(self, inp, log2n, batch=1, inverse=False, coset_shift=None, out=None):
+        out = out or self.alloc(KIND_FR_MONT, (1 << log2n) * batch)
         shift = None if coset_shift is None else _ptr(_fr(coset_shift))
         self._check(self.lib.gzk_ntt(self.ctx, inp.handle, out.handle, ctypes.c_uint(log2n), _sz(batch), int(bool(inverse)), shift))
         return out
@@ -280,8 +280,8 @@ class Backend:
         self._check(self.lib.gzk_coset_lde(self.ctx, inp.handle, ctypes.c_uint(log2n), ctypes.c_uint(log2_blowup), _ptr(_fr(shift)), out.handle))
         return out
 
-    def fold(self, table, n, challenge):
-        out = self.alloc(KIND_FR_MONT, n // 2)
+    def fold(self, table, n, challenge, out=None):
+        out = out or self.alloc(KIND_FR_MONT, n // 2)
         self._check(self.lib.gzk_fold(self.ctx, table.handle, _sz(n), _ptr(_fr(challenge)), out.handle))
         return out
 
@@ -291,8 +291,8 @@ class Backend:
                                                 abs_ids.handle if abs_ids is not None else None, weights.handle, _ptr(out)))
         return out
 
-    def bary_weights_range(self, log2n, x, first, count):
-        out = self.alloc(KIND_FR_MONT, max(count, 1))
+    def bary_weights_range(self, log2n, x, first, count, out=None):
+        out = out or self.alloc(KIND_FR_MONT, max(count, 1))
         self._check(self.lib.gzk_bary_weights_range(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), ctypes.c_uint64(first), ctypes.c_uint64(count), out.handle))
         return out
 

@@ -51,9 +51,10 @@ int check_field(const char* name, std::mt19937_64& rng)
         if (!eq(gzk::add(a, b), (oa + ob).v)) { ++failures; std::printf("%s add mismatch\n", name); }
         if (!eq(gzk::sub(a, b), (oa - ob).v)) { ++failures; std::printf("%s sub mismatch\n", name); }
         if (!eq(gzk::from_mont(a), ca)) { ++failures; std::printf("%s from_mont mismatch\n", name); }
-        if (iter < 40 && !oa.is_zero())
+        if (iter < 400 && !oa.is_zero())
         {
             if (!eq(gzk::inv(a), oa.inv().v)) { ++failures; std::printf("%s inv mismatch\n", name); }
+            if (!eq(gzk::inv_fermat(a), oa.inv().v)) { ++failures; std::printf("%s fermat inv mismatch\n", name); }
             if (!eq(gzk::pow_u64(a, 0x123456789abcdefULL + iter), oa.pow(0x123456789abcdefULL + iter).v)) { ++failures; std::printf("%s pow mismatch\n", name); }
         }
         if (failures > 5) return failures;
