@@ -232,9 +232,12 @@ def main():
             d["w_tau"] = be.bary_weights(lg, tau)
             d["w_z"] = be.alloc(KIND_FR_MONT, n)
         else:
-            d["w_first"] = (begin - 1) % n
-            d["w_tau"] = be.bary_weights_range(lg, tau, d["w_first"], rows + 1)
-            d["w_z"] = be.alloc(KIND_FR_MONT, rows + 1)
+            # weight slice with a one-row halo for the rotation by one; a rank that holds a
+            # whole (tiny) domain keeps the whole vector
+            d["w_first"] = (begin - 1) % n if rows + 1 <= n else 0
+            d["w_count"] = min(rows + 1, n)
+            d["w_tau"] = be.bary_weights_range(lg, tau, d["w_first"], d["w_count"])
+            d["w_z"] = be.alloc(KIND_FR_MONT, d["w_count"])
         domains.append(d)
 
     # builder inputs (edge- and node-shaped columns of one head; reused for every head)
@@ -292,7 +295,7 @@ def main():
             if world == 1:
                 be.bary_weights(d["lg"], z, out=d["w_z"])
             else:
-                be.bary_weights_range(d["lg"], z, d["w_first"], d["rows"] + 1, out=d["w_z"])
+                be.bary_weights_range(d["lg"], z, d["w_first"], d["w_count"], out=d["w_z"])
             outs.append(evaluate(d, d["w_z"], d["n"], (0, 1)))                  # openings: {z, omega*z}
         return outs
 

@@ -706,7 +706,7 @@ extern "C" int gzk_eval_batch_range(gzk_ctx* ctx, gzk_buf* const* cols, size_t k
         // local row c is global row row_offset + c and needs w[(row_offset + c - rot) mod n],
         // stored at buffer index (row_offset + c - rot - weights_first) mod n
         const uint64_t first_needed = (row_offset + n - rotations[p] + n - weights_first) & (n - 1);
-        if (len != 0 && first_needed + len > weights->count)
+        if (len != 0 && weights->count < n && first_needed + len > weights->count)
             return fail(ctx, GZK_E_INVALID, "eval_batch_range: the weight slice does not cover the rows at this rotation");
         effective[p] = (n - first_needed) & (n - 1);
     }
