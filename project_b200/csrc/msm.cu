@@ -13,6 +13,7 @@
 // Signed digits halve the bucket count (2^(c-1) per window): a negative digit adds
 // the negated point.  Group sums do not depend on the order of additions, so the
 // atomics of steps 1 and 3 leave the result bit-identical from run to run.
+#include <cstdlib>
 #include <cstring>
 
 #include "block.cuh"
@@ -24,6 +25,23 @@ namespace gzk
     {
         constexpr int kThreads = 128;
         constexpr int kMaxWindows = 32;
+        // Buckets with more entries than kBigBucket (skewed scalars: small integers, constant
+        // columns, the short top window) are cut into slices of kSliceEntries entries; one CTA
+        // sums a slice, one thread then adds the slices of a bucket.
+        constexpr uint32_t kBigBucket = 1024;
+        constexpr uint32_t kSliceEntries = 2048;
+
+        struct BigItem
+        {
+            uint32_t bucket;
+            uint32_t slice;
+        };
+        struct BigBucket
+        {
+            uint32_t bucket;
+            uint32_t first_item;
+            uint32_t slices;
+        };
 
         struct MsmPlan
         {
@@ -131,6 +149,7 @@ namespace gzk
             const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
             if (b >= buckets) return;
             const uint32_t start = bucket_start[b], size = bucket_size[b];
+            if (size > kBigBucket) return;  // handled cooperatively by msm_big_slices_kernel
             G1Xyzz acc = G1Xyzz::infinity();
 #pragma unroll 1
             for (uint32_t k = 0; k < size; ++k)
@@ -139,6 +158,78 @@ namespace gzk
                 acc = g1_add_mixed(acc, load_affine(points + (e >> 1)), (e & 1u) != 0);
             }
             store_xyzz(out + b, acc);
+        }
+
+        // counters[0] = number of slice items, counters[1] = number of big buckets
+        __global__ void __launch_bounds__(kThreads) msm_plan_big_kernel(const uint32_t* bucket_size, uint32_t buckets, uint32_t* counters,
+                                                                       BigItem* items, BigBucket* big)
+        {
+            const uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+            if (b >= buckets) return;
+            const uint32_t size = bucket_size[b];
+            if (size <= kBigBucket) return;
+            const uint32_t slices = (size + kSliceEntries - 1) / kSliceEntries;
+            const uint32_t first = atomicAdd(counters, slices);
+            const uint32_t slot = atomicAdd(counters + 1, 1u);
+            BigBucket bb;
+            bb.bucket = b;
+            bb.first_item = first;
+            bb.slices = slices;
+            big[slot] = bb;
+            for (uint32_t j = 0; j < slices; ++j)
+            {
+                BigItem it;
+                it.bucket = b;
+                it.slice = j;
+                items[first + j] = it;
+            }
+        }
+
+        // CTA per slice item: the threads stride over the slice, then a shared-memory tree
+        __global__ void __launch_bounds__(kThreads) msm_big_slices_kernel(const G1Affine* points, const uint32_t* bucket_start,
+                                                                         const uint32_t* bucket_size, const uint32_t* entries,
+                                                                         const uint32_t* counters, const BigItem* items, G1Xyzz* partial)
+        {
+            __shared__ G1Xyzz slots[kThreads];
+            if (blockIdx.x >= counters[0]) return;
+            const BigItem it = items[blockIdx.x];
+            const uint32_t start = bucket_start[it.bucket], size = bucket_size[it.bucket];
+            const uint32_t begin = it.slice * kSliceEntries;
+            const uint32_t end = begin + kSliceEntries < size ? begin + kSliceEntries : size;
+            G1Xyzz acc = G1Xyzz::infinity();
+#pragma unroll 1
+            for (uint32_t k = begin + threadIdx.x; k < end; k += kThreads)
+            {
+                const uint32_t e = entries[start + k];
+                acc = g1_add_mixed(acc, load_affine(points + (e >> 1)), (e & 1u) != 0);
+            }
+            slots[threadIdx.x] = acc;
+            __syncthreads();
+            for (uint32_t offset = kThreads / 2; offset > 0; offset >>= 1)
+            {
+                if (threadIdx.x < offset) slots[threadIdx.x] = g1_add(slots[threadIdx.x], slots[threadIdx.x + offset]);
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) store_xyzz(partial + blockIdx.x, slots[0]);
+        }
+
+        // CTA per big bucket: the threads stride over its slice partials, then a tree
+        __global__ void __launch_bounds__(kThreads) msm_big_combine_kernel(const uint32_t* counters, const BigBucket* big, const G1Xyzz* partial,
+                                                                          G1Xyzz* out)
+        {
+            __shared__ G1Xyzz slots[kThreads];
+            if (blockIdx.x >= counters[1]) return;
+            const BigBucket bb = big[blockIdx.x];
+            G1Xyzz acc = G1Xyzz::infinity();
+            for (uint32_t j = threadIdx.x; j < bb.slices; j += kThreads) acc = g1_add(acc, load_xyzz(partial + bb.first_item + j));
+            slots[threadIdx.x] = acc;
+            __syncthreads();
+            for (uint32_t offset = kThreads / 2; offset > 0; offset >>= 1)
+            {
+                if (threadIdx.x < offset) slots[threadIdx.x] = g1_add(slots[threadIdx.x], slots[threadIdx.x + offset]);
+                __syncthreads();
+            }
+            if (threadIdx.x == 0) store_xyzz(out + bb.bucket, slots[0]);
         }
 
         // CTA (window w, bit b): sum of the buckets j (multiplier j+1) with bit b of (j+1) set
@@ -196,7 +287,10 @@ namespace gzk
         {
             uint32_t log2n = 0;
             while ((1ULL << (log2n + 1)) <= n) ++log2n;
-            int c = static_cast<int>(log2n) - 4;
+            // larger windows mean fewer mixed additions (n per window) but 2^(c-1) * c / 2 full
+            // additions per window in the bit-split reduction; log2(n) - 7 balances the two
+            int c = static_cast<int>(log2n) - 6;
+            if (const char* forced = std::getenv("GZK_MSM_WINDOW")) c = std::atoi(forced);  // tuning experiments only
             if (c < 8) c = 8;
             if (c > 16) c = 16;
             MsmPlan p;
@@ -216,8 +310,12 @@ namespace gzk
         const uint64_t buckets = static_cast<uint64_t>(plan.windows) * plan.half;
         const size_t code_bytes = static_cast<size_t>(n) * plan.windows * sizeof(uint32_t);
         const size_t bucket_u32 = buckets * sizeof(uint32_t);
-        const size_t total = 2 * code_bytes + 3 * bucket_u32 + buckets * sizeof(G1Xyzz) + static_cast<size_t>(plan.windows) * plan.c * sizeof(G1Xyzz) +
-                             sizeof(G1Xyzz) + sizeof(G1Affine) + 4096;
+        const uint64_t total_entries = n * plan.windows;
+        const uint64_t max_big = total_entries / kBigBucket + 1;          // buckets that can exceed the threshold
+        const uint64_t max_items = total_entries / kSliceEntries + max_big; // sum of ceil(size / slice) over them
+        const size_t big_bytes = max_items * (sizeof(BigItem) + sizeof(G1Xyzz)) + max_big * sizeof(BigBucket) + 64;
+        const size_t total = big_bytes + 2 * code_bytes + 3 * bucket_u32 + buckets * sizeof(G1Xyzz) + static_cast<size_t>(plan.windows) * plan.c * sizeof(G1Xyzz) +
+                             sizeof(G1Xyzz) + sizeof(G1Affine) + 8192;
         void* scratch = nullptr;
         int rc = ensure_scratch(ctx, 1, total, &scratch);
         if (rc != GZK_OK) return rc;
@@ -236,6 +334,10 @@ namespace gzk
         uint32_t* bucket_size = reinterpret_cast<uint32_t*>(take(bucket_u32));
         uint32_t* bucket_start = reinterpret_cast<uint32_t*>(take(bucket_u32));
         uint32_t* cursor = reinterpret_cast<uint32_t*>(take(bucket_u32));
+        G1Xyzz* big_partial = reinterpret_cast<G1Xyzz*>(take(max_items * sizeof(G1Xyzz)));
+        BigItem* big_items = reinterpret_cast<BigItem*>(take(max_items * sizeof(BigItem)));
+        BigBucket* big_buckets = reinterpret_cast<BigBucket*>(take(max_big * sizeof(BigBucket)));
+        uint32_t* big_counters = reinterpret_cast<uint32_t*>(take(64));
         if (static_cast<size_t>(cur - static_cast<char*>(scratch)) > ctx->scratch[1].bytes)
             return fail(ctx, GZK_E_INVALID, "msm: internal scratch accounting error");
 
@@ -263,10 +365,26 @@ namespace gzk
             msm_scatter_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(code, n, plan, bucket_start, cursor, entries);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(big_counters, 0, 64, ctx->stream));
+        {
+            LaunchScope scope(ctx, "msm_plan_big");
+            msm_plan_big_kernel<<<static_cast<unsigned>((buckets + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
+                bucket_size, static_cast<uint32_t>(buckets), big_counters, big_items, big_buckets);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
         {
             LaunchScope scope(ctx, "msm_buckets");
             msm_buckets_kernel<<<static_cast<unsigned>((buckets + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(
                 static_cast<const G1Affine*>(points->dptr), bucket_start, bucket_size, entries, static_cast<uint32_t>(buckets), bucket_points);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            // grids are upper bounds; CTAs beyond the counted work return at once
+            LaunchScope scope(ctx, "msm_big_buckets", 2);
+            msm_big_slices_kernel<<<static_cast<unsigned>(max_items), kThreads, 0, ctx->stream>>>(
+                static_cast<const G1Affine*>(points->dptr), bucket_start, bucket_size, entries, big_counters, big_items, big_partial);
+            msm_big_combine_kernel<<<static_cast<unsigned>(max_big), kThreads, 0, ctx->stream>>>(
+                big_counters, big_buckets, big_partial, bucket_points);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         {

@@ -120,3 +120,22 @@ def test_commit_batch_and_msm_against_lagrange_srs_agree(be):
     srs = be.srs_lagrange(log2n, G, tau)
     for i in range(k):
         assert np.array_equal(be.msm(bufs[i], srs, valid), points[i])
+
+
+def test_msm_skewed_scalars(be):
+    """Small-integer and constant scalars put thousands of points into one bucket: the
+    cooperative big-bucket path must give the same point."""
+    from project_b200 import KIND_FR
+
+    n = 1 << 15
+    rng = np.random.default_rng(8)
+    kb = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    kb[:, 31] &= 0x3F
+    pts = be.g1_fixed_base_mul(G, be.upload(kb, KIND_FR), n)
+    ks = fr_ints(kb)
+    G0 = (pyref.GX, pyref.GY)
+    for name, scalars in (("ones", [1] * n), ("bits", [int(v) for v in rng.integers(0, 2, size=n)]),
+                          ("small signed", [int(v) % R for v in rng.integers(-40, 40, size=n)])):
+        got = be.msm(be.upload(fr_array(scalars), KIND_FR), pts, n)
+        want = sum(k * s for k, s in zip(ks, scalars)) % R
+        assert bytes(got) == pyref.g1_bytes(pyref.g1_mul(want, G0)), name
