@@ -91,6 +91,9 @@ void* gzk_buf_device_ptr(gzk_buf* buf);
 /* ---- a1: field helpers ---------------------------------------------------------
  * omega_n = 5^((r-1)/n): FieldElement::root_of_unity (field.hpp:87-101). */
 int gzk_root_of_unity(gzk_ctx* ctx, uint64_t size, uint8_t out[32]);
+/* FieldElement +, -, *, inv on the host (field.hpp:112-179) for the caller's scalar
+ * glue: op 0 add, 1 sub, 2 mul, 3 inverse of a (GZK_E_DOMAIN for zero). */
+int gzk_fr_op(int op, const uint8_t a[32], const uint8_t b[32], uint8_t out[32]);
 
 /* ---- a2: barycentric weights ----------------------------------------------------
  * w_i(x) = (x^n - 1) * omega^i / n / (x - omega^i), i < n = 2^log2n.

@@ -459,4 +459,30 @@ extern "C"
         host_fr_to_bytes(from_mont(host_root_of_unity(log2n)), out);
         return GZK_OK;
     }
+
+    // Host-side scalar arithmetic for the O(#columns) glue of a caller (same limb code as the
+    // kernels, run on the CPU): op 0 add, 1 sub, 2 mul, 3 inverse of a (b ignored).
+    int gzk_fr_op(int op, const uint8_t a[32], const uint8_t b[32], uint8_t out[32])
+    {
+        if (a == nullptr || out == nullptr || (op != 3 && b == nullptr)) return GZK_E_INVALID;
+        bool ok_a = false, ok_b = true;
+        const Fr x = host_fr_from_bytes(a, &ok_a);
+        Fr y = Fr::zero();
+        if (op != 3) y = host_fr_from_bytes(b, &ok_b);
+        if (!ok_a || !ok_b) return GZK_E_INVALID;
+        Fr r;
+        switch (op)
+        {
+        case 0: r = add(x, y); break;
+        case 1: r = sub(x, y); break;
+        case 2: r = from_mont(mul(to_mont(x), to_mont(y))); break;
+        case 3:
+            if (x.is_zero()) return GZK_E_DOMAIN;  // FieldElement::inv throws on zero
+            r = from_mont(inv(to_mont(x)));
+            break;
+        default: return GZK_E_INVALID;
+        }
+        host_fr_to_bytes(r, out);
+        return GZK_OK;
+    }
 }
