@@ -43,19 +43,23 @@ namespace gzk
         };
 
         // ---- per-warp TMA ring -------------------------------------------------------
-        // Column values are read exactly once, so they bypass L1 entirely: lane 0 of
-        // each warp streams 4 KiB chunks (128 rows) of the column into a private
-        // shared-memory ring with cp.async.bulk, kStages chunks ahead of the
-        // arithmetic, and the warp waits on the chunk's mbarrier.  That keeps
-        // kStages x 4 KiB per warp in flight towards HBM at no register cost.  Every
-        // wait is bounded; a wait that gives up raises the status word and the
+        // Both operands of the inner product reach the arithmetic through shared memory:
+        // lane 0 of each warp streams 2 KiB chunks (64 rows) of the column, and the
+        // matching 64 weights for every rotation, into a private ring with
+        // cp.async.bulk, one chunk ahead of the arithmetic; the warp waits on the chunk's
+        // mbarrier.  Column values (read once) bypass L1 entirely, the weights come from
+        // L2, and the multiply-accumulate loop sees only short shared-memory latencies
+        // (a global load per term in the loop halves the throughput of this kernel).
+        // Every wait is bounded; a wait that gives up raises the status word and the
         // kernel returns.
-        constexpr int kStages = 4;
-        constexpr int kChunkRows = 128;
+        constexpr int kStages = 2;
+        constexpr int kChunkRows = 64;
         constexpr int kChunkBytes = kChunkRows * 32;
         constexpr int kWarps = kThreads / 32;
-        constexpr size_t kRingBytes = static_cast<size_t>(kWarps) * kStages * kChunkBytes;
-        constexpr size_t kSmemBytes = kRingBytes + static_cast<size_t>(kWarps) * kStages * sizeof(uint64_t);
+        // a ring slot holds the column chunk and, behind it, one weight chunk per rotation
+        __host__ __device__ constexpr size_t slot_bytes(int p) { return static_cast<size_t>(1 + p) * kChunkBytes; }
+        __host__ __device__ constexpr size_t ring_bytes(int p) { return static_cast<size_t>(kWarps) * kStages * slot_bytes(p); }
+        __host__ __device__ constexpr size_t smem_bytes(int p) { return ring_bytes(p) + static_cast<size_t>(kWarps) * kStages * sizeof(uint64_t); }
         constexpr uint32_t kWaitLimit = 1u << 22;
 
         __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -108,8 +112,8 @@ namespace gzk
             extern __shared__ __align__(128) unsigned char smem[];
             const uint32_t lane = threadIdx.x & 31;
             const uint32_t warp_in_cta = threadIdx.x >> 5;
-            unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * kStages * kChunkBytes;
-            uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kRingBytes) + warp_in_cta * kStages;
+            unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * kStages * slot_bytes(P);
+            uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes(P)) + warp_in_cta * kStages;
             if (lane == 0)
             {
 #pragma unroll
@@ -136,7 +140,7 @@ namespace gzk
                 const uint64_t c_begin = static_cast<uint64_t>(tile) * a.tile_rows;
                 const uint64_t c_end = c_begin + a.tile_rows < a.len ? c_begin + a.tile_rows : a.len;
 
-                WideAcc acc[P];
+                WideAcc64 acc[P];
 #pragma unroll
                 for (int p = 0; p < P; ++p) acc[p].clear();
 
@@ -146,13 +150,27 @@ namespace gzk
                     const uint64_t rows = c_end > c_begin ? c_end - c_begin : 0;
                     const uint32_t chunks = static_cast<uint32_t>((rows + kChunkRows - 1) / kChunkRows);
                     auto issue = [&](uint32_t j) {
-                        // chunk j of this unit goes to ring slot (ring_pos + j) % kStages
+                        // chunk j of this unit goes to ring slot (ring_pos + j) % kStages: the column
+                        // rows, then for every rotation the weights those rows meet (the weight index
+                        // wraps around the domain at most once inside a chunk)
                         const uint32_t slot = (ring_pos + j) % kStages;
                         const uint64_t row0 = static_cast<uint64_t>(j) * kChunkRows;
-                        const uint32_t bytes = static_cast<uint32_t>((rows - row0 < kChunkRows ? rows - row0 : kChunkRows) * 32);
+                        const uint32_t rows_j = static_cast<uint32_t>(rows - row0 < kChunkRows ? rows - row0 : kChunkRows);
+                        const uint32_t bytes = rows_j * 32;
                         const uint32_t bar = smem_u32(bars + slot);
-                        mbar_expect_tx(bar, bytes);
-                        bulk_load(smem_u32(ring + static_cast<size_t>(slot) * kChunkBytes), base + row0 * 32, bytes, bar);
+                        unsigned char* dst = ring + static_cast<size_t>(slot) * slot_bytes(P);
+                        mbar_expect_tx(bar, bytes * (1 + P));
+                        bulk_load(smem_u32(dst), base + row0 * 32, bytes, bar);
+#pragma unroll
+                        for (int p = 0; p < P; ++p)
+                        {
+                            const uint64_t w0 = (c_begin + row0 - a.rot[p]) & a.mask;
+                            const uint64_t until_wrap = a.mask + 1 - w0;
+                            const uint32_t first = static_cast<uint32_t>(until_wrap < rows_j ? until_wrap : rows_j);
+                            unsigned char* wdst = dst + static_cast<size_t>(1 + p) * kChunkBytes;
+                            bulk_load(smem_u32(wdst), a.weights + w0, first * 32, bar);
+                            if (first < rows_j) bulk_load(smem_u32(wdst + first * 32), a.weights, (rows_j - first) * 32, bar);
+                        }
                     };
                     uint32_t issued = 0;
                     if (lane == 0)
@@ -174,18 +192,17 @@ namespace gzk
                             ok = false;
                             break;
                         }
-                        const unsigned char* stage = ring + static_cast<size_t>(slot) * kChunkBytes;
+                        const unsigned char* stage = ring + static_cast<size_t>(slot) * slot_bytes(P);
                         const uint64_t row0 = static_cast<uint64_t>(ch) * kChunkRows;
                         const uint32_t rows_here = static_cast<uint32_t>(rows - row0 < kChunkRows ? rows - row0 : kChunkRows);
 #pragma unroll 1
                         for (uint32_t r = lane; r < rows_here; r += 32)
                         {
                             const Fr f = load_fr_shared(stage + r * 32);
-                            const uint64_t c = c_begin + row0 + r;
 #pragma unroll
                             for (int p = 0; p < P; ++p)
                             {
-                                const Fr w = load_fr(a.weights + ((c - a.rot[p]) & a.mask));
+                                const Fr w = load_fr_shared(stage + static_cast<size_t>(1 + p) * kChunkBytes + r * 32);
                                 acc[p].template mac<8>(w.l, f.l);
                             }
                         }
@@ -270,13 +287,13 @@ namespace gzk
                 cudaError_t err;
                 if (p == 2)
                 {
-                    cudaFuncSetAttribute(eval_partial_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
-                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<2>, kThreads, kSmemBytes);
+                    cudaFuncSetAttribute(eval_partial_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes(2)));
+                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<2>, kThreads, smem_bytes(2));
                 }
                 else
                 {
-                    cudaFuncSetAttribute(eval_partial_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBytes));
-                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<1>, kThreads, kSmemBytes);
+                    cudaFuncSetAttribute(eval_partial_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes(1)));
+                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<1>, kThreads, smem_bytes(1));
                 }
                 cached[p] = (err == cudaSuccess && nb > 0) ? nb : 1;
             }
@@ -287,9 +304,9 @@ namespace gzk
         {
             blocks_per_sm(p);  // makes sure the shared-memory opt-in has happened
             if (p == 2)
-                eval_partial_kernel<2><<<blocks, kThreads, kSmemBytes, stream>>>(args);
+                eval_partial_kernel<2><<<blocks, kThreads, smem_bytes(2), stream>>>(args);
             else
-                eval_partial_kernel<1><<<blocks, kThreads, kSmemBytes, stream>>>(args);
+                eval_partial_kernel<1><<<blocks, kThreads, smem_bytes(1), stream>>>(args);
         }
 
         // One warp per (rotation, column) pair: the lanes sum the per-tile partials, the
@@ -459,7 +476,11 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     uint64_t want_tiles = (6 * warps_total + k_count - 1) / k_count;
     uint64_t max_tiles = (len + 255) / 256;
     if (max_tiles == 0) max_tiles = 1;
-    if (want_tiles > 256) want_tiles = 256;
+    // the partial buffer (tiles x P x K x 68 B) is kept below 64 MiB, and below 4096 tiles
+    uint64_t tile_cap = (64ull << 20) / (static_cast<uint64_t>(p_count >= 2 ? 2 : 1) * k_count * kAccLimbs * sizeof(uint32_t));
+    if (tile_cap < 64) tile_cap = 64;
+    if (tile_cap > 4096) tile_cap = 4096;
+    if (want_tiles > tile_cap) want_tiles = tile_cap;
     if (want_tiles > max_tiles) want_tiles = max_tiles;
     if (want_tiles == 0) want_tiles = 1;
     uint64_t tile_rows = (len + want_tiles - 1) / want_tiles;

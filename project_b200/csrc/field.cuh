@@ -717,6 +717,104 @@ namespace gzk
         }
     };
 
+    // Same accumulator with explicit wide multiplies: every limb product is one
+    // mul.wide.u32 (independent of the accumulator, so the four products of a row
+    // chain issue back to back) followed by a 64-bit add-with-carry into 64-bit
+    // accumulator lanes.  The code generated does not depend on the assembler pairing
+    // lo/hi multiply-adds.
+    struct WideAcc64
+    {
+        uint64_t E[8];   // even-aligned lanes: E[k] holds limbs 2k, 2k+1
+        uint64_t O[7];   // odd-aligned lanes, offset by one limb: O[k] holds limbs 2k+1, 2k+2
+        uint32_t cE[5];  // carries out of E lanes 3..7 (limb positions 8,10,12,14,16)
+        uint32_t cO[4];  // carries out of O lanes 3..6 (O limb positions 8,10,12,14)
+
+        GZK_HD void clear()
+        {
+#pragma unroll
+            for (int i = 0; i < 8; ++i) E[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 7; ++i) O[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 5; ++i) cE[i] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) cO[i] = 0;
+        }
+
+        template <int I>
+        GZK_HD void row(const uint32_t* a, uint32_t bi)
+        {
+            // products of this row: even j and odd j
+            const uint64_t e0 = mp::mul_wide(a[(I % 2 == 0) ? 0 : 1], bi);
+            const uint64_t e1 = mp::mul_wide(a[(I % 2 == 0) ? 2 : 3], bi);
+            const uint64_t e2 = mp::mul_wide(a[(I % 2 == 0) ? 4 : 5], bi);
+            const uint64_t e3 = mp::mul_wide(a[(I % 2 == 0) ? 6 : 7], bi);
+            const uint64_t o0 = mp::mul_wide(a[(I % 2 == 0) ? 1 : 0], bi);
+            const uint64_t o1 = mp::mul_wide(a[(I % 2 == 0) ? 3 : 2], bi);
+            const uint64_t o2 = mp::mul_wide(a[(I % 2 == 0) ? 5 : 4], bi);
+            const uint64_t o3 = mp::mul_wide(a[(I % 2 == 0) ? 7 : 6], bi);
+            // E lanes: row I even starts at limb I (lane I/2); row I odd at limb I+1 (lane (I+1)/2)
+            constexpr int le = (I % 2 == 0) ? I / 2 : (I + 1) / 2;
+            E[le] = mp::add_cc_u64(E[le], e0);
+            E[le + 1] = mp::addc_cc_u64(E[le + 1], e1);
+            E[le + 2] = mp::addc_cc_u64(E[le + 2], e2);
+            E[le + 3] = mp::addc_cc_u64(E[le + 3], e3);
+            cE[le] = mp::addc(cE[le], 0);  // carry into limb 2*(le+4): counter index le (positions 8..16)
+            // O lanes: row I even starts at O limb I (lane I/2); row I odd at O limb I-1 (lane (I-1)/2)
+            constexpr int lo = (I % 2 == 0) ? I / 2 : (I - 1) / 2;
+            O[lo] = mp::add_cc_u64(O[lo], o0);
+            O[lo + 1] = mp::addc_cc_u64(O[lo + 1], o1);
+            O[lo + 2] = mp::addc_cc_u64(O[lo + 2], o2);
+            O[lo + 3] = mp::addc_cc_u64(O[lo + 3], o3);
+            cO[lo] = mp::addc(cO[lo], 0);
+        }
+
+        template <int ROWS>
+        GZK_HD void mac(const uint32_t* a, const uint32_t* b)
+        {
+            row<0>(a, b[0]);
+            if (ROWS > 1) row<1>(a, b[1]);
+            if (ROWS > 2) row<2>(a, b[2]);
+            if (ROWS > 3) row<3>(a, b[3]);
+            if (ROWS > 4) row<4>(a, b[4]);
+            if (ROWS > 5) row<5>(a, b[5]);
+            if (ROWS > 6) row<6>(a, b[6]);
+            if (ROWS > 7) row<7>(a, b[7]);
+        }
+
+        GZK_HD void fold(uint32_t* out) const
+        {
+            uint32_t t[17];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+            {
+                out[2 * k] = static_cast<uint32_t>(E[k]);
+                out[2 * k + 1] = static_cast<uint32_t>(E[k] >> 32);
+            }
+            out[16] = 0;
+#pragma unroll
+            for (int k = 0; k < 17; ++k) t[k] = 0;
+#pragma unroll
+            for (int i = 0; i < 5; ++i) t[8 + 2 * i] = cE[i];
+            acc_add<17, 17>(out, t);
+            t[0] = 0;
+#pragma unroll
+            for (int k = 0; k < 7; ++k)
+            {
+                t[2 * k + 1] = static_cast<uint32_t>(O[k]);
+                t[2 * k + 2] = static_cast<uint32_t>(O[k] >> 32);
+            }
+            t[15] = 0;
+            t[16] = 0;
+            acc_add<17, 17>(out, t);
+#pragma unroll
+            for (int k = 0; k < 17; ++k) t[k] = 0;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) t[9 + 2 * i] = cO[i];
+            acc_add<17, 17>(out, t);
+        }
+    };
+
     using Fr = Fe<FrCfg>;
     using Fp = Fe<FpCfg>;
 

@@ -100,6 +100,24 @@ namespace gzk
             asm volatile("madc.hi.u32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
             return r;
         }
+        GZK_D uint64_t mul_wide(uint32_t a, uint32_t b)
+        {
+            uint64_t r;
+            asm volatile("mul.wide.u32 %0, %1, %2;" : "=l"(r) : "r"(a), "r"(b));
+            return r;
+        }
+        GZK_D uint64_t add_cc_u64(uint64_t a, uint64_t b)
+        {
+            uint64_t r;
+            asm volatile("add.cc.u64 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+            return r;
+        }
+        GZK_D uint64_t addc_cc_u64(uint64_t a, uint64_t b)
+        {
+            uint64_t r;
+            asm volatile("addc.cc.u64 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+            return r;
+        }
 #else
         // Host emulation of the carry flag (single-threaded use per thread).
         inline uint32_t& cc_flag()
@@ -133,6 +151,15 @@ namespace gzk
         inline uint32_t madc_lo_cc(uint32_t a, uint32_t b, uint32_t c) { return emu_add(mul_lo(a, b), c, cc_flag(), true); }
         inline uint32_t madc_hi_cc(uint32_t a, uint32_t b, uint32_t c) { return emu_add(mul_hi(a, b), c, cc_flag(), true); }
         inline uint32_t madc_hi(uint32_t a, uint32_t b, uint32_t c) { return emu_add(mul_hi(a, b), c, cc_flag(), false); }
+        inline uint64_t mul_wide(uint32_t a, uint32_t b) { return static_cast<uint64_t>(a) * b; }
+        inline uint64_t emu_add64(uint64_t a, uint64_t b, uint32_t cin)
+        {
+            const unsigned __int128 t = static_cast<unsigned __int128>(a) + b + cin;
+            cc_flag() = static_cast<uint32_t>(t >> 64);
+            return static_cast<uint64_t>(t);
+        }
+        inline uint64_t add_cc_u64(uint64_t a, uint64_t b) { return emu_add64(a, b, 0); }
+        inline uint64_t addc_cc_u64(uint64_t a, uint64_t b) { return emu_add64(a, b, cc_flag()); }
 #endif
     }
 }

@@ -75,6 +75,8 @@ int check_wide(std::mt19937_64& rng)
         uint32_t acc[17] = {};
         gzk::WideAcc wacc;
         wacc.clear();
+        gzk::WideAcc64 wacc64;
+        wacc64.clear();
         oracle::Fr want = oracle::Fr::zero();
         const int terms = 1 + static_cast<int>(rng() % (trial % 50 == 0 ? 5000 : 40));
         for (int t = 0; t < terms; ++t)
@@ -123,6 +125,12 @@ int check_wide(std::mt19937_64& rng)
             }
             acc_add<17, 16>(acc, prod);
             wacc.mac<8>(wl, fl);
+            wacc64.mac<8>(wl, fl);
+        }
+        {
+            uint32_t folded[17];
+            wacc64.fold(folded);
+            if (std::memcmp(folded, acc, sizeof(acc)) != 0) { ++failures; std::printf("WideAcc64 mismatch\n"); }
         }
         {
             uint32_t folded[17];
