@@ -285,9 +285,9 @@ def main():
         local_len = max(0, min(length - d["begin"], d["rows"]))
         return gather_sum(be.eval_batch_range(d["cols"], local_len, d["begin"], d["lg"], weights, d["w_first"], rotations))
 
-    def step_evaluations():
+    def step_domain(d):
         outs = []
-        for d in domains:
+        if True:
             tau_evals = evaluate(d, d["w_tau"], d["valid"], (0,))[0]
             outs.append(be.g1_mul_same_base(G, tau_evals))                      # commit: [p_k(tau)] G
             outs.append(evaluate(d, d["w_tau"], d["n"], (0, 1)))                # quotient: {tau, omega*tau}
@@ -298,6 +298,9 @@ def main():
                 be.bary_weights_range(d["lg"], z, d["w_first"], d["w_count"], out=d["w_z"])
             outs.append(evaluate(d, d["w_z"], d["n"], (0, 1)))                  # openings: {z, omega*z}
         return outs
+
+    def step_evaluations():
+        return [step_domain(d) for d in domains]
 
     # builder outputs are allocated once: the columns of a proof live in the backend's pool
     b_out = {
@@ -386,8 +389,8 @@ def main():
     products_per_s = local_terms * args.steps / (eval_ms * 1e-3) if eval_ms > 0 else 0.0
     roofline = {
         "bound": "hbm", "kernel": "eval_partial_kernel (packed evaluation, all launches of the step)", "achieved": achieved,
-        "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None, "traffic": 570.4e6 + 4.7e6,
-        "traffic_note": "ncu dram read+write of one 2-rotation launch on the 2^18 x 64 profiling case (algorithmic 545.3e6); see profiles/",
+        "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None, "traffic": 560.1e6 + 5.4e6,
+        "traffic_note": "ncu dram read+write of one 2-rotation launch on the 2^18 x 64 profiling case (algorithmic 545.3e6, traffic grows in proportion to columns x rows); see profiles/eval_partial_kernel_edge2p18x64.md",
         "peak_source": peak_src, "launches": eval_launches, "avg_launch_ms": eval_ms / max(1, eval_launches),
         "bytes_per_step": local_bytes,
         "integer_pipe": {"achieved_products_per_s": products_per_s, "measured_peak_products_per_s": mac_peak,
@@ -407,16 +410,27 @@ def main():
         h2d = sum(d["k"] * d["rows"] * 32 for d in domains) * world
         d2h = sum(d["k"] * (5 * 32 + 96) for d in domains)
 
+        def queue_uploads(d):
+            host = pinned[d["name"]].numpy()
+            for buf in d["cols"]:
+                done = 0
+                while done < d["rows"]:
+                    part = min(d["rows"] - done, host.shape[0])
+                    buf.upload_async(host[:part], offset=done)
+                    done += part
+
         def step_e2e():
-            for d in domains:
-                host = pinned[d["name"]].numpy()
-                for buf in d["cols"]:
-                    done = 0
-                    while done < d["rows"]:
-                        part = min(d["rows"] - done, host.shape[0])
-                        buf.upload(host[:part], offset=done)
-                        done += part
-            return step_resident()
+            # uploads run on the copy stream: the columns of the next domain travel while the
+            # current one is evaluated, and the first upload overlaps with the builders
+            outs = []
+            queue_uploads(domains[0])
+            step_builders()
+            for i, d in enumerate(domains):
+                be.copy_fence()
+                if i + 1 < len(domains):
+                    queue_uploads(domains[i + 1])
+                outs.append(step_domain(d))
+            return outs
 
         e2e_steps = max(1, min(args.steps, 3))
         e2e_ms, _, _ = timed(step_e2e, e2e_steps, 1)

@@ -81,6 +81,11 @@ int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, double* produ
 int gzk_buf_alloc(gzk_ctx* ctx, int kind, size_t count, gzk_buf** out);
 int gzk_buf_free(gzk_ctx* ctx, gzk_buf* buf);
 int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
+/* gzk_buf_upload_async queues the copy on a second stream so that it overlaps with kernels
+ * in flight (host memory should be pinned and must stay valid); gzk_copy_fence makes all
+ * work issued afterwards wait for the uploads queued so far. */
+int gzk_buf_upload_async(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
+int gzk_copy_fence(gzk_ctx* ctx);
 /* downloads always deliver the wire format: FR_MONT buffers are converted to
  * canonical on the device first */
 int gzk_buf_download(gzk_ctx* ctx, const gzk_buf* buf, size_t offset, void* host, size_t count);

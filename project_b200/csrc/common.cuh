@@ -67,6 +67,8 @@ struct gzk_ctx
     int device = 0;
     int sm_count = 0;
     cudaStream_t stream = nullptr;
+    cudaStream_t copy_stream = nullptr;  // host-to-device uploads that overlap with kernels
+    cudaEvent_t copy_event = nullptr;
     std::string last_error;
     std::unordered_map<unsigned, gzk::DomainTables> domains;
     gzk::Scratch scratch[4];

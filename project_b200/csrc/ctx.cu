@@ -256,6 +256,8 @@ extern "C"
         ctx->device = device;
         ctx->sm_count = prop.multiProcessorCount;
         if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ctx->copy_event, cudaEventDisableTiming) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 64) != cudaSuccess ||
             cudaMemset(ctx->d_status, 0, 64) != cudaSuccess)
         {
@@ -285,6 +287,9 @@ extern "C"
         timing_collect(ctx);
         g1_release_tables(ctx);
         for (auto e : ctx->event_pool) cudaEventDestroy(e);
+        cudaStreamSynchronize(ctx->copy_stream);
+        cudaEventDestroy(ctx->copy_event);
+        cudaStreamDestroy(ctx->copy_stream);
         cudaStreamDestroy(ctx->stream);
         delete ctx;
     }
@@ -395,6 +400,30 @@ extern "C"
             if (rc != GZK_OK) return rc;
         }
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    // Upload without waiting: the copy is queued on the context's copy stream and overlaps
+    // with kernels already running on the compute stream.  `host` must stay valid (and
+    // should be pinned) until gzk_copy_fence + a synchronisation; kernels issued after
+    // gzk_copy_fence see the data.  FR / I64 / U32 / F64 buffers only (no conversion).
+    int gzk_buf_upload_async(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count)
+    {
+        if (ctx == nullptr || buf == nullptr || (host == nullptr && count != 0)) return GZK_E_INVALID;
+        if (offset + count > buf->count) return fail(ctx, GZK_E_INVALID, "upload exceeds the buffer");
+        if (buf->kind == GZK_KIND_FR_MONT || buf->kind == GZK_KIND_G1) return fail(ctx, GZK_E_INVALID, "upload_async: buffer kind needs conversion, use gzk_buf_upload");
+        if (count == 0) return GZK_OK;
+        char* dst = static_cast<char*>(buf->dptr) + offset * buf->elem_bytes;
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(dst, host, count * buf->elem_bytes, cudaMemcpyHostToDevice, ctx->copy_stream));
+        return GZK_OK;
+    }
+
+    // Orders everything issued on the compute stream from now on after all uploads queued so far.
+    int gzk_copy_fence(gzk_ctx* ctx)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        GZK_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_event, ctx->copy_stream));
+        GZK_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->copy_event, 0));
         return GZK_OK;
     }
 

@@ -71,6 +71,13 @@ class Buffer:
         self.backend._check(self.backend.lib.gzk_buf_upload(self.backend.ctx, self.handle, _sz(offset), _ptr(a), _sz(count)))
         return self
 
+    def upload_async(self, host, offset=0):
+        """Queue the copy on the copy stream; `host` must stay alive until Backend.copy_fence + synchronize."""
+        dtype, width = _KIND_DTYPE[self.kind]
+        a = np.ascontiguousarray(host, dtype=dtype)
+        self.backend._check(self.backend.lib.gzk_buf_upload_async(self.backend.ctx, self.handle, _sz(offset), _ptr(a), _sz(a.size // width)))
+        return self
+
     def download(self, offset=0, count=None):
         dtype, width = _KIND_DTYPE[self.kind]
         count = self.count - offset if count is None else count
@@ -107,6 +114,9 @@ class Backend:
     def _check(self, rc):
         if rc != 0:
             raise GzkError(rc, self.lib.gzk_last_error(self.ctx).decode())
+
+    def copy_fence(self):
+        self._check(self.lib.gzk_copy_fence(self.ctx))
 
     def synchronize(self):
         self._check(self.lib.gzk_ctx_synchronize(self.ctx))

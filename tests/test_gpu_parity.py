@@ -153,3 +153,31 @@ def test_commit_equals_barycentric_evaluation(be):
     # rotation identity instead: sum_c w[c] * col[(c+1) mod n] for col = w-independent constant
     got = fr_ints(be.eval_batch([c1], n, log2n, w, (0, 1, 12345))[:, 0])
     assert got == [1, 1, 1]
+
+
+def test_golden_fixtures_through_the_c_abi(be):
+    """The committed fixtures (tests/golden/hotpath_small.json, produced from Python
+    integers) reproduced by the CUDA library."""
+    import json
+    import os
+
+    from project_b200 import KIND_FR
+
+    with open(os.path.join(os.path.dirname(__file__), "golden", "hotpath_small.json")) as f:
+        g = json.load(f)
+    hx = lambda s: np.frombuffer(bytes.fromhex(s), dtype=np.uint8)
+    assert bytes(be.root_of_unity(g["omega"]["n"])).hex() == g["omega"]["value"]
+    bw = g["bary"]
+    log2n = bw["n"].bit_length() - 1
+    assert be.bary_weights(log2n, hx(bw["x"])).download().tobytes().hex() == bw["weights"]
+    ev = g["eval"]
+    cols = hx(ev["columns"]).reshape(ev["k"], ev["n"], 32)
+    w = be.upload(hx(ev["weights"]).reshape(-1, 32), 1)  # KIND_FR_MONT: converted on upload
+    out = be.eval_batch([be.upload(cols[i], KIND_FR) for i in range(ev["k"])], ev["n"], ev["n"].bit_length() - 1, w, ev["rotations"])
+    assert out.tobytes().hex() == ev["out"]
+    g1 = g["g1_same_base"]
+    assert be.g1_mul_same_base(hx(g1["base"]), hx(g1["scalars"]).reshape(-1, 32)).tobytes().hex() == g1["points"]
+    lg = g["logup"]
+    bufs = [be.upload(hx(lg[k]).reshape(-1, 32), KIND_FR) for k in ("table", "query", "mult", "q_table", "q_query")]
+    n = bufs[0].count
+    assert be.logup_accumulator(*bufs, n, hx(lg["beta"]), lg["active"]).download().tobytes().hex() == lg["out"]
