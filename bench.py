@@ -111,12 +111,15 @@ def cpu_count():
         return os.cpu_count() or 1
 
 
-def cpu_sample(workload, threads, budget_columns=96):
-    """Times the CPU restatement of the reference loops on a bounded sample of the
-    step (the edge-shaped domain, `budget_columns` columns) and scales by the
-    multiply-add count to a whole step.  Returns (ms_per_proof, description)."""
+def cpu_sample(workload, threads, budget_columns=96, heads=16):
+    """Times the CPU restatement of the reference loops on a bounded sample of the step and
+    scales to a whole step: packed evaluation + weights by multiply-add count (all host
+    threads, as the reference fans out), one column of every builder kind single-threaded
+    (as the reference builds them) times the per-proof counts, and a sample of the same-base
+    G1 batch.  Returns (ms_per_proof, description)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ora
+    import pyref
 
     name, lg, k, valid = max((w for w in workload if w[1] <= 18), key=lambda w: w[1] * 1000 + w[2])
     ks = min(k, budget_columns)
@@ -127,10 +130,28 @@ def cpu_sample(workload, threads, budget_columns=96):
     sample_terms = ks * n * 1 + ks * n * 2
     per_term = (t_commit + t_eval) / sample_terms
     bary_per_row = t_bary / n
-    total = per_term * workload_terms(workload) + bary_per_row * sum(1 << w[1] for w in workload)
-    desc = (f"{name}-shaped sample: {ks} columns x 2^{lg} rows, 1- and 2-point packed evaluation "
-            f"({sample_terms / 1e6:.0f}M mul-adds, {t_commit + t_eval:.2f}s) + barycentric weights 2^{lg} ({t_bary:.2f}s), "
-            f"scaled by multiply-add count to one step")
+    eval_s = per_term * workload_terms(workload) + bary_per_row * sum(1 << w[1] for w in workload)
+    # builders: per head 4 LogUp, 2+2 routes, 2 segmented states, 6 bindings (fold + inner product)
+    node = min((w for w in workload), key=lambda w: abs(w[1] - 15))
+    e_valid = min(valid, n - 1)
+    tb = ora.bench_builders(n, e_valid, seed=4)
+    nn = 1 << node[1]
+    tn = ora.bench_builders(nn, min(node[3], nn - 1), seed=5)
+    builders_s = heads * (4 * tb[0] + 2 * tn[1] + 2 * tb[2] + 2 * tb[3] + 6 * (tn[5] * 8 + tb[4] * 16 / max(e_valid, 1)))
+    # same-base G1 batch: 16 scalar multiplications timed, scaled to the number of committed columns
+    G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8)
+    rng = np.random.default_rng(6)
+    sc = rng.integers(0, 256, size=(16, 32), dtype=np.uint8)
+    sc[:, 31] &= 0x3F
+    t0 = time.perf_counter()
+    ora.g1_mul_same_base(G, sc)
+    g1_s = (time.perf_counter() - t0) / 16 * sum(w[2] for w in workload) / max(1, threads)
+    total = eval_s + builders_s + g1_s
+    desc = (f"{name}-shaped sample: {ks} columns x 2^{lg} rows, 1- and 2-point packed evaluation ({sample_terms / 1e6:.0f}M mul-adds, "
+            f"{t_commit + t_eval:.2f}s on {threads} threads) + barycentric weights 2^{lg} ({t_bary:.2f}s), scaled by multiply-add count "
+            f"[{eval_s * 1e3:.0f} ms]; one column of each builder kind single-threaded x per-proof counts for {heads} heads "
+            f"[{builders_s * 1e3:.0f} ms]; 16 double-and-add G1 multiplications scaled to the committed columns over {threads} threads "
+            f"[{g1_s * 1e3:.0f} ms]")
     return total * 1e3, desc
 
 
@@ -142,7 +163,7 @@ def run_reference(args, workload, wl_name):
     times = []
     desc = ""
     for i in range(args.warmup + args.steps):
-        ms, desc = cpu_sample(workload, threads, budget_columns=32)
+        ms, desc = cpu_sample(workload, threads, budget_columns=32, heads=2 if (args.small or args.profile_case) else 16)
         if i >= args.warmup:
             times.append(ms)
     value = float(np.mean(times))
@@ -444,9 +465,8 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = cpu_count()
-        v, desc = cpu_sample(workload, threads)
-        cpu_baseline = {"value": v, "unit": "ms", "cores": threads, "kind": "port",
-                        "sample": desc + "; covers the evaluation part of the step (the builders and the G1 batch are not in the CPU figure)"}
+        v, desc = cpu_sample(workload, threads, heads=heads)
+        cpu_baseline = {"value": v, "unit": "ms", "cores": threads, "kind": "port", "sample": desc}
 
     if rank == 0:
         line = {

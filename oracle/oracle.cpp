@@ -917,6 +917,115 @@ extern "C"
         });
     }
 
+    // Times one column of each builder kind on native-form values, single-threaded as the
+    // reference builds them (lookup.cpp:100-157, trace.cpp:298-361, psq.cpp:7-39,
+    // zkmap.cpp:7-32): seconds[0] LogUp accumulator (n rows, `valid` active), [1] route node,
+    // [2] route edge, [3] segmented prefix state, [4] inner-product accumulator over `valid`
+    // rows, [5] weighted column sum of a valid x 8 matrix (trace.cpp:203-271).
+    int ora_bench_builders(std::size_t n, std::size_t valid, std::uint64_t seed, double* seconds, Bytes* checksum_out)
+    {
+        return guarded([&] {
+            if (valid + 1 > n) throw std::runtime_error("valid must be below n");
+            std::uint64_t state = seed * 0x9E3779B97F4A7C15ULL + 1;
+            auto next = [&]() {
+                state ^= state << 13;
+                state ^= state >> 7;
+                state ^= state << 17;
+                return state;
+            };
+            auto rnd = [&]() {
+                Fr f;
+                for (auto& limb : f.v.w) limb = next();
+                f.v.w[3] >>= 2;
+                return f;
+            };
+            std::vector<Fr> table(n), query(n), mult(n), values(n), q_new(n), q_sel(n, Fr::zero());
+            for (std::size_t i = 0; i < n; ++i)
+            {
+                table[i] = rnd();
+                query[i] = rnd();
+                mult[i] = Fr::from_u64(next() & 63);
+                values[i] = rnd();
+                q_new[i] = (next() & 7) == 0 ? Fr::one() : Fr::zero();
+                if (i < valid) q_sel[i] = Fr::one();
+            }
+            const Fr beta = rnd();
+            Fr sink = Fr::zero();
+            auto clock = [] { return std::chrono::steady_clock::now(); };
+            auto since = [](std::chrono::steady_clock::time_point t0) {
+                return std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count();
+            };
+            {
+                const auto t0 = clock();
+                std::vector<Fr> den(2 * valid), acc(n, Fr::zero());
+                for (std::size_t i = 0; i < valid; ++i)
+                {
+                    den[2 * i] = table[i] + beta;
+                    den[2 * i + 1] = query[i] + beta;
+                }
+                const auto inv = batch_invert(den);
+                Fr run = Fr::zero();
+                for (std::size_t i = 0; i < valid; ++i)
+                {
+                    run += q_sel[i] * mult[i] * inv[2 * i];
+                    run -= q_sel[i] * inv[2 * i + 1];
+                    acc[i + 1] = run;
+                }
+                for (std::size_t i = valid + 1; i < n; ++i) acc[i] = acc[valid];
+                seconds[0] = since(t0);
+                sink += acc[n - 1];
+            }
+            for (int kind = 1; kind <= 2; ++kind)
+            {
+                const auto t0 = clock();
+                std::vector<Fr> den(valid), acc(n, Fr::zero());
+                for (std::size_t i = 0; i < valid; ++i) den[i] = (kind == 1 ? table[i] : query[i]) + beta;
+                const auto inv = batch_invert(den);
+                Fr run = Fr::zero();
+                for (std::size_t i = 0; i < valid; ++i)
+                {
+                    run += kind == 1 ? mult[i] * inv[i] : inv[i];
+                    acc[i + 1] = run;
+                }
+                for (std::size_t i = valid + 1; i < n; ++i) acc[i] = acc[valid];
+                seconds[kind] = since(t0);
+                sink += acc[n - 1];
+            }
+            {
+                const auto t0 = clock();
+                std::vector<Fr> out(n, Fr::zero());
+                out[0] = values[0];
+                for (std::size_t i = 1; i < n; ++i) out[i] = q_new[i] * values[i] + (Fr::one() - q_new[i]) * (out[i - 1] + values[i]);
+                seconds[3] = since(t0);
+                sink += out[n - 1];
+            }
+            {
+                const auto t0 = clock();
+                std::vector<Fr> acc(n, Fr::zero());
+                Fr mu = Fr::zero();
+                for (std::size_t i = 0; i < valid; ++i)
+                {
+                    mu += table[i] * query[i];
+                    acc[i + 1] = mu;
+                }
+                for (std::size_t i = valid + 1; i < n; ++i) acc[i] = acc[valid];
+                seconds[4] = since(t0);
+                sink += acc[n - 1];
+            }
+            {
+                const std::size_t rows = valid / 8 > 0 ? valid / 8 : 1;
+                const auto t0 = clock();
+                Fr total[8];
+                for (auto& t : total) t = Fr::zero();
+                for (std::size_t row = 0; row < rows; ++row)
+                    for (std::size_t c = 0; c < 8; ++c) total[c] += values[row * 8 + c] * table[row];
+                seconds[5] = since(t0);
+                for (auto& t : total) sink += t;
+            }
+            if (checksum_out != nullptr) sink.to_le_bytes(checksum_out);
+        });
+    }
+
     // ---- transcript (transcript.cpp:10-55) -------------------------------------------
     std::uint64_t ora_fnv1a(const char* data, std::size_t size) { return fnv1a(std::string(data, size)); }
 }

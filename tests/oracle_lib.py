@@ -343,3 +343,11 @@ def fh_public_eval(features, rows, feature_count, abs_ids, weights):
     out = np.zeros((5, 32), dtype=np.uint8)
     _check(lib().ora_fh_public_eval(_p(features), _sz(rows), _sz(feature_count), _p(ids), _p(weights), _p(out)))
     return out
+
+
+def bench_builders(n, valid, seed=1):
+    """Seconds per column for [logup, route_node, route_edge, group_prefix, zkmap, fold_rows(valid/8 x 8)]."""
+    sec = (ctypes.c_double * 6)()
+    chk = np.zeros(32, dtype=np.uint8)
+    _check(lib().ora_bench_builders(_sz(n), _sz(valid), ctypes.c_uint64(seed), sec, _p(chk)))
+    return list(sec)
