@@ -269,6 +269,17 @@ int gzk_eval_batch_range(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, siz
 int gzk_fr_sum(const uint8_t* values, size_t groups, size_t count, uint8_t* out);
 int gzk_g1_sum(const uint8_t* points, size_t count, uint8_t out[96]);
 
+/* ---- generated public columns; carry of a sharded running sum ---------------------------------
+ * gzk_generated_column: columns the reference materialises on the host although they are
+ * pure functions of the row index: what = 0 selector (1 for i < valid, build_selector,
+ * src/protocol/lookup.cpp:75-81), 1 index i, 2 i / width, 3 i % width (the row-id /
+ * column-id columns of the feature domain, src/protocol/prover.cpp:2794-2867); zero
+ * beyond `valid`; out is a U32 or I64 column.
+ * gzk_fr_add_scalar: buf[offset .. offset+count) += scalar: applies the carry (sum of the
+ * totals of the lower ranks) to a running-sum column whose rows are split over GPUs. */
+int gzk_generated_column(gzk_ctx* ctx, int what, size_t valid, size_t width, size_t domain_size, gzk_buf* out);
+int gzk_fr_add_scalar(gzk_ctx* ctx, gzk_buf* buf, size_t offset, size_t count, const uint8_t scalar[32]);
+
 /* ---- packed evaluation without any allocation ------------------------------------
  * No counterpart in the reference.  Same result as gzk_eval_batch, for callers that
  * cannot call cudaMalloc while they run: a prover host that has already given all

@@ -115,6 +115,29 @@ namespace gzk
             }
         }
 
+        // generated public columns: 0 selector (1 below `valid`), 1 index i, 2 i / width, 3 i % width
+        __global__ void generated_kernel(int what, uint64_t valid, uint64_t width, uint64_t n, uint32_t* out32, long long* out64)
+        {
+            for (uint64_t i = grid_index(); i < n; i += grid_stride())
+            {
+                uint64_t v = 0;
+                if (i < valid)
+                {
+                    if (what == 0) v = 1;
+                    else if (what == 1) v = i;
+                    else if (what == 2) v = i / width;
+                    else v = i % width;
+                }
+                if (out32 != nullptr) out32[i] = static_cast<uint32_t>(v);
+                else out64[i] = static_cast<long long>(v);
+            }
+        }
+
+        __global__ void add_scalar_kernel(Fr* data, uint64_t count, Fr scalar)
+        {
+            for (uint64_t i = grid_index(); i < count; i += grid_stride()) store_fr(data + i, add(load_fr_plain(data + i), scalar));
+        }
+
         unsigned blocks_for(gzk_ctx* ctx, uint64_t n)
         {
             uint64_t b = (n + kThreads - 1) / kThreads;
@@ -286,5 +309,45 @@ extern "C"
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return finish_with_status(ctx, "first_zero_marker: group bounds out of range");
+    }
+
+    int gzk_generated_column(gzk_ctx* ctx, int what, size_t valid, size_t width, size_t domain_size, gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (domain_size == 0) return GZK_OK;
+        if (what < 0 || what > 3 || (what >= 2 && width == 0)) return fail(ctx, GZK_E_INVALID, "generated_column: unknown generator or zero width");
+        if (out == nullptr || (out->kind != GZK_KIND_U32 && out->kind != GZK_KIND_I64) || out->count < domain_size)
+            return fail(ctx, GZK_E_INVALID, "generated_column: output must be a U32 or I64 buffer of the domain size");
+        if (valid > domain_size) valid = domain_size;
+        if (out->kind == GZK_KIND_U32 && what == 1 && valid > (1ull << 32)) return fail(ctx, GZK_E_INVALID, "generated_column: indices exceed 32 bits");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "generated_column");
+            generated_kernel<<<blocks_for(ctx, domain_size), kThreads, 0, ctx->stream>>>(
+                what, valid, width == 0 ? 1 : width, domain_size, out->kind == GZK_KIND_U32 ? static_cast<uint32_t*>(out->dptr) : nullptr,
+                out->kind == GZK_KIND_I64 ? static_cast<long long*>(out->dptr) : nullptr);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    int gzk_fr_add_scalar(gzk_ctx* ctx, gzk_buf* buf, size_t offset, size_t count, const uint8_t scalar[32])
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (count == 0) return GZK_OK;
+        if (buf == nullptr || scalar == nullptr || buf->kind != GZK_KIND_FR_MONT || offset + count > buf->count)
+            return fail(ctx, GZK_E_INVALID, "fr_add_scalar: needs a Montgomery buffer and a range inside it");
+        Fr v;
+        int rc = scalar_mont(ctx, scalar, &v);
+        if (rc != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "add_scalar");
+            add_scalar_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(static_cast<Fr*>(buf->dptr) + offset, count, v);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
     }
 }

@@ -79,10 +79,14 @@ namespace gzk
             if (threadIdx.x == 0) store_fr(a.cta_products + blockIdx.x, total);
         }
 
-        template <int OP>
+        // LOCAL_INV: the CTA inverts the product of its own 1024 denominators (one serial
+        // inversion per CTA, all CTAs in parallel) instead of reading the result of the
+        // product / single-CTA-inversion passes; used when the whole grid is resident at once.
+        template <int OP, bool LOCAL_INV>
         __global__ void __launch_bounds__(kThreads) scan_main_kernel(ScanArgs a)
         {
             __shared__ Fr slots[3 * kWarps];
+            __shared__ Fr local_inverse;
             __shared__ SegVal seg_slots[kWarps];
             __shared__ uint32_t first_flag;
             const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk + static_cast<uint64_t>(threadIdx.x) * kElems;
@@ -106,7 +110,23 @@ namespace gzk
                     pre[j] = mine;
                     mine = mul(mine, d[j]);
                 }
-                const Fr outer = block_invert_products<kThreads>(mine, load_fr(a.cta_products + blockIdx.x), slots);
+                Fr cta_inverse;
+                if (LOCAL_INV)
+                {
+                    const Fr total = block_product<kThreads>(mine, slots);
+                    if (threadIdx.x == 0)
+                    {
+                        if (total.is_zero()) atomicExch(a.status, GZK_E_DOMAIN);
+                        local_inverse = inv(total);
+                    }
+                    __syncthreads();
+                    cta_inverse = local_inverse;
+                }
+                else
+                {
+                    cta_inverse = load_fr(a.cta_products + blockIdx.x);
+                }
+                const Fr outer = block_invert_products<kThreads>(mine, cta_inverse, slots);
                 Fr suffix = Fr::one();
 #pragma unroll
                 for (int j = kElems - 1; j >= 0; --j)
@@ -281,7 +301,8 @@ namespace gzk
             args.agg_first = args.agg_flag + ctas;
             args.status = ctx->d_status;
             GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
-            if (inverting)
+            const bool local_inverse = inverting && ctas <= static_cast<uint32_t>(ctx->sm_count) * 4;
+            if (inverting && !local_inverse)
             {
                 {
                     LaunchScope scope(ctx, "scan_products");
@@ -292,7 +313,10 @@ namespace gzk
             }
             {
                 LaunchScope scope(ctx, "scan_main");
-                scan_main_kernel<OP><<<ctas, kThreads, 0, ctx->stream>>>(args);
+                if (local_inverse)
+                    scan_main_kernel<OP, true><<<ctas, kThreads, 0, ctx->stream>>>(args);
+                else
+                    scan_main_kernel<OP, false><<<ctas, kThreads, 0, ctx->stream>>>(args);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
             {

@@ -314,6 +314,14 @@ class Backend:
                                                   weights.handle, ctypes.c_uint64(weights_first), _ptr(rot), _sz(rot.size), _ptr(out)))
         return out
 
+    def generated_column(self, what, valid, width, domain_size, kind=KIND_U32):
+        out = self.alloc(kind, domain_size)
+        self._check(self.lib.gzk_generated_column(self.ctx, int(what), _sz(valid), _sz(width), _sz(domain_size), out.handle))
+        return out
+
+    def fr_add_scalar(self, buf, offset, count, scalar):
+        self._check(self.lib.gzk_fr_add_scalar(self.ctx, buf.handle, _sz(offset), _sz(count), _ptr(_fr(scalar))))
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)

@@ -67,3 +67,43 @@ def test_sharded_msm_equals_whole(be):
         begin, end = shard_rows(n, world, rank)
         parts.append(be.msm(be.upload(sb[begin:end], KIND_FR), be.upload(host_pts[begin:end], KIND_G1), end - begin))
     assert np.array_equal(g1_sum(np.stack(parts)), whole)
+
+
+def test_sharded_running_sum_with_carry(be):
+    """A route accumulator whose rows are split over 3 'ranks': each computes its local
+    running sum, the totals are exchanged, and the carry is added on the device."""
+    from project_b200 import KIND_FR, fr_sum, shard_rows
+
+    rng = np.random.default_rng(21)
+    n, valid, world = 8192, 7000, 3
+    query = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    query[:, 31] &= 0x3F
+    beta = fr_array([424242424242])
+    whole = be.route_edge_accumulator(be.upload(query, KIND_FR), valid, n, beta).download()
+    pieces, totals = [], []
+    for rank in range(world):
+        begin, end = shard_rows(valid, world, rank, align=32)
+        rows = end - begin
+        local = be.route_edge_accumulator(be.upload(query[begin:end], KIND_FR), rows, rows + 1, beta)  # out[0..rows]
+        pieces.append((begin, rows, local))
+        totals.append(local.download(offset=rows, count=1)[0])
+    got = np.zeros((n, 32), dtype=np.uint8)
+    for rank, (begin, rows, local) in enumerate(pieces):
+        if rank > 0:
+            carry = fr_sum(np.stack(totals[:rank])) if rank > 1 else totals[0]
+            be.fr_add_scalar(local, 0, rows + 1, carry)
+        got[begin + 1:begin + rows + 1] = local.download(offset=1, count=rows)
+    got[valid + 1:] = got[valid]
+    assert np.array_equal(got, whole)
+
+
+def test_generated_columns(be):
+    from project_b200 import KIND_I64, KIND_U32
+
+    n, valid, width = 5000, 4321, 37
+    sel = be.generated_column(0, valid, 0, n).download()
+    assert sel[:valid].all() and not sel[valid:].any()
+    idx = np.arange(n)
+    assert np.array_equal(be.generated_column(1, valid, 0, n, KIND_I64).download(), np.where(idx < valid, idx, 0))
+    assert np.array_equal(be.generated_column(2, valid, width, n).download(), np.where(idx < valid, idx // width, 0))
+    assert np.array_equal(be.generated_column(3, valid, width, n).download(), np.where(idx < valid, idx % width, 0))
