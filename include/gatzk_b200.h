@@ -249,6 +249,9 @@ int gzk_srs_lagrange(gzk_ctx* ctx, unsigned log2n, const uint8_t base[96], const
 int gzk_ntt(gzk_ctx* ctx, const gzk_buf* in, gzk_buf* out, unsigned log2n, size_t batch, int inverse, const uint8_t* coset_shift);
 int gzk_coset_lde(gzk_ctx* ctx, const gzk_buf* in, unsigned log2n, unsigned log2_blowup, const uint8_t shift[32], gzk_buf* out);
 int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out);
+/* the three values (at 0, 1, 2) of the round polynomial of the same table: what a rank
+ * contributes to the per-round 3-element all-gather before the Fiat-Shamir squeeze */
+int gzk_sumcheck_round_sums(gzk_ctx* ctx, const gzk_buf* table, size_t n, uint8_t out[3 * 32]);
 
 /* ---- sharding across GPUs (one context per GPU, one process per GPU) ---------------------------
  * The reference is a single process; these entry points let the rows of a domain be

@@ -146,6 +146,55 @@ namespace gzk
             }
         }
 
+        // Round sums of a multilinear table for one sumcheck round on a product-free claim:
+        // s0 = sum t[2i], s1 = sum t[2i+1]; block partials, finished by one small block.
+        __global__ void __launch_bounds__(kThreads) round_sums_kernel(ColRef table, uint64_t half, Fr* partial)
+        {
+            __shared__ Fr ws0[kThreads / 32], ws1[kThreads / 32];
+            Fr s0 = Fr::zero(), s1 = Fr::zero();
+            const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+            for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < half; i += stride)
+            {
+                s0 = add(s0, col_load_mont(table, 2 * i));
+                s1 = add(s1, col_load_mont(table, 2 * i + 1));
+            }
+            const int lane = threadIdx.x & 31;
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                const Fr o0 = shfl_fr_idx(s0, (lane + offset) & 31);
+                const Fr o1 = shfl_fr_idx(s1, (lane + offset) & 31);
+                if (lane < offset)
+                {
+                    s0 = add(s0, o0);
+                    s1 = add(s1, o1);
+                }
+            }
+            if (lane == 0)
+            {
+                ws0[threadIdx.x >> 5] = s0;
+                ws1[threadIdx.x >> 5] = s1;
+            }
+            __syncthreads();
+            if (threadIdx.x == 0)
+            {
+                for (int w = 1; w < kThreads / 32; ++w)
+                {
+                    s0 = add(s0, ws0[w]);
+                    s1 = add(s1, ws1[w]);
+                }
+                store_fr(partial + 2 * blockIdx.x, s0);
+                store_fr(partial + 2 * blockIdx.x + 1, s1);
+            }
+        }
+        __global__ void round_sums_finish_kernel(const Fr* partial, uint32_t blocks, Fr* out_canonical)
+        {
+            if (threadIdx.x >= 2) return;
+            Fr s = Fr::zero();
+            for (uint32_t b = 0; b < blocks; ++b) s = add(s, load_fr_plain(partial + 2 * b + threadIdx.x));
+            store_fr(out_canonical + threadIdx.x, from_mont(s));
+        }
+
         int scalar_mont(gzk_ctx* ctx, const uint8_t* bytes, Fr* out)
         {
             bool canonical = false;
@@ -270,6 +319,45 @@ extern "C"
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return GZK_OK;
+    }
+
+    // out[0] = sum_i t[2i], out[1] = sum_i t[2i+1], out[2] = 2*out[1] - out[0]: the values at
+    // 0, 1, 2 of the round polynomial sum_i (t[2i] + X (t[2i+1] - t[2i])) of a sumcheck round.
+    // With the table split over GPUs each rank computes its three values and the ranks
+    // all-gather and add them (gzk_fr_sum) before the Fiat-Shamir squeeze.
+    int gzk_sumcheck_round_sums(gzk_ctx* ctx, const gzk_buf* table, size_t n, uint8_t out[3 * 32])
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (out == nullptr) return fail(ctx, GZK_E_INVALID, "sumcheck_round_sums: null output");
+        std::memset(out, 0, 96);
+        if (n < 2) return GZK_OK;
+        if (table == nullptr || table->kind == GZK_KIND_F64 || table->kind == GZK_KIND_G1 || table->count < n)
+            return fail(ctx, GZK_E_INVALID, "sumcheck_round_sums: table buffer too small or of the wrong kind");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        const uint64_t half = n / 2;
+        uint64_t blocks = (half + kThreads - 1) / kThreads;
+        const uint64_t cap = static_cast<uint64_t>(ctx->sm_count) * 8;
+        if (blocks > cap) blocks = cap;
+        void* scratch = nullptr;
+        int rc = ensure_scratch(ctx, 2, (2 * blocks + 2) * sizeof(Fr), &scratch);
+        if (rc != GZK_OK) return rc;
+        Fr* partial = static_cast<Fr*>(scratch);
+        ColRef t;
+        t.ptr = table->dptr;
+        t.kind = table->kind;
+        {
+            LaunchScope scope(ctx, "round_sums", 2);
+            round_sums_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(t, half, partial);
+            round_sums_finish_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(blocks), partial + 2 * blocks);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out, partial + 2 * blocks, 64, cudaMemcpyDeviceToHost, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        // value at 2 = s0 + 2 (s1 - s0) = 2 s1 - s0, on the host
+        uint8_t twice[32];
+        if (gzk_fr_op(0, out + 32, out + 32, twice) != GZK_OK || gzk_fr_op(1, twice, out, out + 64) != GZK_OK)
+            return fail(ctx, GZK_E_INVALID, "sumcheck_round_sums: internal arithmetic error");
         return GZK_OK;
     }
 

@@ -322,6 +322,11 @@ class Backend:
     def fr_add_scalar(self, buf, offset, count, scalar):
         self._check(self.lib.gzk_fr_add_scalar(self.ctx, buf.handle, _sz(offset), _sz(count), _ptr(_fr(scalar))))
 
+    def sumcheck_round_sums(self, table, n):
+        out = np.zeros((3, 32), dtype=np.uint8)
+        self._check(self.lib.gzk_sumcheck_round_sums(self.ctx, table.handle, _sz(n), _ptr(out)))
+        return out
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)

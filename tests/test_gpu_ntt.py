@@ -89,3 +89,38 @@ def test_fold(be, n):
     t = rand_fr(rng, n)
     r = rand_fr(rng, 1)[0]
     assert np.array_equal(be.fold(be.upload(t, KIND_FR), n, r).download(), ora.fold(t, r))
+
+
+def test_sumcheck_rounds_fold_to_the_multilinear_evaluation(be):
+    """Run all rounds of a sumcheck-style fold on a 2^12 table, sharded over 2 'ranks' per
+    round: the round sums must satisfy s(0)+s(1) = previous claim, s(2) = 2 s(1) - s(0), and
+    the final value must equal the table folded by the oracle."""
+    from project_b200 import KIND_FR, fr_sum
+    import pyref
+    from pyref import R, fr_ints
+
+    rng = np.random.default_rng(55)
+    n = 1 << 12
+    t = rand_fr(rng, n)
+    claim = sum(fr_ints(t)) % R
+    cur_host = t
+    cur = be.upload(t, KIND_FR)
+    while n > 1:
+        half = n // 2
+        if n >= 4:
+            # two ranks, each owning half of the table (an even number of entries)
+            parts = [be.sumcheck_round_sums(be.upload(cur_host[:half], KIND_FR), half), be.sumcheck_round_sums(be.upload(cur_host[half:], KIND_FR), half)]
+            sums = fr_sum(np.stack(parts))
+        else:
+            sums = be.sumcheck_round_sums(cur, n)
+        s0, s1, s2 = fr_ints(sums)
+        assert (s0 + s1) % R == claim
+        assert s2 == (2 * s1 - s0) % R
+        r = rand_fr(rng, 1)[0]
+        r_int = fr_ints(r)[0]
+        claim = (s0 + r_int * (s1 - s0)) % R
+        nxt = be.fold(cur, n, r)
+        cur_host = nxt.download()
+        assert np.array_equal(cur_host, ora.fold(ora.fr_binop(0, cur.download() if cur.kind == 0 else cur.download(), np.zeros((n, 32), np.uint8)), r))
+        cur, n = nxt, half
+    assert fr_ints(cur_host)[0] == claim
