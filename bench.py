@@ -18,6 +18,7 @@ algebra) is O(#columns) and is not part of the step.
           host memory: every step uploads them and reads the results back.
 """
 import argparse
+import concurrent.futures
 import json
 import os
 import subprocess
@@ -188,6 +189,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--small", action="store_true", help="reduced shapes (smoke runs)")
     ap.add_argument("--profile-case", action="store_true", help="one 2^18 x 64-column domain (profiler captures)")
+    ap.add_argument("--builder-threads", type=int, default=4,
+                    help="host threads (one context each) that issue the column builders of independent heads")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the MSM / NTT / fold kernel sweep lines")
@@ -283,6 +286,10 @@ def main():
     }
     w_node = be.bary_weights(node["lg"], tau)
     be.synchronize()
+    # builder calls queue their kernels and return; calls that hand values to the host
+    # (evaluations, the inner-product total) still synchronise, and a device-side error of
+    # a queued call is raised by the synchronize that ends the builder phase
+    be.set_deferred(True)
     step_counter = [0]
 
     def challenge():
@@ -323,36 +330,63 @@ def main():
     def step_evaluations():
         return [step_domain(d) for d in domains]
 
-    # builder outputs are allocated once: the columns of a proof live in the backend's pool
-    b_out = {
-        "edge_mont": [be.alloc(KIND_FR_MONT, ne) for _ in range(3)],
-        "node_mont": be.alloc(KIND_FR_MONT, nn),
-        "edge_i64": be.alloc(KIND_I64, ne),
-        "hist": be.alloc(KIND_U32, 4096),
-        "folded": be.alloc(KIND_FR, 8),
-        "acc16": be.alloc(KIND_FR_MONT, 16),
-    }
+    # The reference builds the columns of a proof from concurrent host tasks (std::async per
+    # head / per column); the same shape here: a few host threads, each with its own context
+    # (its own stream and scratch), so the short builder kernels of independent heads overlap
+    # on the GPU.  Builder outputs are allocated once per worker: the columns of a proof live
+    # in the backend's pool.
+    n_workers = max(1, args.builder_threads)
+    workers = [be] + [Backend(local_rank) for _ in range(n_workers - 1)]
+    for w in workers[1:]:
+        w.set_deferred(True)
+    w_nodes = [w_node] + [w.bary_weights(node["lg"], tau) for w in workers[1:]]
+    for w in workers:
+        w.synchronize()
+
+    def make_outputs(w):
+        return {
+            "edge_mont": [w.alloc(KIND_FR_MONT, ne) for _ in range(3)],
+            "node_mont": w.alloc(KIND_FR_MONT, nn),
+            "edge_i64": w.alloc(KIND_I64, ne),
+            "hist": w.alloc(KIND_U32, 4096),
+            "folded": w.alloc(KIND_FR, 8),
+            "acc16": w.alloc(KIND_FR_MONT, 16),
+        }
+
+    w_outs = [make_outputs(w) for w in workers]
+    pool = concurrent.futures.ThreadPoolExecutor(max_workers=n_workers) if n_workers > 1 else None
+
+    def build_heads(t, beta, my_heads):
+        # column builders of the heads dealt to worker t (heads are independent)
+        w, b_out, wn = workers[t], w_outs[t], w_nodes[t]
+        e_out = b_out["edge_mont"]
+        for head in my_heads:
+            for i in range(4):  # feature / LeakyReLU / range / exp lookups
+                w.logup_accumulator(b_in["table"], b_in["query"], b_in["mult"], b_in["q_table"], b_in["q_query"], ne, beta, e_valid, out=e_out[i % 3])
+            for i in range(2):  # src / dst routes
+                w.route_node_accumulator(b_in["node_tab"], b_in["node_mult"], n_valid, nn, beta, out=b_out["node_mont"])
+                w.route_edge_accumulator(b_in["query"], e_valid, ne, beta, out=e_out[i])
+            for i in range(2):  # PSQ state, max counter
+                w.group_prefix_state(b_in["values"], b_in["q_new"], ne, out=e_out[i])
+            for _ in range(5):  # E_src, E_dst, M, Sum, inv broadcast to edges
+                w.broadcast_node_values(b_in["node_vals"], nn, b_in["src"], e_valid, ne, out=b_out["edge_i64"])
+            for _ in range(3):
+                w.histogram(b_in["hits"], e_valid, 4096, out=b_out["hist"])
+            for _ in range(6):  # bindings: fold rows by weights, then the running inner product
+                w.fold_rows(b_in["matrix"], n_valid, 8, wn, n_valid, out=b_out["folded"])
+                w.zkmap_accumulator(b_out["folded"], b_out["folded"], 8, 16, out=b_out["acc16"])
+            w.weighted_sum(b_in["table"], beta, b_in["query"], e_valid, ne, out=e_out[2])
+        w.synchronize()
 
     def step_builders():
-        # column builders of the heads this rank owns (heads are independent)
         beta = challenge()
-        e_out = b_out["edge_mont"]
-        for head in range(rank, heads, world):
-            for i in range(4):  # feature / LeakyReLU / range / exp lookups
-                be.logup_accumulator(b_in["table"], b_in["query"], b_in["mult"], b_in["q_table"], b_in["q_query"], ne, beta, e_valid, out=e_out[i % 3])
-            for i in range(2):  # src / dst routes
-                be.route_node_accumulator(b_in["node_tab"], b_in["node_mult"], n_valid, nn, beta, out=b_out["node_mont"])
-                be.route_edge_accumulator(b_in["query"], e_valid, ne, beta, out=e_out[i])
-            for i in range(2):  # PSQ state, max counter
-                be.group_prefix_state(b_in["values"], b_in["q_new"], ne, out=e_out[i])
-            for _ in range(5):  # E_src, E_dst, M, Sum, inv broadcast to edges
-                be.broadcast_node_values(b_in["node_vals"], nn, b_in["src"], e_valid, ne, out=b_out["edge_i64"])
-            for _ in range(3):
-                be.histogram(b_in["hits"], e_valid, 4096, out=b_out["hist"])
-            for _ in range(6):  # bindings: fold rows by weights, then the running inner product
-                be.fold_rows(b_in["matrix"], n_valid, 8, w_node, n_valid, out=b_out["folded"])
-                be.zkmap_accumulator(b_out["folded"], b_out["folded"], 8, 16, out=b_out["acc16"])
-            be.weighted_sum(b_in["table"], beta, b_in["query"], e_valid, ne, out=e_out[2])
+        mine = list(range(rank, heads, world))
+        if pool is None:
+            build_heads(0, beta, mine)
+            return
+        futures = [pool.submit(build_heads, t, beta, mine[t::n_workers]) for t in range(n_workers)]
+        for f in futures:
+            f.result()
 
     def step_resident():
         step_builders()
@@ -368,8 +402,9 @@ def main():
         for _ in range(warmup):
             fn()
         barrier()
-        be.timing_reset()
-        be.timing_enable(True)
+        for w in workers:
+            w.timing_reset()
+            w.timing_enable(True)
         start = torch.cuda.Event(enable_timing=True)
         stop = torch.cuda.Event(enable_timing=True)
         with ClockSampler(local_rank) as clocks:
@@ -379,8 +414,12 @@ def main():
             stop.record(stream)
             barrier()
         ms = start.elapsed_time(stop)
-        report = be.timing_report()
-        be.timing_enable(False)
+        report = {}
+        for w in workers:
+            for kname, (count, total_ms) in w.timing_report().items():
+                prev = report.get(kname, (0, 0.0))
+                report[kname] = (prev[0] + count, prev[1] + total_ms)
+            w.timing_enable(False)
         if world > 1:
             t = torch.tensor([ms], device="cuda", dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -475,7 +514,8 @@ def main():
             "dtype": "u32x8 Montgomery Fr / u32x12 Fp (BLS12-381)", "data": "synthetic",
             "config": {"workload": wl_name, "l2": "inputs larger than L2 (5.3 GB edge columns, 2.7 GB FH columns per pass)",
                        "sharding": f"rows of every domain split across {world} rank(s); per-call all-gather of the partial sums (K*P*32 B) over NCCL; "
-                                   f"builder heads dealt round-robin"},
+                                   f"builder heads dealt round-robin",
+                       "builder_threads": n_workers},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
             "kernel_ms": {k: round(v[1], 3) for k, v in report.items()}, "clocks": clocks, "sweep": sweep,
         }

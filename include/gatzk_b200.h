@@ -55,6 +55,13 @@ int gzk_ctx_create(int device, gzk_ctx** out);
 void gzk_ctx_destroy(gzk_ctx* ctx);
 const char* gzk_last_error(const gzk_ctx* ctx);
 int gzk_ctx_synchronize(gzk_ctx* ctx);
+/* Deferred mode: calls whose results stay on the device (the column builders, row folds,
+ * gathers, histograms ...) return as soon as their kernels are queued, so the host runs
+ * ahead of the GPU as a chain of kernels; an error raised on the device (zero denominator,
+ * index out of range) is then reported by the next gzk_ctx_synchronize instead of by the
+ * call itself.  Calls that return values to the host always synchronise.  Off by default
+ * (every call reports its own errors, like the reference's exceptions). */
+int gzk_ctx_set_deferred(gzk_ctx* ctx, int on);
 /* the CUDA stream (cudaStream_t) all work of this context is issued on */
 void* gzk_ctx_stream(gzk_ctx* ctx);
 

@@ -50,7 +50,7 @@ namespace gzk
                 if (e < a.n)
                 {
                     const Fr d = sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, (a.first + e) & a.mask));
-                    if (d.is_zero()) atomicExch(status, 1);
+                    if (d.is_zero()) atomicExch(status, GZK_E_DOMAIN);
                     prod = mul(prod, d);
                 }
             }
@@ -247,7 +247,7 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     if ((rc = ensure_scratch(ctx, 2, static_cast<size_t>(blocks) * 2 * sizeof(Fr), &scratch)) != GZK_OK) return rc;
     Fr* products = static_cast<Fr*>(scratch);
     Fr* tmp = products + blocks;
-    GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+    if ((rc = begin_call(ctx)) != GZK_OK) return rc;
     {
         LaunchScope scope(ctx, "bary_products");
         bary_products_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, ctx->d_status);
@@ -259,11 +259,9 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
         bary_finish_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, static_cast<Fr*>(out->dptr));
     }
     GZK_CUDA_TRY(ctx, cudaGetLastError());
-    int status = 0;
-    GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-    GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (status != 0) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
-    return GZK_OK;
+    rc = finish_call(ctx, "bary_weights: invalid input");
+    if (rc == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
+    return rc;
 }
 
 extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], gzk_buf* out)

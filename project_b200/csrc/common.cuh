@@ -76,6 +76,7 @@ struct gzk_ctx
     size_t pinned_bytes = 0;
     int* d_status = nullptr;  // device-side status word (zero-denominator flags etc.)
     bool timing = false;
+    bool deferred = false;  // builder calls return without synchronising; errors surface at gzk_ctx_synchronize
     std::vector<gzk::FamilyStat> families;
     std::vector<gzk::TimedLaunch> pending;
     std::vector<cudaEvent_t> event_pool;
@@ -106,6 +107,13 @@ namespace gzk
         cudaEvent_t start_ = nullptr;
     };
     void timing_collect(gzk_ctx* ctx);
+
+    // End of a call whose results stay on the device: in the default mode synchronise the
+    // stream and turn a raised status word into an error; in deferred mode return at once
+    // (the status word stays raised until gzk_ctx_synchronize reports it).
+    int finish_call(gzk_ctx* ctx, const char* invalid_message);
+    // Clears the status word at the start of a call (not in deferred mode, where it is sticky).
+    int begin_call(gzk_ctx* ctx);
 
     // Host-side scalar helpers (same arithmetic, emulated carry flag).
     Fr host_fr_from_bytes(const uint8_t* bytes, bool* canonical_ok);

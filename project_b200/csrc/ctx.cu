@@ -119,6 +119,30 @@ namespace gzk
         ctx->pending.clear();
     }
 
+    static int status_to_error(gzk_ctx* ctx, int status, const char* invalid_message)
+    {
+        if (status == 0) return GZK_OK;
+        cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+        if (status == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "batch_invert encountered zero");
+        if (status == GZK_E_TIMEOUT) return fail(ctx, GZK_E_TIMEOUT, "a bounded wait on a bulk copy gave up");
+        return fail(ctx, GZK_E_INVALID, invalid_message);
+    }
+
+    int begin_call(gzk_ctx* ctx)
+    {
+        if (!ctx->deferred) GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        return GZK_OK;
+    }
+
+    int finish_call(gzk_ctx* ctx, const char* invalid_message)
+    {
+        if (ctx->deferred) return GZK_OK;
+        int status = 0;
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return status_to_error(ctx, status, invalid_message);
+    }
+
     Fr host_fr_from_bytes(const uint8_t* bytes, bool* canonical_ok)
     {
         Fr v;
@@ -299,8 +323,18 @@ extern "C"
     int gzk_ctx_synchronize(gzk_ctx* ctx)
     {
         if (ctx == nullptr) return GZK_E_INVALID;
+        int status = 0;
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return status_to_error(ctx, status, "a deferred call reported invalid input (index out of range, non-boolean selector or bad group bounds)");
+    }
+
+    int gzk_ctx_set_deferred(gzk_ctx* ctx, int on)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        const int rc = gzk_ctx_synchronize(ctx);
+        ctx->deferred = on != 0;
+        return rc;
     }
 
     void* gzk_ctx_stream(gzk_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }

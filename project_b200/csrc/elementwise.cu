@@ -160,14 +160,7 @@ namespace gzk
             *out = to_mont(v);
             return GZK_OK;
         }
-        int finish_with_status(gzk_ctx* ctx, const char* message)
-        {
-            int status = 0;
-            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
-            GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-            if (status != 0) return fail(ctx, GZK_E_INVALID, message);
-            return GZK_OK;
-        }
+        int finish_with_status(gzk_ctx* ctx, const char* message) { return finish_call(ctx, message); }
         bool index_kind_ok(const gzk_buf* b) { return b != nullptr && (b->kind == GZK_KIND_U32 || b->kind == GZK_KIND_I64); }
     }
 }
@@ -194,8 +187,7 @@ extern "C"
                                                                                              static_cast<Fr*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_feature_lookup_rows(gzk_ctx* ctx, const gzk_buf* row_ids, const gzk_buf* feature_indices, const gzk_buf* features,
@@ -221,8 +213,7 @@ extern "C"
                                                                                        static_cast<Fr*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_broadcast_node_values(gzk_ctx* ctx, const gzk_buf* node_values, size_t node_count, const gzk_buf* index, size_t edge_count,
@@ -235,7 +226,10 @@ extern "C"
             return fail(ctx, GZK_E_INVALID, "broadcast: input size mismatch");
         if (out->kind != node_values->kind || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "broadcast: output must have the kind of the node values");
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        {
+            const int rc_begin = begin_call(ctx);
+            if (rc_begin != GZK_OK) return rc_begin;
+        }
         {
             LaunchScope scope(ctx, "gather");
             const unsigned blocks = blocks_for(ctx, domain_size);
@@ -260,7 +254,10 @@ extern "C"
         if (out == nullptr || out->kind != GZK_KIND_U32 || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "histogram: output must be a U32 buffer of the domain size");
         if (count != 0 && (!index_kind_ok(indices) || indices->count < count)) return fail(ctx, GZK_E_INVALID, "histogram: indices must be a U32 or I64 buffer");
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        {
+            const int rc_begin = begin_call(ctx);
+            if (rc_begin != GZK_OK) return rc_begin;
+        }
         GZK_CUDA_TRY(ctx, cudaMemsetAsync(out->dptr, 0, domain_size * sizeof(uint32_t), ctx->stream));
         if (count != 0)
         {
@@ -285,8 +282,7 @@ extern "C"
                                                                                    static_cast<long long*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
@@ -295,7 +291,10 @@ extern "C"
         if (ctx == nullptr) return GZK_E_INVALID;
         if (out == nullptr || out->kind != GZK_KIND_U32 || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "first_zero_marker: output must be a U32 buffer of the domain size");
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-        GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        {
+            const int rc_begin = begin_call(ctx);
+            if (rc_begin != GZK_OK) return rc_begin;
+        }
         GZK_CUDA_TRY(ctx, cudaMemsetAsync(out->dptr, 0, domain_size * sizeof(uint32_t), ctx->stream));
         if (groups != 0)
         {
@@ -328,8 +327,7 @@ extern "C"
                 out->kind == GZK_KIND_I64 ? static_cast<long long*>(out->dptr) : nullptr);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_fr_add_scalar(gzk_ctx* ctx, gzk_buf* buf, size_t offset, size_t count, const uint8_t scalar[32])
@@ -347,7 +345,6 @@ extern "C"
             add_scalar_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(static_cast<Fr*>(buf->dptr) + offset, count, v);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 }

@@ -549,7 +549,7 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     int* h_status = reinterpret_cast<int*>(h_out + p_count * k_count * 32);
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    if (*h_status != 0)
+    if (*h_status == GZK_E_TIMEOUT)  // other codes belong to deferred calls and are reported by gzk_ctx_synchronize
     {
         GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
         return fail(ctx, GZK_E_TIMEOUT, "eval_batch: a bounded wait on a bulk copy gave up");

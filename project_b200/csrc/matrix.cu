@@ -270,8 +270,7 @@ extern "C"
         if ((rc = launch_eval_finish(ctx, static_cast<const uint32_t*>(scratch), form, static_cast<uint32_t>(tiles),
                                      static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr), false)) != GZK_OK)
             return rc;
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_linear_form_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* column_powers, gzk_buf* out)
@@ -295,8 +294,7 @@ extern "C"
                                                                                          static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_powers(gzk_ctx* ctx, const uint8_t challenge[32], size_t count, gzk_buf* out)
@@ -314,7 +312,6 @@ extern "C"
             powers_kernel<<<static_cast<unsigned>((count + 127) / 128), 128, 0, ctx->stream>>>(c, count, static_cast<Fr*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 }

@@ -41,7 +41,8 @@ namespace gzk
             ColRef c0, c1, c2, c3, c4;
             uint64_t count;  // rows that carry a term
             uint64_t n;      // length of the output column
-            Fr beta;
+            Fr beta;        // Montgomery form
+            Fr beta_canon;  // the same challenge as a canonical residue
             Fr* out;
             Fr* cta_products;     // pass 1 -> 2 -> 3
             Fr* agg_value;        // per-CTA aggregate / exclusive offset
@@ -51,11 +52,58 @@ namespace gzk
             int* status;
         };
 
+        // ---- residues with a tracked power of R --------------------------------------------
+        // A canonical residue x (kinds FR, U32, I64) is the Montgomery representation of
+        // x/R, so it can enter a Montgomery product as it is stored, provided the missing
+        // factors of R are counted: "deficit" below is that count (1 for canonical kinds, 0
+        // for FR_MONT), a product adds the deficits of its factors, an inversion negates
+        // them, and fix_scale() multiplies the remaining factors back in.  In the lookup
+        // terms the deficits of numerator and denominator cancel, which saves the
+        // conversion multiplication of every load.  All deficits depend only on the buffer
+        // kinds, so every branch on them is uniform over the grid.
+        __device__ __forceinline__ int deficit(const ColRef& c) { return c.kind == GZK_KIND_FR_MONT ? 0 : 1; }
+
+        __device__ __forceinline__ Fr col_load_stored(const ColRef& c, uint64_t i)
+        {
+            if (c.kind == GZK_KIND_FR_MONT || c.kind == GZK_KIND_FR) return load_fr(static_cast<const Fr*>(c.ptr) + i);
+            Fr f = Fr::zero();
+            if (c.kind == GZK_KIND_U32)
+            {
+                f.l[0] = __ldg(static_cast<const uint32_t*>(c.ptr) + i);
+                return f;
+            }
+            const long long v = __ldg(static_cast<const long long*>(c.ptr) + i);
+            const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
+            f.l[0] = static_cast<uint32_t>(mag);
+            f.l[1] = static_cast<uint32_t>(mag >> 32);
+            return v < 0 ? neg(f) : f;
+        }
+
+        // v carries `d` missing factors of R (d > 0) or -d surplus ones (d < 0).
+        __device__ __forceinline__ Fr fix_scale(Fr v, int d)
+        {
+            for (; d > 0; --d) v = to_mont(v);
+            for (; d < 0; ++d) v = from_mont(v);
+            return v;
+        }
+
+        // the challenge in the form of column c
+        __device__ __forceinline__ Fr beta_for(const ScanArgs& a, const ColRef& c) { return deficit(c) ? a.beta_canon : a.beta; }
+
+        // 0 and 1 in the stored form of column c
+        __device__ __forceinline__ bool stored_is_one(const ColRef& c, const Fr& v)
+        {
+            if (deficit(c) == 0) return v == Fr::one();
+            return v.l[0] == 1u && (v.l[1] | v.l[2] | v.l[3] | v.l[4] | v.l[5] | v.l[6] | v.l[7]) == 0u;
+        }
+
+        // Denominator of row e in stored form; its deficit is deficit(c0) (+ deficit(c1) for LogUp).
         template <int OP>
         __device__ __forceinline__ Fr denominator(const ScanArgs& a, uint64_t e)
         {
-            if (OP == kLogup) return mul(add(col_load_mont(a.c0, e), a.beta), add(col_load_mont(a.c1, e), a.beta));
-            return add(col_load_mont(a.c0, e), a.beta);
+            const Fr tb = add(col_load_stored(a.c0, e), beta_for(a, a.c0));
+            if (OP == kLogup) return mul(tb, add(col_load_stored(a.c1, e), beta_for(a, a.c1)));
+            return tb;
         }
 
         template <int OP>
@@ -140,20 +188,28 @@ namespace gzk
                     }
                     else if (OP == kLogup)
                     {
-                        // inverse = 1/((T+b)(Q+b)): 1/(T+b) = inverse*(Q+b), 1/(Q+b) = inverse*(T+b)
-                        const Fr tb = add(col_load_mont(a.c0, e), a.beta);
-                        const Fr qb = add(col_load_mont(a.c1, e), a.beta);
-                        const Fr table_term = mul(mul(col_load_mont(a.c3, e), col_load_mont(a.c2, e)), mul(inverse, qb));
-                        const Fr query_term = mul(col_load_mont(a.c4, e), mul(inverse, tb));
+                        // inverse = 1/((T+b)(Q+b)) with the surplus R^(d0+d1): inverse*(Q+b) = R^d0/(T+b),
+                        // inverse*(T+b) = R^d1/(Q+b)
+                        const int d0 = deficit(a.c0), d1 = deficit(a.c1);
+                        const Fr tb = add(col_load_stored(a.c0, e), beta_for(a, a.c0));
+                        const Fr qb = add(col_load_stored(a.c1, e), beta_for(a, a.c1));
+                        Fr weight = col_load_stored(a.c2, e);       // multiplicity, deficit d2
+                        const Fr sel = col_load_stored(a.c3, e);    // table selector
+                        if (sel.is_zero())
+                            weight = Fr::zero();
+                        else if (!stored_is_one(a.c3, sel))
+                            weight = fix_scale(mul(weight, sel), deficit(a.c3));  // back to deficit d2
+                        const Fr table_term = fix_scale(mul(weight, mul(inverse, qb)), deficit(a.c2) - d0);
+                        const Fr query_term = fix_scale(mul(col_load_stored(a.c4, e), mul(inverse, tb)), deficit(a.c4) - d1);
                         term[j] = sub(table_term, query_term);
                     }
                     else if (OP == kRouteNode)
                     {
-                        term[j] = mul(col_load_mont(a.c1, e), inverse);
+                        term[j] = fix_scale(mul(col_load_stored(a.c1, e), inverse), deficit(a.c1) - deficit(a.c0));
                     }
                     else
                     {
-                        term[j] = inverse;
+                        term[j] = fix_scale(inverse, -deficit(a.c0));
                     }
                 }
             }
@@ -169,15 +225,15 @@ namespace gzk
                     }
                     else if (OP == kProduct)
                     {
-                        term[j] = mul(col_load_mont(a.c0, e), col_load_mont(a.c1, e));
+                        term[j] = fix_scale(mul(col_load_stored(a.c0, e), col_load_stored(a.c1, e)), deficit(a.c0) + deficit(a.c1));
                     }
                     else
                     {
-                        term[j] = col_load_mont(a.c0, e);
-                        const Fr q = col_load_mont(a.c1, e);
+                        term[j] = fix_scale(col_load_stored(a.c0, e), deficit(a.c0));
+                        const Fr q = col_load_stored(a.c1, e);
                         if (!q.is_zero())
                         {
-                            if (q != Fr::one()) atomicExch(a.status, GZK_E_INVALID);
+                            if (!stored_is_one(a.c1, q)) atomicExch(a.status, GZK_E_INVALID);
                             flag[j] = 1;
                             atomicMin(&first_flag, static_cast<uint32_t>(threadIdx.x * kElems + j));
                         }
@@ -300,7 +356,7 @@ namespace gzk
             args.agg_flag = reinterpret_cast<uint32_t*>(base + 3 * static_cast<size_t>(ctas) + 2);
             args.agg_first = args.agg_flag + ctas;
             args.status = ctx->d_status;
-            GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+            if ((rc = begin_call(ctx)) != GZK_OK) return rc;
             const bool local_inverse = inverting && ctas <= static_cast<uint32_t>(ctx->sm_count) * 4;
             if (inverting && !local_inverse)
             {
@@ -312,7 +368,8 @@ namespace gzk
                 if ((rc = launch_batch_invert_single_cta(ctx, args.cta_products, tmp, ctas)) != GZK_OK) return rc;
             }
             {
-                LaunchScope scope(ctx, "scan_main");
+                LaunchScope scope(ctx, OP == kLogup ? "scan_main_logup" : OP == kRouteNode ? "scan_main_route_node" : OP == kRouteEdge ? "scan_main_route_edge"
+                                       : OP == kProduct ? "scan_main_product" : "scan_main_segmented");
                 if (local_inverse)
                     scan_main_kernel<OP, true><<<ctas, kThreads, 0, ctx->stream>>>(args);
                 else
@@ -330,6 +387,7 @@ namespace gzk
                 scan_fixup_kernel<OP><<<static_cast<unsigned>((args.n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(args);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
+            if (total_out_host == nullptr) return finish_call(ctx, "q_new must hold only 0 and 1");
             struct
             {
                 Fr total;
@@ -352,12 +410,13 @@ namespace gzk
             r.kind = b->kind;
             return r;
         }
-        int load_scalar(gzk_ctx* ctx, const uint8_t* bytes, Fr* out_mont)
+        int load_scalar(gzk_ctx* ctx, const uint8_t* bytes, Fr* out_mont, Fr* out_canonical)
         {
             bool canonical = false;
             const Fr v = host_fr_from_bytes(bytes, &canonical);
             if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
             *out_mont = to_mont(v);
+            *out_canonical = v;
             return GZK_OK;
         }
         bool out_ok(const gzk_buf* out, uint64_t n) { return out != nullptr && out->kind == GZK_KIND_FR_MONT && out->count >= n; }
@@ -388,7 +447,7 @@ extern "C"
         args.count = active_count;
         args.n = n;
         args.out = static_cast<Fr*>(out->dptr);
-        int rc = load_scalar(ctx, beta, &args.beta);
+        int rc = load_scalar(ctx, beta, &args.beta, &args.beta_canon);
         if (rc != GZK_OK) return rc;
         return run_scan<kLogup>(ctx, args, true, nullptr);
     }
@@ -408,7 +467,7 @@ extern "C"
         args.count = valid_length;
         args.n = domain_size;
         args.out = static_cast<Fr*>(out->dptr);
-        int rc = load_scalar(ctx, beta, &args.beta);
+        int rc = load_scalar(ctx, beta, &args.beta, &args.beta_canon);
         if (rc != GZK_OK) return rc;
         return run_scan<kRouteNode>(ctx, args, true, nullptr);
     }
@@ -426,7 +485,7 @@ extern "C"
         args.count = valid_length;
         args.n = domain_size;
         args.out = static_cast<Fr*>(out->dptr);
-        int rc = load_scalar(ctx, beta, &args.beta);
+        int rc = load_scalar(ctx, beta, &args.beta, &args.beta_canon);
         if (rc != GZK_OK) return rc;
         return run_scan<kRouteEdge>(ctx, args, true, nullptr);
     }

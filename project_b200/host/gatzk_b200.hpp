@@ -36,6 +36,10 @@ namespace gatzk_b200
         Context(const Context&) = delete;
         Context& operator=(const Context&) = delete;
         gzk_ctx* raw() const { return ctx_; }
+        // Waits for the queued work; throws what a deferred call raised on the device.
+        void synchronize() const { check(gzk_ctx_synchronize(ctx_)); }
+        // Builder calls return once queued (errors surface at synchronize()).
+        void set_deferred(bool on) const { check(gzk_ctx_set_deferred(ctx_, on ? 1 : 0)); }
         void check(int rc) const
         {
             if (rc != GZK_OK) throw std::runtime_error(gzk_last_error(ctx_));

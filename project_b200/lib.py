@@ -115,6 +115,9 @@ class Backend:
         if rc != 0:
             raise GzkError(rc, self.lib.gzk_last_error(self.ctx).decode())
 
+    def set_deferred(self, on=True):
+        self._check(self.lib.gzk_ctx_set_deferred(self.ctx, int(bool(on))))
+
     def copy_fence(self):
         self._check(self.lib.gzk_copy_fence(self.ctx))
 

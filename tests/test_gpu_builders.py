@@ -264,3 +264,84 @@ def test_logup_large_uses_global_inversion_path(be):
 
 def pyref_int(b):
     return int.from_bytes(bytes(b), "little")
+
+
+def test_deferred_mode_queues_builders_and_reports_errors_at_synchronize(be):
+    """In deferred mode a chain of builder calls returns without synchronising and gives
+    the same columns; a zero denominator is reported by the next synchronize."""
+    from project_b200 import KIND_FR, KIND_I64, KIND_U32, GzkError
+
+    rng = np.random.default_rng(77)
+    n = 6000
+    table_i = rng.integers(-500, 500, size=n, dtype=np.int64)
+    query_i = rng.integers(-500, 500, size=n, dtype=np.int64)
+    mult_u = rng.integers(0, 50, size=n, dtype=np.uint32)
+    qt, qq = selector(5500, n), selector(5999, n)
+    betas = [fr_array([987654321987 + 2 * i]) for i in range(4)]
+    bufs = (be.upload(table_i, KIND_I64), be.upload(query_i, KIND_I64), be.upload(mult_u, KIND_U32), be.upload(qt, KIND_FR), be.upload(qq, KIND_FR))
+    want = [ora.logup_accumulator(ora.fr_from_i64(table_i), ora.fr_from_i64(query_i), ora.fr_from_i64(mult_u.astype(np.int64)), qt, qq, b, 5999)
+            for b in betas]
+    be.set_deferred(True)
+    try:
+        outs = [be.logup_accumulator(*bufs, n, b, 5999) for b in betas]
+        be.synchronize()
+        for o, w in zip(outs, want):
+            assert np.array_equal(o.download(), w)
+        bad_beta = fr_array([(-int(table_i[7])) % R])
+        be.logup_accumulator(*bufs, n, bad_beta, 5999)          # queued: no error yet
+        be.logup_accumulator(*bufs, n, betas[0], 5999, out=outs[0])  # a later good call does not clear it
+        with pytest.raises(GzkError) as e:
+            be.synchronize()
+        assert e.value.code == 3
+        be.synchronize()  # reported once
+        assert np.array_equal(outs[0].download(), want[0])
+    finally:
+        be.set_deferred(False)
+    got = be.logup_accumulator(*bufs, n, betas[1], 5999).download()
+    assert np.array_equal(got, want[1])
+
+
+def test_contexts_on_several_host_threads_share_buffers(be):
+    """The reference calls its builders from concurrent host tasks; here each host thread owns a
+    context (stream + scratch) and the threads read the same input buffers."""
+    import threading
+
+    from project_b200 import KIND_FR, KIND_I64, KIND_U32, Backend
+
+    rng = np.random.default_rng(123)
+    n = 20000
+    table_i = rng.integers(-2000, 2000, size=n, dtype=np.int64)
+    query_i = rng.integers(-2000, 2000, size=n, dtype=np.int64)
+    mult_u = rng.integers(0, 50, size=n, dtype=np.uint32)
+    qt, qq = selector(15000, n), selector(n - 1, n)
+    bufs = (be.upload(table_i, KIND_I64), be.upload(query_i, KIND_I64), be.upload(mult_u, KIND_U32), be.upload(qt, KIND_FR), be.upload(qq, KIND_FR))
+    betas = [fr_array([1234567 + 2 * t]) for t in range(4)]
+    want = [ora.logup_accumulator(ora.fr_from_i64(table_i), ora.fr_from_i64(query_i), ora.fr_from_i64(mult_u.astype(np.int64)), qt, qq, b, n - 1)
+            for b in betas]
+    got = [None] * 4
+    errors = []
+
+    def work(t):
+        try:
+            w = Backend(0)
+            try:
+                w.set_deferred(True)
+                outs = [w.logup_accumulator(*bufs, n, betas[t], n - 1) for _ in range(8)]
+                w.synchronize()
+                got[t] = [o.download() for o in outs]
+                for o in outs:
+                    o.free()
+            finally:
+                w.close()
+        except Exception as exc:  # surfaced below: an exception in a thread would otherwise be lost
+            errors.append(exc)
+
+    threads = [threading.Thread(target=work, args=(t,)) for t in range(4)]
+    for th in threads:
+        th.start()
+    for th in threads:
+        th.join()
+    assert not errors, errors
+    for t in range(4):
+        for g in got[t]:
+            assert np.array_equal(g, want[t])
