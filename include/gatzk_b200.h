@@ -87,6 +87,11 @@ int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, double* produ
  * (src/algebra/eval_backend.cpp:61-87): columns stay column-major in HBM. */
 int gzk_buf_alloc(gzk_ctx* ctx, int kind, size_t count, gzk_buf** out);
 int gzk_buf_free(gzk_ctx* ctx, gzk_buf* buf);
+/* A buffer over device memory the caller owns (its own pool, a tensor of its framework, a
+ * communication buffer): nothing is allocated or copied, gzk_buf_free releases only the
+ * handle.  The pointer must be 32-byte aligned memory of the context's GPU and stay valid
+ * while the handle is in use. */
+int gzk_buf_wrap(gzk_ctx* ctx, int kind, size_t count, void* device_ptr, gzk_buf** out);
 int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
 /* gzk_buf_upload_async queues the copy on a second stream so that it overlaps with kernels
  * in flight (host memory should be pinned and must stay valid); gzk_copy_fence makes all
@@ -256,6 +261,20 @@ int gzk_srs_lagrange(gzk_ctx* ctx, unsigned log2n, const uint8_t base[96], const
 int gzk_ntt(gzk_ctx* ctx, const gzk_buf* in, gzk_buf* out, unsigned log2n, size_t batch, int inverse, const uint8_t* coset_shift);
 int gzk_coset_lde(gzk_ctx* ctx, const gzk_buf* in, unsigned log2n, unsigned log2_blowup, const uint8_t shift[32], gzk_buf* out);
 int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out);
+
+/* ---- row-sharded transform (kernel sweep at 2^24 and above, several GPUs) -----------------------
+ * No reference caller.  n = n1*n2, element i = i1*n2 + i2, each GPU owns a block of rows i1.
+ * Forward: pack (gzk_swap_outer) -> all-to-all -> gzk_transpose -> gzk_ntt of length n1 on
+ * every row -> gzk_ntt_twiddle -> pack -> all-to-all -> gzk_transpose -> gzk_ntt of length
+ * n2; the GPU that owns k1 in its block ends with X[k1 + n1*k2] stored as [k1][k2].  The
+ * inverse runs the same steps backwards.  The all-to-all is the caller's (NCCL): data
+ * lands in the receiver's own memory before any kernel reads it.
+ * gzk_swap_outer: out[b][a][c] = in[a][b][c] for a < d0, b < d1, c < d2.
+ * gzk_transpose: out[c][r] = in[r][c].  Both move FR / FR_MONT elements unchanged.
+ * gzk_ntt_twiddle: buf[r][c] *= omega_n^((row_first + r) * c) (inverse: the inverse power). */
+int gzk_swap_outer(gzk_ctx* ctx, const gzk_buf* in, size_t d0, size_t d1, size_t d2, gzk_buf* out);
+int gzk_transpose(gzk_ctx* ctx, const gzk_buf* in, size_t rows, size_t cols, gzk_buf* out);
+int gzk_ntt_twiddle(gzk_ctx* ctx, gzk_buf* buf, unsigned log2n, uint64_t row_first, size_t rows, size_t cols, int inverse);
 /* the three values (at 0, 1, 2) of the round polynomial of the same table: what a rank
  * contributes to the per-round 3-element all-gather before the Fiat-Shamir squeeze */
 int gzk_sumcheck_round_sums(gzk_ctx* ctx, const gzk_buf* table, size_t n, uint8_t out[3 * 32]);

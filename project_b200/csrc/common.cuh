@@ -20,6 +20,7 @@ struct gzk_buf
     size_t count = 0;
     int kind = GZK_KIND_FR;
     size_t elem_bytes = 32;
+    bool owned = true;  // false: dptr belongs to the caller (gzk_buf_wrap)
 };
 
 namespace gzk

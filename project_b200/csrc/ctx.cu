@@ -408,8 +408,39 @@ extern "C"
         if (ctx == nullptr) return GZK_E_INVALID;
         if (buf == nullptr) return GZK_OK;
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        GZK_CUDA_TRY(ctx, cudaFree(buf->dptr));
+        if (buf->owned) GZK_CUDA_TRY(ctx, cudaFree(buf->dptr));
         delete buf;
+        return GZK_OK;
+    }
+
+    int gzk_buf_wrap(gzk_ctx* ctx, int kind, size_t count, void* device_ptr, gzk_buf** out)
+    {
+        if (ctx == nullptr || out == nullptr) return GZK_E_INVALID;
+        size_t elem = 0;
+        switch (kind)
+        {
+        case GZK_KIND_FR:
+        case GZK_KIND_FR_MONT: elem = 32; break;
+        case GZK_KIND_I64:
+        case GZK_KIND_F64: elem = 8; break;
+        case GZK_KIND_U32: elem = 4; break;
+        case GZK_KIND_G1: elem = 96; break;
+        default: return fail(ctx, GZK_E_INVALID, "unknown buffer kind");
+        }
+        if (device_ptr == nullptr || reinterpret_cast<uintptr_t>(device_ptr) % 32 != 0)
+            return fail(ctx, GZK_E_INVALID, "buf_wrap: device pointer must be non-null and 32-byte aligned");
+        cudaPointerAttributes attr{};
+        GZK_CUDA_TRY(ctx, cudaPointerGetAttributes(&attr, device_ptr));
+        if (attr.type != cudaMemoryTypeDevice || attr.device != ctx->device)
+            return fail(ctx, GZK_E_INVALID, "buf_wrap: pointer is not device memory of this context's GPU");
+        gzk_buf* b = new (std::nothrow) gzk_buf();
+        if (b == nullptr) return fail(ctx, GZK_E_INVALID, "out of host memory");
+        b->dptr = device_ptr;
+        b->count = count;
+        b->kind = kind;
+        b->elem_bytes = elem;
+        b->owned = false;
+        *out = b;
         return GZK_OK;
     }
 

@@ -291,8 +291,7 @@ extern "C"
             GZK_CUDA_TRY(ctx, cudaGetLastError());
             s0 += stages;
         } while (s0 < log2n);
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out)
@@ -318,8 +317,7 @@ extern "C"
             fold_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(t, r, half, static_cast<Fr*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-        return GZK_OK;
+        return finish_call(ctx, "invalid input");
     }
 
     // out[0] = sum_i t[2i], out[1] = sum_i t[2i+1], out[2] = 2*out[1] - out[0]: the values at

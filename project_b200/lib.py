@@ -288,6 +288,27 @@ class Backend:
         self._check(self.lib.gzk_ntt(self.ctx, inp.handle, out.handle, ctypes.c_uint(log2n), _sz(batch), int(bool(inverse)), shift))
         return out
 
+    def wrap(self, kind, count, device_ptr):
+        """A Buffer over device memory owned by the caller (e.g. a torch tensor)."""
+        h = ctypes.c_void_p()
+        self._check(self.lib.gzk_buf_wrap(self.ctx, int(kind), _sz(count), ctypes.c_void_p(device_ptr), ctypes.byref(h)))
+        return Buffer(self, h, kind, count)
+
+    def swap_outer(self, inp, d0, d1, d2, out=None):
+        out = out or self.alloc(inp.kind, d0 * d1 * d2)
+        self._check(self.lib.gzk_swap_outer(self.ctx, inp.handle, _sz(d0), _sz(d1), _sz(d2), out.handle))
+        return out
+
+    def transpose(self, inp, rows, cols, out=None):
+        out = out or self.alloc(inp.kind, rows * cols)
+        self._check(self.lib.gzk_transpose(self.ctx, inp.handle, _sz(rows), _sz(cols), out.handle))
+        return out
+
+    def ntt_twiddle(self, buf, log2n, row_first, rows, cols, inverse=False):
+        self._check(self.lib.gzk_ntt_twiddle(self.ctx, buf.handle, ctypes.c_uint(log2n), ctypes.c_uint64(row_first), _sz(rows), _sz(cols),
+                                             int(bool(inverse))))
+        return buf
+
     def coset_lde(self, inp, log2n, log2_blowup, shift):
         out = self.alloc(KIND_FR_MONT, 1 << (log2n + log2_blowup))
         self._check(self.lib.gzk_coset_lde(self.ctx, inp.handle, ctypes.c_uint(log2n), ctypes.c_uint(log2_blowup), _ptr(_fr(shift)), out.handle))

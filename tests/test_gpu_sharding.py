@@ -107,3 +107,34 @@ def test_generated_columns(be):
     assert np.array_equal(be.generated_column(1, valid, 0, n, KIND_I64).download(), np.where(idx < valid, idx, 0))
     assert np.array_equal(be.generated_column(2, valid, width, n).download(), np.where(idx < valid, idx // width, 0))
     assert np.array_equal(be.generated_column(3, valid, width, n).download(), np.where(idx < valid, idx % width, 0))
+
+
+def test_sharded_segmented_state_with_carry(be):
+    """A segmented running sum (restarts where q_new = 1) whose rows are cut at arbitrary
+    places over 4 'ranks': the carry of a rank is the state at the end of the rank before it
+    and reaches only the rows ahead of the rank's first restart."""
+    from project_b200 import KIND_FR, KIND_U32, fr_sum
+
+    rng = np.random.default_rng(31)
+    n = 9000
+    values = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    values[:, 31] &= 0x3F
+    q_new = (rng.random(n) < 0.002).astype(np.uint32)  # long segments, some ranks see no restart
+    q_new[0] = 1
+    q_new[2500:5200] = 0                               # rank 2 of the cut below sees none
+    whole = be.group_prefix_state(be.upload(values, KIND_FR), be.upload(q_new, KIND_U32), n).download()
+    cuts = [0, 1111, 2600, 5100, n]
+    carry = None
+    got = np.zeros_like(whole)
+    for rank in range(4):
+        begin, end = cuts[rank], cuts[rank + 1]
+        rows = end - begin
+        local = be.group_prefix_state(be.upload(values[begin:end], KIND_FR), be.upload(q_new[begin:end], KIND_U32), rows)
+        restarts = np.flatnonzero(q_new[begin:end])
+        reach = int(restarts[0]) if restarts.size else rows  # rows that continue the segment of the rank before
+        if carry is not None and reach > 0:
+            be.fr_add_scalar(local, 0, reach, carry)
+        out = local.download()
+        got[begin:end] = out
+        carry = out[-1]  # the state at the end of this rank (already carries what came before)
+    assert np.array_equal(got, whole)
