@@ -177,11 +177,33 @@ def run_reference(args, workload, wl_name):
         "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    print(json.dumps(line))
+    emit(line)
     return 0
 
 
+_RESULT_OUT = None
+
+
+def claim_stdout():
+    """Libraries (NCCL's version banner, for one) write to file descriptor 1; the result line
+    must be the only thing there.  Keep a private copy of stdout for the result and point
+    descriptor 1 at stderr for everything else."""
+    global _RESULT_OUT
+    if _RESULT_OUT is None:
+        sys.stdout.flush()
+        _RESULT_OUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+    return _RESULT_OUT
+
+
+def emit(line):
+    out = claim_stdout()
+    out.write(json.dumps(line) + "\n")
+    out.flush()
+
+
 def main():
+    claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -194,6 +216,7 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-sweep", action="store_true", help="skip the MSM / NTT / fold kernel sweep lines")
+    ap.add_argument("--sweep-only", action="store_true", help="only the MSM / NTT / fold sweep (profiler captures of those kernels)")
     args = ap.parse_args()
     workload = WORKLOAD_SMALL if args.small else (WORKLOAD_PROFILE if args.profile_case else WORKLOAD_B2)
     wl_name = ("reduced shapes (edge 2^14 x 64, N 2^11 x 32)" if args.small else
@@ -224,6 +247,15 @@ def main():
     rng = np.random.default_rng(1234)
     G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8).copy()
     heads = 2 if (args.small or args.profile_case) else 16
+    if args.sweep_only:
+        if world == 1:
+            sweep = run_sweep(be, rng, G, stream, small=args.small)
+        else:
+            sweep = run_sweep_sharded(be, G, stream, rank, world, local_rank, small=args.small)
+            dist.destroy_process_group()
+        if rank == 0:
+            emit({"sweep": sweep, "n_gpus": world})
+        return 0
 
     # ---- resident inputs: every rank holds its ROW range of every column ---------------
     slabs = {}
@@ -500,6 +532,8 @@ def main():
     sweep = None
     if world == 1 and not args.no_sweep and not args.profile_case:
         sweep = run_sweep(be, rng, G, stream, small=args.small)
+    elif world > 1 and not args.no_sweep and not args.profile_case:
+        sweep = run_sweep_sharded(be, G, stream, rank, world, local_rank, small=args.small)
 
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -519,7 +553,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
             "kernel_ms": {k: round(v[1], 3) for k, v in report.items()}, "clocks": clocks, "sweep": sweep,
         }
-        print(json.dumps(line))
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
     return 0
@@ -569,6 +603,82 @@ def run_sweep(be, rng, G, stream, small=False):
     out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6}
     for b in (scalars, points, vec, res):
         b.free()
+    return out
+
+
+def run_sweep_sharded(be, G, stream, rank, world, device, small=False):
+    """Sweep kernels over all ranks: the row-sharded transform (two all-to-all exchanges over
+    NCCL) and the point-range-sharded MSM (one 96-byte all-gather); device-timed, max over ranks."""
+    import torch
+    import torch.distributed as dist
+
+    from project_b200 import KIND_FR, KIND_FR_MONT, g1_sum
+    from project_b200 import sharded_ntt as sn
+
+    rng = np.random.default_rng(1000 + rank)
+
+    def rand_fr(n):
+        a = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+        a[:, 31] &= 0x3F
+        return a
+
+    def timed_ms(fn, reps=3):
+        fn()
+        be.synchronize()
+        dist.barrier()
+        start = torch.cuda.Event(enable_timing=True)
+        stop = torch.cuda.Event(enable_timing=True)
+        start.record(stream)
+        for _ in range(reps):
+            fn()
+        stop.record(stream)
+        be.synchronize()
+        t = torch.tensor([start.elapsed_time(stop) / reps], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    out = {}
+    if world & (world - 1) == 0:
+        lg = 14 if small else 24
+        n = 1 << lg
+        local = n // world
+        vec = be.upload(rand_fr(local), KIND_FR)
+        work = (be.alloc(KIND_FR, local), be.alloc(KIND_FR_MONT, local))
+        exchange = sn.NcclExchange(be, local, device)
+
+        def transform():
+            work[0].retag(KIND_FR)
+            exchange.run(sn.forward(be, vec, lg, rank, world, work=work))
+
+        ms = timed_ms(transform)
+        be.timing_reset()
+        be.timing_enable(True)
+        transform()
+        be.synchronize()
+        families = {k: round(v[1], 3) for k, v in be.timing_report().items()}
+        be.timing_enable(False)
+        exchange.close()
+        for b in work:
+            b.free()
+        out["ntt_sharded"] = {"log2n": lg, "ranks": world, "ms": ms, "GB_per_s": 2 * 32 * n / ms / 1e6,
+                              "field_mults_per_s": (n // 2) * lg / ms * 1e3, "layout": "rows in, transposed out; 2 all-to-all exchanges",
+                              "kernel_ms_one_transform": families}
+        vec.free()
+    lg = 12 if small else 20
+    n_local = (1 << lg)
+    scalars = be.upload(rand_fr(n_local), KIND_FR)
+    points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n_local), KIND_FR), n_local)
+
+    def msm():
+        part = torch.from_numpy(be.msm(scalars, points, n_local).copy()).cuda()
+        gathered = torch.empty((world, 96), dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(gathered, part)
+        return g1_sum(gathered.cpu().numpy())
+
+    ms = timed_ms(msm)
+    out["msm_sharded"] = {"log2n_per_rank": lg, "ranks": world, "ms": ms, "Mpts_per_s": world * n_local / ms / 1e3}
+    scalars.free()
+    points.free()
     return out
 
 

@@ -92,6 +92,10 @@ int gzk_buf_free(gzk_ctx* ctx, gzk_buf* buf);
  * handle.  The pointer must be 32-byte aligned memory of the context's GPU and stay valid
  * while the handle is in use. */
 int gzk_buf_wrap(gzk_ctx* ctx, int kind, size_t count, void* device_ptr, gzk_buf** out);
+/* Declares which of the two 32-byte forms (GZK_KIND_FR canonical, GZK_KIND_FR_MONT) the
+ * buffer holds from now on, for work areas that are refilled by copies (gzk_transpose,
+ * gzk_swap_outer, an exchange between GPUs); nothing is converted. */
+int gzk_buf_retag(gzk_buf* buf, int kind);
 int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
 /* gzk_buf_upload_async queues the copy on a second stream so that it overlaps with kernels
  * in flight (host memory should be pinned and must stay valid); gzk_copy_fence makes all

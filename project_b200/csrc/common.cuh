@@ -63,6 +63,17 @@ namespace gzk
     };
 }
 
+namespace gzk
+{
+    // Load-time factors of one transform pass (first stage s0, `stages` stages), cached per context.
+    struct NttTwistTable
+    {
+        unsigned s0 = 0, stages = 0;
+        bool inverse = false;
+        Fr* table = nullptr;
+    };
+}
+
 struct gzk_ctx
 {
     int device = 0;
@@ -72,6 +83,8 @@ struct gzk_ctx
     cudaEvent_t copy_event = nullptr;
     std::string last_error;
     std::unordered_map<unsigned, gzk::DomainTables> domains;
+    gzk::Fr* ntt_small[2] = {nullptr, nullptr};  // omega_1024^m and omega_1024^-m, m < 512
+    std::vector<gzk::NttTwistTable> ntt_twists;
     gzk::Scratch scratch[4];
     void* pinned = nullptr;  // small pinned staging area for results
     size_t pinned_bytes = 0;

@@ -306,6 +306,9 @@ extern "C"
         }
         for (auto& s : ctx->scratch)
             if (s.ptr != nullptr) cudaFree(s.ptr);
+        for (Fr* t : ctx->ntt_small)
+            if (t != nullptr) cudaFree(t);
+        for (auto& t : ctx->ntt_twists) cudaFree(t.table);
         if (ctx->pinned != nullptr) cudaFreeHost(ctx->pinned);
         if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
         timing_collect(ctx);
@@ -410,6 +413,16 @@ extern "C"
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         if (buf->owned) GZK_CUDA_TRY(ctx, cudaFree(buf->dptr));
         delete buf;
+        return GZK_OK;
+    }
+
+    int gzk_buf_retag(gzk_buf* buf, int kind)
+    {
+        if (buf == nullptr) return GZK_E_INVALID;
+        const bool field_now = buf->kind == GZK_KIND_FR || buf->kind == GZK_KIND_FR_MONT;
+        const bool field_then = kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT;
+        if (!field_now || !field_then) return GZK_E_INVALID;
+        buf->kind = kind;
         return GZK_OK;
     }
 

@@ -2,13 +2,25 @@
 // (kernel sweep; the reference has no transform on its proving path).
 //
 // Natural order in, natural order out.  The log2(n) radix-2 stages are grouped into
-// passes of up to 10 stages; each pass loads a 1024-element tile into shared
-// memory (limb-planar, conflict-free), runs its stages there and writes the tile
-// back, so a 2^24-point transform touches HBM in 4 passes instead of 24.  Pass 0
-// gathers its tile through the bit-reversal permutation; later passes take tiles
-// of 2^G strided rows by 2^L contiguous elements.  Twiddles come from the two-level
-// omega tables of the domain (a lookup, plus one multiplication where the exponent
-// has low bits).
+// passes (10 stages in the first, up to 8 in the others); each pass loads a
+// 1024-element tile into shared memory (limb-planar, conflict-free), runs its stages
+// there and writes the tile back, so a 2^24-point transform touches HBM in 3 passes
+// instead of 24.  Pass 0 gathers its tile through the bit-reversal permutation; later
+// passes take tiles of 2^S strided rows by 2^(10-S) contiguous elements (S <= 8, at
+// least one 128-byte line per row).
+//
+// Twiddles.  The stage-s butterfly of element pair (.., j) needs omega_(2^(s+1))^j with
+// j the low s bits of the index.  Inside a pass that starts at stage s0, j splits into the
+// bits below s0 ("low", constant through the pass) and the bits of the tile row that the
+// pass has already combined, m: omega_(2^(s+1))^j = omega_(2^(t+1))^m * omega_(2^(s+1))^low
+// with t = s - s0.  Multiplying element (row, low) ONCE, on load, by
+// omega_(2^(s0+S))^(low * bitrev_S(row)) removes the second factor from every stage of the
+// pass (the factor a row still carries after stage t is exactly what the remaining stages
+// expect), so the stages use only the first factor: a 1024th root of unity from a
+// 512-entry table, one multiplication per butterfly and none where m = 0.  The load-time
+// factors come from a table per (s0, S) built once per context ([bitrev row][low], so a
+// warp reads it in the same runs as the data); above 2^25 entries they are generated
+// from the two-level omega tables instead (one more multiplication per element).
 #include <cstring>
 
 #include "block.cuh"
@@ -25,7 +37,9 @@ namespace gzk
         {
             ColRef in;          // pass 0 only
             Fr* data;           // output / in-place working vector (Montgomery)
-            const Fr* lo;       // omega^j or omega^-j
+            const Fr* small;    // omega_1024^m (or the inverse powers), m < 512: in-pass twiddles
+            const Fr* twist;    // pass > 0: load-time factors [bitrev row][low]; NULL = generate them
+            const Fr* lo;       // omega^j or omega^-j (generated load-time factors)
             const Fr* hi;
             unsigned lo_bits;
             unsigned log2n;
@@ -91,6 +105,14 @@ namespace gzk
                 else
                 {
                     v = load_fr_plain(a.data + vec_offset + gi);
+                    const uint32_t c = __brev(e >> a.low_bits) >> (32 - a.stages);
+                    const uint64_t low = gi & ((1ULL << a.s0) - 1ULL);
+                    if (c != 0 && low != 0)
+                    {
+                        const Fr w = a.twist != nullptr ? load_fr(a.twist + ((static_cast<uint64_t>(c) << a.s0) | low))
+                                                        : domain_point(a.lo, a.hi, a.lo_bits, (low * c) << (a.log2n - a.s0 - a.stages));
+                        v = mul(v, w);
+                    }
                 }
                 smem_store(tile, e, v);
             }
@@ -98,7 +120,7 @@ namespace gzk
 
             for (unsigned t = 0; t < a.stages; ++t)
             {
-                const unsigned s = a.s0 + t;  // butterflies pair rows whose `mid` differs in bit t
+                // butterflies pair rows that differ in bit t; m = the t row bits below it
                 for (uint32_t b = threadIdx.x; b < tile_elems / 2; b += kThreads)
                 {
                     // insert a zero at bit (t + low_bits) of b
@@ -106,12 +128,10 @@ namespace gzk
                     const uint32_t lower = b & ((1u << pos) - 1u);
                     const uint32_t e0 = ((b >> pos) << (pos + 1)) | lower;
                     const uint32_t e1 = e0 | (1u << pos);
-                    const uint64_t gi = tile_index(a, tile_id, e0);
-                    const uint64_t j = gi & ((1ULL << s) - 1ULL);
-                    const uint64_t k = j << (a.log2n - s - 1);  // exponent of omega_n
+                    const uint32_t m = lower >> a.low_bits;
                     const Fr u = smem_load(tile, e0);
                     Fr v = smem_load(tile, e1);
-                    if (k != 0) v = mul(v, domain_point(a.lo, a.hi, a.lo_bits, k));
+                    if (m != 0) v = mul(v, load_fr(a.small + (m << (9 - t))));
                     smem_store(tile, e0, add(u, v));
                     smem_store(tile, e1, sub(u, v));
                 }
@@ -133,6 +153,73 @@ namespace gzk
         {
             const uint32_t j = blockIdx.x * blockDim.x + threadIdx.x;
             if (j < count) store_fr(out + j, pow_u64(base, static_cast<uint64_t>(j) << shift_bits));
+        }
+
+        // out[(c << s0) | low] = omega_(2^(s0+S))^(low * c): the load-time factors of a pass
+        __global__ void twist_table_kernel(const Fr* lo, const Fr* hi, unsigned lo_bits, unsigned s0, uint64_t count, Fr* out)
+        {
+            const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            if (i >= count) return;
+            const uint64_t low = i & ((1ULL << s0) - 1ULL), c = i >> s0;
+            store_fr(out + i, domain_point(lo, hi, lo_bits, low * c));
+        }
+        __global__ void small_table_kernel(const Fr* lo, const Fr* hi, unsigned lo_bits, Fr* out)
+        {
+            const uint32_t m = blockIdx.x * blockDim.x + threadIdx.x;
+            if (m < 512) store_fr(out + m, domain_point(lo, hi, lo_bits, m));
+        }
+
+        constexpr unsigned kTwistTableMaxBits = 25;  // 1 GiB of load-time factors at most per table
+
+        // The in-pass twiddle table (omega_1024^(+-m)) of the context, built on first use.
+        int small_table(gzk_ctx* ctx, bool inverse, const Fr** out)
+        {
+            Fr*& slot = ctx->ntt_small[inverse ? 1 : 0];
+            if (slot == nullptr)
+            {
+                const DomainTables* dom = nullptr;
+                int rc = get_domain(ctx, 10, &dom);
+                if (rc != GZK_OK) return rc;
+                GZK_CUDA_TRY(ctx, cudaMalloc(reinterpret_cast<void**>(&slot), 512 * sizeof(Fr)));
+                small_table_kernel<<<4, 128, 0, ctx->stream>>>(inverse ? dom->lo_inv : dom->lo, inverse ? dom->hi_inv : dom->hi, dom->lo_bits, slot);
+                GZK_CUDA_TRY(ctx, cudaGetLastError());
+            }
+            *out = slot;
+            return GZK_OK;
+        }
+
+        // The load-time factor table of a pass (s0, stages), built on first use; *out = NULL
+        // when the table would exceed the size limit (the kernel then generates the factors).
+        int twist_table(gzk_ctx* ctx, unsigned s0, unsigned stages, bool inverse, const Fr** out)
+        {
+            *out = nullptr;
+            if (s0 + stages > kTwistTableMaxBits) return GZK_OK;
+            for (const NttTwistTable& t : ctx->ntt_twists)
+                if (t.s0 == s0 && t.stages == stages && t.inverse == inverse)
+                {
+                    *out = t.table;
+                    return GZK_OK;
+                }
+            const DomainTables* dom = nullptr;
+            int rc = get_domain(ctx, s0 + stages, &dom);
+            if (rc != GZK_OK) return rc;
+            const uint64_t count = 1ULL << (s0 + stages);
+            NttTwistTable entry;
+            entry.s0 = s0;
+            entry.stages = stages;
+            entry.inverse = inverse;
+            const cudaError_t err = cudaMalloc(reinterpret_cast<void**>(&entry.table), count * sizeof(Fr));
+            if (err != cudaSuccess)
+            {
+                cudaGetLastError();  // no room for the table: fall back to generated factors
+                return GZK_OK;
+            }
+            twist_table_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, ctx->stream>>>(
+                inverse ? dom->lo_inv : dom->lo, inverse ? dom->hi_inv : dom->hi, dom->lo_bits, s0, count, entry.table);
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            ctx->ntt_twists.push_back(entry);
+            *out = entry.table;
+            return GZK_OK;
         }
 
         __global__ void fold_kernel(ColRef table, Fr r, uint64_t half, Fr* out)
@@ -233,6 +320,7 @@ extern "C"
         args.lo = inverse ? dom->lo_inv : dom->lo;
         args.hi = inverse ? dom->hi_inv : dom->hi;
         args.lo_bits = dom->lo_bits;
+        if ((rc = small_table(ctx, inverse != 0, &args.small)) != GZK_OK) return rc;
         args.log2n = log2n;
         args.scale = dom->inv_size;
         args.scale_mode = inverse ? 1 : 0;
@@ -264,19 +352,30 @@ extern "C"
         }
 
         const size_t smem = 8 * kTile * sizeof(uint32_t);
+        // pass 0 takes up to 10 stages; the rest is spread evenly over passes of at most 8
+        // stages, each on full 1024-element tiles (2^stages rows of 2^(10-stages) contiguous elements)
+        const unsigned later = log2n > static_cast<unsigned>(kTileBits) ? log2n - kTileBits : 0;
+        const unsigned later_passes = (later + 7) / 8;
+        unsigned later_done = 0, pass_index = 0;
         unsigned s0 = 0;
         do
         {
             const unsigned remaining = log2n - s0;
             unsigned low_bits = 0, stages = 0;
+            args.twist = nullptr;
             if (s0 == 0)
             {
                 stages = remaining < static_cast<unsigned>(kTileBits) ? remaining : kTileBits;
             }
             else
             {
-                low_bits = s0 < 4 ? s0 : 4;
-                stages = remaining < kTileBits - low_bits ? remaining : kTileBits - low_bits;
+                // passes still to run share what is left as evenly as possible
+                const unsigned passes_left = later_passes - pass_index;
+                stages = (later - later_done + passes_left - 1) / passes_left;
+                low_bits = kTileBits - stages;
+                later_done += stages;
+                ++pass_index;
+                if ((rc = twist_table(ctx, s0, stages, inverse != 0, &args.twist)) != GZK_OK) return rc;
             }
             args.s0 = s0;
             args.stages = stages;

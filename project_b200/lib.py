@@ -85,6 +85,13 @@ class Buffer:
         self.backend._check(self.backend.lib.gzk_buf_download(self.backend.ctx, self.handle, _sz(offset), _ptr(out), _sz(count)))
         return out
 
+    def retag(self, kind):
+        """Declare the 32-byte form (KIND_FR / KIND_FR_MONT) a refilled work buffer now holds."""
+        if self.backend.lib.gzk_buf_retag(self.handle, int(kind)) != 0:
+            raise ValueError("retag: only between the two field-element kinds")
+        self.kind = kind
+        return self
+
     @property
     def device_ptr(self):
         return self.backend.lib.gzk_buf_device_ptr(self.handle)

@@ -8,8 +8,10 @@ needs no exchange.
 
 Both directions are generators: they yield a Buffer whose `world` equal chunks go to ranks
 0..world-1 and expect to be sent the Buffer of chunks received from ranks 0..world-1 (an
-all-to-all).  `run_nccl` drives one rank with torch.distributed; `run_emulated` drives all ranks
+all-to-all).  `NcclExchange` drives one rank with torch.distributed; `run_emulated` drives all ranks
 of a single process in lockstep (tests on one GPU)."""
+from .lib import KIND_FR_MONT
+
 
 def split(log2n, world):
     """(log2 n1, log2 n2): both at least log2(world) so that rows and columns split evenly."""
@@ -23,53 +25,48 @@ def split(log2n, world):
     return l1, l2
 
 
-def forward(be, x, log2n, rank, world):
+def forward(be, x, log2n, rank, world, work=None):
     """x: this rank's rows [n1/world][n2] (FR or FR_MONT).  Returns [n1/world][n2] FR_MONT = X[k1 + n1*k2].
-    Intermediate buffers, the yielded ones and the received ones are freed here."""
+    `work` = two Buffers of the local size (one of x's kind, one FR_MONT) to run without
+    allocating; the result is then work[1].  Received Buffers stay the driver's."""
     l1, l2 = split(log2n, world)
     n1, n2 = 1 << l1, 1 << l2
     rows1, cols2 = n1 // world, n2 // world
-    send = be.swap_outer(x, rows1, world, cols2)                 # [dest][i1 local][i2 local]
-    recv = yield send                                            # [src][i1 local][i2 local] = [i1][i2 local]
-    send.free()
-    t = be.transpose(recv, n1, cols2)                            # [i2 local][i1]
-    recv.free()
-    y = be.ntt(t, l1, batch=cols2)                               # [i2 local][k1]
-    t.free()
-    be.ntt_twiddle(y, log2n, rank * cols2, cols2, n1)            # * omega_n^(i2*k1)
-    send = be.swap_outer(y, cols2, world, rows1)                 # [dest][i2 local][k1 local]
-    y.free()
-    recv = yield send                                            # [i2][k1 local]
-    send.free()
-    t = be.transpose(recv, n2, rows1)                            # [k1 local][i2]
-    recv.free()
-    out = be.ntt(t, l2, batch=rows1)                             # [k1 local][k2]
-    t.free()
-    return out
+    a, b = work if work is not None else (be.alloc(x.kind, rows1 * n2), be.alloc(KIND_FR_MONT, rows1 * n2))
+    a.retag(x.kind)
+    recv = yield be.swap_outer(x, rows1, world, cols2, out=a)   # [dest][i1 local][i2 local] -> [i1][i2 local]
+    a.retag(recv.kind)
+    be.transpose(recv, n1, cols2, out=a)                         # [i2 local][i1]
+    be.ntt(a, l1, batch=cols2, out=b)                            # [i2 local][k1]
+    be.ntt_twiddle(b, log2n, rank * cols2, cols2, n1)            # * omega_n^(i2*k1)
+    a.retag(KIND_FR_MONT)
+    recv = yield be.swap_outer(b, cols2, world, rows1, out=a)    # [dest][i2 local][k1 local] -> [i2][k1 local]
+    be.transpose(recv, n2, rows1, out=a)                         # [k1 local][i2]
+    be.ntt(a, l2, batch=rows1, out=b)                            # [k1 local][k2]
+    if work is None:
+        be.synchronize()
+        a.free()
+    return b
 
 
-def inverse(be, xt, log2n, rank, world):
-    """xt: [n1/world][n2] as left by `forward`.  Returns this rank's contiguous rows, FR_MONT."""
+def inverse(be, xt, log2n, rank, world, work=None):
+    """xt: [n1/world][n2] FR_MONT as left by `forward`.  Returns this rank's contiguous rows, FR_MONT
+    (work[1] when `work`, two FR_MONT Buffers of the local size, is given)."""
     l1, l2 = split(log2n, world)
     n1, n2 = 1 << l1, 1 << l2
     rows1, cols2 = n1 // world, n2 // world
-    t = be.ntt(xt, l2, batch=rows1, inverse=True)                # [k1 local][i2]
-    send = be.transpose(t, rows1, n2)                            # [i2][k1 local]: chunk h = rows i2 of rank h
-    t.free()
-    recv = yield send                                            # [src][i2 local][k1 local of src]
-    send.free()
-    y = be.swap_outer(recv, world, cols2, rows1)                 # [i2 local][k1]
-    recv.free()
-    be.ntt_twiddle(y, log2n, rank * cols2, cols2, n1, inverse=True)
-    t = be.ntt(y, l1, batch=cols2, inverse=True)                 # [i2 local][i1]
-    y.free()
-    send = be.transpose(t, cols2, n1)                            # [i1][i2 local]: chunk h = rows i1 of rank h
-    t.free()
-    recv = yield send                                            # [src][i1 local][i2 local of src]
-    send.free()
-    out = be.swap_outer(recv, world, rows1, cols2)               # [i1 local][i2]
-    recv.free()
-    return out
+    a, b = work if work is not None else (be.alloc(KIND_FR_MONT, rows1 * n2), be.alloc(KIND_FR_MONT, rows1 * n2))
+    be.ntt(xt, l2, batch=rows1, inverse=True, out=a)             # [k1 local][i2]
+    recv = yield be.transpose(a, rows1, n2, out=b)               # [i2][k1 local]: chunk h = rows i2 of rank h
+    be.swap_outer(recv, world, cols2, rows1, out=a)              # [i2 local][k1]
+    be.ntt_twiddle(a, log2n, rank * cols2, cols2, n1, inverse=True)
+    be.ntt(a, l1, batch=cols2, inverse=True, out=b)              # [i2 local][i1]
+    recv = yield be.transpose(b, cols2, n1, out=a)               # [i1][i2 local]: chunk h = rows i1 of rank h
+    be.swap_outer(recv, world, rows1, cols2, out=b)              # [i1 local][i2]
+    if work is None:
+        be.synchronize()
+        a.free()
+    return b
 
 
 def run_emulated(backends, inputs, log2n, direction=forward):
@@ -91,35 +88,47 @@ def run_emulated(backends, inputs, log2n, direction=forward):
                 sends.append(gens[g].send(recvs[g]))
             except StopIteration as done:
                 results.append(done.value)
+        for g in range(world):
+            backends[g].synchronize()
+            recvs[g].free()
         if results:
             if len(results) != world:
                 raise RuntimeError("ranks finished at different exchange steps")
             return results
 
 
-def run_nccl(be, gen, count, device):
-    """One rank under torch.distributed (NCCL): every yielded Buffer is exchanged with
-    all_to_all_single into a tensor of this GPU's own memory, which the next kernels read."""
-    import torch
-    import torch.distributed as dist
+class NcclExchange:
+    """The all-to-all of one rank under torch.distributed (NCCL), queued on the context's own
+    stream: chunks land in a persistent tensor of this GPU's memory, which the next kernels read
+    through a wrapped Buffer.  Nothing here waits on the host."""
 
-    stream = torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", device))
-    keep = []
-    try:
-        send = next(gen)
-        while True:
-            be.synchronize()
-            with torch.cuda.stream(stream):
-                src = _as_tensor(send, count, device)
-                dst = torch.empty_like(src)
-                dist.all_to_all_single(dst, src)
-            stream.synchronize()
-            keep = [dst]  # the tensor backs the wrapped Buffer until the generator has consumed it
-            send = gen.send(be.wrap(send.kind, count, dst.data_ptr()))
-    except StopIteration as done:
-        be.synchronize()
-        del keep
-        return done.value
+    def __init__(self, be, count, device):
+        import torch
+
+        self.be, self.count = be, count
+        self.device = torch.device("cuda", device)
+        self.stream = torch.cuda.ExternalStream(be.stream, device=self.device)
+        self.dst = torch.empty((count, 32), dtype=torch.uint8, device=self.device)
+        self.recv = be.wrap(KIND_FR_MONT, count, self.dst.data_ptr())
+
+    def run(self, gen):
+        import torch
+        import torch.distributed as dist
+
+        try:
+            send = next(gen)
+            while True:
+                with torch.cuda.stream(self.stream):
+                    dist.all_to_all_single(self.dst, _as_tensor(send, self.count, self.device))
+                self.recv.retag(send.kind)
+                send = gen.send(self.recv)
+        except StopIteration as done:
+            return done.value
+
+    def close(self):
+        self.be.synchronize()
+        self.recv.free()
+        self.dst = None
 
 
 def _as_tensor(buf, count, device):
@@ -130,7 +139,7 @@ def _as_tensor(buf, count, device):
 
     holder = _Iface()
     holder.__cuda_array_interface__ = {"shape": (count, 32), "typestr": "|u1", "data": (buf.device_ptr, False), "version": 2}
-    return torch.as_tensor(holder, device=torch.device("cuda", device))
+    return torch.as_tensor(holder, device=device)
 
 
-__all__ = ["forward", "inverse", "run_emulated", "run_nccl", "split"]
+__all__ = ["forward", "inverse", "run_emulated", "NcclExchange", "split"]

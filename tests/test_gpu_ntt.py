@@ -24,7 +24,7 @@ def rand_fr(rng, n):
     return a
 
 
-@pytest.mark.parametrize("log2n", [0, 1, 2, 5, 9, 10, 11, 13, 14, 16])
+@pytest.mark.parametrize("log2n", [0, 1, 2, 5, 9, 10, 11, 12, 13, 14, 16, 18, 19, 21])
 def test_ntt_matches_oracle(be, log2n):
     from project_b200 import KIND_FR
 

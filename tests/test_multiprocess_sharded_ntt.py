@@ -13,26 +13,39 @@ class _HostBuf:
     def __init__(self, data, kind=0):
         self.data, self.kind = np.ascontiguousarray(data, dtype=np.uint8).reshape(-1, 32), kind
 
+    def retag(self, kind):
+        self.kind = kind
+        return self
+
     def free(self):
         self.data = None
 
 
 class _HostBackend:
-    """The four calls the sequence makes, on host arrays of canonical field elements."""
+    """The calls the sequence makes, on host arrays of canonical field elements."""
 
     def __init__(self, ora, pyref):
         self.ora, self.pyref = ora, pyref
 
-    def swap_outer(self, b, d0, d1, d2):
-        return _HostBuf(b.data.reshape(d0, d1, d2, 32).transpose(1, 0, 2, 3))
+    def alloc(self, kind, count):
+        return _HostBuf(np.zeros((count, 32), np.uint8), kind)
 
-    def transpose(self, b, rows, cols):
-        return _HostBuf(b.data.reshape(rows, cols, 32).transpose(1, 0, 2))
+    def synchronize(self):
+        pass
 
-    def ntt(self, b, log2n, batch=1, inverse=False):
+    def swap_outer(self, b, d0, d1, d2, out):
+        out.data = np.ascontiguousarray(b.data.reshape(d0, d1, d2, 32).transpose(1, 0, 2, 3)).reshape(-1, 32)
+        return out
+
+    def transpose(self, b, rows, cols, out):
+        out.data = np.ascontiguousarray(b.data.reshape(rows, cols, 32).transpose(1, 0, 2)).reshape(-1, 32)
+        return out
+
+    def ntt(self, b, log2n, batch=1, inverse=False, out=None):
         n = 1 << log2n
         rows = b.data.reshape(batch, n, 32)
-        return _HostBuf(np.concatenate([self.ora.ntt(np.ascontiguousarray(rows[i]), inverse=inverse) for i in range(batch)]))
+        out.data = np.concatenate([self.ora.ntt(np.ascontiguousarray(rows[i]), inverse=inverse) for i in range(batch)])
+        return out
 
     def ntt_twiddle(self, b, log2n, row_first, rows, cols, inverse=False):
         R = self.pyref.R
