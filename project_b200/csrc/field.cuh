@@ -17,6 +17,7 @@ namespace gzk
     struct FrCfg
     {
         static constexpr int N = 8;
+        static constexpr int BITS = 255;
         static constexpr uint32_t INV = 0xffffffffu;  // -r^-1 mod 2^32
         GZK_HD static constexpr uint32_t mod(int i)
         {
@@ -41,6 +42,7 @@ namespace gzk
     struct FpCfg
     {
         static constexpr int N = 12;
+        static constexpr int BITS = 381;
         static constexpr uint32_t INV = 0xfffcfffdu;  // -p^-1 mod 2^32
         GZK_HD static constexpr uint32_t mod(int i)
         {
@@ -408,13 +410,12 @@ namespace gzk
         }
     }
 
-    // Inverse by the binary extended Euclidean algorithm (shifts and subtractions on
+    // Inverse by the plain binary extended Euclidean algorithm (shifts and subtractions on
     // N limbs, about 2*bits short iterations) followed by one Montgomery product that
-    // restores the Montgomery form.  Roughly five times shorter than the Fermat power
-    // as a dependent chain, which matters because every batch inversion of the library
-    // ends in exactly one serial inversion.  a must be non-zero (0 maps to 0).
+    // restores the Montgomery form.  Kept as a cross-check of inv() below.
+    // a must be non-zero (0 maps to 0).
     template <typename Cfg>
-    GZK_HD Fe<Cfg> inv(const Fe<Cfg>& a)
+    GZK_HD Fe<Cfg> inv_binary(const Fe<Cfg>& a)
     {
         constexpr int N = Cfg::N;
         if (a.is_zero()) return a;
@@ -473,6 +474,263 @@ namespace gzk
 #pragma unroll
         for (int i = 0; i < N; ++i) plain.l[i] = from_u ? x1[i] : x2[i];
         // a = A*R  =>  plain = A^-1 R^-1; Montgomery form of A^-1 is A^-1 R = plain * R^2,
+        // i.e. the Montgomery product of plain with R^3.
+        const Fe<Cfg> r3 = mul(Fe<Cfg>::r2(), Fe<Cfg>::r2());
+        return mul(plain, r3);
+    }
+
+    namespace detail
+    {
+        // out[0..N] = a[0..N-1] * k
+        template <int N>
+        GZK_HD void limbs_mul_word(const uint32_t* a, uint32_t k, uint32_t* out)
+        {
+            uint64_t carry = 0;
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+            {
+                const uint64_t w = static_cast<uint64_t>(a[i]) * k + carry;
+                out[i] = static_cast<uint32_t>(w);
+                carry = w >> 32;
+            }
+            out[N] = static_cast<uint32_t>(carry);
+        }
+
+        // x = |x*f + y*g| / 2^31 for N-limb x, y >= 0 and factors given as sign and
+        // magnitude (magnitude <= 2^31, the division is exact); returns true when
+        // x*f + y*g was negative.  Writes N limbs.
+        template <int N>
+        GZK_HD bool lincomb_shift31(const uint32_t* x, const uint32_t* y, uint32_t f_mag, bool f_neg, uint32_t g_mag, bool g_neg, uint32_t* out)
+        {
+            uint32_t p[N + 1], q[N + 1];
+            limbs_mul_word<N>(x, f_mag, p);
+            limbs_mul_word<N>(y, g_mag, q);
+            bool negative = f_neg;
+            if (f_neg == g_neg)
+            {
+                uint64_t carry = 0;
+#pragma unroll
+                for (int i = 0; i <= N; ++i)
+                {
+                    const uint64_t w = static_cast<uint64_t>(p[i]) + q[i] + carry;
+                    p[i] = static_cast<uint32_t>(w);
+                    carry = w >> 32;
+                }
+            }
+            else
+            {
+                uint64_t borrow = 0;
+#pragma unroll
+                for (int i = 0; i <= N; ++i)
+                {
+                    const uint64_t w = static_cast<uint64_t>(p[i]) - q[i] - borrow;
+                    p[i] = static_cast<uint32_t>(w);
+                    borrow = (w >> 32) & 1u;
+                }
+                if (borrow)
+                {
+                    // |p - q| = q - p: negate the two's complement difference
+                    uint64_t carry = 1;
+#pragma unroll
+                    for (int i = 0; i <= N; ++i)
+                    {
+                        const uint64_t w = static_cast<uint64_t>(~p[i]) + carry;
+                        p[i] = static_cast<uint32_t>(w);
+                        carry = w >> 32;
+                    }
+                    negative = g_neg;
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) out[i] = (p[i] >> 31) | (p[i + 1] << 1);
+            return negative;
+        }
+
+        // u = (u*f + v*g) / 2^31 mod modulus for u, v in [0, modulus]; factors as above.
+        template <typename Cfg>
+        GZK_HD void lincomb_mod_shift31(const uint32_t* u, const uint32_t* v, uint32_t f_mag, bool f_neg, uint32_t g_mag, bool g_neg, uint32_t* out)
+        {
+            constexpr int N = Cfg::N;
+            uint32_t un[N], vn[N];
+            // a negative factor is applied to the negated residue: -f*u = f*(modulus - u)
+            {
+                uint64_t borrow_u = 0, borrow_v = 0;
+#pragma unroll
+                for (int i = 0; i < N; ++i)
+                {
+                    const uint64_t wu = static_cast<uint64_t>(Cfg::mod(i)) - u[i] - borrow_u;
+                    const uint64_t wv = static_cast<uint64_t>(Cfg::mod(i)) - v[i] - borrow_v;
+                    un[i] = f_neg ? static_cast<uint32_t>(wu) : u[i];
+                    vn[i] = g_neg ? static_cast<uint32_t>(wv) : v[i];
+                    borrow_u = (wu >> 32) & 1u;
+                    borrow_v = (wv >> 32) & 1u;
+                }
+            }
+            uint32_t p[N + 1], q[N + 1];
+            limbs_mul_word<N>(un, f_mag, p);
+            limbs_mul_word<N>(vn, g_mag, q);
+            uint64_t carry = 0;
+#pragma unroll
+            for (int i = 0; i <= N; ++i)
+            {
+                const uint64_t w = static_cast<uint64_t>(p[i]) + q[i] + carry;
+                p[i] = static_cast<uint32_t>(w);
+                carry = w >> 32;
+            }
+            // add the multiple of the modulus that clears the low 31 bits (Montgomery step with 2^31)
+            const uint32_t k = (p[0] * Cfg::INV) & 0x7fffffffu;
+            uint32_t km[N + 1];
+            uint32_t mod[N];
+#pragma unroll
+            for (int i = 0; i < N; ++i) mod[i] = Cfg::mod(i);
+            limbs_mul_word<N>(mod, k, km);
+            carry = 0;
+#pragma unroll
+            for (int i = 0; i <= N; ++i)
+            {
+                const uint64_t w = static_cast<uint64_t>(p[i]) + km[i] + carry;
+                p[i] = static_cast<uint32_t>(w);
+                carry = w >> 32;
+            }
+            uint32_t r[N];
+#pragma unroll
+            for (int i = 0; i < N; ++i) r[i] = (p[i] >> 31) | (p[i + 1] << 1);
+            // r < 2 * modulus: one conditional subtraction
+            uint32_t d[N];
+            uint64_t borrow = 0;
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+            {
+                const uint64_t w = static_cast<uint64_t>(r[i]) - Cfg::mod(i) - borrow;
+                d[i] = static_cast<uint32_t>(w);
+                borrow = (w >> 32) & 1u;
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) out[i] = borrow ? r[i] : d[i];
+        }
+    }
+
+    // Inverse by the binary GCD with word-sized approximations (Pornin, "Optimized Binary
+    // GCD for Modular Inversion", 2020): 31 steps of the binary algorithm are run on 64-bit
+    // stand-ins for a and b (their low 31 bits and the 33 bits below the longer one's top)
+    // while the steps are recorded as four small factors; the factors are then applied once
+    // to the full-length a, b and to the cofactors u, v.  ceil((2*bits-1)/31) such rounds
+    // reach a = 0, b = 1, v = 1/value.  The cofactor update divides by 2^31 modulo the
+    // modulus each round, so no correction is left at the end except the Montgomery one.
+    // About four times shorter as a dependent chain than inv_binary(); every batch inversion
+    // of the library ends in exactly one such serial inversion.  a must be non-zero (0 maps to 0).
+    template <typename Cfg>
+    GZK_HD Fe<Cfg> inv(const Fe<Cfg>& value)
+    {
+        constexpr int N = Cfg::N;
+        constexpr int kRounds = (2 * Cfg::BITS - 1 + 30) / 31;
+        if (value.is_zero()) return value;
+        uint32_t a[N], b[N], u[N], v[N];
+#pragma unroll
+        for (int i = 0; i < N; ++i)
+        {
+            a[i] = value.l[i];
+            b[i] = Cfg::mod(i);
+            u[i] = 0;
+            v[i] = 0;
+        }
+        u[0] = 1;
+        for (int round = 0; round < kRounds; ++round)
+        {
+            // 64-bit stand-ins: exact when both fit 64 bits, else low 31 bits + the 33 bits under the common top
+            uint32_t ah = a[1], al = a[0], bh = b[1], bl = b[0];
+            bool wide = false;
+#pragma unroll
+            for (int i = N - 1; i >= 2; --i)
+            {
+                if (!wide && (a[i] | b[i]) != 0)
+                {
+                    ah = a[i];
+                    al = a[i - 1];
+                    bh = b[i];
+                    bl = b[i - 1];
+                    wide = true;
+                }
+            }
+            uint64_t xa = (static_cast<uint64_t>(ah) << 32) | al;
+            uint64_t xb = (static_cast<uint64_t>(bh) << 32) | bl;
+            if (wide)
+            {
+                // leading zeros of the common top limb
+#if defined(__CUDA_ARCH__)
+                const int lead = __clz(static_cast<int>(ah | bh));
+#else
+                uint32_t top = ah | bh;
+                int lead = 0;
+                while ((top & 0x80000000u) == 0)
+                {
+                    top <<= 1;
+                    ++lead;
+                }
+#endif
+                xa = ((xa >> (31 - lead)) << 31) | (a[0] & 0x7fffffffu);
+                xb = ((xb >> (31 - lead)) << 31) | (b[0] & 0x7fffffffu);
+            }
+            int64_t f0 = 1, g0 = 0, f1 = 0, g1 = 1;
+            for (int step = 0; step < 31; ++step)
+            {
+                const bool odd = (xa & 1u) != 0;
+                if (odd && xa < xb)
+                {
+                    const uint64_t tx = xa;
+                    xa = xb;
+                    xb = tx;
+                    int64_t t = f0;
+                    f0 = f1;
+                    f1 = t;
+                    t = g0;
+                    g0 = g1;
+                    g1 = t;
+                }
+                if (odd)
+                {
+                    xa -= xb;
+                    f0 -= f1;
+                    g0 -= g1;
+                }
+                xa >>= 1;
+                f1 <<= 1;
+                g1 <<= 1;
+            }
+            bool f0n = f0 < 0, g0n = g0 < 0, f1n = f1 < 0, g1n = g1 < 0;
+            const uint32_t f0m = static_cast<uint32_t>(f0n ? -f0 : f0), g0m = static_cast<uint32_t>(g0n ? -g0 : g0);
+            const uint32_t f1m = static_cast<uint32_t>(f1n ? -f1 : f1), g1m = static_cast<uint32_t>(g1n ? -g1 : g1);
+            uint32_t na[N], nb[N];
+            if (detail::lincomb_shift31<N>(a, b, f0m, f0n, g0m, g0n, na))
+            {
+                f0n = !f0n;
+                g0n = !g0n;
+            }
+            if (detail::lincomb_shift31<N>(a, b, f1m, f1n, g1m, g1n, nb))
+            {
+                f1n = !f1n;
+                g1n = !g1n;
+            }
+            uint32_t nu[N], nv[N];
+            detail::lincomb_mod_shift31<Cfg>(u, v, f0m, f0n, g0m, g0n, nu);
+            detail::lincomb_mod_shift31<Cfg>(u, v, f1m, f1n, g1m, g1n, nv);
+            uint32_t a_any = 0;
+#pragma unroll
+            for (int i = 0; i < N; ++i)
+            {
+                a[i] = na[i];
+                b[i] = nb[i];
+                u[i] = nu[i];
+                v[i] = nv[i];
+                a_any |= na[i];
+            }
+            if (a_any == 0) break;  // b holds the gcd (1), v its cofactor
+        }
+        Fe<Cfg> plain;  // (value as an integer)^-1 mod modulus
+#pragma unroll
+        for (int i = 0; i < N; ++i) plain.l[i] = v[i];
+        plain = reduce_once(plain);
+        // value = A*R  =>  plain = A^-1 R^-1; the Montgomery form of A^-1 is A^-1 R = plain * R^2,
         // i.e. the Montgomery product of plain with R^3.
         const Fe<Cfg> r3 = mul(Fe<Cfg>::r2(), Fe<Cfg>::r2());
         return mul(plain, r3);

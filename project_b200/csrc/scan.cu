@@ -22,7 +22,7 @@ namespace gzk
 
     namespace
     {
-        constexpr int kThreads = 256;
+        constexpr int kThreads = 128;
         constexpr int kElems = 4;
         constexpr int kChunk = kThreads * kElems;
         constexpr int kWarps = kThreads / 32;

@@ -51,11 +51,40 @@ int check_field(const char* name, std::mt19937_64& rng)
         if (!eq(gzk::add(a, b), (oa + ob).v)) { ++failures; std::printf("%s add mismatch\n", name); }
         if (!eq(gzk::sub(a, b), (oa - ob).v)) { ++failures; std::printf("%s sub mismatch\n", name); }
         if (!eq(gzk::from_mont(a), ca)) { ++failures; std::printf("%s from_mont mismatch\n", name); }
-        if (iter < 400 && !oa.is_zero())
+        if (iter < 6000 && !oa.is_zero())
         {
             if (!eq(gzk::inv(a), oa.inv().v)) { ++failures; std::printf("%s inv mismatch\n", name); }
             if (!eq(gzk::inv_fermat(a), oa.inv().v)) { ++failures; std::printf("%s fermat inv mismatch\n", name); }
+            if (!eq(gzk::inv_binary(a), oa.inv().v)) { ++failures; std::printf("%s binary inv mismatch\n", name); }
             if (!eq(gzk::pow_u64(a, 0x123456789abcdefULL + iter), oa.pow(0x123456789abcdefULL + iter).v)) { ++failures; std::printf("%s pow mismatch\n", name); }
+        }
+        if (failures > 5) return failures;
+    }
+    // inversion of sparse values: single bits, and the modulus minus a single bit, taken as
+    // Montgomery representations directly (any residue is one)
+    for (int bit = 0; bit < Cfg::BITS; ++bit)
+    {
+        for (int variant = 0; variant < 2; ++variant)
+        {
+            oracle::BigInt<N64> c{};
+            c.w[bit / 64] = 1ULL << (bit % 64);
+            if (variant == 1)
+            {
+                oracle::BigInt<N64> m = OFe::P().modulus, d{};
+                unsigned __int128 borrow = 0;
+                for (int i = 0; i < N64; ++i)
+                {
+                    const unsigned __int128 w = static_cast<unsigned __int128>(m.w[i]) - c.w[i] - borrow;
+                    d.w[i] = static_cast<uint64_t>(w);
+                    borrow = (w >> 64) & 1;
+                }
+                c = d;
+            }
+            if (oracle::cmp(c, OFe::P().modulus) >= 0) continue;
+            OFe o;
+            o.v = c;
+            if (o.is_zero()) continue;
+            if (!eq(gzk::inv(to_dev(c)), o.inv().v)) { ++failures; std::printf("%s sparse inv mismatch (bit %d, variant %d)\n", name, bit, variant); }
         }
         if (failures > 5) return failures;
     }
