@@ -131,6 +131,64 @@ namespace gzk
             }
             store_xyzz(out + i, acc);
         }
+
+        // The same sum with the 32 windows of a scalar dealt to kLanes adjacent lanes
+        // (kWindows / kLanes mixed additions each) and the lane sums combined by a shuffle
+        // tree of full additions.  A batch of a few hundred scalars (the columns of one
+        // commit barrier) is bound by the length of the dependent chain, not by
+        // throughput: 4 mixed + 3 full additions instead of 32 mixed ones.
+        constexpr int kLanes = 8;
+        __device__ __forceinline__ G1Xyzz shfl_down_xyzz(const G1Xyzz& p, int offset)
+        {
+            G1Xyzz o;
+#pragma unroll
+            for (int i = 0; i < FpCfg::N; ++i)
+            {
+                o.X.l[i] = __shfl_down_sync(0xffffffffu, p.X.l[i], offset, kLanes);
+                o.Y.l[i] = __shfl_down_sync(0xffffffffu, p.Y.l[i], offset, kLanes);
+                o.ZZ.l[i] = __shfl_down_sync(0xffffffffu, p.ZZ.l[i], offset, kLanes);
+                o.ZZZ.l[i] = __shfl_down_sync(0xffffffffu, p.ZZZ.l[i], offset, kLanes);
+            }
+            return o;
+        }
+        __global__ void __launch_bounds__(kThreads) fixed_base_mul_lanes_kernel(const G1Affine* table, ColRef scalars, size_t count, G1Xyzz* out)
+        {
+            const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            const size_t i = t / kLanes;
+            const int part = static_cast<int>(t % kLanes);
+            const size_t i_load = i < count ? i : count - 1;  // idle lanes keep the warp's shuffles whole
+            Fr s = load_fr(static_cast<const Fr*>(scalars.ptr) + i_load);
+            if (scalars.kind == GZK_KIND_FR_MONT) s = from_mont(s);
+            G1Xyzz acc = G1Xyzz::infinity();
+#pragma unroll 1
+            for (int w = part * (kWindows / kLanes); w < (part + 1) * (kWindows / kLanes); ++w)
+            {
+                const uint32_t digit = (s.l[w >> 2] >> ((w & 3) * 8)) & 0xffu;
+                if (digit != 0) acc = g1_add_mixed(acc, load_affine(table + w * kEntries + (digit - 1)));
+            }
+#pragma unroll 1
+            for (int offset = kLanes / 2; offset > 0; offset >>= 1)
+            {
+                const G1Xyzz other = shfl_down_xyzz(acc, offset);
+                if (part < offset) acc = g1_add(acc, other);
+            }
+            if (part == 0 && i < count) store_xyzz(out + i, acc);
+        }
+
+        // Sum over the 32 byte-windows of every scalar: lane-split for chain-bound batch sizes.
+        void launch_fixed_base_mul(gzk_ctx* ctx, const G1Affine* table, const ColRef& s, size_t count, G1Xyzz* xyzz)
+        {
+            static_assert(kWindows % kLanes == 0 && 32 % kLanes == 0, "lanes must divide the windows and the warp");
+            if (count < 16384)
+            {
+                const size_t threads = count * kLanes;
+                fixed_base_mul_lanes_kernel<<<static_cast<unsigned>((threads + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(table, s, count, xyzz);
+            }
+            else
+            {
+                fixed_base_mul_kernel<<<static_cast<unsigned>((count + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(table, s, count, xyzz);
+            }
+        }
     }
 
     // Converts `count` XYZZ points to affine (Montgomery coordinates in `out_mont`, or
@@ -277,7 +335,7 @@ extern "C"
         s.kind = scalars->kind;
         {
             LaunchScope scope(ctx, "g1_fixed_base_mul");
-            fixed_base_mul_kernel<<<static_cast<unsigned>((count + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(table, s, count, xyzz);
+            launch_fixed_base_mul(ctx, table, s, count, xyzz);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         if ((rc = launch_xyzz_to_affine(ctx, xyzz, count, z, static_cast<G1Affine*>(out->dptr), false)) != GZK_OK) return rc;
@@ -313,7 +371,7 @@ extern "C"
         s.kind = GZK_KIND_FR;
         {
             LaunchScope scope(ctx, "g1_fixed_base_mul");
-            fixed_base_mul_kernel<<<static_cast<unsigned>((count + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(table, s, count, xyzz);
+            launch_fixed_base_mul(ctx, table, s, count, xyzz);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         if ((rc = launch_xyzz_to_affine(ctx, xyzz, count, z, affine, true)) != GZK_OK) return rc;
