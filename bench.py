@@ -362,20 +362,61 @@ def main():
 
     one_at_a_time = [False]  # set for the pass that times each kernel by itself
 
-    def step_evaluations():
-        # The reference evaluates its seven domains from seven concurrent host tasks
-        # (one std::async per domain bundle); on one GPU the domains are dealt to the worker
-        # contexts the same way, so the launch and read-back latencies of the small domains
-        # hide behind the kernels of the large ones.  With several ranks every evaluation
-        # ends in a collective, which has to be issued in one order on every rank: sequential.
-        if pool is None or world > 1 or one_at_a_time[0]:
-            return [step_domain(d) for d in domains]
+    def local_eval(d, weights, length, rotations, w):
+        if world == 1:
+            return w.eval_batch(d["cols"], length, d["lg"], weights, rotations)
+        local_len = max(0, min(length - d["begin"], d["rows"]))
+        return w.eval_batch_range(d["cols"], local_len, d["begin"], d["lg"], weights, d["w_first"], rotations)
+
+    def phase(fn):
+        """fn(domain, worker context) over all domains -> {domain name: result}.  The reference
+        evaluates its seven domains from seven concurrent host tasks (one std::async per domain
+        bundle); here the domains are dealt to the worker contexts the same way, so the launch
+        and read-back latencies of the small domains hide behind the kernels of the large ones."""
+        if pool is None or one_at_a_time[0]:
+            return {d["name"]: fn(d, be) for d in domains}
 
         def run_group(t):
-            return [step_domain(d, workers[t]) for d in domain_groups[t]]
+            return [(d["name"], fn(d, workers[t])) for d in domain_groups[t]]
 
-        futures = [pool.submit(run_group, t) for t in range(n_workers)]
-        return [f.result() for f in futures]
+        out = {}
+        for f in [pool.submit(run_group, t) for t in range(n_workers)]:
+            out.update(f.result())
+        return out
+
+    def gather_all(parts):
+        """One all-gather per protocol barrier: the partial sums of every domain travel together
+        (K*P*32 bytes per domain) and are added mod r; issued from the main thread only."""
+        if world == 1:
+            return parts
+        names = [d["name"] for d in domains]
+        flat = np.concatenate([parts[name].reshape(-1, 32) for name in names])
+        summed = gather_sum(flat)
+        out, at = {}, 0
+        for name in names:
+            count = parts[name].size // 32
+            out[name] = summed[at:at + count].reshape(parts[name].shape)
+            at += count
+        return out
+
+    def step_evaluations():
+        # barrier 1: tau-evaluations of every column (valid prefix), then the commitments [p_k(tau)] G
+        tau_evals = gather_all(phase(lambda d, w: local_eval(d, d["w_tau"], d["valid"], (0,), w)))
+        commits = phase(lambda d, w: w.g1_mul_same_base(G, tau_evals[d["name"]][0]))
+        # barrier 2: quotient evaluations at {tau, omega*tau}
+        quotient = gather_all(phase(lambda d, w: local_eval(d, d["w_tau"], d["n"], (0, 1), w)))
+        # barrier 3: fresh weights at the challenge z, openings at {z, omega*z}
+        z = challenge()
+
+        def open_domain(d, w):
+            if world == 1:
+                w.bary_weights(d["lg"], z, out=d["w_z"])
+            else:
+                w.bary_weights_range(d["lg"], z, d["w_first"], d["w_count"], out=d["w_z"])
+            return local_eval(d, d["w_z"], d["n"], (0, 1), w)
+
+        opened = gather_all(phase(open_domain))
+        return commits, quotient, opened
 
     # The reference builds the columns of a proof from concurrent host tasks (std::async per
     # head / per column); the same shape here: a few host threads, each with its own context
@@ -487,7 +528,7 @@ def main():
     # side by side, so a kernel's event-to-event time there includes its neighbours.  The
     # roofline needs the kernel by itself: the same steps once more, issued from one thread.
     iso_steps = args.steps
-    if n_workers > 1 and world == 1:
+    if n_workers > 1:
         one_at_a_time[0] = True
         iso_steps = max(1, min(args.steps, 3))
         _, report, _ = timed(step_resident, iso_steps, 1)
@@ -580,7 +621,7 @@ def main():
             "ms_per_step": ms_per_step, "higher_is_better": False, "scaling": "strong", "vs_baseline": None,
             "dtype": "u32x8 Montgomery Fr / u32x12 Fp (BLS12-381)", "data": "synthetic",
             "config": {"workload": wl_name, "l2": "inputs larger than L2 (5.3 GB edge columns, 2.7 GB FH columns per pass)",
-                       "sharding": f"rows of every domain split across {world} rank(s); per-call all-gather of the partial sums (K*P*32 B) over NCCL; "
+                       "sharding": f"rows of every domain split across {world} rank(s); one all-gather of the partial sums (K*P*32 B per domain) over NCCL at each of the 3 protocol barriers; "
                                    f"builder heads dealt round-robin",
                        "builder_threads": n_workers},
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches,
