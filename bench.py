@@ -678,6 +678,29 @@ def run_sweep(be, rng, G, stream, small=False):
     out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6}
     for b in (scalars, points, vec, res):
         b.free()
+    # fp64 forward of one attention head at the mid-size graph's shape (time only: not a roofline target)
+    from project_b200 import KIND_F64, KIND_U32, incoming_lists
+
+    nodes, inner, width, directed = (512, 32, 8, 2000) if small else (19717, 500, 8, 88648)
+    src = np.concatenate([rng.integers(0, nodes, size=directed), np.arange(nodes)]).astype(np.uint32)
+    dst = np.concatenate([rng.integers(0, nodes, size=directed), np.arange(nodes)]).astype(np.uint32)
+    order = np.argsort(dst, kind="stable")
+    src, dst = src[order], dst[order]
+    ptr, inc = incoming_lists(src, dst, nodes)
+    feats = rng.exponential(1.0, size=(nodes, inner)) * (rng.random((nodes, inner)) < 0.1)
+    up = lambda a, kind: be.upload(np.ascontiguousarray(a).reshape(-1), kind)
+    args = (up(feats, KIND_F64), up(rng.uniform(-0.1, 0.1, size=(inner, width)), KIND_F64), up(rng.uniform(-1, 1, size=width), KIND_F64), 0.0,
+            up(rng.uniform(-1, 1, size=width), KIND_F64), 0.0, up(np.zeros(width), KIND_F64), True, up(src, KIND_U32), up(dst, KIND_U32),
+            nodes, inner, width, up(ptr, KIND_U32), up(inc, KIND_U32))
+
+    trace = be.gat_head_forward(*args)
+
+    def forward():
+        be.gat_head_forward(*args, out=trace)
+        be.synchronize()
+
+    ms = timed_ms(forward)
+    out["head_forward_fp64"] = {"nodes": nodes, "edges": int(src.size), "input_width": inner, "output_width": width, "ms": ms}
     return out
 
 

@@ -40,7 +40,7 @@ extern "C" {
 #define GZK_KIND_FR_MONT 1
 #define GZK_KIND_I64 2
 #define GZK_KIND_U32 3
-#define GZK_KIND_F64 4   /* IEEE doubles: input of gzk_quantize only */
+#define GZK_KIND_F64 4   /* IEEE doubles: the fp64 forward pass and the input of gzk_quantize */
 #define GZK_KIND_G1 5    /* affine G1 points, 96 bytes; wire format on upload/download, Montgomery on the device */
 
 typedef struct gzk_ctx gzk_ctx;
@@ -242,6 +242,63 @@ int gzk_g1_mul_same_base(gzk_ctx* ctx, const uint8_t base[96], const uint8_t* sc
 int gzk_g1_fixed_base_mul(gzk_ctx* ctx, const uint8_t base[96], const gzk_buf* scalars, size_t count, gzk_buf* out);
 int gzk_commit_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n, const gzk_buf* weights_tau,
                      const uint8_t base[96], uint8_t* tau_evals_out, uint8_t* points_out);
+
+/* ---- fp64 forward pass of one attention head -----------------------------------------------------
+ * Replaces attention_head_forward_impl (src/model/gat.cpp:474-615, with matmul / matvec /
+ * leaky_relu / elu of :354-401): H' = X W, the two score vectors, per destination node the
+ * softmax statistics M / Sum / inv and the alpha-weighted aggregation over its incoming
+ * edges, the per-edge columns S, Z, Delta, U, alpha, and H_agg = ELU(H_agg_pre + bias).
+ * Every sum runs serially in index order with separate multiply and add, as on the host,
+ * so H', E_src, E_dst, S, Z, M, Delta are bit-identical to the reference; U, Sum, inv, alpha
+ * and H_agg inherit the last-place behaviour of the CUDA exp / expm1.
+ * The incoming list (incoming_ptr[node_count+1], incoming_src[incoming_count]) holds, per
+ * destination node, its sources in edge order followed by the node itself when the edges
+ * carry no self loop - the `incoming_sources` the reference builds on the host
+ * (gat.cpp:521-538); edge_src / edge_dst are the edges in their original order.
+ * All matrices are row-major F64 buffers; index lists are U32 buffers.  Outputs marked
+ * optional may be NULL.  Errors: GZK_E_INVALID for an endpoint out of range (the
+ * reference throws "edge out of bounds while running attention head forward"). */
+typedef struct gzk_gat_head
+{
+    const gzk_buf* features;         /* node_count x input_width */
+    uint32_t input_width;
+    uint32_t output_width;
+    const gzk_buf* seq_kernel;       /* input_width x output_width */
+    const gzk_buf* attn_src_kernel;  /* output_width */
+    const gzk_buf* attn_dst_kernel;  /* output_width */
+    double attn_src_bias;
+    double attn_dst_bias;
+    const gzk_buf* output_bias;      /* output_bias_count entries, or NULL (apply_output_bias = false) */
+    size_t output_bias_count;
+    int apply_activation;            /* ELU on the output when non-zero */
+} gzk_gat_head;
+typedef struct gzk_gat_graph
+{
+    size_t node_count;
+    size_t edge_count;
+    const gzk_buf* edge_src;         /* edge_count */
+    const gzk_buf* edge_dst;         /* edge_count */
+    size_t incoming_count;
+    const gzk_buf* incoming_ptr;     /* node_count + 1 */
+    const gzk_buf* incoming_src;     /* incoming_count */
+} gzk_gat_graph;
+typedef struct gzk_gat_trace
+{
+    gzk_buf* H_prime;                /* node_count x output_width */
+    gzk_buf* E_src;                  /* node_count */
+    gzk_buf* E_dst;                  /* node_count */
+    gzk_buf* M;                      /* node_count */
+    gzk_buf* Sum;                    /* node_count */
+    gzk_buf* inv;                    /* node_count */
+    gzk_buf* S;                      /* edge_count, optional */
+    gzk_buf* Z;                      /* edge_count, optional */
+    gzk_buf* Delta;                  /* edge_count, optional */
+    gzk_buf* U;                      /* edge_count, optional */
+    gzk_buf* alpha;                  /* edge_count, optional */
+    gzk_buf* H_agg_pre_bias;         /* node_count x output_width, optional */
+    gzk_buf* H_agg;                  /* node_count x output_width, optional */
+} gzk_gat_trace;
+int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, const gzk_gat_graph* graph, const gzk_gat_trace* out);
 
 /* ---- MSM (kernel sweep; honest-prover commitment) ----------------------------------------------
  * gzk_msm: out = sum_i [scalars[i]] points[i]; scalars FR or FR_MONT, points a G1

@@ -16,6 +16,7 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <limits>
 #include <functional>
 #include <string>
 #include <thread>
@@ -582,6 +583,80 @@ extern "C"
                         break;
                     }
             store_fr(s, out);
+        });
+    }
+
+    // ---- a10: fp64 forward pass of one attention head ----------------------------------
+    // gat.cpp:474-615 (attention_head_forward_impl) with matmul :366-391, matvec :394-405,
+    // leaky_relu :354-357, elu :360-363.  Row-major arrays; `has_bias` mirrors
+    // apply_output_bias; outputs as the fields of HeadForwardTrace.  Every loop keeps the
+    // reference's order (k-ascending products, incoming sources in edge order with the node
+    // itself appended when it has no self loop), so the results carry the same roundings.
+    int ora_gat_head_forward(const double* features, std::size_t nodes, std::size_t inner, const double* seq_kernel, std::size_t width,
+                             const double* attn_src, double bias_src, const double* attn_dst, double bias_dst, const double* out_bias,
+                             std::size_t out_bias_count, int has_bias, int apply_activation, const std::uint32_t* edge_src,
+                             const std::uint32_t* edge_dst, std::size_t edges, double* H_prime, double* E_src, double* E_dst, double* S, double* Z,
+                             double* M, double* Delta, double* U, double* Sum, double* inv, double* alpha, double* H_agg_pre, double* H_agg)
+    {
+        return guarded([&] {
+            auto leaky = [](double v) { return v >= 0.0 ? v : 0.2 * v; };
+            for (std::size_t e = 0; e < edges; ++e)
+                if (edge_src[e] >= nodes || edge_dst[e] >= nodes) throw std::runtime_error("edge out of bounds while running attention head forward");
+            for (std::size_t i = 0; i < nodes * width; ++i) H_prime[i] = 0.0;
+            for (std::size_t i = 0; i < nodes; ++i)
+                for (std::size_t k = 0; k < inner; ++k)
+                {
+                    const double lhs = features[i * inner + k];
+                    for (std::size_t j = 0; j < width; ++j) H_prime[i * width + j] += lhs * seq_kernel[k * width + j];
+                }
+            for (std::size_t i = 0; i < nodes; ++i)
+            {
+                E_dst[i] = bias_dst;
+                E_src[i] = bias_src;
+                for (std::size_t c = 0; c < width; ++c)
+                {
+                    E_dst[i] += H_prime[i * width + c] * attn_dst[c];
+                    E_src[i] += H_prime[i * width + c] * attn_src[c];
+                }
+            }
+            std::vector<std::vector<std::size_t>> incoming(nodes);
+            for (std::size_t e = 0; e < edges; ++e) incoming[edge_dst[e]].push_back(edge_src[e]);
+            for (std::size_t d = 0; d < nodes; ++d)
+                if (std::find(incoming[d].begin(), incoming[d].end(), d) == incoming[d].end()) incoming[d].push_back(d);
+            for (std::size_t d = 0; d < nodes; ++d)
+            {
+                M[d] = -std::numeric_limits<double>::infinity();
+                for (const auto s : incoming[d]) M[d] = std::max(M[d], leaky(E_dst[d] + E_src[s]));
+            }
+            for (std::size_t d = 0; d < nodes; ++d)
+            {
+                Sum[d] = 0.0;
+                for (const auto s : incoming[d]) Sum[d] += std::exp(leaky(E_dst[d] + E_src[s]) - M[d]);
+            }
+            for (std::size_t d = 0; d < nodes; ++d) inv[d] = 1.0 / Sum[d];
+            for (std::size_t i = 0; i < nodes * width; ++i) H_agg_pre[i] = 0.0;
+            for (std::size_t d = 0; d < nodes; ++d)
+                for (const auto s : incoming[d])
+                {
+                    const double a = std::exp(leaky(E_dst[d] + E_src[s]) - M[d]) * inv[d];
+                    for (std::size_t c = 0; c < width; ++c) H_agg_pre[d * width + c] += a * H_prime[s * width + c];
+                }
+            for (std::size_t e = 0; e < edges; ++e)
+            {
+                const std::size_t s = edge_src[e], d = edge_dst[e];
+                S[e] = E_dst[d] + E_src[s];
+                Z[e] = leaky(S[e]);
+                Delta[e] = M[d] - Z[e];
+                U[e] = std::exp(Z[e] - M[d]);
+                alpha[e] = U[e] * inv[d];
+            }
+            for (std::size_t d = 0; d < nodes; ++d)
+                for (std::size_t c = 0; c < width; ++c)
+                {
+                    double v = H_agg_pre[d * width + c];
+                    if (has_bias && c < out_bias_count) v += out_bias[c];
+                    H_agg[d * width + c] = apply_activation ? (v >= 0.0 ? v : std::expm1(v)) : v;
+                }
         });
     }
 

@@ -6,5 +6,5 @@ operator interface under project_b200/host/.  This Python package only loads
 the library through ctypes for tests and benchmarks; it holds no compute path
 of its own and raises if the CUDA library is missing.
 """
-from .lib import fr_sum, g1_sum, shard_rows  # noqa: F401
+from .lib import fr_sum, g1_sum, incoming_lists, shard_rows  # noqa: F401
 from .lib import Backend, Buffer, GzkError, load_library, KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, KIND_F64, KIND_G1  # noqa: F401

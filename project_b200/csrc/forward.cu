@@ -1,0 +1,230 @@
+// fp64 forward pass of one attention head (the witness the prover quantises):
+//   H' = X W;  e_src = H' a_src + b_src;  e_dst = H' a_dst + b_dst;
+//   per destination node over its incoming edges (in the order given):
+//     M = max LeakyReLU(e_dst + e_src),  Sum = sum exp(LeakyReLU(.) - M),  inv = 1/Sum,
+//     H_agg_pre = sum alpha * H'[src],  alpha = exp(LeakyReLU(.) - M) * inv;
+//   per edge: S, Z = LeakyReLU(S), Delta = M - Z, U = exp(Z - M), alpha = U * inv;
+//   H_agg = ELU(H_agg_pre + bias).
+//
+// The reference computes every sum serially in index order with separate multiply and
+// add; so do these kernels (one thread owns one sum, __dmul_rn / __dadd_rn so that no
+// fused multiply-add is formed), which makes H', e_src, e_dst, S, Z, M and Delta
+// bit-identical to the host computation.  exp and expm1 come from the CUDA math
+// library and may differ from the host's in the last unit; everything downstream of
+// them (U, Sum, inv, alpha, H_agg) is equal to within a few units in the last place.
+//
+// Parallelism: rows x output columns for the projection, one thread per node for the
+// score vectors and the softmax statistics, one thread per (node, column) for the
+// aggregation, one per edge for the edge columns.  The incoming edges of a node are a
+// CSR list built by the caller (the host builds it in the reference too).
+#include <cmath>
+
+#include "common.cuh"
+
+namespace gzk
+{
+    namespace
+    {
+        constexpr int kThreads = 256;
+
+        __device__ __forceinline__ double leaky_relu(double v) { return v >= 0.0 ? v : __dmul_rn(0.2, v); }
+
+        // out[i][j] = sum_k x[i][k] * w[k][j], k ascending (one thread per output)
+        __global__ void __launch_bounds__(kThreads) project_kernel(const double* x, const double* w, uint64_t rows, uint32_t inner, uint32_t width,
+                                                                   double* out)
+        {
+            const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (idx >= rows * width) return;
+            const uint64_t i = idx / width;
+            const uint32_t j = static_cast<uint32_t>(idx - i * width);
+            const double* xr = x + i * inner;
+            double acc = 0.0;
+            for (uint32_t k = 0; k < inner; ++k) acc = __dadd_rn(acc, __dmul_rn(xr[k], __ldg(w + static_cast<uint64_t>(k) * width + j)));
+            out[idx] = acc;
+        }
+
+        // e[i] = bias + sum_c h[i][c] * a[c], c ascending; both score vectors in one pass
+        __global__ void __launch_bounds__(kThreads) scores_kernel(const double* h, uint64_t rows, uint32_t width, const double* a_src, double b_src,
+                                                                  const double* a_dst, double b_dst, double* e_src, double* e_dst)
+        {
+            const uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (i >= rows) return;
+            const double* hr = h + i * width;
+            double s = b_src, d = b_dst;
+            for (uint32_t c = 0; c < width; ++c)
+            {
+                const double v = hr[c];
+                s = __dadd_rn(s, __dmul_rn(v, __ldg(a_src + c)));
+                d = __dadd_rn(d, __dmul_rn(v, __ldg(a_dst + c)));
+            }
+            e_src[i] = s;
+            e_dst[i] = d;
+        }
+
+        // M, Sum, inv of every destination node over its incoming list
+        __global__ void __launch_bounds__(kThreads) softmax_stats_kernel(const double* e_src, const double* e_dst, const uint32_t* in_ptr,
+                                                                         const uint32_t* in_src, uint64_t nodes, double* m_out, double* sum_out,
+                                                                         double* inv_out)
+        {
+            const uint64_t dst = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (dst >= nodes) return;
+            const uint32_t begin = in_ptr[dst], end = in_ptr[dst + 1];
+            const double ed = e_dst[dst];
+            double m = -INFINITY;
+            for (uint32_t p = begin; p < end; ++p) m = fmax(m, leaky_relu(__dadd_rn(ed, e_src[in_src[p]])));
+            double sum = 0.0;
+            for (uint32_t p = begin; p < end; ++p) sum = __dadd_rn(sum, exp(__dsub_rn(leaky_relu(__dadd_rn(ed, e_src[in_src[p]])), m)));
+            m_out[dst] = m;
+            sum_out[dst] = sum;
+            inv_out[dst] = __ddiv_rn(1.0, sum);
+        }
+
+        // H_agg_pre[dst][c] = sum over incoming src of alpha * H'[src][c]; H_agg = act(H_agg_pre + bias)
+        __global__ void __launch_bounds__(kThreads) aggregate_kernel(const double* h, const double* e_src, const double* e_dst, const double* m_in,
+                                                                     const double* inv_in, const uint32_t* in_ptr, const uint32_t* in_src,
+                                                                     uint64_t nodes, uint32_t width, const double* out_bias, uint32_t bias_count,
+                                                                     int apply_activation, double* pre_out, double* agg_out)
+        {
+            const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (idx >= nodes * width) return;
+            const uint64_t dst = idx / width;
+            const uint32_t c = static_cast<uint32_t>(idx - dst * width);
+            const uint32_t begin = in_ptr[dst], end = in_ptr[dst + 1];
+            const double ed = e_dst[dst], m = m_in[dst], inv = inv_in[dst];
+            double acc = 0.0;
+            for (uint32_t p = begin; p < end; ++p)
+            {
+                const uint32_t src = in_src[p];
+                const double alpha = __dmul_rn(exp(__dsub_rn(leaky_relu(__dadd_rn(ed, e_src[src])), m)), inv);
+                acc = __dadd_rn(acc, __dmul_rn(alpha, h[static_cast<uint64_t>(src) * width + c]));
+            }
+            if (pre_out != nullptr) pre_out[idx] = acc;
+            double v = acc;
+            if (out_bias != nullptr && c < bias_count) v = __dadd_rn(v, out_bias[c]);
+            if (agg_out != nullptr) agg_out[idx] = apply_activation ? (v >= 0.0 ? v : expm1(v)) : v;
+        }
+
+        __global__ void __launch_bounds__(kThreads) edge_columns_kernel(const double* e_src, const double* e_dst, const double* m_in, const double* inv_in,
+                                                                        const uint32_t* src, const uint32_t* dst, uint64_t edges, uint64_t nodes,
+                                                                        double* s_out, double* z_out, double* delta_out, double* u_out,
+                                                                        double* alpha_out, int* status)
+        {
+            const uint64_t e = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (e >= edges) return;
+            const uint32_t a = src[e], b = dst[e];
+            if (a >= nodes || b >= nodes)
+            {
+                atomicExch(status, GZK_E_INVALID);
+                return;
+            }
+            const double s = __dadd_rn(e_dst[b], e_src[a]);
+            const double z = leaky_relu(s);
+            const double u = exp(__dsub_rn(z, m_in[b]));
+            if (s_out != nullptr) s_out[e] = s;
+            if (z_out != nullptr) z_out[e] = z;
+            if (delta_out != nullptr) delta_out[e] = __dsub_rn(m_in[b], z);
+            if (u_out != nullptr) u_out[e] = u;
+            if (alpha_out != nullptr) alpha_out[e] = __dmul_rn(u, inv_in[b]);
+        }
+
+        __global__ void __launch_bounds__(kThreads) check_incoming_kernel(const uint32_t* in_ptr, const uint32_t* in_src, uint64_t nodes, uint64_t in_count,
+                                                                          int* status)
+        {
+            const uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (i < nodes && (in_ptr[i] > in_ptr[i + 1] || in_ptr[i + 1] > in_count)) atomicExch(status, GZK_E_INVALID);
+            if (i == 0 && in_ptr[0] != 0) atomicExch(status, GZK_E_INVALID);
+            if (i < in_count && in_src[i] >= nodes) atomicExch(status, GZK_E_INVALID);
+        }
+
+        bool f64_ok(const gzk_buf* b, uint64_t need) { return b != nullptr && b->kind == GZK_KIND_F64 && b->count >= need; }
+        bool f64_opt(const gzk_buf* b, uint64_t need) { return b == nullptr || f64_ok(b, need); }
+        bool u32_ok(const gzk_buf* b, uint64_t need) { return b != nullptr && b->kind == GZK_KIND_U32 && b->count >= need; }
+        double* f64_ptr(const gzk_buf* b) { return b == nullptr ? nullptr : static_cast<double*>(b->dptr); }
+        unsigned grid_for(uint64_t work) { return static_cast<unsigned>((work + kThreads - 1) / kThreads); }
+    }
+}
+
+using namespace gzk;
+
+extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, const gzk_gat_graph* graph, const gzk_gat_trace* out)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (head == nullptr || graph == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "gat_head_forward: null argument");
+    const uint64_t nodes = graph->node_count, edges = graph->edge_count, in_count = graph->incoming_count;
+    const uint32_t inner = head->input_width, width = head->output_width;
+    if (nodes == 0) return GZK_OK;
+    if (inner == 0 || width == 0) return fail(ctx, GZK_E_INVALID, "gat_head_forward: empty weight matrix");
+    if (nodes > 0xfffffffeULL || in_count > 0xffffffffULL || nodes * width > (1ULL << 40)) return fail(ctx, GZK_E_INVALID, "gat_head_forward: graph too large");
+    if (!f64_ok(head->features, nodes * inner) || !f64_ok(head->seq_kernel, static_cast<uint64_t>(inner) * width) ||
+        !f64_ok(head->attn_src_kernel, width) || !f64_ok(head->attn_dst_kernel, width))
+        return fail(ctx, GZK_E_INVALID, "gat_head_forward: feature / weight buffers must be F64 buffers of the stated shapes");
+    if (head->output_bias != nullptr && !f64_ok(head->output_bias, head->output_bias_count)) return fail(ctx, GZK_E_INVALID, "gat_head_forward: bad output bias buffer");
+    if ((edges != 0 && (!u32_ok(graph->edge_src, edges) || !u32_ok(graph->edge_dst, edges))) || !u32_ok(graph->incoming_ptr, nodes + 1) ||
+        (in_count != 0 && !u32_ok(graph->incoming_src, in_count)))
+        return fail(ctx, GZK_E_INVALID, "gat_head_forward: edge lists must be U32 buffers (incoming_ptr has node_count + 1 entries)");
+    if (!f64_ok(out->H_prime, nodes * width) || !f64_ok(out->E_src, nodes) || !f64_ok(out->E_dst, nodes) || !f64_ok(out->M, nodes) ||
+        !f64_ok(out->Sum, nodes) || !f64_ok(out->inv, nodes))
+        return fail(ctx, GZK_E_INVALID, "gat_head_forward: H_prime, E_src, E_dst, M, Sum and inv outputs are required F64 buffers");
+    if (!f64_opt(out->S, edges) || !f64_opt(out->Z, edges) || !f64_opt(out->Delta, edges) || !f64_opt(out->U, edges) || !f64_opt(out->alpha, edges) ||
+        !f64_opt(out->H_agg_pre_bias, nodes * width) || !f64_opt(out->H_agg, nodes * width))
+        return fail(ctx, GZK_E_INVALID, "gat_head_forward: optional outputs must be F64 buffers of the stated shapes");
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    int rc = begin_call(ctx);
+    if (rc != GZK_OK) return rc;
+    const uint32_t* in_ptr = static_cast<const uint32_t*>(graph->incoming_ptr->dptr);
+    const uint32_t* in_src = in_count != 0 ? static_cast<const uint32_t*>(graph->incoming_src->dptr) : nullptr;
+    {
+        LaunchScope scope(ctx, "forward_check");
+        check_incoming_kernel<<<grid_for(nodes > in_count ? nodes : in_count), kThreads, 0, ctx->stream>>>(in_ptr, in_src, nodes, in_count, ctx->d_status);
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    // the lists are read by the kernels below: settle their validity first
+    {
+        int status = 0;
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        if (status == GZK_E_INVALID)
+        {
+            GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+            return fail(ctx, GZK_E_INVALID, "edge out of bounds while running attention head forward");
+        }
+    }
+    {
+        LaunchScope scope(ctx, "forward_project");
+        project_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(f64_ptr(head->features), f64_ptr(head->seq_kernel), nodes, inner, width,
+                                                                              f64_ptr(out->H_prime));
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    {
+        LaunchScope scope(ctx, "forward_scores");
+        scores_kernel<<<grid_for(nodes), kThreads, 0, ctx->stream>>>(f64_ptr(out->H_prime), nodes, width, f64_ptr(head->attn_src_kernel), head->attn_src_bias,
+                                                                     f64_ptr(head->attn_dst_kernel), head->attn_dst_bias, f64_ptr(out->E_src),
+                                                                     f64_ptr(out->E_dst));
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    {
+        LaunchScope scope(ctx, "forward_softmax_stats");
+        softmax_stats_kernel<<<grid_for(nodes), kThreads, 0, ctx->stream>>>(f64_ptr(out->E_src), f64_ptr(out->E_dst), in_ptr, in_src, nodes, f64_ptr(out->M),
+                                                                            f64_ptr(out->Sum), f64_ptr(out->inv));
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    if (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr)
+    {
+        LaunchScope scope(ctx, "forward_aggregate");
+        aggregate_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(
+            f64_ptr(out->H_prime), f64_ptr(out->E_src), f64_ptr(out->E_dst), f64_ptr(out->M), f64_ptr(out->inv), in_ptr, in_src, nodes, width,
+            f64_ptr(head->output_bias), head->output_bias != nullptr ? static_cast<uint32_t>(head->output_bias_count) : 0u, head->apply_activation,
+            f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg));
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    if (edges != 0 && (out->S != nullptr || out->Z != nullptr || out->Delta != nullptr || out->U != nullptr || out->alpha != nullptr))
+    {
+        LaunchScope scope(ctx, "forward_edge_columns");
+        edge_columns_kernel<<<grid_for(edges), kThreads, 0, ctx->stream>>>(
+            f64_ptr(out->E_src), f64_ptr(out->E_dst), f64_ptr(out->M), f64_ptr(out->inv), static_cast<const uint32_t*>(graph->edge_src->dptr),
+            static_cast<const uint32_t*>(graph->edge_dst->dptr), edges, nodes, f64_ptr(out->S), f64_ptr(out->Z), f64_ptr(out->Delta), f64_ptr(out->U),
+            f64_ptr(out->alpha), ctx->d_status);
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    return finish_call(ctx, "edge out of bounds while running attention head forward");
+}

@@ -10,6 +10,7 @@
 // Columns live on the GPU; only scalars, commitments and opened values come back.
 #pragma once
 
+#include <algorithm>
 #include <array>
 #include <cstdint>
 #include <cstring>
@@ -454,6 +455,134 @@ namespace gatzk_b200
             std::uint8_t mu[32];
             ctx.check(gzk_zkmap_accumulator(ctx.raw(), a_values.raw(), b_values.raw(), count, domain_size, trace.accumulator->raw(), mu));
             trace.mu = algebra::FieldElement::from_bytes(mu);
+            return trace;
+        }
+    }
+
+    // Mirror of the reference's fp64 forward of one attention head (include/gatzk/model/gat.hpp:21-46,
+    // src/model/gat.cpp:474-615): same parameter and trace types, same call shape; the loops run on the GPU.
+    namespace model
+    {
+        using FloatMatrix = std::vector<std::vector<double>>;
+        struct Edge
+        {
+            std::size_t src = 0;
+            std::size_t dst = 0;
+        };
+        struct AttentionHeadParameters
+        {
+            FloatMatrix seq_kernel_fp;
+            std::vector<double> attn_dst_kernel_fp;
+            double attn_dst_bias_fp = 0.0;
+            std::vector<double> attn_src_kernel_fp;
+            double attn_src_bias_fp = 0.0;
+            std::vector<double> output_bias_fp;
+        };
+        struct HeadForwardTrace
+        {
+            FloatMatrix H_prime;
+            std::vector<double> E_src, E_dst, S, Z, M, Delta, U, Sum, inv, alpha;
+            FloatMatrix H_agg_pre_bias, H_agg;
+        };
+
+        inline HeadForwardTrace attention_head_forward(const Context& ctx, const FloatMatrix& features, const std::vector<Edge>& edges,
+                                                       const AttentionHeadParameters& parameters, bool apply_output_bias, bool apply_activation)
+        {
+            HeadForwardTrace trace;
+            if (features.empty()) return trace;
+            const std::size_t nodes = features.size(), inner = features.front().size();
+            const std::size_t width = parameters.seq_kernel_fp.empty() ? 0 : parameters.seq_kernel_fp.front().size();
+            if (parameters.seq_kernel_fp.size() != inner) throw std::runtime_error("float matrix multiply dimension mismatch");
+            for (const auto& edge : edges)
+                if (edge.src >= nodes || edge.dst >= nodes) throw std::runtime_error("edge out of bounds while running attention head forward");
+            auto upload_f64 = [&](const std::vector<double>& v) {
+                auto b = std::make_shared<DeviceBuffer>(ctx, GZK_KIND_F64, v.empty() ? 1 : v.size());
+                if (!v.empty()) b->upload(v.data(), v.size());
+                return b;
+            };
+            auto upload_u32 = [&](const std::vector<std::uint32_t>& v) {
+                auto b = std::make_shared<DeviceBuffer>(ctx, GZK_KIND_U32, v.empty() ? 1 : v.size());
+                if (!v.empty()) b->upload(v.data(), v.size());
+                return b;
+            };
+            auto flatten = [](const FloatMatrix& m) {
+                std::vector<double> out;
+                for (const auto& row : m) out.insert(out.end(), row.begin(), row.end());
+                return out;
+            };
+            // incoming sources per destination in edge order, the node itself appended when it has no self loop
+            std::vector<std::vector<std::uint32_t>> incoming(nodes);
+            std::vector<std::uint32_t> edge_src(edges.size()), edge_dst(edges.size());
+            for (std::size_t e = 0; e < edges.size(); ++e)
+            {
+                edge_src[e] = static_cast<std::uint32_t>(edges[e].src);
+                edge_dst[e] = static_cast<std::uint32_t>(edges[e].dst);
+                incoming[edges[e].dst].push_back(edge_src[e]);
+            }
+            std::vector<std::uint32_t> in_ptr(nodes + 1, 0), in_src;
+            for (std::size_t d = 0; d < nodes; ++d)
+            {
+                if (std::find(incoming[d].begin(), incoming[d].end(), static_cast<std::uint32_t>(d)) == incoming[d].end())
+                    incoming[d].push_back(static_cast<std::uint32_t>(d));
+                in_src.insert(in_src.end(), incoming[d].begin(), incoming[d].end());
+                in_ptr[d + 1] = static_cast<std::uint32_t>(in_src.size());
+            }
+            const auto d_features = upload_f64(flatten(features)), d_w = upload_f64(flatten(parameters.seq_kernel_fp));
+            const auto d_asrc = upload_f64(parameters.attn_src_kernel_fp), d_adst = upload_f64(parameters.attn_dst_kernel_fp);
+            const auto d_bias = upload_f64(parameters.output_bias_fp);
+            const auto d_es = upload_u32(edge_src), d_ed = upload_u32(edge_dst), d_ptr = upload_u32(in_ptr), d_in = upload_u32(in_src);
+            gzk_gat_head head{};
+            head.features = d_features->raw();
+            head.input_width = static_cast<std::uint32_t>(inner);
+            head.output_width = static_cast<std::uint32_t>(width);
+            head.seq_kernel = d_w->raw();
+            head.attn_src_kernel = d_asrc->raw();
+            head.attn_dst_kernel = d_adst->raw();
+            head.attn_src_bias = parameters.attn_src_bias_fp;
+            head.attn_dst_bias = parameters.attn_dst_bias_fp;
+            head.output_bias = apply_output_bias ? d_bias->raw() : nullptr;
+            head.output_bias_count = apply_output_bias ? parameters.output_bias_fp.size() : 0;
+            head.apply_activation = apply_activation ? 1 : 0;
+            gzk_gat_graph graph{};
+            graph.node_count = nodes;
+            graph.edge_count = edges.size();
+            graph.edge_src = d_es->raw();
+            graph.edge_dst = d_ed->raw();
+            graph.incoming_count = in_src.size();
+            graph.incoming_ptr = d_ptr->raw();
+            graph.incoming_src = d_in->raw();
+            const std::size_t e_count = edges.empty() ? 1 : edges.size();
+            DeviceBuffer h(ctx, GZK_KIND_F64, nodes * width), pre(ctx, GZK_KIND_F64, nodes * width), agg(ctx, GZK_KIND_F64, nodes * width);
+            DeviceBuffer es(ctx, GZK_KIND_F64, nodes), ed(ctx, GZK_KIND_F64, nodes), m(ctx, GZK_KIND_F64, nodes), sum(ctx, GZK_KIND_F64, nodes),
+                inv(ctx, GZK_KIND_F64, nodes);
+            DeviceBuffer s(ctx, GZK_KIND_F64, e_count), z(ctx, GZK_KIND_F64, e_count), delta(ctx, GZK_KIND_F64, e_count), u(ctx, GZK_KIND_F64, e_count),
+                alpha(ctx, GZK_KIND_F64, e_count);
+            gzk_gat_trace out{h.raw(), es.raw(), ed.raw(), m.raw(), sum.raw(), inv.raw(), s.raw(), z.raw(), delta.raw(), u.raw(), alpha.raw(), pre.raw(), agg.raw()};
+            ctx.check(gzk_gat_head_forward(ctx.raw(), &head, &graph, &out));
+            auto vec = [](const DeviceBuffer& b, std::size_t count) {
+                std::vector<double> v(count);
+                if (count != 0) b.download(v.data(), count);
+                return v;
+            };
+            auto mat = [&](const DeviceBuffer& b) {
+                const auto v = vec(b, nodes * width);
+                FloatMatrix out_m(nodes, std::vector<double>(width));
+                for (std::size_t i = 0; i < nodes; ++i) std::copy(v.begin() + i * width, v.begin() + (i + 1) * width, out_m[i].begin());
+                return out_m;
+            };
+            trace.H_prime = mat(h);
+            trace.E_src = vec(es, nodes);
+            trace.E_dst = vec(ed, nodes);
+            trace.S = vec(s, edges.size());
+            trace.Z = vec(z, edges.size());
+            trace.M = vec(m, nodes);
+            trace.Delta = vec(delta, edges.size());
+            trace.U = vec(u, edges.size());
+            trace.Sum = vec(sum, nodes);
+            trace.inv = vec(inv, nodes);
+            trace.alpha = vec(alpha, edges.size());
+            trace.H_agg_pre_bias = mat(pre);
+            trace.H_agg = mat(agg);
             return trace;
         }
     }

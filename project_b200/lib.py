@@ -60,6 +60,38 @@ def _fr(x):
     return a
 
 
+class _GatHead(ctypes.Structure):
+    _fields_ = [("features", ctypes.c_void_p), ("input_width", ctypes.c_uint32), ("output_width", ctypes.c_uint32),
+                ("seq_kernel", ctypes.c_void_p), ("attn_src_kernel", ctypes.c_void_p), ("attn_dst_kernel", ctypes.c_void_p),
+                ("attn_src_bias", ctypes.c_double), ("attn_dst_bias", ctypes.c_double), ("output_bias", ctypes.c_void_p),
+                ("output_bias_count", ctypes.c_size_t), ("apply_activation", ctypes.c_int)]
+
+
+class _GatGraph(ctypes.Structure):
+    _fields_ = [("node_count", ctypes.c_size_t), ("edge_count", ctypes.c_size_t), ("edge_src", ctypes.c_void_p), ("edge_dst", ctypes.c_void_p),
+                ("incoming_count", ctypes.c_size_t), ("incoming_ptr", ctypes.c_void_p), ("incoming_src", ctypes.c_void_p)]
+
+
+class _GatTrace(ctypes.Structure):
+    _fields_ = [(name, ctypes.c_void_p) for name in ("H_prime", "E_src", "E_dst", "M", "Sum", "inv", "S", "Z", "Delta", "U", "alpha",
+                                                     "H_agg_pre_bias", "H_agg")]
+
+
+def incoming_lists(edge_src, edge_dst, node_count):
+    """The per-destination source lists the reference builds on the host (src/model/gat.cpp:521-538): sources in edge order,
+    the node itself appended when it has no self loop.  Returns (ptr[node_count + 1], src[...]) as uint32 arrays."""
+    lists = [[] for _ in range(node_count)]
+    for s, d in zip(np.asarray(edge_src).tolist(), np.asarray(edge_dst).tolist()):
+        lists[d].append(s)
+    for d in range(node_count):
+        if d not in lists[d]:
+            lists[d].append(d)
+    ptr = np.zeros(node_count + 1, dtype=np.uint32)
+    ptr[1:] = np.cumsum([len(x) for x in lists])
+    src = np.array([s for x in lists for s in x], dtype=np.uint32)
+    return ptr, src
+
+
 class Buffer:
     def __init__(self, backend, handle, kind, count):
         self.backend, self.handle, self.kind, self.count = backend, handle, kind, count
@@ -249,6 +281,24 @@ class Backend:
     def quantize(self, values, count):
         out = self.alloc(KIND_I64, count)
         self._check(self.lib.gzk_quantize(self.ctx, values.handle, _sz(count), out.handle))
+        return out
+
+    def gat_head_forward(self, features, seq_kernel, attn_src, bias_src, attn_dst, bias_dst, out_bias, apply_activation, edge_src, edge_dst,
+                         node_count, input_width, output_width, incoming_ptr, incoming_src, out=None):
+        """All arguments are Buffers (F64 matrices, U32 lists) except the scalars; returns the trace fields as a dict of F64 Buffers
+        (`out`: such a dict from an earlier call, to be refilled)."""
+        edges = edge_src.count if edge_src is not None else 0
+        if out is None:
+            out = {name: self.alloc(KIND_F64, node_count * output_width) for name in ("H_prime", "H_agg_pre_bias", "H_agg")}
+            out.update({name: self.alloc(KIND_F64, node_count) for name in ("E_src", "E_dst", "M", "Sum", "inv")})
+            out.update({name: self.alloc(KIND_F64, max(edges, 1)) for name in ("S", "Z", "Delta", "U", "alpha")})
+        head = _GatHead(features.handle, input_width, output_width, seq_kernel.handle, attn_src.handle, attn_dst.handle, bias_src, bias_dst,
+                        out_bias.handle if out_bias is not None else None, out_bias.count if out_bias is not None else 0, int(bool(apply_activation)))
+        graph = _GatGraph(node_count, edges, edge_src.handle if edges else None, edge_dst.handle if edges else None, incoming_src.count,
+                          incoming_ptr.handle, incoming_src.handle)
+        trace = _GatTrace(*[out[name].handle for name in ("H_prime", "E_src", "E_dst", "M", "Sum", "inv", "S", "Z", "Delta", "U", "alpha",
+                                                          "H_agg_pre_bias", "H_agg")])
+        self._check(self.lib.gzk_gat_head_forward(self.ctx, ctypes.byref(head), ctypes.byref(graph), ctypes.byref(trace)))
         return out
 
     def first_zero_marker(self, delta, group_begin, group_end, groups, domain_size):

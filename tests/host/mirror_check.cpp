@@ -1,5 +1,6 @@
 // Runs the C++ host mirror (project_b200/host/gatzk_b200.hpp) on a GPU and checks its
 // results against the CPU oracle (test infrastructure), value for value.
+#include <cmath>
 #include <cstdio>
 #include <random>
 
@@ -17,6 +18,11 @@ extern "C"
     int ora_horner(const std::uint8_t* coefficients, std::size_t n, const std::uint8_t* x, std::uint8_t* out);
     int ora_logup_accumulator(const std::uint8_t*, const std::uint8_t*, const std::uint8_t*, const std::uint8_t*, const std::uint8_t*, std::size_t,
                               const std::uint8_t*, std::size_t, std::uint8_t*);
+    int ora_gat_head_forward(const double* features, std::size_t nodes, std::size_t inner, const double* seq_kernel, std::size_t width,
+                             const double* attn_src, double bias_src, const double* attn_dst, double bias_dst, const double* out_bias,
+                             std::size_t out_bias_count, int has_bias, int apply_activation, const std::uint32_t* edge_src,
+                             const std::uint32_t* edge_dst, std::size_t edges, double* H_prime, double* E_src, double* E_dst, double* S, double* Z,
+                             double* M, double* Delta, double* U, double* Sum, double* inv, double* alpha, double* H_agg_pre, double* H_agg);
 }
 
 using namespace gatzk_b200;
@@ -173,6 +179,69 @@ int main()
         threw = true;
     }
     CHECK(threw, "inverting zero throws");
+
+    // fp64 forward of one attention head through the mirror of the reference's types
+    {
+        const std::size_t nodes = 70, inner = 13, width = 8;
+        std::uniform_real_distribution<double> uni(-1.0, 1.0);
+        model::FloatMatrix features(nodes, std::vector<double>(inner));
+        for (auto& row : features)
+            for (auto& v : row) v = uni(rng);
+        model::AttentionHeadParameters params;
+        params.seq_kernel_fp.assign(inner, std::vector<double>(width));
+        for (auto& row : params.seq_kernel_fp)
+            for (auto& v : row) v = 0.4 * uni(rng);
+        params.attn_src_kernel_fp.resize(width);
+        params.attn_dst_kernel_fp.resize(width);
+        params.output_bias_fp.resize(width);
+        for (std::size_t c = 0; c < width; ++c)
+        {
+            params.attn_src_kernel_fp[c] = uni(rng);
+            params.attn_dst_kernel_fp[c] = uni(rng);
+            params.output_bias_fp[c] = 0.1 * uni(rng);
+        }
+        params.attn_src_bias_fp = 0.03;
+        params.attn_dst_bias_fp = -0.02;
+        std::vector<model::Edge> edges;
+        for (std::size_t e = 0; e < 400; ++e) edges.push_back({static_cast<std::size_t>(rng() % nodes), static_cast<std::size_t>(rng() % nodes)});
+        const auto trace = model::attention_head_forward(ctx, features, edges, params, true, true);
+        std::vector<double> xf, wf;
+        for (const auto& row : features) xf.insert(xf.end(), row.begin(), row.end());
+        for (const auto& row : params.seq_kernel_fp) wf.insert(wf.end(), row.begin(), row.end());
+        std::vector<std::uint32_t> es(edges.size()), ed(edges.size());
+        for (std::size_t e = 0; e < edges.size(); ++e)
+        {
+            es[e] = static_cast<std::uint32_t>(edges[e].src);
+            ed[e] = static_cast<std::uint32_t>(edges[e].dst);
+        }
+        std::vector<double> H(nodes * width), Es(nodes), Ed(nodes), S(edges.size()), Z(edges.size()), M(nodes), D(edges.size()), U(edges.size()), Sum(nodes),
+            Inv(nodes), A(edges.size()), Pre(nodes * width), Agg(nodes * width);
+        CHECK(ora_gat_head_forward(xf.data(), nodes, inner, wf.data(), width, params.attn_src_kernel_fp.data(), params.attn_src_bias_fp,
+                                   params.attn_dst_kernel_fp.data(), params.attn_dst_bias_fp, params.output_bias_fp.data(), width, 1, 1, es.data(),
+                                   ed.data(), edges.size(), H.data(), Es.data(), Ed.data(), S.data(), Z.data(), M.data(), D.data(), U.data(), Sum.data(),
+                                   Inv.data(), A.data(), Pre.data(), Agg.data()) == 0,
+              "oracle forward runs");
+        bool exact = true, close = true;
+        double h_max = 0.0;
+        for (double v : H) h_max = std::max(h_max, std::fabs(v));
+        for (std::size_t i = 0; i < nodes; ++i)
+        {
+            exact = exact && trace.E_src[i] == Es[i] && trace.E_dst[i] == Ed[i] && trace.M[i] == M[i];
+            close = close && std::fabs(trace.Sum[i] - Sum[i]) <= 4e-15 * Sum[i] && std::fabs(trace.inv[i] - Inv[i]) <= 4e-15 * Inv[i];
+            for (std::size_t c = 0; c < width; ++c)
+            {
+                exact = exact && trace.H_prime[i][c] == H[i * width + c];
+                close = close && std::fabs(trace.H_agg[i][c] - Agg[i * width + c]) <= 4e-15 * std::max(h_max, std::fabs(Agg[i * width + c]));
+            }
+        }
+        for (std::size_t e = 0; e < edges.size(); ++e)
+        {
+            exact = exact && trace.S[e] == S[e] && trace.Z[e] == Z[e] && trace.Delta[e] == D[e];
+            close = close && std::fabs(trace.U[e] - U[e]) <= 4e-15 * U[e] && std::fabs(trace.alpha[e] - A[e]) <= 4e-15 * A[e];
+        }
+        CHECK(exact, "head forward: H', E_src, E_dst, S, Z, M, Delta bit-identical");
+        CHECK(close, "head forward: U, Sum, inv, alpha, H_agg within 4e-15");
+    }
     std::printf(failures == 0 ? "OK\n" : "FAILED %d\n", failures);
     return failures == 0 ? 0 : 1;
 }

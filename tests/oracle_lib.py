@@ -351,3 +351,27 @@ def bench_builders(n, valid, seed=1):
     chk = np.zeros(32, dtype=np.uint8)
     _check(lib().ora_bench_builders(_sz(n), _sz(valid), ctypes.c_uint64(seed), sec, _p(chk)))
     return list(sec)
+
+
+def gat_head_forward(features, seq_kernel, attn_src, bias_src, attn_dst, bias_dst, out_bias, apply_activation, edge_src, edge_dst):
+    """gat.cpp:474-615 on row-major float64 arrays; returns the HeadForwardTrace fields as a dict."""
+    features = np.ascontiguousarray(features, dtype=np.float64)
+    seq_kernel = np.ascontiguousarray(seq_kernel, dtype=np.float64)
+    nodes, inner = features.shape
+    width = seq_kernel.shape[1]
+    attn_src = np.ascontiguousarray(attn_src, dtype=np.float64)
+    attn_dst = np.ascontiguousarray(attn_dst, dtype=np.float64)
+    bias = np.ascontiguousarray(out_bias if out_bias is not None else np.zeros(0), dtype=np.float64)
+    es = np.ascontiguousarray(edge_src, dtype=np.uint32)
+    ed = np.ascontiguousarray(edge_dst, dtype=np.uint32)
+    edges = es.size
+    out = {name: np.zeros((nodes, width)) for name in ("H_prime", "H_agg_pre_bias", "H_agg")}
+    out.update({name: np.zeros(nodes) for name in ("E_src", "E_dst", "M", "Sum", "inv")})
+    out.update({name: np.zeros(edges) for name in ("S", "Z", "Delta", "U", "alpha")})
+    dp = lambda a: a.ctypes.data_as(ctypes.c_void_p)
+    _check(lib().ora_gat_head_forward(dp(features), _sz(nodes), _sz(inner), dp(seq_kernel), _sz(width), dp(attn_src), ctypes.c_double(bias_src),
+                                      dp(attn_dst), ctypes.c_double(bias_dst), dp(bias), _sz(bias.size), int(out_bias is not None),
+                                      int(bool(apply_activation)), dp(es), dp(ed), _sz(edges), dp(out["H_prime"]), dp(out["E_src"]),
+                                      dp(out["E_dst"]), dp(out["S"]), dp(out["Z"]), dp(out["M"]), dp(out["Delta"]), dp(out["U"]), dp(out["Sum"]),
+                                      dp(out["inv"]), dp(out["alpha"]), dp(out["H_agg_pre_bias"]), dp(out["H_agg"])))
+    return out

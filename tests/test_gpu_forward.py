@@ -1,0 +1,108 @@
+"""fp64 forward pass of an attention head on the GPU against the CPU oracle (which follows the
+reference's loops and uses the host's exp / expm1).
+
+Bar: every value that involves no transcendental function (H', E_src, E_dst, S, Z, M, Delta) is
+bit-identical; values downstream of exp / expm1 (U, Sum, inv, alpha, H_agg_pre_bias, H_agg)
+agree to a relative 4e-15 (a few units in the last place: the CUDA and host math libraries may
+round the last bit of exp differently), the signed sums H_agg_pre_bias / H_agg to 4e-15 of the
+largest summand magnitude (max |H'|), since their terms can cancel; the quantised witness (round half away at scale 16)
+is identical wherever 16*v is further than 1e-9 from a rounding boundary."""
+import numpy as np
+import pytest
+
+import oracle_lib as ora
+
+pytestmark = pytest.mark.gpu
+
+EXACT = ("H_prime", "E_src", "E_dst", "S", "Z", "M", "Delta")
+CLOSE = ("U", "Sum", "inv", "alpha", "H_agg_pre_bias", "H_agg")
+REL_TOL = 4e-15
+
+
+@pytest.fixture(scope="module")
+def be():
+    from project_b200 import Backend
+
+    b = Backend(0)
+    yield b
+    b.close()
+
+
+def random_graph(rng, nodes, edges, self_loops):
+    src = rng.integers(0, nodes, size=edges, dtype=np.uint32)
+    dst = np.sort(rng.integers(0, nodes, size=edges, dtype=np.uint32))  # grouped by destination like the prover's edge list
+    if self_loops:
+        src = np.concatenate([src, np.arange(nodes, dtype=np.uint32)])
+        dst = np.concatenate([dst, np.arange(nodes, dtype=np.uint32)])
+        order = np.argsort(dst, kind="stable")
+        src, dst = src[order], dst[order]
+    return src, dst
+
+
+def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, shuffle=False):
+    from project_b200 import KIND_F64, KIND_U32, incoming_lists
+
+    x = rng.normal(size=(nodes, inner)) * (rng.random((nodes, inner)) < 0.3)
+    w = rng.uniform(-0.4, 0.4, size=(inner, width))
+    a_src, a_dst = rng.uniform(-1, 1, size=width), rng.uniform(-1, 1, size=width)
+    b_src, b_dst = float(rng.uniform(-0.1, 0.1)), float(rng.uniform(-0.1, 0.1))
+    out_bias = rng.uniform(-0.2, 0.2, size=width) if bias else None
+    src, dst = random_graph(rng, nodes, edges, self_loops)
+    if shuffle:  # the reference accepts any edge order; the incoming lists then follow that order
+        perm = rng.permutation(src.size)
+        src, dst = src[perm], dst[perm]
+    want = ora.gat_head_forward(x, w, a_src, b_src, a_dst, b_dst, out_bias, activation, src, dst)
+    ptr, inc = incoming_lists(src, dst, nodes)
+    up = lambda a, kind: be.upload(np.ascontiguousarray(a).reshape(-1), kind)
+    got = be.gat_head_forward(up(x, KIND_F64), up(w, KIND_F64), up(a_src, KIND_F64), b_src, up(a_dst, KIND_F64), b_dst,
+                              up(out_bias, KIND_F64) if bias else None, activation, up(src, KIND_U32) if src.size else None,
+                              up(dst, KIND_U32) if src.size else None, nodes, inner, width, up(ptr, KIND_U32), up(inc, KIND_U32))
+    for name in EXACT:
+        g = got[name].download()[:want[name].size].reshape(want[name].shape)
+        assert np.array_equal(g.view(np.uint64), want[name].view(np.uint64)), name
+    for name in CLOSE:
+        g = got[name].download()[:want[name].size].reshape(want[name].shape)
+        scale = np.maximum(np.abs(want[name]), 1e-300)
+        if name.startswith("H_agg"):
+            scale = np.maximum(scale, np.abs(want["H_prime"]).max())
+        assert np.all(np.abs(g - want[name]) <= REL_TOL * scale + 1e-300), name
+    # the quantised witness
+    for name in ("H_agg", "alpha", "U"):
+        g = got[name]
+        count = want[name].size
+        if count == 0:
+            continue
+        q = be.quantize(g, count).download()
+        wq = ora.quantize(want[name].reshape(-1))
+        scaled = want[name].reshape(-1) * 16.0
+        away_from_boundary = np.abs(np.abs(scaled - np.floor(scaled)) - 0.5) > 1e-9
+        assert np.array_equal(q[away_from_boundary], wq[away_from_boundary]), name
+
+
+@pytest.mark.parametrize("nodes,inner,width,edges,self_loops,bias,activation", [
+    (1, 3, 2, 0, False, True, True),
+    (40, 17, 8, 150, True, True, True),
+    (300, 50, 8, 2000, True, False, True),
+    (300, 64, 7, 1500, False, True, False),
+    (2000, 33, 64, 15000, True, True, True),
+])
+def test_head_forward_matches_oracle(be, nodes, inner, width, edges, self_loops, bias, activation):
+    run_case(be, np.random.default_rng(nodes * 7 + width), nodes, inner, width, edges, self_loops, bias, activation)
+
+
+def test_head_forward_unsorted_edges(be):
+    run_case(be, np.random.default_rng(99), 120, 20, 8, 700, False, True, True, shuffle=True)
+
+
+def test_head_forward_rejects_bad_endpoint(be):
+    from project_b200 import KIND_F64, KIND_U32, GzkError
+
+    nodes, inner, width = 10, 4, 2
+    up = lambda a, kind: be.upload(np.ascontiguousarray(a).reshape(-1), kind)
+    ptr = np.arange(nodes + 1, dtype=np.uint32)
+    inc = np.arange(nodes, dtype=np.uint32)
+    inc[3] = 77  # beyond the node count
+    with pytest.raises(GzkError) as e:
+        be.gat_head_forward(up(np.ones((nodes, inner)), KIND_F64), up(np.ones((inner, width)), KIND_F64), up(np.ones(width), KIND_F64), 0.0,
+                            up(np.ones(width), KIND_F64), 0.0, None, True, None, None, nodes, inner, width, up(ptr, KIND_U32), up(inc, KIND_U32))
+    assert e.value.code == 1

@@ -271,3 +271,38 @@ def test_golden_fixtures():
     lg = g["logup"]
     out = ora.logup_accumulator(*(hx(lg[k]).reshape(-1, 32) for k in ("table", "query", "mult", "q_table", "q_query")), hx(lg["beta"]), lg["active"])
     assert out.tobytes().hex() == lg["out"]
+
+
+def test_gat_head_forward_against_numpy_restatement():
+    """The oracle's forward pass against an independent vectorised restatement (same formulas, numpy
+    order of summation, so compared to a relative 1e-12)."""
+    rng = np.random.default_rng(5)
+    nodes, inner, width, edges = 60, 11, 5, 300
+    x = rng.normal(size=(nodes, inner))
+    w = rng.uniform(-0.5, 0.5, size=(inner, width))
+    a_src, a_dst = rng.uniform(-1, 1, size=width), rng.uniform(-1, 1, size=width)
+    bias = rng.uniform(-0.2, 0.2, size=width)
+    src = rng.integers(0, nodes, size=edges).astype(np.uint32)
+    dst = rng.integers(0, nodes, size=edges).astype(np.uint32)
+    got = ora.gat_head_forward(x, w, a_src, 0.05, a_dst, -0.03, bias, True, src, dst)
+    h = x @ w
+    e_src, e_dst = h @ a_src + 0.05, h @ a_dst - 0.03
+    leaky = lambda v: np.where(v >= 0, v, 0.2 * v)
+    inc = [[] for _ in range(nodes)]
+    for s, d in zip(src.tolist(), dst.tolist()):
+        inc[d].append(s)
+    for d in range(nodes):
+        if d not in inc[d]:
+            inc[d].append(d)
+    m = np.array([max(leaky(e_dst[d] + e_src[s]) for s in inc[d]) for d in range(nodes)])
+    total = np.array([sum(np.exp(leaky(e_dst[d] + e_src[s]) - m[d]) for s in inc[d]) for d in range(nodes)])
+    agg = np.stack([sum(np.exp(leaky(e_dst[d] + e_src[s]) - m[d]) / total[d] * h[s] for s in inc[d]) for d in range(nodes)])
+    out = agg + bias
+    out = np.where(out >= 0, out, np.expm1(out))
+    close = lambda a, b: np.allclose(a, b, rtol=1e-12, atol=1e-14)
+    assert close(got["H_prime"], h) and close(got["E_src"], e_src) and close(got["E_dst"], e_dst)
+    assert close(got["M"], m) and close(got["Sum"], total) and close(got["inv"], 1 / total)
+    assert close(got["H_agg"], out)
+    s = e_dst[dst] + e_src[src]
+    assert close(got["S"], s) and close(got["Z"], leaky(s)) and close(got["Delta"], m[dst] - leaky(s))
+    assert close(got["U"], np.exp(leaky(s) - m[dst])) and close(got["alpha"], np.exp(leaky(s) - m[dst]) / total[dst])
