@@ -658,12 +658,19 @@ def run_sweep(be, rng, G, stream, small=False):
         return a
 
     out = {}
-    lg = 14 if small else 20
-    n = 1 << lg
-    scalars = be.upload(rand_fr(n), KIND_FR)
-    points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n), KIND_FR), n)
-    ms = timed_ms(lambda: be.msm(scalars, points, n))
-    out["msm"] = {"log2n": lg, "ms": ms, "Mpts_per_s": n / ms / 1e3}
+    for lg in ((14,) if small else (20, 22)):
+        n = 1 << lg
+        scalars = be.upload(rand_fr(n), KIND_FR)
+        points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n), KIND_FR), n)
+        ms = timed_ms(lambda: be.msm(scalars, points, n))
+        entry = {"log2n": lg, "ms": ms, "Mpts_per_s": n / ms / 1e3}
+        # the same MSM against the resident table of shifted bases (the SRS layout)
+        table, wb = be.msm_precompute(points, n)
+        ms = timed_ms(lambda: be.msm_precomputed(scalars, table, n, wb))
+        entry["resident_table"] = {"window_bits": wb, "table_GB": table.count * 96 / 1e9, "ms": ms, "Mpts_per_s": n / ms / 1e3}
+        out["msm" if lg <= 20 else f"msm_2p{lg}"] = entry
+        for b in (scalars, points, table):
+            b.free()
     lg = 14 if small else 22
     n = 1 << lg
     from project_b200 import KIND_FR_MONT
@@ -676,7 +683,7 @@ def run_sweep(be, rng, G, stream, small=False):
     r = rand_fr(1)[0]
     ms = timed_ms(lambda: be.fold(vec, n, r, out=res))
     out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6}
-    for b in (scalars, points, vec, res):
+    for b in (vec, res):
         b.free()
     # fp64 forward of one attention head at the mid-size graph's shape (time only: not a roofline target)
     from project_b200 import KIND_F64, KIND_U32, incoming_lists
@@ -767,16 +774,20 @@ def run_sweep_sharded(be, G, stream, rank, world, device, small=False):
     scalars = be.upload(rand_fr(n_local), KIND_FR)
     points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n_local), KIND_FR), n_local)
 
+    table, wb = be.msm_precompute(points, n_local)  # each rank keeps the shifted copies of its own point range
+
     def msm():
-        part = torch.from_numpy(be.msm(scalars, points, n_local).copy()).cuda()
+        part = torch.from_numpy(be.msm_precomputed(scalars, table, n_local, wb).copy()).cuda()
         gathered = torch.empty((world, 96), dtype=torch.uint8, device="cuda")
         dist.all_gather_into_tensor(gathered, part)
         return g1_sum(gathered.cpu().numpy())
 
     ms = timed_ms(msm)
-    out["msm_sharded"] = {"log2n_per_rank": lg, "ranks": world, "ms": ms, "Mpts_per_s": world * n_local / ms / 1e3}
+    out["msm_sharded"] = {"log2n_per_rank": lg, "ranks": world, "ms": ms, "Mpts_per_s": world * n_local / ms / 1e3,
+                          "layout": "point range per rank, resident table of shifted bases, 96-byte all-gather"}
     scalars.free()
     points.free()
+    table.free()
     return out
 
 

@@ -308,6 +308,17 @@ int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, const gzk_gat_g
  * gzk_srs_lagrange: out_points[i] = [L_i(tau)] base over the 2^log2n domain. */
 int gzk_msm(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, size_t n, uint8_t out[96]);
 int gzk_srs_lagrange(gzk_ctx* ctx, unsigned log2n, const uint8_t base[96], const uint8_t tau[32], gzk_buf* out_points);
+/* MSM against a FIXED point set that stays resident (an SRS): gzk_msm_precompute fills `table`
+ * (a G1 buffer of gzk_msm_table_points(n, window_bits) points) with 2^(window_bits*w) P_i for
+ * every window w of the signed-digit decomposition; gzk_msm_precomputed then adds the digits
+ * of all windows into one set of 2^(window_bits-1) buckets - same result as gzk_msm, without
+ * the per-window reductions and the chain of ~254 doublings at the end.
+ * gzk_msm_window_bits(n) is the recommended window for n points.  The table costs
+ * ceil(255/window_bits) times the memory of the points and one pass of doublings to build. */
+unsigned gzk_msm_window_bits(size_t n);
+size_t gzk_msm_table_points(size_t n, unsigned window_bits);
+int gzk_msm_precompute(gzk_ctx* ctx, const gzk_buf* points, size_t n, unsigned window_bits, gzk_buf* table);
+int gzk_msm_precomputed(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* table, size_t n, unsigned window_bits, uint8_t out[96]);
 
 /* ---- NTT / coset LDE / multilinear fold (kernel sweep) -------------------------------------------
  * No reference caller: the reference evaluates by barycentric weights and never

@@ -10,6 +10,12 @@
 //                 CTA sums the buckets whose multiplier has that bit set
 //   6. finish     per window Horner over the bits, shift by 2^(c*w), sum, to affine
 //
+// With a precomputed table of the points shifted by every window (gzk_msm_precompute:
+// 2^(c*w) P_i for all w, the layout for a resident SRS) the digits of all windows fall
+// into ONE set of 2^(c-1) buckets: no per-window reduction and no chain of c*w doublings
+// at the end (254 dependent doublings cost 2.8 ms whatever the size), and the window can
+// be wider because only one window's buckets are reduced.
+//
 // Signed digits halve the bucket count (2^(c-1) per window): a negative digit adds
 // the negated point.  Group sums do not depend on the order of additions, so the
 // atomics of steps 1 and 3 leave the result bit-identical from run to run.
@@ -48,6 +54,7 @@ namespace gzk
             uint32_t c;        // window bits
             uint32_t windows;  // ceil(256 / c)
             uint32_t half;     // 2^(c-1) buckets per window
+            uint32_t shared;   // 1: all windows share one bucket set and entries index the shifted-point table [w*n + i]
         };
 
         // code[w*n + i] = 0 for a zero digit, else ((|d|-1) << 1 | negative) + 1
@@ -83,7 +90,7 @@ namespace gzk
                 if (d != 0)
                 {
                     out = (((d - 1) << 1) | negative) + 1;
-                    atomicAdd(bucket_count + static_cast<uint64_t>(w) * plan.half + (d - 1), 1u);
+                    atomicAdd(bucket_count + (plan.shared ? 0 : static_cast<uint64_t>(w) * plan.half) + (d - 1), 1u);
                 }
                 code[static_cast<uint64_t>(w) * n + i] = out;
             }
@@ -136,9 +143,9 @@ namespace gzk
                 const uint64_t w = t / n;
                 const uint64_t i = t - w * n;
                 const uint32_t payload = v - 1;
-                const uint64_t bucket = w * plan.half + (payload >> 1);
+                const uint64_t bucket = (plan.shared ? 0 : w * plan.half) + (payload >> 1);
                 const uint32_t pos = atomicAdd(cursor + bucket, 1u);
-                entries[bucket_start[bucket] + pos] = (static_cast<uint32_t>(i) << 1) | (payload & 1u);
+                entries[bucket_start[bucket] + pos] = (static_cast<uint32_t>(plan.shared ? t : i) << 1) | (payload & 1u);
             }
         }
 
@@ -283,6 +290,144 @@ namespace gzk
             }
         }
 
+        // ---- shared-bucket path: reduction of ONE bucket set -----------------------------------
+        // sum_d d * B_d over d = 1 .. 2^(c-1) (B_d = bucket d-1).  Write d = hi * 2^h + lo and lay the
+        // buckets out as a matrix [hi][lo]: with the row sums R_hi and the column sums C_lo,
+        //   sum_d d * B_d = sum_lo lo * C_lo + 2^h * sum_hi hi * R_hi,
+        // so the bulk of the work is 2 additions per bucket in short independent trees, and the
+        // two weighted sums run over 2^h and 2^(c-1-h)+1 points only; those are split by the bits
+        // of the multiplier: bit_sums[b] for b < h from the columns, for b >= h from the rows,
+        // and sum_b 2^b * bit_sums[b] is the result.
+        __device__ __forceinline__ G1Xyzz cta_tree_sum(G1Xyzz acc, G1Xyzz* slots)
+        {
+            slots[threadIdx.x] = acc;
+            __syncthreads();
+            for (uint32_t offset = kThreads / 2; offset > 0; offset >>= 1)
+            {
+                if (threadIdx.x < offset) slots[threadIdx.x] = g1_add(slots[threadIdx.x], slots[threadIdx.x + offset]);
+                __syncthreads();
+            }
+            return slots[0];
+        }
+        // CTAs [0, rows): row sums; CTAs [rows, rows + cols): column sums.  rc = [rows row sums][cols column sums]
+        __global__ void __launch_bounds__(kThreads) msm_rowcol_kernel(const G1Xyzz* buckets, uint32_t half, uint32_t h, uint32_t rows, G1Xyzz* rc)
+        {
+            __shared__ G1Xyzz slots[kThreads];
+            const uint32_t cols = 1u << h;
+            G1Xyzz acc = G1Xyzz::infinity();
+            if (blockIdx.x < rows)
+            {
+                const uint32_t hi = blockIdx.x;
+                for (uint32_t lo = threadIdx.x; lo < cols; lo += kThreads)
+                {
+                    const uint32_t d = (hi << h) | lo;
+                    if (d >= 1 && d <= half) acc = g1_add(acc, load_xyzz(buckets + (d - 1)));
+                }
+            }
+            else
+            {
+                const uint32_t lo = blockIdx.x - rows;
+                for (uint32_t hi = threadIdx.x; hi < rows; hi += kThreads)
+                {
+                    const uint32_t d = (hi << h) | lo;
+                    if (d >= 1 && d <= half) acc = g1_add(acc, load_xyzz(buckets + (d - 1)));
+                }
+            }
+            const G1Xyzz total = cta_tree_sum(acc, slots);
+            if (threadIdx.x == 0) store_xyzz(rc + blockIdx.x, total);
+        }
+        // CTA b < h: sum of the column sums whose lo has bit b; CTA b >= h: sum of the row sums whose hi has bit b - h
+        __global__ void __launch_bounds__(kThreads) msm_rowcol_bits_kernel(const G1Xyzz* rc, uint32_t h, uint32_t rows, G1Xyzz* bit_sums)
+        {
+            __shared__ G1Xyzz slots[kThreads];
+            const uint32_t b = blockIdx.x;
+            const bool from_cols = b < h;
+            const uint32_t count = from_cols ? (1u << h) : rows;
+            const uint32_t bit = from_cols ? b : b - h;
+            const G1Xyzz* src = from_cols ? rc + rows : rc;
+            G1Xyzz acc = G1Xyzz::infinity();
+            for (uint32_t j = threadIdx.x; j < count; j += kThreads)
+                if ((j >> bit) & 1u) acc = g1_add(acc, load_xyzz(src + j));
+            const G1Xyzz total = cta_tree_sum(acc, slots);
+            if (threadIdx.x == 0) store_xyzz(bit_sums + b, total);
+        }
+        // thread b shifts the sum of bit b by b doublings (at most c - 1), then a tree; thread 0 converts to affine
+        __global__ void __launch_bounds__(kMaxWindows) msm_finish_shared_kernel(const G1Xyzz* bit_sums, uint32_t c, G1Xyzz* out_xyzz, G1Affine* out_canonical)
+        {
+            __shared__ G1Xyzz slots[kMaxWindows];
+            const uint32_t b = threadIdx.x;
+            G1Xyzz acc = G1Xyzz::infinity();
+            if (b < c)
+            {
+                acc = load_xyzz(bit_sums + b);
+                for (uint32_t k = 0; k < b; ++k) acc = g1_double(acc);
+            }
+            slots[b] = acc;
+            __syncthreads();
+            for (uint32_t offset = kMaxWindows / 2; offset > 0; offset >>= 1)
+            {
+                if (b < offset) slots[b] = g1_add(slots[b], slots[b + offset]);
+                __syncthreads();
+            }
+            if (b == 0)
+            {
+                store_xyzz(out_xyzz, slots[0]);
+                G1Affine a = g1_to_affine(slots[0]);
+                a.x = from_mont(a.x);
+                a.y = from_mont(a.y);
+                store_affine(out_canonical, a);
+            }
+        }
+
+        // next[i] = 2^c * prev[i] (affine Montgomery in and out; one inversion per point, all in parallel)
+        __global__ void __launch_bounds__(kThreads) msm_table_window_kernel(const G1Affine* prev, G1Affine* next, uint64_t n, uint32_t c)
+        {
+            const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            if (i >= n) return;
+            const G1Affine p = load_affine(prev + i);
+            if (p.is_infinity())
+            {
+                store_affine(next + i, p);
+                return;
+            }
+            G1Xyzz acc = G1Xyzz::from_affine(p);
+#pragma unroll 1
+            for (uint32_t k = 0; k < c; ++k) acc = g1_double(acc);
+            store_affine(next + i, g1_to_affine(acc));
+        }
+
+        // Windows needed for scalars below the group order r: ceil(255 / c), plus one when the top
+        // digit could still reach 2^(c-1) and push a carry out.
+        uint32_t windows_for(uint32_t c)
+        {
+            uint32_t windows = (255 + c - 1) / c;
+            const uint32_t top_shift = c * (windows - 1);
+            // largest top digit = (r - 1) >> top_shift, from the modulus limbs
+            uint64_t top = 0;
+            for (int limb = 7; limb >= 0; --limb)
+            {
+                const uint32_t lo_bit = 32u * static_cast<uint32_t>(limb);
+                if (lo_bit + 32 <= top_shift) break;
+                const uint64_t word = FrCfg::mod(limb);
+                if (lo_bit >= top_shift)
+                    top |= word << (lo_bit - top_shift);
+                else
+                    top |= word >> (top_shift - lo_bit);
+            }
+            if (top + 1 > (1ULL << (c - 1))) ++windows;  // top digit + incoming carry may exceed the signed range
+            return windows;
+        }
+
+        MsmPlan make_shared_plan(uint32_t c)
+        {
+            MsmPlan p;
+            p.c = c;
+            p.windows = windows_for(c);
+            p.half = 1u << (c - 1);
+            p.shared = 1;
+            return p;
+        }
+
         MsmPlan make_plan(uint64_t n)
         {
             uint32_t log2n = 0;
@@ -297,6 +442,7 @@ namespace gzk
             p.c = static_cast<uint32_t>(c);
             p.windows = (256 + p.c - 1) / p.c;
             p.half = 1u << (p.c - 1);
+            p.shared = 0;
             return p;
         }
     }
@@ -304,18 +450,20 @@ namespace gzk
     // MSM over device-resident scalars and points; the XYZZ result is left in
     // `out_xyzz` (device, optional use by multi-GPU combiners) and the canonical
     // affine result is copied to `out_host`.
-    int msm_run(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, uint64_t n, uint8_t out_host[96])
+    static int msm_run_plan(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, uint64_t n, const MsmPlan& plan, uint8_t out_host[96])
     {
-        const MsmPlan plan = make_plan(n);
-        const uint64_t buckets = static_cast<uint64_t>(plan.windows) * plan.half;
+        const uint64_t buckets = plan.shared ? plan.half : static_cast<uint64_t>(plan.windows) * plan.half;
         const size_t code_bytes = static_cast<size_t>(n) * plan.windows * sizeof(uint32_t);
         const size_t bucket_u32 = buckets * sizeof(uint32_t);
         const uint64_t total_entries = n * plan.windows;
         const uint64_t max_big = total_entries / kBigBucket + 1;          // buckets that can exceed the threshold
         const uint64_t max_items = total_entries / kSliceEntries + max_big; // sum of ceil(size / slice) over them
         const size_t big_bytes = max_items * (sizeof(BigItem) + sizeof(G1Xyzz)) + max_big * sizeof(BigBucket) + 64;
+        const uint32_t split_h = (plan.c - 1) / 2;                          // low bits of the bucket multiplier
+        const uint32_t split_rows = (1u << (plan.c - 1 - split_h)) + 1;     // values of the high part, 0 .. 2^(c-1-h)
+        const size_t chunk_bytes = plan.shared ? (static_cast<size_t>(split_rows) + (1u << split_h)) * sizeof(G1Xyzz) : 0;
         const size_t total = big_bytes + 2 * code_bytes + 3 * bucket_u32 + buckets * sizeof(G1Xyzz) + static_cast<size_t>(plan.windows) * plan.c * sizeof(G1Xyzz) +
-                             sizeof(G1Xyzz) + sizeof(G1Affine) + 8192;
+                             chunk_bytes + sizeof(G1Xyzz) + sizeof(G1Affine) + 8192;
         void* scratch = nullptr;
         int rc = ensure_scratch(ctx, 1, total, &scratch);
         if (rc != GZK_OK) return rc;
@@ -338,6 +486,7 @@ namespace gzk
         BigItem* big_items = reinterpret_cast<BigItem*>(take(max_items * sizeof(BigItem)));
         BigBucket* big_buckets = reinterpret_cast<BigBucket*>(take(max_big * sizeof(BigBucket)));
         uint32_t* big_counters = reinterpret_cast<uint32_t*>(take(64));
+        G1Xyzz* bit_partial = reinterpret_cast<G1Xyzz*>(take(chunk_bytes));
         if (static_cast<size_t>(cur - static_cast<char*>(scratch)) > ctx->scratch[1].bytes)
             return fail(ctx, GZK_E_INVALID, "msm: internal scratch accounting error");
 
@@ -387,12 +536,24 @@ namespace gzk
                 big_counters, big_buckets, big_partial, bucket_points);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
+        if (plan.shared)
         {
-            LaunchScope scope(ctx, "msm_bits");
-            msm_bits_kernel<<<plan.windows * plan.c, kThreads, 0, ctx->stream>>>(bucket_points, plan, bit_sums);
+            {
+                LaunchScope scope(ctx, "msm_bits", 2);
+                msm_rowcol_kernel<<<split_rows + (1u << split_h), kThreads, 0, ctx->stream>>>(bucket_points, plan.half, split_h, split_rows, bit_partial);
+                msm_rowcol_bits_kernel<<<plan.c, kThreads, 0, ctx->stream>>>(bit_partial, split_h, split_rows, bit_sums);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            LaunchScope scope(ctx, "msm_finish");
+            msm_finish_shared_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan.c, result_xyzz, result_affine);
         }
-        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        else
         {
+            {
+                LaunchScope scope(ctx, "msm_bits");
+                msm_bits_kernel<<<plan.windows * plan.c, kThreads, 0, ctx->stream>>>(bucket_points, plan, bit_sums);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
             LaunchScope scope(ctx, "msm_finish");
             msm_finish_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan, result_xyzz, result_affine);
         }
@@ -403,7 +564,94 @@ namespace gzk
     }
 }
 
+namespace gzk
+{
+    int msm_run(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, uint64_t n, uint8_t out_host[96])
+    {
+        return msm_run_plan(ctx, scalars, points, n, make_plan(n), out_host);
+    }
+}
+
 using namespace gzk;
+
+extern "C" unsigned gzk_msm_window_bits(size_t n)
+{
+    // Start from log2(n) - 3 (a few hundred entries per bucket, >= 2^15 buckets so that one bucket
+    // set keeps every SM busy) and compare its neighbours by additions: n per window, 2 per bucket
+    // for the reduction, and a surcharge when the top window is only a few bits wide (its handful
+    // of buckets then take n / 2^bits points each and go through the slower cooperative path).
+    unsigned log2n = 0;
+    while ((static_cast<size_t>(1) << (log2n + 1)) <= n) ++log2n;
+    int c0 = static_cast<int>(log2n) - 3;
+    if (c0 < 16) c0 = 16;
+    if (c0 > 23) c0 = 23;
+    double best_cost = 0.0;
+    unsigned best = static_cast<unsigned>(c0);
+    for (int c = c0 - 1; c <= c0 + 1; ++c)
+    {
+        const uint32_t windows = windows_for(static_cast<uint32_t>(c));
+        const uint32_t full = (255 + static_cast<uint32_t>(c) - 1) / static_cast<uint32_t>(c);
+        const int top_bits = 255 - c * static_cast<int>(full - 1);
+        // a window beyond ceil(255 / c) only receives the carries of the one below it: about n / 2 entries
+        double cost = (static_cast<double>(full) + (windows > full ? 0.5 : 0.0)) * static_cast<double>(n) + 2.0 * static_cast<double>(1ULL << (c - 1));
+        if (top_bits > 0 && top_bits < 12) cost += 1.5 * static_cast<double>(n);
+        if (static_cast<double>(windows) * static_cast<double>(n) / static_cast<double>(1ULL << (c - 1)) > 768.0) cost += 4.0 * static_cast<double>(n);
+        if (best_cost == 0.0 || cost < best_cost)
+        {
+            best_cost = cost;
+            best = static_cast<unsigned>(c);
+        }
+    }
+    return best;
+}
+
+extern "C" size_t gzk_msm_table_points(size_t n, unsigned window_bits)
+{
+    if (window_bits < 2 || window_bits > 24) return 0;
+    return n * windows_for(window_bits);
+}
+
+extern "C" int gzk_msm_precompute(gzk_ctx* ctx, const gzk_buf* points, size_t n, unsigned window_bits, gzk_buf* table)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (points == nullptr || table == nullptr || points->kind != GZK_KIND_G1 || table->kind != GZK_KIND_G1 || points->count < n)
+        return fail(ctx, GZK_E_INVALID, "msm_precompute: points and table must be G1 buffers");
+    if (window_bits < 8 || window_bits > 24) return fail(ctx, GZK_E_INVALID, "msm_precompute: window_bits must lie in [8, 24]");
+    const uint32_t windows = windows_for(window_bits);
+    if (table->count < n * windows || table->dptr == points->dptr) return fail(ctx, GZK_E_INVALID, "msm_precompute: table needs gzk_msm_table_points(n, window_bits) points of its own");
+    if (n == 0) return GZK_OK;
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    G1Affine* t = static_cast<G1Affine*>(table->dptr);
+    GZK_CUDA_TRY(ctx, cudaMemcpyAsync(t, points->dptr, n * sizeof(G1Affine), cudaMemcpyDeviceToDevice, ctx->stream));
+    for (uint32_t w = 1; w < windows; ++w)
+    {
+        LaunchScope scope(ctx, "msm_table_window");
+        msm_table_window_kernel<<<static_cast<unsigned>((n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(t + static_cast<size_t>(w - 1) * n,
+                                                                                                          t + static_cast<size_t>(w) * n, n, window_bits);
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    return finish_call(ctx, "invalid input");
+}
+
+extern "C" int gzk_msm_precomputed(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* table, size_t n, unsigned window_bits, uint8_t out[96])
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (out == nullptr) return fail(ctx, GZK_E_INVALID, "msm_precomputed: null output");
+    if (n == 0)
+    {
+        std::memset(out, 0, 96);
+        return GZK_OK;
+    }
+    if (scalars == nullptr || table == nullptr) return fail(ctx, GZK_E_INVALID, "msm_precomputed: null argument");
+    if (window_bits < 8 || window_bits > 24) return fail(ctx, GZK_E_INVALID, "msm_precomputed: window_bits must lie in [8, 24]");
+    if ((scalars->kind != GZK_KIND_FR && scalars->kind != GZK_KIND_FR_MONT) || scalars->count < n)
+        return fail(ctx, GZK_E_INVALID, "msm_precomputed: scalars must be an FR or FR_MONT buffer of n elements");
+    const MsmPlan plan = make_shared_plan(window_bits);
+    if (table->kind != GZK_KIND_G1 || table->count < n * plan.windows) return fail(ctx, GZK_E_INVALID, "msm_precomputed: table does not hold gzk_msm_table_points(n, window_bits) points");
+    if (n * plan.windows >= (1ULL << 31)) return fail(ctx, GZK_E_INVALID, "msm_precomputed: at most 2^31 - 1 table points per call");
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    return msm_run_plan(ctx, scalars, table, n, plan, out);
+}
 
 extern "C" int gzk_msm(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* points, size_t n, uint8_t out[96])
 {

@@ -33,6 +33,8 @@ def load_library():
         _lib = ctypes.CDLL(LIB_PATH)
         _lib.gzk_last_error.restype = ctypes.c_char_p
         _lib.gzk_last_error.argtypes = [ctypes.c_void_p]
+        _lib.gzk_msm_table_points.restype = ctypes.c_size_t
+        _lib.gzk_msm_window_bits.restype = ctypes.c_uint
         _lib.gzk_buf_count.restype = ctypes.c_size_t
         _lib.gzk_buf_count.argtypes = [ctypes.c_void_p]
         _lib.gzk_buf_kind.argtypes = [ctypes.c_void_p]
@@ -331,6 +333,21 @@ class Backend:
     def msm(self, scalars, points, n):
         out = np.zeros(96, dtype=np.uint8)
         self._check(self.lib.gzk_msm(self.ctx, scalars.handle, points.handle, _sz(n), _ptr(out)))
+        return out
+
+    def msm_window_bits(self, n):
+        return int(self.lib.gzk_msm_window_bits(_sz(n)))
+
+    def msm_precompute(self, points, n, window_bits=None):
+        """(table Buffer, window_bits): the shifted copies of a resident point set for msm_precomputed."""
+        window_bits = window_bits or self.msm_window_bits(n)
+        table = self.alloc(KIND_G1, int(self.lib.gzk_msm_table_points(_sz(n), ctypes.c_uint(window_bits))))
+        self._check(self.lib.gzk_msm_precompute(self.ctx, points.handle, _sz(n), ctypes.c_uint(window_bits), table.handle))
+        return table, window_bits
+
+    def msm_precomputed(self, scalars, table, n, window_bits):
+        out = np.zeros(96, dtype=np.uint8)
+        self._check(self.lib.gzk_msm_precomputed(self.ctx, scalars.handle, table.handle, _sz(n), ctypes.c_uint(window_bits), _ptr(out)))
         return out
 
     def srs_lagrange(self, log2n, base, tau):

@@ -139,3 +139,42 @@ def test_msm_skewed_scalars(be):
         got = be.msm(be.upload(fr_array(scalars), KIND_FR), pts, n)
         want = sum(k * s for k, s in zip(ks, scalars)) % R
         assert bytes(got) == pyref.g1_bytes(pyref.g1_mul(want, G0)), name
+
+
+@pytest.mark.parametrize("n,window_bits", [(1, 8), (37, 9), (300, 13), (5000, 16), (1 << 15, None)])
+def test_msm_precomputed_table_equals_plain_msm(be, n, window_bits):
+    """The shared-bucket MSM over the table of shifted points gives the point of gzk_msm (and of the
+    scalar identity) for uniform and for skewed scalars, canonical and Montgomery."""
+    from project_b200 import KIND_FR, KIND_FR_MONT
+
+    rng = random.Random(900 + n)
+    ks = pyref.rand_fr(rng, n)
+    if n >= 37:
+        ks[5] = 0           # a point at infinity among the bases
+        ks[7] = ks[6]
+    pts = be.g1_fixed_base_mul(G, be.upload(fr_array(ks), KIND_FR), n)
+    table, wb = be.msm_precompute(pts, n, window_bits)
+    assert table.count % n == 0 and table.count // n >= (255 + wb - 1) // wb
+    G0 = (pyref.GX, pyref.GY)
+    cases = {"uniform": pyref.rand_fr(rng, n), "ones": [1] * n, "minus one": [R - 1] * n,
+             "small signed": [rng.randrange(-40, 40) % R for _ in range(n)], "top": [(R - 1 - i) % R for i in range(n)]}
+    if n >= 37:
+        cases["uniform"][0:4] = [0, 1, R - 1, (1 << 254) % R]
+        cases["uniform"][7] = (R - cases["uniform"][6]) % R
+    for name, scalars in cases.items():
+        want = pyref.g1_bytes(pyref.g1_mul(sum(k * s for k, s in zip(ks, scalars)) % R, G0))
+        buf = be.upload(fr_array(scalars), KIND_FR)
+        assert bytes(be.msm_precomputed(buf, table, n, wb)) == want, name
+        assert bytes(be.msm(buf, pts, n)) == want, name
+    mont = be.upload(fr_array(cases["uniform"]), KIND_FR_MONT)
+    assert bytes(be.msm_precomputed(mont, table, n, wb)) == bytes(be.msm(mont, pts, n))
+    assert not be.msm_precomputed(mont, table, 0, wb).any()
+
+
+def test_msm_precomputed_rejects_short_table(be):
+    from project_b200 import KIND_FR, KIND_G1, GzkError
+
+    n = 64
+    pts = be.g1_fixed_base_mul(G, be.upload(fr_array(list(range(1, n + 1))), KIND_FR), n)
+    with pytest.raises(GzkError):
+        be.msm_precomputed(be.upload(fr_array([1] * n), KIND_FR), pts, n, 16)  # a plain point buffer is not a table
