@@ -192,15 +192,15 @@ namespace gzk
             // outer = 1 / (product of this thread's elements)
             Fr outer = mul(load_fr(block_inverses + blockIdx.x), mul(mul(left, warp_pre[warp]), mul(right, warp_suf[warp])));
             // walk the thread's elements backwards: inverse_j = outer * suffix_j * pre_j
-            Fr suffix = Fr::one();
+            Fr rest = outer;  // inverse of the product of the thread's elements 0 .. j
 #pragma unroll
             for (int j = kElems - 1; j >= 0; --j)
             {
                 const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
-                const Fr inverse = mul(outer, mul(pre[j], suffix));
+                const Fr inverse = mul(rest, pre[j]);
                 // omega^e = x - d_e: cheaper to rebuild than to keep in registers
                 if (e < a.n) store_fr(out + e, mul(mul(a.scale, sub(a.x, d[j])), inverse));
-                suffix = mul(suffix, d[j]);
+                if (j > 0) rest = mul(rest, d[j]);
             }
         }
     }
@@ -305,13 +305,13 @@ namespace gzk
             }
             __syncthreads();
             const Fr outer = mul(load_fr(block_inverses + blockIdx.x), mul(mul(left, warp_pre[warp]), mul(right, warp_suf[warp])));
-            Fr suffix = Fr::one();
+            Fr rest = mul(a.scale, outer);  // (x^n-1)/n over the product of the thread's denominators 0 .. j
 #pragma unroll
             for (int j = kElems - 1; j >= 0; --j)
             {
                 const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
-                const Fr scaled_inverse = mul(a.scale, mul(outer, mul(pre[j], suffix)));  // (x^n-1)/n / D_e
-                suffix = mul(suffix, d[j]);
+                const Fr scaled_inverse = mul(rest, pre[j]);  // (x^n-1)/n / D_e
+                if (j > 0) rest = mul(rest, d[j]);
                 if (e >= a.n) continue;
                 const Fr p1 = domain_point(a.lo, a.hi, a.lo_bits, e);
                 const Fr p2 = sqr(p1);

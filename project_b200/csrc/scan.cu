@@ -175,13 +175,13 @@ namespace gzk
                     cta_inverse = load_fr(a.cta_products + blockIdx.x);
                 }
                 const Fr outer = block_invert_products<kThreads>(mine, cta_inverse, slots);
-                Fr suffix = Fr::one();
+                Fr rest = outer;  // inverse of the product of the thread's rows 0 .. j
 #pragma unroll
                 for (int j = kElems - 1; j >= 0; --j)
                 {
                     const uint64_t e = base + j;
-                    const Fr inverse = mul(outer, mul(pre[j], suffix));
-                    suffix = mul(suffix, d[j]);
+                    const Fr inverse = mul(rest, pre[j]);
+                    if (j > 0) rest = mul(rest, d[j]);
                     if (e >= a.count)
                     {
                         term[j] = Fr::zero();
@@ -338,6 +338,95 @@ namespace gzk
             }
         }
 
+        // Sum of one Fr per thread over the CTA, returned to every thread.
+        __device__ __forceinline__ Fr cta_sum(Fr v, Fr* warp_slots)
+        {
+            const int lane = threadIdx.x & 31;
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                const Fr other = shfl_fr_idx(v, (lane + offset) & 31);
+                if (lane < offset) v = add(v, other);
+            }
+            if (lane == 0) warp_slots[threadIdx.x >> 5] = v;
+            __syncthreads();
+            Fr total = warp_slots[0];
+#pragma unroll
+            for (int w = 1; w < kWarps; ++w) total = add(total, warp_slots[w]);
+            __syncthreads();
+            return total;
+        }
+
+        // Fix-up that derives the offset of its chunk from the raw CTA aggregates itself (every
+        // CTA re-adds at most a few thousand 32-byte values from L2), which saves the separate
+        // single-CTA scan of the aggregates when there are few of them.  A CTA covers kThreads
+        // consecutive outputs, all inside one chunk of the main pass.
+        template <int OP>
+        __global__ void __launch_bounds__(kThreads) scan_fixup_fused_kernel(ScanArgs a, uint32_t ctas)
+        {
+            __shared__ Fr warp_slots[kWarps];
+            __shared__ int last_start;
+            const uint64_t first = static_cast<uint64_t>(blockIdx.x) * kThreads;
+            const uint64_t idx = first + threadIdx.x;
+            const uint32_t chunk = static_cast<uint32_t>(first / kChunk);
+            if (OP == kSegmented)
+            {
+                if (chunk == 0) return;
+                // the running segment reaches back to the last chunk in which a segment started
+                if (threadIdx.x == 0) last_start = -1;
+                __syncthreads();
+                int mine = -1;
+                for (uint32_t i = threadIdx.x; i < chunk; i += kThreads)
+                    if (a.agg_flag[i] != 0) mine = static_cast<int>(i);
+                if (mine >= 0) atomicMax(&last_start, mine);
+                __syncthreads();
+                const uint32_t from = last_start < 0 ? 0u : static_cast<uint32_t>(last_start);
+                Fr part = Fr::zero();
+                for (uint32_t i = from + threadIdx.x; i < chunk; i += kThreads) part = add(part, load_fr(a.agg_value + i));
+                const Fr offset = cta_sum(part, warp_slots);
+                if (idx < a.n && static_cast<uint32_t>(idx - static_cast<uint64_t>(chunk) * kChunk) < a.agg_first[chunk])
+                    store_fr(a.out + idx, add(load_fr_plain(a.out + idx), offset));
+                return;
+            }
+            // out[idx] for 1 <= idx <= count belongs to chunk (idx - 1) / kChunk: the CTA's first output sits
+            // one chunk lower when the CTA starts on a chunk boundary
+            const bool needs_total = first + kThreads > a.count + 1 || blockIdx.x == 0;
+            Fr before = Fr::zero(), rest = Fr::zero();
+            const uint32_t limit = needs_total ? ctas : chunk;
+            for (uint32_t i = threadIdx.x; i < limit; i += kThreads)
+            {
+                const Fr v = load_fr(a.agg_value + i);
+                if (i < chunk)
+                    before = add(before, v);
+                else
+                    rest = add(rest, v);
+            }
+            const Fr offset = cta_sum(before, warp_slots);
+            Fr total = offset;
+            if (needs_total) total = add(offset, cta_sum(rest, warp_slots));
+            if (blockIdx.x == 0 && threadIdx.x == 0) store_fr(a.total, total);
+            if (idx >= a.n) return;
+            if (idx == 0)
+            {
+                store_fr(a.out, Fr::zero());
+            }
+            else if (idx <= a.count)
+            {
+                if (idx - 1 >= static_cast<uint64_t>(chunk) * kChunk)
+                {
+                    if (chunk != 0) store_fr(a.out + idx, add(load_fr_plain(a.out + idx), offset));
+                }
+                else if (chunk >= 2)
+                {
+                    store_fr(a.out + idx, add(load_fr_plain(a.out + idx), sub(offset, load_fr(a.agg_value + (chunk - 1)))));
+                }
+            }
+            else
+            {
+                store_fr(a.out + idx, total);
+            }
+        }
+
         template <int OP>
         int run_scan(gzk_ctx* ctx, ScanArgs& args, bool inverting, uint8_t* total_out_host)
         {
@@ -376,15 +465,27 @@ namespace gzk
                     scan_main_kernel<OP, false><<<ctas, kThreads, 0, ctx->stream>>>(args);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
+            if (ctas <= 2048)
             {
-                LaunchScope scope(ctx, "scan_offsets");
-                scan_offsets_kernel<<<1, kThreads, 0, ctx->stream>>>(args.agg_value, args.agg_flag, ctas, args.total);
+                if (args.n > 0 || total_out_host != nullptr)
+                {
+                    LaunchScope scope(ctx, "scan_fixup");
+                    const uint64_t outputs = args.n > 0 ? args.n : 1;
+                    scan_fixup_fused_kernel<OP><<<static_cast<unsigned>((outputs + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(args, ctas);
+                }
             }
-            GZK_CUDA_TRY(ctx, cudaGetLastError());
-            if (args.n > 0)
+            else
             {
-                LaunchScope scope(ctx, "scan_fixup");
-                scan_fixup_kernel<OP><<<static_cast<unsigned>((args.n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(args);
+                {
+                    LaunchScope scope(ctx, "scan_offsets");
+                    scan_offsets_kernel<<<1, kThreads, 0, ctx->stream>>>(args.agg_value, args.agg_flag, ctas, args.total);
+                }
+                GZK_CUDA_TRY(ctx, cudaGetLastError());
+                if (args.n > 0)
+                {
+                    LaunchScope scope(ctx, "scan_fixup");
+                    scan_fixup_kernel<OP><<<static_cast<unsigned>((args.n + kThreads - 1) / kThreads), kThreads, 0, ctx->stream>>>(args);
+                }
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
             if (total_out_host == nullptr) return finish_call(ctx, "q_new must hold only 0 and 1");
