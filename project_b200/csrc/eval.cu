@@ -16,6 +16,7 @@
 // touch).  Units are dealt to warps in contiguous runs, which balances any K and
 // n over 148 SMs without atomics.  Each unit produces one 17-limb partial sum in
 // context-owned scratch.
+#include <atomic>
 #include <cstring>
 
 #include "common.cuh"
@@ -280,8 +281,8 @@ namespace gzk
         // kernels into their dynamic shared-memory size).  Allocates nothing.
         int blocks_per_sm(int p)
         {
-            static int cached[3] = {0, 0, 0};
-            if (cached[p] == 0)
+            static std::atomic<int> cached[3];  // zero-initialised; contexts on several host threads may race to fill a slot with the same value
+            if (cached[p].load(std::memory_order_relaxed) == 0)
             {
                 int nb = 0;
                 cudaError_t err;
@@ -295,9 +296,9 @@ namespace gzk
                     cudaFuncSetAttribute(eval_partial_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes(1)));
                     err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<1>, kThreads, smem_bytes(1));
                 }
-                cached[p] = (err == cudaSuccess && nb > 0) ? nb : 1;
+                cached[p].store((err == cudaSuccess && nb > 0) ? nb : 1, std::memory_order_relaxed);
             }
-            return cached[p];
+            return cached[p].load(std::memory_order_relaxed);
         }
 
         void launch_eval_partial(cudaStream_t stream, const EvalArgs& args, int p, unsigned blocks)

@@ -3,6 +3,7 @@
 // inversion.
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 
 #include "block.cuh"
@@ -231,6 +232,13 @@ namespace gzk
         {
             G1Affine* table = nullptr;  // [kWindows][kEntries], Montgomery affine
         };
+        // One table per (context, base).  Contexts live on different host threads, so the
+        // container is guarded; an entry itself is only ever touched by the thread of its context.
+        std::mutex& table_cache_mutex()
+        {
+            static std::mutex m;
+            return m;
+        }
         std::map<std::pair<gzk_ctx*, std::string>, BaseTable>& table_cache()
         {
             static std::map<std::pair<gzk_ctx*, std::string>, BaseTable> cache;
@@ -250,11 +258,14 @@ namespace gzk
         {
             const std::string key(reinterpret_cast<const char*>(base), 96);
             auto& cache = table_cache();
-            const auto it = cache.find({ctx, key});
-            if (it != cache.end())
             {
-                *out = it->second.table;
-                return GZK_OK;
+                std::lock_guard<std::mutex> lock(table_cache_mutex());
+                const auto it = cache.find({ctx, key});
+                if (it != cache.end())
+                {
+                    *out = it->second.table;
+                    return GZK_OK;
+                }
             }
             if (!fp_canonical(base) || !fp_canonical(base + 48)) return fail(ctx, GZK_E_INVALID, "g1: base coordinates are not canonical");
             G1Affine b;
@@ -286,7 +297,10 @@ namespace gzk
             GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
             GZK_CUDA_TRY(ctx, cudaFree(xyzz));
             GZK_CUDA_TRY(ctx, cudaFree(z));
-            cache[{ctx, key}] = t;
+            {
+                std::lock_guard<std::mutex> lock(table_cache_mutex());
+                cache[{ctx, key}] = t;
+            }
             *out = t.table;
             return GZK_OK;
         }
@@ -294,6 +308,7 @@ namespace gzk
 
     void g1_release_tables(gzk_ctx* ctx)
     {
+        std::lock_guard<std::mutex> lock(table_cache_mutex());
         auto& cache = table_cache();
         for (auto it = cache.begin(); it != cache.end();)
         {

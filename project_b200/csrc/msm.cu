@@ -6,8 +6,8 @@
 //   2. offsets    exclusive scan of the bucket counts (one CTA)
 //   3. scatter    (point index, sign) pairs are written bucket by bucket
 //   4. buckets    one thread per bucket adds its points (mixed XYZZ additions)
-//   5. bits       sum_j j*B_j is split by the bits of j: for every (window, bit) one
-//                 CTA sums the buckets whose multiplier has that bit set
+//   5. bits       sum_d d*B_d of a bucket set: row and column sums of the buckets laid out as a
+//                 matrix, then the two small weighted sums split by the bits of the multiplier
 //   6. finish     per window Horner over the bits, shift by 2^(c*w), sum, to affine
 //
 // With a precomputed table of the points shifted by every window (gzk_msm_precompute:
@@ -239,24 +239,6 @@ namespace gzk
             if (threadIdx.x == 0) store_xyzz(out + bb.bucket, slots[0]);
         }
 
-        // CTA (window w, bit b): sum of the buckets j (multiplier j+1) with bit b of (j+1) set
-        __global__ void __launch_bounds__(kThreads) msm_bits_kernel(const G1Xyzz* buckets, MsmPlan plan, G1Xyzz* bit_sums)
-        {
-            __shared__ G1Xyzz slots[kThreads];
-            const uint32_t w = blockIdx.x / plan.c, bit = blockIdx.x % plan.c;
-            G1Xyzz acc = G1Xyzz::infinity();
-            for (uint32_t j = threadIdx.x; j < plan.half; j += kThreads)
-                if (((j + 1) >> bit) & 1u) acc = g1_add(acc, load_xyzz(buckets + static_cast<uint64_t>(w) * plan.half + j));
-            slots[threadIdx.x] = acc;
-            __syncthreads();
-            for (uint32_t offset = kThreads / 2; offset > 0; offset >>= 1)
-            {
-                if (threadIdx.x < offset) slots[threadIdx.x] = g1_add(slots[threadIdx.x], slots[threadIdx.x + offset]);
-                __syncthreads();
-            }
-            if (threadIdx.x == 0) store_xyzz(bit_sums + blockIdx.x, slots[0]);
-        }
-
         // one thread per window, then a tree over the windows; thread 0 converts to affine
         __global__ void __launch_bounds__(kMaxWindows) msm_finish_kernel(const G1Xyzz* bit_sums, MsmPlan plan, G1Xyzz* out_xyzz,
                                                                         G1Affine* out_canonical)
@@ -310,10 +292,13 @@ namespace gzk
             return slots[0];
         }
         // CTAs [0, rows): row sums; CTAs [rows, rows + cols): column sums.  rc = [rows row sums][cols column sums]
+        // (blockIdx.y = window when every window has its own bucket set)
         __global__ void __launch_bounds__(kThreads) msm_rowcol_kernel(const G1Xyzz* buckets, uint32_t half, uint32_t h, uint32_t rows, G1Xyzz* rc)
         {
             __shared__ G1Xyzz slots[kThreads];
             const uint32_t cols = 1u << h;
+            buckets += static_cast<uint64_t>(blockIdx.y) * half;
+            rc += static_cast<uint64_t>(blockIdx.y) * (rows + cols);
             G1Xyzz acc = G1Xyzz::infinity();
             if (blockIdx.x < rows)
             {
@@ -341,6 +326,8 @@ namespace gzk
         {
             __shared__ G1Xyzz slots[kThreads];
             const uint32_t b = blockIdx.x;
+            rc += static_cast<uint64_t>(blockIdx.y) * (rows + (1u << h));
+            bit_sums += static_cast<uint64_t>(blockIdx.y) * gridDim.x;
             const bool from_cols = b < h;
             const uint32_t count = from_cols ? (1u << h) : rows;
             const uint32_t bit = from_cols ? b : b - h;
@@ -461,7 +448,8 @@ namespace gzk
         const size_t big_bytes = max_items * (sizeof(BigItem) + sizeof(G1Xyzz)) + max_big * sizeof(BigBucket) + 64;
         const uint32_t split_h = (plan.c - 1) / 2;                          // low bits of the bucket multiplier
         const uint32_t split_rows = (1u << (plan.c - 1 - split_h)) + 1;     // values of the high part, 0 .. 2^(c-1-h)
-        const size_t chunk_bytes = plan.shared ? (static_cast<size_t>(split_rows) + (1u << split_h)) * sizeof(G1Xyzz) : 0;
+        const uint32_t bucket_sets = plan.shared ? 1u : plan.windows;
+        const size_t chunk_bytes = static_cast<size_t>(bucket_sets) * (static_cast<size_t>(split_rows) + (1u << split_h)) * sizeof(G1Xyzz);
         const size_t total = big_bytes + 2 * code_bytes + 3 * bucket_u32 + buckets * sizeof(G1Xyzz) + static_cast<size_t>(plan.windows) * plan.c * sizeof(G1Xyzz) +
                              chunk_bytes + sizeof(G1Xyzz) + sizeof(G1Affine) + 8192;
         void* scratch = nullptr;
@@ -536,26 +524,19 @@ namespace gzk
                 big_counters, big_buckets, big_partial, bucket_points);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        if (plan.shared)
         {
-            {
-                LaunchScope scope(ctx, "msm_bits", 2);
-                msm_rowcol_kernel<<<split_rows + (1u << split_h), kThreads, 0, ctx->stream>>>(bucket_points, plan.half, split_h, split_rows, bit_partial);
-                msm_rowcol_bits_kernel<<<plan.c, kThreads, 0, ctx->stream>>>(bit_partial, split_h, split_rows, bit_sums);
-            }
-            GZK_CUDA_TRY(ctx, cudaGetLastError());
-            LaunchScope scope(ctx, "msm_finish");
-            msm_finish_shared_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan.c, result_xyzz, result_affine);
+            LaunchScope scope(ctx, "msm_bits", 2);
+            msm_rowcol_kernel<<<dim3(split_rows + (1u << split_h), bucket_sets), kThreads, 0, ctx->stream>>>(bucket_points, plan.half, split_h, split_rows,
+                                                                                                    bit_partial);
+            msm_rowcol_bits_kernel<<<dim3(plan.c, bucket_sets), kThreads, 0, ctx->stream>>>(bit_partial, split_h, split_rows, bit_sums);
         }
-        else
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
         {
-            {
-                LaunchScope scope(ctx, "msm_bits");
-                msm_bits_kernel<<<plan.windows * plan.c, kThreads, 0, ctx->stream>>>(bucket_points, plan, bit_sums);
-            }
-            GZK_CUDA_TRY(ctx, cudaGetLastError());
             LaunchScope scope(ctx, "msm_finish");
-            msm_finish_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan, result_xyzz, result_affine);
+            if (plan.shared)
+                msm_finish_shared_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan.c, result_xyzz, result_affine);
+            else
+                msm_finish_kernel<<<1, kMaxWindows, 0, ctx->stream>>>(bit_sums, plan, result_xyzz, result_affine);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out_host, result_affine, 96, cudaMemcpyDeviceToHost, ctx->stream));

@@ -39,3 +39,28 @@ def test_no_cpu_fallback_without_gpu():
 
     with pytest.raises(GzkError):
         Backend(0)
+
+
+def test_msm_window_choice_is_host_arithmetic():
+    """gzk_msm_window_bits / gzk_msm_table_points run on the host: the window avoids widths whose top
+    window is only a few bits wide for 255-bit scalars, and the table holds one copy of the points per window."""
+    import ctypes
+
+    from project_b200 import load_library
+
+    lib = load_library()
+    lib.gzk_msm_window_bits.restype = ctypes.c_uint
+    lib.gzk_msm_table_points.restype = ctypes.c_size_t
+    for log2n in range(10, 27):
+        n = 1 << log2n
+        c = lib.gzk_msm_window_bits(ctypes.c_size_t(n))
+        assert 15 <= c <= 24
+        full = -(-255 // c)
+        top_bits = 255 - c * (full - 1)
+        assert top_bits >= 12, (log2n, c)
+        points = lib.gzk_msm_table_points(ctypes.c_size_t(n), ctypes.c_uint(c))
+        assert points in (n * full, n * (full + 1))
+    # 17-bit windows need a 16th window: the top digit of a scalar just below the group order exceeds 2^16
+    assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(17)) == 16
+    assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(16)) == 16
+    assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(20)) == 13
