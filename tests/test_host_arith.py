@@ -15,6 +15,11 @@ def test_device_arithmetic_matches_oracle_on_host():
     _run(os.path.join(ROOT, "tests", "host", "mp_host_check.cpp"))
 
 
+def test_proof_byte_codec_on_host():
+    """Size formula of the reference's proof_size_bytes, byte round trip and reader errors (pure host code)."""
+    _run(os.path.join(ROOT, "tests", "host", "proof_codec_check.cpp"))
+
+
 def _run(src):
     with tempfile.TemporaryDirectory() as tmp:
         exe = os.path.join(tmp, "mp_host_check")
