@@ -16,8 +16,17 @@ namespace gzk
         // out[i] = left[i] + lambda * right[i] for i < count, zero tail.
         __global__ void weighted_sum_kernel(ColRef left, ColRef right, Fr lambda, uint64_t count, uint64_t n, Fr* out)
         {
+            // canonical columns are combined as stored (lambda in Montgomery form times a canonical value
+            // is the canonical product) and converted once: two multiplications per row instead of three
+            const bool stored = deficit(left) == 1 && deficit(right) == 1;
             for (uint64_t i = grid_index(); i < n; i += grid_stride())
-                store_fr(out + i, i < count ? add(col_load_mont(left, i), mul(lambda, col_load_mont(right, i))) : Fr::zero());
+            {
+                Fr v = Fr::zero();
+                if (i < count)
+                    v = stored ? to_mont(add(col_load_stored(left, i), mul(lambda, col_load_stored(right, i))))
+                               : add(col_load_mont(left, i), mul(lambda, col_load_mont(right, i)));
+                store_fr(out + i, v);
+            }
         }
 
         // out[row*width + c] = row_id[row] + eta_i * feature_index[c] + eta_v * features[row*width + c]
@@ -25,12 +34,17 @@ namespace gzk
                                             Fr eta_index, Fr eta_value, Fr* out)
         {
             const uint64_t total = rows * width;
+            const bool stored = deficit(row_ids) == 1 && deficit(feature_indices) == 1 && deficit(features) == 1;  // all canonical: convert once
             for (uint64_t i = grid_index(); i < total; i += grid_stride())
             {
                 const uint64_t row = i / width;
                 const uint32_t c = static_cast<uint32_t>(i - row * width);
-                const Fr v = add(add(col_load_mont(row_ids, row), mul(eta_index, col_load_mont(feature_indices, c))),
-                                 mul(eta_value, col_load_mont(features, i)));
+                Fr v;
+                if (stored)
+                    v = to_mont(add(add(col_load_stored(row_ids, row), mul(eta_index, col_load_stored(feature_indices, c))),
+                                    mul(eta_value, col_load_stored(features, i))));
+                else
+                    v = add(add(col_load_mont(row_ids, row), mul(eta_index, col_load_mont(feature_indices, c))), mul(eta_value, col_load_mont(features, i)));
                 store_fr(out + i, v);
             }
         }

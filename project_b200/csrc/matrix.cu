@@ -21,7 +21,9 @@ namespace gzk
         // ---- Horner ------------------------------------------------------------------
         // CTA b owns coefficients [b*span, (b+1)*span).  Thread t runs Horner in x^T over
         // the coefficients s+t, s+t+T, ... (coalesced across the CTA), scales by x^t; the
-        // CTA sum is scaled by x^s.  One Montgomery multiplication per coefficient.
+        // CTA sum is scaled by x^s.  One Montgomery multiplication per coefficient: the coefficients
+        // enter as stored (x in Montgomery form times a canonical value stays canonical), so a canonical
+        // matrix gives the canonical result directly and a Montgomery one is converted at the end.
         __global__ void __launch_bounds__(kThreads) horner_kernel(ColRef coeffs, uint64_t total, uint64_t span, Fr x, Fr x_stride,
                                                                   Fr* partial)
         {
@@ -35,7 +37,7 @@ namespace gzk
                 for (uint64_t j = steps + 1; j-- > 0;)
                 {
                     acc = mul(acc, x_stride);
-                    acc = add(acc, col_load_mont(coeffs, s + threadIdx.x + j * kThreads));
+                    acc = add(acc, col_load_stored(coeffs, s + threadIdx.x + j * kThreads));
                 }
                 acc = mul(acc, pow_u64(x, threadIdx.x));
             }
@@ -57,12 +59,12 @@ namespace gzk
             }
         }
 
-        __global__ void sum_partials_kernel(const Fr* partial, uint32_t count, Fr* out_canonical)
+        __global__ void sum_partials_kernel(const Fr* partial, uint32_t count, int montgomery, Fr* out_canonical)
         {
             if (threadIdx.x != 0 || blockIdx.x != 0) return;
             Fr sum = Fr::zero();
             for (uint32_t i = 0; i < count; ++i) sum = add(sum, load_fr_plain(partial + i));
-            store_fr(out_canonical, from_mont(sum));
+            store_fr(out_canonical, montgomery ? from_mont(sum) : sum);
         }
 
         // ---- fold rows ----------------------------------------------------------------
@@ -221,7 +223,7 @@ extern "C"
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         {
             LaunchScope scope(ctx, "horner_sum");
-            sum_partials_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(ctas), partial + ctas);
+            sum_partials_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(ctas), matrix->kind == GZK_KIND_FR_MONT ? 1 : 0, partial + ctas);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out, partial + ctas, 32, cudaMemcpyDeviceToHost, ctx->stream));

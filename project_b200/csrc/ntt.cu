@@ -225,11 +225,16 @@ namespace gzk
         __global__ void fold_kernel(ColRef table, Fr r, uint64_t half, Fr* out)
         {
             const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+            // A canonical table enters as stored: r (Montgomery) times a canonical difference is the canonical
+            // product, so lo + r (hi - lo) is formed in canonical form and converted once (two
+            // multiplications per output instead of three); a Montgomery table needs one.
+            const bool canonical = deficit(table) != 0;
             for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < half; i += stride)
             {
-                const Fr lo = col_load_mont(table, 2 * i);
-                const Fr hi = col_load_mont(table, 2 * i + 1);
-                store_fr(out + i, add(lo, mul(r, sub(hi, lo))));
+                const Fr lo = col_load_stored(table, 2 * i);
+                const Fr hi = col_load_stored(table, 2 * i + 1);
+                const Fr folded = add(lo, mul(r, sub(hi, lo)));
+                store_fr(out + i, canonical ? to_mont(folded) : folded);
             }
         }
 
@@ -240,10 +245,16 @@ namespace gzk
             __shared__ Fr ws0[kThreads / 32], ws1[kThreads / 32];
             Fr s0 = Fr::zero(), s1 = Fr::zero();
             const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
+            // sums of the stored residues; a canonical table is converted once per thread, not per element
             for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < half; i += stride)
             {
-                s0 = add(s0, col_load_mont(table, 2 * i));
-                s1 = add(s1, col_load_mont(table, 2 * i + 1));
+                s0 = add(s0, col_load_stored(table, 2 * i));
+                s1 = add(s1, col_load_stored(table, 2 * i + 1));
+            }
+            if (deficit(table) != 0)
+            {
+                s0 = to_mont(s0);
+                s1 = to_mont(s1);
             }
             const int lane = threadIdx.x & 31;
 #pragma unroll

@@ -61,24 +61,6 @@ namespace gzk
         // terms the deficits of numerator and denominator cancel, which saves the
         // conversion multiplication of every load.  All deficits depend only on the buffer
         // kinds, so every branch on them is uniform over the grid.
-        __device__ __forceinline__ int deficit(const ColRef& c) { return c.kind == GZK_KIND_FR_MONT ? 0 : 1; }
-
-        __device__ __forceinline__ Fr col_load_stored(const ColRef& c, uint64_t i)
-        {
-            if (c.kind == GZK_KIND_FR_MONT || c.kind == GZK_KIND_FR) return load_fr(static_cast<const Fr*>(c.ptr) + i);
-            Fr f = Fr::zero();
-            if (c.kind == GZK_KIND_U32)
-            {
-                f.l[0] = __ldg(static_cast<const uint32_t*>(c.ptr) + i);
-                return f;
-            }
-            const long long v = __ldg(static_cast<const long long*>(c.ptr) + i);
-            const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
-            f.l[0] = static_cast<uint32_t>(mag);
-            f.l[1] = static_cast<uint32_t>(mag >> 32);
-            return v < 0 ? neg(f) : f;
-        }
-
         // v carries `d` missing factors of R (d > 0) or -d surplus ones (d < 0).
         __device__ __forceinline__ Fr fix_scale(Fr v, int d)
         {
