@@ -17,6 +17,7 @@
 // n over 148 SMs without atomics.  Each unit produces one 17-limb partial sum in
 // context-owned scratch.
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.cuh"
@@ -474,7 +475,9 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     // several times over, but at most 256 tiles so the partial buffer stays small.
     const uint64_t resident_blocks = static_cast<uint64_t>(ctx->sm_count) * blocks_per_sm(p_count >= 2 ? 2 : 1);
     const uint64_t warps_total = resident_blocks * (kThreads / 32);
-    uint64_t want_tiles = (6 * warps_total + k_count - 1) / k_count;
+    uint64_t per_warp = 8;
+    if (const char* forced = std::getenv("GZK_EVAL_UNITS_PER_WARP")) per_warp = static_cast<uint64_t>(std::atoi(forced)) > 0 ? std::atoi(forced) : per_warp;  // tuning experiments only
+    uint64_t want_tiles = (per_warp * warps_total + k_count - 1) / k_count;
     uint64_t max_tiles = (len + 255) / 256;
     if (max_tiles == 0) max_tiles = 1;
     // the partial buffer (tiles x P x K x 68 B) is kept below 64 MiB, and below 4096 tiles
@@ -484,6 +487,24 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     if (want_tiles > tile_cap) want_tiles = tile_cap;
     if (want_tiles > max_tiles) want_tiles = max_tiles;
     if (want_tiles == 0) want_tiles = 1;
+    // Every warp takes the same number of (tile, column) units, give or take one: among the tile counts close to
+    // the wanted one take the one that leaves the fewest warps idle while the last units run.
+    {
+        uint64_t best = want_tiles;
+        double best_waste = 2.0;
+        for (uint64_t t = want_tiles; t >= 1 && t + want_tiles / 4 >= want_tiles; --t)
+        {
+            const uint64_t units = t * k_count;
+            const uint64_t rounds = (units + warps_total - 1) / warps_total;
+            const double waste = 1.0 - static_cast<double>(units) / static_cast<double>(rounds * warps_total);
+            if (waste < best_waste - 1e-9)
+            {
+                best_waste = waste;
+                best = t;
+            }
+        }
+        want_tiles = best;
+    }
     uint64_t tile_rows = (len + want_tiles - 1) / want_tiles;
     tile_rows = (tile_rows + kChunkRows - 1) / kChunkRows * kChunkRows;
     if (tile_rows == 0) tile_rows = kChunkRows;
@@ -650,6 +671,24 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     if (want_tiles > kStaticMaxTiles) want_tiles = kStaticMaxTiles;
     if (want_tiles > max_tiles) want_tiles = max_tiles;
     if (want_tiles == 0) want_tiles = 1;
+    // Every warp takes the same number of (tile, column) units, give or take one: among the tile counts close to
+    // the wanted one take the one that leaves the fewest warps idle while the last units run.
+    {
+        uint64_t best = want_tiles;
+        double best_waste = 2.0;
+        for (uint64_t t = want_tiles; t >= 1 && t + want_tiles / 4 >= want_tiles; --t)
+        {
+            const uint64_t units = t * k_count;
+            const uint64_t rounds = (units + warps_total - 1) / warps_total;
+            const double waste = 1.0 - static_cast<double>(units) / static_cast<double>(rounds * warps_total);
+            if (waste < best_waste - 1e-9)
+            {
+                best_waste = waste;
+                best = t;
+            }
+        }
+        want_tiles = best;
+    }
     uint64_t tile_rows = (len + want_tiles - 1) / want_tiles;
     tile_rows = (tile_rows + kChunkRows - 1) / kChunkRows * kChunkRows;
     if (tile_rows == 0) tile_rows = kChunkRows;
