@@ -717,7 +717,7 @@ def run_sweep_sharded(be, G, stream, rank, world, device, small=False):
     import torch
     import torch.distributed as dist
 
-    from project_b200 import KIND_FR, KIND_FR_MONT, g1_sum
+    from project_b200 import KIND_FR, KIND_FR_MONT, fr_sum, g1_sum
     from project_b200 import sharded_ntt as sn
 
     rng = np.random.default_rng(1000 + rank)
@@ -756,6 +756,18 @@ def run_sweep_sharded(be, G, stream, rank, world, device, small=False):
             exchange.run(sn.forward(be, vec, lg, rank, world, work=work))
 
         ms = timed_ms(transform)
+        # self-check without a CPU pass: X[0] (first element of rank 0's block) is the sum of all inputs
+        sums = be.sumcheck_round_sums(vec, local)
+        mine = torch.from_numpy(fr_sum(np.stack([sums[0], sums[1]]))).cuda()
+        every = torch.empty((world, 32), dtype=torch.uint8, device="cuda")
+        dist.all_gather_into_tensor(every, mine)
+        good = 1
+        if rank == 0 and not np.array_equal(work[1].download(count=1)[0], fr_sum(every.cpu().numpy())):
+            good = 0
+        verdict = torch.tensor([good], device="cuda", dtype=torch.int32)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)  # every rank learns the outcome: none is left waiting in a collective
+        if int(verdict.item()) == 0:
+            raise RuntimeError("row-sharded transform: X[0] does not equal the sum of the inputs")
         be.timing_reset()
         be.timing_enable(True)
         transform()

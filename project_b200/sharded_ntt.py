@@ -69,12 +69,12 @@ def inverse(be, xt, log2n, rank, world, work=None):
     return b
 
 
-def run_emulated(backends, inputs, log2n, direction=forward):
-    """All ranks in one process: backends[g] / inputs[g] per rank; the exchange goes through the host."""
+def run_emulated(backends, inputs, log2n, direction=forward, works=None):
+    """All ranks in one process: backends[g] / inputs[g] (/ works[g]) per rank; the exchange goes through the host."""
     import numpy as np
 
     world = len(backends)
-    gens = [direction(backends[g], inputs[g], log2n, g, world) for g in range(world)]
+    gens = [direction(backends[g], inputs[g], log2n, g, world, work=None if works is None else works[g]) for g in range(world)]
     sends = [next(gen) for gen in gens]
     while True:
         host = [s.download().reshape(world, -1, 32) for s in sends]

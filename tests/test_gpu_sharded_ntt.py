@@ -73,3 +73,35 @@ def test_sharded_forward_matches_oracle_and_inverse_round_trips(be, log2n, world
     back = sn.run_emulated([be] * world, outs, log2n, sn.inverse)
     for g, b in enumerate(back):
         assert np.array_equal(b.download(), x[g * rows1 * n2:(g + 1) * rows1 * n2])
+
+
+def test_sharded_transform_with_preallocated_work_buffers(be):
+    """The allocation-free form used under NCCL: two work buffers per rank, refilled and retagged in place."""
+    from project_b200 import KIND_FR, KIND_FR_MONT
+    from project_b200 import sharded_ntt as sn
+
+    rng = np.random.default_rng(4242)
+    log2n, world = 13, 4
+    n = 1 << log2n
+    x = rand_fr(rng, n)
+    want = ora.ntt(x)
+    l1, l2 = sn.split(log2n, world)
+    n1, n2 = 1 << l1, 1 << l2
+    rows1 = n1 // world
+    local = rows1 * n2
+    inputs = [be.upload(x[g * local:(g + 1) * local], KIND_FR) for g in range(world)]
+    works = [(be.alloc(KIND_FR, local), be.alloc(KIND_FR_MONT, local)) for _ in range(world)]
+    for _ in range(2):  # twice: the second run starts from work buffers left in the Montgomery kind
+        outs = sn.run_emulated([be] * world, inputs, log2n, sn.forward, works=works)
+        for g, o in enumerate(outs):
+            assert o is works[g][1]
+            block = o.download().reshape(rows1, n2, 32)
+            k1 = g * rows1 + np.arange(rows1)
+            for k2 in range(0, n2, 7):
+                assert np.array_equal(block[:, k2], want[k1 + n1 * k2])
+    # the inverse from a copy of the transposed output, through its own work buffers
+    xt = [be.upload(o.download(), KIND_FR_MONT) for o in outs]
+    works_inv = [(be.alloc(KIND_FR_MONT, local), be.alloc(KIND_FR_MONT, local)) for _ in range(world)]
+    back = sn.run_emulated([be] * world, xt, log2n, sn.inverse, works=works_inv)
+    for g, b in enumerate(back):
+        assert np.array_equal(b.download(), x[g * local:(g + 1) * local])
