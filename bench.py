@@ -682,7 +682,12 @@ def run_sweep(be, rng, G, stream, small=False):
                   "field_mults_per_s": (n // 2) * lg / ms * 1e3}
     r = rand_fr(1)[0]
     ms = timed_ms(lambda: be.fold(vec, n, r, out=res))
-    out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6}
+    out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6, "forms": "canonical table -> Montgomery output (2 multiplications per output)"}
+    # a table kept in one form through the rounds of a sumcheck costs one multiplication per output
+    half = be.alloc(KIND_FR, n // 2)
+    ms = timed_ms(lambda: be.fold(vec, n, r, out=half))
+    out["fold_same_form"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6, "forms": "canonical table -> canonical output (1 multiplication per output)"}
+    half.free()
     for b in (vec, res):
         b.free()
     # fp64 forward of one attention head at the mid-size graph's shape (time only: not a roofline target)

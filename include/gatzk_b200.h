@@ -329,7 +329,9 @@ int gzk_msm_precomputed(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* tab
  * be NULL (shift 1).  `out` is FR_MONT and must differ from `in`.
  * gzk_coset_lde: evaluations on the 2^log2n domain -> evaluations on shift * the
  * 2^(log2n+log2_blowup) domain.
- * gzk_fold: out[i] = t[2i] + r*(t[2i+1] - t[2i]), i < n/2 (one sumcheck round). */
+ * gzk_fold: out[i] = t[2i] + r*(t[2i+1] - t[2i]), i < n/2 (one sumcheck round); out is an FR or
+ *   FR_MONT buffer - a table kept in one form (canonical in and out, or Montgomery in and out) costs
+ *   one multiplication per output, a change of form one more. */
 int gzk_ntt(gzk_ctx* ctx, const gzk_buf* in, gzk_buf* out, unsigned log2n, size_t batch, int inverse, const uint8_t* coset_shift);
 int gzk_coset_lde(gzk_ctx* ctx, const gzk_buf* in, unsigned log2n, unsigned log2_blowup, const uint8_t shift[32], gzk_buf* out);
 int gzk_fold(gzk_ctx* ctx, const gzk_buf* table, size_t n, const uint8_t challenge[32], gzk_buf* out);

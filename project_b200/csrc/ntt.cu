@@ -222,19 +222,22 @@ namespace gzk
             return GZK_OK;
         }
 
-        __global__ void fold_kernel(ColRef table, Fr r, uint64_t half, Fr* out)
+        __global__ void fold_kernel(ColRef table, Fr r, uint64_t half, Fr* out, bool out_canonical)
         {
             const uint64_t stride = static_cast<uint64_t>(gridDim.x) * blockDim.x;
             // A canonical table enters as stored: r (Montgomery) times a canonical difference is the canonical
             // product, so lo + r (hi - lo) is formed in canonical form and converted once (two
-            // multiplications per output instead of three); a Montgomery table needs one.
+            // multiplications per output instead of three); a Montgomery table needs one, and so does a canonical
+            // table folded into a canonical (FR) output: a table that stays in one form costs one per round.
             const bool canonical = deficit(table) != 0;
             for (uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < half; i += stride)
             {
                 const Fr lo = col_load_stored(table, 2 * i);
                 const Fr hi = col_load_stored(table, 2 * i + 1);
-                const Fr folded = add(lo, mul(r, sub(hi, lo)));
-                store_fr(out + i, canonical ? to_mont(folded) : folded);
+                Fr folded = add(lo, mul(r, sub(hi, lo)));  // in the form of the table
+                if (canonical && !out_canonical) folded = to_mont(folded);
+                if (!canonical && out_canonical) folded = from_mont(folded);
+                store_fr(out + i, folded);
             }
         }
 
@@ -410,7 +413,8 @@ extern "C"
         if (n < 2) return GZK_OK;
         if (table == nullptr || out == nullptr || challenge == nullptr) return fail(ctx, GZK_E_INVALID, "fold: null argument");
         if (table->kind == GZK_KIND_F64 || table->kind == GZK_KIND_G1 || table->count < n) return fail(ctx, GZK_E_INVALID, "fold: table buffer too small or of the wrong kind");
-        if (out->kind != GZK_KIND_FR_MONT || out->count < n / 2) return fail(ctx, GZK_E_INVALID, "fold: output must be a Montgomery buffer of n/2 elements");
+        if ((out->kind != GZK_KIND_FR_MONT && out->kind != GZK_KIND_FR) || out->count < n / 2)
+            return fail(ctx, GZK_E_INVALID, "fold: output must be an FR or FR_MONT buffer of n/2 elements");
         Fr r;
         int rc = scalar_mont(ctx, challenge, &r);
         if (rc != GZK_OK) return rc;
@@ -424,7 +428,7 @@ extern "C"
         if (blocks > cap) blocks = cap;
         {
             LaunchScope scope(ctx, "fold");
-            fold_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(t, r, half, static_cast<Fr*>(out->dptr));
+            fold_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, ctx->stream>>>(t, r, half, static_cast<Fr*>(out->dptr), out->kind == GZK_KIND_FR);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return finish_call(ctx, "invalid input");

@@ -88,7 +88,16 @@ def test_fold(be, n):
     rng = np.random.default_rng(n)
     t = rand_fr(rng, n)
     r = rand_fr(rng, 1)[0]
-    assert np.array_equal(be.fold(be.upload(t, KIND_FR), n, r).download(), ora.fold(t, r))
+    want = ora.fold(t, r)
+    assert np.array_equal(be.fold(be.upload(t, KIND_FR), n, r).download(), want)
+    # every pairing of table form and output form
+    from project_b200 import KIND_FR_MONT
+
+    for table_kind in (KIND_FR, KIND_FR_MONT):
+        for out_kind in (KIND_FR, KIND_FR_MONT):
+            out = be.alloc(out_kind, n // 2)
+            be.fold(be.upload(t, table_kind), n, r, out=out)
+            assert np.array_equal(out.download(), want), (table_kind, out_kind)
 
 
 def test_sumcheck_rounds_fold_to_the_multilinear_evaluation(be):
