@@ -64,3 +64,16 @@ def test_msm_window_choice_is_host_arithmetic():
     assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(17)) == 16
     assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(16)) == 16
     assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(20)) == 13
+
+
+def test_header_is_plain_c(tmp_path):
+    """The boundary is a C ABI: the header must compile as C99 (and as C++) with nothing but its own declarations."""
+    import os
+    import subprocess
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    src = tmp_path / "include_only.c"
+    src.write_text('#include "gatzk_b200.h"\nint main(void) { return GZK_OK; }\n')
+    inc = os.path.join(root, "include")
+    subprocess.run(["gcc", "-std=c99", "-Wall", "-Wextra", "-pedantic", "-Werror", "-fsyntax-only", f"-I{inc}", str(src)], check=True)
+    subprocess.run(["g++", "-std=c++17", "-Wall", "-Wextra", "-Werror", "-fsyntax-only", "-x", "c++", f"-I{inc}", str(src)], check=True)
