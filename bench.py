@@ -585,17 +585,25 @@ def main():
                     buf.upload_async(host[:part], offset=done)
                     done += part
 
+        # Columns are independent, so a domain is uploaded and evaluated in groups of columns: the
+        # evaluation of one group runs while the next group travels, and only the last group's
+        # kernels are left after the last byte has arrived.
+        group_columns = 96
+        units = []
+        for d in domains:
+            for first in range(0, len(d["cols"]), group_columns):
+                units.append(dict(d, cols=d["cols"][first:first + group_columns]))
+
         def step_e2e():
-            # uploads run on the copy stream: the columns of the next domain travel while the
-            # current one is evaluated, and the first upload overlaps with the builders
+            # uploads run on the copy stream; the first one overlaps with the builders
             outs = []
-            queue_uploads(domains[0])
+            queue_uploads(units[0])
             step_builders()
-            for i, d in enumerate(domains):
+            for i, u in enumerate(units):
                 be.copy_fence()
-                if i + 1 < len(domains):
-                    queue_uploads(domains[i + 1])
-                outs.append(step_domain(d))
+                if i + 1 < len(units):
+                    queue_uploads(units[i + 1])
+                outs.append(step_domain(u))
             return outs
 
         e2e_steps = max(1, min(args.steps, 3))
