@@ -2,7 +2,7 @@
 //   w_i = (x^n - 1)/n * omega^i / (x - omega^i).
 // The n field inversions are one batch inversion, organised for the GPU as
 //   pass 1  per-CTA product of its 1024 denominators,
-//   pass 2  one CTA inverts all CTA products (scan of products + ONE Fermat
+//   pass 2  one CTA inverts all CTA products (scan of products + ONE field
 //           inversion for the whole vector),
 //   pass 3  per-CTA: in-CTA exclusive prefix/suffix products turn the CTA inverse
 //           into the 1024 element inverses; the weight is written once, coalesced.

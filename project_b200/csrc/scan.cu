@@ -5,13 +5,16 @@
 // batch inversion for the whole column.
 //
 // Passes (no inter-CTA waiting anywhere, so nothing can spin):
-//   1. (inverting ops) per-CTA product of the 1024 denominators of its rows
-//   2. (inverting ops) one CTA inverts all CTA products: a single Fermat inversion
-//   3. per-CTA: rebuild denominators, recover each inverse from in-CTA
-//      prefix/suffix products, form the terms, scan them locally, write the local
-//      running sums and the CTA aggregate
-//   4. one CTA turns the aggregates into exclusive CTA offsets and the grand total
-//   5. elementwise fix-up: add the CTA offset, fill the tail with the total
+//   main    per CTA of 512 rows: build the denominators, invert their product (each CTA
+//           inverts its own when the whole grid is resident at once; very long columns
+//           collect the CTA products in a first pass and invert them in one CTA), recover
+//           each inverse from in-CTA prefix products, form the terms, scan them locally,
+//           write the local running sums and the CTA aggregate
+//   fix-up  elementwise: add the offset of the row's CTA (re-derived from the raw
+//           aggregates by every fix-up CTA when there are at most 2048 of them, else
+//           scanned by one CTA first), fill the tail with the total
+// Operands enter the multiplier as they are stored (canonical or Montgomery) with the
+// missing powers of R tracked per buffer kind, see "residues with a tracked power of R".
 #include <cstring>
 
 #include "block.cuh"
