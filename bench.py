@@ -551,7 +551,9 @@ def main():
     local_bytes = sum(32 * (k * valid + valid) + 2 * 32 * (k + 1) * local_rows[name] for name, lg, k, valid in local_workload)
     local_terms = sum(k * valid + 4 * k * local_rows[name] for name, lg, k, valid in local_workload)
     achieved = local_bytes * iso_steps / (eval_ms * 1e-3) / 1e9 if eval_ms > 0 else 0.0
-    mac_peak = be.measure_mac_peak(2, 20000)
+    from project_b200.lib import measure_mac_peak
+
+    mac_peak = measure_mac_peak(local_rank, 2, 20000)
     products_per_s = local_terms * iso_steps / (eval_ms * 1e-3) if eval_ms > 0 else 0.0
     roofline = {
         "bound": "hbm", "kernel": "eval_partial_kernel (packed evaluation, all launches of a step; durations from the one-thread pass, each launch by itself)", "achieved": achieved,

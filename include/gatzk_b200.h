@@ -75,10 +75,14 @@ int gzk_timing_reset(gzk_ctx* ctx);
 int gzk_timing_family_count(gzk_ctx* ctx);
 int gzk_timing_get(gzk_ctx* ctx, int index, const char** name, uint64_t* launches, double* total_ms);
 
-/* Integer-pipe ceiling for the roofline of the inner-product kernels: 8x8-limb
- * multiply-accumulates per second over the whole GPU on register operands, with
- * 1 or 2 independent accumulators per lane.  No reference counterpart. */
-int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, double* products_per_second);
+/* Test facility for the device-side failure handling.  The packed-evaluation kernel waits
+ * for its bulk copies with a bounded number of polls; when a wait runs out the kernel raises
+ * GZK_E_TIMEOUT in the status word and returns.  While this switch is on (process-wide),
+ * every launch of that kernel arms its chunk barriers but issues no copy and polls only a
+ * few hundred times, so the waits do run out - with nothing in flight and no fault - and the
+ * error path can be exercised: gzk_eval_batch returns GZK_E_TIMEOUT, gzk_eval_batch_static
+ * poisons its outputs.  No reference counterpart (the reference has no device-side waits). */
+int gzk_debug_inject_eval_stall(int on);
 
 /* ---- device buffers -----------------------------------------------------------
  * Replace the host std::vector<FieldElement> column storage of
@@ -402,9 +406,19 @@ int gzk_fr_add_scalar(gzk_ctx* ctx, gzk_buf* buf, size_t offset, size_t count, c
  *  - the first call on each device also looks up the device address of the array
  *    and the SM count; make that first call before starting any stream capture.
  *  - all calls on a device share the one array, which keeps whatever the previous
- *    call left in it.  Every slot a call reads it has written itself first, so
- *    nothing needs clearing, but two calls that overlap on the GPU (different
- *    streams, or different host threads) race on the array: serialise them.
+ *    call left in it.  The call clears the one word that must start at zero (its
+ *    status word) on `stream` before the kernels; every other slot a call reads it
+ *    has written itself first.  Two calls that overlap on the GPU (different streams,
+ *    or different host threads) race on the array: serialise them.
+ *  - pointers are checked before anything is launched: field-element columns, the
+ *    weights and out_device must be 32-byte aligned, I64 columns 8-byte, U32 columns
+ *    4-byte aligned, and all must be device memory of `device`; otherwise
+ *    GZK_E_INVALID and nothing runs.
+ *  - device-side failure: if a bounded wait inside the kernel gives up (GZK_E_TIMEOUT
+ *    in gzk_eval_batch), this entry point has no host-side result to put a code in -
+ *    it returns when the work is queued - so every one of the call's outputs is set
+ *    to 32 bytes of 0xFF, which is not a canonical field element.  A caller that
+ *    reads 0xFF..FF from out_device must treat the whole call as failed.
  *  - err / err_cap: optional buffer for a failure message. */
 int gzk_eval_batch_static(int device, void* stream, const void* const* col_ptrs, const int* col_kinds, size_t k_count,
                           size_t len, unsigned log2n, const void* weights_mont, const uint64_t* rotations,

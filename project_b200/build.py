@@ -8,6 +8,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(HERE, "libgatzk_b200.so")
+TUNING_LIB_PATH = os.path.join(HERE, "libgatzk_b200_tuning.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -55,6 +56,10 @@ def build(verbose=False, force=False):
                 raise RuntimeError(f"nvcc failed on {path}")
     if jobs or not os.path.exists(LIB_PATH):
         subprocess.run([nvcc, "-shared", "-o", LIB_PATH, *objs, "-gencode", "arch=compute_100a,code=sm_100a"], check=True)
+    # measurement aids (the integer-pipe ceiling) live in a library of their own
+    tuning_src = os.path.join(CSRC, "tuning", "mac_peak.cu")
+    if force or _stale(TUNING_LIB_PATH, [tuning_src] + headers):
+        subprocess.run([nvcc, *NVCC_FLAGS[:-2], "-shared", tuning_src, "-o", TUNING_LIB_PATH], check=True)
     return LIB_PATH
 
 

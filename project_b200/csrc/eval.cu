@@ -42,6 +42,8 @@ namespace gzk
             uint64_t rot[2];
             uint32_t* partial;        // [tile][p][k][17]
             int* status;              // raised when a bounded wait gives up
+            uint32_t wait_limit;      // polls a wait on a chunk may take before it gives up
+            uint32_t skip_copies;     // stall injection (gzk_debug_inject_eval_stall): announce the chunks but issue no copy
         };
 
         // ---- per-warp TMA ring -------------------------------------------------------
@@ -91,9 +93,9 @@ namespace gzk
             return done != 0;
         }
         // Bounded wait: false when the limit ran out.
-        __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity)
+        __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, uint32_t limit)
         {
-            for (uint32_t spin = 0; spin < kWaitLimit; ++spin)
+            for (uint32_t spin = 0; spin < limit; ++spin)
                 if (mbar_try_wait(bar, parity)) return true;
             return false;
         }
@@ -162,6 +164,7 @@ namespace gzk
                         const uint32_t bar = smem_u32(bars + slot);
                         unsigned char* dst = ring + static_cast<size_t>(slot) * slot_bytes(P);
                         mbar_expect_tx(bar, bytes * (1 + P));
+                        if (a.skip_copies) return;  // injected stall: the barrier is armed, nothing is in flight
                         bulk_load(smem_u32(dst), base + row0 * 32, bytes, bar);
 #pragma unroll
                         for (int p = 0; p < P; ++p)
@@ -188,7 +191,7 @@ namespace gzk
                         }
                         const uint32_t slot = (ring_pos + ch) % kStages;
                         const uint32_t parity = ((ring_pos + ch) / kStages) & 1u;
-                        ok = mbar_wait(smem_u32(bars + slot), parity);
+                        ok = mbar_wait(smem_u32(bars + slot), parity, a.wait_limit);
                         if (!__all_sync(0xffffffffu, ok))
                         {
                             ok = false;
@@ -216,7 +219,7 @@ namespace gzk
                         // bounded chance to land, and leave
                         if (lane == 0) atomicExch(a.status, GZK_E_TIMEOUT);
                         for (uint32_t j = 0; j < issued && j < chunks; ++j)
-                            mbar_wait(smem_u32(bars + (ring_pos + j) % kStages), ((ring_pos + j) / kStages) & 1u);
+                            mbar_wait(smem_u32(bars + (ring_pos + j) % kStages), ((ring_pos + j) / kStages) & 1u, a.wait_limit);
                         return;
                     }
                     ring_pos += chunks;
@@ -278,12 +281,17 @@ namespace gzk
             }
         }
 
-        // Resident CTAs per SM of the two kernel variants (queried once; also opts the
-        // kernels into their dynamic shared-memory size).  Allocates nothing.
+        // Resident CTAs per SM of the two kernel variants on the CURRENT device (queried once per
+        // device; also opts the kernels into their dynamic shared-memory size, which is a
+        // per-device attribute).  Allocates nothing.
+        constexpr int kOptInDevices = 64;
         int blocks_per_sm(int p)
         {
-            static std::atomic<int> cached[3];  // zero-initialised; contexts on several host threads may race to fill a slot with the same value
-            if (cached[p].load(std::memory_order_relaxed) == 0)
+            static std::atomic<int> per_device[kOptInDevices][3];  // zero-initialised; contexts on several host threads may race to fill a slot with the same value
+            int device = 0;
+            cudaGetDevice(&device);
+            std::atomic<int>* cached = per_device[device >= 0 && device < kOptInDevices ? device : 0];
+            if (device < 0 || device >= kOptInDevices || cached[p].load(std::memory_order_relaxed) == 0)
             {
                 int nb = 0;
                 cudaError_t err;
@@ -302,9 +310,16 @@ namespace gzk
             return cached[p].load(std::memory_order_relaxed);
         }
 
-        void launch_eval_partial(cudaStream_t stream, const EvalArgs& args, int p, unsigned blocks)
+        // Stall injection for tests of the bounded waits (gzk_debug_inject_eval_stall).
+        std::atomic<int> g_inject_stall{0};
+        constexpr uint32_t kInjectedWaitLimit = 1u << 10;
+
+        void launch_eval_partial(cudaStream_t stream, EvalArgs args, int p, unsigned blocks)
         {
-            blocks_per_sm(p);  // makes sure the shared-memory opt-in has happened
+            blocks_per_sm(p);  // makes sure the shared-memory opt-in has happened on this device
+            const bool inject = g_inject_stall.load(std::memory_order_relaxed) != 0;
+            args.wait_limit = inject ? kInjectedWaitLimit : kWaitLimit;
+            args.skip_copies = inject ? 1u : 0u;
             if (p == 2)
                 eval_partial_kernel<2><<<blocks, kThreads, smem_bytes(2), stream>>>(args);
             else
@@ -313,12 +328,27 @@ namespace gzk
 
         // One warp per (rotation, column) pair: the lanes sum the per-tile partials, the
         // warp adds them up exactly, lane 0 reduces once and writes the result.
+        // `poison_status`: when given and raised (a bounded wait of the partial kernel gave up, so some
+        // partial sums were never written), every output becomes 32 bytes of 0xFF - not a canonical
+        // field element - instead of a sum over stale partials.
         __global__ void eval_finish_kernel(const uint32_t* partial, const int* kinds, uint32_t tiles, uint32_t p_count,
-                                           uint32_t k_count, Fr* out_canonical, int uniform_kind = -1, int out_montgomery = 0)
+                                           uint32_t k_count, Fr* out_canonical, int uniform_kind = -1, int out_montgomery = 0,
+                                           const int* poison_status = nullptr)
         {
             const uint32_t lane = threadIdx.x & 31;
             const uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
             if (idx >= p_count * k_count) return;
+            if (poison_status != nullptr && *poison_status != 0)
+            {
+                if (lane == 0)
+                {
+                    Fr bad;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) bad.l[i] = 0xffffffffu;
+                    store_fr(out_canonical + idx, bad);
+                }
+                return;
+            }
             const uint32_t p = idx / k_count;
             const uint32_t k = idx - p * k_count;
             uint32_t acc[kAccLimbs];
@@ -366,46 +396,6 @@ namespace gzk
 
 namespace gzk
 {
-    namespace
-    {
-        // Integer-pipe ceiling of the inner product arithmetic: every lane runs the
-        // 8x8-limb multiply-accumulate on register operands, no memory traffic.
-        template <int CHAINS>
-        __global__ void __launch_bounds__(kThreads) mac_peak_kernel(uint32_t iters, uint32_t* sink)
-        {
-            WideAcc acc[CHAINS];
-            Fr w, f;
-#pragma unroll
-            for (int i = 0; i < 8; ++i)
-            {
-                w.l[i] = threadIdx.x * 2654435761u + i * 40503u + blockIdx.x;
-                f.l[i] = threadIdx.x * 2246822519u + i * 3266489917u + 17u;
-            }
-#pragma unroll
-            for (int c = 0; c < CHAINS; ++c) acc[c].clear();
-            for (uint32_t it = 0; it < iters; ++it)
-            {
-#pragma unroll
-                for (int c = 0; c < CHAINS; ++c) acc[c].template mac<8>(w.l, f.l);
-                w.l[0] += it;  // keep the operands loop-variant
-                f.l[7] ^= it;
-            }
-            uint32_t sum[kAccLimbs];
-            uint32_t x = 0;
-#pragma unroll
-            for (int c = 0; c < CHAINS; ++c)
-            {
-                acc[c].fold(sum);
-#pragma unroll
-                for (int i = 0; i < kAccLimbs; ++i) x ^= sum[i];
-            }
-            if (x == 0x12345678u) sink[0] = x;  // practically never: defeats dead-code elimination
-        }
-    }
-}
-
-namespace gzk
-{
     // For the other inner-product kernels of the library, which produce partial sums
     // in the same [tile][p][k][17] layout: sum over tiles, reduce once, write results.
     int launch_eval_finish(gzk_ctx* ctx, const uint32_t* partial, int uniform_kind, uint32_t tiles, uint32_t k_count,
@@ -420,41 +410,6 @@ namespace gzk
 }
 
 using namespace gzk;
-
-// Measures the multiply-accumulate ceiling (8x8-limb products per second over the
-// whole GPU) with `chains` independent accumulators per lane (1 or 2).
-extern "C" int gzk_measure_mac_peak(gzk_ctx* ctx, int chains, uint32_t iters, double* products_per_second)
-{
-    if (ctx == nullptr || products_per_second == nullptr) return GZK_E_INVALID;
-    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-    int nb = 0;
-    if (chains == 2)
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, mac_peak_kernel<2>, kThreads, 0);
-    else
-        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, mac_peak_kernel<1>, kThreads, 0);
-    if (nb <= 0) nb = 1;
-    const unsigned blocks = static_cast<unsigned>(ctx->sm_count * nb);
-    cudaEvent_t e0, e1;
-    GZK_CUDA_TRY(ctx, cudaEventCreate(&e0));
-    GZK_CUDA_TRY(ctx, cudaEventCreate(&e1));
-    for (int rep = 0; rep < 2; ++rep)
-    {
-        GZK_CUDA_TRY(ctx, cudaEventRecord(e0, ctx->stream));
-        if (chains == 2)
-            mac_peak_kernel<2><<<blocks, kThreads, 0, ctx->stream>>>(iters, reinterpret_cast<uint32_t*>(ctx->d_status) + 8);
-        else
-            mac_peak_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(iters, reinterpret_cast<uint32_t*>(ctx->d_status) + 8);
-        GZK_CUDA_TRY(ctx, cudaEventRecord(e1, ctx->stream));
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
-    }
-    float ms = 0.f;
-    GZK_CUDA_TRY(ctx, cudaEventElapsedTime(&ms, e0, e1));
-    cudaEventDestroy(e0);
-    cudaEventDestroy(e1);
-    const double products = static_cast<double>(blocks) * kThreads * static_cast<double>(iters) * (chains == 2 ? 2 : 1);
-    *products_per_second = products / (ms * 1e-3);
-    return GZK_OK;
-}
 
 // Shared body of gzk_eval_batch and gzk_eval_batch_range.  `rotations` are already the
 // effective ones: row c of a column meets weights[(c - rotation) mod n] of the buffer.
@@ -476,7 +431,9 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     const uint64_t resident_blocks = static_cast<uint64_t>(ctx->sm_count) * blocks_per_sm(p_count >= 2 ? 2 : 1);
     const uint64_t warps_total = resident_blocks * (kThreads / 32);
     uint64_t per_warp = 8;
-    if (const char* forced = std::getenv("GZK_EVAL_UNITS_PER_WARP")) per_warp = static_cast<uint64_t>(std::atoi(forced)) > 0 ? std::atoi(forced) : per_warp;  // tuning experiments only
+#ifdef GZK_BUILD_TUNING
+    if (const char* forced = std::getenv("GZK_EVAL_UNITS_PER_WARP")) per_warp = static_cast<uint64_t>(std::atoi(forced)) > 0 ? std::atoi(forced) : per_warp;
+#endif
     uint64_t want_tiles = (per_warp * warps_total + k_count - 1) / k_count;
     uint64_t max_tiles = (len + 255) / 256;
     if (max_tiles == 0) max_tiles = 1;
@@ -641,6 +598,19 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     if (len > n) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: len exceeds the domain size");
     for (size_t p = 0; p < p_count; ++p)
         if (rotations[p] >= n) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: rotation out of range");
+    // The kernels read field elements as 16-byte vectors and through 16-byte bulk copies: a
+    // misaligned or foreign pointer would fault on the GPU, so it is refused here, before any
+    // launch.  cudaPointerGetAttributes is a query; it allocates nothing.
+    auto device_memory_ok = [&](const void* p, size_t align) {
+        if (reinterpret_cast<uintptr_t>(p) % align != 0) return false;
+        cudaPointerAttributes attr{};
+        if (cudaPointerGetAttributes(&attr, p) != cudaSuccess)
+        {
+            cudaGetLastError();
+            return false;
+        }
+        return attr.type == cudaMemoryTypeDevice && attr.device == device;
+    };
     for (size_t k = 0; k < k_count; ++k)
     {
         if (col_ptrs[k] == nullptr) return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: null column pointer");
@@ -648,6 +618,14 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
             return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: unknown column kind");
     }
     if (cudaSetDevice(device) != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: cudaSetDevice failed");
+    for (size_t k = 0; k < k_count; ++k)
+    {
+        const size_t align = col_kinds[k] == GZK_KIND_U32 ? 4 : col_kinds[k] == GZK_KIND_I64 ? 8 : 32;
+        if (!device_memory_ok(col_ptrs[k], align))
+            return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: a column pointer is misaligned (32 bytes for field elements, 8 for I64, 4 for U32) or is not memory of this GPU");
+    }
+    if (!device_memory_ok(weights_mont, 32) || !device_memory_ok(out_device, 32))
+        return static_fail(err, err_cap, GZK_E_INVALID, "eval_batch_static: weights / output pointer is misaligned (32 bytes) or is not memory of this GPU");
     if (g_static_addr[device] == nullptr)
     {
         // one-time set-up for this device, with the device current
@@ -700,6 +678,9 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     std::memcpy(table + kStaticMaxColumns * sizeof(void*), col_kinds, k_count * sizeof(int));
     if (cudaMemcpyAsync(scratch, table, kStaticTableBytes, cudaMemcpyHostToDevice, s) != cudaSuccess)
         return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: copying the column table failed");
+    // the array keeps what the previous call left: the status word must start at zero
+    if (cudaMemsetAsync(scratch + kStaticStatusOffset, 0, sizeof(int), s) != cudaSuccess)
+        return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: clearing the status word failed");
 
     EvalArgs args;
     args.cols = reinterpret_cast<const void* const*>(scratch);
@@ -722,8 +703,18 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
     eval_finish_kernel<<<(outs + 3) / 4, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
-                                                         static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device));
+                                                         static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device), -1, 0, args.status);
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
+    return GZK_OK;
+}
+
+// Test facility for the bounded waits of the packed-evaluation kernel: while switched on, every
+// launch of that kernel (all contexts of the process, gzk_eval_batch_static included) arms its
+// chunk barriers but issues no bulk copy and polls each barrier only a few hundred times, so the
+// waits run out, the kernel raises its status word and returns with nothing in flight.
+extern "C" int gzk_debug_inject_eval_stall(int on)
+{
+    g_inject_stall.store(on != 0 ? 1 : 0, std::memory_order_relaxed);
     return GZK_OK;
 }
 

@@ -422,7 +422,9 @@ namespace gzk
             // larger windows mean fewer mixed additions (n per window) but 2^(c-1) * c / 2 full
             // additions per window in the bit-split reduction; log2(n) - 7 balances the two
             int c = static_cast<int>(log2n) - 6;
-            if (const char* forced = std::getenv("GZK_MSM_WINDOW")) c = std::atoi(forced);  // tuning experiments only
+#ifdef GZK_BUILD_TUNING
+            if (const char* forced = std::getenv("GZK_MSM_WINDOW")) c = std::atoi(forced);
+#endif
             if (c < 8) c = 8;
             if (c > 16) c = 16;
             MsmPlan p;
@@ -647,7 +649,8 @@ extern "C" int gzk_msm(gzk_ctx* ctx, const gzk_buf* scalars, const gzk_buf* poin
     if ((scalars->kind != GZK_KIND_FR && scalars->kind != GZK_KIND_FR_MONT) || scalars->count < n)
         return fail(ctx, GZK_E_INVALID, "msm: scalars must be an FR or FR_MONT buffer of n elements");
     if (points->kind != GZK_KIND_G1 || points->count < n) return fail(ctx, GZK_E_INVALID, "msm: points must be a G1 buffer of n elements");
-    if (n >= (1ULL << 31)) return fail(ctx, GZK_E_INVALID, "msm: at most 2^31 - 1 points per call");
+    // the counting sort addresses n * windows (point, window) entries with 32-bit offsets
+    if (n * make_plan(n).windows >= (1ULL << 31)) return fail(ctx, GZK_E_INVALID, "msm: at most 2^31 - 1 (point, window) entries per call (about 2^26 points); split the point range and add the results with gzk_g1_sum");
     GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
     return msm_run(ctx, scalars, points, n, out);
 }

@@ -182,10 +182,6 @@ class Backend:
             out[name.value.decode()] = (int(launches.value), float(ms.value))
         return out
 
-    def measure_mac_peak(self, chains=1, iters=20000):
-        out = ctypes.c_double()
-        self._check(self.lib.gzk_measure_mac_peak(self.ctx, int(chains), ctypes.c_uint32(iters), ctypes.byref(out)))
-        return out.value
 
     @property
     def stream(self):
@@ -447,6 +443,26 @@ def eval_batch_static(device, stream, col_ptrs, col_kinds, length, log2n, weight
                                    ctypes.c_void_p(weights_ptr), _ptr(rot), _sz(rot.size), ctypes.c_void_p(out_ptr), err, _sz(256))
     if rc != 0:
         raise GzkError(rc, err.value.decode())
+
+
+def inject_eval_stall(on):
+    """gzk_debug_inject_eval_stall: makes the bounded waits of the packed-evaluation kernel run out (tests only)."""
+    load_library().gzk_debug_inject_eval_stall(int(bool(on)))
+
+
+TUNING_LIB_PATH = os.path.join(HERE, "libgatzk_b200_tuning.so")
+
+
+def measure_mac_peak(device=0, chains=1, iters=20000):
+    """Integer-pipe ceiling (8x8-limb multiply-accumulates per second) from the separate tuning library."""
+    if not os.path.exists(TUNING_LIB_PATH):
+        raise RuntimeError(f"{TUNING_LIB_PATH} is missing: build it with `python -m project_b200.build`")
+    lib = ctypes.CDLL(TUNING_LIB_PATH)
+    out = ctypes.c_double()
+    rc = lib.gzk_tuning_mac_peak(int(device), int(chains), ctypes.c_uint32(iters), ctypes.byref(out))
+    if rc != 0:
+        raise GzkError(2, f"gzk_tuning_mac_peak: CUDA error {rc}")
+    return out.value
 
 
 def fr_sum(values):

@@ -6,10 +6,13 @@ import re
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def declared_symbols():
+LIBRARY_OF_HEADER = {"gatzk_b200.h": "libgatzk_b200.so", "gatzk_b200_tuning.h": "libgatzk_b200_tuning.so"}
+
+
+def declared_symbols(header=None):
     names = []
     for fname in sorted(os.listdir(os.path.join(ROOT, "include"))):
-        if not fname.endswith(".h"):
+        if not fname.endswith(".h") or (header is not None and fname != header):
             continue
         text = open(os.path.join(ROOT, "include", fname)).read()
         text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
@@ -21,11 +24,14 @@ def test_library_exports_every_declared_symbol():
     import __graft_entry__ as entry
 
     entry.build()
-    lib = ctypes.CDLL(os.path.join(ROOT, "project_b200", "libgatzk_b200.so"))
-    names = declared_symbols()
-    assert len(names) >= 15
-    missing = [n for n in names if not hasattr(lib, n)]
-    assert not missing, f"declared in include/*.h but not exported: {missing}"
+    headers = [f for f in sorted(os.listdir(os.path.join(ROOT, "include"))) if f.endswith(".h")]
+    assert set(headers) == set(LIBRARY_OF_HEADER), "every header of include/ must name the library that exports it"
+    for header in headers:
+        lib = ctypes.CDLL(os.path.join(ROOT, "project_b200", LIBRARY_OF_HEADER[header]))
+        names = declared_symbols(header)
+        assert len(names) >= (15 if header == "gatzk_b200.h" else 1)
+        missing = [n for n in names if not hasattr(lib, n)]
+        assert not missing, f"declared in include/{header} but not exported: {missing}"
 
 
 def test_no_cpu_fallback_without_gpu():

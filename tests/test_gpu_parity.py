@@ -181,3 +181,32 @@ def test_golden_fixtures_through_the_c_abi(be):
     bufs = [be.upload(hx(lg[k]).reshape(-1, 32), KIND_FR) for k in ("table", "query", "mult", "q_table", "q_query")]
     n = bufs[0].count
     assert be.logup_accumulator(*bufs, n, hx(lg["beta"]), lg["active"]).download().tobytes().hex() == lg["out"]
+
+
+def test_bounded_wait_that_runs_out_returns_timeout():
+    """Failure handling without a fault: with the stall injection on, the kernel's chunk barriers are armed
+    but no copy is issued, every bounded wait gives up, and the call returns GZK_E_TIMEOUT (4); the context
+    stays usable and the next call is correct."""
+    from project_b200 import GzkError
+    from project_b200.lib import inject_eval_stall
+
+    be = Backend(0)
+    rng = np.random.default_rng(11)
+    log2n, k = 11, 4
+    n = 1 << log2n
+    cols = rng.integers(0, 256, size=(k, n, 32), dtype=np.uint8)
+    cols[:, :, 31] &= 0x3F
+    x = np.zeros(32, dtype=np.uint8)
+    x[0] = 9
+    w = be.bary_weights(log2n, x)
+    bufs = [be.upload(cols[i], KIND_FR) for i in range(k)]
+    inject_eval_stall(True)
+    try:
+        with pytest.raises(GzkError) as info:
+            be.eval_batch(bufs, n, log2n, w, (0, 1))
+        assert info.value.code == 4
+    finally:
+        inject_eval_stall(False)
+    got = be.eval_batch(bufs, n, log2n, w, (0, 1))
+    assert np.array_equal(got, ora.eval_rotations(cols, w.download(), (0, 1)))
+    be.close()

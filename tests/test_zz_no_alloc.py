@@ -58,4 +58,46 @@ def test_static_entry_point_matches_regular_one_twice():
         eval_batch_static(0, be.stream, [col.device_ptr] * 257, [KIND_FR] * 257, 16, 4, w.device_ptr, (0,), out.device_ptr)
     with pytest.raises(GzkError, match="2 rotations"):
         eval_batch_static(0, be.stream, [col.device_ptr], [KIND_FR], 16, 4, w.device_ptr, (0, 1, 2), out.device_ptr)
+    # a misaligned or non-device pointer is refused on the host, before anything is launched
+    with pytest.raises(GzkError, match="misaligned"):
+        eval_batch_static(0, be.stream, [col.device_ptr + 4], [KIND_FR], 15, 4, w.device_ptr, (0,), out.device_ptr)
+    with pytest.raises(GzkError, match="misaligned"):
+        eval_batch_static(0, be.stream, [col.device_ptr], [KIND_FR], 16, 4, w.device_ptr + 16, (0,), out.device_ptr)
+    host_memory = np.zeros(16 * 32 + 64, dtype=np.uint8)
+    host_ptr = (host_memory.ctypes.data + 31) & ~31
+    with pytest.raises(GzkError, match="not memory of this GPU"):
+        eval_batch_static(0, be.stream, [host_ptr], [KIND_FR], 16, 4, w.device_ptr, (0,), out.device_ptr)
+    be.close()
+
+
+def test_static_entry_point_poisons_outputs_when_a_wait_runs_out():
+    """A bounded wait that gives up must not come back as a plausible result: with the stall
+    injection on, the outputs of the call are 0xFF bytes; the next call (injection off)
+    clears the status word itself and is correct again."""
+    from project_b200 import KIND_FR, Backend
+    from project_b200.lib import eval_batch_static, inject_eval_stall
+
+    be = Backend(0)
+    rng = np.random.default_rng(5)
+    log2n, k = 10, 3
+    n = 1 << log2n
+    x = np.zeros(32, dtype=np.uint8)
+    x[0] = 77
+    w = be.bary_weights(log2n, x)
+    host = _columns(rng, k, n)
+    bufs = [be.upload(host[i], KIND_FR) for i in range(k)]
+    want = be.eval_batch(bufs, n, log2n, w, (0, 1))
+    out = be.alloc(KIND_FR, 2 * k)
+    be.synchronize()
+    args = (0, be.stream, [b.device_ptr for b in bufs], [b.kind for b in bufs], n, log2n, w.device_ptr, (0, 1), out.device_ptr)
+    inject_eval_stall(True)
+    try:
+        eval_batch_static(*args)
+        be.synchronize()
+    finally:
+        inject_eval_stall(False)
+    assert np.all(out.download() == 0xFF)
+    eval_batch_static(*args)
+    be.synchronize()
+    assert np.array_equal(out.download().reshape(2, k, 32), want)
     be.close()
