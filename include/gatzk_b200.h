@@ -143,6 +143,15 @@ int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf*
 int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                    const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host);
 
+/* The same sums left on the device, for consumers that are themselves on the device (the
+ * same-base G1 multiplication of a commit barrier, an exchange of partial sums between GPUs):
+ * out[out_offset + p*k_count + k], canonical for an FR buffer, Montgomery for an FR_MONT one.
+ * Nothing is read back, so in deferred mode these calls only queue kernels.  Together with
+ * gzk_matrix_horner_device and gzk_g1_fixed_base_mul they form KZG::commit_batch
+ * (src/crypto/kzg.cpp:458-542) with ONE read-back per batch of columns. */
+int gzk_eval_batch_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
+                          const gzk_buf* weights, const uint64_t* rotations, size_t p_count, gzk_buf* out, size_t out_offset);
+
 /* ---- a7: LogUp and route running sums ----------------------------------------------
  * Input columns may be of any kind; `out` is FR_MONT with count >= n.  One batch
  * inversion per call; GZK_E_DOMAIN ("batch_invert encountered zero") when a
@@ -192,6 +201,10 @@ int gzk_fold_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols,
                   gzk_buf* out);
 int gzk_linear_form_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* column_powers, gzk_buf* out);
 int gzk_powers(gzk_ctx* ctx, const uint8_t challenge[32], size_t count, gzk_buf* out);
+/* gzk_matrix_horner with the value left in out[out_offset] on the device (FR: canonical, FR_MONT:
+ * Montgomery form). */
+int gzk_matrix_horner_device(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const uint8_t x[32], gzk_buf* out,
+                             size_t out_offset);
 
 /* ---- a10: witness-column leaves ---------------------------------------------------------------
  * gzk_weighted_sum: out[i] = left[i] + lambda*right[i], i < count, zero tail
@@ -220,6 +233,37 @@ int gzk_histogram(gzk_ctx* ctx, const gzk_buf* indices, size_t count, size_t dom
 int gzk_quantize(gzk_ctx* ctx, const gzk_buf* values, size_t count, gzk_buf* out);
 int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
                           size_t domain_size, gzk_buf* out);
+
+/* ---- a10: column packs and lookup multiplicities ---------------------------------------------------
+ * gzk_linear_combination: out[i] = sum_j coefficients[j] * cols[j][i] for i < count, zero tail;
+ *   1 to 8 terms, coefficients = terms x 32 bytes.  The routing-table packs with up to six
+ *   challenge powers (src/protocol/trace.cpp:2978-3006), table packs T_x + eta*T_y
+ *   (cached_pair_lookup_table, trace.cpp:1958-1988) and the average of the output heads
+ *   (average_field_matrices, trace.cpp:994-1018) are of this shape.
+ * gzk_mul_columns: out[i] = left[i] * right[i] for i < count, zero tail (the products
+ *   alpha * H_star_edge of trace.cpp:2716-2719).
+ * gzk_banded_lookup_multiplicity: multiplicity column of a lookup into one of the static
+ *   tables.  The reference finds the table row of every query in a hash map and counts the hits
+ *   (build_single_lookup_artifacts / build_pair_lookup_artifacts + multiplicity_from_indices,
+ *   trace.cpp:1916-1933, 2011-2096).  Its tables (make_range_table, make_lrelu_table,
+ *   make_elu_table, make_exp_table, src/protocol/prover.cpp:460-535) are all "banded": row
+ *   band*(x - x_min) + j holds the j-th candidate second component for first component x, so the
+ *   row is arithmetic on x plus a scan of `band` candidates table_y[...] (first match wins, as the
+ *   hash map keeps the first of equal pairs).  x / y: I64 or U32 query columns (y and table_y NULL
+ *   for the single-column range table, band 1); out: U32 column of domain_size.  A query that is
+ *   not in the table gives GZK_E_INVALID "lookup query escaped static table", as the reference throws.
+ * gzk_buf_zero: clears a buffer (the zero tails of padded columns).
+ * gzk_copy_block: dst[dst_offset + r*dst_stride + c] = src[src_offset + r*src_stride + c] for
+ *   r < rows, c < width: concatenation of per-head matrices (model::forward_note_style,
+ *   src/model/gat.cpp:1155-1194) and flattening / padding of matrices into columns. */
+int gzk_linear_combination(gzk_ctx* ctx, const gzk_buf* const* cols, const uint8_t* coefficients, size_t terms, size_t count,
+                           size_t domain_size, gzk_buf* out);
+int gzk_mul_columns(gzk_ctx* ctx, const gzk_buf* left, const gzk_buf* right, size_t count, size_t domain_size, gzk_buf* out);
+int gzk_banded_lookup_multiplicity(gzk_ctx* ctx, const gzk_buf* x, const gzk_buf* y, size_t count, int64_t x_min, size_t band,
+                                   const gzk_buf* table_y, size_t table_size, size_t domain_size, gzk_buf* out);
+int gzk_buf_zero(gzk_ctx* ctx, gzk_buf* buf);
+int gzk_copy_block(gzk_ctx* ctx, const gzk_buf* src, size_t src_offset, size_t src_stride, gzk_buf* dst, size_t dst_offset,
+                   size_t dst_stride, size_t rows, size_t width);
 
 /* ---- a11: public feature-domain columns that are never materialised ---------------------------
  * out[0..4] = sum_{i < rows*feature_count} w[i] * {1, i / fc, i % fc, abs_ids[i / fc],
@@ -366,6 +410,8 @@ int gzk_sumcheck_round_sums(gzk_ctx* ctx, const gzk_buf* table, size_t n, uint8_
  * gzk_eval_batch_range: partial sums of gzk_eval_batch over the local rows
  *   [row_offset, row_offset+len) given a weight slice starting at weights_first that
  *   covers row_offset-rot .. row_offset+len-1-rot for every rotation.
+ * gzk_eval_batch_range_device: the same partial sums left in a device buffer (see
+ *   gzk_eval_batch_device), ready for an all-gather between GPUs.
  * gzk_fr_sum: out[i] = sum_g values[g][i] over `groups` GPUs (host arithmetic).
  * gzk_g1_sum: sum of `count` affine points (host arithmetic): the per-GPU results of an
  *   MSM whose point range was split over the GPUs. */
@@ -373,6 +419,9 @@ int gzk_bary_weights_range(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], ui
 int gzk_eval_batch_range(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, uint64_t row_offset, unsigned log2n,
                          const gzk_buf* weights, uint64_t weights_first, const uint64_t* rotations, size_t p_count,
                          uint8_t* out_host);
+int gzk_eval_batch_range_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, uint64_t row_offset, unsigned log2n,
+                                const gzk_buf* weights, uint64_t weights_first, const uint64_t* rotations, size_t p_count,
+                                gzk_buf* out, size_t out_offset);
 int gzk_fr_sum(const uint8_t* values, size_t groups, size_t count, uint8_t* out);
 int gzk_g1_sum(const uint8_t* points, size_t count, uint8_t out[96]);
 

@@ -1,0 +1,74 @@
+/* gatzk_b200_flow.h — C entry points of libgatzk_b200_flow.so: the commit + prove flow of the
+ * multi-head GAT prover (project_b200/host/prover_flow.hpp) driven over libgatzk_b200.so.
+ *
+ * The flow is the host orchestration of one proof: forward pass and quantised witness of every
+ * attention head, the column builders, the commit barriers chained by the Fiat-Shamir
+ * transcript, and the evaluations of the prove phase.  It mirrors build_multihead_trace
+ * (src/protocol/trace.cpp:2110-4270) and the multi-head branch of prove
+ * (src/protocol/prover.cpp:3050-3398) on a model, graph and feature matrix handed over as
+ * plain arrays; benchmarks and parity tests call it through these functions.
+ *
+ * All functions return 0 on success; gzk_flow_error() gives the message of the last failure
+ * on the calling thread. */
+#ifndef GATZK_B200_FLOW_H
+#define GATZK_B200_FLOW_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct gzk_flow gzk_flow;
+
+typedef struct gzk_flow_config
+{
+    uint64_t node_count, feature_count, class_count, edge_count;
+    uint64_t hidden_layer_count;
+    const uint64_t* hidden_heads;     /* heads per hidden layer */
+    const uint64_t* hidden_head_dim;  /* output width of a head, per hidden layer */
+    uint64_t output_heads;
+    uint32_t range_bits;              /* size of the range table: 2^range_bits (config key range_bits) */
+    uint64_t seed;                    /* KZG::setup: tau = seed + 17 (src/crypto/kzg.cpp:378) */
+    const double* features;           /* node_count x feature_count, row-major */
+    const uint32_t* edge_src;         /* edge_count endpoints, edges sorted by destination, one self loop per node */
+    const uint32_t* edge_dst;
+    /* model parameters, one block per head, hidden heads in layer order then output heads:
+     * seq_kernel (input_dim x width, row-major), attn_src (width), attn_dst (width),
+     * attn_src_bias, attn_dst_bias, output_bias (width; used by output heads only) */
+    const double* params;
+    uint64_t param_count;
+    const uint8_t* generator;         /* affine G1 generator, 96 bytes (x || y, little-endian) */
+} gzk_flow_config;
+
+const char* gzk_flow_error(void);
+/* Prepares everything that depends only on the key, the graph, the tables and the model
+ * parameters (domains, weights at tau, public and static commitments): the reference's
+ * build_context (src/protocol/prover.cpp:2579-3030). */
+int gzk_flow_create(int device, const gzk_flow_config* config, gzk_flow** out);
+void gzk_flow_destroy(gzk_flow* flow);
+/* One commit + prove pass from the host inputs; everything witness-dependent is recomputed. */
+int gzk_flow_prove(gzk_flow* flow);
+/* Text listing of the last proof run, one value per line (challenges, tau-evaluations,
+ * commitments, quotient scalars, opened values, witnesses, external evaluations, witness
+ * scalars): returns the length; copies at most cap bytes. */
+size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap);
+/* The proof as bytes in the layout proof_size_bytes counts (src/protocol/prover.cpp:3831-3905). */
+size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap);
+/* counters of the last run: commit barriers, challenges, dynamic commitments, opened columns,
+ * then the seven domain sizes FH, edge, in, d, cat, C, N */
+int gzk_flow_stats(gzk_flow* flow, uint64_t out[11]);
+/* A committed column of the last run by label: its buffer kind (GZK_KIND_*), stored length and,
+ * when out is not NULL, its first min(length, cap_elements) elements in the wire format of
+ * gzk_buf_download. */
+int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements);
+/* newline-separated labels of the opened columns of a domain ("FH", "edge", "in", "d", "cat", "C", "N") */
+size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap);
+/* the gzk_ctx the flow issues its work on (for gzk_timing_* and stream queries) */
+void* gzk_flow_context(gzk_flow* flow);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -9,6 +9,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ_DIR = os.path.join(CSRC, "build")
 LIB_PATH = os.path.join(HERE, "libgatzk_b200.so")
 TUNING_LIB_PATH = os.path.join(HERE, "libgatzk_b200_tuning.so")
+FLOW_LIB_PATH = os.path.join(HERE, "libgatzk_b200_flow.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -60,6 +61,13 @@ def build(verbose=False, force=False):
     tuning_src = os.path.join(CSRC, "tuning", "mac_peak.cu")
     if force or _stale(TUNING_LIB_PATH, [tuning_src] + headers):
         subprocess.run([nvcc, *NVCC_FLAGS[:-2], "-shared", tuning_src, "-o", TUNING_LIB_PATH], check=True)
+    # the commit + prove flow: plain C++ host code over the C ABI of the library above
+    host = os.path.join(HERE, "host")
+    flow_deps = [os.path.join(host, f) for f in ("flow_gpu.cpp", "prover_flow.hpp", "prover_flow_tail.hpp", "flow_c_impl.hpp", "proof_codec.hpp")]
+    flow_deps += [os.path.join(os.path.dirname(HERE), "include", f) for f in ("gatzk_b200.h", "gatzk_b200_flow.h")]
+    if force or _stale(FLOW_LIB_PATH, flow_deps + [LIB_PATH]):
+        subprocess.run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-Wextra", flow_deps[0], "-o", FLOW_LIB_PATH,
+                        f"-L{HERE}", "-lgatzk_b200", "-Wl,-rpath,$ORIGIN"], check=True)
     return LIB_PATH
 
 

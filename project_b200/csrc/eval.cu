@@ -413,8 +413,12 @@ using namespace gzk;
 
 // Shared body of gzk_eval_batch and gzk_eval_batch_range.  `rotations` are already the
 // effective ones: row c of a column meets weights[(c - rotation) mod n] of the buffer.
+// With `dest` set the results stay on the device (dest[p * k_count + k], Montgomery form when
+// dest_montgomery) and the call ends like a builder call: no read-back, no synchronisation in
+// deferred mode.
 static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
-                           const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host)
+                           const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host,
+                           Fr* dest = nullptr, bool dest_montgomery = false)
 {
     const uint64_t n = 1ULL << log2n;
     if (k_count > (1u << 20)) return fail(ctx, GZK_E_INVALID, "eval_batch: too many columns");
@@ -485,7 +489,8 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(d_table, h_table, table_bytes, cudaMemcpyHostToDevice, ctx->stream));
     const void* const* d_ptrs = static_cast<const void* const*>(d_table);
     const int* d_kinds = reinterpret_cast<const int*>(static_cast<const char*>(d_table) + k_count * sizeof(void*));
-    Fr* d_out = reinterpret_cast<Fr*>(static_cast<char*>(d_table) + table_padded);
+    Fr* d_out = dest != nullptr ? dest : reinterpret_cast<Fr*>(static_cast<char*>(d_table) + table_padded);
+    if (dest != nullptr && (rc = begin_call(ctx)) != GZK_OK) return rc;
 
     uint8_t* h_out = static_cast<uint8_t*>(h_table) + table_padded;
     for (size_t p0 = 0; p0 < p_count; p0 += 2)
@@ -520,10 +525,12 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
         {
             LaunchScope scope(ctx, "eval_finish");
             eval_finish_kernel<<<(outs + 3) / 4, 128, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
-                                                                           static_cast<uint32_t>(k_count), d_out + p0 * k_count);
+                                                                           static_cast<uint32_t>(k_count), d_out + p0 * k_count, -1,
+                                                                           dest != nullptr && dest_montgomery ? 1 : 0);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
     }
+    if (dest != nullptr) return finish_call(ctx, "eval_batch_device: invalid input");
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(h_out, d_out, p_count * k_count * 32, cudaMemcpyDeviceToHost, ctx->stream));
     int* h_status = reinterpret_cast<int*>(h_out + p_count * k_count * 32);
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
@@ -731,6 +738,58 @@ extern "C" int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count
     if (weights->kind != GZK_KIND_FR_MONT || weights->count < n)
         return fail(ctx, GZK_E_INVALID, "eval_batch: weights must be a Montgomery buffer of the domain size");
     return eval_batch_impl(ctx, cols, k_count, len, log2n, weights, rotations, p_count, out_host);
+}
+
+// Same sums as gzk_eval_batch, left on the device: out[out_offset + p * k_count + k], canonical for an
+// FR buffer, Montgomery for an FR_MONT one.  Nothing is read back, so in deferred mode the call only
+// queues kernels; the values feed device-side consumers (same-base G1 multiplication, an exchange
+// between GPUs, gzk_fr_sum_device).
+extern "C" int gzk_eval_batch_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
+                                     const gzk_buf* weights, const uint64_t* rotations, size_t p_count, gzk_buf* out, size_t out_offset)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (k_count == 0 || p_count == 0) return GZK_OK;
+    if (cols == nullptr || weights == nullptr || rotations == nullptr || out == nullptr)
+        return fail(ctx, GZK_E_INVALID, "eval_batch_device: null argument");
+    if (log2n > 32) return fail(ctx, GZK_E_INVALID, "eval_batch_device: domain too large");
+    const uint64_t n = 1ULL << log2n;
+    if (len > n) return fail(ctx, GZK_E_INVALID, "domain evaluation backend weight size mismatch");
+    if (weights->kind != GZK_KIND_FR_MONT || weights->count < n)
+        return fail(ctx, GZK_E_INVALID, "eval_batch_device: weights must be a Montgomery buffer of the domain size");
+    if ((out->kind != GZK_KIND_FR && out->kind != GZK_KIND_FR_MONT) || out_offset + p_count * k_count > out->count)
+        return fail(ctx, GZK_E_INVALID, "eval_batch_device: output must be an FR or FR_MONT buffer that holds p_count * k_count values at out_offset");
+    return eval_batch_impl(ctx, cols, k_count, len, log2n, weights, rotations, p_count, nullptr, static_cast<Fr*>(out->dptr) + out_offset,
+                           out->kind == GZK_KIND_FR_MONT);
+}
+
+// Row-sharded form with the partial sums left on the device (see gzk_eval_batch_range for the
+// meaning of row_offset / weights_first).
+extern "C" int gzk_eval_batch_range_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, uint64_t row_offset, unsigned log2n,
+                                           const gzk_buf* weights, uint64_t weights_first, const uint64_t* rotations, size_t p_count,
+                                           gzk_buf* out, size_t out_offset)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (k_count == 0 || p_count == 0) return GZK_OK;
+    if (cols == nullptr || weights == nullptr || rotations == nullptr || out == nullptr)
+        return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: null argument");
+    if (log2n > 32) return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: domain too large");
+    const uint64_t n = 1ULL << log2n;
+    if (len > n || row_offset >= n || weights_first >= n) return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: range exceeds the domain");
+    if (weights->kind != GZK_KIND_FR_MONT) return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: weights must be a Montgomery buffer");
+    if (p_count > 16) return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: too many rotations");
+    if ((out->kind != GZK_KIND_FR && out->kind != GZK_KIND_FR_MONT) || out_offset + p_count * k_count > out->count)
+        return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: output must be an FR or FR_MONT buffer that holds p_count * k_count values at out_offset");
+    uint64_t effective[16];
+    for (size_t p = 0; p < p_count; ++p)
+    {
+        if (rotations[p] >= n) return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: rotation out of range");
+        const uint64_t first_needed = (row_offset + n - rotations[p] + n - weights_first) & (n - 1);
+        if (len != 0 && weights->count < n && first_needed + len > weights->count)
+            return fail(ctx, GZK_E_INVALID, "eval_batch_range_device: the weight slice does not cover the rows at this rotation");
+        effective[p] = (n - first_needed) & (n - 1);
+    }
+    return eval_batch_impl(ctx, cols, k_count, len, log2n, weights, effective, p_count, nullptr, static_cast<Fr*>(out->dptr) + out_offset,
+                           out->kind == GZK_KIND_FR_MONT);
 }
 
 // Row-sharded form: this GPU holds rows [row_offset, row_offset + len) of every column

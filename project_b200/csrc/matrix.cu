@@ -59,12 +59,15 @@ namespace gzk
             }
         }
 
-        __global__ void sum_partials_kernel(const Fr* partial, uint32_t count, int montgomery, Fr* out_canonical)
+        // `down` > 0: that many conversions out of Montgomery form; < 0: into it.
+        __global__ void sum_partials_kernel(const Fr* partial, uint32_t count, int down, Fr* out)
         {
             if (threadIdx.x != 0 || blockIdx.x != 0) return;
             Fr sum = Fr::zero();
             for (uint32_t i = 0; i < count; ++i) sum = add(sum, load_fr_plain(partial + i));
-            store_fr(out_canonical, montgomery ? from_mont(sum) : sum);
+            for (; down > 0; --down) sum = from_mont(sum);
+            for (; down < 0; ++down) sum = to_mont(sum);
+            store_fr(out, sum);
         }
 
         // ---- fold rows ----------------------------------------------------------------
@@ -189,6 +192,41 @@ using namespace gzk;
 
 extern "C"
 {
+    // Shared body: the evaluation ends in dest (canonical, or Montgomery form when dest_montgomery).
+    static int matrix_horner_enqueue(gzk_ctx* ctx, const gzk_buf* matrix, uint64_t total, const Fr& x, Fr* dest, bool dest_montgomery,
+                                     Fr** scratch_result)
+    {
+        uint64_t ctas = (total + static_cast<uint64_t>(kThreads) * 8 - 1) / (static_cast<uint64_t>(kThreads) * 8);
+        const uint64_t max_ctas = static_cast<uint64_t>(ctx->sm_count) * 8;
+        if (ctas > max_ctas) ctas = max_ctas;
+        uint64_t span = (total + ctas - 1) / ctas;
+        span = (span + kThreads - 1) / kThreads * kThreads;
+        ctas = (total + span - 1) / span;
+        void* scratch = nullptr;
+        int rc = ensure_scratch(ctx, 2, (ctas + 1) * sizeof(Fr), &scratch);
+        if (rc != GZK_OK) return rc;
+        Fr* partial = static_cast<Fr*>(scratch);
+        ColRef m;
+        m.ptr = matrix->dptr;
+        m.kind = matrix->kind;
+        {
+            LaunchScope scope(ctx, "horner");
+            horner_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, total, span, x, pow_u64(x, kThreads), partial);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        Fr* result = dest != nullptr ? dest : partial + ctas;
+        {
+            // the partial sums are Montgomery values of the canonical result (canonical entries) or of its
+            // Montgomery form (Montgomery entries): one or two conversions bring them to the wanted form
+            LaunchScope scope(ctx, "horner_sum");
+            const int down = (matrix->kind == GZK_KIND_FR_MONT ? 1 : 0) - (dest_montgomery ? 1 : 0);
+            sum_partials_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(ctas), down, result);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        if (scratch_result != nullptr) *scratch_result = result;
+        return GZK_OK;
+    }
+
     int gzk_matrix_horner(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const uint8_t x_bytes[32], uint8_t out[32])
     {
         if (ctx == nullptr) return GZK_E_INVALID;
@@ -204,31 +242,36 @@ extern "C"
         int rc = scalar_mont(ctx, x_bytes, &x);
         if (rc != GZK_OK) return rc;
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
-        uint64_t ctas = (total + static_cast<uint64_t>(kThreads) * 8 - 1) / (static_cast<uint64_t>(kThreads) * 8);
-        const uint64_t max_ctas = static_cast<uint64_t>(ctx->sm_count) * 8;
-        if (ctas > max_ctas) ctas = max_ctas;
-        uint64_t span = (total + ctas - 1) / ctas;
-        span = (span + kThreads - 1) / kThreads * kThreads;
-        ctas = (total + span - 1) / span;
-        void* scratch = nullptr;
-        if ((rc = ensure_scratch(ctx, 2, (ctas + 1) * sizeof(Fr), &scratch)) != GZK_OK) return rc;
-        Fr* partial = static_cast<Fr*>(scratch);
-        ColRef m;
-        m.ptr = matrix->dptr;
-        m.kind = matrix->kind;
-        {
-            LaunchScope scope(ctx, "horner");
-            horner_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, total, span, x, pow_u64(x, kThreads), partial);
-        }
-        GZK_CUDA_TRY(ctx, cudaGetLastError());
-        {
-            LaunchScope scope(ctx, "horner_sum");
-            sum_partials_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(ctas), matrix->kind == GZK_KIND_FR_MONT ? 1 : 0, partial + ctas);
-        }
-        GZK_CUDA_TRY(ctx, cudaGetLastError());
-        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out, partial + ctas, 32, cudaMemcpyDeviceToHost, ctx->stream));
+        Fr* result = nullptr;
+        if ((rc = matrix_horner_enqueue(ctx, matrix, total, x, nullptr, false, &result)) != GZK_OK) return rc;
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(out, result, 32, cudaMemcpyDeviceToHost, ctx->stream));
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return GZK_OK;
+    }
+
+    // Same evaluation, left on the device in out[out_offset] (canonical for an FR buffer, Montgomery
+    // for an FR_MONT one); nothing is read back.
+    int gzk_matrix_horner_device(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const uint8_t x_bytes[32], gzk_buf* out,
+                                 size_t out_offset)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (x_bytes == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "matrix_horner_device: null argument");
+        if ((out->kind != GZK_KIND_FR && out->kind != GZK_KIND_FR_MONT) || out_offset >= out->count)
+            return fail(ctx, GZK_E_INVALID, "matrix_horner_device: output must be an FR or FR_MONT buffer that holds out_offset");
+        const uint64_t total = static_cast<uint64_t>(rows) * cols;
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        Fr* dest = static_cast<Fr*>(out->dptr) + out_offset;
+        if (total == 0)
+        {
+            GZK_CUDA_TRY(ctx, cudaMemsetAsync(dest, 0, sizeof(Fr), ctx->stream));
+            return GZK_OK;
+        }
+        if (matrix == nullptr || matrix->count < total) return fail(ctx, GZK_E_INVALID, "matrix_horner_device: matrix buffer too small");
+        Fr x;
+        int rc = scalar_mont(ctx, x_bytes, &x);
+        if (rc != GZK_OK) return rc;
+        if ((rc = matrix_horner_enqueue(ctx, matrix, total, x, dest, out->kind == GZK_KIND_FR_MONT, nullptr)) != GZK_OK) return rc;
+        return finish_call(ctx, "invalid input");
     }
 
     int gzk_fold_rows(gzk_ctx* ctx, const gzk_buf* matrix, size_t rows, size_t cols, const gzk_buf* row_weights, size_t row_count,

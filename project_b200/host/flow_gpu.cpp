@@ -1,0 +1,262 @@
+// libgatzk_b200_flow.so: the prover flow (prover_flow.hpp) over the C ABI of libgatzk_b200.so.
+// Every Backend method is one gzk_* call; columns are gzk_buf handles that live on the GPU from
+// the forward pass to the last opening.  The context runs in deferred mode: builder calls only
+// queue kernels, the host reads values back once per commit barrier.
+#include <cstring>
+
+#include "../../include/gatzk_b200.h"
+#include "flow_c_impl.hpp"
+
+namespace
+{
+    using namespace gatzk_flow;
+
+    class GpuBackend;
+    struct GpuCol : Col
+    {
+        GpuBackend* owner = nullptr;
+        gzk_buf* buf = nullptr;
+        ~GpuCol() override;
+    };
+
+    class GpuBackend : public Backend
+    {
+    public:
+        explicit GpuBackend(int device)
+        {
+            if (gzk_ctx_create(device, &ctx_) != GZK_OK) throw std::runtime_error("b200 backend: no usable sm_100 GPU (there is no CPU fallback)");
+            check(gzk_ctx_set_deferred(ctx_, 1));
+        }
+        ~GpuBackend() override
+        {
+            for (auto& slot : pool_)
+                for (gzk_buf* b : slot.second) gzk_buf_free(ctx_, b);
+            gzk_ctx_destroy(ctx_);
+        }
+        gzk_ctx* context() const { return ctx_; }
+        // Buffers go back to a free list keyed by (kind, count) instead of to cudaFree: every proof
+        // allocates the same set of columns, so from the second proof on nothing is allocated, and a
+        // recycled buffer is safe to reuse at once because all work is ordered on the one stream.
+        void recycle(int kind, std::size_t count, gzk_buf* buf) { pool_[{kind, count}].push_back(buf); }
+
+        Fe fr_op(int op, const Fe& a, const Fe& b) override
+        {
+            Fe out{};
+            if (gzk_fr_op(op, a.data(), b.data(), out.data()) != GZK_OK) throw std::runtime_error("field operation on a non-canonical or zero operand");
+            return out;
+        }
+        Fe root_of_unity(std::uint64_t size) override
+        {
+            Fe out{};
+            check(gzk_root_of_unity(ctx_, size, out.data()));
+            return out;
+        }
+        ColP alloc(int kind, std::size_t count) override
+        {
+            auto c = std::make_shared<GpuCol>();
+            c->owner = this;
+            c->kind = kind;
+            c->count = count;
+            auto& free_list = pool_[{kind, count}];
+            if (!free_list.empty())
+            {
+                c->buf = free_list.back();
+                free_list.pop_back();
+            }
+            else
+            {
+                check(gzk_buf_alloc(ctx_, kind, count, &c->buf));
+            }
+            return c;
+        }
+        void upload(const ColP& col, const void* host, std::size_t count) override { check(gzk_buf_upload(ctx_, raw(col), 0, host, count)); }
+        void download(const ColP& col, std::size_t offset, std::size_t count, void* host) override
+        {
+            check(gzk_buf_download(ctx_, raw(col), offset, host, count));
+        }
+        void zero(const ColP& col) override { check(gzk_buf_zero(ctx_, raw(col))); }
+        void copy_block(const ColP& src, std::size_t so, std::size_t ss, const ColP& dst, std::size_t d_o, std::size_t ds, std::size_t rows,
+                        std::size_t width) override
+        {
+            check(gzk_copy_block(ctx_, raw(src), so, ss, raw(dst), d_o, ds, rows, width));
+        }
+        void head_forward(const HeadDesc& h, const GraphCols& g, const HeadTraceCols& o) override
+        {
+            gzk_gat_head head{};
+            head.features = raw(h.features);
+            head.input_width = static_cast<std::uint32_t>(h.input_width);
+            head.output_width = static_cast<std::uint32_t>(h.output_width);
+            head.seq_kernel = raw(h.seq_kernel);
+            head.attn_src_kernel = raw(h.attn_src);
+            head.attn_dst_kernel = raw(h.attn_dst);
+            head.attn_src_bias = h.attn_src_bias;
+            head.attn_dst_bias = h.attn_dst_bias;
+            head.output_bias = h.output_bias ? raw(h.output_bias) : nullptr;
+            head.output_bias_count = h.output_bias ? h.output_bias->count : 0;
+            head.apply_activation = h.apply_activation ? 1 : 0;
+            gzk_gat_graph graph{};
+            graph.node_count = g.node_count;
+            graph.edge_count = g.edge_count;
+            graph.edge_src = raw(g.edge_src);
+            graph.edge_dst = raw(g.edge_dst);
+            graph.incoming_count = g.incoming_count;
+            graph.incoming_ptr = raw(g.incoming_ptr);
+            graph.incoming_src = raw(g.incoming_src);
+            gzk_gat_trace tr{};
+            tr.H_prime = raw(o.H_prime);
+            tr.E_src = raw(o.E_src);
+            tr.E_dst = raw(o.E_dst);
+            tr.M = raw(o.M);
+            tr.Sum = raw(o.Sum);
+            tr.inv = raw(o.inv);
+            tr.S = raw(o.S);
+            tr.Z = raw(o.Z);
+            tr.Delta = raw(o.Delta);
+            tr.U = raw(o.U);
+            tr.alpha = raw(o.alpha);
+            tr.H_agg_pre_bias = raw(o.H_agg_pre_bias);
+            tr.H_agg = raw(o.H_agg);
+            check(gzk_gat_head_forward(ctx_, &head, &graph, &tr));
+        }
+        void quantize(const ColP& v, std::size_t count, const ColP& out) override { check(gzk_quantize(ctx_, raw(v), count, raw(out))); }
+        void gather(const ColP& nv, std::size_t node_count, const ColP& index, std::size_t edge_count, std::size_t domain_size, const ColP& out) override
+        {
+            check(gzk_broadcast_node_values(ctx_, raw(nv), node_count, raw(index), edge_count, domain_size, raw(out)));
+        }
+        void linear_combination(const std::vector<ColP>& cols, const std::vector<Fe>& coefficients, std::size_t count, std::size_t domain_size,
+                                const ColP& out) override
+        {
+            std::vector<const gzk_buf*> bufs;
+            std::vector<std::uint8_t> coeff(cols.size() * 32);
+            for (std::size_t j = 0; j < cols.size(); ++j)
+            {
+                bufs.push_back(raw(cols[j]));
+                std::memcpy(&coeff[32 * j], coefficients[j].data(), 32);
+            }
+            check(gzk_linear_combination(ctx_, bufs.data(), coeff.data(), cols.size(), count, domain_size, raw(out)));
+        }
+        void mul_columns(const ColP& l, const ColP& r, std::size_t count, std::size_t domain_size, const ColP& out) override
+        {
+            check(gzk_mul_columns(ctx_, raw(l), raw(r), count, domain_size, raw(out)));
+        }
+        void linear_form_rows(const ColP& m, std::size_t rows, std::size_t cols, const ColP& powers, const ColP& out) override
+        {
+            check(gzk_linear_form_rows(ctx_, raw(m), rows, cols, raw(powers), raw(out)));
+        }
+        void powers(const Fe& c, std::size_t count, const ColP& out) override { check(gzk_powers(ctx_, c.data(), count, raw(out))); }
+        void lookup_multiplicity(const ColP& x, const ColP& y, std::size_t count, std::int64_t x_min, std::size_t band, const ColP& table_y,
+                                 std::size_t table_size, std::size_t domain_size, const ColP& out) override
+        {
+            check(gzk_banded_lookup_multiplicity(ctx_, raw(x), y ? raw(y) : nullptr, count, x_min, band, table_y ? raw(table_y) : nullptr, table_size,
+                                                 domain_size, raw(out)));
+        }
+        void first_zero_marker(const ColP& delta, const ColP& gb, const ColP& ge, std::size_t groups, std::size_t domain_size, const ColP& out) override
+        {
+            check(gzk_first_zero_marker(ctx_, raw(delta), raw(gb), raw(ge), groups, domain_size, raw(out)));
+        }
+        void logup(const ColP& table, const ColP& query, const ColP& m, const ColP& qt, const ColP& qq, std::size_t n, const Fe& beta,
+                   std::size_t active, const ColP& out) override
+        {
+            check(gzk_logup_accumulator(ctx_, raw(table), raw(query), raw(m), raw(qt), raw(qq), n, beta.data(), active, raw(out)));
+        }
+        void route_node(const ColP& table, const ColP& m, std::size_t valid, std::size_t domain_size, const Fe& beta, const ColP& out) override
+        {
+            check(gzk_route_node_accumulator(ctx_, raw(table), raw(m), valid, domain_size, beta.data(), raw(out)));
+        }
+        void route_edge(const ColP& query, std::size_t valid, std::size_t domain_size, const Fe& beta, const ColP& out) override
+        {
+            check(gzk_route_edge_accumulator(ctx_, raw(query), valid, domain_size, beta.data(), raw(out)));
+        }
+        void group_prefix_state(const ColP& values, const ColP& q_new, std::size_t n, const ColP& out) override
+        {
+            check(gzk_group_prefix_state(ctx_, raw(values), raw(q_new), n, raw(out)));
+        }
+        void zkmap(const ColP& a, const ColP& b, std::size_t count, std::size_t domain_size, const ColP& out) override
+        {
+            check(gzk_zkmap_accumulator(ctx_, raw(a), raw(b), count, domain_size, raw(out), nullptr));
+        }
+        void bary_weights(unsigned log2n, const Fe& x, const ColP& out) override { check(gzk_bary_weights(ctx_, log2n, x.data(), raw(out))); }
+        void fold_rows(const ColP& m, std::size_t rows, std::size_t cols, const ColP& weights, std::size_t row_count, const ColP& out) override
+        {
+            check(gzk_fold_rows(ctx_, raw(m), rows, cols, raw(weights), row_count, raw(out)));
+        }
+        void eval_device(const std::vector<ColP>& cols, std::size_t len, unsigned log2n, const ColP& weights, const std::vector<std::uint64_t>& rotations,
+                         const ColP& out, std::size_t out_offset) override
+        {
+            std::vector<gzk_buf*> bufs;
+            for (const auto& c : cols) bufs.push_back(raw(c));
+            check(gzk_eval_batch_device(ctx_, bufs.data(), bufs.size(), len, log2n, raw(weights), rotations.data(), rotations.size(), raw(out), out_offset));
+        }
+        void horner_device(const ColP& m, std::size_t rows, std::size_t cols, const Fe& x, const ColP& out, std::size_t out_offset) override
+        {
+            check(gzk_matrix_horner_device(ctx_, raw(m), rows, cols, x.data(), raw(out), out_offset));
+        }
+        void g1_fixed_base(const G1& base, const ColP& scalars, std::size_t count, const ColP& out_points) override
+        {
+            check(gzk_g1_fixed_base_mul(ctx_, base.data(), raw(scalars), count, raw(out_points)));
+        }
+        void fh_public_eval(const ColP& features, std::size_t rows, std::size_t fc, const ColP& abs_ids, const ColP& weights, Fe out[5]) override
+        {
+            std::uint8_t bytes[5 * 32];
+            check(gzk_fh_public_eval(ctx_, raw(features), rows, fc, abs_ids ? raw(abs_ids) : nullptr, raw(weights), bytes));
+            for (int i = 0; i < 5; ++i) std::memcpy(out[i].data(), bytes + 32 * i, 32);
+        }
+        void synchronize() override { check(gzk_ctx_synchronize(ctx_)); }
+
+    private:
+        static gzk_buf* raw(const ColP& c)
+        {
+            if (c == nullptr) throw std::runtime_error("flow: missing column");
+            return static_cast<GpuCol*>(c.get())->buf;
+        }
+        void check(int rc) const
+        {
+            if (rc != GZK_OK) throw std::runtime_error(gzk_last_error(ctx_));
+        }
+        gzk_ctx* ctx_ = nullptr;
+        std::map<std::pair<int, std::size_t>, std::vector<gzk_buf*>> pool_;
+    };
+
+    GpuCol::~GpuCol()
+    {
+        if (buf != nullptr) owner->recycle(kind, count, buf);
+    }
+}
+
+struct gzk_flow : gatzk_flow::FlowHandle
+{
+};
+
+extern "C"
+{
+    const char* gzk_flow_error(void) { return gatzk_flow::flow_error_slot().c_str(); }
+    int gzk_flow_create(int device, const gzk_flow_config* config, gzk_flow** out)
+    {
+        gatzk_flow::FlowHandle* handle = nullptr;
+        std::unique_ptr<gatzk_flow::Backend> backend;
+        const int rc0 = gatzk_flow::flow_guard([&] { backend = std::make_unique<GpuBackend>(device); });
+        if (rc0 != 0) return rc0;
+        const int rc = gatzk_flow::flow_create_impl(std::move(backend), config, &handle);
+        if (rc == 0) *out = static_cast<gzk_flow*>(handle);
+        return rc;
+    }
+    void gzk_flow_destroy(gzk_flow* flow)
+    {
+        if (flow == nullptr) return;
+        flow->flow.reset();  // columns go before the context
+        delete static_cast<gatzk_flow::FlowHandle*>(flow);
+    }
+    int gzk_flow_prove(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow); }
+    size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap) { return gatzk_flow::flow_dump_impl(flow, out, cap); }
+    size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap) { return gatzk_flow::flow_proof_bytes_impl(flow, out, cap); }
+    int gzk_flow_stats(gzk_flow* flow, uint64_t out[11]) { return gatzk_flow::flow_stats_impl(flow, out); }
+    int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements)
+    {
+        return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);
+    }
+    size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap)
+    {
+        return gatzk_flow::flow_domain_labels_impl(flow, domain, out, cap);
+    }
+    void* gzk_flow_context(gzk_flow* flow) { return flow == nullptr ? nullptr : static_cast<GpuBackend*>(flow->backend.get())->context(); }
+}

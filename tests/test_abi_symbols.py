@@ -6,7 +6,8 @@ import re
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-LIBRARY_OF_HEADER = {"gatzk_b200.h": "libgatzk_b200.so", "gatzk_b200_tuning.h": "libgatzk_b200_tuning.so"}
+LIBRARY_OF_HEADER = {"gatzk_b200.h": "libgatzk_b200.so", "gatzk_b200_tuning.h": "libgatzk_b200_tuning.so",
+                     "gatzk_b200_flow.h": "libgatzk_b200_flow.so"}
 
 
 def declared_symbols(header=None):

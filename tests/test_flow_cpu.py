@@ -1,0 +1,57 @@
+"""The prover flow over the CPU restatement: structure of the proof it produces.  (The comparison
+with the GPU backend is tests/test_gpu_proof_parity.py.)"""
+import numpy as np
+
+import oracle_lib as ora
+import pyref
+from project_b200 import synthetic
+from project_b200.flow import Flow
+
+G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8).copy()
+
+
+def run(shape):
+    flow = Flow(ora.lib(), "ora_flow_", 2, synthetic.make_inputs(**shape), G)
+    flow.prove()
+    return flow
+
+
+def test_label_counts_follow_the_protocol_order():
+    """#dynamic commitments = 5 + 82 H + 5 L + 68 K + 2 [K > 1] (src/protocol/challenges.cpp:396-507); the
+    opened labels per domain: edge 43 H + 36 K, in 3 H, d 15 H, cat 3 L + 3 K, C 9 K, N 18 H + 17 K + L."""
+    # the head layout of the small citation configuration (8 hidden heads of width 8, one output head):
+    # 734 dynamic commitments
+    flow = run(dict(seed=5, nodes=24, directed_edges=60, feature_count=6, hidden=[(8, 8)], output_heads=1, class_count=7))
+    stats = flow.stats()
+    assert stats["dynamic_commitments"] == 734
+    h, k, layers = 8, 1, 1
+    expect = {"edge": 43 * h + 36 * k, "in": 3 * h, "d": 15 * h, "cat": 3 * layers + 3 * k, "C": 9 * k, "N": 18 * h + 17 * k + layers}
+    for domain, count in expect.items():
+        assert len(flow.domain_labels(domain)) == count, domain
+    # proof_size_bytes (src/protocol/prover.cpp:3831-3905) of the serialised proof: 48-byte points, 32-byte
+    # values, (#labels + 1) rows of two values per bundle
+    listing = flow.dump()
+    rows = sum(1 for line in listing.splitlines() if line.startswith("opened "))
+    assert rows == sum(expect.values()) + 5 + 7  # + the five feature-domain labels + one quotient row per bundle
+    size = len(flow.proof_bytes())
+    commitments = 734
+    ext = sum(1 for line in listing.splitlines() if line.startswith("external "))
+    scalars = sum(1 for line in listing.splitlines() if line.startswith("witness_scalar "))
+    meta = sum(1 for _ in range(24)) * 8
+    fixed = 8 + 8 + 8 + 48 * commitments + 8 + 48 * 7 + 8 + 7 * (8 + 48) + rows * (8 + 64) + 8 + 32 * ext + 8 + 32 * scalars + 48
+    blocks = sum(8 + len(b) for b in ["M_pub", "Com_dyn", "S_route", "Eval_ext", "Eval_dom", "Com_quot", "Open_dom", "W_ext", "Pi_bind"])
+    # what is left are the metadata strings themselves
+    assert size - fixed - blocks - meta > 0
+    flow.close()
+
+
+def test_two_proofs_of_one_context_are_identical_and_inputs_matter():
+    shape = dict(seed=6, nodes=30, directed_edges=80, feature_count=8, hidden=[(2, 4)], output_heads=2, class_count=3)
+    flow = run(shape)
+    first = flow.proof_bytes().copy()
+    flow.prove()
+    assert np.array_equal(first, flow.proof_bytes())
+    other = run(dict(shape, seed=7))
+    assert not np.array_equal(first[-4000:], other.proof_bytes()[-4000:])
+    flow.close()
+    other.close()

@@ -187,7 +187,7 @@ def test_bounded_wait_that_runs_out_returns_timeout():
     """Failure handling without a fault: with the stall injection on, the kernel's chunk barriers are armed
     but no copy is issued, every bounded wait gives up, and the call returns GZK_E_TIMEOUT (4); the context
     stays usable and the next call is correct."""
-    from project_b200 import GzkError
+    from project_b200 import KIND_FR, Backend, GzkError
     from project_b200.lib import inject_eval_stall
 
     be = Backend(0)
