@@ -474,9 +474,22 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     // device-side tables and scratch
     const size_t table_bytes = k_count * (sizeof(void*) + sizeof(int));
     const size_t table_padded = (table_bytes + 31) & ~static_cast<size_t>(31);
+    // Host copy of the column table.  A call that reads results back ends with a synchronisation, so
+    // it can stage through the context's pinned area; a call that leaves its results on the device
+    // returns while its copy may still be queued, so its table lives in pageable memory of its own
+    // (the runtime copies a pageable source to its staging area before cudaMemcpyAsync returns).
     void* h_table = nullptr;
-    int rc = ensure_pinned(ctx, table_padded + p_count * k_count * 32 + 64, &h_table);
-    if (rc != GZK_OK) return rc;
+    std::vector<unsigned char> pageable_table;
+    int rc = GZK_OK;
+    if (dest != nullptr)
+    {
+        pageable_table.resize(table_padded);
+        h_table = pageable_table.data();
+    }
+    else if ((rc = ensure_pinned(ctx, table_padded + p_count * k_count * 32 + 64, &h_table)) != GZK_OK)
+    {
+        return rc;
+    }
     void* d_table = nullptr;
     if ((rc = ensure_scratch(ctx, 0, table_padded + p_count * k_count * 32, &d_table)) != GZK_OK) return rc;
     const void** h_ptrs = static_cast<const void**>(h_table);
