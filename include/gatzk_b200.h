@@ -74,6 +74,11 @@ int gzk_timing_enable(gzk_ctx* ctx, int on);
 int gzk_timing_reset(gzk_ctx* ctx);
 int gzk_timing_family_count(gzk_ctx* ctx);
 int gzk_timing_get(gzk_ctx* ctx, int index, const char** name, uint64_t* launches, double* total_ms);
+/* Work of the packed-evaluation launches since the last gzk_timing_reset, for rooflines: out[0]
+ * algorithmic bytes (every column element once per launch at its stored width of 4 / 8 / 32 bytes,
+ * the weight vector once per rotation), out[1] 32x32-bit limb products of the inner loops (64 per
+ * term for field-element columns, 16 for I64, 8 for U32), out[2] (row, column, rotation) terms. */
+int gzk_eval_work_counters(gzk_ctx* ctx, uint64_t out[3]);
 
 /* Test facility for the device-side failure handling.  The packed-evaluation kernel waits
  * for its bulk copies with a bounded number of polls; when a wait runs out the kernel raises
@@ -106,6 +111,10 @@ int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, 
  * work issued afterwards wait for the uploads queued so far. */
 int gzk_buf_upload_async(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
 int gzk_copy_fence(gzk_ctx* ctx);
+/* Page-locks / releases a range of the caller's host memory (the reference keeps its inputs in
+ * ordinary std::vector storage): uploads from a registered range are direct DMA transfers. */
+int gzk_host_register(void* host, size_t bytes);
+int gzk_host_unregister(void* host);
 /* downloads always deliver the wire format: FR_MONT buffers are converted to
  * canonical on the device first */
 int gzk_buf_download(gzk_ctx* ctx, const gzk_buf* buf, size_t offset, void* host, size_t count);
@@ -170,6 +179,38 @@ int gzk_route_node_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf
                                size_t domain_size, const uint8_t beta[32], gzk_buf* out);
 int gzk_route_edge_accumulator(gzk_ctx* ctx, const gzk_buf* query, size_t valid_length, size_t domain_size,
                                const uint8_t beta[32], gzk_buf* out);
+
+/* Several independent running sums in ONE pair of launches.  The accumulators that sit between two
+ * Fiat-Shamir points of one attention head (the lookup sums, the node and edge sums of a routing
+ * argument, the segmented states, the small inner-product accumulators: src/protocol/trace.cpp:2565-2772)
+ * do not depend on one another; alone each is a short latency chain on a fraction of the GPU, queued
+ * together they fill it.  A job is one call of the single-column functions, with the same meaning of
+ * its fields and the same errors:
+ *   GZK_SCAN_LOGUP        c0..c4 = table, query, multiplicity, q_table, q_query; count = active_count
+ *   GZK_SCAN_ROUTE_NODE   c0, c1 = table, multiplicity; count = valid_length
+ *   GZK_SCAN_ROUTE_EDGE   c0 = query; count = valid_length
+ *   GZK_SCAN_ZKMAP        c0, c1 = a, b; count = number of products (the total is out[count])
+ *   GZK_SCAN_GROUP_PREFIX c0, c1 = values, q_new; count ignored (the whole domain)
+ * beta: 32 bytes for the first three operations, NULL otherwise.  At most 2^20 rows per job. */
+#define GZK_SCAN_LOGUP 0
+#define GZK_SCAN_ROUTE_NODE 1
+#define GZK_SCAN_ROUTE_EDGE 2
+#define GZK_SCAN_ZKMAP 3
+#define GZK_SCAN_GROUP_PREFIX 4
+typedef struct gzk_scan_job
+{
+    int op;
+    const gzk_buf* c0;
+    const gzk_buf* c1;
+    const gzk_buf* c2;
+    const gzk_buf* c3;
+    const gzk_buf* c4;
+    size_t count;
+    size_t domain_size;
+    const uint8_t* beta;
+    gzk_buf* out;
+} gzk_scan_job;
+int gzk_running_sums_batch(gzk_ctx* ctx, const gzk_scan_job* jobs, size_t job_count);
 
 /* ---- a8: segmented prefix states over the dst-sorted edge list ------------------------
  * out[0] = v[0]; out[i] = q_new[i] ? v[i] : out[i-1] + v[i].  q_new must hold only
@@ -274,6 +315,11 @@ int gzk_copy_block(gzk_ctx* ctx, const gzk_buf* src, size_t src_offset, size_t s
  * Weights at the wanted point come from gzk_bary_weights. */
 int gzk_fh_public_eval(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
                        const gzk_buf* weights, uint8_t out[5 * 32]);
+/* The same five sums at the rotated point omega^rotation * z, from the weights at z of the whole
+ * 2^log2n domain: entry i then meets weights[(i - rotation) mod n], as the rotated evaluations of
+ * evaluate_with_native_weight_rotations do (src/algebra/eval_backend.cpp:309-444). */
+int gzk_fh_public_eval_rotated(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
+                               const gzk_buf* weights, unsigned log2n, uint64_t rotation, uint8_t out[5 * 32]);
 
 /* ---- a5: G1 -----------------------------------------------------------------------------------
  * gzk_g1_mul_same_base: points[k] = [scalars[k]] base for K host scalars (32-byte

@@ -48,8 +48,11 @@ const char* gzk_flow_error(void);
  * build_context (src/protocol/prover.cpp:2579-3030). */
 int gzk_flow_create(int device, const gzk_flow_config* config, gzk_flow** out);
 void gzk_flow_destroy(gzk_flow* flow);
-/* One commit + prove pass from the host inputs; everything witness-dependent is recomputed. */
+/* One commit + prove pass from the host inputs; everything witness-dependent is recomputed.
+ * gzk_flow_prove_resident does the same with the feature matrix already on the device (uploaded
+ * when the flow was created) instead of uploading it again. */
 int gzk_flow_prove(gzk_flow* flow);
+int gzk_flow_prove_resident(gzk_flow* flow);
 /* Text listing of the last proof run, one value per line (challenges, tau-evaluations,
  * commitments, quotient scalars, opened values, witnesses, external evaluations, witness
  * scalars): returns the length; copies at most cap bytes. */
@@ -57,8 +60,9 @@ size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap);
 /* The proof as bytes in the layout proof_size_bytes counts (src/protocol/prover.cpp:3831-3905). */
 size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap);
 /* counters of the last run: commit barriers, challenges, dynamic commitments, opened columns,
- * then the seven domain sizes FH, edge, in, d, cat, C, N */
-int gzk_flow_stats(gzk_flow* flow, uint64_t out[11]);
+ * the seven domain sizes FH, edge, in, d, cat, C, N, then the bytes uploaded to and downloaded
+ * from the backend during the run */
+int gzk_flow_stats(gzk_flow* flow, uint64_t out[13]);
 /* A committed column of the last run by label: its buffer kind (GZK_KIND_*), stored length and,
  * when out is not NULL, its first min(length, cap_elements) elements in the wire format of
  * gzk_buf_download. */

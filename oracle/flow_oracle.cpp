@@ -486,9 +486,20 @@ namespace
         }
         // evaluate_lazy_large_fh_public_group_points, src/protocol/prover.cpp:1205-1675: dot products of the
         // weights with generated columns {1, row, col, abs id, feature}
-        void fh_public_eval(const ColP& features, std::size_t rows, std::size_t fc, const ColP& abs_ids, const ColP& weights, Fe out[5]) override
+        void fh_public_eval(const ColP& features, std::size_t rows, std::size_t fc, const ColP& abs_ids, const ColP& weights, unsigned log2n,
+                            std::uint64_t rotation, Fe out[5]) override
         {
-            const auto& w = cpu(weights).fr;
+            // the weights at the rotated point, as the reference builds them for its second opening point
+            // (a rotation of the vector: w_i(omega z) = w_{i-1}(z))
+            const std::size_t n = static_cast<std::size_t>(1) << log2n;
+            std::vector<Fr> rotated;
+            if (rotation != 0)
+            {
+                const auto& base = cpu(weights).fr;
+                rotated.resize(n);
+                for (std::size_t i = 0; i < n; ++i) rotated[i] = base[(i + n - rotation) & (n - 1)];
+            }
+            const auto& w = rotation != 0 ? rotated : cpu(weights).fr;
             const auto& f = as_field(features);
             const CpuCol* ids = abs_ids ? &cpu(abs_ids) : nullptr;
             const std::size_t valid = rows * fc;
@@ -578,10 +589,11 @@ extern "C"
         flow->flow.reset();
         delete static_cast<gatzk_flow::FlowHandle*>(flow);
     }
-    int ora_flow_prove(ora_flow* flow) { return gatzk_flow::flow_prove_impl(flow); }
+    int ora_flow_prove(ora_flow* flow) { return gatzk_flow::flow_prove_impl(flow, false); }
+    int ora_flow_prove_resident(ora_flow* flow) { return gatzk_flow::flow_prove_impl(flow, true); }
     size_t ora_flow_dump(ora_flow* flow, char* out, size_t cap) { return gatzk_flow::flow_dump_impl(flow, out, cap); }
     size_t ora_flow_proof_bytes(ora_flow* flow, uint8_t* out, size_t cap) { return gatzk_flow::flow_proof_bytes_impl(flow, out, cap); }
-    int ora_flow_stats(ora_flow* flow, uint64_t out[11]) { return gatzk_flow::flow_stats_impl(flow, out); }
+    int ora_flow_stats(ora_flow* flow, uint64_t out[13]) { return gatzk_flow::flow_stats_impl(flow, out); }
     int ora_flow_column(ora_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements)
     {
         return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);

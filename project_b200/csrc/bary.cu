@@ -326,6 +326,93 @@ namespace gzk
         }
     }
 
+    namespace
+    {
+        // Whole-domain weights in ONE launch: every CTA builds the denominators of its 1024 quartets,
+        // inverts THEIR product itself (one serial inversion per CTA, all CTAs in parallel) and writes
+        // its 4096 weights.  Nothing is exchanged between CTAs, so there is neither a products pass nor
+        // a separate inversion pass: on a small domain (a few CTAs) the call is one short chain instead
+        // of three dependent launches, on a large one the serial inversions hide behind the arithmetic
+        // of the CTA that shares the SM.
+        __global__ void __launch_bounds__(kThreads, 2) bary4_fused_kernel(BaryArgs a, Fr* out, int* status)
+        {
+            __shared__ Fr warp_incl[kThreads / 32];
+            __shared__ Fr warp_pre[kThreads / 32];
+            __shared__ Fr warp_suf[kThreads / 32];
+            __shared__ Fr cta_inverse;
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk;
+            const int lane = threadIdx.x & 31;
+            const int warp = threadIdx.x >> 5;
+
+            Fr d[kElems], pre[kElems];
+            Fr mine = Fr::one();
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
+                Fr p1, p2;
+                d[j] = e < a.n ? quartet_denominator(a, e, &p1, &p2) : Fr::one();
+                pre[j] = mine;
+                mine = mul(mine, d[j]);
+            }
+            Fr incl = mine, sufx = mine;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1)
+            {
+                const Fr up = shfl_fr(incl, (lane - offset) & 31);
+                const Fr down = shfl_fr(sufx, (lane + offset) & 31);
+                if (lane >= offset) incl = mul(incl, up);
+                if (lane + offset < 32) sufx = mul(sufx, down);
+            }
+            Fr left = shfl_fr(incl, (lane - 1) & 31);
+            Fr right = shfl_fr(sufx, (lane + 1) & 31);
+            if (lane == 0) left = Fr::one();
+            if (lane == 31) right = Fr::one();
+            if (lane == 31) warp_incl[warp] = incl;
+            __syncthreads();
+            if (threadIdx.x == 0)
+            {
+                Fr run = Fr::one();
+#pragma unroll
+                for (int w = 0; w < kThreads / 32; ++w)
+                {
+                    warp_pre[w] = run;
+                    run = mul(run, warp_incl[w]);
+                }
+                const Fr total = run;
+                run = Fr::one();
+#pragma unroll
+                for (int w = kThreads / 32 - 1; w >= 0; --w)
+                {
+                    warp_suf[w] = run;
+                    run = mul(run, warp_incl[w]);
+                }
+                if (total.is_zero()) atomicExch(status, GZK_E_DOMAIN);
+                cta_inverse = inv(total);
+            }
+            __syncthreads();
+            const Fr outer = mul(cta_inverse, mul(mul(left, warp_pre[warp]), mul(right, warp_suf[warp])));
+            Fr rest = mul(a.scale, outer);  // (x^n-1)/n over the product of the thread's denominators 0 .. j
+#pragma unroll
+            for (int j = kElems - 1; j >= 0; --j)
+            {
+                const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
+                const Fr scaled_inverse = mul(rest, pre[j]);  // (x^n-1)/n / D_e
+                if (j > 0) rest = mul(rest, d[j]);
+                if (e >= a.n) continue;
+                const Fr p1 = domain_point(a.lo, a.hi, a.lo_bits, e);
+                const Fr p2 = sqr(p1);
+                const Fr ip1 = mul(a.root4, p1);
+                const Fr plus = add(a.x2, p2), minus = sub(a.x2, p2);
+                const Fr ea = mul(scaled_inverse, p1), eia = mul(scaled_inverse, ip1);
+                store_fr(out + e, mul(ea, mul(add(a.x, p1), plus)));                          // point  a
+                store_fr(out + e + 2 * a.n, neg(mul(ea, mul(sub(a.x, p1), plus))));           // point -a
+                store_fr(out + e + a.n, mul(eia, mul(add(a.x, ip1), minus)));                 // point  Ia
+                store_fr(out + e + 3 * a.n, neg(mul(eia, mul(sub(a.x, ip1), minus))));        // point -Ia
+            }
+        }
+    }
+
     // Shared with other translation units: in-place batch inversion of a device
     // array of Montgomery values by one CTA; `tmp` must hold `count` elements.
     int launch_batch_invert_single_cta(gzk_ctx* ctx, Fr* values, Fr* tmp, uint32_t count)
@@ -389,14 +476,8 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     if (quartets)
     {
         {
-            LaunchScope scope(ctx, "bary_products");
-            bary4_products_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, ctx->d_status);
-        }
-        GZK_CUDA_TRY(ctx, cudaGetLastError());
-        if ((rc = launch_batch_invert_single_cta(ctx, products, tmp, blocks)) != GZK_OK) return rc;
-        {
-            LaunchScope scope(ctx, "bary_finish");
-            bary4_finish_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, static_cast<Fr*>(out->dptr));
+            LaunchScope scope(ctx, "bary_fused");
+            bary4_fused_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         rc = finish_call(ctx, "bary_weights: invalid input");

@@ -94,6 +94,10 @@ struct gzk_ctx
     std::vector<gzk::FamilyStat> families;
     std::vector<gzk::TimedLaunch> pending;
     std::vector<cudaEvent_t> event_pool;
+    // work counters of the packed-evaluation launches since the last gzk_timing_reset
+    uint64_t eval_algorithmic_bytes = 0;  // column values once per launch + the weights once per rotation
+    uint64_t eval_limb_products = 0;      // 32x32-bit products of the inner loops
+    uint64_t eval_terms = 0;              // (row, column, rotation) terms
 };
 
 namespace gzk

@@ -125,6 +125,7 @@ namespace gzk
         cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
         if (status == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "batch_invert encountered zero");
         if (status == GZK_E_TIMEOUT) return fail(ctx, GZK_E_TIMEOUT, "a bounded wait on a bulk copy gave up");
+        if (status != GZK_E_INVALID) return fail(ctx, GZK_E_INVALID, std::string(invalid_message) + " [unexpected status word " + std::to_string(status) + "]");
         return fail(ctx, GZK_E_INVALID, invalid_message);
     }
 
@@ -359,6 +360,18 @@ extern "C"
             f.launches = 0;
             f.total_ms = 0.0;
         }
+        ctx->eval_algorithmic_bytes = 0;
+        ctx->eval_limb_products = 0;
+        ctx->eval_terms = 0;
+        return GZK_OK;
+    }
+
+    int gzk_eval_work_counters(gzk_ctx* ctx, uint64_t out[3])
+    {
+        if (ctx == nullptr || out == nullptr) return GZK_E_INVALID;
+        out[0] = ctx->eval_algorithmic_bytes;
+        out[1] = ctx->eval_limb_products;
+        out[2] = ctx->eval_terms;
         return GZK_OK;
     }
 
@@ -502,6 +515,30 @@ extern "C"
         if (ctx == nullptr) return GZK_E_INVALID;
         GZK_CUDA_TRY(ctx, cudaEventRecord(ctx->copy_event, ctx->copy_stream));
         GZK_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, ctx->copy_event, 0));
+        return GZK_OK;
+    }
+
+    // Pins (page-locks) a range of the caller's host memory so that uploads from it run as DMA at the
+    // full host-to-device rate instead of through the runtime's staging copies.
+    int gzk_host_register(void* host, size_t bytes)
+    {
+        if (host == nullptr || bytes == 0) return GZK_E_INVALID;
+        const cudaError_t err = cudaHostRegister(host, bytes, cudaHostRegisterDefault);
+        if (err != cudaSuccess)
+        {
+            cudaGetLastError();
+            return GZK_E_CUDA;
+        }
+        return GZK_OK;
+    }
+    int gzk_host_unregister(void* host)
+    {
+        if (host == nullptr) return GZK_E_INVALID;
+        if (cudaHostUnregister(host) != cudaSuccess)
+        {
+            cudaGetLastError();
+            return GZK_E_CUDA;
+        }
         return GZK_OK;
     }
 

@@ -506,6 +506,20 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     if (dest != nullptr && (rc = begin_call(ctx)) != GZK_OK) return rc;
 
     uint8_t* h_out = static_cast<uint8_t*>(h_table) + table_padded;
+    {
+        // per launch pair: every column element once (4 / 8 / 32 bytes), the weights once per rotation
+        uint64_t column_bytes = 0, limbs = 0;
+        for (size_t k = 0; k < k_count; ++k)
+        {
+            const int kind = cols[k]->kind;
+            column_bytes += len * (kind == GZK_KIND_U32 ? 4u : kind == GZK_KIND_I64 ? 8u : 32u);
+            limbs += len * (kind == GZK_KIND_U32 ? 8u : kind == GZK_KIND_I64 ? 16u : 64u);
+        }
+        const uint64_t launches = (p_count + 1) / 2;
+        ctx->eval_algorithmic_bytes += launches * column_bytes + p_count * len * 32;
+        ctx->eval_limb_products += limbs * p_count;
+        ctx->eval_terms += static_cast<uint64_t>(len) * k_count * p_count;
+    }
     for (size_t p0 = 0; p0 < p_count; p0 += 2)
     {
         const uint32_t p_now = p_count - p0 >= 2 ? 2 : 1;

@@ -34,6 +34,8 @@ namespace gzk
             ColRef features;      // kFeature
             ColRef abs_ids;       // kAbsId (U32 or I64, one per row)
             uint32_t* partial;    // [warp][17]
+            uint64_t rotation;    // entry i meets weights[(i - rotation) & mask]
+            uint64_t mask;        // domain size - 1 when rotated, all ones otherwise
         };
 
         template <int GEN>
@@ -49,7 +51,7 @@ namespace gzk
             acc.clear();
             for (uint64_t i = begin + lane; i < end; i += 32)
             {
-                Fr w = load_fr(a.weights + i);
+                Fr w = load_fr(a.weights + ((i - a.rotation) & a.mask));
                 if (GEN == kOnes)
                 {
                     const uint32_t one = 1;
@@ -112,8 +114,29 @@ namespace gzk
 using namespace gzk;
 
 // out[0..4] = sum_{i < rows*feature_count} w[i] * {1, i / fc, i % fc, abs_ids[i / fc], features[i]}
+static int fh_public_eval_impl(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
+                               const gzk_buf* weights, uint64_t rotation, uint64_t mask, uint8_t out[5 * 32]);
+
 extern "C" int gzk_fh_public_eval(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
                                   const gzk_buf* weights, uint8_t out[5 * 32])
+{
+    return fh_public_eval_impl(ctx, features, rows, feature_count, abs_ids, weights, 0, ~0ULL, out);
+}
+
+// The same sums at the rotated point omega^rotation * z from the weights at z: the weight of entry i at
+// the rotated point is weights[(i - rotation) mod n] (w_i(omega z) = w_{i-1}(z)), so no second weight
+// vector is needed for the {z, omega z} pairs of the prover.
+extern "C" int gzk_fh_public_eval_rotated(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
+                                          const gzk_buf* weights, unsigned log2n, uint64_t rotation, uint8_t out[5 * 32])
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (log2n > 32 || weights == nullptr || weights->count < (1ULL << log2n) || rotation >= (1ULL << log2n))
+        return fail(ctx, GZK_E_INVALID, "fh_public_eval_rotated: needs the weights of the whole domain and a rotation inside it");
+    return fh_public_eval_impl(ctx, features, rows, feature_count, abs_ids, weights, rotation, (1ULL << log2n) - 1, out);
+}
+
+static int fh_public_eval_impl(gzk_ctx* ctx, const gzk_buf* features, size_t rows, size_t feature_count, const gzk_buf* abs_ids,
+                               const gzk_buf* weights, uint64_t rotation, uint64_t mask, uint8_t out[5 * 32])
 {
     if (ctx == nullptr) return GZK_E_INVALID;
     if (out == nullptr) return fail(ctx, GZK_E_INVALID, "fh_public_eval: null output");
@@ -135,6 +158,8 @@ extern "C" int gzk_fh_public_eval(gzk_ctx* ctx, const gzk_buf* features, size_t 
     if (rc != GZK_OK) return rc;
     LazyArgs args{};
     args.weights = static_cast<const Fr*>(weights->dptr);
+    args.rotation = rotation;
+    args.mask = mask;
     args.valid = valid;
     args.feature_count = static_cast<uint32_t>(feature_count);
     if (features != nullptr)

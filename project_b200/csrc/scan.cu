@@ -115,14 +115,24 @@ namespace gzk
         // LOCAL_INV: the CTA inverts the product of its own 1024 denominators (one serial
         // inversion per CTA, all CTAs in parallel) instead of reading the result of the
         // product / single-CTA-inversion passes; used when the whole grid is resident at once.
-        template <int OP, bool LOCAL_INV>
-        __global__ void __launch_bounds__(kThreads) scan_main_kernel(ScanArgs a)
+        // Shared memory of one CTA of the main pass (the batched kernel shares one copy between its ops).
+        struct MainShared
         {
-            __shared__ Fr slots[3 * kWarps];
-            __shared__ Fr local_inverse;
-            __shared__ SegVal seg_slots[kWarps];
-            __shared__ uint32_t first_flag;
-            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk + static_cast<uint64_t>(threadIdx.x) * kElems;
+            Fr slots[3 * kWarps];
+            Fr local_inverse;
+            SegVal seg_slots[kWarps];
+            uint32_t first_flag;
+        };
+
+        // `block`: index of the CTA within its own job (blockIdx.x for a single-job launch).
+        template <int OP, bool LOCAL_INV>
+        __device__ __forceinline__ void scan_main_body(const ScanArgs& a, uint32_t block, MainShared& sh)
+        {
+            Fr* slots = sh.slots;
+            Fr& local_inverse = sh.local_inverse;
+            SegVal* seg_slots = sh.seg_slots;
+            uint32_t& first_flag = sh.first_flag;
+            const uint64_t base = static_cast<uint64_t>(block) * kChunk + static_cast<uint64_t>(threadIdx.x) * kElems;
             if (threadIdx.x == 0) first_flag = kChunk;
             __syncthreads();
 
@@ -157,7 +167,7 @@ namespace gzk
                 }
                 else
                 {
-                    cta_inverse = load_fr(a.cta_products + blockIdx.x);
+                    cta_inverse = load_fr(a.cta_products + block);
                 }
                 const Fr outer = block_invert_products<kThreads>(mine, cta_inverse, slots);
                 Fr rest = outer;  // inverse of the product of the thread's rows 0 .. j
@@ -258,10 +268,17 @@ namespace gzk
             }
             if (threadIdx.x == 0)
             {
-                store_fr(a.agg_value + blockIdx.x, aggregate.v);
-                a.agg_flag[blockIdx.x] = aggregate.flag;
-                a.agg_first[blockIdx.x] = first_flag;
+                store_fr(a.agg_value + block, aggregate.v);
+                a.agg_flag[block] = aggregate.flag;
+                a.agg_first[block] = first_flag;
             }
+        }
+
+        template <int OP, bool LOCAL_INV>
+        __global__ void __launch_bounds__(kThreads) scan_main_kernel(ScanArgs a)
+        {
+            __shared__ MainShared sh;
+            scan_main_body<OP, LOCAL_INV>(a, blockIdx.x, sh);
         }
 
         // Exclusive segmented scan of the CTA aggregates (in place) by one CTA.
@@ -346,12 +363,18 @@ namespace gzk
         // CTA re-adds at most a few thousand 32-byte values from L2), which saves the separate
         // single-CTA scan of the aggregates when there are few of them.  A CTA covers kThreads
         // consecutive outputs, all inside one chunk of the main pass.
-        template <int OP>
-        __global__ void __launch_bounds__(kThreads) scan_fixup_fused_kernel(ScanArgs a, uint32_t ctas)
+        struct FixupShared
         {
-            __shared__ Fr warp_slots[kWarps];
-            __shared__ int last_start;
-            const uint64_t first = static_cast<uint64_t>(blockIdx.x) * kThreads;
+            Fr warp_slots[kWarps];
+            int last_start;
+        };
+
+        template <int OP>
+        __device__ __forceinline__ void scan_fixup_fused_body(const ScanArgs& a, uint32_t ctas, uint32_t block, FixupShared& sh)
+        {
+            Fr* warp_slots = sh.warp_slots;
+            int& last_start = sh.last_start;
+            const uint64_t first = static_cast<uint64_t>(block) * kThreads;
             const uint64_t idx = first + threadIdx.x;
             const uint32_t chunk = static_cast<uint32_t>(first / kChunk);
             if (OP == kSegmented)
@@ -375,7 +398,7 @@ namespace gzk
             }
             // out[idx] for 1 <= idx <= count belongs to chunk (idx - 1) / kChunk: the CTA's first output sits
             // one chunk lower when the CTA starts on a chunk boundary
-            const bool needs_total = first + kThreads > a.count + 1 || blockIdx.x == 0;
+            const bool needs_total = first + kThreads > a.count + 1 || block == 0;
             Fr before = Fr::zero(), rest = Fr::zero();
             const uint32_t limit = needs_total ? ctas : chunk;
             for (uint32_t i = threadIdx.x; i < limit; i += kThreads)
@@ -389,7 +412,7 @@ namespace gzk
             const Fr offset = cta_sum(before, warp_slots);
             Fr total = offset;
             if (needs_total) total = add(offset, cta_sum(rest, warp_slots));
-            if (blockIdx.x == 0 && threadIdx.x == 0) store_fr(a.total, total);
+            if (block == 0 && threadIdx.x == 0) store_fr(a.total, total);
             if (idx >= a.n) return;
             if (idx == 0)
             {
@@ -409,6 +432,69 @@ namespace gzk
             else
             {
                 store_fr(a.out + idx, total);
+            }
+        }
+
+        template <int OP>
+        __global__ void __launch_bounds__(kThreads) scan_fixup_fused_kernel(ScanArgs a, uint32_t ctas)
+        {
+            __shared__ FixupShared sh;
+            scan_fixup_fused_body<OP>(a, ctas, blockIdx.x, sh);
+        }
+
+        // ---- several independent running sums in one pair of launches ---------------------------------
+        // The column builders between two Fiat-Shamir points of one attention head (three or four lookup
+        // accumulators, the node and edge sums of a routing argument, the segmented states) do not depend
+        // on one another.  Each alone is a latency chain on a third of the machine (one serial inversion
+        // per CTA); queued as ONE grid their chains overlap and the launch count drops from 2 J to 2.
+        // A CTA finds its job from the prefix table of CTA counts and runs that job's body.
+        constexpr int kMaxBatchJobs = 16;
+        struct BatchJob
+        {
+            ScanArgs args;
+            int op;
+            uint32_t main_begin, main_ctas;    // CTAs of the main pass: [main_begin, main_begin + main_ctas)
+            uint32_t fix_begin, fix_ctas;      // CTAs of the fix-up pass
+        };
+        struct BatchTable
+        {
+            BatchJob jobs[kMaxBatchJobs];
+            uint32_t count;
+        };
+
+        __global__ void __launch_bounds__(kThreads) scan_batch_main_kernel(const BatchTable* table)
+        {
+            __shared__ MainShared sh;
+            uint32_t j = 0;
+            while (j + 1 < table->count && blockIdx.x >= table->jobs[j + 1].main_begin) ++j;
+            const BatchJob& job = table->jobs[j];
+            const uint32_t block = blockIdx.x - job.main_begin;
+            if (block >= job.main_ctas) return;
+            switch (job.op)
+            {
+            case kLogup: scan_main_body<kLogup, true>(job.args, block, sh); break;
+            case kRouteNode: scan_main_body<kRouteNode, true>(job.args, block, sh); break;
+            case kRouteEdge: scan_main_body<kRouteEdge, true>(job.args, block, sh); break;
+            case kProduct: scan_main_body<kProduct, true>(job.args, block, sh); break;
+            default: scan_main_body<kSegmented, true>(job.args, block, sh); break;
+            }
+        }
+
+        __global__ void __launch_bounds__(kThreads) scan_batch_fixup_kernel(const BatchTable* table)
+        {
+            __shared__ FixupShared sh;
+            uint32_t j = 0;
+            while (j + 1 < table->count && blockIdx.x >= table->jobs[j + 1].fix_begin) ++j;
+            const BatchJob& job = table->jobs[j];
+            const uint32_t block = blockIdx.x - job.fix_begin;
+            if (block >= job.fix_ctas) return;
+            switch (job.op)
+            {
+            case kLogup: scan_fixup_fused_body<kLogup>(job.args, job.main_ctas, block, sh); break;
+            case kRouteNode: scan_fixup_fused_body<kRouteNode>(job.args, job.main_ctas, block, sh); break;
+            case kRouteEdge: scan_fixup_fused_body<kRouteEdge>(job.args, job.main_ctas, block, sh); break;
+            case kProduct: scan_fixup_fused_body<kProduct>(job.args, job.main_ctas, block, sh); break;
+            default: scan_fixup_fused_body<kSegmented>(job.args, job.main_ctas, block, sh); break;
             }
         }
 
@@ -596,6 +682,131 @@ extern "C"
         args.beta = Fr::zero();
         args.out = static_cast<Fr*>(out_acc->dptr);
         return run_scan<kProduct>(ctx, args, false, mu_out);
+    }
+
+    int gzk_running_sums_batch(gzk_ctx* ctx, const gzk_scan_job* jobs, size_t job_count)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (job_count == 0) return GZK_OK;
+        if (jobs == nullptr) return fail(ctx, GZK_E_INVALID, "running_sums_batch: null job list");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        int rc = begin_call(ctx);
+        if (rc != GZK_OK) return rc;
+        size_t done = 0;
+        while (done < job_count)
+        {
+            // jobs are queued in groups of at most kMaxBatchJobs
+            BatchTable table{};
+            size_t scratch_frs = 0, scratch_u32 = 0;
+            struct Layout
+            {
+                size_t fr_at, u32_at;
+            } layout[kMaxBatchJobs];
+            uint32_t main_total = 0, fix_total = 0;
+            while (done < job_count && table.count < kMaxBatchJobs)
+            {
+                const gzk_scan_job& j = jobs[done];
+                BatchJob& b = table.jobs[table.count];
+                ScanArgs& a = b.args;
+                a = ScanArgs{};
+                a.beta = Fr::zero();
+                size_t count = j.count;
+                const size_t n = j.domain_size;
+                if (!out_ok(j.out, n)) return fail(ctx, GZK_E_INVALID, "running_sums_batch: every output must be a Montgomery buffer of its domain size");
+                if (n == 0)
+                {
+                    ++done;
+                    continue;
+                }
+                switch (j.op)
+                {
+                case GZK_SCAN_LOGUP:
+                    if (count > n - 1) count = n - 1;
+                    if (j.beta == nullptr || !col_ok(j.c0, count) || !col_ok(j.c1, count) || !col_ok(j.c2, count) || !col_ok(j.c3, count) || !col_ok(j.c4, count))
+                        return fail(ctx, GZK_E_INVALID, "lookup accumulator input size mismatch");
+                    a.c0 = ref(j.c0);
+                    a.c1 = ref(j.c1);
+                    a.c2 = ref(j.c2);
+                    a.c3 = ref(j.c3);
+                    a.c4 = ref(j.c4);
+                    break;
+                case GZK_SCAN_ROUTE_NODE:
+                    if (count >= n) return fail(ctx, GZK_E_INVALID, "route accumulator needs valid_length < domain_size");
+                    if (j.beta == nullptr || !col_ok(j.c0, count) || !col_ok(j.c1, count)) return fail(ctx, GZK_E_INVALID, "route node accumulator input size mismatch");
+                    a.c0 = ref(j.c0);
+                    a.c1 = ref(j.c1);
+                    break;
+                case GZK_SCAN_ROUTE_EDGE:
+                    if (count >= n) return fail(ctx, GZK_E_INVALID, "route accumulator needs valid_length < domain_size");
+                    if (j.beta == nullptr || !col_ok(j.c0, count)) return fail(ctx, GZK_E_INVALID, "route edge accumulator input size mismatch");
+                    a.c0 = ref(j.c0);
+                    break;
+                case GZK_SCAN_ZKMAP:
+                    if (count != 0 && count + 1 > n) return fail(ctx, GZK_E_INVALID, "zkMaP accumulator exceeds its domain");
+                    if (!col_ok(j.c0, count) || !col_ok(j.c1, count)) return fail(ctx, GZK_E_INVALID, "zkMaP input size mismatch");
+                    a.c0 = ref(j.c0);
+                    a.c1 = ref(j.c1);
+                    break;
+                case GZK_SCAN_GROUP_PREFIX:
+                    count = n;
+                    if (!col_ok(j.c0, n) || !col_ok(j.c1, n)) return fail(ctx, GZK_E_INVALID, "prefix state input size mismatch");
+                    a.c0 = ref(j.c0);
+                    a.c1 = ref(j.c1);
+                    break;
+                default: return fail(ctx, GZK_E_INVALID, "running_sums_batch: unknown operation");
+                }
+                if (j.op <= GZK_SCAN_ROUTE_EDGE && (rc = load_scalar(ctx, j.beta, &a.beta, &a.beta_canon)) != GZK_OK) return rc;
+                a.count = count;
+                a.n = n;
+                a.out = static_cast<Fr*>(j.out->dptr);
+                a.status = ctx->d_status;
+                const uint64_t span = j.op == GZK_SCAN_GROUP_PREFIX ? n : count;
+                const uint64_t ctas = (span + kChunk - 1) / kChunk > 0 ? (span + kChunk - 1) / kChunk : 1;
+                if (ctas > 2048) return fail(ctx, GZK_E_INVALID, "running_sums_batch: at most 2^20 rows per job; use the single-column entry point for longer columns");
+                b.op = j.op == GZK_SCAN_LOGUP ? kLogup : j.op == GZK_SCAN_ROUTE_NODE ? kRouteNode : j.op == GZK_SCAN_ROUTE_EDGE ? kRouteEdge
+                       : j.op == GZK_SCAN_ZKMAP ? kProduct : kSegmented;
+                b.main_begin = main_total;
+                b.main_ctas = static_cast<uint32_t>(ctas);
+                b.fix_begin = fix_total;
+                b.fix_ctas = static_cast<uint32_t>((n + kThreads - 1) / kThreads);
+                main_total += b.main_ctas;
+                fix_total += b.fix_ctas;
+                layout[table.count] = {scratch_frs, scratch_u32};
+                scratch_frs += ctas + 1;       // aggregates + total
+                scratch_u32 += 2 * ctas;       // flags + first-restart marks
+                ++table.count;
+                ++done;
+            }
+            if (table.count == 0) continue;
+            const size_t table_bytes = (sizeof(BatchTable) + 31) & ~static_cast<size_t>(31);
+            void* scratch = nullptr;
+            if ((rc = ensure_scratch(ctx, 2, table_bytes + scratch_frs * sizeof(Fr) + scratch_u32 * sizeof(uint32_t), &scratch)) != GZK_OK) return rc;
+            Fr* fr_base = reinterpret_cast<Fr*>(static_cast<char*>(scratch) + table_bytes);
+            uint32_t* u32_base = reinterpret_cast<uint32_t*>(fr_base + scratch_frs);
+            for (uint32_t t = 0; t < table.count; ++t)
+            {
+                ScanArgs& a = table.jobs[t].args;
+                const uint32_t ctas = table.jobs[t].main_ctas;
+                a.cta_products = nullptr;  // every CTA inverts its own product
+                a.agg_value = fr_base + layout[t].fr_at;
+                a.total = a.agg_value + ctas;
+                a.agg_flag = u32_base + layout[t].u32_at;
+                a.agg_first = a.agg_flag + ctas;
+            }
+            // the table travels from pageable memory of this call: the copy is staged before the call returns
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(scratch, &table, sizeof(BatchTable), cudaMemcpyHostToDevice, ctx->stream));
+            {
+                LaunchScope scope(ctx, "scan_batch_main");
+                scan_batch_main_kernel<<<main_total, kThreads, 0, ctx->stream>>>(static_cast<const BatchTable*>(scratch));
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            {
+                LaunchScope scope(ctx, "scan_batch_fixup");
+                scan_batch_fixup_kernel<<<fix_total, kThreads, 0, ctx->stream>>>(static_cast<const BatchTable*>(scratch));
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+        }
+        return finish_call(ctx, "q_new must hold only 0 and 1");
     }
 
     int gzk_group_prefix_state(gzk_ctx* ctx, const gzk_buf* values, const gzk_buf* q_new, size_t n, gzk_buf* out)

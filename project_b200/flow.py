@@ -53,8 +53,8 @@ class Flow:
         if rc != 0:
             raise FlowError(self._fn("error")().decode())
 
-    def prove(self):
-        self._check(self._fn("prove")(self.handle))
+    def prove(self, inputs_resident=False):
+        self._check(self._fn("prove_resident" if inputs_resident else "prove")(self.handle))
 
     def dump(self):
         fn = self._fn("dump")
@@ -71,11 +71,11 @@ class Flow:
         return buf
 
     def stats(self):
-        out = (ctypes.c_uint64 * 11)()
+        out = (ctypes.c_uint64 * 13)()
         self._check(self._fn("stats")(self.handle, out))
         v = list(out)
         return {"commit_barriers": v[0], "challenges": v[1], "dynamic_commitments": v[2], "opened_columns": v[3],
-                "domains": dict(zip(DOMAINS, v[4:]))}
+                "domains": dict(zip(DOMAINS, v[4:11])), "h2d_bytes": v[11], "d2h_bytes": v[12]}
 
     def domain_labels(self, domain):
         fn = self._fn("domain_labels")

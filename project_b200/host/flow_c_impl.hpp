@@ -94,9 +94,9 @@ namespace gatzk_flow
             *out = handle.release();
         });
     }
-    inline int flow_prove_impl(FlowHandle* h)
+    inline int flow_prove_impl(FlowHandle* h, bool inputs_resident = false)
     {
-        return flow_guard([&] { h->flow->prove(); });
+        return flow_guard([&] { h->flow->prove(inputs_resident); });
     }
     inline std::size_t copy_out(const std::string& s, char* out, std::size_t cap)
     {
@@ -110,7 +110,7 @@ namespace gatzk_flow
         if (out != nullptr && cap > 0) std::memcpy(out, bytes.data(), std::min(cap, bytes.size()));
         return bytes.size();
     }
-    inline int flow_stats_impl(FlowHandle* h, std::uint64_t out[11])
+    inline int flow_stats_impl(FlowHandle* h, std::uint64_t out[13])
     {
         const auto& s = h->flow->stats();
         out[0] = s.commit_barriers;
@@ -119,6 +119,8 @@ namespace gatzk_flow
         out[3] = s.opened_columns;
         static const char* names[7] = {"FH", "edge", "in", "d", "cat", "C", "N"};
         for (int i = 0; i < 7; ++i) out[4 + i] = h->flow->domain_size(names[i]);
+        out[11] = h->backend->uploaded_bytes;
+        out[12] = h->backend->downloaded_bytes;
         return 0;
     }
     inline int flow_column_impl(FlowHandle* h, const char* label, int* kind, std::uint64_t* length, void* out, std::size_t cap_elements)

@@ -69,10 +69,15 @@ namespace
             }
             return c;
         }
-        void upload(const ColP& col, const void* host, std::size_t count) override { check(gzk_buf_upload(ctx_, raw(col), 0, host, count)); }
+        void upload(const ColP& col, const void* host, std::size_t count) override
+        {
+            check(gzk_buf_upload(ctx_, raw(col), 0, host, count));
+            uploaded_bytes += count * element_bytes(col->kind);
+        }
         void download(const ColP& col, std::size_t offset, std::size_t count, void* host) override
         {
             check(gzk_buf_download(ctx_, raw(col), offset, host, count));
+            downloaded_bytes += count * element_bytes(col->kind);
         }
         void zero(const ColP& col) override { check(gzk_buf_zero(ctx_, raw(col))); }
         void copy_block(const ColP& src, std::size_t so, std::size_t ss, const ColP& dst, std::size_t d_o, std::size_t ds, std::size_t rows,
@@ -175,6 +180,26 @@ namespace
         {
             check(gzk_zkmap_accumulator(ctx_, raw(a), raw(b), count, domain_size, raw(out), nullptr));
         }
+        void running_sums_batch(const std::vector<ScanJob>& jobs) override
+        {
+            std::vector<gzk_scan_job> raw_jobs(jobs.size());
+            for (std::size_t i = 0; i < jobs.size(); ++i)
+            {
+                const ScanJob& j = jobs[i];
+                gzk_scan_job& r = raw_jobs[i];
+                r.op = j.op;  // the numbering of ScanJob::Op is that of GZK_SCAN_*
+                r.c0 = j.c0 ? raw(j.c0) : nullptr;
+                r.c1 = j.c1 ? raw(j.c1) : nullptr;
+                r.c2 = j.c2 ? raw(j.c2) : nullptr;
+                r.c3 = j.c3 ? raw(j.c3) : nullptr;
+                r.c4 = j.c4 ? raw(j.c4) : nullptr;
+                r.count = j.count;
+                r.domain_size = j.domain_size;
+                r.beta = j.op <= ScanJob::kRouteEdge ? j.beta.data() : nullptr;
+                r.out = raw(j.out);
+            }
+            check(gzk_running_sums_batch(ctx_, raw_jobs.data(), raw_jobs.size()));
+        }
         void bary_weights(unsigned log2n, const Fe& x, const ColP& out) override { check(gzk_bary_weights(ctx_, log2n, x.data(), raw(out))); }
         void fold_rows(const ColP& m, std::size_t rows, std::size_t cols, const ColP& weights, std::size_t row_count, const ColP& out) override
         {
@@ -195,15 +220,17 @@ namespace
         {
             check(gzk_g1_fixed_base_mul(ctx_, base.data(), raw(scalars), count, raw(out_points)));
         }
-        void fh_public_eval(const ColP& features, std::size_t rows, std::size_t fc, const ColP& abs_ids, const ColP& weights, Fe out[5]) override
+        void fh_public_eval(const ColP& features, std::size_t rows, std::size_t fc, const ColP& abs_ids, const ColP& weights, unsigned log2n,
+                            std::uint64_t rotation, Fe out[5]) override
         {
             std::uint8_t bytes[5 * 32];
-            check(gzk_fh_public_eval(ctx_, raw(features), rows, fc, abs_ids ? raw(abs_ids) : nullptr, raw(weights), bytes));
+            check(gzk_fh_public_eval_rotated(ctx_, raw(features), rows, fc, abs_ids ? raw(abs_ids) : nullptr, raw(weights), log2n, rotation, bytes));
             for (int i = 0; i < 5; ++i) std::memcpy(out[i].data(), bytes + 32 * i, 32);
         }
         void synchronize() override { check(gzk_ctx_synchronize(ctx_)); }
 
     private:
+        static std::size_t element_bytes(int kind) { return kind == kU32 ? 4 : (kind == kI64 || kind == kF64) ? 8 : kind == kG1 ? 96 : 32; }
         static gzk_buf* raw(const ColP& c)
         {
             if (c == nullptr) throw std::runtime_error("flow: missing column");
@@ -237,19 +264,26 @@ extern "C"
         const int rc0 = gatzk_flow::flow_guard([&] { backend = std::make_unique<GpuBackend>(device); });
         if (rc0 != 0) return rc0;
         const int rc = gatzk_flow::flow_create_impl(std::move(backend), config, &handle);
-        if (rc == 0) *out = static_cast<gzk_flow*>(handle);
+        if (rc != 0) return rc;
+        // the per-proof upload of the feature matrix comes from this copy: page-lock it (best effort)
+        const auto& features = handle->flow->inputs().features;
+        if (!features.empty()) gzk_host_register(const_cast<double*>(features.data()), features.size() * sizeof(double));
+        *out = static_cast<gzk_flow*>(handle);
         return rc;
     }
     void gzk_flow_destroy(gzk_flow* flow)
     {
         if (flow == nullptr) return;
+        if (flow->flow != nullptr && !flow->flow->inputs().features.empty())
+            gzk_host_unregister(const_cast<double*>(flow->flow->inputs().features.data()));
         flow->flow.reset();  // columns go before the context
         delete static_cast<gatzk_flow::FlowHandle*>(flow);
     }
-    int gzk_flow_prove(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow); }
+    int gzk_flow_prove(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow, false); }
+    int gzk_flow_prove_resident(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow, true); }
     size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap) { return gatzk_flow::flow_dump_impl(flow, out, cap); }
     size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap) { return gatzk_flow::flow_proof_bytes_impl(flow, out, cap); }
-    int gzk_flow_stats(gzk_flow* flow, uint64_t out[11]) { return gatzk_flow::flow_stats_impl(flow, out); }
+    int gzk_flow_stats(gzk_flow* flow, uint64_t out[13]) { return gatzk_flow::flow_stats_impl(flow, out); }
     int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements)
     {
         return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);

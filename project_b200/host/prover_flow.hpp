@@ -74,7 +74,19 @@ namespace gatzk_flow
         ColP H_prime, E_src, E_dst, M, Sum, inv, S, Z, Delta, U, alpha, H_agg_pre_bias, H_agg;  // F64
     };
 
-    // The compute backend: every call is one leaf of SURVEY-style rows a2-a11 of the hot path.
+    // One running-sum column to build: the arguments of Backend::logup / route_node / route_edge /
+    // zkmap / group_prefix_state, so that independent ones can be handed over together.
+    struct ScanJob
+    {
+        enum Op : int { kLogup = 0, kRouteNode = 1, kRouteEdge = 2, kZkmap = 3, kGroupPrefix = 4 };
+        int op = kLogup;
+        ColP c0, c1, c2, c3, c4;
+        std::size_t count = 0, domain_size = 0;
+        Fe beta{};
+        ColP out;
+    };
+
+    // The compute backend: every call is one data-parallel leaf of the hot path.
     class Backend
     {
     public:
@@ -111,6 +123,21 @@ namespace gatzk_flow
         virtual void route_edge(const ColP& query, std::size_t valid, std::size_t domain_size, const Fe& beta, const ColP& out) = 0;
         virtual void group_prefix_state(const ColP& values, const ColP& q_new, std::size_t n, const ColP& out) = 0;
         virtual void zkmap(const ColP& a, const ColP& b, std::size_t count, std::size_t domain_size, const ColP& out) = 0;
+        // independent running sums of one phase; a backend may run them in one launch
+        virtual void running_sums_batch(const std::vector<ScanJob>& jobs)
+        {
+            for (const auto& j : jobs)
+            {
+                switch (j.op)
+                {
+                case ScanJob::kLogup: logup(j.c0, j.c1, j.c2, j.c3, j.c4, j.domain_size, j.beta, j.count, j.out); break;
+                case ScanJob::kRouteNode: route_node(j.c0, j.c1, j.count, j.domain_size, j.beta, j.out); break;
+                case ScanJob::kRouteEdge: route_edge(j.c0, j.count, j.domain_size, j.beta, j.out); break;
+                case ScanJob::kZkmap: zkmap(j.c0, j.c1, j.count, j.domain_size, j.out); break;
+                default: group_prefix_state(j.c0, j.c1, j.domain_size, j.out); break;
+                }
+            }
+        }
         // a2 / a9: weights and row folds
         virtual void bary_weights(unsigned log2n, const Fe& x, const ColP& out) = 0;
         virtual void fold_rows(const ColP& matrix, std::size_t rows, std::size_t cols, const ColP& weights, std::size_t row_count, const ColP& out) = 0;
@@ -119,9 +146,12 @@ namespace gatzk_flow
                                  const std::vector<std::uint64_t>& rotations, const ColP& out, std::size_t out_offset) = 0;
         virtual void horner_device(const ColP& matrix, std::size_t rows, std::size_t cols, const Fe& x, const ColP& out, std::size_t out_offset) = 0;
         virtual void g1_fixed_base(const G1& base, const ColP& scalars, std::size_t count, const ColP& out_points) = 0;
+        // weights: those of the whole 2^log2n domain at a point z; rotation r gives the sums at omega^r * z
         virtual void fh_public_eval(const ColP& features, std::size_t rows, std::size_t feature_count, const ColP& abs_ids, const ColP& weights,
-                                    Fe out[5]) = 0;
+                                    unsigned log2n, std::uint64_t rotation, Fe out[5]) = 0;
         virtual void synchronize() = 0;
+        // bytes moved between host and backend since the last reset (end-to-end accounting)
+        std::uint64_t uploaded_bytes = 0, downloaded_bytes = 0;
     };
 
     // ---- host scalars -------------------------------------------------------------------------
@@ -289,14 +319,16 @@ namespace gatzk_flow
         ProverFlow(Backend& backend, FlowInputs inputs) : be_(backend), in_(std::move(inputs)) { setup(); }
 
         // One commit + prove pass from the host inputs (features, parameters, graph).  Nothing that
-        // depends on the witness is reused between calls.
-        void prove();
+        // depends on the witness is reused between calls.  inputs_resident: the fp64 feature matrix is
+        // taken from the copy uploaded at set-up instead of being uploaded again.
+        void prove(bool inputs_resident = false);
 
         const gatzk_b200::protocol::Proof& proof() const { return proof_; }
         const std::vector<std::pair<std::string, Fe>>& challenges() const { return challenge_log_; }
         const std::vector<std::pair<std::string, Fe>>& tau_evaluations() const { return tau_eval_log_; }
         const std::vector<std::pair<std::string, Fe>>& quotient_scalars() const { return quotient_log_; }
         const FlowStats& stats() const { return stats_; }
+        const FlowInputs& inputs() const { return in_; }
         std::size_t domain_size(const std::string& name) const { return dom_.at(name).size; }
         // a column of the last proof by label (tests compare a few against the CPU restatement)
         ColP column(const std::string& label, std::size_t* length = nullptr) const
@@ -425,6 +457,49 @@ namespace gatzk_flow
         void absorb_dyn(Transcript& t, const std::string& label) { t.absorb_commitment(label, commitments_.at(label).point); }
         void absorb_static(Transcript& t, const std::string& label) { t.absorb_commitment(label, static_commitments_.at(label).point); }
 
+        // running sums are queued and handed to the backend together at the next commit barrier
+        std::vector<ScanJob> scan_queue_;
+        void queue_scan(int op, const ColP& c0, const ColP& c1, const ColP& c2, const ColP& c3, const ColP& c4, std::size_t count,
+                        std::size_t domain_size, const Fe& beta, const ColP& out)
+        {
+            ScanJob j;
+            j.op = op;
+            j.c0 = c0;
+            j.c1 = c1;
+            j.c2 = c2;
+            j.c3 = c3;
+            j.c4 = c4;
+            j.count = count;
+            j.domain_size = domain_size;
+            j.beta = beta;
+            j.out = out;
+            scan_queue_.push_back(j);
+        }
+        void flush_scans()
+        {
+            if (scan_queue_.empty()) return;
+            be_.running_sums_batch(scan_queue_);
+            scan_queue_.clear();
+        }
+        struct PendingTotal
+        {
+            std::string name;
+            ColP column;
+            std::size_t index;
+        };
+        std::vector<PendingTotal> pending_totals_;
+        void resolve_totals()
+        {
+            flush_scans();
+            for (const auto& p : pending_totals_)
+            {
+                Fe v{};
+                be_.download(p.column, p.index, 1, v.data());
+                witness_scalars_.push_back({p.name, v});
+            }
+            pending_totals_.clear();
+        }
+
         struct Binding
         {
             ColP a, b, acc;
@@ -440,8 +515,7 @@ namespace gatzk_flow
                                  const ColP& q_query);
         struct Route
         {
-            ColP table, query, node_acc, edge_acc;
-            Fe total{};
+            ColP table, query, node_acc, edge_acc;  // the routed total is node_acc[node_count]
         };
         Route build_route(const std::vector<ColP>& node_cols, const std::vector<ColP>& edge_cols, const Fe& eta, const ColP& multiplicity,
                           const Fe& beta);
@@ -469,7 +543,7 @@ namespace gatzk_flow
         GraphCols graph_;
         // public / static columns
         ColP ids_i64_, src_i64_, dst_i64_, src_u32_, dst_u32_, q_new_, q_edge_valid_, group_begin_, group_end_, features_q_;
-        ColP src_multiplicity_, dst_multiplicity_;
+        ColP src_multiplicity_, dst_multiplicity_, features_f64_;
         ColP t_range_, t_l_x_, t_l_y_, t_exp_x_, t_exp_y_, t_elu_x_, t_elu_y_;
         ColP q_tbl_l_, q_qry_l_, q_tbl_r_, q_qry_r_, q_tbl_exp_, q_qry_exp_, q_tbl_elu_, q_qry_elu_;
         std::size_t range_size_ = 0, lrelu_bound_ = 0, groups_ = 0;
@@ -478,7 +552,6 @@ namespace gatzk_flow
         std::map<std::string, Commitment> static_commitments_;
         std::map<std::string, ColumnEntry> static_columns_;
         Fe fh_public_tau_[5], fh_public_omega_tau_[5];
-        ColP fh_w_omega_tau_;
         // per-proof state
         std::map<std::string, Commitment> commitments_;
         std::vector<std::string> commitment_order_;
@@ -762,12 +835,11 @@ namespace gatzk_flow
             std::vector<std::int64_t> fq(in_.features.size());
             for (std::size_t i = 0; i < fq.size(); ++i) fq[i] = quantize_value(in_.features[i]);
             features_q_ = upload_i64(fq);
+            features_f64_ = upload_f64(in_.features);
             commit_static_matrix("V_T_H", features_q_, n_nodes_, in_.feature_count);
             const Domain& fh = dom_.at("FH");
-            be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, fh.w_tau, fh_public_tau_);
-            fh_w_omega_tau_ = be_.alloc(kFrMont, fh.size);
-            be_.bary_weights(fh.log2n, mul(tau_, fh.omega), fh_w_omega_tau_);
-            be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, fh_w_omega_tau_, fh_public_omega_tau_);
+            be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, fh.w_tau, fh.log2n, 0, fh_public_tau_);
+            be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, fh.w_tau, fh.log2n, 1, fh_public_omega_tau_);
         }
         be_.synchronize();
     }
@@ -778,38 +850,49 @@ namespace gatzk_flow
     inline void ProverFlow::commit_batch(const std::vector<CommitItem>& items)
     {
         if (items.empty()) return;
+        flush_scans();
+        // Scalars are laid out group by group (matrices first, then the columns of each (domain, stored
+        // length) group), so that a group is ONE evaluation call; `slot` maps an item to its place and
+        // the results are put back into label order on the host after the single read-back.
         const ColP scalars = be_.alloc(kFr, items.size());
         std::map<std::pair<std::string, std::size_t>, std::vector<std::size_t>> groups;
+        std::vector<std::size_t> slot(items.size());
+        std::size_t next = 0;
         for (std::size_t i = 0; i < items.size(); ++i)
         {
             if (items[i].matrix)
-                be_.horner_device(items[i].col, items[i].rows, items[i].cols, tau_, scalars, i);
+            {
+                slot[i] = next;
+                be_.horner_device(items[i].col, items[i].rows, items[i].cols, tau_, scalars, next++);
+            }
             else
+            {
                 groups[{items[i].domain, items[i].length}].push_back(i);
+            }
         }
-        // columns of one group land contiguously in a staging buffer, then move to their slots
         for (const auto& group : groups)
         {
             const Domain& d = dom_.at(group.first.first);
             std::vector<ColP> cols;
-            for (const auto i : group.second) cols.push_back(items[i].col);
-            // consecutive item indices can be written in place; otherwise one call per run
-            std::size_t at = 0;
-            while (at < group.second.size())
+            for (const auto i : group.second)
             {
-                std::size_t run = 1;
-                while (at + run < group.second.size() && group.second[at + run] == group.second[at] + run) ++run;
-                std::vector<ColP> part(cols.begin() + static_cast<std::ptrdiff_t>(at), cols.begin() + static_cast<std::ptrdiff_t>(at + run));
-                be_.eval_device(part, group.first.second, d.log2n, d.w_tau, {0}, scalars, group.second[at]);
-                at += run;
+                cols.push_back(items[i].col);
+                slot[i] = next + cols.size() - 1;
             }
+            be_.eval_device(cols, group.first.second, d.log2n, d.w_tau, {0}, scalars, next);
+            next += cols.size();
         }
         const ColP points = be_.alloc(kG1, items.size());
         be_.g1_fixed_base(in_.generator, scalars, items.size(), points);
-        std::vector<Fe> evals(items.size());
-        std::vector<G1> pts(items.size());
-        be_.download(scalars, 0, items.size(), evals.data());
-        be_.download(points, 0, items.size(), pts.data());
+        std::vector<Fe> evals(items.size()), evals_by_slot(items.size());
+        std::vector<G1> pts(items.size()), pts_by_slot(items.size());
+        be_.download(scalars, 0, items.size(), evals_by_slot.data());
+        be_.download(points, 0, items.size(), pts_by_slot.data());
+        for (std::size_t i = 0; i < items.size(); ++i)
+        {
+            evals[i] = evals_by_slot[slot[i]];
+            pts[i] = pts_by_slot[slot[i]];
+        }
         for (std::size_t i = 0; i < items.size(); ++i)
         {
             commitments_[items[i].label] = Commitment{pts[i], evals[i]};
@@ -839,7 +922,7 @@ namespace gatzk_flow
         be_.fold_rows(matrix, rows, cols, weights, rows, out.a);
         out.b = parameter_values;
         out.acc = be_.alloc(kFrMont, dd.size);
-        be_.zkmap(out.a, out.b, cols, dd.size, out.acc);
+        queue_scan(ScanJob::kZkmap, out.a, out.b, nullptr, nullptr, nullptr, cols, dd.size, Fe{}, out.acc);
         if (weights_out != nullptr) *weights_out = weights;
         return out;
     }
@@ -867,7 +950,7 @@ namespace gatzk_flow
         out.multiplicity = be_.alloc(kU32, e.size);
         be_.lookup_multiplicity(left, table_y != nullptr ? right : nullptr, valid, x_min, band, table_y, table_size, e.size, out.multiplicity);
         out.acc = be_.alloc(kFrMont, e.size);
-        be_.logup(out.table, out.query, out.multiplicity, q_table, q_query, e.size, beta, std::min(valid, e.size - 1), out.acc);
+        queue_scan(ScanJob::kLogup, out.table, out.query, out.multiplicity, q_table, q_query, std::min(valid, e.size - 1), e.size, beta, out.acc);
         return out;
     }
 
@@ -885,10 +968,9 @@ namespace gatzk_flow
         out.query = be_.alloc(kFrMont, e.size);
         be_.linear_combination(edge_cols, eta_powers, n_edges_, e.size, out.query);
         out.node_acc = be_.alloc(kFrMont, n.size);
-        be_.route_node(out.table, multiplicity, n_nodes_, n.size, beta, out.node_acc);
+        queue_scan(ScanJob::kRouteNode, out.table, multiplicity, nullptr, nullptr, nullptr, n_nodes_, n.size, beta, out.node_acc);
         out.edge_acc = be_.alloc(kFrMont, e.size);
-        be_.route_edge(out.query, n_edges_, e.size, beta, out.edge_acc);
-        be_.download(out.node_acc, n_nodes_, 1, out.total.data());  // route.total = node_acc[real_node_count]
+        queue_scan(ScanJob::kRouteEdge, out.query, nullptr, nullptr, nullptr, nullptr, n_edges_, e.size, beta, out.edge_acc);
         return out;
     }
 
@@ -1071,7 +1153,7 @@ namespace gatzk_flow
         const ColP s_max = be_.alloc(kU32, e.size);
         be_.first_zero_marker(w.delta, group_begin_, group_end_, groups_, e.size, s_max);
         const ColP c_max = be_.alloc(kFrMont, e.size);
-        be_.group_prefix_state(s_max, q_new_, e.size, c_max);
+        queue_scan(ScanJob::kGroupPrefix, s_max, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, c_max);
         const Lookup range = build_pair_lookup(t_range_, nullptr, range_size_, 0, 1, w.delta, nullptr, n_edges_, fe_u64(0), beta_r, q_tbl_r_, q_qry_r_);
         const Lookup exp_l = build_pair_lookup(t_exp_x_, t_exp_y_, range_size_ * 5, 0, 5, w.delta, w.u, n_edges_, eta_exp, beta_exp, q_tbl_exp_, q_qry_exp_);
 
@@ -1084,7 +1166,7 @@ namespace gatzk_flow
         be_.linear_combination({w.sum, h_agg_pre_star}, {fe_u64(1), lambda_psq}, n_nodes_, n_nodes_, t_psq);
         const ColP t_psq_edge = to_edges(t_psq, dst_u32_);
         const ColP psq = be_.alloc(kFrMont, e.size);
-        be_.group_prefix_state(w_psq, q_new_, e.size, psq);
+        queue_scan(ScanJob::kGroupPrefix, w_psq, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, psq);
         // the source route packs ids + eta * value with powers(eta, 2) = {1, eta} (trace.cpp:2737-2772)
         const Route src_route = build_route({ids_i64_, w.e_src}, {src_i64_, h_star_edge}, eta_src, src_multiplicity_, beta_src);
 
@@ -1158,9 +1240,11 @@ namespace gatzk_flow
                       column_item(prefix + "m_dst", dst_multiplicity_, "N", n.size), column_item(prefix + "R_dst_node", dst_route.node_acc, "N", n.size),
                       column_item(prefix + "R_dst", dst_route.edge_acc, "edge", e.size)});
 
-        witness_scalars_.push_back({"S_src_h" + h, src_route.total});
-        witness_scalars_.push_back({"S_dst_h" + h, dst_route.total});
-        witness_scalars_.push_back({"S_t_h" + h, t_route.total});
+        // route.total = node_acc[real_node_count] (build_route_trace, trace.cpp:1792)
+        pending_totals_.push_back({"S_src_h" + h, src_route.node_acc, n_nodes_});
+        pending_totals_.push_back({"S_dst_h" + h, dst_route.node_acc, n_nodes_});
+        pending_totals_.push_back({"S_t_h" + h, t_route.node_acc, n_nodes_});
+        resolve_totals();
         // external evaluations, trace.cpp:3062-3073: Horner of the matrix, barycentric evaluation of the
         // columns at the binding points (the weights at those points exist already)
         {

@@ -132,7 +132,7 @@ namespace gatzk_flow
         const ColP s_max = be_.alloc(kU32, e.size);
         be_.first_zero_marker(w.delta, group_begin_, group_end_, groups_, e.size, s_max);
         const ColP c_max = be_.alloc(kFrMont, e.size);
-        be_.group_prefix_state(s_max, q_new_, e.size, c_max);
+        queue_scan(ScanJob::kGroupPrefix, s_max, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, c_max);
         const Lookup range = build_pair_lookup(t_range_, nullptr, range_size_, 0, 1, w.delta, nullptr, n_edges_, fe_u64(0), beta_r, q_tbl_r_, q_qry_r_);
         const Lookup exp_l = build_pair_lookup(t_exp_x_, t_exp_y_, range_size_ * 5, 0, 5, w.delta, w.u, n_edges_, eta_exp, beta_exp, q_tbl_exp_, q_qry_exp_);
 
@@ -145,7 +145,7 @@ namespace gatzk_flow
         be_.linear_combination({w.sum, y_star}, {fe_u64(1), lambda}, n_nodes_, n_nodes_, t_out);
         const ColP t_out_edge = to_edges(t_out, dst_u32_);
         const ColP psq = be_.alloc(kFrMont, e.size);
-        be_.group_prefix_state(w_out, q_new_, e.size, psq);
+        queue_scan(ScanJob::kGroupPrefix, w_out, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, psq);
 
         commit_batch({column_item(prefix + "E_src_edge", w.e_src_edge, "edge", e.size), column_item(prefix + "E_dst_edge", w.e_dst_edge, "edge", e.size),
                       column_item(prefix + "Y_prime_star", y_prime_star, "N", n_nodes_),
@@ -201,9 +201,10 @@ namespace gatzk_flow
                       column_item(prefix + "R_dst_node", dst_route.node_acc, "N", n.size), column_item(prefix + "R_dst", dst_route.edge_acc, "edge", e.size)});
 
         const std::string s_suffix = legacy ? "_out" : "_out" + k;
-        witness_scalars_.push_back({"S_src" + s_suffix, src_route.total});
-        witness_scalars_.push_back({"S_dst" + s_suffix, dst_route.total});
-        witness_scalars_.push_back({"S_t" + s_suffix, t_route.total});
+        pending_totals_.push_back({"S_src" + s_suffix, src_route.node_acc, n_nodes_});
+        pending_totals_.push_back({"S_dst" + s_suffix, dst_route.node_acc, n_nodes_});
+        pending_totals_.push_back({"S_t" + s_suffix, t_route.node_acc, n_nodes_});
+        resolve_totals();
         {
             const ColP out = be_.alloc(kFr, 4);
             be_.horner_device(y_prime, n_nodes_, c, y_proj, out, 0);
@@ -219,8 +220,10 @@ namespace gatzk_flow
         }
     }
 
-    inline void ProverFlow::prove()
+    inline void ProverFlow::prove(bool inputs_resident)
     {
+        be_.uploaded_bytes = 0;
+        be_.downloaded_bytes = 0;
         commitments_.clear();
         commitment_order_.clear();
         columns_.clear();
@@ -334,7 +337,7 @@ namespace gatzk_flow
         }
 
         // ---- forward pass + quantised witness (cached_forward_artifacts, trace.cpp:1281-1349) ------------
-        ColP layer_input = upload_f64(in_.features);
+        ColP layer_input = inputs_resident ? features_f64_ : upload_f64(in_.features);
         std::size_t input_dim = in_.feature_count;
         std::vector<std::vector<HeadWitness>> hidden_witness(in_.hidden_layers.size());
         std::vector<ColP> concat_q(in_.hidden_layers.size());
@@ -531,10 +534,8 @@ namespace gatzk_flow
                 // the feature-domain columns are never materialised: generated public columns at z and
                 // omega*z (a11) and the lazy lookup columns as the same combinations as their commitments
                 Fe at_z[5], at_wz[5];
-                be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, w_z, at_z);
-                const ColP w_wz = be_.alloc(kFrMont, d.size);
-                be_.bary_weights(d.log2n, z1, w_wz);
-                be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, w_wz, at_wz);
+                be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, w_z, d.log2n, 0, at_z);
+                be_.fh_public_eval(features_q_, n_nodes_, in_.feature_count, ids_i64_, w_z, d.log2n, 1, at_wz);
                 const Fe eta_i = challenges_.at("eta_feat"), eta_v = mul(eta_i, eta_i);
                 auto combos = [&](const Fe* p) {
                     std::array<Fe, 5> o;

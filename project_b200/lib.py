@@ -62,6 +62,14 @@ def _fr(x):
     return a
 
 
+class _ScanJob(ctypes.Structure):
+    _fields_ = [("op", ctypes.c_int), ("c0", ctypes.c_void_p), ("c1", ctypes.c_void_p), ("c2", ctypes.c_void_p), ("c3", ctypes.c_void_p),
+                ("c4", ctypes.c_void_p), ("count", ctypes.c_size_t), ("domain_size", ctypes.c_size_t), ("beta", ctypes.c_void_p), ("out", ctypes.c_void_p)]
+
+
+SCAN_LOGUP, SCAN_ROUTE_NODE, SCAN_ROUTE_EDGE, SCAN_ZKMAP, SCAN_GROUP_PREFIX = 0, 1, 2, 3, 4
+
+
 class _GatHead(ctypes.Structure):
     _fields_ = [("features", ctypes.c_void_p), ("input_width", ctypes.c_uint32), ("output_width", ctypes.c_uint32),
                 ("seq_kernel", ctypes.c_void_p), ("attn_src_kernel", ctypes.c_void_p), ("attn_dst_kernel", ctypes.c_void_p),
@@ -223,6 +231,22 @@ class Backend:
         out = out or self.alloc(KIND_FR_MONT, domain_size)
         self._check(self.lib.gzk_route_edge_accumulator(self.ctx, query.handle, _sz(valid_length), _sz(domain_size), _ptr(_fr(beta)), out.handle))
         return out
+
+    def running_sums_batch(self, jobs):
+        """jobs: list of (op, [input Buffers], count, domain_size, beta or None, out Buffer): gzk_running_sums_batch."""
+        raw = (_ScanJob * len(jobs))()
+        keep = []
+        for r, (op, cols, count, domain_size, beta, out) in zip(raw, jobs):
+            r.op = op
+            handles = [c.handle for c in cols] + [None] * (5 - len(cols))
+            r.c0, r.c1, r.c2, r.c3, r.c4 = handles
+            r.count, r.domain_size = int(count), int(domain_size)
+            if beta is not None:
+                b = _fr(beta).copy()
+                keep.append(b)
+                r.beta = b.ctypes.data
+            r.out = out.handle
+        self._check(self.lib.gzk_running_sums_batch(self.ctx, raw, _sz(len(jobs))))
 
     def group_prefix_state(self, values, q_new, n, out=None):
         out = out or self.alloc(KIND_FR_MONT, n)

@@ -345,3 +345,71 @@ def test_contexts_on_several_host_threads_share_buffers(be):
     for t in range(4):
         for g in got[t]:
             assert np.array_equal(g, want[t])
+
+
+@pytest.mark.parametrize("jobs", [1, 4, 10, 19])
+def test_running_sums_batch_matches_the_single_column_builders(be, jobs):
+    """J independent running sums of mixed operations, sizes and column kinds in one call: every output equals
+    what the oracle builds for that column alone."""
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32
+    from project_b200.lib import SCAN_GROUP_PREFIX, SCAN_LOGUP, SCAN_ROUTE_EDGE, SCAN_ROUTE_NODE, SCAN_ZKMAP
+
+    rng = np.random.default_rng(1000 + jobs)
+    queue, expect = [], []
+    for j in range(jobs):
+        op = [SCAN_LOGUP, SCAN_ROUTE_NODE, SCAN_ROUTE_EDGE, SCAN_GROUP_PREFIX, SCAN_ZKMAP][j % 5]
+        n = int(rng.choice([16, 700, 4096, 30000, 70001]))
+        beta = fr_array([int(rng.integers(1, 1 << 62))])
+        small = j % 2 == 1  # every other job reads small-integer columns
+        out = be.alloc(KIND_FR_MONT, n)
+        if op == SCAN_LOGUP:
+            t_valid, q_valid = int(rng.integers(1, n)), int(rng.integers(1, n))
+            qt_u, qq_u = (np.arange(n) < t_valid).astype(np.uint32), (np.arange(n) < q_valid).astype(np.uint32)
+            if small:
+                t, q = rng.integers(-900, 900, size=n, dtype=np.int64), rng.integers(-900, 900, size=n, dtype=np.int64)
+                m = rng.integers(0, 40, size=n, dtype=np.uint32)
+                cols = [be.upload(t, KIND_I64), be.upload(q, KIND_I64), be.upload(m, KIND_U32)]
+                t, q, m = ora.fr_from_i64(t), ora.fr_from_i64(q), ora.fr_from_i64(m.astype(np.int64))
+            else:
+                t, q, m = rand_fr(rng, n), rand_fr(rng, n), rand_fr(rng, n)
+                cols = [be.upload(x, KIND_FR) for x in (t, q, m)]
+            cols += [be.upload(qt_u, KIND_U32), be.upload(qq_u, KIND_U32)]
+            active = min(max(t_valid, q_valid), n - 1)
+            want = ora.logup_accumulator(t, q, m, selector(t_valid, n), selector(q_valid, n), beta, active)
+            queue.append((op, cols, active, n, beta, out))
+        elif op == SCAN_ROUTE_NODE:
+            valid = int(rng.integers(0, n))
+            t, m = rand_fr(rng, n), rng.integers(0, 9, size=n, dtype=np.uint32)
+            want = ora.route_node_accumulator(t, ora.fr_from_i64(m.astype(np.int64)), valid, beta)
+            queue.append((op, [be.upload(t, KIND_FR), be.upload(m, KIND_U32)], valid, n, beta, out))
+        elif op == SCAN_ROUTE_EDGE:
+            valid = int(rng.integers(0, n))
+            q = rand_fr(rng, n)
+            want = ora.route_edge_accumulator(q, valid, beta)
+            queue.append((op, [be.upload(q, KIND_FR)], valid, n, beta, out))
+        elif op == SCAN_GROUP_PREFIX:
+            v = rng.integers(0, 4000, size=n, dtype=np.int64)
+            q_new = (rng.random(n) < 0.1).astype(np.uint32)
+            want = ora.group_prefix_state(ora.fr_from_i64(v), ora.fr_from_i64(q_new.astype(np.int64)))
+            queue.append((op, [be.upload(v, KIND_I64), be.upload(q_new, KIND_U32)], n, n, None, out))
+        else:
+            count = int(rng.integers(0, n))
+            a, b = rand_fr(rng, max(count, 1)), rand_fr(rng, max(count, 1))
+            want, _ = ora.zkmap_accumulator(a[:count], b[:count], n)
+            queue.append((op, [be.upload(a, KIND_FR), be.upload(b, KIND_FR)], count, n, None, out))
+        expect.append(want)
+    be.running_sums_batch(queue)
+    for job, want in zip(queue, expect):
+        assert np.array_equal(job[5].download(), want), f"job of op {job[0]} with {job[3]} rows"
+
+
+def test_running_sums_batch_reports_a_zero_denominator(be):
+    from project_b200 import KIND_FR, KIND_FR_MONT, GzkError
+    from project_b200.lib import SCAN_ROUTE_EDGE
+
+    n = 64
+    q = np.zeros((n, 32), dtype=np.uint8)
+    q[:, 0] = 3
+    beta = fr_array([R - 3])  # query + beta = 0 in every row
+    with pytest.raises(GzkError, match="batch_invert encountered zero"):
+        be.running_sums_batch([(SCAN_ROUTE_EDGE, [be.upload(q, KIND_FR)], 10, n, beta, be.alloc(KIND_FR_MONT, n))])

@@ -40,7 +40,8 @@ def test_gpu_proof_equals_cpu_proof_field_by_field(shape):
     gpu.prove()
     assert first_difference(gpu.dump(), cpu.dump()) is None
     assert np.array_equal(gpu.proof_bytes(), cpu.proof_bytes())
-    assert gpu.stats() == cpu.stats()
+    counters = ("commit_barriers", "challenges", "dynamic_commitments", "opened_columns", "domains")
+    assert {k: gpu.stats()[k] for k in counters} == {k: cpu.stats()[k] for k in counters}
     # a second proof on the same context recomputes everything and gives the same bytes
     gpu.prove()
     assert np.array_equal(gpu.proof_bytes(), cpu.proof_bytes())
