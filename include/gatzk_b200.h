@@ -272,6 +272,13 @@ int gzk_broadcast_node_values(gzk_ctx* ctx, const gzk_buf* node_values, size_t n
                               size_t domain_size, gzk_buf* out);
 int gzk_histogram(gzk_ctx* ctx, const gzk_buf* indices, size_t count, size_t domain_size, gzk_buf* out);
 int gzk_quantize(gzk_ctx* ctx, const gzk_buf* values, size_t count, gzk_buf* out);
+/* gzk_quantize that also counts, into flagged[0] (a U32 buffer; added to, not cleared), the values
+ * whose 16*|v| lies within `guard` of a rounding boundary k + 1/2.  The forward pass on the GPU is
+ * bit-identical to the host's up to exp / expm1, whose last bit may differ between the CUDA and the
+ * host math library; a quantised value can then differ from the reference's only if 16*v is that
+ * close to a boundary.  A caller that needs the byte-identical witness re-computes on the host,
+ * with the reference's own loop (src/model/gat.cpp:474-615), whenever the count is not zero. */
+int gzk_quantize_guarded(gzk_ctx* ctx, const gzk_buf* values, size_t count, double guard, gzk_buf* out, gzk_buf* flagged);
 int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* group_begin, const gzk_buf* group_end, size_t groups,
                           size_t domain_size, gzk_buf* out);
 

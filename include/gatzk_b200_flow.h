@@ -60,9 +60,11 @@ size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap);
 /* The proof as bytes in the layout proof_size_bytes counts (src/protocol/prover.cpp:3831-3905). */
 size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap);
 /* counters of the last run: commit barriers, challenges, dynamic commitments, opened columns,
- * the seven domain sizes FH, edge, in, d, cat, C, N, then the bytes uploaded to and downloaded
- * from the backend during the run */
-int gzk_flow_stats(gzk_flow* flow, uint64_t out[13]);
+ * the seven domain sizes FH, edge, in, d, cat, C, N, the bytes uploaded to and downloaded from the
+ * backend during the run, and the number of forward-pass values found within the guard band of a
+ * rounding boundary (when not zero the forward pass was repeated on the host, see
+ * gzk_quantize_guarded) */
+int gzk_flow_stats(gzk_flow* flow, uint64_t out[14]);
 /* A committed column of the last run by label: its buffer kind (GZK_KIND_*), stored length and,
  * when out is not NULL, its first min(length, cap_elements) elements in the wire format of
  * gzk_buf_download. */

@@ -593,7 +593,7 @@ extern "C"
     int ora_flow_prove_resident(ora_flow* flow) { return gatzk_flow::flow_prove_impl(flow, true); }
     size_t ora_flow_dump(ora_flow* flow, char* out, size_t cap) { return gatzk_flow::flow_dump_impl(flow, out, cap); }
     size_t ora_flow_proof_bytes(ora_flow* flow, uint8_t* out, size_t cap) { return gatzk_flow::flow_proof_bytes_impl(flow, out, cap); }
-    int ora_flow_stats(ora_flow* flow, uint64_t out[13]) { return gatzk_flow::flow_stats_impl(flow, out); }
+    int ora_flow_stats(ora_flow* flow, uint64_t out[14]) { return gatzk_flow::flow_stats_impl(flow, out); }
     int ora_flow_column(ora_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements)
     {
         return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);

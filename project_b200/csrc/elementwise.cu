@@ -99,6 +99,26 @@ namespace gzk
             }
         }
 
+        // The same rounding, and a count of the values that sit within `guard` of a rounding boundary
+        // (16 |v| within guard of k + 1/2): the values whose quantised form could differ if v carried an
+        // error of that size, e.g. from a last-place difference between two exp implementations.
+        __global__ void quantize_guarded_kernel(const double* values, uint64_t count, double guard, long long* out, unsigned int* flagged)
+        {
+            unsigned int mine = 0;
+            for (uint64_t i = grid_index(); i < count; i += grid_stride())
+            {
+                const double v = values[i];
+                const double scaled = __dmul_rn(v, 16.0);
+                const double shifted = v >= 0.0 ? __dadd_rn(scaled, 0.5) : __dadd_rn(scaled, -0.5);
+                out[i] = static_cast<long long>(shifted);
+                // distance of |16 v| + 1/2 from the nearest integer = distance of |16 v| from the nearest k + 1/2
+                const double a = fabs(shifted);
+                const double dist = fabs(a - rint(a));
+                if (!(dist >= guard)) ++mine;  // also counts NaN
+            }
+            if (mine != 0) atomicAdd(flagged, mine);
+        }
+
         // one thread per destination group: mark the first row whose delta is zero
         __global__ void first_zero_kernel(ColRef delta, ColRef group_begin, ColRef group_end, uint64_t groups, uint64_t n, uint32_t* out,
                                           int* status)
@@ -294,6 +314,25 @@ extern "C"
             LaunchScope scope(ctx, "quantize");
             quantize_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(static_cast<const double*>(values->dptr), count,
                                                                                    static_cast<long long*>(out->dptr));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        return finish_call(ctx, "invalid input");
+    }
+
+    int gzk_quantize_guarded(gzk_ctx* ctx, const gzk_buf* values, size_t count, double guard, gzk_buf* out, gzk_buf* flagged)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (count == 0) return GZK_OK;
+        if (values == nullptr || values->kind != GZK_KIND_F64 || values->count < count) return fail(ctx, GZK_E_INVALID, "quantize: input must be an F64 buffer");
+        if (out == nullptr || out->kind != GZK_KIND_I64 || out->count < count) return fail(ctx, GZK_E_INVALID, "quantize: output must be an I64 buffer");
+        if (flagged == nullptr || flagged->kind != GZK_KIND_U32 || flagged->count < 1) return fail(ctx, GZK_E_INVALID, "quantize_guarded: the counter must be a U32 buffer");
+        if (!(guard >= 0.0 && guard <= 0.5)) return fail(ctx, GZK_E_INVALID, "quantize_guarded: the guard band must lie in [0, 0.5]");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        {
+            LaunchScope scope(ctx, "quantize");
+            quantize_guarded_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(static_cast<const double*>(values->dptr), count, guard,
+                                                                                           static_cast<long long*>(out->dptr),
+                                                                                           static_cast<unsigned int*>(flagged->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return finish_call(ctx, "invalid input");

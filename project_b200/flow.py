@@ -71,11 +71,11 @@ class Flow:
         return buf
 
     def stats(self):
-        out = (ctypes.c_uint64 * 13)()
+        out = (ctypes.c_uint64 * 14)()
         self._check(self._fn("stats")(self.handle, out))
         v = list(out)
         return {"commit_barriers": v[0], "challenges": v[1], "dynamic_commitments": v[2], "opened_columns": v[3],
-                "domains": dict(zip(DOMAINS, v[4:11])), "h2d_bytes": v[11], "d2h_bytes": v[12]}
+                "domains": dict(zip(DOMAINS, v[4:11])), "h2d_bytes": v[11], "d2h_bytes": v[12], "guard_flags": v[13]}
 
     def domain_labels(self, domain):
         fn = self._fn("domain_labels")

@@ -110,7 +110,7 @@ namespace gatzk_flow
         if (out != nullptr && cap > 0) std::memcpy(out, bytes.data(), std::min(cap, bytes.size()));
         return bytes.size();
     }
-    inline int flow_stats_impl(FlowHandle* h, std::uint64_t out[13])
+    inline int flow_stats_impl(FlowHandle* h, std::uint64_t out[14])
     {
         const auto& s = h->flow->stats();
         out[0] = s.commit_barriers;
@@ -121,6 +121,7 @@ namespace gatzk_flow
         for (int i = 0; i < 7; ++i) out[4 + i] = h->flow->domain_size(names[i]);
         out[11] = h->backend->uploaded_bytes;
         out[12] = h->backend->downloaded_bytes;
+        out[13] = s.guard_flags;
         return 0;
     }
     inline int flow_column_impl(FlowHandle* h, const char* label, int* kind, std::uint64_t* length, void* out, std::size_t cap_elements)

@@ -124,6 +124,10 @@ namespace
             check(gzk_gat_head_forward(ctx_, &head, &graph, &tr));
         }
         void quantize(const ColP& v, std::size_t count, const ColP& out) override { check(gzk_quantize(ctx_, raw(v), count, raw(out))); }
+        void quantize_guarded(const ColP& v, std::size_t count, double guard, const ColP& out, const ColP& flagged) override
+        {
+            check(gzk_quantize_guarded(ctx_, raw(v), count, guard, raw(out), raw(flagged)));
+        }
         void gather(const ColP& nv, std::size_t node_count, const ColP& index, std::size_t edge_count, std::size_t domain_size, const ColP& out) override
         {
             check(gzk_broadcast_node_values(ctx_, raw(nv), node_count, raw(index), edge_count, domain_size, raw(out)));
@@ -283,7 +287,7 @@ extern "C"
     int gzk_flow_prove_resident(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow, true); }
     size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap) { return gatzk_flow::flow_dump_impl(flow, out, cap); }
     size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap) { return gatzk_flow::flow_proof_bytes_impl(flow, out, cap); }
-    int gzk_flow_stats(gzk_flow* flow, uint64_t out[13]) { return gatzk_flow::flow_stats_impl(flow, out); }
+    int gzk_flow_stats(gzk_flow* flow, uint64_t out[14]) { return gatzk_flow::flow_stats_impl(flow, out); }
     int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements)
     {
         return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);

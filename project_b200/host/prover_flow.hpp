@@ -38,6 +38,7 @@
 #include <utility>
 #include <vector>
 
+#include "host_forward.hpp"
 #include "proof_codec.hpp"
 
 namespace gatzk_flow
@@ -104,6 +105,14 @@ namespace gatzk_flow
         // a10: forward pass and witness leaves
         virtual void head_forward(const HeadDesc& head, const GraphCols& graph, const HeadTraceCols& out) = 0;
         virtual void quantize(const ColP& values, std::size_t count, const ColP& out) = 0;
+        // quantize + count (added to flagged[0], a U32 buffer) of the values within `guard` of a rounding
+        // boundary; a backend whose forward pass IS the reference's host loop has nothing to flag
+        virtual void quantize_guarded(const ColP& values, std::size_t count, double guard, const ColP& out, const ColP& flagged)
+        {
+            (void)guard;
+            (void)flagged;
+            quantize(values, count, out);
+        }
         virtual void gather(const ColP& node_values, std::size_t node_count, const ColP& index, std::size_t edge_count, std::size_t domain_size,
                             const ColP& out) = 0;
         virtual void linear_combination(const std::vector<ColP>& cols, const std::vector<Fe>& coefficients, std::size_t count,
@@ -286,7 +295,14 @@ namespace gatzk_flow
     struct FlowStats
     {
         std::size_t commit_barriers = 0, challenges = 0, dynamic_commitments = 0, opened_columns = 0;
+        std::size_t guard_flags = 0;  // forward-pass values within the guard band of a rounding boundary (host re-check ran when > 0)
     };
+
+    // Guard band of the quantisation, in units of 16*v: the forward pass on the GPU equals the host's bit
+    // for bit up to exp / expm1 (relative difference <= 2^-51 per call); sums of at most 2^20 such terms,
+    // values below 2^9 and two layers of amplification by at most 2^10 each keep |16 v_gpu - 16 v_host|
+    // far below 2^-30, so a value outside the band rounds the same way on both sides.
+    constexpr double kQuantizeGuard = 1.0 / 1073741824.0;
 
     inline std::size_t next_power_of_two(std::size_t v)
     {
@@ -527,7 +543,13 @@ namespace gatzk_flow
             ColP e_src_edge, e_dst_edge, m_edge, sum_edge, inv_edge;
             ColP h_agg_f64;                                        // the head's fp64 output (next layer's input)
         };
-        HeadWitness run_head(const ColP& layer_input_f64, std::size_t input_dim, std::size_t width, const HeadParams& p, bool output_head);
+        // host_input: when set, the forward pass of the head runs on the host (host_head_forward) on this
+        // row-major input instead of on the backend; host_output receives the head's fp64 output
+        HeadWitness run_head(const ColP& layer_input_f64, std::size_t input_dim, std::size_t width, const HeadParams& p, bool output_head,
+                             const std::vector<double>* host_input = nullptr, std::vector<double>* host_output = nullptr);
+        void forward_all(bool inputs_resident, bool on_host, std::vector<std::vector<HeadWitness>>& hidden_witness, std::vector<ColP>& concat_q,
+                         std::vector<HeadWitness>& output_witness, std::size_t& final_width);
+        ColP guard_counter_;
         void commit_hidden_head(Transcript& t, std::size_t head_index, std::size_t layer_index, std::size_t local_head, const HeadWitness& w);
         void commit_hidden_concat(Transcript& t, std::size_t layer_index, const ColP& concat_q, std::size_t width);
         void commit_output_head(Transcript& t, std::size_t head_index, const HeadWitness& w, const ColP& h_cat_q, std::size_t cat_width,
@@ -977,20 +999,9 @@ namespace gatzk_flow
     // attention_head_forward_impl + quantize_hidden_witness_cpu / quantize_output_witness_cpu
     // (src/model/gat.cpp:474-615; trace.cpp:1143-1279)
     inline ProverFlow::HeadWitness ProverFlow::run_head(const ColP& layer_input, std::size_t input_dim, std::size_t width, const HeadParams& p,
-                                                        bool output_head)
+                                                        bool output_head, const std::vector<double>* host_input, std::vector<double>* host_output)
     {
         const std::size_t edge_size = dom_.at("edge").size;
-        HeadDesc head;
-        head.features = layer_input;
-        head.input_width = input_dim;
-        head.output_width = width;
-        head.seq_kernel = upload_f64(p.seq_kernel);
-        head.attn_src = upload_f64(p.attn_src);
-        head.attn_dst = upload_f64(p.attn_dst);
-        head.attn_src_bias = p.attn_src_bias;
-        head.attn_dst_bias = p.attn_dst_bias;
-        head.output_bias = output_head && !p.output_bias.empty() ? upload_f64(p.output_bias) : nullptr;
-        head.apply_activation = !output_head;
         HeadTraceCols tr;
         auto f64 = [&](std::size_t n) { return be_.alloc(kF64, std::max<std::size_t>(1, n)); };
         tr.H_prime = f64(n_nodes_ * width);
@@ -1006,18 +1017,61 @@ namespace gatzk_flow
         tr.Delta = f64(n_edges_);
         tr.U = f64(n_edges_);
         tr.alpha = f64(n_edges_);
-        be_.head_forward(head, graph_, tr);
+        if (host_input == nullptr)
+        {
+            HeadDesc head;
+            head.features = layer_input;
+            head.input_width = input_dim;
+            head.output_width = width;
+            head.seq_kernel = upload_f64(p.seq_kernel);
+            head.attn_src = upload_f64(p.attn_src);
+            head.attn_dst = upload_f64(p.attn_dst);
+            head.attn_src_bias = p.attn_src_bias;
+            head.attn_dst_bias = p.attn_dst_bias;
+            head.output_bias = output_head && !p.output_bias.empty() ? upload_f64(p.output_bias) : nullptr;
+            head.apply_activation = !output_head;
+            be_.head_forward(head, graph_, tr);
+        }
+        else
+        {
+            const HostHeadTrace h = host_head_forward(*host_input, n_nodes_, input_dim, p.seq_kernel, width, p.attn_src, p.attn_src_bias, p.attn_dst,
+                                                      p.attn_dst_bias, p.output_bias, output_head && !p.output_bias.empty(), !output_head, in_.edge_src,
+                                                      in_.edge_dst);
+            auto put = [&](const ColP& col, const std::vector<double>& v) {
+                if (!v.empty()) be_.upload(col, v.data(), v.size());
+            };
+            put(tr.H_prime, h.H_prime);
+            put(tr.H_agg_pre_bias, h.H_agg_pre_bias);
+            put(tr.H_agg, h.H_agg);
+            put(tr.E_src, h.E_src);
+            put(tr.E_dst, h.E_dst);
+            put(tr.M, h.M);
+            put(tr.Sum, h.Sum);
+            put(tr.inv, h.inv);
+            put(tr.S, h.S);
+            put(tr.Z, h.Z);
+            put(tr.Delta, h.Delta);
+            put(tr.U, h.U);
+            put(tr.alpha, h.alpha);
+            if (host_output != nullptr) *host_output = h.H_agg;
+        }
 
         HeadWitness w;
         auto q_nodes = [&](const ColP& v, std::size_t n) {
             const ColP out = be_.alloc(kI64, std::max<std::size_t>(1, n));
-            be_.quantize(v, n, out);
+            if (host_input == nullptr)
+                be_.quantize_guarded(v, n, kQuantizeGuard, out, guard_counter_);
+            else
+                be_.quantize(v, n, out);
             return out;
         };
         auto q_edges = [&](const ColP& v) {
             const ColP out = be_.alloc(kI64, edge_size);
             be_.zero(out);
-            be_.quantize(v, n_edges_, out);
+            if (host_input == nullptr)
+                be_.quantize_guarded(v, n_edges_, kQuantizeGuard, out, guard_counter_);
+            else
+                be_.quantize(v, n_edges_, out);
             return out;
         };
         w.h_prime = q_nodes(tr.H_prime, n_nodes_ * width);

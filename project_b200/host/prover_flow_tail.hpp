@@ -220,6 +220,48 @@ namespace gatzk_flow
         }
     }
 
+    // model::forward_note_style (src/model/gat.cpp:1141-1220) + the quantisation of every head
+    inline void ProverFlow::forward_all(bool inputs_resident, bool on_host, std::vector<std::vector<HeadWitness>>& hidden_witness,
+                                        std::vector<ColP>& concat_q, std::vector<HeadWitness>& output_witness, std::size_t& final_width)
+    {
+        hidden_witness.assign(in_.hidden_layers.size(), {});
+        concat_q.assign(in_.hidden_layers.size(), nullptr);
+        output_witness.clear();
+        layer_inputs_q_.clear();
+        ColP layer_input = on_host ? nullptr : (inputs_resident ? features_f64_ : upload_f64(in_.features));
+        std::vector<double> host_input = on_host ? in_.features : std::vector<double>{};
+        std::size_t input_dim = in_.feature_count;
+        for (std::size_t li = 0; li < in_.hidden_layers.size(); ++li)
+        {
+            const auto& layer = in_.hidden_layers[li];
+            const std::size_t width = layer.head_dim * layer.heads.size();
+            const ColP concat = be_.alloc(kF64, n_nodes_ * width);
+            std::vector<double> host_concat(on_host ? n_nodes_ * width : 0);
+            for (std::size_t hi = 0; hi < layer.heads.size(); ++hi)
+            {
+                std::vector<double> head_out;
+                hidden_witness[li].push_back(run_head(layer_input, input_dim, layer.head_dim, layer.heads[hi], false, on_host ? &host_input : nullptr,
+                                                      on_host ? &head_out : nullptr));
+                be_.copy_block(hidden_witness[li].back().h_agg_f64, 0, layer.head_dim, concat, hi * layer.head_dim, width, n_nodes_, layer.head_dim);
+                if (on_host)  // concatenate_columns
+                    for (std::size_t r = 0; r < n_nodes_; ++r)
+                        for (std::size_t c = 0; c < layer.head_dim; ++c) host_concat[r * width + hi * layer.head_dim + c] = head_out[r * layer.head_dim + c];
+            }
+            concat_q[li] = be_.alloc(kI64, n_nodes_ * width);
+            if (on_host)
+                be_.quantize(concat, n_nodes_ * width, concat_q[li]);
+            else
+                be_.quantize_guarded(concat, n_nodes_ * width, kQuantizeGuard, concat_q[li], guard_counter_);
+            layer_inputs_q_[li + 1] = concat_q[li];
+            layer_input = concat;
+            host_input.swap(host_concat);
+            input_dim = width;
+        }
+        for (const auto& head : in_.output_layer.heads)
+            output_witness.push_back(run_head(layer_input, input_dim, in_.class_count, head, true, on_host ? &host_input : nullptr, nullptr));
+        final_width = input_dim;
+    }
+
     inline void ProverFlow::prove(bool inputs_resident)
     {
         be_.uploaded_bytes = 0;
@@ -337,28 +379,21 @@ namespace gatzk_flow
         }
 
         // ---- forward pass + quantised witness (cached_forward_artifacts, trace.cpp:1281-1349) ------------
-        ColP layer_input = inputs_resident ? features_f64_ : upload_f64(in_.features);
-        std::size_t input_dim = in_.feature_count;
-        std::vector<std::vector<HeadWitness>> hidden_witness(in_.hidden_layers.size());
-        std::vector<ColP> concat_q(in_.hidden_layers.size());
-        for (std::size_t li = 0; li < in_.hidden_layers.size(); ++li)
-        {
-            const auto& layer = in_.hidden_layers[li];
-            const std::size_t width = layer.head_dim * layer.heads.size();
-            const ColP concat = be_.alloc(kF64, n_nodes_ * width);
-            for (std::size_t hi = 0; hi < layer.heads.size(); ++hi)
-            {
-                hidden_witness[li].push_back(run_head(layer_input, input_dim, layer.head_dim, layer.heads[hi], false));
-                be_.copy_block(hidden_witness[li].back().h_agg_f64, 0, layer.head_dim, concat, hi * layer.head_dim, width, n_nodes_, layer.head_dim);
-            }
-            concat_q[li] = be_.alloc(kI64, n_nodes_ * width);
-            be_.quantize(concat, n_nodes_ * width, concat_q[li]);
-            layer_inputs_q_[li + 1] = concat_q[li];
-            layer_input = concat;
-            input_dim = width;
-        }
+        // On the backend first; if any value lies within the guard band of a rounding boundary, once more on
+        // the host with the reference's loop, so that the quantised witness is the reference's bit for bit.
+        std::vector<std::vector<HeadWitness>> hidden_witness;
+        std::vector<ColP> concat_q;
         std::vector<HeadWitness> output_witness;
-        for (const auto& head : in_.output_layer.heads) output_witness.push_back(run_head(layer_input, input_dim, in_.class_count, head, true));
+        std::size_t input_dim = in_.feature_count;
+        guard_counter_ = be_.alloc(kU32, 1);
+        be_.zero(guard_counter_);
+        forward_all(inputs_resident, false, hidden_witness, concat_q, output_witness, input_dim);
+        {
+            std::uint32_t flagged = 0;
+            be_.download(guard_counter_, 0, 1, &flagged);
+            stats_.guard_flags = flagged;
+            if (flagged != 0) forward_all(inputs_resident, true, hidden_witness, concat_q, output_witness, input_dim);
+        }
 
         // ---- commit chain: heads in transcript order -----------------------------------------------------
         std::size_t global_head = 0;

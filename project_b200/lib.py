@@ -305,6 +305,13 @@ class Backend:
         self._check(self.lib.gzk_quantize(self.ctx, values.handle, _sz(count), out.handle))
         return out
 
+    def quantize_guarded(self, values, count, guard):
+        """(I64 buffer, number of values within `guard` of a rounding boundary)."""
+        out = self.alloc(KIND_I64, count)
+        counter = self.upload(np.zeros(1, dtype=np.uint32), KIND_U32)
+        self._check(self.lib.gzk_quantize_guarded(self.ctx, values.handle, _sz(count), ctypes.c_double(guard), out.handle, counter.handle))
+        return out, int(counter.download()[0])
+
     def gat_head_forward(self, features, seq_kernel, attn_src, bias_src, attn_dst, bias_dst, out_bias, apply_activation, edge_src, edge_dst,
                          node_count, input_width, output_width, incoming_ptr, incoming_src, out=None):
         """All arguments are Buffers (F64 matrices, U32 lists) except the scalars; returns the trace fields as a dict of F64 Buffers

@@ -72,11 +72,18 @@ def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, 
         count = want[name].size
         if count == 0:
             continue
-        q = be.quantize(g, count).download()
+        # guarded quantisation: when no value is flagged as close to a rounding boundary, EVERY quantised value
+        # equals the oracle's (no mask); flagged values are the ones the prover flow re-computes on the host
+        q_buf, flagged = be.quantize_guarded(g, count, 2.0 ** -30)
+        q = q_buf.download()
         wq = ora.quantize(want[name].reshape(-1))
-        scaled = want[name].reshape(-1) * 16.0
-        away_from_boundary = np.abs(np.abs(scaled - np.floor(scaled)) - 0.5) > 1e-9
-        assert np.array_equal(q[away_from_boundary], wq[away_from_boundary]), name
+        if flagged == 0:
+            assert np.array_equal(q, wq), name
+        else:
+            scaled = np.abs(want[name].reshape(-1) * 16.0) + 0.5
+            near = np.abs(scaled - np.rint(scaled)) < 2.0 ** -29
+            assert np.array_equal(q[~near], wq[~near]), name
+            assert flagged <= int(near.sum()) + 1
 
 
 @pytest.mark.parametrize("nodes,inner,width,edges,self_loops,bias,activation", [

@@ -52,3 +52,23 @@ def test_gpu_proof_equals_cpu_proof_field_by_field(shape):
         assert kind_g == kind_c and np.array_equal(col_g, col_c), label
     cpu.close()
     gpu.close()
+
+
+def test_values_on_a_rounding_boundary_take_the_host_recheck():
+    """Inputs on a 1/32 grid put many forward-pass values exactly on a rounding boundary of the
+    quantisation (16 v = k + 1/2).  The GPU flow must notice (guard_flags > 0), repeat the forward pass
+    with the host loop, and still produce the CPU proof byte for byte."""
+    shape = dict(seed=9, nodes=48, directed_edges=160, feature_count=8, hidden=[(2, 4)], output_heads=1, class_count=3)
+    inputs = synthetic.make_inputs(**shape)
+    rng = np.random.default_rng(4)
+    inputs["features"] = rng.integers(0, 9, size=inputs["features"].shape) / 4.0
+    inputs["params"] = np.round(inputs["params"] * 8.0) / 8.0
+    cpu = Flow(ora.lib(), "ora_flow_", 2, inputs, G)
+    gpu = gpu_flow(0, inputs, G)
+    cpu.prove()
+    gpu.prove()
+    assert gpu.stats()["guard_flags"] > 0
+    assert first_difference(gpu.dump(), cpu.dump()) is None
+    assert np.array_equal(gpu.proof_bytes(), cpu.proof_bytes())
+    cpu.close()
+    gpu.close()

@@ -306,3 +306,21 @@ def test_gat_head_forward_against_numpy_restatement():
     s = e_dst[dst] + e_src[src]
     assert close(got["S"], s) and close(got["Z"], leaky(s)) and close(got["Delta"], m[dst] - leaky(s))
     assert close(got["U"], np.exp(leaky(s) - m[dst])) and close(got["alpha"], np.exp(leaky(s) - m[dst]) / total[dst])
+
+
+def test_gat_head_forward_against_the_reference_python_forward():
+    """Pin of the oracle's attention-head forward to REFERENCE-GENERATED output: the fixture
+    tests/golden/forward_head.npz holds what `head_forward` of the reference's scripts/gat_reference.py
+    (lines 37-87) computes for a seeded 120-node graph, once with the hidden-head switches (no output bias,
+    ELU) and once with the output-head ones (bias, no activation); see tests/golden/make_forward_golden.py.
+    numpy's matrix products add in another order than the C++ loops of src/model/gat.cpp, so the comparison
+    is to a relative 1e-12 (absolute 1e-13), not bit for bit."""
+    import os
+
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "forward_head.npz"))
+    close = lambda a, b: np.allclose(a, b, rtol=1e-12, atol=1e-13)
+    for tag, bias, activation in (("hidden", None, True), ("output", g["output_bias"], False)):
+        got = ora.gat_head_forward(g["features"], g["seq_kernel"], g["attn_src"], float(g["attn_src_bias"][0]), g["attn_dst"],
+                                   float(g["attn_dst_bias"][0]), bias, activation, g["edge_src"], g["edge_dst"])
+        for name in ("H_prime", "E_src", "E_dst", "M", "Sum", "inv", "S", "Z", "Delta", "U", "alpha", "H_agg_pre_bias", "H_agg"):
+            assert close(got[name], g[f"{tag}_{name}"]), (tag, name, float(np.max(np.abs(got[name] - g[f"{tag}_{name}"]))))
