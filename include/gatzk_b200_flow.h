@@ -53,6 +53,13 @@ void gzk_flow_destroy(gzk_flow* flow);
  * when the flow was created) instead of uploading it again. */
 int gzk_flow_prove(gzk_flow* flow);
 int gzk_flow_prove_resident(gzk_flow* flow);
+/* Honest-prover commitments.  The reference commits with the trapdoor: [p(tau)] G from the scalar
+ * p(tau) (src/crypto/kzg.cpp:402-419).  With the switch on, every later proof run ALSO commits each
+ * column as a multi-scalar multiplication against a resident structured reference string (the
+ * Lagrange basis [L_i(tau)] G of its domain; the monomial basis [tau^i] G for the matrices, which are
+ * coefficient polynomials) and compares the point with the trapdoor one.  counts (optional) receives
+ * the number of commitments checked so far and the number of mismatches. */
+int gzk_flow_set_msm_commit(gzk_flow* flow, int on, uint64_t counts[2]);
 /* Text listing of the last proof run, one value per line (challenges, tau-evaluations,
  * commitments, quotient scalars, opened values, witnesses, external evaluations, witness
  * scalars): returns the length; copies at most cap bytes. */

@@ -89,7 +89,13 @@ namespace gzk
             const uint64_t n = 1ULL << a.log2n;
             const uint32_t tile_elems = 1u << (a.stages + a.low_bits);
             const uint64_t vec_offset = static_cast<uint64_t>(blockIdx.y) * n;
-            const uint64_t tile_id = blockIdx.x;
+            // Pass 0 gathers through the bit-reversal permutation: element e of tile T comes from
+            // rev10(e) * n/1024 + rev(T), one 32-byte element per 128-byte line.  The four tiles T, T + Q,
+            // T + 2Q, T + 3Q (Q = tiles / 4) read the four elements of the SAME lines, so they are given
+            // to four consecutive CTAs: they run side by side and three of the four line reads hit L2
+            // instead of DRAM.
+            uint64_t tile_id = blockIdx.x;
+            if (a.s0 == 0 && gridDim.x >= 4) tile_id = static_cast<uint64_t>(blockIdx.x & 3u) * (gridDim.x >> 2) + (blockIdx.x >> 2);
 
             for (uint32_t e = threadIdx.x; e < tile_elems; e += kThreads)
             {

@@ -56,6 +56,12 @@ class Flow:
     def prove(self, inputs_resident=False):
         self._check(self._fn("prove_resident" if inputs_resident else "prove")(self.handle))
 
+    def set_msm_commit(self, on):
+        """Switch the MSM commitment path of a GPU flow; returns (commitments checked so far, mismatches)."""
+        counts = (ctypes.c_uint64 * 2)()
+        self._check(self._fn("set_msm_commit")(self.handle, int(bool(on)), counts))
+        return int(counts[0]), int(counts[1])
+
     def dump(self):
         fn = self._fn("dump")
         size = fn(self.handle, None, ctypes.c_size_t(0))

@@ -232,6 +232,26 @@ namespace
             for (int i = 0; i < 5; ++i) std::memcpy(out[i].data(), bytes + 32 * i, 32);
         }
         void synchronize() override { check(gzk_ctx_synchronize(ctx_)); }
+        bool supports_msm() const override { return true; }
+        ColP srs_lagrange(unsigned log2n, const G1& base, const Fe& tau) override
+        {
+            const ColP out = alloc(kG1, static_cast<std::size_t>(1) << log2n);
+            check(gzk_srs_lagrange(ctx_, log2n, base.data(), tau.data(), raw(out)));
+            return out;
+        }
+        ColP msm_table(const ColP& points, std::size_t n, unsigned* window_bits) override
+        {
+            *window_bits = gzk_msm_window_bits(n);
+            const ColP table = alloc(kG1, gzk_msm_table_points(n, *window_bits));
+            check(gzk_msm_precompute(ctx_, raw(points), n, *window_bits, raw(table)));
+            return table;
+        }
+        G1 msm(const ColP& scalars, const ColP& table, std::size_t n, unsigned window_bits) override
+        {
+            G1 out{};
+            check(gzk_msm_precomputed(ctx_, raw(scalars), raw(table), n, window_bits, out.data()));
+            return out;
+        }
 
     private:
         static std::size_t element_bytes(int kind) { return kind == kU32 ? 4 : (kind == kI64 || kind == kF64) ? 8 : kind == kG1 ? 96 : 32; }
@@ -285,6 +305,17 @@ extern "C"
     }
     int gzk_flow_prove(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow, false); }
     int gzk_flow_prove_resident(gzk_flow* flow) { return gatzk_flow::flow_prove_impl(flow, true); }
+    int gzk_flow_set_msm_commit(gzk_flow* flow, int on, uint64_t counts[2])
+    {
+        if (flow == nullptr) return 1;
+        flow->flow->set_msm_commit(on != 0);
+        if (counts != nullptr)
+        {
+            counts[0] = flow->flow->msm_commitments();
+            counts[1] = flow->flow->msm_mismatches();
+        }
+        return 0;
+    }
     size_t gzk_flow_dump(gzk_flow* flow, char* out, size_t cap) { return gatzk_flow::flow_dump_impl(flow, out, cap); }
     size_t gzk_flow_proof_bytes(gzk_flow* flow, uint8_t* out, size_t cap) { return gatzk_flow::flow_proof_bytes_impl(flow, out, cap); }
     int gzk_flow_stats(gzk_flow* flow, uint64_t out[14]) { return gatzk_flow::flow_stats_impl(flow, out); }

@@ -159,6 +159,13 @@ namespace gatzk_flow
         virtual void fh_public_eval(const ColP& features, std::size_t rows, std::size_t feature_count, const ColP& abs_ids, const ColP& weights,
                                     unsigned log2n, std::uint64_t rotation, Fe out[5]) = 0;
         virtual void synchronize() = 0;
+        // Honest-prover commitment by multi-scalar multiplication (optional): structured reference strings
+        // [L_i(tau)] G of a domain / [tau^i] G, the resident table of shifted bases of such a point set,
+        // and sum_i scalars[i] * P_i against it.  `scalars` is a field-element column (kFr / kFrMont).
+        virtual bool supports_msm() const { return false; }
+        virtual ColP srs_lagrange(unsigned, const G1&, const Fe&) { throw std::runtime_error("this backend has no MSM commitment path"); }
+        virtual ColP msm_table(const ColP&, std::size_t, unsigned*) { throw std::runtime_error("this backend has no MSM commitment path"); }
+        virtual G1 msm(const ColP&, const ColP&, std::size_t, unsigned) { throw std::runtime_error("this backend has no MSM commitment path"); }
         // bytes moved between host and backend since the last reset (end-to-end accounting)
         std::uint64_t uploaded_bytes = 0, downloaded_bytes = 0;
     };
@@ -345,6 +352,12 @@ namespace gatzk_flow
         const std::vector<std::pair<std::string, Fe>>& quotient_scalars() const { return quotient_log_; }
         const FlowStats& stats() const { return stats_; }
         const FlowInputs& inputs() const { return in_; }
+        // Commit every column ALSO as an MSM against the resident SRS (Lagrange basis of its domain, monomial
+        // basis for the matrices) and compare the point with the trapdoor commitment [p(tau)] G: the honest
+        // prover's commitment path.  The SRS tables are built on first use and stay resident.
+        void set_msm_commit(bool on) { msm_commit_ = on; }
+        std::size_t msm_commitments() const { return msm_checked_; }
+        std::size_t msm_mismatches() const { return msm_mismatches_; }
         std::size_t domain_size(const std::string& name) const { return dom_.at(name).size; }
         // a column of the last proof by label (tests compare a few against the CPU restatement)
         ColP column(const std::string& label, std::size_t* length = nullptr) const
@@ -556,6 +569,17 @@ namespace gatzk_flow
                                 std::vector<ColP>* y_lin_all, std::vector<ColP>* y_all);
         void prove_openings(Transcript& t);
         Fe eval_column_at(const ColP& col, std::size_t length, const std::string& domain, const ColP& weights);
+
+        struct SrsTable
+        {
+            ColP table;
+            unsigned window_bits = 0;
+        };
+        const SrsTable& srs_for(bool monomial, const std::string& domain, std::size_t n);
+        G1 msm_commit(const CommitItem& item);
+        bool msm_commit_ = false;
+        std::size_t msm_checked_ = 0, msm_mismatches_ = 0;
+        std::map<std::pair<int, std::size_t>, SrsTable> srs_tables_;  // (0 = Lagrange of a domain size / 1 = monomial, point count)
 
         Backend& be_;
         FlowInputs in_;
@@ -915,6 +939,14 @@ namespace gatzk_flow
             evals[i] = evals_by_slot[slot[i]];
             pts[i] = pts_by_slot[slot[i]];
         }
+        if (msm_commit_)
+        {
+            for (std::size_t i = 0; i < items.size(); ++i)
+            {
+                ++msm_checked_;
+                if (msm_commit(items[i]) != pts[i]) ++msm_mismatches_;
+            }
+        }
         for (std::size_t i = 0; i < items.size(); ++i)
         {
             commitments_[items[i].label] = Commitment{pts[i], evals[i]};
@@ -928,6 +960,47 @@ namespace gatzk_flow
         }
         ++stats_.commit_barriers;
         stats_.dynamic_commitments += items.size();
+    }
+
+    // SRS of `n` points with its table of shifted bases: the Lagrange basis [L_i(tau)] G of a domain (n = the
+    // domain size) or the monomial basis [tau^i] G, i < n (for the matrices, which are committed as
+    // coefficient polynomials).  What an honest KZG setup would hand the prover instead of tau.
+    inline const ProverFlow::SrsTable& ProverFlow::srs_for(bool monomial, const std::string& domain, std::size_t n)
+    {
+        const auto key = std::make_pair(monomial ? 1 : 0, n);
+        const auto it = srs_tables_.find(key);
+        if (it != srs_tables_.end()) return it->second;
+        ColP points;
+        if (monomial)
+        {
+            const ColP powers = be_.alloc(kFrMont, n);
+            be_.powers(tau_, n, powers);
+            points = be_.alloc(kG1, n);
+            be_.g1_fixed_base(in_.generator, powers, n, points);
+        }
+        else
+        {
+            points = be_.srs_lagrange(dom_.at(domain).log2n, in_.generator, tau_);
+        }
+        SrsTable t;
+        t.table = be_.msm_table(points, n, &t.window_bits);
+        return srs_tables_.emplace(key, t).first->second;
+    }
+
+    inline G1 ProverFlow::msm_commit(const CommitItem& item)
+    {
+        const std::size_t count = item.matrix ? item.rows * item.cols : item.length;
+        if (count == 0) return G1{};
+        const std::size_t n = item.matrix ? count : dom_.at(item.domain).size;
+        const SrsTable& srs = srs_for(item.matrix, item.domain, n);
+        // the MSM reads field elements: small-integer columns are widened first (padded with zeros up to n)
+        ColP scalars = item.col;
+        if ((item.col->kind != kFr && item.col->kind != kFrMont) || item.col->count < n)
+        {
+            scalars = be_.alloc(kFrMont, n);
+            be_.linear_combination({item.col}, {fe_u64(1)}, count, n, scalars);
+        }
+        return be_.msm(scalars, srs.table, n, srs.window_bits);
     }
 
     // build_binding_trace, src/protocol/trace.cpp:1595-1621

@@ -410,8 +410,8 @@ class Backend:
                                              int(bool(inverse))))
         return buf
 
-    def coset_lde(self, inp, log2n, log2_blowup, shift):
-        out = self.alloc(KIND_FR_MONT, 1 << (log2n + log2_blowup))
+    def coset_lde(self, inp, log2n, log2_blowup, shift, out=None):
+        out = out or self.alloc(KIND_FR_MONT, 1 << (log2n + log2_blowup))
         self._check(self.lib.gzk_coset_lde(self.ctx, inp.handle, ctypes.c_uint(log2n), ctypes.c_uint(log2_blowup), _ptr(_fr(shift)), out.handle))
         return out
 

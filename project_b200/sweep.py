@@ -1,6 +1,16 @@
 """Stand-alone kernels of the kernel sweep (MSM Mpts/s, NTT / fold GB/s, fp64 head forward), device-timed
 with CUDA events on the backend's stream.  Measurement code used by bench.py; not on the proving path."""
+import ctypes
+
 import numpy as np
+
+
+def _sz(v):
+    return ctypes.c_size_t(int(v))
+
+
+def _c_uint(v):
+    return ctypes.c_uint(int(v))
 
 
 def _stream_of(be, device):
@@ -9,17 +19,26 @@ def _stream_of(be, device):
     return torch.cuda.ExternalStream(be.stream, device=torch.device("cuda", device))
 
 
-def run_sweep(be, device, small=False):
-    """Stand-alone kernels of the sweep at one representative size each (device-timed)."""
+def run_sweep(be, device, small=False, budget_gb=40.0):
+    """The kernel sweep: G1 MSM 2^16..2^26 (plain, and against a resident table of shifted bases while the
+    table fits `budget_gb`), Fr NTT / inverse NTT / coset NTT 2^16..2^26 at batch 1, 4, 16, 64 (while
+    n * batch <= 2^28), coset LDE with blow-up 2, sumcheck fold 2^20..2^26; each line with its time, its
+    rate (Mpts/s or GB/s of algorithmic bytes) and the fraction of the integer-pipe roof measured in the
+    same run.  Inputs are generated on the device: scalars and vectors are the powers of a seeded
+    challenge (uniform-looking field elements), MSM bases are [k_i] G for such k_i."""
     import torch
 
     import pyref
 
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_G1
+    from project_b200.lib import measure_mac_peak
+
     stream = _stream_of(be, device)
     rng = np.random.default_rng(1234)
     G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8).copy()
-
-    from project_b200 import KIND_FR
+    mac_peak = measure_mac_peak(device, 2, 20000)       # 8x8-limb products per second
+    fr_mul_roof = mac_peak * 64.0 / 136.0               # Montgomery multiplications in Fr (136 limb products each)
+    fp_mul_roof = mac_peak * 64.0 / 300.0               # ... in Fp (12 limbs: 300 limb products each)
 
     def timed_ms(fn, reps=3):
         fn()
@@ -33,45 +52,128 @@ def run_sweep(be, device, small=False):
         be.synchronize()
         return start.elapsed_time(stop) / reps
 
-    def rand_fr(n):
-        a = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
-        a[:, 31] &= 0x3F
-        return a
+    def challenge(seed):
+        c = np.zeros(32, dtype=np.uint8)
+        c[:8] = np.frombuffer(np.uint64((0x9E3779B97F4A7C15 * seed) % (1 << 64) | 1).tobytes(), dtype=np.uint8)
+        c[8:16] = np.frombuffer(np.uint64((0xC2B2AE3D27D4EB4F * seed) % (1 << 64)).tobytes(), dtype=np.uint8)
+        return c
 
-    out = {}
-    for lg in ((14,) if small else (20, 22)):
+    def device_vector(n, seed):
+        """n field elements c^0, c^1, ... (Montgomery form) built on the device"""
+        return be.powers(challenge(seed), n)
+
+    out = {"integer_roof": {"limb_products_per_s": mac_peak * 64, "fr_mults_per_s": fr_mul_roof, "fp_mults_per_s": fp_mul_roof,
+                            "note": "8x8-limb multiply-accumulate rate measured on register operands; a Montgomery multiplication costs 136 (Fr) / 300 (Fp) limb products"}}
+    sizes = (12, 14) if small else (16, 18, 20, 22, 24, 26)
+
+    # ---- MSM -------------------------------------------------------------------------------------------
+    msm = []
+    for lg in sizes:
         n = 1 << lg
-        scalars = be.upload(rand_fr(n), KIND_FR)
-        points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n), KIND_FR), n)
-        ms = timed_ms(lambda: be.msm(scalars, points, n))
-        entry = {"log2n": lg, "ms": ms, "Mpts_per_s": n / ms / 1e3}
-        # the same MSM against the resident table of shifted bases (the SRS layout)
-        table, wb = be.msm_precompute(points, n)
-        ms = timed_ms(lambda: be.msm_precomputed(scalars, table, n, wb))
-        entry["resident_table"] = {"window_bits": wb, "table_GB": table.count * 96 / 1e9, "ms": ms, "Mpts_per_s": n / ms / 1e3}
-        out["msm" if lg <= 20 else f"msm_2p{lg}"] = entry
-        for b in (scalars, points, table):
-            b.free()
-    lg = 14 if small else 22
-    n = 1 << lg
-    from project_b200 import KIND_FR_MONT
+        scalars = device_vector(n, 1)
+        multipliers = device_vector(n, 2)
+        points = be.g1_fixed_base_mul(G, multipliers, n)
+        multipliers.free()
+        ms = timed_ms(lambda: be.msm(scalars, points, n), reps=2 if lg >= 24 else 3)
+        c = min(16, max(8, lg - 6))
+        windows = -(-256 // c)
+        adds = n * windows * 10 + 2 * (1 << (c - 1)) * windows * 14  # Fp multiplications: mixed additions + bucket reduction
+        entry = {"log2n": lg, "ms": ms, "Mpts_per_s": n / ms / 1e3, "window_bits": c,
+                 "integer_roof_frac": adds / (ms * 1e-3) / fp_mul_roof}
+        wb = be.msm_window_bits(n)
+        table_points = int(be.lib.gzk_msm_table_points(_sz(n), _c_uint(wb)))
+        if table_points * 96 / 1e9 <= budget_gb:
+            table, wb = be.msm_precompute(points, n)
+            ms = timed_ms(lambda: be.msm_precomputed(scalars, table, n, wb), reps=2 if lg >= 24 else 3)
+            w2 = table_points // n
+            adds = n * w2 * 10 + 2 * (1 << (wb - 1)) * 14
+            entry["resident_table"] = {"window_bits": wb, "table_GB": table_points * 96 / 1e9, "ms": ms, "Mpts_per_s": n / ms / 1e3,
+                                       "integer_roof_frac": adds / (ms * 1e-3) / fp_mul_roof}
+            table.free()
+        else:
+            entry["resident_table"] = f"table of shifted bases would take {table_points * 96 / 1e9:.0f} GB (budget {budget_gb:.0f} GB)"
+        msm.append(entry)
+        scalars.free()
+        points.free()
+    out["msm"] = msm
 
-    vec = be.upload(rand_fr(n), KIND_FR)
-    res = be.alloc(KIND_FR_MONT, n)
-    ms = timed_ms(lambda: be.ntt(vec, lg, out=res))
-    out["ntt"] = {"log2n": lg, "batch": 1, "ms": ms, "GB_per_s": 2 * 32 * n / ms / 1e6,
-                  "field_mults_per_s": (n // 2) * lg / ms * 1e3}
-    r = rand_fr(1)[0]
-    ms = timed_ms(lambda: be.fold(vec, n, r, out=res))
-    out["fold"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6, "forms": "canonical table -> Montgomery output (2 multiplications per output)"}
-    # a table kept in one form through the rounds of a sumcheck costs one multiplication per output
-    half = be.alloc(KIND_FR, n // 2)
-    ms = timed_ms(lambda: be.fold(vec, n, r, out=half))
-    out["fold_same_form"] = {"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6, "forms": "canonical table -> canonical output (1 multiplication per output)"}
-    half.free()
-    for b in (vec, res):
-        b.free()
-    # fp64 forward of one attention head at the mid-size graph's shape (time only: not a roofline target)
+    # ---- NTT / inverse / coset / LDE -------------------------------------------------------------------
+    ntt = []
+    shift = np.zeros(32, dtype=np.uint8)
+    shift[0] = 5
+    for lg in sizes:
+        n = 1 << lg
+        for batch in ((1, 4) if small else (1, 4, 16, 64)):
+            if n * batch > (1 << 28):
+                continue
+            vec = device_vector(n * batch, 3)
+            res = be.alloc(KIND_FR_MONT, n * batch)
+            passes = 1 + (max(0, lg - 10) + 7) // 8
+            mults = batch * ((n // 2) * lg + n * (passes - 1))
+            entry = {"log2n": lg, "batch": batch}
+            for name, kw in (("forward", {}), ("inverse", {"inverse": True}), ("coset_forward", {"coset_shift": shift})):
+                ms = timed_ms(lambda: be.ntt(vec, lg, batch=batch, out=res, **kw), reps=2 if n * batch >= (1 << 26) else 3)
+                extra = batch * n if name != "forward" else 0  # the scaling by 1/n or by the coset powers
+                entry[name] = {"ms": ms, "GB_per_s": 2 * 32 * n * batch / ms / 1e6, "integer_roof_frac": (mults + extra) / (ms * 1e-3) / fr_mul_roof}
+            ntt.append(entry)
+            vec.free()
+            res.free()
+    out["ntt"] = ntt
+    lde = []
+    for lg in sizes:
+        if lg + 1 > 27:
+            continue
+        n = 1 << lg
+        vec = device_vector(n, 4)
+        wide = be.alloc(KIND_FR_MONT, 2 * n)
+        ms = timed_ms(lambda: be.coset_lde(vec, lg, 1, shift, out=wide), reps=2)
+        wide.free()
+        lde.append({"log2n": lg, "blowup": 2, "ms": ms, "GB_per_s": 32 * n * 3 / ms / 1e6})
+        vec.free()
+    out["coset_lde"] = lde
+
+    # ---- sumcheck fold ----------------------------------------------------------------------------------
+    fold = []
+    for lg in ((12, 14) if small else (20, 22, 24, 26)):
+        n = 1 << lg
+        vec = device_vector(n, 5)  # Montgomery table
+        half = be.alloc(KIND_FR_MONT, n // 2)
+        r = challenge(6)
+        ms = timed_ms(lambda: be.fold(vec, n, r, out=half))
+        fold.append({"log2n": lg, "ms": ms, "GB_per_s": 48 * n / ms / 1e6, "integer_roof_frac": (n // 2) / (ms * 1e-3) / fr_mul_roof,
+                     "forms": "table kept in Montgomery form (1 multiplication per output)"})
+        vec.free()
+        half.free()
+    out["fold"] = fold
+
+    # ---- CPU stand-ins on the host cores (the reference has no MSM, NTT or fold: these are the oracle's) ------
+    try:
+        import time
+
+        import oracle_lib as ora
+
+        cpu = {}
+        m = 1 << 10
+        sc = rng.integers(0, 256, size=(m, 32), dtype=np.uint8)
+        sc[:, 31] &= 0x3F
+        pts = ora.g1_mul_same_base(G, sc[:64])
+        pts = np.tile(pts, (m // 64, 1))
+        t0 = time.perf_counter()
+        ora.g1_msm_naive(pts, sc)
+        cpu["msm_naive_2p10"] = {"ms": (time.perf_counter() - t0) * 1e3, "note": "double-and-add per point, one thread"}
+        v = rng.integers(0, 256, size=(1 << 16, 32), dtype=np.uint8)
+        v[:, 31] &= 0x3F
+        t0 = time.perf_counter()
+        ora.ntt(v)
+        cpu["ntt_2p16"] = {"ms": (time.perf_counter() - t0) * 1e3, "note": "radix-2 transform, one thread"}
+        t0 = time.perf_counter()
+        ora.fold(v, sc[0])
+        cpu["fold_2p16"] = {"ms": (time.perf_counter() - t0) * 1e3, "note": "one thread"}
+        out["cpu_stand_ins"] = cpu
+    except Exception as e:  # the sweep numbers do not depend on the stand-ins
+        out["cpu_stand_ins"] = f"unavailable: {e}"
+
+    # ---- fp64 forward of one attention head at the mid-size graph's shape (time only: not a roofline target) ---
     from project_b200 import KIND_F64, KIND_U32, incoming_lists
 
     nodes, inner, width, directed = (512, 32, 8, 2000) if small else (19717, 500, 8, 88648)
@@ -85,15 +187,13 @@ def run_sweep(be, device, small=False):
     args = (up(feats, KIND_F64), up(rng.uniform(-0.1, 0.1, size=(inner, width)), KIND_F64), up(rng.uniform(-1, 1, size=width), KIND_F64), 0.0,
             up(rng.uniform(-1, 1, size=width), KIND_F64), 0.0, up(np.zeros(width), KIND_F64), True, up(src, KIND_U32), up(dst, KIND_U32),
             nodes, inner, width, up(ptr, KIND_U32), up(inc, KIND_U32))
-
     trace = be.gat_head_forward(*args)
 
     def forward():
         be.gat_head_forward(*args, out=trace)
         be.synchronize()
 
-    ms = timed_ms(forward)
-    out["head_forward_fp64"] = {"nodes": nodes, "edges": int(src.size), "input_width": inner, "output_width": width, "ms": ms}
+    out["head_forward_fp64"] = {"nodes": nodes, "edges": int(src.size), "input_width": inner, "output_width": width, "ms": timed_ms(forward)}
     return out
 
 

@@ -72,3 +72,16 @@ def test_values_on_a_rounding_boundary_take_the_host_recheck():
     assert np.array_equal(gpu.proof_bytes(), cpu.proof_bytes())
     cpu.close()
     gpu.close()
+
+
+def test_msm_commitments_equal_the_trapdoor_commitments():
+    """Every commitment of a proof, computed once more as an MSM of the column against the resident SRS
+    (Lagrange basis of its domain, monomial basis for the matrices), is the same point as [p(tau)] G."""
+    shape = dict(seed=12, nodes=40, directed_edges=120, feature_count=10, hidden=[(2, 4)], output_heads=2, class_count=3)
+    gpu = gpu_flow(0, synthetic.make_inputs(**shape), G)
+    gpu.set_msm_commit(True)
+    gpu.prove()
+    checked, mismatches = gpu.set_msm_commit(False)
+    assert checked == gpu.stats()["dynamic_commitments"] - 4  # the four lazy feature-lookup commitments are scalar combinations
+    assert mismatches == 0
+    gpu.close()
