@@ -478,6 +478,38 @@ int gzk_eval_batch_range_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_cou
 int gzk_fr_sum(const uint8_t* values, size_t groups, size_t count, uint8_t* out);
 int gzk_g1_sum(const uint8_t* points, size_t count, uint8_t out[96]);
 
+/* ---- exchange between GPUs (one process and one context per GPU) -----------------------------------
+ * The reference is a single process; this is what `--gpus N` of a multi-GPU host needs beside the
+ * range entry points above.  A communicator wraps NCCL (bound at run time: libnccl.so.2) and issues
+ * its collectives on the context's stream, so they are ordered with the kernels around them; data
+ * always lands in the receiving GPU's own memory before a kernel of this library reads it.
+ * gzk_comm_unique_id: rank 0 makes the 128-byte id and hands it to the other ranks by any host
+ *   channel; gzk_comm_create: collective over all ranks.
+ * gzk_comm_allgather: out[g*count .. ) = rank g's in[0 .. count) (any buffer kind; raw elements).
+ * gzk_comm_allgather_fr_sum: out[i] = sum over all ranks of their in[i] mod r - the partial sums of
+ *   gzk_eval_batch_range_device, combined on the device (replaces the host's gzk_fr_sum).
+ * gzk_comm_alltoall: chunk g of `in` goes to rank g, chunk h of `out` comes from rank h.
+ * gzk_ntt_sharded: the row-sharded forward transform of 2^log2n elements as one call (see the
+ *   row-sharded transform above): `rows` = this rank's rows, result X[k1 + n1*k2] for k1 in this
+ *   rank's block in `out` (Montgomery form); `work` = a second buffer of the local size.
+ * gzk_comm_wait: host-side wait for everything queued on the context's stream, bounded by the
+ *   communicator's time limit (gzk_comm_set_timeout, default 30 s).  When the limit runs out - a
+ *   peer never joined a collective - the communicator is aborted (ncclCommAbort), the call returns
+ *   GZK_E_TIMEOUT and every later exchange on this communicator fails at once; the context itself
+ *   stays usable. */
+typedef struct gzk_comm gzk_comm;
+int gzk_comm_unique_id(uint8_t out[128]);
+int gzk_comm_create(gzk_ctx* ctx, int nranks, int rank, const uint8_t unique_id[128], gzk_comm** out);
+void gzk_comm_destroy(gzk_comm* comm);
+int gzk_comm_set_timeout(gzk_comm* comm, double seconds);
+int gzk_comm_rank(const gzk_comm* comm);
+int gzk_comm_size(const gzk_comm* comm);
+int gzk_comm_wait(gzk_comm* comm);
+int gzk_comm_allgather(gzk_comm* comm, const gzk_buf* in, size_t count, gzk_buf* out);
+int gzk_comm_allgather_fr_sum(gzk_comm* comm, const gzk_buf* in, size_t count, gzk_buf* out);
+int gzk_comm_alltoall(gzk_comm* comm, const gzk_buf* in, size_t count_per_rank, gzk_buf* out);
+int gzk_ntt_sharded(gzk_comm* comm, const gzk_buf* rows, unsigned log2n, gzk_buf* work, gzk_buf* out);
+
 /* ---- generated public columns; carry of a sharded running sum ---------------------------------
  * gzk_generated_column: columns the reference materialises on the host although they are
  * pure functions of the row index: what = 0 selector (1 for i < valid, build_selector,

@@ -452,6 +452,14 @@ class Backend:
         self._check(self.lib.gzk_sumcheck_round_sums(self.ctx, table.handle, _sz(n), _ptr(out)))
         return out
 
+    def eval_batch_range_device(self, cols, length, row_offset, log2n, weights, weights_first, rotations, out, out_offset=0):
+        handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
+        rot = np.ascontiguousarray(rotations, dtype=np.uint64)
+        self._check(self.lib.gzk_eval_batch_range_device(self.ctx, handles, _sz(len(cols)), _sz(length), ctypes.c_uint64(row_offset), ctypes.c_uint(log2n),
+                                                         weights.handle, ctypes.c_uint64(weights_first), _ptr(rot), _sz(rot.size), out.handle,
+                                                         _sz(out_offset)))
+        return out
+
     def eval_batch(self, cols, length, log2n, weights, rotations=(0,)):
         handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
         rot = np.ascontiguousarray(rotations, dtype=np.uint64)
@@ -474,6 +482,55 @@ def eval_batch_static(device, stream, col_ptrs, col_kinds, length, log2n, weight
                                    ctypes.c_void_p(weights_ptr), _ptr(rot), _sz(rot.size), ctypes.c_void_p(out_ptr), err, _sz(256))
     if rc != 0:
         raise GzkError(rc, err.value.decode())
+
+
+class Comm:
+    """gzk_comm: the NCCL communicator of one rank, bound to a Backend (its stream orders the collectives)."""
+
+    def __init__(self, backend, nranks, rank, unique_id):
+        self.be = backend
+        uid = np.ascontiguousarray(unique_id, dtype=np.uint8).reshape(-1)
+        assert uid.size == 128
+        h = ctypes.c_void_p()
+        backend._check(backend.lib.gzk_comm_create(backend.ctx, int(nranks), int(rank), _ptr(uid), ctypes.byref(h)))
+        self.handle, self.nranks, self.rank = h, nranks, rank
+
+    @staticmethod
+    def unique_id():
+        out = np.zeros(128, dtype=np.uint8)
+        if load_library().gzk_comm_unique_id(_ptr(out)) != 0:
+            raise GzkError(2, "gzk_comm_unique_id: NCCL is not available")
+        return out
+
+    def set_timeout(self, seconds):
+        self.be._check(self.be.lib.gzk_comm_set_timeout(self.handle, ctypes.c_double(seconds)))
+
+    def wait(self):
+        self.be._check(self.be.lib.gzk_comm_wait(self.handle))
+
+    def allgather(self, inp, count, out):
+        self.be._check(self.be.lib.gzk_comm_allgather(self.handle, inp.handle, _sz(count), out.handle))
+        return out
+
+    def allgather_fr_sum(self, inp, count, out):
+        self.be._check(self.be.lib.gzk_comm_allgather_fr_sum(self.handle, inp.handle, _sz(count), out.handle))
+        return out
+
+    def alltoall(self, inp, count_per_rank, out):
+        self.be._check(self.be.lib.gzk_comm_alltoall(self.handle, inp.handle, _sz(count_per_rank), out.handle))
+        return out
+
+    def ntt_sharded(self, rows, log2n, work, out):
+        self.be._check(self.be.lib.gzk_ntt_sharded(self.handle, rows.handle, ctypes.c_uint(log2n), work.handle, out.handle))
+        return out
+
+    def close(self):
+        if self.handle:
+            fn = self.be.lib.gzk_comm_destroy
+            fn.restype = None
+            fn.argtypes = [ctypes.c_void_p]
+            fn(self.handle)
+            self.handle = None
 
 
 def inject_eval_stall(on):
