@@ -325,11 +325,102 @@ namespace gatzk_b200
                 return out;
             }
 
+            // eval_backend.cpp:142-189: the values of the named columns at one row (the point is omega^index)
+            std::vector<FieldElement> values_at_direct_index(const std::vector<std::string>& labels, std::size_t index) const
+            {
+                std::vector<FieldElement> out(labels.size());
+                for (std::size_t i = 0; i < labels.size(); ++i)
+                {
+                    const auto it = label_to_index_.find(labels[i]);
+                    if (it == label_to_index_.end()) throw std::runtime_error("domain evaluation backend is missing label: " + labels[i]);
+                    const auto* polynomial = polynomials_[it->second].second;
+                    if (index < polynomial->length)
+                    {
+                        std::uint8_t raw[32];
+                        polynomial->data->download(raw, 1, index);
+                        out[i] = FieldElement::from_bytes(raw);
+                    }
+                }
+                return out;
+            }
+            const std::shared_ptr<RootOfUnityDomain>& domain() const { return domain_; }
+
         private:
             const Context* ctx_;
             std::shared_ptr<RootOfUnityDomain> domain_;
             std::vector<std::pair<std::string, const Polynomial*>> polynomials_;
             std::map<std::string, std::size_t> label_to_index_;
+        };
+    }
+
+    namespace protocol
+    {
+        // The verifier evaluates the PUBLIC columns itself, with the same packed backend the prover uses
+        // (PublicEvaluationBackendRegistry + the precompute of VerifierEvaluationCache,
+        // src/protocol/verifier.cpp:218-262, 540-565): all public columns of a domain are grouped in one
+        // backend, and the first request at a point evaluates the whole group - by direct row access when
+        // the point is a domain point (include/gatzk/algebra/domain_evaluation.hpp:40-71), by barycentric
+        // weights otherwise.  On the reference's large runs this is most of verify_time (176 s of the
+        // 169k-node run); here it is one weights call and one packed evaluation per (domain, point).
+        class PublicEvaluationBackendRegistry
+        {
+        public:
+            PublicEvaluationBackendRegistry(const Context& ctx, const std::map<std::string, algebra::Polynomial>& public_polynomials) : ctx_(&ctx)
+            {
+                std::map<std::string, std::vector<std::pair<std::string, const algebra::Polynomial*>>> groups;
+                std::map<std::string, std::shared_ptr<algebra::RootOfUnityDomain>> domains;
+                for (const auto& item : public_polynomials)
+                {
+                    const auto& polynomial = item.second;
+                    if (polynomial.basis != algebra::PolynomialBasis::Evaluation || polynomial.domain == nullptr) continue;
+                    const auto key = polynomial.domain->name + ":" + std::to_string(polynomial.domain->size);
+                    groups[key].push_back({item.first, &polynomial});
+                    domains[key] = polynomial.domain;
+                    label_domain_[item.first] = key;
+                }
+                for (auto& group : groups)
+                {
+                    std::vector<std::string> labels;
+                    for (const auto& p : group.second) labels.push_back(p.first);
+                    labels_.emplace(group.first, std::move(labels));
+                    backends_.emplace(group.first, algebra::PackedEvaluationBackend(ctx, domains.at(group.first), std::move(group.second)));
+                }
+            }
+            // value of one public column at a point; the whole domain group is evaluated on the first request
+            // at that point and cached, as the reference's verifier does
+            algebra::FieldElement eval(const std::string& label, const algebra::FieldElement& point)
+            {
+                const auto dom = label_domain_.find(label);
+                if (dom == label_domain_.end()) throw std::runtime_error("unsupported verifier public polynomial label: " + label);
+                const std::string point_key(reinterpret_cast<const char*>(point.bytes()), 32);
+                const auto cache_key = dom->second + "@" + point_key;
+                auto hit = cache_.find(cache_key);
+                if (hit == cache_.end())
+                {
+                    const auto& backend = backends_.at(dom->second);
+                    const auto& labels = labels_.at(dom->second);
+                    std::vector<algebra::FieldElement> values;
+                    std::size_t shift = 0;
+                    if (backend.domain()->rotation_shift(point, &shift))
+                        values = backend.values_at_direct_index(labels, shift);
+                    else
+                        values = backend.evaluate_with_native_weights(labels, backend.domain()->barycentric_weights_native(point));
+                    std::map<std::string, algebra::FieldElement> by_label;
+                    for (std::size_t i = 0; i < labels.size(); ++i) by_label.emplace(labels[i], values[i]);
+                    hit = cache_.emplace(cache_key, std::move(by_label)).first;
+                    ++group_evaluations_;
+                }
+                return hit->second.at(label);
+            }
+            std::size_t group_evaluations() const { return group_evaluations_; }
+
+        private:
+            const Context* ctx_;
+            std::map<std::string, algebra::PackedEvaluationBackend> backends_;
+            std::map<std::string, std::vector<std::string>> labels_;
+            std::map<std::string, std::string> label_domain_;
+            std::map<std::string, std::map<std::string, algebra::FieldElement>> cache_;
+            std::size_t group_evaluations_ = 0;
         };
     }
 

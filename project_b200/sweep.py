@@ -198,22 +198,23 @@ def run_sweep(be, device, small=False, budget_gb=40.0):
 
 
 def run_sweep_sharded(be, G, rank, world, device, small=False):
-    """Sweep kernels over all ranks: the row-sharded transform (two all-to-all exchanges over
-    NCCL) and the point-range-sharded MSM (one 96-byte all-gather); device-timed, max over ranks."""
+    """Sharded kernels over all ranks through the library's own communicator (gzk_comm_*): the row-sharded
+    transform (two all-to-all exchanges), the point-range-sharded MSM (an all-gather of one point per rank),
+    the row-sharded packed evaluation of an edge-shaped domain with the partial sums combined on the
+    device, and - on 8 ranks - the evaluation phase of the 169k-node configuration, whose opened edge
+    columns (294 x 2^26 rows) only fit when their rows are split over 8 GPUs.  Device-timed, max over ranks."""
     import torch
     import torch.distributed as dist
 
-    from project_b200 import KIND_FR, KIND_FR_MONT, fr_sum, g1_sum
-    from project_b200 import sharded_ntt as sn
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_G1, KIND_I64, fr_sum, g1_sum, shard_rows
+    from project_b200.lib import Comm
 
     stream = _stream_of(be, device)
-
-    rng = np.random.default_rng(1000 + rank)
-
-    def rand_fr(n):
-        a = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
-        a[:, 31] &= 0x3F
-        return a
+    box = [Comm.unique_id() if rank == 0 else None]
+    dist.broadcast_object_list(box, src=0)
+    comm = Comm(be, world, rank, box[0])
+    comm.set_timeout(120.0)
+    be.set_deferred(True)
 
     def timed_ms(fn, reps=3):
         fn()
@@ -230,64 +231,103 @@ def run_sweep_sharded(be, G, rank, world, device, small=False):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    def challenge(seed):
+        c = np.zeros(32, dtype=np.uint8)
+        c[:8] = np.frombuffer(np.uint64((0x9E3779B97F4A7C15 * seed) % (1 << 64) | 1).tobytes(), dtype=np.uint8)
+        return c
+
+    def all_ok(flag):
+        verdict = torch.tensor([1 if flag else 0], device="cuda", dtype=torch.int32)
+        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)  # every rank learns the outcome: none is left waiting in a collective
+        return int(verdict.item()) == 1
+
     out = {}
+    # ---- row-sharded transform ---------------------------------------------------------------------------
     if world & (world - 1) == 0:
         lg = 14 if small else 24
         n = 1 << lg
         local = n // world
-        vec = be.upload(rand_fr(local), KIND_FR)
-        work = (be.alloc(KIND_FR, local), be.alloc(KIND_FR_MONT, local))
-        exchange = sn.NcclExchange(be, local, device)
-
-        def transform():
-            work[0].retag(KIND_FR)
-            exchange.run(sn.forward(be, vec, lg, rank, world, work=work))
-
-        ms = timed_ms(transform)
+        vec = be.powers(challenge(100 + rank), local)
+        work, res = be.alloc(KIND_FR_MONT, local), be.alloc(KIND_FR_MONT, local)
+        ms = timed_ms(lambda: comm.ntt_sharded(vec, lg, work, res))
         # self-check without a CPU pass: X[0] (first element of rank 0's block) is the sum of all inputs
         sums = be.sumcheck_round_sums(vec, local)
-        mine = torch.from_numpy(fr_sum(np.stack([sums[0], sums[1]]))).cuda()
-        every = torch.empty((world, 32), dtype=torch.uint8, device="cuda")
-        dist.all_gather_into_tensor(every, mine)
-        good = 1
-        if rank == 0 and not np.array_equal(work[1].download(count=1)[0], fr_sum(every.cpu().numpy())):
-            good = 0
-        verdict = torch.tensor([good], device="cuda", dtype=torch.int32)
-        dist.all_reduce(verdict, op=dist.ReduceOp.MIN)  # every rank learns the outcome: none is left waiting in a collective
-        if int(verdict.item()) == 0:
+        mine = be.upload(fr_sum(np.stack([sums[0], sums[1]])).reshape(1, 32), KIND_FR)
+        total = be.alloc(KIND_FR, 1)
+        comm.allgather_fr_sum(mine, 1, total)
+        comm.wait()
+        good = rank != 0 or np.array_equal(res.download(count=1)[0], total.download()[0])
+        if not all_ok(good):
             raise RuntimeError("row-sharded transform: X[0] does not equal the sum of the inputs")
-        be.timing_reset()
-        be.timing_enable(True)
-        transform()
-        be.synchronize()
-        families = {k: round(v[1], 3) for k, v in be.timing_report().items()}
-        be.timing_enable(False)
-        exchange.close()
-        for b in work:
+        out["ntt_sharded"] = {"log2n": lg, "ranks": world, "ms": ms, "GB_per_s": 2 * 32 * n / ms / 1e6, "field_mults_per_s": (n // 2) * lg / ms * 1e3,
+                              "layout": "rows in, transposed out; 2 all-to-all exchanges inside gzk_ntt_sharded", "self_check": "ok"}
+        for b in (vec, work, res):
             b.free()
-        out["ntt_sharded"] = {"log2n": lg, "ranks": world, "ms": ms, "GB_per_s": 2 * 32 * n / ms / 1e6,
-                              "field_mults_per_s": (n // 2) * lg / ms * 1e3, "layout": "rows in, transposed out; 2 all-to-all exchanges",
-                              "kernel_ms_one_transform": families}
-        vec.free()
+    # ---- point-range-sharded MSM ---------------------------------------------------------------------------
     lg = 12 if small else 20
-    n_local = (1 << lg)
-    scalars = be.upload(rand_fr(n_local), KIND_FR)
-    points = be.g1_fixed_base_mul(G, be.upload(rand_fr(n_local), KIND_FR), n_local)
-
+    n_local = 1 << lg
+    scalars = be.powers(challenge(200 + rank), n_local)
+    multipliers = be.powers(challenge(300 + rank), n_local)
+    points = be.g1_fixed_base_mul(G, multipliers, n_local)
     table, wb = be.msm_precompute(points, n_local)  # each rank keeps the shifted copies of its own point range
+    part_buf, all_buf = be.alloc(KIND_G1, 1), be.alloc(KIND_G1, world)
 
     def msm():
-        part = torch.from_numpy(be.msm_precomputed(scalars, table, n_local, wb).copy()).cuda()
-        gathered = torch.empty((world, 96), dtype=torch.uint8, device="cuda")
-        dist.all_gather_into_tensor(gathered, part)
-        return g1_sum(gathered.cpu().numpy())
+        part_buf.upload(be.msm_precomputed(scalars, table, n_local, wb).reshape(1, 96))
+        comm.allgather(part_buf, 1, all_buf)
+        comm.wait()
+        return g1_sum(all_buf.download())
 
     ms = timed_ms(msm)
     out["msm_sharded"] = {"log2n_per_rank": lg, "ranks": world, "ms": ms, "Mpts_per_s": world * n_local / ms / 1e3,
-                          "layout": "point range per rank, resident table of shifted bases, 96-byte all-gather"}
-    scalars.free()
-    points.free()
-    table.free()
+                          "layout": "point range per rank, resident table of shifted bases, all-gather of one point per rank"}
+    for b in (scalars, multipliers, points, table, part_buf, all_buf):
+        b.free()
+
+    # ---- row-sharded packed evaluation, partial sums combined on the device ----------------------------------
+    def sharded_evaluation(log2n, k_field, k_int, label):
+        n = 1 << log2n
+        begin, end = shard_rows(n, world, rank, align=32)
+        rows = end - begin
+        w_first, w_count = (begin - 1) % n, min(rows + 1, n)
+        cols = [be.powers(challenge(1000 + 17 * i + rank), rows) for i in range(k_field)]
+        cols += [be.generated_column(1 + (i % 3), rows, 7 + i, rows, kind=KIND_I64) for i in range(k_int)]
+        k = len(cols)
+        tau = np.zeros(32, dtype=np.uint8)
+        tau[0] = 28
+        w_tau = be.bary_weights_range(log2n, tau, w_first, w_count)
+        w_z = be.alloc(KIND_FR_MONT, w_count)
+        partial, summed = be.alloc(KIND_FR_MONT, 4 * k), be.alloc(KIND_FR_MONT, 4 * k)
+        counter = [0]
+
+        def step():
+            counter[0] += 1
+            be.eval_batch_range_device(cols, rows, begin, log2n, w_tau, w_first, (0, 1), partial, 0)          # quotient: {tau, omega tau}
+            be.bary_weights_range(log2n, challenge(5000 + counter[0]), w_first, w_count, out=w_z)              # fresh opening point
+            be.eval_batch_range_device(cols, rows, begin, log2n, w_z, w_first, (0, 1), partial, 2 * k)        # openings: {z, omega z}
+            comm.allgather_fr_sum(partial, 4 * k, summed)
+            comm.wait()
+            return summed.download()
+
+        ms = timed_ms(step, reps=2)
+        bytes_per_rank = sum(c.count * (8 if c.kind == KIND_I64 else 32) for c in cols)
+        entry = {"domain": label, "log2n": log2n, "columns": k, "field_columns": k_field, "int64_columns": k_int, "ranks": world, "ms": ms,
+                 "resident_GB_per_rank": bytes_per_rank / 1e9,
+                 "step": "evaluation of every column at {tau, omega tau} and at a fresh {z, omega z} (weights at z computed per step), partial sums "
+                         "summed over the ranks on the device (gzk_comm_allgather_fr_sum), one read-back"}
+        for b in cols + [w_tau, w_z, partial, summed]:
+            b.free()
+        return entry
+
+    try:
+        out["eval_sharded_edge"] = sharded_evaluation(12 if small else 18, 8 if small else 375, 8 if small else 257, "edge domain of the mid-size configuration (632 opened columns, 2^18 rows)")
+    except Exception as e:  # keep the other lines of the sweep
+        out["eval_sharded_edge"] = f"failed: {e}"
+    if world == 8 and not small:
+        try:
+            # the 169k-node configuration: 294 opened edge columns (about half of them small integers) x 2^26 rows
+            out["b4_8gpu_evaluation"] = sharded_evaluation(26, 147, 147, "edge domain of the 169k-node configuration (294 opened columns, 2^26 rows)")
+        except Exception as e:
+            out["b4_8gpu_evaluation"] = f"failed: {e}"
+    comm.close()
     return out
-
-

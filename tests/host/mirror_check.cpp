@@ -242,6 +242,40 @@ int main()
         CHECK(exact, "head forward: H', E_src, E_dst, S, Z, M, Delta bit-identical");
         CHECK(close, "head forward: U, Sum, inv, alpha, H_agg within 4e-15");
     }
+    // ---- verifier side: public columns of a domain evaluated as one group per point ----------------------
+    {
+        const std::size_t n = 1 << 11;
+        auto domain = algebra::RootOfUnityDomain::create(ctx, "N", n);
+        std::map<std::string, algebra::Polynomial> publics;
+        std::vector<std::vector<FieldElement>> data;
+        const char* names[3] = {"P_I", "P_Q_N", "P_src"};
+        for (int k = 0; k < 3; ++k)
+        {
+            std::vector<FieldElement> column(n - 100 * k);  // stored prefixes of different lengths
+            for (std::size_t i = 0; i < column.size(); ++i) column[i] = k == 1 ? FieldElement(i < 1500 ? 1 : 0) : FieldElement(rng() % 100000);
+            data.push_back(column);
+            publics.emplace(names[k], algebra::Polynomial::from_evaluations(ctx, names[k], column, domain));
+        }
+        protocol::PublicEvaluationBackendRegistry registry(ctx, publics);
+        const FieldElement z(0x51ed270b5ULL);
+        std::vector<std::uint8_t> weights(n * 32);
+        ora_bary_weights(z.bytes(), n, weights.data());
+        bool same = true;
+        for (int k = 0; k < 3; ++k)
+        {
+            const auto padded = flat(data[k], n);
+            const std::uint64_t rot = 0;
+            std::uint8_t want[32];
+            ora_eval_rotations(padded.data(), 1, n, weights.data(), &rot, 1, 1, want);
+            same = same && registry.eval(names[k], z) == FieldElement::from_bytes(want);
+        }
+        CHECK(same, "verifier public columns at a challenge point");
+        CHECK(registry.group_evaluations() == 1, "one packed evaluation serves the whole domain group");
+        // a point of the domain takes the direct-index branch: column value at that row, zero beyond the stored prefix
+        const FieldElement on_domain = domain->omega.pow(1950);
+        CHECK(registry.eval("P_I", on_domain) == data[0][1950], "direct index inside the stored prefix");
+        CHECK(registry.eval("P_src", on_domain) == FieldElement::zero(), "direct index beyond the stored prefix");
+    }
     std::printf(failures == 0 ? "OK\n" : "FAILED %d\n", failures);
     return failures == 0 ? 0 : 1;
 }
