@@ -24,6 +24,7 @@
 #include <thread>
 
 #include "common.cuh"
+#include "../host/bounded_wait.hpp"
 
 namespace
 {
@@ -205,23 +206,25 @@ extern "C"
     {
         int rc = comm_ready(c, "comm_wait");
         if (rc != GZK_OK) return rc;
-        const auto start = std::chrono::steady_clock::now();
-        for (;;)
-        {
-            const cudaError_t q = cudaStreamQuery(c->ctx->stream);
-            if (q == cudaSuccess) return GZK_OK;
-            if (q != cudaErrorNotReady) return cuda_fail(c->ctx, q, "cudaStreamQuery");
-            const double waited = std::chrono::duration<double>(std::chrono::steady_clock::now() - start).count();
-            if (waited > c->timeout_seconds)
-            {
+        cudaError_t query_error = cudaSuccess;
+        const WaitResult result = bounded_wait(
+            [&]() {
+                const cudaError_t q = cudaStreamQuery(c->ctx->stream);
+                if (q == cudaSuccess) return WaitState::Ready;
+                if (q == cudaErrorNotReady) return WaitState::Pending;
+                query_error = q;
+                return WaitState::Failed;
+            },
+            [&]() {
                 nccl().CommAbort(c->comm);
                 c->comm = nullptr;
                 c->aborted = true;
                 cudaStreamSynchronize(c->ctx->stream);  // the aborted collective's kernel ends
-                return fail(c->ctx, GZK_E_TIMEOUT, "comm_wait: a collective did not complete within the time limit; the communicator was aborted");
-            }
-            std::this_thread::sleep_for(std::chrono::microseconds(50));
-        }
+            },
+            c->timeout_seconds);
+        if (result == WaitResult::Completed) return GZK_OK;
+        if (result == WaitResult::QueryFailed) return cuda_fail(c->ctx, query_error, "cudaStreamQuery");
+        return fail(c->ctx, GZK_E_TIMEOUT, "comm_wait: a collective did not complete within the time limit; the communicator was aborted");
     }
 
     int gzk_comm_allgather(gzk_comm* c, const gzk_buf* in, size_t count, gzk_buf* out)

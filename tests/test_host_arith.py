@@ -20,10 +20,15 @@ def test_proof_byte_codec_on_host():
     _run(os.path.join(ROOT, "tests", "host", "proof_codec_check.cpp"))
 
 
+def test_exchange_wait_gives_up_when_a_peer_never_posts():
+    """The host-side wait behind gzk_comm_wait with a fake stream query: times out, aborts once, keeps going."""
+    _run(os.path.join(ROOT, "tests", "host", "bounded_wait_check.cpp"))
+
+
 def _run(src):
     with tempfile.TemporaryDirectory() as tmp:
         exe = os.path.join(tmp, "mp_host_check")
-        subprocess.run(["g++", "-O2", "-std=c++17", "-o", exe, src], check=True)
+        subprocess.run(["g++", "-O2", "-std=c++17", "-pthread", "-o", exe, src], check=True)
         out = subprocess.run([exe], capture_output=True, text=True, timeout=600)
     assert out.returncode == 0, out.stdout + out.stderr
     assert out.stdout.strip().endswith("OK")
