@@ -40,6 +40,13 @@ typedef struct gzk_flow_config
     const double* params;
     uint64_t param_count;
     const uint8_t* generator;         /* affine G1 generator, 96 bytes (x || y, little-endian) */
+    /* not zero: edge-domain columns are stored as prefixes (the rows that carry data; a running sum up to
+     * its final value, which the remaining rows repeat) instead of whole-domain vectors.  The committed
+     * polynomials and the proof are the same; memory drops from (columns x domain size) to
+     * (columns x edge count), which is what lets the 169k-node configuration (edge domain 2^26, about
+     * 300 opened edge columns) run on one device.  The reference stores whole-domain vectors
+     * (0.3-0.65 TB of host memory at that size).  Not combinable with gzk_flow_set_msm_commit. */
+    uint32_t compact_columns;
 } gzk_flow_config;
 
 const char* gzk_flow_error(void);

@@ -334,20 +334,25 @@ namespace gzk
         // a separate inversion pass: on a small domain (a few CTAs) the call is one short chain instead
         // of three dependent launches, on a large one the serial inversions hide behind the arithmetic
         // of the CTA that shares the SM.
+        // ELEMS quartets per thread: the whole-domain call of a SMALL domain (a few thousand points, the
+        // node-domain weights every binding of the flow asks for) is one dependent chain, so it takes one
+        // quartet per thread and spreads over as many SMs as it has 256-quartet groups; a large domain
+        // takes four and amortises the serial inversion over 1024 quartets.
+        template <int ELEMS>
         __global__ void __launch_bounds__(kThreads, 2) bary4_fused_kernel(BaryArgs a, Fr* out, int* status)
         {
             __shared__ Fr warp_incl[kThreads / 32];
             __shared__ Fr warp_pre[kThreads / 32];
             __shared__ Fr warp_suf[kThreads / 32];
             __shared__ Fr cta_inverse;
-            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk;
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kThreads * ELEMS);
             const int lane = threadIdx.x & 31;
             const int warp = threadIdx.x >> 5;
 
-            Fr d[kElems], pre[kElems];
+            Fr d[ELEMS], pre[ELEMS];
             Fr mine = Fr::one();
 #pragma unroll
-            for (int j = 0; j < kElems; ++j)
+            for (int j = 0; j < ELEMS; ++j)
             {
                 const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
                 Fr p1, p2;
@@ -394,7 +399,7 @@ namespace gzk
             const Fr outer = mul(cta_inverse, mul(mul(left, warp_pre[warp]), mul(right, warp_suf[warp])));
             Fr rest = mul(a.scale, outer);  // (x^n-1)/n over the product of the thread's denominators 0 .. j
 #pragma unroll
-            for (int j = kElems - 1; j >= 0; --j)
+            for (int j = ELEMS - 1; j >= 0; --j)
             {
                 const uint64_t e = base + static_cast<uint64_t>(j) * kThreads + threadIdx.x;
                 const Fr scaled_inverse = mul(rest, pre[j]);  // (x^n-1)/n / D_e
@@ -467,7 +472,9 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
         args.x4 = sqr(args.x2);
         args.root4 = host_root_of_unity(2);
     }
-    const uint32_t blocks = static_cast<uint32_t>((args.n + kChunk - 1) / kChunk);
+    // a whole small domain: one quartet per thread (see bary4_fused_kernel)
+    const bool short_chain = quartets && args.n <= (1u << 16);
+    const uint32_t blocks = short_chain ? static_cast<uint32_t>((args.n + kThreads - 1) / kThreads) : static_cast<uint32_t>((args.n + kChunk - 1) / kChunk);
     void* scratch = nullptr;
     if ((rc = ensure_scratch(ctx, 2, static_cast<size_t>(blocks) * 2 * sizeof(Fr), &scratch)) != GZK_OK) return rc;
     Fr* products = static_cast<Fr*>(scratch);
@@ -477,7 +484,10 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     {
         {
             LaunchScope scope(ctx, "bary_fused");
-            bary4_fused_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
+            if (short_chain)
+                bary4_fused_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
+            else
+                bary4_fused_kernel<kElems><<<blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         rc = finish_call(ctx, "bary_weights: invalid input");

@@ -176,6 +176,43 @@ namespace gzk
             if (part == 0 && i < count) store_xyzz(out + i, acc);
         }
 
+        // The lane-split sum followed, in the same launch, by the conversion to affine coordinates: each
+        // point's own denominator is inverted by the lane that holds the sum.  A shared (batch) inversion
+        // saves arithmetic but puts a prefix pass, one serial inversion and a suffix pass on the chain,
+        // and three launches; for the few dozen points of one commit barrier every point inverting for
+        // itself, all at once, is the shorter chain.
+        constexpr size_t kFusedAffineLimit = 1024;
+        __global__ void __launch_bounds__(128) fixed_base_mul_affine_kernel(const G1Affine* table, ColRef scalars, size_t count, G1Affine* out, int canonical)
+        {
+            const size_t t = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+            const size_t i = t / kLanes;
+            const int part = static_cast<int>(t % kLanes);
+            const size_t i_load = i < count ? i : count - 1;
+            Fr s = load_fr(static_cast<const Fr*>(scalars.ptr) + i_load);
+            if (scalars.kind == GZK_KIND_FR_MONT) s = from_mont(s);
+            G1Xyzz acc = G1Xyzz::infinity();
+#pragma unroll 1
+            for (int w = part * (kWindows / kLanes); w < (part + 1) * (kWindows / kLanes); ++w)
+            {
+                const uint32_t digit = (s.l[w >> 2] >> ((w & 3) * 8)) & 0xffu;
+                if (digit != 0) acc = g1_add_mixed(acc, load_affine(table + w * kEntries + (digit - 1)));
+            }
+#pragma unroll 1
+            for (int offset = kLanes / 2; offset > 0; offset >>= 1)
+            {
+                const G1Xyzz other = shfl_down_xyzz(acc, offset);
+                if (part < offset) acc = g1_add(acc, other);
+            }
+            if (part != 0 || i >= count) return;
+            G1Affine a = g1_to_affine(acc);
+            if (canonical)
+            {
+                a.x = from_mont(a.x);
+                a.y = from_mont(a.y);
+            }
+            store_affine(out + i, a);
+        }
+
         // Sum over the 32 byte-windows of every scalar: lane-split for chain-bound batch sizes.
         void launch_fixed_base_mul(gzk_ctx* ctx, const G1Affine* table, const ColRef& s, size_t count, G1Xyzz* xyzz)
         {
@@ -348,12 +385,21 @@ extern "C"
         ColRef s;
         s.ptr = scalars->dptr;
         s.kind = scalars->kind;
+        if (count <= kFusedAffineLimit)
         {
-            LaunchScope scope(ctx, "g1_fixed_base_mul");
-            launch_fixed_base_mul(ctx, table, s, count, xyzz);
+            LaunchScope scope(ctx, "g1_fixed_base_mul_affine");
+            fixed_base_mul_affine_kernel<<<static_cast<unsigned>((count * kLanes + 127) / 128), 128, 0, ctx->stream>>>(table, s, count, static_cast<G1Affine*>(out->dptr), 0);
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
         }
-        GZK_CUDA_TRY(ctx, cudaGetLastError());
-        if ((rc = launch_xyzz_to_affine(ctx, xyzz, count, z, static_cast<G1Affine*>(out->dptr), false)) != GZK_OK) return rc;
+        else
+        {
+            {
+                LaunchScope scope(ctx, "g1_fixed_base_mul");
+                launch_fixed_base_mul(ctx, table, s, count, xyzz);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            if ((rc = launch_xyzz_to_affine(ctx, xyzz, count, z, static_cast<G1Affine*>(out->dptr), false)) != GZK_OK) return rc;
+        }
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return GZK_OK;
     }
@@ -384,12 +430,21 @@ extern "C"
         ColRef s;
         s.ptr = d_scalars;
         s.kind = GZK_KIND_FR;
+        if (count <= kFusedAffineLimit)
         {
-            LaunchScope scope(ctx, "g1_fixed_base_mul");
-            launch_fixed_base_mul(ctx, table, s, count, xyzz);
+            LaunchScope scope(ctx, "g1_fixed_base_mul_affine");
+            fixed_base_mul_affine_kernel<<<static_cast<unsigned>((count * kLanes + 127) / 128), 128, 0, ctx->stream>>>(table, s, count, affine, 1);
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
         }
-        GZK_CUDA_TRY(ctx, cudaGetLastError());
-        if ((rc = launch_xyzz_to_affine(ctx, xyzz, count, z, affine, true)) != GZK_OK) return rc;
+        else
+        {
+            {
+                LaunchScope scope(ctx, "g1_fixed_base_mul");
+                launch_fixed_base_mul(ctx, table, s, count, xyzz);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            if ((rc = launch_xyzz_to_affine(ctx, xyzz, count, z, affine, true)) != GZK_OK) return rc;
+        }
         GZK_CUDA_TRY(ctx, cudaMemcpyAsync(points_out_host, affine, count * 96, cudaMemcpyDeviceToHost, ctx->stream));
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return GZK_OK;

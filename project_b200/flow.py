@@ -16,7 +16,7 @@ class FlowConfig(ctypes.Structure):
                 ("hidden_layer_count", ctypes.c_uint64), ("hidden_heads", ctypes.c_void_p), ("hidden_head_dim", ctypes.c_void_p),
                 ("output_heads", ctypes.c_uint64), ("range_bits", ctypes.c_uint32), ("seed", ctypes.c_uint64), ("features", ctypes.c_void_p),
                 ("edge_src", ctypes.c_void_p), ("edge_dst", ctypes.c_void_p), ("params", ctypes.c_void_p), ("param_count", ctypes.c_uint64),
-                ("generator", ctypes.c_void_p)]
+                ("generator", ctypes.c_void_p), ("compact_columns", ctypes.c_uint32)]
 
 
 class FlowError(RuntimeError):
@@ -26,7 +26,7 @@ class FlowError(RuntimeError):
 class Flow:
     """One prepared proof context (model, graph, features, key) on one backend."""
 
-    def __init__(self, lib, prefix, target, inputs, generator, seed=11, range_bits=12):
+    def __init__(self, lib, prefix, target, inputs, generator, seed=11, range_bits=12, compact_columns=False):
         self.lib, self.prefix = lib, prefix
         self._fn = lambda name: getattr(lib, prefix + name)
         self._fn("error").restype = ctypes.c_char_p
@@ -44,7 +44,8 @@ class Flow:
         k = self._keep
         cfg = FlowConfig(inputs["nodes"], inputs["feature_count"], inputs["class_count"], k["src"].size, len(inputs["hidden"]),
                          k["heads"].ctypes.data, k["dims"].ctypes.data, inputs["output_heads"], range_bits, seed, k["features"].ctypes.data,
-                         k["src"].ctypes.data, k["dst"].ctypes.data, k["params"].ctypes.data, k["params"].size, k["generator"].ctypes.data)
+                         k["src"].ctypes.data, k["dst"].ctypes.data, k["params"].ctypes.data, k["params"].size, k["generator"].ctypes.data,
+                         int(bool(compact_columns)))
         handle = ctypes.c_void_p()
         self._check(self._fn("create")(int(target), ctypes.byref(cfg), ctypes.byref(handle)))
         self.handle = handle

@@ -33,6 +33,7 @@ namespace gatzk_flow
         in.edge_src.assign(c.edge_src, c.edge_src + c.edge_count);
         in.edge_dst.assign(c.edge_dst, c.edge_dst + c.edge_count);
         in.range_bits = c.range_bits;
+        in.compact_columns = c.compact_columns != 0;
         in.seed = c.seed;
         std::memcpy(in.generator.data(), c.generator, 96);
         const double* p = c.params;

@@ -186,10 +186,18 @@ namespace
         }
         void running_sums_batch(const std::vector<ScanJob>& jobs) override
         {
-            std::vector<gzk_scan_job> raw_jobs(jobs.size());
-            for (std::size_t i = 0; i < jobs.size(); ++i)
+            // the batched entry point takes jobs of at most 2^20 rows; longer columns (the edge domain of the
+            // large configurations) fill the machine by themselves and go through the single-column calls
+            constexpr std::uint64_t kBatchRows = 1ull << 20;
+            std::vector<ScanJob> small_jobs, long_jobs;
+            for (const ScanJob& j : jobs)
+                ((j.op == ScanJob::kGroupPrefix ? j.domain_size : j.count) > kBatchRows ? long_jobs : small_jobs).push_back(j);
+            if (!long_jobs.empty()) Backend::running_sums_batch(long_jobs);
+            if (small_jobs.empty()) return;
+            std::vector<gzk_scan_job> raw_jobs(small_jobs.size());
+            for (std::size_t i = 0; i < small_jobs.size(); ++i)
             {
-                const ScanJob& j = jobs[i];
+                const ScanJob& j = small_jobs[i];
                 gzk_scan_job& r = raw_jobs[i];
                 r.op = j.op;  // the numbering of ScanJob::Op is that of GZK_SCAN_*
                 r.c0 = j.c0 ? raw(j.c0) : nullptr;

@@ -291,6 +291,11 @@ namespace gatzk_flow
         std::uint64_t seed = 11;
         G1 generator{};
         std::string dataset_name = "synthetic";
+        // Store the edge-domain columns as prefixes: the rows that carry data, plus for a running sum the
+        // constant it stays at afterwards (see ProverFlow::ColumnEntry).  Same polynomials, same proof;
+        // the only way the 169k-node configuration (edge domain 2^26, about 300 opened edge columns)
+        // fits the memory of one device.
+        bool compact_columns = false;
     };
 
     struct Commitment
@@ -378,7 +383,9 @@ namespace gatzk_flow
         {
             ColP col;
             std::string domain;
-            std::size_t length = 0;  // stored prefix; zero beyond it
+            std::size_t length = 0;  // stored prefix; beyond it the column is zero, or `tail` when const_tail
+            bool const_tail = false;
+            Fe tail{};               // the column's value on rows length .. domain size - 1 (its last stored element)
         };
         struct CommitItem
         {
@@ -389,6 +396,7 @@ namespace gatzk_flow
             std::size_t length = 0;   // columns: valid prefix; matrices: rows * cols
             std::size_t rows = 0, cols = 0;
             bool opened = true;       // matrices are commitment-only
+            bool const_tail = false;  // rows beyond `length` repeat the last stored element (a running sum after its last term)
         };
 
         // scalar helpers
@@ -462,6 +470,13 @@ namespace gatzk_flow
             it.col = col;
             it.domain = domain;
             it.length = length;
+            return it;
+        }
+        // a running sum stored up to (and including) its final value
+        CommitItem tail_item(const std::string& label, const ColP& col, const std::string& domain, std::size_t length)
+        {
+            CommitItem it = column_item(label, col, domain, length);
+            it.const_tail = compact_ && length < dom_.at(domain).size;
             return it;
         }
         CommitItem matrix_item(const std::string& label, const ColP& matrix, std::size_t rows, std::size_t cols)
@@ -538,6 +553,7 @@ namespace gatzk_flow
         struct Lookup
         {
             ColP table, query, multiplicity, acc;
+            std::size_t store = 0;  // stored rows of the four columns
         };
         Lookup build_pair_lookup(const ColP& table_x, const ColP& table_y, std::size_t table_size, std::int64_t x_min, std::size_t band,
                                  const ColP& left, const ColP& right, std::size_t valid, const Fe& eta, const Fe& beta, const ColP& q_table,
@@ -586,6 +602,26 @@ namespace gatzk_flow
         std::map<std::string, Domain> dom_;
         Fe tau_{};
         std::size_t n_nodes_ = 0, n_edges_ = 0;
+        bool compact_ = false;
+        std::size_t es_ = 0;      // stored rows of an edge-domain column: the domain size, or (compact) the data rows + 1
+        ColP ones_;               // a column of ones (compact): weight of a prefix = its evaluation
+        std::size_t ones_len_ = 0;
+        static std::size_t round64(std::size_t v) { return (v + 63) / 64 * 64; }
+        // stored rows of the columns of a lookup with `active` data rows
+        std::size_t lookup_store(std::size_t active) const
+        {
+            return compact_ ? std::min(dom_.at("edge").size, std::max(es_, round64(active + 1))) : dom_.at("edge").size;
+        }
+        ColP ones_col(std::size_t length)
+        {
+            if (ones_len_ < length)
+            {
+                const std::vector<std::uint32_t> host(length, 1u);
+                ones_ = upload_u32(host);
+                ones_len_ = length;
+            }
+            return ones_;
+        }
         GraphCols graph_;
         // public / static columns
         ColP ids_i64_, src_i64_, dst_i64_, src_u32_, dst_u32_, q_new_, q_edge_valid_, group_begin_, group_end_, features_q_;
@@ -693,6 +729,8 @@ namespace gatzk_flow
             next_power_of_two(std::max({n_nodes_, n_edges_, n_nodes_ * d_h, lrelu_table_size, elu_table_size, exp_table_size, range_size_}) + 2);
         add_domain("FH", fh_size);
         add_domain("edge", edge_size);
+        compact_ = in_.compact_columns;
+        es_ = compact_ ? std::min(edge_size, round64(std::max({n_nodes_, n_edges_, lrelu_table_size, elu_table_size, exp_table_size, range_size_}) + 1)) : edge_size;
         add_domain("in", next_power_of_two(max_in + 2));
         add_domain("d", next_power_of_two(d_h + 2));
         add_domain("cat", next_power_of_two(d_cat + 2));
@@ -900,7 +938,7 @@ namespace gatzk_flow
         // Scalars are laid out group by group (matrices first, then the columns of each (domain, stored
         // length) group), so that a group is ONE evaluation call; `slot` maps an item to its place and
         // the results are put back into label order on the host after the single read-back.
-        const ColP scalars = be_.alloc(kFr, items.size());
+        ColP scalars = be_.alloc(kFr, items.size());
         std::map<std::pair<std::string, std::size_t>, std::vector<std::size_t>> groups;
         std::vector<std::size_t> slot(items.size());
         std::size_t next = 0;
@@ -916,6 +954,19 @@ namespace gatzk_flow
                 groups[{items[i].domain, items[i].length}].push_back(i);
             }
         }
+        // prefix-stored running sums: the rows beyond the prefix hold the column's last stored value, so
+        // p(tau) = (sum over the prefix) + tail * (weight of the remaining rows), and that weight is
+        // 1 - (evaluation of a column of ones over the prefix) because the weights of a domain sum to 1
+        std::vector<std::size_t> tail_items;
+        std::map<std::pair<std::string, std::size_t>, std::size_t> ones_slot;
+        for (const auto& group : groups)
+            for (const auto i : group.second)
+                if (items[i].const_tail)
+                {
+                    tail_items.push_back(i);
+                    ones_slot.emplace(group.first, ones_slot.size());
+                }
+        const ColP ones_out = tail_items.empty() ? nullptr : be_.alloc(kFr, ones_slot.size());
         for (const auto& group : groups)
         {
             const Domain& d = dom_.at(group.first.first);
@@ -927,12 +978,28 @@ namespace gatzk_flow
             }
             be_.eval_device(cols, group.first.second, d.log2n, d.w_tau, {0}, scalars, next);
             next += cols.size();
+            const auto ones = ones_slot.find(group.first);
+            if (ones != ones_slot.end()) be_.eval_device({ones_col(group.first.second)}, group.first.second, d.log2n, d.w_tau, {0}, ones_out, ones->second);
+        }
+        std::vector<Fe> evals(items.size()), evals_by_slot(items.size());
+        std::vector<Fe> tails(items.size());
+        if (!tail_items.empty())
+        {
+            std::vector<Fe> ones_host(ones_slot.size());
+            be_.download(scalars, 0, items.size(), evals_by_slot.data());
+            be_.download(ones_out, 0, ones_host.size(), ones_host.data());
+            for (const auto i : tail_items)
+            {
+                be_.download(items[i].col, items[i].length - 1, 1, &tails[i]);
+                const Fe rest = sub(fe_u64(1), ones_host[ones_slot.at({items[i].domain, items[i].length})]);
+                evals_by_slot[slot[i]] = add(evals_by_slot[slot[i]], mul(tails[i], rest));
+            }
+            scalars = upload_fe(evals_by_slot, items.size());
         }
         const ColP points = be_.alloc(kG1, items.size());
         be_.g1_fixed_base(in_.generator, scalars, items.size(), points);
-        std::vector<Fe> evals(items.size()), evals_by_slot(items.size());
         std::vector<G1> pts(items.size()), pts_by_slot(items.size());
-        be_.download(scalars, 0, items.size(), evals_by_slot.data());
+        if (tail_items.empty()) be_.download(scalars, 0, items.size(), evals_by_slot.data());
         be_.download(points, 0, items.size(), pts_by_slot.data());
         for (std::size_t i = 0; i < items.size(); ++i)
         {
@@ -941,6 +1008,7 @@ namespace gatzk_flow
         }
         if (msm_commit_)
         {
+            if (compact_) throw std::runtime_error("flow: the MSM commitment check needs whole-domain columns (compact_columns off)");
             for (std::size_t i = 0; i < items.size(); ++i)
             {
                 ++msm_checked_;
@@ -954,7 +1022,7 @@ namespace gatzk_flow
             tau_eval_log_.push_back({items[i].label, evals[i]});
             if (!items[i].matrix)
             {
-                columns_[items[i].label] = ColumnEntry{items[i].col, items[i].domain, items[i].length};
+                columns_[items[i].label] = ColumnEntry{items[i].col, items[i].domain, items[i].length, items[i].const_tail, tails[i]};
                 opened_[items[i].domain].push_back(items[i].label);
             }
         }
@@ -1030,22 +1098,24 @@ namespace gatzk_flow
     {
         const Domain& e = dom_.at("edge");
         Lookup out;
+        const std::size_t store = lookup_store(std::max(table_size, valid));
+        out.store = store;
         if (table_y != nullptr)
         {
-            out.table = be_.alloc(kFrMont, e.size);
-            be_.linear_combination({table_x, table_y}, {fe_u64(1), eta}, table_size, e.size, out.table);
-            out.query = be_.alloc(kFrMont, e.size);
-            be_.linear_combination({left, right}, {fe_u64(1), eta}, valid, e.size, out.query);
+            out.table = be_.alloc(kFrMont, store);
+            be_.linear_combination({table_x, table_y}, {fe_u64(1), eta}, table_size, store, out.table);
+            out.query = be_.alloc(kFrMont, store);
+            be_.linear_combination({left, right}, {fe_u64(1), eta}, valid, store, out.query);
         }
         else
         {
             out.table = table_x;  // cached_single_lookup_table: the padded table itself
             out.query = left;     // build_single_lookup_artifacts copies the query values
         }
-        out.multiplicity = be_.alloc(kU32, e.size);
-        be_.lookup_multiplicity(left, table_y != nullptr ? right : nullptr, valid, x_min, band, table_y, table_size, e.size, out.multiplicity);
-        out.acc = be_.alloc(kFrMont, e.size);
-        queue_scan(ScanJob::kLogup, out.table, out.query, out.multiplicity, q_table, q_query, std::min(valid, e.size - 1), e.size, beta, out.acc);
+        out.multiplicity = be_.alloc(kU32, store);
+        be_.lookup_multiplicity(left, table_y != nullptr ? right : nullptr, valid, x_min, band, table_y, table_size, store, out.multiplicity);
+        out.acc = be_.alloc(kFrMont, store);
+        queue_scan(ScanJob::kLogup, out.table, out.query, out.multiplicity, q_table, q_query, std::min(valid, e.size - 1), store, beta, out.acc);
         return out;
     }
 
@@ -1055,17 +1125,16 @@ namespace gatzk_flow
                                                      const ColP& multiplicity, const Fe& beta)
     {
         const Domain& n = dom_.at("N");
-        const Domain& e = dom_.at("edge");
         const auto eta_powers = powers_host(eta, node_cols.size());
         Route out;
         out.table = be_.alloc(kFrMont, n.size);
         be_.linear_combination(node_cols, eta_powers, n_nodes_, n.size, out.table);
-        out.query = be_.alloc(kFrMont, e.size);
-        be_.linear_combination(edge_cols, eta_powers, n_edges_, e.size, out.query);
+        out.query = be_.alloc(kFrMont, es_);
+        be_.linear_combination(edge_cols, eta_powers, n_edges_, es_, out.query);
         out.node_acc = be_.alloc(kFrMont, n.size);
         queue_scan(ScanJob::kRouteNode, out.table, multiplicity, nullptr, nullptr, nullptr, n_nodes_, n.size, beta, out.node_acc);
-        out.edge_acc = be_.alloc(kFrMont, e.size);
-        queue_scan(ScanJob::kRouteEdge, out.query, nullptr, nullptr, nullptr, nullptr, n_edges_, e.size, beta, out.edge_acc);
+        out.edge_acc = be_.alloc(kFrMont, es_);
+        queue_scan(ScanJob::kRouteEdge, out.query, nullptr, nullptr, nullptr, nullptr, n_edges_, es_, beta, out.edge_acc);
         return out;
     }
 
@@ -1074,7 +1143,7 @@ namespace gatzk_flow
     inline ProverFlow::HeadWitness ProverFlow::run_head(const ColP& layer_input, std::size_t input_dim, std::size_t width, const HeadParams& p,
                                                         bool output_head, const std::vector<double>* host_input, std::vector<double>* host_output)
     {
-        const std::size_t edge_size = dom_.at("edge").size;
+        const std::size_t edge_size = es_;
         HeadTraceCols tr;
         auto f64 = [&](std::size_t n) { return be_.alloc(kF64, std::max<std::size_t>(1, n)); };
         tr.H_prime = f64(n_nodes_ * width);
@@ -1181,7 +1250,6 @@ namespace gatzk_flow
         (void)local_head;
         const auto& layer = in_.hidden_layers[layer_index];
         const std::size_t d = layer.head_dim;
-        const Domain& e = dom_.at("edge");
         const Domain& n = dom_.at("N");
         const std::string h = std::to_string(head_index);
         const std::string prefix = "P_h" + h + "_";
@@ -1190,10 +1258,10 @@ namespace gatzk_flow
         commit_batch({matrix_item(prefix + "H_prime", w.h_prime, n_nodes_, d), column_item(prefix + "E_src", w.e_src, "N", n_nodes_),
                       column_item(prefix + "E_dst", w.e_dst, "N", n_nodes_), column_item(prefix + "S", w.s, "edge", n_edges_),
                       column_item(prefix + "Z", w.z, "edge", n_edges_), column_item(prefix + "M", w.m, "N", n_nodes_),
-                      column_item(prefix + "M_edge", w.m_edge, "edge", e.size), column_item(prefix + "Delta", w.delta, "edge", n_edges_),
+                      column_item(prefix + "M_edge", w.m_edge, "edge", es_), column_item(prefix + "Delta", w.delta, "edge", n_edges_),
                       column_item(prefix + "U", w.u, "edge", n_edges_), column_item(prefix + "Sum", w.sum, "N", n_nodes_),
-                      column_item(prefix + "Sum_edge", w.sum_edge, "edge", e.size), column_item(prefix + "inv", w.inv, "N", n_nodes_),
-                      column_item(prefix + "inv_edge", w.inv_edge, "edge", e.size), column_item(prefix + "alpha", w.alpha, "edge", n_edges_),
+                      column_item(prefix + "Sum_edge", w.sum_edge, "edge", es_), column_item(prefix + "inv", w.inv, "N", n_nodes_),
+                      column_item(prefix + "inv_edge", w.inv_edge, "edge", es_), column_item(prefix + "alpha", w.alpha, "edge", n_edges_),
                       matrix_item(prefix + "H_agg_pre", w.h_agg_pre, n_nodes_, d), matrix_item(prefix + "H_agg", w.h_agg, n_nodes_, d)});
 
         absorb_dyn(t, input_label);
@@ -1219,8 +1287,8 @@ namespace gatzk_flow
             return out;
         };
         auto to_edges = [&](const ColP& node_values, const ColP& index) {
-            const ColP out = be_.alloc(kFrMont, e.size);
-            be_.gather(node_values, n_nodes_, index, n_edges_, e.size, out);
+            const ColP out = be_.alloc(kFrMont, es_);
+            be_.gather(node_values, n_nodes_, index, n_edges_, es_, out);
             return out;
         };
         const ColP h_star = compress(w.h_prime), h_agg_pre_star = compress(w.h_agg_pre), h_agg_star = compress(w.h_agg);
@@ -1277,23 +1345,23 @@ namespace gatzk_flow
         const std::size_t lrelu_size = lrelu_bound_ * 2 + 1;
         const Lookup lrelu = build_pair_lookup(t_l_x_, t_l_y_, lrelu_size, -static_cast<std::int64_t>(lrelu_bound_), 1, w.s, w.z, n_edges_, eta_l,
                                                beta_l, q_tbl_l_, q_qry_l_);
-        const ColP s_max = be_.alloc(kU32, e.size);
-        be_.first_zero_marker(w.delta, group_begin_, group_end_, groups_, e.size, s_max);
-        const ColP c_max = be_.alloc(kFrMont, e.size);
-        queue_scan(ScanJob::kGroupPrefix, s_max, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, c_max);
+        const ColP s_max = be_.alloc(kU32, es_);
+        be_.first_zero_marker(w.delta, group_begin_, group_end_, groups_, es_, s_max);
+        const ColP c_max = be_.alloc(kFrMont, es_);
+        queue_scan(ScanJob::kGroupPrefix, s_max, q_new_, nullptr, nullptr, nullptr, es_, es_, Fe{}, c_max);
         const Lookup range = build_pair_lookup(t_range_, nullptr, range_size_, 0, 1, w.delta, nullptr, n_edges_, fe_u64(0), beta_r, q_tbl_r_, q_qry_r_);
         const Lookup exp_l = build_pair_lookup(t_exp_x_, t_exp_y_, range_size_ * 5, 0, 5, w.delta, w.u, n_edges_, eta_exp, beta_exp, q_tbl_exp_, q_qry_exp_);
 
         const Fe lambda_psq = challenge(t, "lambda_psq_h" + h);
-        const ColP widehat = be_.alloc(kFrMont, e.size);
-        be_.mul_columns(w.alpha, h_star_edge, n_edges_, e.size, widehat);
-        const ColP w_psq = be_.alloc(kFrMont, e.size);
-        be_.linear_combination({w.u, widehat}, {fe_u64(1), lambda_psq}, e.size, e.size, w_psq);  // build_weighted_sum runs over the whole column
+        const ColP widehat = be_.alloc(kFrMont, es_);
+        be_.mul_columns(w.alpha, h_star_edge, n_edges_, es_, widehat);
+        const ColP w_psq = be_.alloc(kFrMont, es_);
+        be_.linear_combination({w.u, widehat}, {fe_u64(1), lambda_psq}, es_, es_, w_psq);  // build_weighted_sum runs over the whole column
         const ColP t_psq = be_.alloc(kFrMont, n_nodes_);
         be_.linear_combination({w.sum, h_agg_pre_star}, {fe_u64(1), lambda_psq}, n_nodes_, n_nodes_, t_psq);
         const ColP t_psq_edge = to_edges(t_psq, dst_u32_);
-        const ColP psq = be_.alloc(kFrMont, e.size);
-        queue_scan(ScanJob::kGroupPrefix, w_psq, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, psq);
+        const ColP psq = be_.alloc(kFrMont, es_);
+        queue_scan(ScanJob::kGroupPrefix, w_psq, q_new_, nullptr, nullptr, nullptr, es_, es_, Fe{}, psq);
         // the source route packs ids + eta * value with powers(eta, 2) = {1, eta} (trace.cpp:2737-2772)
         const Route src_route = build_route({ids_i64_, w.e_src}, {src_i64_, h_star_edge}, eta_src, src_multiplicity_, beta_src);
 
@@ -1304,23 +1372,23 @@ namespace gatzk_flow
                       column_item(prefix + "a_dst", dst_b.a, "d", dd), column_item(prefix + "b_dst", dst_b.b, "d", dd),
                       column_item(prefix + "Acc_dst", dst_b.acc, "d", dd), column_item(prefix + "a_star", star_b.a, "d", dd),
                       column_item(prefix + "b_star", star_b.b, "d", dd), column_item(prefix + "Acc_star", star_b.acc, "d", dd),
-                      column_item(prefix + "E_src_edge", w.e_src_edge, "edge", e.size), column_item(prefix + "E_dst_edge", w.e_dst_edge, "edge", e.size),
-                      column_item(prefix + "H_src_star_edge", h_star_edge, "edge", e.size), column_item(prefix + "Table_src", src_route.table, "N", n.size),
-                      column_item(prefix + "Query_src", src_route.query, "edge", e.size), column_item(prefix + "m_src", src_multiplicity_, "N", n.size),
-                      column_item(prefix + "R_src_node", src_route.node_acc, "N", n.size), column_item(prefix + "R_src", src_route.edge_acc, "edge", e.size),
-                      column_item(prefix + "Table_L", lrelu.table, "edge", e.size), column_item(prefix + "Query_L", lrelu.query, "edge", e.size),
-                      column_item(prefix + "m_L", lrelu.multiplicity, "edge", e.size), column_item(prefix + "R_L", lrelu.acc, "edge", e.size),
-                      column_item(prefix + "s_max", s_max, "edge", e.size), column_item(prefix + "C_max", c_max, "edge", e.size),
-                      column_item(prefix + "Table_R", range.table, "edge", e.size), column_item(prefix + "Query_R", range.query, "edge", e.size),
-                      column_item(prefix + "m_R", range.multiplicity, "edge", e.size), column_item(prefix + "R_R", range.acc, "edge", e.size),
-                      column_item(prefix + "Table_exp", exp_l.table, "edge", e.size), column_item(prefix + "Query_exp", exp_l.query, "edge", e.size),
-                      column_item(prefix + "m_exp", exp_l.multiplicity, "edge", e.size), column_item(prefix + "R_exp", exp_l.acc, "edge", e.size),
+                      column_item(prefix + "E_src_edge", w.e_src_edge, "edge", es_), column_item(prefix + "E_dst_edge", w.e_dst_edge, "edge", es_),
+                      column_item(prefix + "H_src_star_edge", h_star_edge, "edge", es_), column_item(prefix + "Table_src", src_route.table, "N", n.size),
+                      column_item(prefix + "Query_src", src_route.query, "edge", es_), column_item(prefix + "m_src", src_multiplicity_, "N", n.size),
+                      column_item(prefix + "R_src_node", src_route.node_acc, "N", n.size), tail_item(prefix + "R_src", src_route.edge_acc, "edge", es_),
+                      column_item(prefix + "Table_L", lrelu.table, "edge", es_), column_item(prefix + "Query_L", lrelu.query, "edge", es_),
+                      column_item(prefix + "m_L", lrelu.multiplicity, "edge", es_), tail_item(prefix + "R_L", lrelu.acc, "edge", es_),
+                      column_item(prefix + "s_max", s_max, "edge", es_), tail_item(prefix + "C_max", c_max, "edge", es_),
+                      column_item(prefix + "Table_R", range.table, "edge", es_), column_item(prefix + "Query_R", range.query, "edge", es_),
+                      column_item(prefix + "m_R", range.multiplicity, "edge", es_), tail_item(prefix + "R_R", range.acc, "edge", es_),
+                      column_item(prefix + "Table_exp", exp_l.table, "edge", es_), column_item(prefix + "Query_exp", exp_l.query, "edge", es_),
+                      column_item(prefix + "m_exp", exp_l.multiplicity, "edge", es_), tail_item(prefix + "R_exp", exp_l.acc, "edge", es_),
                       column_item(prefix + "H_agg_pre_star", h_agg_pre_star, "N", n_nodes_),
-                      column_item(prefix + "H_agg_pre_star_edge", h_agg_pre_star_edge, "edge", e.size),
-                      column_item(prefix + "widehat_v_pre_star", widehat, "edge", e.size), column_item(prefix + "w_psq", w_psq, "edge", e.size),
-                      column_item(prefix + "T_psq", t_psq, "N", n_nodes_), column_item(prefix + "T_psq_edge", t_psq_edge, "edge", e.size),
-                      column_item(prefix + "PSQ", psq, "edge", e.size), column_item(prefix + "H_agg_star", h_agg_star, "N", n_nodes_),
-                      column_item(prefix + "H_agg_star_edge", h_agg_star_edge, "edge", e.size)});
+                      column_item(prefix + "H_agg_pre_star_edge", h_agg_pre_star_edge, "edge", es_),
+                      column_item(prefix + "widehat_v_pre_star", widehat, "edge", es_), column_item(prefix + "w_psq", w_psq, "edge", es_),
+                      column_item(prefix + "T_psq", t_psq, "N", n_nodes_), column_item(prefix + "T_psq_edge", t_psq_edge, "edge", es_),
+                      tail_item(prefix + "PSQ", psq, "edge", es_), column_item(prefix + "H_agg_star", h_agg_star, "N", n_nodes_),
+                      column_item(prefix + "H_agg_star_edge", h_agg_star_edge, "edge", es_)});
 
         absorb_dyn(t, prefix + "T_psq");
         absorb_dyn(t, prefix + "T_psq_edge");
@@ -1358,14 +1426,14 @@ namespace gatzk_flow
                       column_item(prefix + "Acc_agg_pre", agg_pre_b.acc, "d", dd), column_item(prefix + "a_agg", agg_b.a, "d", dd),
                       column_item(prefix + "b_agg", agg_b.b, "d", dd), column_item(prefix + "Acc_agg", agg_b.acc, "d", dd),
                       column_item(prefix + "H_agg_pre_flat", w.h_agg_pre, "edge", flat), column_item(prefix + "H_agg_flat", w.h_agg, "edge", flat),
-                      column_item(prefix + "Table_ELU", elu.table, "edge", e.size), column_item(prefix + "Query_ELU", elu.query, "edge", e.size),
-                      column_item(prefix + "m_ELU", elu.multiplicity, "edge", e.size), column_item(prefix + "R_ELU", elu.acc, "edge", e.size),
-                      column_item(prefix + "Table_t", t_route.table, "N", n.size), column_item(prefix + "Query_t", t_route.query, "edge", e.size),
+                      column_item(prefix + "Table_ELU", elu.table, "edge", elu.store), column_item(prefix + "Query_ELU", elu.query, "edge", elu.store),
+                      column_item(prefix + "m_ELU", elu.multiplicity, "edge", elu.store), tail_item(prefix + "R_ELU", elu.acc, "edge", elu.store),
+                      column_item(prefix + "Table_t", t_route.table, "N", n.size), column_item(prefix + "Query_t", t_route.query, "edge", es_),
                       column_item(prefix + "m_t", dst_multiplicity_, "N", n.size), column_item(prefix + "R_t_node", t_route.node_acc, "N", n.size),
-                      column_item(prefix + "R_t", t_route.edge_acc, "edge", e.size)});
-        commit_batch({column_item(prefix + "Table_dst", dst_route.table, "N", n.size), column_item(prefix + "Query_dst", dst_route.query, "edge", e.size),
+                      tail_item(prefix + "R_t", t_route.edge_acc, "edge", es_)});
+        commit_batch({column_item(prefix + "Table_dst", dst_route.table, "N", n.size), column_item(prefix + "Query_dst", dst_route.query, "edge", es_),
                       column_item(prefix + "m_dst", dst_multiplicity_, "N", n.size), column_item(prefix + "R_dst_node", dst_route.node_acc, "N", n.size),
-                      column_item(prefix + "R_dst", dst_route.edge_acc, "edge", e.size)});
+                      tail_item(prefix + "R_dst", dst_route.edge_acc, "edge", es_)});
 
         // route.total = node_acc[real_node_count] (build_route_trace, trace.cpp:1792)
         pending_totals_.push_back({"S_src_h" + h, src_route.node_acc, n_nodes_});

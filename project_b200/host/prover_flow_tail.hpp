@@ -42,7 +42,6 @@ namespace gatzk_flow
     {
         const bool legacy = in_.output_layer.heads.size() == 1;
         const std::size_t c = in_.class_count;
-        const Domain& e = dom_.at("edge");
         const Domain& n = dom_.at("N");
         const std::string k = std::to_string(head_index);
         const std::string base = legacy ? "P_out" : "P_out" + k, prefix = base + "_";
@@ -68,10 +67,10 @@ namespace gatzk_flow
         commit_batch({matrix_item(prefix + "Y_prime", y_prime, n_nodes_, c), column_item(prefix + "E_src", w.e_src, "N", n_nodes_),
                       column_item(prefix + "E_dst", w.e_dst, "N", n_nodes_), column_item(prefix + "S", w.s, "edge", n_edges_),
                       column_item(prefix + "Z", w.z, "edge", n_edges_), column_item(prefix + "M", w.m, "N", n_nodes_),
-                      column_item(prefix + "M_edge", w.m_edge, "edge", e.size), column_item(prefix + "Delta", w.delta, "edge", n_edges_),
+                      column_item(prefix + "M_edge", w.m_edge, "edge", es_), column_item(prefix + "Delta", w.delta, "edge", n_edges_),
                       column_item(prefix + "U", w.u, "edge", n_edges_), column_item(prefix + "Sum", w.sum, "N", n_nodes_),
-                      column_item(prefix + "Sum_edge", w.sum_edge, "edge", e.size), column_item(prefix + "inv", w.inv, "N", n_nodes_),
-                      column_item(prefix + "inv_edge", w.inv_edge, "edge", e.size), column_item(prefix + "alpha", w.alpha, "edge", n_edges_),
+                      column_item(prefix + "Sum_edge", w.sum_edge, "edge", es_), column_item(prefix + "inv", w.inv, "N", n_nodes_),
+                      column_item(prefix + "inv_edge", w.inv_edge, "edge", es_), column_item(prefix + "alpha", w.alpha, "edge", n_edges_),
                       matrix_item(y_lin_label, y_lin, n_nodes_, c), matrix_item(y_label, y, n_nodes_, c)});
 
         absorb_dyn(t, "P_H_cat");
@@ -116,8 +115,8 @@ namespace gatzk_flow
             return out;
         };
         auto to_edges = [&](const ColP& node_values, const ColP& index) {
-            const ColP out = be_.alloc(kFrMont, e.size);
-            be_.gather(node_values, n_nodes_, index, n_edges_, e.size, out);
+            const ColP out = be_.alloc(kFrMont, es_);
+            be_.gather(node_values, n_nodes_, index, n_edges_, es_, out);
             return out;
         };
         const ColP y_prime_star = compress(y_prime), y_star = compress(y_lin);
@@ -129,40 +128,40 @@ namespace gatzk_flow
         const std::size_t lrelu_size = lrelu_bound_ * 2 + 1;
         const Lookup lrelu = build_pair_lookup(t_l_x_, t_l_y_, lrelu_size, -static_cast<std::int64_t>(lrelu_bound_), 1, w.s, w.z, n_edges_, eta_l,
                                                beta_l, q_tbl_l_, q_qry_l_);
-        const ColP s_max = be_.alloc(kU32, e.size);
-        be_.first_zero_marker(w.delta, group_begin_, group_end_, groups_, e.size, s_max);
-        const ColP c_max = be_.alloc(kFrMont, e.size);
-        queue_scan(ScanJob::kGroupPrefix, s_max, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, c_max);
+        const ColP s_max = be_.alloc(kU32, es_);
+        be_.first_zero_marker(w.delta, group_begin_, group_end_, groups_, es_, s_max);
+        const ColP c_max = be_.alloc(kFrMont, es_);
+        queue_scan(ScanJob::kGroupPrefix, s_max, q_new_, nullptr, nullptr, nullptr, es_, es_, Fe{}, c_max);
         const Lookup range = build_pair_lookup(t_range_, nullptr, range_size_, 0, 1, w.delta, nullptr, n_edges_, fe_u64(0), beta_r, q_tbl_r_, q_qry_r_);
         const Lookup exp_l = build_pair_lookup(t_exp_x_, t_exp_y_, range_size_ * 5, 0, 5, w.delta, w.u, n_edges_, eta_exp, beta_exp, q_tbl_exp_, q_qry_exp_);
 
         const Fe lambda = challenge(t, cname("lambda_out"));
-        const ColP widehat = be_.alloc(kFrMont, e.size);
-        be_.mul_columns(w.alpha, y_prime_star_edge, n_edges_, e.size, widehat);
-        const ColP w_out = be_.alloc(kFrMont, e.size);
-        be_.linear_combination({w.u, widehat}, {fe_u64(1), lambda}, e.size, e.size, w_out);
+        const ColP widehat = be_.alloc(kFrMont, es_);
+        be_.mul_columns(w.alpha, y_prime_star_edge, n_edges_, es_, widehat);
+        const ColP w_out = be_.alloc(kFrMont, es_);
+        be_.linear_combination({w.u, widehat}, {fe_u64(1), lambda}, es_, es_, w_out);
         const ColP t_out = be_.alloc(kFrMont, n_nodes_);
         be_.linear_combination({w.sum, y_star}, {fe_u64(1), lambda}, n_nodes_, n_nodes_, t_out);
         const ColP t_out_edge = to_edges(t_out, dst_u32_);
-        const ColP psq = be_.alloc(kFrMont, e.size);
-        queue_scan(ScanJob::kGroupPrefix, w_out, q_new_, nullptr, nullptr, nullptr, e.size, e.size, Fe{}, psq);
+        const ColP psq = be_.alloc(kFrMont, es_);
+        queue_scan(ScanJob::kGroupPrefix, w_out, q_new_, nullptr, nullptr, nullptr, es_, es_, Fe{}, psq);
 
-        commit_batch({column_item(prefix + "E_src_edge", w.e_src_edge, "edge", e.size), column_item(prefix + "E_dst_edge", w.e_dst_edge, "edge", e.size),
+        commit_batch({column_item(prefix + "E_src_edge", w.e_src_edge, "edge", es_), column_item(prefix + "E_dst_edge", w.e_dst_edge, "edge", es_),
                       column_item(prefix + "Y_prime_star", y_prime_star, "N", n_nodes_),
-                      column_item(prefix + "Y_prime_star_edge", y_prime_star_edge, "edge", e.size),
-                      column_item(prefix + "Table_src", src_route.table, "N", n.size), column_item(prefix + "Query_src", src_route.query, "edge", e.size),
+                      column_item(prefix + "Y_prime_star_edge", y_prime_star_edge, "edge", es_),
+                      column_item(prefix + "Table_src", src_route.table, "N", n.size), column_item(prefix + "Query_src", src_route.query, "edge", es_),
                       column_item(prefix + "m_src", src_multiplicity_, "N", n.size), column_item(prefix + "R_src_node", src_route.node_acc, "N", n.size),
-                      column_item(prefix + "R_src", src_route.edge_acc, "edge", e.size), column_item(prefix + "Table_L", lrelu.table, "edge", e.size),
-                      column_item(prefix + "Query_L", lrelu.query, "edge", e.size), column_item(prefix + "m_L", lrelu.multiplicity, "edge", e.size),
-                      column_item(prefix + "R_L", lrelu.acc, "edge", e.size), column_item(prefix + "s_max", s_max, "edge", e.size),
-                      column_item(prefix + "C_max", c_max, "edge", e.size), column_item(prefix + "Table_R", range.table, "edge", e.size),
-                      column_item(prefix + "Query_R", range.query, "edge", e.size), column_item(prefix + "m_R", range.multiplicity, "edge", e.size),
-                      column_item(prefix + "R_R", range.acc, "edge", e.size), column_item(prefix + "Table_exp", exp_l.table, "edge", e.size),
-                      column_item(prefix + "Query_exp", exp_l.query, "edge", e.size), column_item(prefix + "m_exp", exp_l.multiplicity, "edge", e.size),
-                      column_item(prefix + "R_exp", exp_l.acc, "edge", e.size), column_item(prefix + "widehat_y_star", widehat, "edge", e.size),
-                      column_item(prefix + "w", w_out, "edge", e.size), column_item(prefix + "T", t_out, "N", n_nodes_),
-                      column_item(prefix + "T_edge", t_out_edge, "edge", e.size), column_item(prefix + "PSQ", psq, "edge", e.size),
-                      column_item(prefix + "Y_star", y_star, "N", n_nodes_), column_item(prefix + "Y_star_edge", y_star_edge, "edge", e.size)});
+                      tail_item(prefix + "R_src", src_route.edge_acc, "edge", es_), column_item(prefix + "Table_L", lrelu.table, "edge", es_),
+                      column_item(prefix + "Query_L", lrelu.query, "edge", es_), column_item(prefix + "m_L", lrelu.multiplicity, "edge", es_),
+                      tail_item(prefix + "R_L", lrelu.acc, "edge", es_), column_item(prefix + "s_max", s_max, "edge", es_),
+                      tail_item(prefix + "C_max", c_max, "edge", es_), column_item(prefix + "Table_R", range.table, "edge", es_),
+                      column_item(prefix + "Query_R", range.query, "edge", es_), column_item(prefix + "m_R", range.multiplicity, "edge", es_),
+                      tail_item(prefix + "R_R", range.acc, "edge", es_), column_item(prefix + "Table_exp", exp_l.table, "edge", es_),
+                      column_item(prefix + "Query_exp", exp_l.query, "edge", es_), column_item(prefix + "m_exp", exp_l.multiplicity, "edge", es_),
+                      tail_item(prefix + "R_exp", exp_l.acc, "edge", es_), column_item(prefix + "widehat_y_star", widehat, "edge", es_),
+                      column_item(prefix + "w", w_out, "edge", es_), column_item(prefix + "T", t_out, "N", n_nodes_),
+                      column_item(prefix + "T_edge", t_out_edge, "edge", es_), tail_item(prefix + "PSQ", psq, "edge", es_),
+                      column_item(prefix + "Y_star", y_star, "N", n_nodes_), column_item(prefix + "Y_star_edge", y_star_edge, "edge", es_)});
 
         absorb_dyn(t, prefix + "T");
         absorb_dyn(t, prefix + "T_edge");
@@ -188,17 +187,17 @@ namespace gatzk_flow
         const Route dst_route = build_route({ids_i64_, w.e_dst, w.m, w.sum, w.inv, y_star},
                                             {dst_i64_, w.e_dst_edge, w.m_edge, w.sum_edge, w.inv_edge, y_star_edge}, eta_dst, dst_multiplicity_, beta_dst);
         const std::size_t dc = cd.size, dcat = dom_.at("cat").size;
-        commit_batch({column_item(prefix + "Table_t", t_route.table, "N", n.size), column_item(prefix + "Query_t", t_route.query, "edge", e.size),
+        commit_batch({column_item(prefix + "Table_t", t_route.table, "N", n.size), column_item(prefix + "Query_t", t_route.query, "edge", es_),
                       column_item(prefix + "m_t", dst_multiplicity_, "N", n.size), column_item(prefix + "R_t_node", t_route.node_acc, "N", n.size),
-                      column_item(prefix + "R_t", t_route.edge_acc, "edge", e.size), column_item(prefix + "a_proj", proj.a, "cat", dcat),
+                      tail_item(prefix + "R_t", t_route.edge_acc, "edge", es_), column_item(prefix + "a_proj", proj.a, "cat", dcat),
                       column_item(prefix + "b_proj", proj.b, "cat", dcat), column_item(prefix + "Acc_proj", proj.acc, "cat", dcat),
                       column_item(prefix + "a_src", src_b.a, "C", dc), column_item(prefix + "b_src", src_b.b, "C", dc),
                       column_item(prefix + "Acc_src", src_b.acc, "C", dc), column_item(prefix + "a_dst", dst_b.a, "C", dc),
                       column_item(prefix + "b_dst", dst_b.b, "C", dc), column_item(prefix + "Acc_dst", dst_b.acc, "C", dc),
                       column_item(prefix + "a_y", y_b.a, "C", dc), column_item(prefix + "b_y", y_b.b, "C", dc),
                       column_item(prefix + "Acc_y", y_b.acc, "C", dc), column_item(prefix + "Table_dst", dst_route.table, "N", n.size),
-                      column_item(prefix + "Query_dst", dst_route.query, "edge", e.size), column_item(prefix + "m_dst", dst_multiplicity_, "N", n.size),
-                      column_item(prefix + "R_dst_node", dst_route.node_acc, "N", n.size), column_item(prefix + "R_dst", dst_route.edge_acc, "edge", e.size)});
+                      column_item(prefix + "Query_dst", dst_route.query, "edge", es_), column_item(prefix + "m_dst", dst_multiplicity_, "N", n.size),
+                      column_item(prefix + "R_dst_node", dst_route.node_acc, "N", n.size), tail_item(prefix + "R_dst", dst_route.edge_acc, "edge", es_)});
 
         const std::string s_suffix = legacy ? "_out" : "_out" + k;
         pending_totals_.push_back({"S_src" + s_suffix, src_route.node_acc, n_nodes_});
@@ -488,25 +487,65 @@ namespace gatzk_flow
             }
             const ColP result = be_.alloc(kFr, 2 * labels.size());
             std::size_t offset = 0;
-            std::vector<std::pair<std::size_t, const std::vector<std::string>*>> placed;
+            struct Placed
+            {
+                std::size_t offset;
+                const std::vector<std::string>* labels;
+                std::size_t ones;  // slot pair of the ones column of this length, or npos
+            };
+            constexpr std::size_t npos = static_cast<std::size_t>(-1);
+            std::vector<Placed> placed;
+            std::size_t tail_groups = 0;
+            for (const auto& group : by_length)
+                for (const auto& label : group.second)
+                {
+                    const auto c = columns_.find(label);
+                    if (c != columns_.end() && c->second.const_tail)
+                    {
+                        ++tail_groups;
+                        break;
+                    }
+                }
+            const ColP ones_out = tail_groups == 0 ? nullptr : be_.alloc(kFr, 2 * tail_groups);
+            std::size_t ones_next = 0;
             for (const auto& group : by_length)
             {
                 std::vector<ColP> cols;
+                bool has_tail = false;
                 for (const auto& label : group.second)
                 {
                     const auto c = columns_.find(label);
                     cols.push_back(c != columns_.end() ? c->second.col : static_columns_.at(label).col);
+                    has_tail = has_tail || (c != columns_.end() && c->second.const_tail);
                 }
                 be_.eval_device(cols, group.first, d.log2n, weights, {0, 1}, result, offset);
-                placed.push_back({offset, &group.second});
+                std::size_t ones = npos;
+                if (has_tail)
+                {
+                    ones = ones_next;
+                    be_.eval_device({ones_col(group.first)}, group.first, d.log2n, weights, {0, 1}, ones_out, ones_next);
+                    ones_next += 2;
+                }
+                placed.push_back({offset, &group.second, ones});
                 offset += 2 * cols.size();
             }
-            std::vector<Fe> host(2 * labels.size());
+            std::vector<Fe> host(2 * labels.size()), ones_host(2 * tail_groups);
             be_.download(result, 0, host.size(), host.data());
+            if (tail_groups != 0) be_.download(ones_out, 0, ones_host.size(), ones_host.data());
             for (const auto& p : placed)
             {
-                const std::size_t k = p.second->size();
-                for (std::size_t i = 0; i < k; ++i) out[(*p.second)[i]] = {host[p.first + i], host[p.first + k + i]};
+                const std::size_t k = p.labels->size();
+                for (std::size_t i = 0; i < k; ++i)
+                {
+                    std::array<Fe, 2> value = {host[p.offset + i], host[p.offset + k + i]};
+                    const auto c = columns_.find((*p.labels)[i]);
+                    if (c != columns_.end() && c->second.const_tail)
+                    {
+                        // rows beyond the stored prefix hold the running sum's final value (see commit_batch)
+                        for (int r = 0; r < 2; ++r) value[r] = add(value[r], mul(c->second.tail, sub(fe_u64(1), ones_host[p.ones + r])));
+                    }
+                    out[(*p.labels)[i]] = value;
+                }
             }
         };
 

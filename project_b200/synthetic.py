@@ -9,9 +9,10 @@ shapes (node / edge / feature counts, head layout), not their values."""
 import numpy as np
 
 
-def make_graph(rng, nodes, directed_edges, power_law=False):
-    """(src, dst) uint32 arrays: `directed_edges` random edges, deduplicated, plus a self loop per
-    node, stably sorted by destination."""
+def make_graph(rng, nodes, directed_edges, power_law=False, symmetrize=False):
+    """(src, dst) uint32 arrays: `directed_edges` random edges (with their reverses when `symmetrize`,
+    the loader's symmetrize_edges switch), deduplicated, plus a self loop per node, stably sorted by
+    destination."""
     if power_law:
         weights = (np.arange(1, nodes + 1, dtype=np.float64)) ** (-1.0 / 1.5)
         weights /= weights.sum()
@@ -20,16 +21,21 @@ def make_graph(rng, nodes, directed_edges, power_law=False):
     else:
         src = rng.integers(0, nodes, size=directed_edges)
         dst = rng.integers(0, nodes, size=directed_edges)
+    if symmetrize:
+        src, dst = np.concatenate([src, dst]), np.concatenate([dst, src])
     keep = src != dst
-    pairs = np.unique(np.stack([src[keep], dst[keep]], axis=1), axis=0)
-    src = np.concatenate([pairs[:, 0], np.arange(nodes)])
-    dst = np.concatenate([pairs[:, 1], np.arange(nodes)])
+    keys = np.unique(src[keep].astype(np.int64) * nodes + dst[keep])  # ordered by (src, dst)
+    src = np.concatenate([keys // nodes, np.arange(nodes)])
+    dst = np.concatenate([keys % nodes, np.arange(nodes)])
     order = np.argsort(dst, kind="stable")
     return src[order].astype(np.uint32), dst[order].astype(np.uint32)
 
 
 def make_features(rng, nodes, width, density=0.1, kind="exp"):
-    """Row-normalised non-negative features (loader.cpp:18-34 normalises rows to sum 1)."""
+    """Row-normalised non-negative features (loader.cpp:18-34 normalises rows to sum 1); kind "gauss":
+    dense N(0,1) values, unnormalised."""
+    if kind == "gauss":
+        return rng.standard_normal((nodes, width))
     mask = rng.random((nodes, width)) < density
     values = rng.exponential(1.0, size=(nodes, width)) if kind == "exp" else np.ones((nodes, width))
     feats = values * mask
@@ -62,11 +68,12 @@ def make_params(rng, feature_count, hidden, output_heads, class_count):
     return np.concatenate(blocks).astype(np.float64)
 
 
-def make_inputs(seed, nodes, directed_edges, feature_count, hidden, output_heads, class_count, density=0.1, power_law=False):
+def make_inputs(seed, nodes, directed_edges, feature_count, hidden, output_heads, class_count, density=0.1, power_law=False, symmetrize=False,
+                feature_kind="exp"):
     rng = np.random.default_rng(seed)
-    src, dst = make_graph(rng, nodes, directed_edges, power_law)
+    src, dst = make_graph(rng, nodes, directed_edges, power_law, symmetrize)
     return {
         "nodes": nodes, "feature_count": feature_count, "class_count": class_count, "hidden": list(hidden), "output_heads": output_heads,
-        "edge_src": src, "edge_dst": dst, "features": make_features(rng, nodes, feature_count, density),
+        "edge_src": src, "edge_dst": dst, "features": make_features(rng, nodes, feature_count, density, feature_kind),
         "params": make_params(rng, feature_count, hidden, output_heads, class_count),
     }

@@ -55,3 +55,24 @@ def test_two_proofs_of_one_context_are_identical_and_inputs_matter():
     assert not np.array_equal(first[-4000:], other.proof_bytes()[-4000:])
     flow.close()
     other.close()
+
+
+def test_prefix_stored_columns_give_the_same_proof():
+    """compact_columns stores the edge-domain columns as prefixes (running sums up to their final value,
+    which the remaining rows repeat); every challenge, evaluation, commitment and opened value must equal
+    the whole-domain run's.  The second shape has node_count x head_dim above the largest lookup table, so
+    the ELU lookup columns are longer than the other edge columns."""
+    for shape in (dict(seed=6, nodes=30, directed_edges=80, feature_count=8, hidden=[(2, 4)], output_heads=2, class_count=3),
+                  dict(seed=8, nodes=200, directed_edges=500, feature_count=6, hidden=[(1, 128)], output_heads=1, class_count=3)):
+        inputs = synthetic.make_inputs(**shape)
+        full = Flow(ora.lib(), "ora_flow_", 2, inputs, G)
+        compact = Flow(ora.lib(), "ora_flow_", 2, inputs, G, compact_columns=True)
+        full.prove()
+        compact.prove()
+        a, b = full.dump().splitlines(), compact.dump().splitlines()
+        assert len(a) == len(b)
+        differing = [(x, y) for x, y in zip(a, b) if x != y]
+        assert not differing, differing[:3]
+        assert np.array_equal(full.proof_bytes(), compact.proof_bytes())
+        full.close()
+        compact.close()

@@ -85,3 +85,30 @@ def test_msm_commitments_equal_the_trapdoor_commitments():
     assert checked == gpu.stats()["dynamic_commitments"] - 4  # the four lazy feature-lookup commitments are scalar combinations
     assert mismatches == 0
     gpu.close()
+
+
+@pytest.mark.parametrize("shape", [
+    dict(seed=1, nodes=40, directed_edges=120, feature_count=12, hidden=[(2, 4)], output_heads=2, class_count=3),
+    dict(seed=8, nodes=200, directed_edges=500, feature_count=6, hidden=[(1, 128)], output_heads=1, class_count=3),
+    # more than 2^20 rows in the edge columns: the running sums take the single-column entry points
+    dict(seed=4, nodes=9000, directed_edges=30000, feature_count=6, hidden=[(1, 128)], output_heads=1, class_count=3),
+])
+def test_prefix_stored_gpu_proof_equals_whole_domain_cpu_proof(shape):
+    """compact_columns on the GPU (edge-domain columns stored as prefixes, running sums with their constant
+    tail) against the whole-domain CPU run: the same proof."""
+    inputs = synthetic.make_inputs(**shape)
+    big = shape["nodes"] > 1000
+    cpu = Flow(ora.lib(), "ora_flow_", 8, inputs, G, compact_columns=big)  # the large shape: both compact (CPU time)
+    gpu = gpu_flow(0, inputs, G, compact_columns=True)
+    cpu.prove()
+    gpu.prove()
+    assert first_difference(gpu.dump(), cpu.dump()) is None
+    assert np.array_equal(gpu.proof_bytes(), cpu.proof_bytes())
+    if big:
+        # and the whole-domain GPU run agrees with the compact one
+        full = gpu_flow(0, inputs, G)
+        full.prove()
+        assert np.array_equal(full.proof_bytes(), gpu.proof_bytes())
+        full.close()
+    cpu.close()
+    gpu.close()
