@@ -2,21 +2,26 @@
 """Benchmark of the B200 proving backend on the reference's headline metric.
 
 Metric: commit+prove ms/proof.  A "step" is ONE proof: the whole commit + prove flow of the
-multi-head GAT prover (project_b200/host/prover_flow.hpp) on the mid-size configuration
-(N=19717 nodes, 500 features, 8 hidden heads of width 8, 8 output heads of 3 classes; domains
-n_FH=2^24, n_edge=2^18, n_N=2^15, n_in=2^9, n_cat=2^7, n_d=2^4, n_C=2^3) - the largest of the
-configurations that fits one GPU.  The flow follows the reference's schedule: fp64 forward pass
-and quantised witness of every head, then ONE Fiat-Shamir transcript over the heads in order, per
-head the commit barriers of the reference (every barrier reads its commitment points back to the
-host, hashes them and only then builds the next columns), then the quotient evaluations at
-{tau, omega*tau}, fresh barycentric weights at the opening challenges and the evaluations at
-{z, omega*z}.  1212 dynamic commitments and 69 commit barriers per proof.
+multi-head GAT prover (project_b200/host/prover_flow.hpp).  The default workload is the
+configuration the metric is quoted on, the 169k-node citation-style GAT (N=169343, about 2.5 M
+edges with self loops, 128 features, two hidden layers of 3 heads x 256, one output head of 40
+classes; domains n_FH=2^25, n_edge=2^26, n_N=2^18, n_in=2^10, n_cat=2^10, n_d=2^9, n_C=2^6): with
+the edge-domain columns stored as prefixes it fits one GPU.  The mid-size configuration (b2:
+N=19717, 8x8 hidden, 8x3 output) is measured beside it in `b2`.  The flow follows the reference's
+schedule: fp64 forward pass and quantised witness of every head, then ONE Fiat-Shamir transcript
+over the heads in order, per head the commit barriers of the reference (every barrier reads its
+commitment points back to the host, hashes them and only then builds the next columns), then the
+quotient evaluations at {tau, omega*tau}, fresh barycentric weights at the opening challenges and
+the evaluations at {z, omega*z}.
 
 `value`   device-timed step with the feature matrix already in HBM.
 `e2e`     the same call with the feature matrix and the model parameters uploaded from host memory
           every step (results always come back to the host: that is how the transcript advances).
-`--impl reference`  the same flow, same inputs, over the CPU restatement (oracle/), all host
-          threads: the whole workload every step.
+`--impl reference`  the same flow over the CPU restatement (oracle/), all host threads.  For b2
+          and small: the whole workload every step.  For b4 (about seven minutes and 150 GB per
+          proof on 16 cores): the same model on a graph of 1/16 of the nodes and edges, whole flow
+          every step, time scaled by 16 (the flow's cost is linear in nodes and edges: measured
+          26.3 s at 1/16 and 103.7 s at 1/4 on 16 cores).
 """
 import argparse
 import ctypes
@@ -34,6 +39,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "commit+prove ms/proof"
 WORKLOADS = {
+    # the configuration the metric is quoted on: citation-style graph, power-law out-degree, symmetrised, dense Gaussian features
+    "b4": dict(seed=11, nodes=169343, directed_edges=1166243, feature_count=128, hidden=[(3, 256), (3, 256)], output_heads=1, class_count=40,
+               power_law=True, symmetrize=True, feature_kind="gauss"),
     # mid-size GAT of the configuration list: power-law graph, 10 % dense exponential features
     "b2": dict(seed=11, nodes=19717, directed_edges=88648, feature_count=500, hidden=[(8, 8)], output_heads=8, class_count=3, density=0.1,
                power_law=True),
@@ -41,11 +49,40 @@ WORKLOADS = {
     "small": dict(seed=11, nodes=1500, directed_edges=6000, feature_count=64, hidden=[(2, 8)], output_heads=2, class_count=3, density=0.1,
                   power_law=True),
 }
+# workloads whose edge-domain columns are stored as prefixes (whole-domain vectors would not fit one device)
+COMPACT = {"b4"}
+# the CPU arm of b4 runs the same model on 1/CPU_SAMPLE_DIVISOR of the nodes and edges and scales the time
+CPU_SAMPLE_DIVISOR = 16
 WORKLOAD_NAMES = {
+    "b4": "169k-node citation-style GAT (N=169343, 2.5M edges with self loops, 128 features, (3+3)x256 hidden, 1x40 output): one full "
+          "commit+prove flow per step, 575 dynamic commitments, 40 Fiat-Shamir-chained commit barriers, 7 domains (FH 2^25, edge 2^26, N 2^18), "
+          "edge-domain columns stored as prefixes",
     "b2": "mid-size GAT (N=19717, 500 features, 8x8 hidden, 8x3 output): one full commit+prove flow per step, 1212 dynamic commitments, "
           "69 Fiat-Shamir-chained commit barriers, 7 domains (FH 2^24, edge 2^18, N 2^15)",
     "small": "reduced shapes (N=1500, 64 features, 2x8 hidden, 2x3 output), same flow",
 }
+
+
+def cpu_sample_inputs(workload):
+    """Inputs of the CPU arm and the factor its time is multiplied by."""
+    from project_b200 import synthetic
+
+    shape = dict(WORKLOADS[workload])
+    if workload != "b4":
+        return synthetic.make_inputs(**shape), 1
+    shape["nodes"] //= CPU_SAMPLE_DIVISOR
+    shape["directed_edges"] //= CPU_SAMPLE_DIVISOR
+    return synthetic.make_inputs(**shape), CPU_SAMPLE_DIVISOR
+
+
+def cpu_sample_text(workload, stats, threads):
+    if workload == "b4":
+        return (f"the whole commit+prove flow ({stats['dynamic_commitments']} commitments, {stats['commit_barriers']} barriers) of the same model on a "
+                f"graph of 1/{CPU_SAMPLE_DIVISOR} of the nodes and edges ({WORKLOADS['b4']['nodes'] // CPU_SAMPLE_DIVISOR} nodes), over the CPU "
+                f"restatement, {threads} host threads; time multiplied by {CPU_SAMPLE_DIVISOR} (cost linear in nodes and edges: 26.3 s at 1/16, "
+                f"103.7 s at 1/4 measured on 16 cores; the full size needs about 150 GB of host memory and seven minutes per proof)")
+    return (f"full workload every step: the whole commit+prove flow ({stats['dynamic_commitments']} commitments, {stats['commit_barriers']} barriers) "
+            f"over the CPU restatement of the reference's leaves, {threads} host threads where the reference fans out, builders serial per column")
 
 
 class ClockSampler:
@@ -132,13 +169,13 @@ def config_of(args, world):
             "sharding": "one proof per rank (independent proofs, no data-path collective)" if world > 1 else "single GPU"}
 
 
-def cpu_flow_run(inputs, steps, warmup, threads):
+def cpu_flow_run(inputs, steps, warmup, threads, compact=False):
     """The flow over the CPU restatement, whole workload every step.  Returns (mean ms per proof, per-step list, stats)."""
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as ora
     from project_b200.flow import Flow
 
-    flow = Flow(ora.lib(), "ora_flow_", threads, inputs, generator_bytes())
+    flow = Flow(ora.lib(), "ora_flow_", threads, inputs, generator_bytes(), compact_columns=compact)
     times = []
     for i in range(warmup + steps):
         t0 = time.perf_counter()
@@ -150,21 +187,23 @@ def cpu_flow_run(inputs, steps, warmup, threads):
     return float(np.mean(times)), times, stats
 
 
-def run_reference(args, inputs):
+def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
     threads = cpu_count()
-    value, times, stats = cpu_flow_run(inputs, args.steps, args.warmup, threads)
-    sample = (f"full workload every step: the whole commit+prove flow ({stats['dynamic_commitments']} commitments, {stats['commit_barriers']} barriers) "
-              f"over the CPU restatement of the reference's leaves, {threads} host threads where the reference fans out, builders serial per column")
+    inputs, factor = cpu_sample_inputs(args.workload)
+    warmup = args.warmup if factor == 1 else min(args.warmup, 1)  # the CPU flow has no warm-up effect worth 26 s a step
+    value, times, stats = cpu_flow_run(inputs, args.steps, warmup, threads, compact=args.workload in COMPACT)
+    value *= factor
+    sample = cpu_sample_text(args.workload, stats, threads)
     emit({
-        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
         "ms_per_step": value, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
         "dtype": "u32x8 Montgomery Fr / u32x12 Fp (BLS12-381)", "data": "synthetic", "config": config_of(args, args.gpus),
         "cpu_baseline": {"value": value, "unit": "ms", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "ms", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}, "gpu_launches": 0,
-        "step_ms": [round(t, 1) for t in times],
+        "step_ms": [round(t * factor, 1) for t in times],
     })
     return 0
 
@@ -206,7 +245,8 @@ def main():
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="b2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="b4", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-b2", action="store_true", help="skip the mid-size configuration measured beside b4")
     ap.add_argument("--small", action="store_true", help="same as --workload small")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
@@ -218,9 +258,10 @@ def main():
         args.workload = "small"
     from project_b200 import synthetic
 
-    inputs = synthetic.make_inputs(**WORKLOADS[args.workload])
     if args.impl == "reference":
-        return run_reference(args, inputs)
+        return run_reference(args)
+    inputs = synthetic.make_inputs(**WORKLOADS[args.workload])
+    compact = args.workload in COMPACT
 
     import torch
 
@@ -252,7 +293,7 @@ def main():
             emit({"sweep": result, "n_gpus": world})
         return 0
 
-    flow = gpu_flow(local_rank, inputs, G)
+    flow = gpu_flow(local_rank, inputs, G, compact_columns=compact)
     ctx = flow.context()
     lib.gzk_ctx_stream.restype = ctypes.c_void_p
     stream = torch.cuda.ExternalStream(lib.gzk_ctx_stream(ctx), device=torch.device("cuda", local_rank))
@@ -262,7 +303,7 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    def timed(fn, steps, warmup):
+    def timed(fn, steps, warmup, stream=stream):
         for _ in range(warmup):
             fn()
         barrier()
@@ -294,6 +335,8 @@ def main():
     ms_per_step = ms_total / args.steps / world  # `world` independent proofs run side by side
     launches_per_step = sum(v[0] for v in timing_report().values()) // (args.steps + args.warmup)
     stats = flow.stats()
+    free_bytes, total_bytes = torch.cuda.mem_get_info()
+    resident_gb = (total_bytes - free_bytes) / 1e9  # columns of one proof, tables, weights, pooled buffers
 
     # per-kernel durations: one more proof with every launch bracketed by CUDA events
     lib.gzk_timing_reset(ctx)
@@ -344,7 +387,7 @@ def main():
 
     # ---- honest-prover commitments: every column also committed as an MSM against the resident SRS ----
     commit_msm = None
-    if not args.no_msm:
+    if not args.no_msm and not compact:
         flow.set_msm_commit(True)
         flow.prove(inputs_resident=True)  # builds the SRS tables (set-up, not timed)
         before = flow.set_msm_commit(True)
@@ -366,6 +409,29 @@ def main():
             check = "another rank failed"
 
     flow.close()
+    del flow
+    # ---- the mid-size configuration beside the headline one ------------------------------------------
+    b2 = None
+    if args.workload == "b4" and not args.no_b2:
+        flow2 = gpu_flow(local_rank, synthetic.make_inputs(**WORKLOADS["b2"]), G)
+        stream2 = torch.cuda.ExternalStream(lib.gzk_ctx_stream(flow2.context()), device=torch.device("cuda", local_rank))
+        ms2, _ = timed(lambda: flow2.prove(inputs_resident=True), args.steps, args.warmup, stream2)
+        e2e2, _ = timed(lambda: flow2.prove(inputs_resident=False), 2, 1, stream2)
+        stats2 = flow2.stats()
+        b2 = {"workload": WORKLOAD_NAMES["b2"], "ms_per_proof": ms2 / args.steps / world, "e2e_ms_per_proof": e2e2 / 2 / world,
+              "dynamic_commitments": stats2["dynamic_commitments"], "commit_barriers": stats2["commit_barriers"], "self_check": self_check(flow2, ora)}
+        if not args.no_msm:
+            flow2.set_msm_commit(True)
+            flow2.prove(inputs_resident=True)  # builds the SRS tables (set-up, not timed)
+            before = flow2.set_msm_commit(True)
+            msm_ms, _ = timed(lambda: flow2.prove(inputs_resident=True), 1, 0, stream2)
+            after = flow2.set_msm_commit(False)
+            b2["commit_msm"] = {"ms_per_proof_added": msm_ms / world - b2["ms_per_proof"], "msm_commitments": after[0] - before[0],
+                                "mismatches_vs_trapdoor": after[1],
+                                "note": "every committed column also committed as a Pippenger MSM against the resident SRS table and compared "
+                                        "with the trapdoor point [p(tau)] G"}
+        flow2.close()
+        del flow2
     sweep = None
     if not args.no_sweep:
         from project_b200 import sweep as sw
@@ -376,9 +442,9 @@ def main():
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.no_cpu:
         threads = cpu_count()
-        v, _, cstats = cpu_flow_run(inputs, 1, 0, threads)
-        cpu_baseline = {"value": v, "unit": "ms", "cores": threads, "kind": "port",
-                        "sample": f"one full proof ({cstats['dynamic_commitments']} commitments) of the same flow over the CPU restatement, {threads} host threads"}
+        cpu_inputs, factor = cpu_sample_inputs(args.workload)
+        v, _, cstats = cpu_flow_run(cpu_inputs, 1, 0, threads, compact=compact)
+        cpu_baseline = {"value": v * factor, "unit": "ms", "cores": threads, "kind": "port", "sample": "one proof: " + cpu_sample_text(args.workload, cstats, threads)}
 
     if rank == 0:
         emit({
@@ -388,7 +454,7 @@ def main():
             "roofline": roofline, "cpu_baseline": cpu_baseline, "e2e": e2e, "gpu_launches": launches_per_step * args.steps,
             "self_check": check, "proof": {k: stats[k] for k in ("commit_barriers", "challenges", "dynamic_commitments", "opened_columns", "domains")},
             "kernel_ms": kernel_ms, "kernel_ms_note": "one proof, every launch bracketed by CUDA events (sums per kernel family)",
-            "clocks": clocks, "commit_msm": commit_msm, "sweep": sweep,
+            "clocks": clocks, "resident_gb": resident_gb, "commit_msm": commit_msm, "b2": b2, "sweep": sweep,
         })
     if world > 1:
         dist.destroy_process_group()
