@@ -87,6 +87,10 @@ int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* leng
 size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap);
 /* the gzk_ctx the flow issues its work on (for gzk_timing_* and stream queries) */
 void* gzk_flow_context(gzk_flow* flow);
+/* Test hook (no counterpart in the reference): while on, every device buffer the flow allocates is
+ * filled with a byte pattern first, so a builder that reads a row nobody wrote gives a wrong proof
+ * deterministically instead of depending on what the memory held before. */
+void gzk_flow_debug_poison_allocations(int on);
 
 #ifdef __cplusplus
 }

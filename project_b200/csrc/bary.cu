@@ -59,7 +59,7 @@ namespace gzk
                 if (e < a.n)
                 {
                     const Fr d = sub(a.x, domain_point(a.lo, a.hi, a.lo_bits, (a.first + e) & a.mask));
-                    if (d.is_zero()) atomicExch(status, GZK_E_DOMAIN);
+                    if (d.is_zero()) raise_status(status, GZK_E_DOMAIN, 101);
                     prod = mul(prod, d);
                 }
             }
@@ -229,7 +229,7 @@ namespace gzk
                 {
                     Fr p1, p2;
                     const Fr d = quartet_denominator(a, e, &p1, &p2);
-                    if (d.is_zero()) atomicExch(status, GZK_E_DOMAIN);
+                    if (d.is_zero()) raise_status(status, GZK_E_DOMAIN, 102);
                     prod = mul(prod, d);
                 }
             }
@@ -392,7 +392,7 @@ namespace gzk
                     warp_suf[w] = run;
                     run = mul(run, warp_incl[w]);
                 }
-                if (total.is_zero()) atomicExch(status, GZK_E_DOMAIN);
+                if (total.is_zero()) raise_status(status, GZK_E_DOMAIN, 103);
                 cta_inverse = inv(total);
             }
             __syncthreads();

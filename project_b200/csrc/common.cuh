@@ -147,6 +147,14 @@ namespace gzk
 
 #if defined(__CUDACC__)
     // 32-byte element access as two 128-bit transactions.
+    // Raises the context's status word from a kernel.  The word after it records where: a number that is
+    // unique per raising site (file index * 100 + running number), reported with the error message.
+    __device__ __forceinline__ void raise_status(int* status, int code, int site)
+    {
+        atomicExch(status, code);
+        status[1] = site;
+    }
+
     __device__ __forceinline__ Fr load_fr(const Fr* p)
     {
         const uint4* q = reinterpret_cast<const uint4*>(p);

@@ -119,27 +119,30 @@ namespace gzk
         ctx->pending.clear();
     }
 
-    static int status_to_error(gzk_ctx* ctx, int status, const char* invalid_message)
+    // words[0] = status code, words[1] = the raising site (see raise_status)
+    static int status_to_error(gzk_ctx* ctx, const int* words, const char* invalid_message)
     {
+        const int status = words[0];
         if (status == 0) return GZK_OK;
-        cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
-        if (status == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "batch_invert encountered zero");
-        if (status == GZK_E_TIMEOUT) return fail(ctx, GZK_E_TIMEOUT, "a bounded wait on a bulk copy gave up");
-        if (status != GZK_E_INVALID) return fail(ctx, GZK_E_INVALID, std::string(invalid_message) + " [unexpected status word " + std::to_string(status) + "]");
-        return fail(ctx, GZK_E_INVALID, invalid_message);
+        cudaMemsetAsync(ctx->d_status, 0, 2 * sizeof(int), ctx->stream);
+        const std::string site = " [raised at site " + std::to_string(words[1]) + "]";
+        if (status == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "batch_invert encountered zero" + site);
+        if (status == GZK_E_TIMEOUT) return fail(ctx, GZK_E_TIMEOUT, "a bounded wait on a bulk copy gave up" + site);
+        if (status != GZK_E_INVALID) return fail(ctx, GZK_E_INVALID, std::string(invalid_message) + " [unexpected status word " + std::to_string(status) + "]" + site);
+        return fail(ctx, GZK_E_INVALID, invalid_message + site);
     }
 
     int begin_call(gzk_ctx* ctx)
     {
-        if (!ctx->deferred) GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));
+        if (!ctx->deferred) GZK_CUDA_TRY(ctx, cudaMemsetAsync(ctx->d_status, 0, 2 * sizeof(int), ctx->stream));
         return GZK_OK;
     }
 
     int finish_call(gzk_ctx* ctx, const char* invalid_message)
     {
         if (ctx->deferred) return GZK_OK;
-        int status = 0;
-        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        int status[2] = {0, 0};
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(status, ctx->d_status, sizeof(status), cudaMemcpyDeviceToHost, ctx->stream));
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return status_to_error(ctx, status, invalid_message);
     }
@@ -327,8 +330,8 @@ extern "C"
     int gzk_ctx_synchronize(gzk_ctx* ctx)
     {
         if (ctx == nullptr) return GZK_E_INVALID;
-        int status = 0;
-        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(&status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+        int status[2] = {0, 0};
+        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(status, ctx->d_status, sizeof(status), cudaMemcpyDeviceToHost, ctx->stream));
         GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return status_to_error(ctx, status, "a deferred call reported invalid input (index out of range, non-boolean selector or bad group bounds)");
     }

@@ -69,7 +69,7 @@ namespace gzk
                     if (src < node_count)
                         v = node_values[src];
                     else
-                        atomicExch(status, GZK_E_INVALID);
+                        raise_status(status, GZK_E_INVALID, 501);
                 }
                 out[e] = v;
             }
@@ -83,7 +83,7 @@ namespace gzk
                 if (b < domain_size)
                     atomicAdd(out + b, 1u);
                 else
-                    atomicExch(status, GZK_E_INVALID);
+                    raise_status(status, GZK_E_INVALID, 502);
             }
         }
 
@@ -128,7 +128,7 @@ namespace gzk
                 const uint64_t b = index_at(group_begin, g), e = index_at(group_end, g);
                 if (e > n || b > e)
                 {
-                    atomicExch(status, GZK_E_INVALID);
+                    raise_status(status, GZK_E_INVALID, 503);
                     continue;
                 }
                 for (uint64_t k = b; k < e; ++k)

@@ -217,7 +217,7 @@ namespace gzk
                     {
                         // a copy never completed: flag it, give the copies still in flight a
                         // bounded chance to land, and leave
-                        if (lane == 0) atomicExch(a.status, GZK_E_TIMEOUT);
+                        if (lane == 0) raise_status(a.status, GZK_E_TIMEOUT, 601);
                         for (uint32_t j = 0; j < issued && j < chunks; ++j)
                             mbar_wait(smem_u32(bars + (ring_pos + j) % kStages), ((ring_pos + j) / kStages) & 1u, a.wait_limit);
                         return;

@@ -43,6 +43,67 @@ namespace gzk
             out[idx] = acc;
         }
 
+        // The same sums for wide heads, tiled: a CTA owns 64 rows x 64 output columns, a thread 4 x 4 of them;
+        // the 16-deep slices of X and W pass through shared memory, so each loaded value feeds four
+        // multiply-adds instead of one.  Every output is still accumulated over k ascending with a separate
+        // multiplication and addition, so the results are the one-thread-per-output kernel's bit for bit.
+        constexpr int kTileM = 64, kTileN = 64, kTileK = 16;
+        __global__ void __launch_bounds__(kThreads) project_tiled_kernel(const double* x, const double* w, uint64_t rows, uint32_t inner, uint32_t width,
+                                                                         double* out)
+        {
+            __shared__ double xs[kTileK][kTileM + 1];
+            __shared__ double ws[kTileK][kTileN];
+            const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
+            const uint64_t i0 = static_cast<uint64_t>(blockIdx.y) * kTileM;
+            const uint32_t j0 = blockIdx.x * kTileN;
+            double acc[4][4];
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+#pragma unroll
+                for (int c = 0; c < 4; ++c) acc[r][c] = 0.0;
+            const uint32_t x_row = threadIdx.x >> 2, x_k = (threadIdx.x & 3) * 4;   // 64 rows x 16 k
+            const uint32_t w_k = threadIdx.x >> 4, w_j = (threadIdx.x & 15) * 4;    // 16 k x 64 columns
+            for (uint32_t k0 = 0; k0 < inner; k0 += kTileK)
+            {
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                {
+                    const uint64_t row = i0 + x_row;
+                    const uint32_t k = k0 + x_k + q;
+                    xs[x_k + q][x_row] = (row < rows && k < inner) ? x[row * inner + k] : 0.0;
+                    const uint32_t kw = k0 + w_k, j = j0 + w_j + q;
+                    ws[w_k][w_j + q] = (kw < inner && j < width) ? __ldg(w + static_cast<uint64_t>(kw) * width + j) : 0.0;
+                }
+                __syncthreads();
+                const uint32_t k_count = inner - k0 < kTileK ? inner - k0 : kTileK;
+                for (uint32_t kk = 0; kk < k_count; ++kk)
+                {
+                    double a[4], b[4];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r) a[r] = xs[kk][ty * 4 + r];
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) b[c] = ws[kk][tx * 4 + c];
+#pragma unroll
+                    for (int r = 0; r < 4; ++r)
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) acc[r][c] = __dadd_rn(acc[r][c], __dmul_rn(a[r], b[c]));
+                }
+                __syncthreads();
+            }
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+            {
+                const uint64_t row = i0 + ty * 4 + r;
+                if (row >= rows) continue;
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                {
+                    const uint32_t j = j0 + tx * 4 + c;
+                    if (j < width) out[row * width + j] = acc[r][c];
+                }
+            }
+        }
+
         // e[i] = bias + sum_c h[i][c] * a[c], c ascending; both score vectors in one pass
         __global__ void __launch_bounds__(kThreads) scores_kernel(const double* h, uint64_t rows, uint32_t width, const double* a_src, double b_src,
                                                                   const double* a_dst, double b_dst, double* e_src, double* e_dst)
@@ -77,6 +138,78 @@ namespace gzk
             m_out[dst] = m;
             sum_out[dst] = sum;
             inv_out[dst] = __ddiv_rn(1.0, sum);
+        }
+
+        // The same statistics with one warp per destination node, plus the attention weight of every entry
+        // of the incoming lists (alpha_in[p], p the position in in_src).  A node with tens of thousands of
+        // incoming edges (the hubs of a power-law graph) would keep a single thread busy long after the rest
+        // of the grid has drained; here the lanes evaluate 32 exponentials at a time and only the additions
+        // stay serial - in list order, one after the other, because the reference adds them in that order
+        // and floating-point addition is not associative.  (The maximum is exact in any order.)
+        __global__ void __launch_bounds__(kThreads) softmax_stats_warp_kernel(const double* e_src, const double* e_dst, const uint32_t* in_ptr,
+                                                                              const uint32_t* in_src, uint64_t nodes, double* m_out, double* sum_out,
+                                                                              double* inv_out, double* alpha_in)
+        {
+            const uint64_t dst = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+            const uint32_t lane = threadIdx.x & 31;
+            if (dst >= nodes) return;
+            const uint32_t begin = in_ptr[dst], end = in_ptr[dst + 1];
+            const double ed = e_dst[dst];
+            double m = -INFINITY;
+            for (uint32_t p = begin + lane; p < end; p += 32) m = fmax(m, leaky_relu(__dadd_rn(ed, e_src[in_src[p]])));
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1) m = fmax(m, __shfl_xor_sync(0xffffffffu, m, offset));
+            double sum = 0.0;
+            for (uint32_t base = begin; base < end; base += 32)
+            {
+                const uint32_t p = base + lane;
+                double t = 0.0;
+                if (p < end)
+                {
+                    t = exp(__dsub_rn(leaky_relu(__dadd_rn(ed, e_src[in_src[p]])), m));
+                    alpha_in[p] = t;
+                }
+                const uint32_t here = end - base < 32 ? end - base : 32;
+                for (uint32_t l = 0; l < here; ++l) sum = __dadd_rn(sum, __shfl_sync(0xffffffffu, t, l));
+            }
+            const double inv = __ddiv_rn(1.0, sum);
+            if (lane == 0)
+            {
+                m_out[dst] = m;
+                sum_out[dst] = sum;
+                inv_out[dst] = inv;
+            }
+            for (uint32_t p = begin + lane; p < end; p += 32) alpha_in[p] = __dmul_rn(alpha_in[p], inv);  // written by this same lane above
+        }
+
+        // Aggregation with the attention weights already in alpha_in: no exponential inside the serial sum.
+        __global__ void __launch_bounds__(kThreads) aggregate_alpha_kernel(const double* h, const double* alpha_in, const uint32_t* in_ptr,
+                                                                           const uint32_t* in_src, uint64_t nodes, uint32_t width, const double* out_bias,
+                                                                           uint32_t bias_count, int apply_activation, double* pre_out, double* agg_out)
+        {
+            const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (idx >= nodes * width) return;
+            const uint64_t dst = idx / width;
+            const uint32_t c = static_cast<uint32_t>(idx - dst * width);
+            const uint32_t begin = in_ptr[dst], end = in_ptr[dst + 1];
+            double acc = 0.0;
+            uint32_t p = begin;
+            for (; p + 4 <= end; p += 4)
+            {
+                // the four loads do not depend on acc: they are in flight together
+                const double a0 = alpha_in[p], a1 = alpha_in[p + 1], a2 = alpha_in[p + 2], a3 = alpha_in[p + 3];
+                const double h0 = h[static_cast<uint64_t>(in_src[p]) * width + c], h1 = h[static_cast<uint64_t>(in_src[p + 1]) * width + c];
+                const double h2 = h[static_cast<uint64_t>(in_src[p + 2]) * width + c], h3 = h[static_cast<uint64_t>(in_src[p + 3]) * width + c];
+                acc = __dadd_rn(acc, __dmul_rn(a0, h0));
+                acc = __dadd_rn(acc, __dmul_rn(a1, h1));
+                acc = __dadd_rn(acc, __dmul_rn(a2, h2));
+                acc = __dadd_rn(acc, __dmul_rn(a3, h3));
+            }
+            for (; p < end; ++p) acc = __dadd_rn(acc, __dmul_rn(alpha_in[p], h[static_cast<uint64_t>(in_src[p]) * width + c]));
+            if (pre_out != nullptr) pre_out[idx] = acc;
+            double v = acc;
+            if (out_bias != nullptr && c < bias_count) v = __dadd_rn(v, out_bias[c]);
+            if (agg_out != nullptr) agg_out[idx] = apply_activation ? (v >= 0.0 ? v : expm1(v)) : v;
         }
 
         // H_agg_pre[dst][c] = sum over incoming src of alpha * H'[src][c]; H_agg = act(H_agg_pre + bias)
@@ -114,7 +247,7 @@ namespace gzk
             const uint32_t a = src[e], b = dst[e];
             if (a >= nodes || b >= nodes)
             {
-                atomicExch(status, GZK_E_INVALID);
+                raise_status(status, GZK_E_INVALID, 701);
                 return;
             }
             const double s = __dadd_rn(e_dst[b], e_src[a]);
@@ -131,9 +264,9 @@ namespace gzk
                                                                           int* status)
         {
             const uint64_t i = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
-            if (i < nodes && (in_ptr[i] > in_ptr[i + 1] || in_ptr[i + 1] > in_count)) atomicExch(status, GZK_E_INVALID);
-            if (i == 0 && in_ptr[0] != 0) atomicExch(status, GZK_E_INVALID);
-            if (i < in_count && in_src[i] >= nodes) atomicExch(status, GZK_E_INVALID);
+            if (i < nodes && (in_ptr[i] > in_ptr[i + 1] || in_ptr[i + 1] > in_count)) raise_status(status, GZK_E_INVALID, 702);
+            if (i == 0 && in_ptr[0] != 0) raise_status(status, GZK_E_INVALID, 703);
+            if (i < in_count && in_src[i] >= nodes) raise_status(status, GZK_E_INVALID, 704);
         }
 
         bool f64_ok(const gzk_buf* b, uint64_t need) { return b != nullptr && b->kind == GZK_KIND_F64 && b->count >= need; }
@@ -189,6 +322,14 @@ extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, cons
             return fail(ctx, GZK_E_INVALID, "edge out of bounds while running attention head forward");
         }
     }
+    if (width >= 32)
+    {
+        LaunchScope scope(ctx, "forward_project");
+        const dim3 grid((width + kTileN - 1) / kTileN, static_cast<unsigned>((nodes + kTileM - 1) / kTileM));
+        project_tiled_kernel<<<grid, kThreads, 0, ctx->stream>>>(f64_ptr(head->features), f64_ptr(head->seq_kernel), nodes, inner, width,
+                                                                 f64_ptr(out->H_prime));
+    }
+    else
     {
         LaunchScope scope(ctx, "forward_project");
         project_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(f64_ptr(head->features), f64_ptr(head->seq_kernel), nodes, inner, width,
@@ -202,13 +343,35 @@ extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, cons
                                                                      f64_ptr(out->E_dst));
     }
     GZK_CUDA_TRY(ctx, cudaGetLastError());
+    // long incoming lists (an average above 4 entries, or any list above 64): one warp per node and the
+    // attention weights kept per list entry; short lists keep the one-thread-per-node kernels
+    const bool by_warp = in_count > 4 * nodes || in_count >= (1u << 16);
+    double* alpha_in = nullptr;
+    if (by_warp)
+    {
+        void* scratch = nullptr;
+        if ((rc = ensure_scratch(ctx, 0, (in_count + 1) * sizeof(double), &scratch)) != GZK_OK) return rc;
+        alpha_in = static_cast<double*>(scratch);
+        LaunchScope scope(ctx, "forward_softmax_stats");
+        softmax_stats_warp_kernel<<<grid_for(nodes * 32), kThreads, 0, ctx->stream>>>(f64_ptr(out->E_src), f64_ptr(out->E_dst), in_ptr, in_src, nodes,
+                                                                                      f64_ptr(out->M), f64_ptr(out->Sum), f64_ptr(out->inv), alpha_in);
+    }
+    else
     {
         LaunchScope scope(ctx, "forward_softmax_stats");
         softmax_stats_kernel<<<grid_for(nodes), kThreads, 0, ctx->stream>>>(f64_ptr(out->E_src), f64_ptr(out->E_dst), in_ptr, in_src, nodes, f64_ptr(out->M),
                                                                             f64_ptr(out->Sum), f64_ptr(out->inv));
     }
     GZK_CUDA_TRY(ctx, cudaGetLastError());
-    if (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr)
+    if (by_warp && (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr))
+    {
+        LaunchScope scope(ctx, "forward_aggregate");
+        aggregate_alpha_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(
+            f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, nodes, width, f64_ptr(head->output_bias),
+            head->output_bias != nullptr ? static_cast<uint32_t>(head->output_bias_count) : 0u, head->apply_activation, f64_ptr(out->H_agg_pre_bias),
+            f64_ptr(out->H_agg));
+    }
+    else if (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr)
     {
         LaunchScope scope(ctx, "forward_aggregate");
         aggregate_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(

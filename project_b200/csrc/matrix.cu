@@ -59,6 +59,88 @@ namespace gzk
             }
         }
 
+        // Matrix entries by buffer kind, resolved at compile time so that a kernel can issue the loads of
+        // several entries before the multiply-adds that consume them (a branch on the kind inside the loop
+        // would pin every load behind the previous product).  acc += w * entry as an exact integer:
+        // field-element entries are used as stored; a small-integer entry v enters as its magnitude (one or
+        // two limbs) against w or, for v < 0, r - w (w * (r - |v|) is congruent to (r - w) * |v|): 8 x 2 limb
+        // products instead of the 8 x 8 plus a conversion that widening it to a field element would cost.
+        // The sum then carries the same power of R as one over canonical field elements.
+        template <int KIND>
+        struct Entry
+        {
+            using Raw = Fr;
+            static __device__ __forceinline__ Raw zero() { return Fr::zero(); }
+            static __device__ __forceinline__ Raw load(const void* ptr, uint64_t i) { return load_fr(static_cast<const Fr*>(ptr) + i); }
+            static __device__ __forceinline__ void mac(WideAcc& acc, const Fr& w, const Raw& v) { acc.mac<8>(w.l, v.l); }
+        };
+        template <>
+        struct Entry<GZK_KIND_U32>
+        {
+            using Raw = uint32_t;
+            static __device__ __forceinline__ Raw zero() { return 0u; }
+            static __device__ __forceinline__ Raw load(const void* ptr, uint64_t i) { return __ldg(static_cast<const uint32_t*>(ptr) + i); }
+            static __device__ __forceinline__ void mac(WideAcc& acc, const Fr& w, const Raw& v) { acc.mac<1>(w.l, &v); }
+        };
+        template <>
+        struct Entry<GZK_KIND_I64>
+        {
+            using Raw = long long;
+            static __device__ __forceinline__ Raw zero() { return 0; }
+            static __device__ __forceinline__ Raw load(const void* ptr, uint64_t i) { return __ldg(static_cast<const long long*>(ptr) + i); }
+            static __device__ __forceinline__ void mac(WideAcc& acc, const Fr& w, const Raw& v)
+            {
+                const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
+                const uint32_t f[2] = {static_cast<uint32_t>(mag), static_cast<uint32_t>(mag >> 32)};
+                const Fr signed_w = v < 0 ? sub(Fr::zero(), w) : w;
+                acc.mac<2>(signed_w.l, f);
+            }
+        };
+        // FR and FR_MONT share the field-element code
+        constexpr int entry_kind(int kind) { return kind == GZK_KIND_U32 || kind == GZK_KIND_I64 ? kind : GZK_KIND_FR; }
+
+        // Small-integer coefficients: Horner costs a full field multiplication per coefficient although the
+        // coefficient itself is one or two limbs.  Cut the polynomial into blocks of 256 coefficients,
+        // r_b = sum_j c[256 b + j] x^j as an exact 8 x 2 limb inner product against the 256 powers of x
+        // (one warp per block, each lane keeps its eight powers in registers), and leave Horner to the
+        // 256 times shorter polynomial sum_b r_b (x^256)^b.  out[b] is the Montgomery form of r_b.
+        constexpr int kDotBlock = 256;
+        template <int KIND>
+        __global__ void __launch_bounds__(kThreads) block_dot_kernel(const void* coeffs, uint64_t total, const Fr* powers, uint64_t blocks, Fr* out)
+        {
+            const uint32_t lane = threadIdx.x & 31;
+            const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+            const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
+            Fr p[kDotBlock / 32];
+#pragma unroll
+            for (int k = 0; k < kDotBlock / 32; ++k) p[k] = load_fr(powers + lane + 32 * k);
+            for (uint64_t b = warp; b < blocks; b += warps)
+            {
+                WideAcc acc;
+                acc.clear();
+                typename Entry<KIND>::Raw raw[kDotBlock / 32];
+#pragma unroll
+                for (int k = 0; k < kDotBlock / 32; ++k)
+                {
+                    const uint64_t i = b * kDotBlock + lane + 32 * k;
+                    raw[k] = i < total ? Entry<KIND>::load(coeffs, i) : Entry<KIND>::zero();
+                }
+#pragma unroll
+                for (int k = 0; k < kDotBlock / 32; ++k) Entry<KIND>::mac(acc, p[k], raw[k]);
+                uint32_t sum[kAccLimbs];
+                acc.fold(sum);
+#pragma unroll
+                for (int offset = 16; offset > 0; offset >>= 1)
+                {
+                    uint32_t other[kAccLimbs];
+#pragma unroll
+                    for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, sum[i], offset);
+                    acc_add<kAccLimbs, kAccLimbs>(sum, other);
+                }
+                if (lane == 0) store_fr(out + b, mul(redc_wide<FrCfg, 9>(sum), fr_const_2_544()));
+            }
+        }
+
         // `down` > 0: that many conversions out of Montgomery form; < 0: into it.
         __global__ void sum_partials_kernel(const Fr* partial, uint32_t count, int down, Fr* out)
         {
@@ -71,19 +153,11 @@ namespace gzk
         }
 
         // ---- fold rows ----------------------------------------------------------------
-        // Raw limbs of a matrix entry for the unreduced accumulator: FR and FR_MONT
-        // entries are used as stored (the final reduction accounts for the form),
-        // small-integer kinds are widened to Montgomery form first.
-        __device__ __forceinline__ Fr entry_raw(const ColRef& m, uint64_t i)
-        {
-            if (m.kind == GZK_KIND_FR || m.kind == GZK_KIND_FR_MONT) return load_fr(static_cast<const Fr*>(m.ptr) + i);
-            return col_load_mont(m, i);
-        }
-
         // CTA (tile, column chunk): threads are laid out as (row lane, column); each
         // thread accumulates w[row] * M[row][c] unreduced over the rows of the tile that
         // fall on its row lane; row lanes are then summed through shared memory.
-        __global__ void __launch_bounds__(kThreads) fold_rows_kernel(ColRef matrix, const Fr* weights, uint64_t row_count, uint32_t cols,
+        template <int KIND>
+        __global__ void __launch_bounds__(kThreads) fold_rows_kernel(const void* matrix, const Fr* weights, uint64_t row_count, uint32_t cols,
                                                                      uint64_t tile_rows, uint32_t col_chunks, uint32_t* partial)
         {
             extern __shared__ uint32_t lanes_sum[];  // [kThreads][17]
@@ -100,12 +174,16 @@ namespace gzk
             acc.clear();
             if (row_lane < row_lanes && c < cols)
             {
-                for (uint64_t row = r_begin + row_lane; row < r_end; row += row_lanes)
+                uint64_t row = r_begin + row_lane;
+                for (; row + 3ull * row_lanes < r_end; row += 4ull * row_lanes)
                 {
-                    const Fr w = load_fr(weights + row);
-                    const Fr v = entry_raw(matrix, row * cols + c);
-                    acc.mac<8>(w.l, v.l);
+                    typename Entry<KIND>::Raw raw[4];
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) raw[u] = Entry<KIND>::load(matrix, (row + static_cast<uint64_t>(u) * row_lanes) * cols + c);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) Entry<KIND>::mac(acc, load_fr(weights + row + static_cast<uint64_t>(u) * row_lanes), raw[u]);
                 }
+                for (; row < r_end; row += row_lanes) Entry<KIND>::mac(acc, load_fr(weights + row), Entry<KIND>::load(matrix, row * cols + c));
             }
             uint32_t sum[kAccLimbs];
             acc.fold(sum);
@@ -129,19 +207,25 @@ namespace gzk
 
         // ---- linear form over rows -------------------------------------------------------
         // One warp per row: lanes stride over the columns, exact warp sum, one reduction.
-        __global__ void __launch_bounds__(kThreads) linear_form_kernel(ColRef matrix, const Fr* powers, uint64_t rows, uint32_t cols, Fr* out)
+        template <int KIND>
+        __global__ void __launch_bounds__(kThreads) linear_form_kernel(const void* matrix, int montgomery_entries, const Fr* powers, uint64_t rows,
+                                                                       uint32_t cols, Fr* out)
         {
             const uint32_t lane = threadIdx.x & 31;
             const uint64_t row = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
             if (row >= rows) return;
             WideAcc acc;
             acc.clear();
-            for (uint32_t j = lane; j < cols; j += 32)
+            uint32_t j = lane;
+            for (; j + 96 < cols; j += 128)
             {
-                const Fr p = load_fr(powers + j);
-                const Fr v = entry_raw(matrix, row * cols + j);
-                acc.mac<8>(p.l, v.l);
+                typename Entry<KIND>::Raw raw[4];
+#pragma unroll
+                for (int u = 0; u < 4; ++u) raw[u] = Entry<KIND>::load(matrix, row * cols + j + 32 * u);
+#pragma unroll
+                for (int u = 0; u < 4; ++u) Entry<KIND>::mac(acc, load_fr(powers + j + 32 * u), raw[u]);
             }
+            for (; j < cols; j += 32) Entry<KIND>::mac(acc, load_fr(powers + j), Entry<KIND>::load(matrix, row * cols + j));
             uint32_t sum[kAccLimbs];
             acc.fold(sum);
 #pragma unroll
@@ -156,9 +240,9 @@ namespace gzk
             {
                 const Fr reduced = redc_wide<FrCfg, 9>(sum);
                 Fr fix;
-                if (matrix.kind == GZK_KIND_FR)
+                if (!montgomery_entries)
                 {
-                    fix = fr_const_2_544();
+                    fix = fr_const_2_544();  // canonical and small-integer entries: one factor of R less in the sum
                 }
                 else
                 {
@@ -196,22 +280,50 @@ extern "C"
     static int matrix_horner_enqueue(gzk_ctx* ctx, const gzk_buf* matrix, uint64_t total, const Fr& x, Fr* dest, bool dest_montgomery,
                                      Fr** scratch_result)
     {
-        uint64_t ctas = (total + static_cast<uint64_t>(kThreads) * 8 - 1) / (static_cast<uint64_t>(kThreads) * 8);
+        const bool small_kind = matrix->kind == GZK_KIND_I64 || matrix->kind == GZK_KIND_U32;
+        const bool blocked = small_kind && total >= (1u << 16);
+        const uint64_t dot_blocks = blocked ? (total + kDotBlock - 1) / kDotBlock : 0;
+        const uint64_t horner_total = blocked ? dot_blocks : total;
+        uint64_t ctas = (horner_total + static_cast<uint64_t>(kThreads) * 8 - 1) / (static_cast<uint64_t>(kThreads) * 8);
         const uint64_t max_ctas = static_cast<uint64_t>(ctx->sm_count) * 8;
         if (ctas > max_ctas) ctas = max_ctas;
-        uint64_t span = (total + ctas - 1) / ctas;
+        uint64_t span = (horner_total + ctas - 1) / ctas;
         span = (span + kThreads - 1) / kThreads * kThreads;
-        ctas = (total + span - 1) / span;
+        ctas = (horner_total + span - 1) / span;
         void* scratch = nullptr;
-        int rc = ensure_scratch(ctx, 2, (ctas + 1) * sizeof(Fr), &scratch);
+        int rc = ensure_scratch(ctx, 2, (ctas + 1 + (blocked ? kDotBlock + dot_blocks : 0)) * sizeof(Fr), &scratch);
         if (rc != GZK_OK) return rc;
         Fr* partial = static_cast<Fr*>(scratch);
         ColRef m;
         m.ptr = matrix->dptr;
         m.kind = matrix->kind;
+        Fr x_horner = x;
+        if (blocked)
+        {
+            Fr* powers = partial + ctas + 1;
+            Fr* block_values = powers + kDotBlock;
+            {
+                LaunchScope scope(ctx, "powers");
+                powers_kernel<<<1, kDotBlock, 0, ctx->stream>>>(x, kDotBlock, powers);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            const uint64_t warps_wanted = dot_blocks < static_cast<uint64_t>(ctx->sm_count) * 64 ? dot_blocks : static_cast<uint64_t>(ctx->sm_count) * 64;
+            {
+                LaunchScope scope(ctx, "horner_block_dot");
+                const unsigned grid = static_cast<unsigned>((warps_wanted * 32 + kThreads - 1) / kThreads);
+                if (matrix->kind == GZK_KIND_I64)
+                    block_dot_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values);
+                else
+                    block_dot_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values);
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            m.ptr = block_values;
+            m.kind = GZK_KIND_FR_MONT;
+            x_horner = pow_u64(x, kDotBlock);
+        }
         {
             LaunchScope scope(ctx, "horner");
-            horner_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, total, span, x, pow_u64(x, kThreads), partial);
+            horner_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, horner_total, span, x_horner, pow_u64(x_horner, kThreads), partial);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         Fr* result = dest != nullptr ? dest : partial + ctas;
@@ -219,7 +331,7 @@ extern "C"
             // the partial sums are Montgomery values of the canonical result (canonical entries) or of its
             // Montgomery form (Montgomery entries): one or two conversions bring them to the wanted form
             LaunchScope scope(ctx, "horner_sum");
-            const int down = (matrix->kind == GZK_KIND_FR_MONT ? 1 : 0) - (dest_montgomery ? 1 : 0);
+            const int down = (m.kind == GZK_KIND_FR_MONT ? 1 : 0) - (dest_montgomery ? 1 : 0);
             sum_partials_kernel<<<1, 32, 0, ctx->stream>>>(partial, static_cast<uint32_t>(ctas), down, result);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
@@ -306,12 +418,24 @@ extern "C"
         const size_t smem = static_cast<size_t>(kThreads) * kAccLimbs * sizeof(uint32_t);
         {
             LaunchScope scope(ctx, "fold_rows");
-            fold_rows_kernel<<<static_cast<unsigned>(tiles * col_chunks), kThreads, smem, ctx->stream>>>(
-                m, static_cast<const Fr*>(row_weights->dptr), row_count, static_cast<uint32_t>(cols), tile_rows, col_chunks,
-                static_cast<uint32_t*>(scratch));
+            const unsigned grid = static_cast<unsigned>(tiles * col_chunks);
+            const Fr* w = static_cast<const Fr*>(row_weights->dptr);
+            uint32_t* partial = static_cast<uint32_t*>(scratch);
+            switch (entry_kind(matrix->kind))
+            {
+            case GZK_KIND_I64:
+                fold_rows_kernel<GZK_KIND_I64><<<grid, kThreads, smem, ctx->stream>>>(m.ptr, w, row_count, static_cast<uint32_t>(cols), tile_rows, col_chunks, partial);
+                break;
+            case GZK_KIND_U32:
+                fold_rows_kernel<GZK_KIND_U32><<<grid, kThreads, smem, ctx->stream>>>(m.ptr, w, row_count, static_cast<uint32_t>(cols), tile_rows, col_chunks, partial);
+                break;
+            default:
+                fold_rows_kernel<GZK_KIND_FR><<<grid, kThreads, smem, ctx->stream>>>(m.ptr, w, row_count, static_cast<uint32_t>(cols), tile_rows, col_chunks, partial);
+                break;
+            }
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
-        const int form = matrix->kind == GZK_KIND_FR ? GZK_KIND_FR : GZK_KIND_FR_MONT;
+        const int form = matrix->kind == GZK_KIND_FR_MONT ? GZK_KIND_FR_MONT : GZK_KIND_FR;  // small integers count as canonical values
         if ((rc = launch_eval_finish(ctx, static_cast<const uint32_t*>(scratch), form, static_cast<uint32_t>(tiles),
                                      static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr), false)) != GZK_OK)
             return rc;
@@ -335,8 +459,16 @@ extern "C"
         const uint64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
         {
             LaunchScope scope(ctx, "linear_form");
-            linear_form_kernel<<<static_cast<unsigned>(ctas), kThreads, 0, ctx->stream>>>(m, static_cast<const Fr*>(column_powers->dptr), rows,
-                                                                                         static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr));
+            const unsigned grid = static_cast<unsigned>(ctas);
+            const Fr* powers = static_cast<const Fr*>(column_powers->dptr);
+            const int mont = matrix->kind == GZK_KIND_FR_MONT ? 1 : 0;
+            Fr* dst = static_cast<Fr*>(out->dptr);
+            switch (entry_kind(matrix->kind))
+            {
+            case GZK_KIND_I64: linear_form_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst); break;
+            case GZK_KIND_U32: linear_form_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst); break;
+            default: linear_form_kernel<GZK_KIND_FR><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst); break;
+            }
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return finish_call(ctx, "invalid input");

@@ -103,7 +103,63 @@ namespace gzk
                         }
                     }
                 }
-                if (!hit) atomicExch(status, GZK_E_INVALID);
+                if (!hit) raise_status(status, GZK_E_INVALID, 1301);
+            }
+        }
+
+        // The same count with one private histogram per CTA in shared memory (tables of up to 56k entries fit).
+        // Queries of a real witness pile up on a few table rows (most activations sit near zero), and
+        // millions of global atomics on one address serialise; here the lanes of a warp that hit the same
+        // row are counted by one of them (match.any), the CTA counts in shared memory, and only the
+        // non-zero bins of each CTA reach global memory.
+        constexpr int kHistThreads = 1024;
+        __global__ void __launch_bounds__(kHistThreads) banded_multiplicity_shared_kernel(ColRef x, ColRef y, int has_y, uint64_t count, long long x_min,
+                                                                                          uint32_t band, const long long* table_y, uint32_t table_size,
+                                                                                          uint32_t* out, int* status)
+        {
+            extern __shared__ uint32_t hist[];
+            for (uint32_t i = threadIdx.x; i < table_size; i += kHistThreads) hist[i] = 0;
+            __syncthreads();
+            constexpr uint32_t kNone = 0xffffffffu;
+            const uint32_t lane = threadIdx.x & 31;
+            const uint64_t stride = static_cast<uint64_t>(gridDim.x) * kHistThreads;
+            for (uint64_t base = static_cast<uint64_t>(blockIdx.x) * kHistThreads; base < count; base += stride)
+            {
+                const uint64_t i = base + threadIdx.x;  // the whole warp stays in the loop: base is uniform
+                uint32_t slot = kNone;
+                if (i < count)
+                {
+                    const long long rel = int_at(x, i) - x_min;
+                    if (rel >= 0 && static_cast<uint64_t>(rel) * band + band <= table_size)
+                    {
+                        const uint32_t first = static_cast<uint32_t>(rel) * band;
+                        if (!has_y)
+                        {
+                            slot = first;
+                        }
+                        else
+                        {
+                            const long long yv = int_at(y, i);
+                            for (uint32_t j = 0; j < band; ++j)
+                            {
+                                if (__ldg(table_y + first + j) == yv)
+                                {
+                                    slot = first + j;
+                                    break;
+                                }
+                            }
+                        }
+                    }
+                    if (slot == kNone) raise_status(status, GZK_E_INVALID, 1302);
+                }
+                const uint32_t peers = __match_any_sync(0xffffffffu, slot);
+                if (slot != kNone && lane == static_cast<uint32_t>(__ffs(peers) - 1)) atomicAdd(hist + slot, static_cast<uint32_t>(__popc(peers)));
+            }
+            __syncthreads();
+            for (uint32_t i = threadIdx.x; i < table_size; i += kHistThreads)
+            {
+                const uint32_t v = hist[i];
+                if (v != 0) atomicAdd(out + i, v);
             }
         }
 
@@ -211,7 +267,25 @@ extern "C"
         int rc = begin_call(ctx);
         if (rc != GZK_OK) return rc;
         GZK_CUDA_TRY(ctx, cudaMemsetAsync(out->dptr, 0, domain_size * sizeof(uint32_t), ctx->stream));
-        if (count != 0)
+        constexpr size_t kSharedTableLimit = 56 * 1024;  // 224 KB of counters
+        if (count >= (1u << 16) && table_size <= kSharedTableLimit)
+        {
+            static bool opted_in[64] = {};
+            if (ctx->device >= 0 && ctx->device < 64 && !opted_in[ctx->device])
+            {
+                GZK_CUDA_TRY(ctx, cudaFuncSetAttribute(banded_multiplicity_shared_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                       static_cast<int>(kSharedTableLimit * sizeof(uint32_t))));
+                opted_in[ctx->device] = true;
+            }
+            uint64_t ctas = (count + kHistThreads - 1) / kHistThreads;
+            if (ctas > static_cast<uint64_t>(ctx->sm_count)) ctas = ctx->sm_count;
+            LaunchScope scope(ctx, "lookup_multiplicity");
+            banded_multiplicity_shared_kernel<<<static_cast<unsigned>(ctas), kHistThreads, table_size * sizeof(uint32_t), ctx->stream>>>(
+                ref(x), has_y ? ref(y) : ref(x), has_y ? 1 : 0, count, static_cast<long long>(x_min), static_cast<uint32_t>(band),
+                has_y ? static_cast<const long long*>(table_y->dptr) : nullptr, static_cast<uint32_t>(table_size), static_cast<uint32_t*>(out->dptr),
+                ctx->d_status);
+        }
+        else if (count != 0)
         {
             LaunchScope scope(ctx, "lookup_multiplicity");
             banded_multiplicity_kernel<<<blocks_for(ctx, count), kThreads, 0, ctx->stream>>>(

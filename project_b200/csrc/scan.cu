@@ -91,6 +91,27 @@ namespace gzk
             return tb;
         }
 
+        // LogUp rows with only one side switched on by its 0/1 selector (almost all of them: the table
+        // fills the first rows of the column, the queries run on for millions more) need the inverse of
+        // that side alone.  *side = 1 table only, 2 query only, 0 neither (denominator 1), 3 the general
+        // two-sided term (also taken when a selector is neither 0 nor 1, and by the other operations).
+        template <int OP>
+        __device__ __forceinline__ Fr row_denominator(const ScanArgs& a, uint64_t e, int* side)
+        {
+            *side = 3;
+            if (OP == kLogup)
+            {
+                const Fr sel_t = col_load_stored(a.c3, e), sel_q = col_load_stored(a.c4, e);
+                const bool t_on = !sel_t.is_zero(), q_on = !sel_q.is_zero();
+                const bool plain = (!t_on || stored_is_one(a.c3, sel_t)) && (!q_on || stored_is_one(a.c4, sel_q));
+                if (plain) *side = (t_on ? 1 : 0) | (q_on ? 2 : 0);
+                if (*side == 0) return Fr::one();
+                if (*side == 1) return add(col_load_stored(a.c0, e), beta_for(a, a.c0));
+                if (*side == 2) return add(col_load_stored(a.c1, e), beta_for(a, a.c1));
+            }
+            return denominator<OP>(a, e);
+        }
+
         template <int OP>
         __global__ void __launch_bounds__(kThreads) scan_products_kernel(ScanArgs a)
         {
@@ -103,8 +124,9 @@ namespace gzk
                 const uint64_t e = base + j;
                 if (e < a.count)
                 {
-                    const Fr d = denominator<OP>(a, e);
-                    if (d.is_zero()) atomicExch(a.status, GZK_E_DOMAIN);
+                    int side;
+                    const Fr d = row_denominator<OP>(a, e, &side);
+                    if (d.is_zero()) raise_status(a.status, GZK_E_DOMAIN, 1401);
                     prod = mul(prod, d);
                 }
             }
@@ -144,12 +166,14 @@ namespace gzk
             if (OP == kLogup || OP == kRouteNode || OP == kRouteEdge)
             {
                 Fr d[kElems], pre[kElems];
+                int side[kElems];
                 Fr mine = Fr::one();
 #pragma unroll
                 for (int j = 0; j < kElems; ++j)
                 {
                     const uint64_t e = base + j;
-                    d[j] = e < a.count ? denominator<OP>(a, e) : Fr::one();
+                    side[j] = 3;
+                    d[j] = e < a.count ? row_denominator<OP>(a, e, &side[j]) : Fr::one();
                     pre[j] = mine;
                     mine = mul(mine, d[j]);
                 }
@@ -159,7 +183,7 @@ namespace gzk
                     const Fr total = block_product<kThreads>(mine, slots);
                     if (threadIdx.x == 0)
                     {
-                        if (total.is_zero()) atomicExch(a.status, GZK_E_DOMAIN);
+                        if (total.is_zero()) raise_status(a.status, GZK_E_DOMAIN, 1402);
                         local_inverse = inv(total);
                     }
                     __syncthreads();
@@ -180,6 +204,20 @@ namespace gzk
                     if (e >= a.count)
                     {
                         term[j] = Fr::zero();
+                    }
+                    else if (OP == kLogup && side[j] == 0)
+                    {
+                        term[j] = Fr::zero();
+                    }
+                    else if (OP == kLogup && side[j] == 1)
+                    {
+                        // inverse = R^d0/(T+b); the selector is one, so the weight is the multiplicity itself
+                        term[j] = fix_scale(mul(col_load_stored(a.c2, e), inverse), deficit(a.c2) - deficit(a.c0));
+                    }
+                    else if (OP == kLogup && side[j] == 2)
+                    {
+                        // inverse = R^d1/(Q+b), the selector is one: the term is -1/(Q+b)
+                        term[j] = sub(Fr::zero(), fix_scale(inverse, -deficit(a.c1)));
                     }
                     else if (OP == kLogup)
                     {
@@ -228,7 +266,7 @@ namespace gzk
                         const Fr q = col_load_stored(a.c1, e);
                         if (!q.is_zero())
                         {
-                            if (!stored_is_one(a.c1, q)) atomicExch(a.status, GZK_E_INVALID);
+                            if (!stored_is_one(a.c1, q)) raise_status(a.status, GZK_E_INVALID, 1403);
                             flag[j] = 1;
                             atomicMin(&first_flag, static_cast<uint32_t>(threadIdx.x * kElems + j));
                         }

@@ -2,6 +2,7 @@
 // Every Backend method is one gzk_* call; columns are gzk_buf handles that live on the GPU from
 // the forward pass to the last opening.  The context runs in deferred mode: builder calls only
 // queue kernels, the host reads values back once per commit barrier.
+#include <atomic>
 #include <cstring>
 
 #include "../../include/gatzk_b200.h"
@@ -18,6 +19,10 @@ namespace
         gzk_buf* buf = nullptr;
         ~GpuCol() override;
     };
+
+    // test hook: fill every buffer handed out by alloc() with a byte pattern, so that a column builder that
+    // reads a row nobody wrote shows up as a wrong proof instead of depending on what the memory held before
+    std::atomic<int> g_poison_allocations{0};
 
     class GpuBackend : public Backend
     {
@@ -66,6 +71,15 @@ namespace
             else
             {
                 check(gzk_buf_alloc(ctx_, kind, count, &c->buf));
+            }
+            if (g_poison_allocations.load() != 0 && count != 0)
+            {
+                // canonical field elements for the field kinds (an upload checks nothing but converts them), 0xA5 bytes otherwise
+                const std::size_t bytes = count * element_bytes(kind);
+                std::vector<std::uint8_t> pattern(bytes, 0xA5);
+                if (kind == kFr || kind == kFrMont || kind == kG1)
+                    for (std::size_t i = 31; i < bytes; i += 32) pattern[i] = 0x05;
+                check(gzk_buf_upload(ctx_, c->buf, 0, pattern.data(), count));
             }
             return c;
         }
@@ -335,5 +349,6 @@ extern "C"
     {
         return gatzk_flow::flow_domain_labels_impl(flow, domain, out, cap);
     }
+    void gzk_flow_debug_poison_allocations(int on) { g_poison_allocations.store(on); }
     void* gzk_flow_context(gzk_flow* flow) { return flow == nullptr ? nullptr : static_cast<GpuBackend*>(flow->backend.get())->context(); }
 }

@@ -112,3 +112,30 @@ def test_prefix_stored_gpu_proof_equals_whole_domain_cpu_proof(shape):
         full.close()
     cpu.close()
     gpu.close()
+
+
+def test_no_builder_reads_a_row_nobody_wrote():
+    """With every fresh device buffer of the flow filled with a byte pattern, the GPU proof is still the CPU
+    proof: no kernel of the flow depends on the previous contents of its output or scratch buffers."""
+    import ctypes
+
+    from project_b200.flow import FLOW_LIB_PATH
+    from project_b200.lib import load_library
+
+    load_library()
+    hook = ctypes.CDLL(FLOW_LIB_PATH).gzk_flow_debug_poison_allocations
+    for shape, compact in ((dict(seed=3, nodes=50, directed_edges=200, feature_count=9, hidden=[(2, 3), (2, 2)], output_heads=1, class_count=4), False),
+                           (dict(seed=1, nodes=40, directed_edges=120, feature_count=12, hidden=[(2, 4)], output_heads=2, class_count=3), True)):
+        inputs = synthetic.make_inputs(**shape)
+        cpu = Flow(ora.lib(), "ora_flow_", 4, inputs, G)
+        cpu.prove()
+        hook(1)
+        try:
+            gpu = gpu_flow(0, inputs, G, compact_columns=compact)
+            gpu.prove()
+            gpu.prove()
+        finally:
+            hook(0)
+        assert first_difference(gpu.dump(), cpu.dump()) is None
+        cpu.close()
+        gpu.close()
