@@ -161,6 +161,19 @@ int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t le
 int gzk_eval_batch_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                           const gzk_buf* weights, const uint64_t* rotations, size_t p_count, gzk_buf* out, size_t out_offset);
 
+/* The same accumulator for a lookup into a banded static table, computed without one inversion per
+ * row.  Every query (x[i], y[i]) equals some table row - the lookup argument proves exactly that, and
+ * gzk_banded_lookup_multiplicity has located the row already - so 1/(query_i + beta) is one of the
+ * table_size values 1/(table_t + beta).  Those are inverted once (pass 0), and the accumulator's
+ * term of row i becomes  [i < table_size] multiplicity[i] / (table_i + beta)  -  1/(table_{hit(i)} + beta),
+ * a 32-byte fetch per row.  The selectors are taken to be the prefix indicators the reference builds
+ * (table rows first, queries on rows < active_count; src/protocol/prover.cpp:460-535), x_min / band /
+ * table_y describe the table as in gzk_banded_lookup_multiplicity.  Same output as
+ * gzk_logup_accumulator on the packed columns (src/protocol/lookup.cpp:100-157); a query outside
+ * the table raises GZK_E_INVALID. */
+int gzk_logup_accumulator_indexed(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* multiplicity, const gzk_buf* x, const gzk_buf* y,
+                                  size_t active_count, int64_t x_min, size_t band, const gzk_buf* table_y, size_t table_size, size_t n,
+                                  const uint8_t beta[32], gzk_buf* out);
 /* ---- a7: LogUp and route running sums ----------------------------------------------
  * Input columns may be of any kind; `out` is FR_MONT with count >= n.  One batch
  * inversion per call; GZK_E_DOMAIN ("batch_invert encountered zero") when a

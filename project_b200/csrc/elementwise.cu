@@ -119,30 +119,39 @@ namespace gzk
             if (mine != 0) atomicAdd(flagged, mine);
         }
 
-        // one thread per destination group: mark the first row whose delta is zero
+        // one warp per destination group: mark the first row whose delta is zero.  The lanes test 32 rows at a
+        // time (a hub of a power-law graph has tens of thousands of incoming edges; one thread walking them
+        // would outlast the rest of the grid).
         __global__ void first_zero_kernel(ColRef delta, ColRef group_begin, ColRef group_end, uint64_t groups, uint64_t n, uint32_t* out,
                                           int* status)
         {
-            for (uint64_t g = grid_index(); g < groups; g += grid_stride())
+            const uint32_t lane = threadIdx.x & 31;
+            const uint64_t warps = grid_stride() >> 5;
+            for (uint64_t g = grid_index() >> 5; g < groups; g += warps)
             {
                 const uint64_t b = index_at(group_begin, g), e = index_at(group_end, g);
                 if (e > n || b > e)
                 {
-                    raise_status(status, GZK_E_INVALID, 503);
+                    if (lane == 0) raise_status(status, GZK_E_INVALID, 503);
                     continue;
                 }
-                for (uint64_t k = b; k < e; ++k)
+                for (uint64_t base = b; base < e; base += 32)
                 {
-                    bool zero;
-                    if (delta.kind == GZK_KIND_I64)
-                        zero = __ldg(static_cast<const long long*>(delta.ptr) + k) == 0;
-                    else if (delta.kind == GZK_KIND_U32)
-                        zero = __ldg(static_cast<const uint32_t*>(delta.ptr) + k) == 0;
-                    else
-                        zero = load_fr(static_cast<const Fr*>(delta.ptr) + k).is_zero();
-                    if (zero)
+                    const uint64_t k = base + lane;
+                    bool zero = false;
+                    if (k < e)
                     {
-                        out[k] = 1;
+                        if (delta.kind == GZK_KIND_I64)
+                            zero = __ldg(static_cast<const long long*>(delta.ptr) + k) == 0;
+                        else if (delta.kind == GZK_KIND_U32)
+                            zero = __ldg(static_cast<const uint32_t*>(delta.ptr) + k) == 0;
+                        else
+                            zero = load_fr(static_cast<const Fr*>(delta.ptr) + k).is_zero();
+                    }
+                    const uint32_t hits = __ballot_sync(0xffffffffu, zero);
+                    if (hits != 0)
+                    {
+                        if (lane == static_cast<uint32_t>(__ffs(hits) - 1)) out[k] = 1;
                         break;
                     }
                 }
@@ -355,7 +364,7 @@ extern "C"
                 !index_kind_ok(group_end) || group_begin->count < groups || group_end->count < groups)
                 return fail(ctx, GZK_E_INVALID, "first_zero_marker: input size mismatch");
             LaunchScope scope(ctx, "first_zero");
-            first_zero_kernel<<<blocks_for(ctx, groups), kThreads, 0, ctx->stream>>>(ref(delta), ref(group_begin), ref(group_end), groups,
+            first_zero_kernel<<<blocks_for(ctx, groups * 32), kThreads, 0, ctx->stream>>>(ref(delta), ref(group_begin), ref(group_end), groups,
                                                                                      delta->count < domain_size ? delta->count : domain_size,
                                                                                      static_cast<uint32_t*>(out->dptr), ctx->d_status);
         }

@@ -18,12 +18,17 @@ namespace gzk
         struct CombineArgs
         {
             ColRef cols[kMaxTerms];
-            Fr coeff[kMaxTerms];      // Montgomery form
-            uint32_t unit[kMaxTerms]; // coefficient is 1: the term is added without a multiplication
+            Fr k_pos[kMaxTerms];  // coefficient * 2^288 (* R for the kinds stored as plain residues), see combine_kernel
+            Fr k_neg[kMaxTerms];  // r - k_pos, for negative small integers
             uint32_t terms;
         };
 
-        // out[i] = sum_j coeff[j] * col_j[i] for i < count, zero tail.
+        // out[i] = sum_j coeff[j] * col_j[i] for i < count, zero tail.  The sum of a row is formed as ONE exact
+        // integer, sum_j k_j * v_j with v_j the stored value (one or two limbs for the small-integer kinds,
+        // eight for field elements), and reduced once: nine reduction rows divide by 2^288, which the
+        // constants k_j = coeff_j * 2^288 (times R when the column holds plain residues) undo, so the result
+        // is the Montgomery form of the sum.  A row of two small-integer terms costs 32 + 72 limb products
+        // instead of the four full field multiplications (512) of converting and scaling each value.
         __global__ void combine_kernel(CombineArgs a, uint64_t count, uint64_t n, Fr* out)
         {
             for (uint64_t i = grid_index(); i < n; i += grid_stride())
@@ -31,14 +36,36 @@ namespace gzk
                 Fr v = Fr::zero();
                 if (i < count)
                 {
+                    WideAcc acc;
+                    acc.clear();
 #pragma unroll 1
                     for (uint32_t j = 0; j < a.terms; ++j)
                     {
-                        // a Montgomery coefficient times a canonical value is the canonical product; one
-                        // conversion per canonical term keeps the sum in Montgomery form
-                        const Fr x = col_load_mont(a.cols[j], i);
-                        v = add(v, a.unit[j] ? x : mul(a.coeff[j], x));
+                        const ColRef& c = a.cols[j];
+                        if (c.kind == GZK_KIND_FR || c.kind == GZK_KIND_FR_MONT)
+                        {
+                            const Fr x = load_fr(static_cast<const Fr*>(c.ptr) + i);
+                            acc.mac<8>(a.k_pos[j].l, x.l);
+                        }
+                        else if (c.kind == GZK_KIND_U32)
+                        {
+                            const uint32_t x = __ldg(static_cast<const uint32_t*>(c.ptr) + i);
+                            acc.mac<1>(a.k_pos[j].l, &x);
+                        }
+                        else
+                        {
+                            const long long x = __ldg(static_cast<const long long*>(c.ptr) + i);
+                            const unsigned long long mag = x < 0 ? 0ULL - static_cast<unsigned long long>(x) : static_cast<unsigned long long>(x);
+                            const uint32_t f[2] = {static_cast<uint32_t>(mag), static_cast<uint32_t>(mag >> 32)};
+                            if (x < 0)
+                                acc.mac<2>(a.k_neg[j].l, f);
+                            else
+                                acc.mac<2>(a.k_pos[j].l, f);
+                        }
                     }
+                    uint32_t sum[17];
+                    acc.fold(sum);
+                    v = redc_wide<FrCfg, 9>(sum);
                 }
                 store_fr(out + i, v);
             }
@@ -219,8 +246,13 @@ extern "C"
             const Fr c = host_fr_from_bytes(coefficients + 32 * j, &canonical);
             if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
             args.cols[j] = ref(cols[j]);
-            args.coeff[j] = to_mont(c);
-            args.unit[j] = (c.l[0] == 1u && (c.l[1] | c.l[2] | c.l[3] | c.l[4] | c.l[5] | c.l[6] | c.l[7]) == 0u) ? 1u : 0u;
+            // 2^288 in Montgomery form, by doubling
+            Fr two288 = Fr::one();
+            for (int d = 0; d < 288; ++d) two288 = add(two288, two288);
+            Fr k = mul(to_mont(c), two288);  // c * R * 2^288: for columns of plain residues (FR, I64, U32)
+            if (cols[j]->kind == GZK_KIND_FR_MONT) k = from_mont(k);  // the stored value already carries R
+            args.k_pos[j] = k;
+            args.k_neg[j] = sub(Fr::zero(), k);
         }
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
         {

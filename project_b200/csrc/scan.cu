@@ -37,6 +37,7 @@ namespace gzk
             kRouteEdge = 2,  // term = 1/(query+beta)
             kProduct = 3,    // term = a*b
             kSegmented = 4,  // term = value, running sum restarts where q_new = 1
+            kLogupIndexed = 5,  // the LogUp term with every inverse fetched from a table of 1/(T_t+beta), see scan_main_body
         };
 
         struct ScanArgs
@@ -53,6 +54,12 @@ namespace gzk
             uint32_t* agg_first;  // first row (CTA-relative) that starts a segment, kChunk if none
             Fr* total;            // grand total (Montgomery)
             int* status;
+            // kLogupIndexed: c0 / c1 hold the integer query keys (x, y), c2 the multiplicities
+            const Fr* inv_table;       // 1/(T_t + beta) for every table row t, Montgomery form
+            const long long* table_y;  // second key column of the banded table (null: single-column table)
+            uint64_t table_size;
+            long long x_min;
+            uint32_t band;
         };
 
         // ---- residues with a tracked power of R --------------------------------------------
@@ -89,6 +96,41 @@ namespace gzk
             const Fr tb = add(col_load_stored(a.c0, e), beta_for(a, a.c0));
             if (OP == kLogup) return mul(tb, add(col_load_stored(a.c1, e), beta_for(a, a.c1)));
             return tb;
+        }
+
+        // inv_out[t] = 1/(table[t] + beta) in Montgomery form, t < count: the per-CTA batch inversion of the
+        // main pass on its own (each CTA inverts the product of its 512 denominators).
+        __global__ void __launch_bounds__(kThreads) shifted_inverse_kernel(ScanArgs a, Fr* inv_out)
+        {
+            __shared__ Fr slots[3 * kWarps];
+            __shared__ Fr local_inverse;
+            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * kChunk + static_cast<uint64_t>(threadIdx.x) * kElems;
+            Fr d[kElems], pre[kElems];
+            Fr mine = Fr::one();
+#pragma unroll
+            for (int j = 0; j < kElems; ++j)
+            {
+                const uint64_t e = base + j;
+                d[j] = e < a.count ? add(col_load_stored(a.c0, e), beta_for(a, a.c0)) : Fr::one();
+                pre[j] = mine;
+                mine = mul(mine, d[j]);
+            }
+            const Fr total = block_product<kThreads>(mine, slots);
+            if (threadIdx.x == 0)
+            {
+                if (total.is_zero()) raise_status(a.status, GZK_E_DOMAIN, 1404);
+                local_inverse = inv(total);
+            }
+            __syncthreads();
+            Fr rest = block_invert_products<kThreads>(mine, local_inverse, slots);
+#pragma unroll
+            for (int j = kElems - 1; j >= 0; --j)
+            {
+                const uint64_t e = base + j;
+                const Fr inverse = mul(rest, pre[j]);
+                if (j > 0) rest = mul(rest, d[j]);
+                if (e < a.count) store_fr(inv_out + e, fix_scale(inverse, -deficit(a.c0)));
+            }
         }
 
         // LogUp rows with only one side switched on by its 0/1 selector (almost all of them: the table
@@ -259,6 +301,54 @@ namespace gzk
                     else if (OP == kProduct)
                     {
                         term[j] = fix_scale(mul(col_load_stored(a.c0, e), col_load_stored(a.c1, e)), deficit(a.c0) + deficit(a.c1));
+                    }
+                    else if (OP == kLogupIndexed)
+                    {
+                        // Every query equals some table row (that is what the lookup proves, and what the
+                        // multiplicity pass has already checked), so 1/(Q_e + beta) IS inv_table[row hit by e]:
+                        // a 32-byte fetch from a table that stays in L2 instead of a share in a batch inversion.
+                        // The table side of row e < table_size is multiplicity[e] * inv_table[e].  Selectors are
+                        // the prefix indicators the reference builds: table rows first, queries on rows < count.
+                        Fr t = Fr::zero();
+                        if (e < a.table_size)
+                        {
+                            const uint32_t m = __ldg(static_cast<const uint32_t*>(a.c2.ptr) + e);
+                            if (m != 0)
+                            {
+                                Fr plain = Fr::zero();
+                                plain.l[0] = m;
+                                t = to_mont(mul(plain, load_fr(a.inv_table + e)));
+                            }
+                        }
+                        const long long rel = (a.c0.kind == GZK_KIND_U32 ? static_cast<long long>(__ldg(static_cast<const uint32_t*>(a.c0.ptr) + e))
+                                                                          : __ldg(static_cast<const long long*>(a.c0.ptr) + e)) - a.x_min;
+                        uint64_t slot = ~0ull;
+                        if (rel >= 0 && static_cast<uint64_t>(rel) * a.band + a.band <= a.table_size)
+                        {
+                            const uint64_t first = static_cast<uint64_t>(rel) * a.band;
+                            if (a.table_y == nullptr)
+                            {
+                                slot = first;
+                            }
+                            else
+                            {
+                                const long long yv = a.c1.kind == GZK_KIND_U32 ? static_cast<long long>(__ldg(static_cast<const uint32_t*>(a.c1.ptr) + e))
+                                                                               : __ldg(static_cast<const long long*>(a.c1.ptr) + e);
+                                for (uint32_t b = 0; b < a.band; ++b)
+                                {
+                                    if (__ldg(a.table_y + first + b) == yv)
+                                    {
+                                        slot = first + b;
+                                        break;
+                                    }
+                                }
+                            }
+                        }
+                        if (slot == ~0ull)
+                            raise_status(a.status, GZK_E_INVALID, 1405);
+                        else
+                            t = sub(t, load_fr(a.inv_table + slot));
+                        term[j] = t;
                     }
                     else
                     {
@@ -537,7 +627,7 @@ namespace gzk
         }
 
         template <int OP>
-        int run_scan(gzk_ctx* ctx, ScanArgs& args, bool inverting, uint8_t* total_out_host)
+        int run_scan(gzk_ctx* ctx, ScanArgs& args, bool inverting, uint8_t* total_out_host, bool call_begun = false)
         {
             GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
             const uint64_t span = OP == kSegmented ? args.n : args.count;
@@ -554,7 +644,7 @@ namespace gzk
             args.agg_flag = reinterpret_cast<uint32_t*>(base + 3 * static_cast<size_t>(ctas) + 2);
             args.agg_first = args.agg_flag + ctas;
             args.status = ctx->d_status;
-            if ((rc = begin_call(ctx)) != GZK_OK) return rc;
+            if (!call_begun && (rc = begin_call(ctx)) != GZK_OK) return rc;
             const bool local_inverse = inverting && ctas <= static_cast<uint32_t>(ctx->sm_count) * 4;
             if (inverting && !local_inverse)
             {
@@ -566,7 +656,7 @@ namespace gzk
                 if ((rc = launch_batch_invert_single_cta(ctx, args.cta_products, tmp, ctas)) != GZK_OK) return rc;
             }
             {
-                LaunchScope scope(ctx, OP == kLogup ? "scan_main_logup" : OP == kRouteNode ? "scan_main_route_node" : OP == kRouteEdge ? "scan_main_route_edge"
+                LaunchScope scope(ctx, OP == kLogup ? "scan_main_logup" : OP == kLogupIndexed ? "scan_main_logup_indexed" : OP == kRouteNode ? "scan_main_route_node" : OP == kRouteEdge ? "scan_main_route_edge"
                                        : OP == kProduct ? "scan_main_product" : "scan_main_segmented");
                 if (local_inverse)
                     scan_main_kernel<OP, true><<<ctas, kThreads, 0, ctx->stream>>>(args);
@@ -637,6 +727,51 @@ using namespace gzk;
 
 extern "C"
 {
+    int gzk_logup_accumulator_indexed(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* multiplicity, const gzk_buf* x, const gzk_buf* y,
+                                      size_t active_count, int64_t x_min, size_t band, const gzk_buf* table_y, size_t table_size, size_t n,
+                                      const uint8_t beta[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (beta == nullptr || !out_ok(out, n)) return fail(ctx, GZK_E_INVALID, "logup: output must be a Montgomery buffer of n elements");
+        if (n > 0 && active_count > n - 1) active_count = n - 1;  // lookup.cpp:117
+        if (n == 0) return GZK_OK;
+        const bool has_y = y != nullptr;
+        auto keys_ok = [&](const gzk_buf* b) { return b != nullptr && (b->kind == GZK_KIND_I64 || b->kind == GZK_KIND_U32) && b->count >= active_count; };
+        if (band == 0 || band > 64 || table_size == 0 || table_size % band != 0 || table_size > n || has_y != (table_y != nullptr) || (!has_y && band != 1))
+            return fail(ctx, GZK_E_INVALID, "logup (indexed): the table must hold a whole number of bands and fit the column");
+        if (!col_ok(table, table_size) || multiplicity == nullptr || multiplicity->kind != GZK_KIND_U32 || multiplicity->count < table_size || !keys_ok(x) ||
+            (has_y && (!keys_ok(y) || table_y->kind != GZK_KIND_I64 || table_y->count < table_size)))
+            return fail(ctx, GZK_E_INVALID, "lookup accumulator input size mismatch");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        ScanArgs args{};
+        int rc = load_scalar(ctx, beta, &args.beta, &args.beta_canon);
+        if (rc != GZK_OK) return rc;
+        void* scratch = nullptr;
+        if ((rc = ensure_scratch(ctx, 1, table_size * sizeof(Fr), &scratch)) != GZK_OK) return rc;
+        // pass 0: the inverses of the shifted table
+        args.c0 = ref(table);
+        args.count = table_size;
+        args.status = ctx->d_status;
+        if ((rc = begin_call(ctx)) != GZK_OK) return rc;
+        {
+            LaunchScope scope(ctx, "logup_table_inverses");
+            shifted_inverse_kernel<<<static_cast<unsigned>((table_size + kChunk - 1) / kChunk), kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(scratch));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        args.c0 = ref(x);
+        args.c1 = has_y ? ref(y) : ref(x);
+        args.c2 = ref(multiplicity);
+        args.count = active_count;
+        args.n = n;
+        args.out = static_cast<Fr*>(out->dptr);
+        args.inv_table = static_cast<const Fr*>(scratch);
+        args.table_y = has_y ? static_cast<const long long*>(table_y->dptr) : nullptr;
+        args.table_size = table_size;
+        args.x_min = static_cast<long long>(x_min);
+        args.band = static_cast<uint32_t>(band);
+        return run_scan<kLogupIndexed>(ctx, args, false, nullptr, true);
+    }
+
     int gzk_logup_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* query, const gzk_buf* multiplicity,
                               const gzk_buf* q_table, const gzk_buf* q_query, size_t n, const uint8_t beta[32],
                               size_t active_count, gzk_buf* out)

@@ -206,6 +206,21 @@ namespace
             std::vector<ScanJob> small_jobs, long_jobs;
             for (const ScanJob& j : jobs)
                 ((j.op == ScanJob::kGroupPrefix ? j.domain_size : j.count) > kBatchRows ? long_jobs : small_jobs).push_back(j);
+            for (auto it = long_jobs.begin(); it != long_jobs.end();)
+            {
+                // a long lookup accumulator: inverses fetched from the table (one inversion per table row, not per query)
+                if (it->op == ScanJob::kLogup && it->key_x != nullptr && it->table_size != 0 && it->table_size <= it->count)
+                {
+                    check(gzk_logup_accumulator_indexed(ctx_, raw(it->c0), raw(it->c2), raw(it->key_x), it->key_y ? raw(it->key_y) : nullptr, it->count,
+                                                        it->x_min, it->band, it->table_y ? raw(it->table_y) : nullptr, it->table_size, it->domain_size,
+                                                        it->beta.data(), raw(it->out)));
+                    it = long_jobs.erase(it);
+                }
+                else
+                {
+                    ++it;
+                }
+            }
             if (!long_jobs.empty()) Backend::running_sums_batch(long_jobs);
             if (small_jobs.empty()) return;
             std::vector<gzk_scan_job> raw_jobs(small_jobs.size());

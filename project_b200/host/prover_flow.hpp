@@ -85,6 +85,11 @@ namespace gatzk_flow
         std::size_t count = 0, domain_size = 0;
         Fe beta{};
         ColP out;
+        // kLogup of a lookup into a banded static table: the integer keys of the queries and the shape of the
+        // table, for backends that fetch the inverses from the table instead of inverting every row
+        ColP key_x, key_y, table_y;
+        std::int64_t x_min = 0;
+        std::size_t band = 0, table_size = 0;
     };
 
     // The compute backend: every call is one data-parallel leaf of the hot path.
@@ -633,6 +638,7 @@ namespace gatzk_flow
         std::map<std::string, ColP> param_matrices_;            // quantised seq_kernel per head label (I64)
         std::map<std::string, Commitment> static_commitments_;
         std::map<std::string, ColumnEntry> static_columns_;
+        std::map<std::string, Fe> static_omega_tau_;  // value of a key-dependent column at omega * tau (filled by the first proof)
         Fe fh_public_tau_[5], fh_public_omega_tau_[5];
         // per-proof state
         std::map<std::string, Commitment> commitments_;
@@ -1116,6 +1122,13 @@ namespace gatzk_flow
         be_.lookup_multiplicity(left, table_y != nullptr ? right : nullptr, valid, x_min, band, table_y, table_size, store, out.multiplicity);
         out.acc = be_.alloc(kFrMont, store);
         queue_scan(ScanJob::kLogup, out.table, out.query, out.multiplicity, q_table, q_query, std::min(valid, e.size - 1), store, beta, out.acc);
+        ScanJob& job = scan_queue_.back();
+        job.key_x = left;
+        job.key_y = table_y != nullptr ? right : nullptr;
+        job.table_y = table_y;
+        job.x_min = x_min;
+        job.band = band;
+        job.table_size = table_size;
         return out;
     }
 

@@ -471,27 +471,39 @@ namespace gatzk_flow
         const Fe alpha_quot = challenge(t, "alpha_quot");
         static const char* kDomains[7] = {"FH", "edge", "in", "d", "cat", "C", "N"};
         static const char* kBundles[7] = {"FH", "edge", "in", "d_h", "cat", "C", "N"};
-        // all columns of a domain evaluated at two points: grouped by stored length, one result buffer
-        auto evaluate_domain = [&](const std::string& domain, const ColP& weights, std::map<std::string, std::array<Fe, 2>>& out) {
+        // All columns of a domain evaluated at two points (the point of `weights` and omega times it): grouped
+        // by stored length, one result buffer.  With at_tau the point is tau itself: the first value of every
+        // column is the evaluation its commitment was made from, and the key-dependent columns' values at
+        // omega*tau are computed once per context, so only rotation 1 of the witness columns is evaluated.
+        auto evaluate_domain = [&](const std::string& domain, const ColP& weights, bool at_tau, std::map<std::string, std::array<Fe, 2>>& out) {
             const auto it = opened_.find(domain);
             std::vector<std::string> labels = it == opened_.end() ? std::vector<std::string>{} : it->second;
             for (const auto& item : static_columns_)
-                if (item.second.domain == domain) labels.push_back(item.first);
+            {
+                if (item.second.domain != domain) continue;
+                const auto cached = static_omega_tau_.find(item.first);
+                if (at_tau && cached != static_omega_tau_.end())
+                    out[item.first] = {static_commitments_.at(item.first).tau_evaluation, cached->second};
+                else
+                    labels.push_back(item.first);
+            }
             if (labels.empty()) return;
             const Domain& d = dom_.at(domain);
+            const std::vector<std::uint64_t> rotations = at_tau ? std::vector<std::uint64_t>{1} : std::vector<std::uint64_t>{0, 1};
+            const std::size_t points = rotations.size();
             std::map<std::size_t, std::vector<std::string>> by_length;
             for (const auto& label : labels)
             {
                 const auto c = columns_.find(label);
                 by_length[c != columns_.end() ? c->second.length : static_columns_.at(label).length].push_back(label);
             }
-            const ColP result = be_.alloc(kFr, 2 * labels.size());
+            const ColP result = be_.alloc(kFr, points * labels.size());
             std::size_t offset = 0;
             struct Placed
             {
                 std::size_t offset;
                 const std::vector<std::string>* labels;
-                std::size_t ones;  // slot pair of the ones column of this length, or npos
+                std::size_t ones;  // first slot of the ones column of this length, or npos
             };
             constexpr std::size_t npos = static_cast<std::size_t>(-1);
             std::vector<Placed> placed;
@@ -506,7 +518,7 @@ namespace gatzk_flow
                         break;
                     }
                 }
-            const ColP ones_out = tail_groups == 0 ? nullptr : be_.alloc(kFr, 2 * tail_groups);
+            const ColP ones_out = tail_groups == 0 ? nullptr : be_.alloc(kFr, points * tail_groups);
             std::size_t ones_next = 0;
             for (const auto& group : by_length)
             {
@@ -518,18 +530,18 @@ namespace gatzk_flow
                     cols.push_back(c != columns_.end() ? c->second.col : static_columns_.at(label).col);
                     has_tail = has_tail || (c != columns_.end() && c->second.const_tail);
                 }
-                be_.eval_device(cols, group.first, d.log2n, weights, {0, 1}, result, offset);
+                be_.eval_device(cols, group.first, d.log2n, weights, rotations, result, offset);
                 std::size_t ones = npos;
                 if (has_tail)
                 {
                     ones = ones_next;
-                    be_.eval_device({ones_col(group.first)}, group.first, d.log2n, weights, {0, 1}, ones_out, ones_next);
-                    ones_next += 2;
+                    be_.eval_device({ones_col(group.first)}, group.first, d.log2n, weights, rotations, ones_out, ones_next);
+                    ones_next += points;
                 }
                 placed.push_back({offset, &group.second, ones});
-                offset += 2 * cols.size();
+                offset += points * cols.size();
             }
-            std::vector<Fe> host(2 * labels.size()), ones_host(2 * tail_groups);
+            std::vector<Fe> host(points * labels.size()), ones_host(points * tail_groups);
             be_.download(result, 0, host.size(), host.data());
             if (tail_groups != 0) be_.download(ones_out, 0, ones_host.size(), ones_host.data());
             for (const auto& p : placed)
@@ -537,14 +549,29 @@ namespace gatzk_flow
                 const std::size_t k = p.labels->size();
                 for (std::size_t i = 0; i < k; ++i)
                 {
-                    std::array<Fe, 2> value = {host[p.offset + i], host[p.offset + k + i]};
-                    const auto c = columns_.find((*p.labels)[i]);
-                    if (c != columns_.end() && c->second.const_tail)
+                    const std::string& label = (*p.labels)[i];
+                    const auto c = columns_.find(label);
+                    Fe value[2];
+                    for (std::size_t r = 0; r < points; ++r)
                     {
+                        value[r] = host[p.offset + r * k + i];
                         // rows beyond the stored prefix hold the running sum's final value (see commit_batch)
-                        for (int r = 0; r < 2; ++r) value[r] = add(value[r], mul(c->second.tail, sub(fe_u64(1), ones_host[p.ones + r])));
+                        if (c != columns_.end() && c->second.const_tail)
+                            value[r] = add(value[r], mul(c->second.tail, sub(fe_u64(1), ones_host[p.ones + r])));
                     }
-                    out[(*p.labels)[i]] = value;
+                    if (!at_tau)
+                    {
+                        out[label] = {value[0], value[1]};
+                    }
+                    else if (c != columns_.end())
+                    {
+                        out[label] = {commitments_.at(label).tau_evaluation, value[0]};
+                    }
+                    else
+                    {
+                        static_omega_tau_[label] = value[0];
+                        out[label] = {static_commitments_.at(label).tau_evaluation, value[0]};
+                    }
                 }
             }
         };
@@ -555,7 +582,7 @@ namespace gatzk_flow
         {
             const Domain& d = dom_.at(kDomains[di]);
             std::map<std::string, std::array<Fe, 2>> values;
-            evaluate_domain(kDomains[di], d.w_tau, values);
+            evaluate_domain(kDomains[di], d.w_tau, true, values);
             if (std::string(kDomains[di]) == "FH")
             {
                 // generated public columns at tau and omega*tau (prepared with the key) and P_H
@@ -601,7 +628,7 @@ namespace gatzk_flow
             const ColP w_z = be_.alloc(kFrMont, d.size);
             be_.bary_weights(d.log2n, z0, w_z);
             std::map<std::string, std::array<Fe, 2>> values;
-            evaluate_domain(kDomains[di], w_z, values);
+            evaluate_domain(kDomains[di], w_z, false, values);
             std::vector<std::string> labels = domain_labels(kDomains[di]);
             if (std::string(kDomains[di]) == "FH")
             {

@@ -221,6 +221,30 @@ class Backend:
                                                    _sz(n), _ptr(_fr(beta)), _sz(active_count), out.handle))
         return out
 
+    def logup_accumulator_indexed(self, table, mult, x, y, active_count, x_min, band, table_y, table_size, n, beta, out=None):
+        """LogUp accumulator of a lookup into a banded static table with the inverses fetched per table row."""
+        out = out or self.alloc(KIND_FR_MONT, n)
+        self._check(self.lib.gzk_logup_accumulator_indexed(self.ctx, table.handle, mult.handle, x.handle, y.handle if y is not None else None,
+                                                           _sz(active_count), ctypes.c_int64(x_min), _sz(band),
+                                                           table_y.handle if table_y is not None else None, _sz(table_size), _sz(n), _ptr(_fr(beta)),
+                                                           out.handle))
+        return out
+
+    def linear_combination(self, cols, coefficients, count, domain_size, out=None):
+        """out[i] = sum_j coefficients[j] * cols[j][i] for i < count, zero tail (Montgomery buffer)."""
+        handles = (ctypes.c_void_p * len(cols))(*[c.handle for c in cols])
+        coeff = np.ascontiguousarray(coefficients, dtype=np.uint8).reshape(len(cols), 32)
+        out = out or self.alloc(KIND_FR_MONT, domain_size)
+        self._check(self.lib.gzk_linear_combination(self.ctx, handles, _ptr(coeff), _sz(len(cols)), _sz(count), _sz(domain_size), out.handle))
+        return out
+
+    def banded_lookup_multiplicity(self, x, y, count, x_min, band, table_y, table_size, domain_size, out=None):
+        out = out or self.alloc(KIND_U32, domain_size)
+        self._check(self.lib.gzk_banded_lookup_multiplicity(self.ctx, x.handle, y.handle if y is not None else None, _sz(count), ctypes.c_int64(x_min),
+                                                            _sz(band), table_y.handle if table_y is not None else None, _sz(table_size),
+                                                            _sz(domain_size), out.handle))
+        return out
+
     def route_node_accumulator(self, table, mult, valid_length, domain_size, beta, out=None):
         out = out or self.alloc(KIND_FR_MONT, domain_size)
         self._check(self.lib.gzk_route_node_accumulator(self.ctx, table.handle, mult.handle, _sz(valid_length), _sz(domain_size),

@@ -413,3 +413,51 @@ def test_running_sums_batch_reports_a_zero_denominator(be):
     beta = fr_array([R - 3])  # query + beta = 0 in every row
     with pytest.raises(GzkError, match="batch_invert encountered zero"):
         be.running_sums_batch([(SCAN_ROUTE_EDGE, [be.upload(q, KIND_FR)], 10, n, beta, be.alloc(KIND_FR_MONT, n))])
+
+
+@pytest.mark.parametrize("has_y", [True, False])
+def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y):
+    """A lookup into a banded static table: the accumulator with the inverses fetched from the table's own
+    1/(T_t + beta) must equal, element for element, the one that inverts every row (and the oracle's)."""
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, GzkError
+
+    rng = np.random.default_rng(77 + has_y)
+    band = 3 if has_y else 1
+    xs = 700
+    x_min = -350
+    table_size = xs * band
+    n = 70000
+    valid = 66001
+    table_x = np.repeat(np.arange(x_min, x_min + xs, dtype=np.int64), band)
+    table_y = (table_x * 7 + np.tile(np.arange(band, dtype=np.int64), xs) - 1) if has_y else None
+    pick = rng.integers(0, table_size, size=valid)
+    pick[:5000] = 17 * band  # a hot row
+    qx = table_x[pick]
+    qy = table_y[pick] if has_y else None
+    eta = fr_array([0x1234567])
+    beta = fr_array([int(rng.integers(1, 1 << 62))])
+    pad = lambda v: np.concatenate([v, np.zeros(n - v.size, dtype=np.int64)])
+    bx, by = be.upload(pad(qx), KIND_I64), (be.upload(pad(qy), KIND_I64) if has_y else None)
+    btx, bty = be.upload(pad(table_x), KIND_I64), (be.upload(pad(table_y), KIND_I64) if has_y else None)
+    mult = be.banded_lookup_multiplicity(bx, by, valid, x_min, band, bty, table_size, n)
+    if has_y:
+        one = fr_array([1])
+        table = be.linear_combination([btx, bty], np.concatenate([one, eta]), table_size, n)
+        query = be.linear_combination([bx, by], np.concatenate([one, eta]), valid, n)
+    else:
+        table, query = btx, bx
+    qt, qq = be.upload(selector(table_size, n), KIND_FR), be.upload(selector(valid, n), KIND_FR)
+    plain = be.logup_accumulator(table, query, mult, qt, qq, n, beta, valid).download()
+    indexed = be.logup_accumulator_indexed(table, mult, bx, by, valid, x_min, band, bty, table_size, n, beta).download()
+    assert np.array_equal(indexed, plain)
+    assert not indexed[-1].any()  # every query is in the table: the sums cancel
+    as_fr = lambda b: b.download() if has_y else ora.fr_from_i64(b.download())
+    want = ora.logup_accumulator(as_fr(table), as_fr(query), ora.fr_from_i64(mult.download().astype(np.int64)), selector(table_size, n),
+                                 selector(valid, n), beta, valid)
+    assert np.array_equal(indexed, want)
+    # a query outside the table is reported
+    bad = pad(qx).copy()
+    bad[3] = x_min + xs + 5
+    with pytest.raises(GzkError) as e:
+        be.logup_accumulator_indexed(table, mult, be.upload(bad, KIND_I64), by, valid, x_min, band, bty, table_size, n, beta)
+    assert e.value.code == 1
