@@ -29,6 +29,9 @@ namespace gzk
         // constants k_j = coeff_j * 2^288 (times R when the column holds plain residues) undo, so the result
         // is the Montgomery form of the sum.  A row of two small-integer terms costs 32 + 72 limb products
         // instead of the four full field multiplications (512) of converting and scaling each value.
+        // SMALL: every term is a small-integer column, so the sum has at most eleven limbs and three reduction
+        // rows are enough (the constants then carry 2^96 instead of 2^288).
+        template <bool SMALL>
         __global__ void combine_kernel(CombineArgs a, uint64_t count, uint64_t n, Fr* out)
         {
             for (uint64_t i = grid_index(); i < n; i += grid_stride())
@@ -65,7 +68,7 @@ namespace gzk
                     }
                     uint32_t sum[17];
                     acc.fold(sum);
-                    v = redc_wide<FrCfg, 9>(sum);
+                    v = SMALL ? redc_wide<FrCfg, 3>(sum) : redc_wide<FrCfg, 9>(sum);
                 }
                 store_fr(out + i, v);
             }
@@ -239,6 +242,8 @@ extern "C"
         if (out->kind != GZK_KIND_FR_MONT || out->count < domain_size) return fail(ctx, GZK_E_INVALID, "linear_combination: output must be a Montgomery buffer of the domain size");
         CombineArgs args{};
         args.terms = static_cast<uint32_t>(terms);
+        bool all_small = true;
+        for (size_t j = 0; j < terms; ++j) all_small = all_small && int_like(cols[j]);
         for (size_t j = 0; j < terms; ++j)
         {
             if (!field_like(cols[j]) || cols[j]->count < count) return fail(ctx, GZK_E_INVALID, "linear_combination: input size mismatch");
@@ -246,9 +251,9 @@ extern "C"
             const Fr c = host_fr_from_bytes(coefficients + 32 * j, &canonical);
             if (!canonical) return fail(ctx, GZK_E_INVALID, "scalar argument is not a canonical field element");
             args.cols[j] = ref(cols[j]);
-            // 2^288 in Montgomery form, by doubling
+            // 2^288 (2^96 when no term is a field-element column) in Montgomery form, by doubling
             Fr two288 = Fr::one();
-            for (int d = 0; d < 288; ++d) two288 = add(two288, two288);
+            for (int d = 0; d < (all_small ? 96 : 288); ++d) two288 = add(two288, two288);
             Fr k = mul(to_mont(c), two288);  // c * R * 2^288: for columns of plain residues (FR, I64, U32)
             if (cols[j]->kind == GZK_KIND_FR_MONT) k = from_mont(k);  // the stored value already carries R
             args.k_pos[j] = k;
@@ -257,7 +262,10 @@ extern "C"
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
         {
             LaunchScope scope(ctx, "linear_combination");
-            combine_kernel<<<blocks_for(ctx, domain_size), kThreads, 0, ctx->stream>>>(args, count, domain_size, static_cast<Fr*>(out->dptr));
+            if (all_small)
+                combine_kernel<true><<<blocks_for(ctx, domain_size), kThreads, 0, ctx->stream>>>(args, count, domain_size, static_cast<Fr*>(out->dptr));
+            else
+                combine_kernel<false><<<blocks_for(ctx, domain_size), kThreads, 0, ctx->stream>>>(args, count, domain_size, static_cast<Fr*>(out->dptr));
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return finish_call(ctx, "invalid input");

@@ -270,6 +270,7 @@ namespace
         }
         void synchronize() override { check(gzk_ctx_synchronize(ctx_)); }
         bool supports_msm() const override { return true; }
+        bool supports_indexed_logup() const override { return true; }
         ColP srs_lagrange(unsigned log2n, const G1& base, const Fe& tau) override
         {
             const ColP out = alloc(kG1, static_cast<std::size_t>(1) << log2n);

@@ -168,6 +168,9 @@ namespace gatzk_flow
         // [L_i(tau)] G of a domain / [tau^i] G, the resident table of shifted bases of such a point set,
         // and sum_i scalars[i] * P_i against it.  `scalars` is a field-element column (kFr / kFrMont).
         virtual bool supports_msm() const { return false; }
+        // the backend's running_sums_batch takes kLogup jobs without a packed query column (c1 null) when the
+        // job carries the integer keys and the shape of the banded table
+        virtual bool supports_indexed_logup() const { return false; }
         virtual ColP srs_lagrange(unsigned, const G1&, const Fe&) { throw std::runtime_error("this backend has no MSM commitment path"); }
         virtual ColP msm_table(const ColP&, std::size_t, unsigned*) { throw std::runtime_error("this backend has no MSM commitment path"); }
         virtual G1 msm(const ColP&, const ColP&, std::size_t, unsigned) { throw std::runtime_error("this backend has no MSM commitment path"); }
@@ -391,6 +394,9 @@ namespace gatzk_flow
             std::size_t length = 0;  // stored prefix; beyond it the column is zero, or `tail` when const_tail
             bool const_tail = false;
             Fe tail{};               // the column's value on rows length .. domain size - 1 (its last stored element)
+            // a column that is a fixed linear combination of other opened columns of its domain (the packed
+            // table / query columns of a lookup): its value at any point is that combination of theirs
+            std::vector<std::pair<std::string, Fe>> derived_from;
         };
         struct CommitItem
         {
@@ -402,6 +408,7 @@ namespace gatzk_flow
             std::size_t rows = 0, cols = 0;
             bool opened = true;       // matrices are commitment-only
             bool const_tail = false;  // rows beyond `length` repeat the last stored element (a running sum after its last term)
+            std::vector<std::pair<std::string, Fe>> derived_from;  // see ColumnEntry
         };
 
         // scalar helpers
@@ -558,11 +565,28 @@ namespace gatzk_flow
         struct Lookup
         {
             ColP table, query, multiplicity, acc;
-            std::size_t store = 0;  // stored rows of the four columns
+            std::size_t store = 0;        // stored rows of the accumulator (and of the other columns unless table_store says otherwise)
+            std::size_t table_store = 0;  // stored rows of table and multiplicity
+            Fe eta{};
+            bool pair = false;
         };
         Lookup build_pair_lookup(const ColP& table_x, const ColP& table_y, std::size_t table_size, std::int64_t x_min, std::size_t band,
                                  const ColP& left, const ColP& right, std::size_t valid, const Fe& eta, const Fe& beta, const ColP& q_table,
                                  const ColP& q_query);
+        // The packed columns of a lookup as commit items.  Prefix-stored runs do not evaluate them: table =
+        // table_x + eta * table_y and query = left + eta * right are combinations of columns that are opened
+        // anyway (x_label / y_label), so their value at any point follows from those.
+        CommitItem packed_item(const std::string& label, const ColP& col, std::size_t length, const Lookup& lookup, const std::string& x_label,
+                               const std::string& y_label)
+        {
+            CommitItem it = column_item(label, col, "edge", length);
+            if (compact_)
+            {
+                it.derived_from.push_back({x_label, fe_u64(1)});
+                if (lookup.pair) it.derived_from.push_back({y_label, lookup.eta});
+            }
+            return it;
+        }
         struct Route
         {
             ColP table, query, node_acc, edge_acc;  // the routed total is node_acc[node_count]
@@ -955,7 +979,7 @@ namespace gatzk_flow
                 slot[i] = next;
                 be_.horner_device(items[i].col, items[i].rows, items[i].cols, tau_, scalars, next++);
             }
-            else
+            else if (items[i].derived_from.empty())
             {
                 groups[{items[i].domain, items[i].length}].push_back(i);
             }
@@ -989,23 +1013,52 @@ namespace gatzk_flow
         }
         std::vector<Fe> evals(items.size()), evals_by_slot(items.size());
         std::vector<Fe> tails(items.size());
-        if (!tail_items.empty())
+        std::vector<std::size_t> derived_items;
+        for (std::size_t i = 0; i < items.size(); ++i)
+            if (!items[i].matrix && !items[i].derived_from.empty())
+            {
+                slot[i] = next++;
+                derived_items.push_back(i);
+            }
+        const bool host_fix = !tail_items.empty() || !derived_items.empty();
+        if (host_fix)
         {
             std::vector<Fe> ones_host(ones_slot.size());
             be_.download(scalars, 0, items.size(), evals_by_slot.data());
-            be_.download(ones_out, 0, ones_host.size(), ones_host.data());
+            if (!tail_items.empty()) be_.download(ones_out, 0, ones_host.size(), ones_host.data());
             for (const auto i : tail_items)
             {
                 be_.download(items[i].col, items[i].length - 1, 1, &tails[i]);
                 const Fe rest = sub(fe_u64(1), ones_host[ones_slot.at({items[i].domain, items[i].length})]);
                 evals_by_slot[slot[i]] = add(evals_by_slot[slot[i]], mul(tails[i], rest));
             }
+            // combinations of columns that are evaluated in this barrier, were committed earlier, or are static
+            std::map<std::string, std::size_t> here;
+            for (std::size_t i = 0; i < items.size(); ++i) here[items[i].label] = i;
+            for (const auto i : derived_items)
+            {
+                Fe value = fe_u64(0);
+                for (const auto& term : items[i].derived_from)
+                {
+                    Fe source;
+                    const auto in_batch = here.find(term.first);
+                    const auto earlier = commitments_.find(term.first);
+                    if (in_batch != here.end())
+                        source = evals_by_slot[slot[in_batch->second]];
+                    else if (earlier != commitments_.end())
+                        source = earlier->second.tau_evaluation;
+                    else
+                        source = static_commitments_.at(term.first).tau_evaluation;
+                    value = add(value, mul(term.second, source));
+                }
+                evals_by_slot[slot[i]] = value;
+            }
             scalars = upload_fe(evals_by_slot, items.size());
         }
         const ColP points = be_.alloc(kG1, items.size());
         be_.g1_fixed_base(in_.generator, scalars, items.size(), points);
         std::vector<G1> pts(items.size()), pts_by_slot(items.size());
-        if (tail_items.empty()) be_.download(scalars, 0, items.size(), evals_by_slot.data());
+        if (!host_fix) be_.download(scalars, 0, items.size(), evals_by_slot.data());
         be_.download(points, 0, items.size(), pts_by_slot.data());
         for (std::size_t i = 0; i < items.size(); ++i)
         {
@@ -1028,7 +1081,7 @@ namespace gatzk_flow
             tau_eval_log_.push_back({items[i].label, evals[i]});
             if (!items[i].matrix)
             {
-                columns_[items[i].label] = ColumnEntry{items[i].col, items[i].domain, items[i].length, items[i].const_tail, tails[i]};
+                columns_[items[i].label] = ColumnEntry{items[i].col, items[i].domain, items[i].length, items[i].const_tail, tails[i], items[i].derived_from};
                 opened_[items[i].domain].push_back(items[i].label);
             }
         }
@@ -1106,22 +1159,33 @@ namespace gatzk_flow
         Lookup out;
         const std::size_t store = lookup_store(std::max(table_size, valid));
         out.store = store;
+        out.eta = eta;
+        out.pair = table_y != nullptr;
+        // A long lookup on a backend that fetches the inverses from the inverted table needs neither the packed
+        // query column nor table rows beyond the table: nothing reads them (their evaluations are derived).
+        const bool keys_only = compact_ && be_.supports_indexed_logup() && valid > (static_cast<std::size_t>(1) << 20) && table_size <= valid;
+        const std::size_t table_store = keys_only ? std::min(store, round64(table_size + 1)) : store;
+        out.table_store = table_store;
         if (table_y != nullptr)
         {
-            out.table = be_.alloc(kFrMont, store);
-            be_.linear_combination({table_x, table_y}, {fe_u64(1), eta}, table_size, store, out.table);
-            out.query = be_.alloc(kFrMont, store);
-            be_.linear_combination({left, right}, {fe_u64(1), eta}, valid, store, out.query);
+            out.table = be_.alloc(kFrMont, table_store);
+            be_.linear_combination({table_x, table_y}, {fe_u64(1), eta}, table_size, table_store, out.table);
+            if (!keys_only)
+            {
+                out.query = be_.alloc(kFrMont, store);
+                be_.linear_combination({left, right}, {fe_u64(1), eta}, valid, store, out.query);
+            }
         }
         else
         {
             out.table = table_x;  // cached_single_lookup_table: the padded table itself
             out.query = left;     // build_single_lookup_artifacts copies the query values
         }
-        out.multiplicity = be_.alloc(kU32, store);
-        be_.lookup_multiplicity(left, table_y != nullptr ? right : nullptr, valid, x_min, band, table_y, table_size, store, out.multiplicity);
+        out.multiplicity = be_.alloc(kU32, table_store);
+        be_.lookup_multiplicity(left, table_y != nullptr ? right : nullptr, valid, x_min, band, table_y, table_size, table_store, out.multiplicity);
         out.acc = be_.alloc(kFrMont, store);
-        queue_scan(ScanJob::kLogup, out.table, out.query, out.multiplicity, q_table, q_query, std::min(valid, e.size - 1), store, beta, out.acc);
+        queue_scan(ScanJob::kLogup, out.table, keys_only ? nullptr : out.query, out.multiplicity, q_table, q_query, std::min(valid, e.size - 1), store, beta,
+                   out.acc);
         ScanJob& job = scan_queue_.back();
         job.key_x = left;
         job.key_y = table_y != nullptr ? right : nullptr;
@@ -1389,13 +1453,13 @@ namespace gatzk_flow
                       column_item(prefix + "H_src_star_edge", h_star_edge, "edge", es_), column_item(prefix + "Table_src", src_route.table, "N", n.size),
                       column_item(prefix + "Query_src", src_route.query, "edge", es_), column_item(prefix + "m_src", src_multiplicity_, "N", n.size),
                       column_item(prefix + "R_src_node", src_route.node_acc, "N", n.size), tail_item(prefix + "R_src", src_route.edge_acc, "edge", es_),
-                      column_item(prefix + "Table_L", lrelu.table, "edge", es_), column_item(prefix + "Query_L", lrelu.query, "edge", es_),
-                      column_item(prefix + "m_L", lrelu.multiplicity, "edge", es_), tail_item(prefix + "R_L", lrelu.acc, "edge", es_),
+                      packed_item(prefix + "Table_L", lrelu.table, lrelu.table_store, lrelu, "V_T_L_x", "V_T_L_y"), packed_item(prefix + "Query_L", lrelu.query, lrelu.store, lrelu, prefix + "S", prefix + "Z"),
+                      column_item(prefix + "m_L", lrelu.multiplicity, "edge", lrelu.table_store), tail_item(prefix + "R_L", lrelu.acc, "edge", lrelu.store),
                       column_item(prefix + "s_max", s_max, "edge", es_), tail_item(prefix + "C_max", c_max, "edge", es_),
-                      column_item(prefix + "Table_R", range.table, "edge", es_), column_item(prefix + "Query_R", range.query, "edge", es_),
-                      column_item(prefix + "m_R", range.multiplicity, "edge", es_), tail_item(prefix + "R_R", range.acc, "edge", es_),
-                      column_item(prefix + "Table_exp", exp_l.table, "edge", es_), column_item(prefix + "Query_exp", exp_l.query, "edge", es_),
-                      column_item(prefix + "m_exp", exp_l.multiplicity, "edge", es_), tail_item(prefix + "R_exp", exp_l.acc, "edge", es_),
+                      packed_item(prefix + "Table_R", range.table, range.table_store, range, "V_T_range", ""), packed_item(prefix + "Query_R", range.query, range.store, range, prefix + "Delta", ""),
+                      column_item(prefix + "m_R", range.multiplicity, "edge", range.table_store), tail_item(prefix + "R_R", range.acc, "edge", range.store),
+                      packed_item(prefix + "Table_exp", exp_l.table, exp_l.table_store, exp_l, "V_T_exp_x", "V_T_exp_y"), packed_item(prefix + "Query_exp", exp_l.query, exp_l.store, exp_l, prefix + "Delta", prefix + "U"),
+                      column_item(prefix + "m_exp", exp_l.multiplicity, "edge", exp_l.table_store), tail_item(prefix + "R_exp", exp_l.acc, "edge", exp_l.store),
                       column_item(prefix + "H_agg_pre_star", h_agg_pre_star, "N", n_nodes_),
                       column_item(prefix + "H_agg_pre_star_edge", h_agg_pre_star_edge, "edge", es_),
                       column_item(prefix + "widehat_v_pre_star", widehat, "edge", es_), column_item(prefix + "w_psq", w_psq, "edge", es_),
@@ -1439,8 +1503,8 @@ namespace gatzk_flow
                       column_item(prefix + "Acc_agg_pre", agg_pre_b.acc, "d", dd), column_item(prefix + "a_agg", agg_b.a, "d", dd),
                       column_item(prefix + "b_agg", agg_b.b, "d", dd), column_item(prefix + "Acc_agg", agg_b.acc, "d", dd),
                       column_item(prefix + "H_agg_pre_flat", w.h_agg_pre, "edge", flat), column_item(prefix + "H_agg_flat", w.h_agg, "edge", flat),
-                      column_item(prefix + "Table_ELU", elu.table, "edge", elu.store), column_item(prefix + "Query_ELU", elu.query, "edge", elu.store),
-                      column_item(prefix + "m_ELU", elu.multiplicity, "edge", elu.store), tail_item(prefix + "R_ELU", elu.acc, "edge", elu.store),
+                      packed_item(prefix + "Table_ELU", elu.table, elu.table_store, elu, "V_T_ELU_x", "V_T_ELU_y"), packed_item(prefix + "Query_ELU", elu.query, elu.store, elu, prefix + "H_agg_pre_flat", prefix + "H_agg_flat"),
+                      column_item(prefix + "m_ELU", elu.multiplicity, "edge", elu.table_store), tail_item(prefix + "R_ELU", elu.acc, "edge", elu.store),
                       column_item(prefix + "Table_t", t_route.table, "N", n.size), column_item(prefix + "Query_t", t_route.query, "edge", es_),
                       column_item(prefix + "m_t", dst_multiplicity_, "N", n.size), column_item(prefix + "R_t_node", t_route.node_acc, "N", n.size),
                       tail_item(prefix + "R_t", t_route.edge_acc, "edge", es_)});

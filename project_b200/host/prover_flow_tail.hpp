@@ -151,14 +151,14 @@ namespace gatzk_flow
                       column_item(prefix + "Y_prime_star_edge", y_prime_star_edge, "edge", es_),
                       column_item(prefix + "Table_src", src_route.table, "N", n.size), column_item(prefix + "Query_src", src_route.query, "edge", es_),
                       column_item(prefix + "m_src", src_multiplicity_, "N", n.size), column_item(prefix + "R_src_node", src_route.node_acc, "N", n.size),
-                      tail_item(prefix + "R_src", src_route.edge_acc, "edge", es_), column_item(prefix + "Table_L", lrelu.table, "edge", es_),
-                      column_item(prefix + "Query_L", lrelu.query, "edge", es_), column_item(prefix + "m_L", lrelu.multiplicity, "edge", es_),
-                      tail_item(prefix + "R_L", lrelu.acc, "edge", es_), column_item(prefix + "s_max", s_max, "edge", es_),
-                      tail_item(prefix + "C_max", c_max, "edge", es_), column_item(prefix + "Table_R", range.table, "edge", es_),
-                      column_item(prefix + "Query_R", range.query, "edge", es_), column_item(prefix + "m_R", range.multiplicity, "edge", es_),
-                      tail_item(prefix + "R_R", range.acc, "edge", es_), column_item(prefix + "Table_exp", exp_l.table, "edge", es_),
-                      column_item(prefix + "Query_exp", exp_l.query, "edge", es_), column_item(prefix + "m_exp", exp_l.multiplicity, "edge", es_),
-                      tail_item(prefix + "R_exp", exp_l.acc, "edge", es_), column_item(prefix + "widehat_y_star", widehat, "edge", es_),
+                      tail_item(prefix + "R_src", src_route.edge_acc, "edge", es_), packed_item(prefix + "Table_L", lrelu.table, lrelu.table_store, lrelu, "V_T_L_x", "V_T_L_y"),
+                      packed_item(prefix + "Query_L", lrelu.query, lrelu.store, lrelu, prefix + "S", prefix + "Z"), column_item(prefix + "m_L", lrelu.multiplicity, "edge", lrelu.table_store),
+                      tail_item(prefix + "R_L", lrelu.acc, "edge", lrelu.store), column_item(prefix + "s_max", s_max, "edge", es_),
+                      tail_item(prefix + "C_max", c_max, "edge", es_), packed_item(prefix + "Table_R", range.table, range.table_store, range, "V_T_range", ""),
+                      packed_item(prefix + "Query_R", range.query, range.store, range, prefix + "Delta", ""), column_item(prefix + "m_R", range.multiplicity, "edge", range.table_store),
+                      tail_item(prefix + "R_R", range.acc, "edge", range.store), packed_item(prefix + "Table_exp", exp_l.table, exp_l.table_store, exp_l, "V_T_exp_x", "V_T_exp_y"),
+                      packed_item(prefix + "Query_exp", exp_l.query, exp_l.store, exp_l, prefix + "Delta", prefix + "U"), column_item(prefix + "m_exp", exp_l.multiplicity, "edge", exp_l.table_store),
+                      tail_item(prefix + "R_exp", exp_l.acc, "edge", exp_l.store), column_item(prefix + "widehat_y_star", widehat, "edge", es_),
                       column_item(prefix + "w", w_out, "edge", es_), column_item(prefix + "T", t_out, "N", n_nodes_),
                       column_item(prefix + "T_edge", t_out_edge, "edge", es_), tail_item(prefix + "PSQ", psq, "edge", es_),
                       column_item(prefix + "Y_star", y_star, "N", n_nodes_), column_item(prefix + "Y_star_edge", y_star_edge, "edge", es_)});
@@ -487,7 +487,31 @@ namespace gatzk_flow
                 else
                     labels.push_back(item.first);
             }
-            if (labels.empty()) return;
+            // combinations of other opened columns are not evaluated: their values follow from those
+            std::vector<std::string> derived;
+            {
+                std::vector<std::string> evaluated;
+                for (const auto& label : labels)
+                {
+                    const auto c = columns_.find(label);
+                    (c != columns_.end() && !c->second.derived_from.empty() ? derived : evaluated).push_back(label);
+                }
+                labels.swap(evaluated);
+            }
+            auto finish_derived = [&]() {
+                for (const auto& label : derived)
+                {
+                    std::array<Fe, 2> value = {fe_u64(0), fe_u64(0)};
+                    for (const auto& term : columns_.at(label).derived_from)
+                        for (int r = 0; r < 2; ++r) value[r] = add(value[r], mul(term.second, out.at(term.first)[r]));
+                    out[label] = value;
+                }
+            };
+            if (labels.empty())
+            {
+                finish_derived();
+                return;
+            }
             const Domain& d = dom_.at(domain);
             const std::vector<std::uint64_t> rotations = at_tau ? std::vector<std::uint64_t>{1} : std::vector<std::uint64_t>{0, 1};
             const std::size_t points = rotations.size();
@@ -574,6 +598,7 @@ namespace gatzk_flow
                     }
                 }
             }
+            finish_derived();
         };
 
         // ---- quotient scalars at tau ------------------------------------------------------------------
