@@ -410,9 +410,12 @@ namespace gzk
         }
 
         // Exclusive segmented scan of the CTA aggregates (in place) by one CTA.
-        __global__ void __launch_bounds__(kThreads) scan_offsets_kernel(Fr* agg_value, uint32_t* agg_flag, uint32_t ctas, Fr* total_out)
+        // 1024 threads: the aggregates of a 2^26-row column (131072 of them) are 128 per thread instead of 1024
+        constexpr int kOffsetThreads = 1024;
+        __global__ void __launch_bounds__(kOffsetThreads) scan_offsets_kernel(Fr* agg_value, uint32_t* agg_flag, uint32_t ctas, Fr* total_out)
         {
-            __shared__ SegVal seg_slots[kWarps];
+            constexpr int kThreads = kOffsetThreads;
+            __shared__ SegVal seg_slots[kThreads / 32];
             const uint32_t run_len = (ctas + kThreads - 1) / kThreads;
             const uint32_t begin = threadIdx.x * run_len < ctas ? threadIdx.x * run_len : ctas;
             const uint32_t end = begin + run_len < ctas ? begin + run_len : ctas;
@@ -677,7 +680,7 @@ namespace gzk
             {
                 {
                     LaunchScope scope(ctx, "scan_offsets");
-                    scan_offsets_kernel<<<1, kThreads, 0, ctx->stream>>>(args.agg_value, args.agg_flag, ctas, args.total);
+                    scan_offsets_kernel<<<1, kOffsetThreads, 0, ctx->stream>>>(args.agg_value, args.agg_flag, ctas, args.total);
                 }
                 GZK_CUDA_TRY(ctx, cudaGetLastError());
                 if (args.n > 0)
