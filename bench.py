@@ -253,9 +253,15 @@ def main():
     ap.add_argument("--no-msm", action="store_true", help="skip the MSM-commitment measurement")
     ap.add_argument("--no-sweep", action="store_true", help="skip the MSM / NTT / fold kernel sweep lines")
     ap.add_argument("--sweep-only", action="store_true", help="only the MSM / NTT / fold sweep")
+    ap.add_argument("--profile-case", default=None, help="run one small single-kernel case (project_b200/profile_cases.py) and exit")
     args = ap.parse_args()
     if args.small:
         args.workload = "small"
+    if args.profile_case is not None:
+        from project_b200 import profile_cases
+
+        emit({"profile_case": args.profile_case, "launches_and_us_per_launch": profile_cases.run_case(args.profile_case)})
+        return 0
     from project_b200 import synthetic
 
     if args.impl == "reference":
@@ -374,7 +380,7 @@ def main():
         "peak_source": peak_src, "launches": eval_launches, "avg_launch_ms": eval_ms / max(1, eval_launches), "bytes_per_step": int(work[0]),
         "integer_pipe": {"achieved_limb_products_per_s": limb_rate, "measured_peak_limb_products_per_s": mac_peak * 64,
                          "frac": limb_rate / (mac_peak * 64) if mac_peak else None,
-                         "note": "the binding roof: 64 32x32-bit products per term of a field-element column, 16 for an I64 column, 8 for U32; "
+                         "note": "the binding roof: 64 32x32-bit products per term of a field-element column, 8 for a small-integer column (I64 values that fit one limb, U32); "
                                  "at two evaluation points per element the integer pipe saturates at about a third of the HBM rate; "
                                  "peak measured in this run on register operands"},
     }

@@ -93,7 +93,11 @@ namespace gzk
                 const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
                 const uint32_t f[2] = {static_cast<uint32_t>(mag), static_cast<uint32_t>(mag >> 32)};
                 const Fr signed_w = v < 0 ? sub(Fr::zero(), w) : w;
-                acc.mac<2>(signed_w.l, f);
+                // witness values are a few dozen bits at most: the second limb is almost never set
+                if (f[1] == 0)
+                    acc.mac<1>(signed_w.l, f);
+                else
+                    acc.mac<2>(signed_w.l, f);
             }
         };
         // FR and FR_MONT share the field-element code
