@@ -161,6 +161,14 @@ int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t le
 int gzk_eval_batch_device(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                           const gzk_buf* weights, const uint64_t* rotations, size_t p_count, gzk_buf* out, size_t out_offset);
 
+/* The edge side of a route whose query of edge e is the table row of the node the edge points at
+ * (query columns = node columns gathered by `index`, as build_route_trace's callers construct them,
+ * src/protocol/trace.cpp:1776-1794, 2737-2772): 1/(query_e + beta) = 1/(table_{index[e]} + beta), so the
+ * node_count table inverses are computed once and the running sum fetches them.  Same output as
+ * gzk_route_edge_accumulator on the gathered query column; an index outside the table raises
+ * GZK_E_INVALID. */
+int gzk_route_edge_accumulator_indexed(gzk_ctx* ctx, const gzk_buf* table, size_t node_count, const gzk_buf* index, size_t valid_length,
+                                       size_t domain_size, const uint8_t beta[32], gzk_buf* out);
 /* The same accumulator for a lookup into a banded static table, computed without one inversion per
  * row.  Every query (x[i], y[i]) equals some table row - the lookup argument proves exactly that, and
  * gzk_banded_lookup_multiplicity has located the row already - so 1/(query_i + beta) is one of the
@@ -316,7 +324,8 @@ int gzk_first_zero_marker(gzk_ctx* ctx, const gzk_buf* delta, const gzk_buf* gro
  * gzk_buf_zero: clears a buffer (the zero tails of padded columns).
  * gzk_copy_block: dst[dst_offset + r*dst_stride + c] = src[src_offset + r*src_stride + c] for
  *   r < rows, c < width: concatenation of per-head matrices (model::forward_note_style,
- *   src/model/gat.cpp:1155-1194) and flattening / padding of matrices into columns. */
+ *   src/model/gat.cpp:1155-1194) and flattening / padding of matrices into columns; src_stride 0
+ *   repeats one source row (the quantised output bias under every row, trace.cpp:1257-1268). */
 int gzk_linear_combination(gzk_ctx* ctx, const gzk_buf* const* cols, const uint8_t* coefficients, size_t terms, size_t count,
                            size_t domain_size, gzk_buf* out);
 int gzk_mul_columns(gzk_ctx* ctx, const gzk_buf* left, const gzk_buf* right, size_t count, size_t domain_size, gzk_buf* out);

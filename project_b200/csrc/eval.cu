@@ -13,8 +13,8 @@
 // Work decomposition: the row range is cut into tiles; a unit of work is one
 // (tile, column) pair, enumerated tile-major so that the warps of a CTA stream
 // different columns against the SAME weight tile (served by L1/L2 after the first
-// touch).  Units are dealt to warps in contiguous runs, which balances any K and
-// n over 148 SMs without atomics.  Each unit produces one 17-limb partial sum in
+// touch).  Units are dealt to warps round-robin, which balances any K and n over
+// 148 SMs without atomics and keeps the tiles in flight neighbours.  Each unit produces one 17-limb partial sum in
 // context-owned scratch.
 #include <atomic>
 #include <cstdlib>
@@ -130,12 +130,14 @@ namespace gzk
             const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
             const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
             const uint64_t units = static_cast<uint64_t>(a.tiles) * a.k_count;
-            const uint64_t per_warp = (units + warps - 1) / warps;
-            const uint64_t u_begin = warp * per_warp;
-            const uint64_t u_end = u_begin + per_warp < units ? u_begin + per_warp : units;
             uint32_t ring_pos = 0;  // chunks this warp has pushed through the ring so far
 
-            for (uint64_t u = u_begin; u < u_end; ++u)
+            // Units are tile-major and dealt round-robin: at any moment the grid works on a window of
+            // consecutive units, i.e. on all columns of a few hundred neighbouring tiles, so a weight tile is
+            // fetched from DRAM once and served from L2 to the warps that take the other columns of that
+            // tile.  (Contiguous runs per warp would put every warp on a tile of its own: the whole weight
+            // vector, far larger than L2, would cycle through the cache once per column.)
+            for (uint64_t u = warp; u < units; u += warps)
             {
                 const uint32_t tile = static_cast<uint32_t>(u / a.k_count);
                 const uint32_t k = static_cast<uint32_t>(u - static_cast<uint64_t>(tile) * a.k_count);

@@ -51,8 +51,10 @@ namespace gzk
         __global__ void __launch_bounds__(kThreads) project_tiled_kernel(const double* x, const double* w, uint64_t rows, uint32_t inner, uint32_t width,
                                                                          double* out)
         {
-            __shared__ double xs[kTileK][kTileM + 1];
-            __shared__ double ws[kTileK][kTileN];
+            // rows padded to 66 doubles: 16-byte aligned groups of four for the vector loads below, and the four
+            // k-groups of a store land on different banks
+            __shared__ __align__(16) double xs[kTileK][kTileM + 2];
+            __shared__ __align__(16) double ws[kTileK][kTileN];
             const uint32_t tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
             const uint64_t i0 = static_cast<uint64_t>(blockIdx.y) * kTileM;
             const uint32_t j0 = blockIdx.x * kTileN;
@@ -79,10 +81,10 @@ namespace gzk
                 for (uint32_t kk = 0; kk < k_count; ++kk)
                 {
                     double a[4], b[4];
-#pragma unroll
-                    for (int r = 0; r < 4; ++r) a[r] = xs[kk][ty * 4 + r];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) b[c] = ws[kk][tx * 4 + c];
+                    const double2 a01 = *reinterpret_cast<const double2*>(&xs[kk][ty * 4]), a23 = *reinterpret_cast<const double2*>(&xs[kk][ty * 4 + 2]);
+                    const double2 b01 = *reinterpret_cast<const double2*>(&ws[kk][tx * 4]), b23 = *reinterpret_cast<const double2*>(&ws[kk][tx * 4 + 2]);
+                    a[0] = a01.x; a[1] = a01.y; a[2] = a23.x; a[3] = a23.y;
+                    b[0] = b01.x; b[1] = b01.y; b[2] = b23.x; b[3] = b23.y;
 #pragma unroll
                     for (int r = 0; r < 4; ++r)
 #pragma unroll
@@ -185,15 +187,29 @@ namespace gzk
         // Aggregation with the attention weights already in alpha_in: no exponential inside the serial sum.
         __global__ void __launch_bounds__(kThreads) aggregate_alpha_kernel(const double* h, const double* alpha_in, const uint32_t* in_ptr,
                                                                            const uint32_t* in_src, uint64_t nodes, uint32_t width, const double* out_bias,
-                                                                           uint32_t bias_count, int apply_activation, double* pre_out, double* agg_out)
+                                                                           uint32_t bias_count, int apply_activation, double* pre_out, double* agg_out,
+                                                                           uint32_t heavy_above)
         {
             const uint64_t idx = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
             if (idx >= nodes * width) return;
             const uint64_t dst = idx / width;
             const uint32_t c = static_cast<uint32_t>(idx - dst * width);
             const uint32_t begin = in_ptr[dst], end = in_ptr[dst + 1];
+            if (end - begin > heavy_above) return;  // aggregate_heavy_kernel owns this node
             double acc = 0.0;
             uint32_t p = begin;
+            // Long lists (the hubs of a power-law graph: tens of thousands of entries for one node) would pay one
+            // gather latency per entry if walked one by one.  The products are exact and independent of the
+            // running sum, so sixteen of them are formed at a time (sixteen gathers in flight) and only the
+            // additions stay serial, in list order.
+            for (; p + 16 <= end; p += 16)
+            {
+                double prod[16];
+#pragma unroll
+                for (int u = 0; u < 16; ++u) prod[u] = __dmul_rn(alpha_in[p + u], h[static_cast<uint64_t>(in_src[p + u]) * width + c]);
+#pragma unroll
+                for (int u = 0; u < 16; ++u) acc = __dadd_rn(acc, prod[u]);
+            }
             for (; p + 4 <= end; p += 4)
             {
                 // the four loads do not depend on acc: they are in flight together
@@ -210,6 +226,95 @@ namespace gzk
             double v = acc;
             if (out_bias != nullptr && c < bias_count) v = __dadd_rn(v, out_bias[c]);
             if (agg_out != nullptr) agg_out[idx] = apply_activation ? (v >= 0.0 ? v : expm1(v)) : v;
+        }
+
+        // ---- nodes with long incoming lists ------------------------------------------------------------
+        // The sum over a list is serial by definition, but a thread that walks 10 000 entries and waits for a
+        // gather from HBM at each of them takes milliseconds.  These nodes get a CTA each (a thread per column)
+        // whose gathers run ahead of the additions as asynchronous copies into a ring of shared-memory stages:
+        // sixteen entries per stage, four stages in flight, every thread copies and later reads only its own
+        // column, so no barrier is needed - only cp.async.wait_group.
+        constexpr uint32_t kHeavyDegree = 512;
+        constexpr int kAggStages = 4, kAggChunk = 16;
+        constexpr size_t kAggSmemBytes = static_cast<size_t>(kAggStages) * kAggChunk * kThreads * sizeof(double);  // 128 KiB
+
+        __global__ void list_heavy_nodes_kernel(const uint32_t* in_ptr, uint64_t nodes, uint32_t* heavy, uint32_t* heavy_count)
+        {
+            const uint64_t dst = static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x;
+            if (dst >= nodes) return;
+            if (in_ptr[dst + 1] - in_ptr[dst] > kHeavyDegree) heavy[atomicAdd(heavy_count, 1u)] = static_cast<uint32_t>(dst);
+        }
+
+        __device__ __forceinline__ void cp_async_f64(double* smem_dst, const double* src)
+        {
+            asm volatile("cp.async.ca.shared.global [%0], [%1], 8;" ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))), "l"(src) : "memory");
+        }
+        __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+        template <int PENDING>
+        __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(PENDING) : "memory"); }
+
+        __global__ void __launch_bounds__(kThreads) aggregate_heavy_kernel(const double* h, const double* alpha_in, const uint32_t* in_ptr,
+                                                                           const uint32_t* in_src, const uint32_t* heavy, const uint32_t* heavy_count,
+                                                                           uint32_t width, const double* out_bias, uint32_t bias_count,
+                                                                           int apply_activation, double* pre_out, double* agg_out)
+        {
+            extern __shared__ double agg_stage[];  // [stage][entry][thread]
+            const uint32_t count = *heavy_count;
+            for (uint32_t item = blockIdx.x; item < count; item += gridDim.x)
+            {
+                const uint64_t dst = heavy[item];
+                const uint32_t begin = in_ptr[dst], end = in_ptr[dst + 1];
+                const uint32_t chunks = (end - begin + kAggChunk - 1) / kAggChunk;
+                for (uint32_t c0 = 0; c0 < width; c0 += kThreads)
+                {
+                    const uint32_t c = c0 + threadIdx.x;
+                    const bool active = c < width;
+                    auto issue = [&](uint32_t ch) {
+                        if (active)
+                        {
+                            const uint32_t base = begin + ch * kAggChunk;
+                            double* slot = agg_stage + static_cast<size_t>(ch % kAggStages) * kAggChunk * kThreads + threadIdx.x;
+#pragma unroll
+                            for (int e = 0; e < kAggChunk; ++e)
+                                if (base + e < end) cp_async_f64(slot + e * kThreads, h + static_cast<uint64_t>(in_src[base + e]) * width + c);
+                        }
+                        cp_async_commit();  // one group per step, empty or not, so that the wait below counts steps
+                    };
+                    for (uint32_t ch = 0; ch < kAggStages - 1; ++ch)
+                    {
+                        if (ch < chunks)
+                            issue(ch);
+                        else
+                            cp_async_commit();
+                    }
+                    double acc = 0.0;
+                    for (uint32_t ch = 0; ch < chunks; ++ch)
+                    {
+                        if (ch + kAggStages - 1 < chunks)
+                            issue(ch + kAggStages - 1);
+                        else
+                            cp_async_commit();
+                        cp_async_wait<kAggStages - 1>();  // everything but the newest three groups has landed: chunk ch is in
+                        if (active)
+                        {
+                            const uint32_t base = begin + ch * kAggChunk;
+                            const double* slot = agg_stage + static_cast<size_t>(ch % kAggStages) * kAggChunk * kThreads + threadIdx.x;
+#pragma unroll
+                            for (int e = 0; e < kAggChunk; ++e)
+                                if (base + e < end) acc = __dadd_rn(acc, __dmul_rn(alpha_in[base + e], slot[e * kThreads]));
+                        }
+                    }
+                    cp_async_wait<0>();
+                    if (active)
+                    {
+                        const uint64_t idx = dst * width + c;
+                        if (pre_out != nullptr) pre_out[idx] = acc;
+                        double v = acc;
+                        if (out_bias != nullptr && c < bias_count) v = __dadd_rn(v, out_bias[c]);
+                        if (agg_out != nullptr) agg_out[idx] = apply_activation ? (v >= 0.0 ? v : expm1(v)) : v;
+                    }
+                }
+            }
         }
 
         // H_agg_pre[dst][c] = sum over incoming src of alpha * H'[src][c]; H_agg = act(H_agg_pre + bias)
@@ -350,7 +455,8 @@ extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, cons
     if (by_warp)
     {
         void* scratch = nullptr;
-        if ((rc = ensure_scratch(ctx, 0, (in_count + 1) * sizeof(double), &scratch)) != GZK_OK) return rc;
+        // alpha_in, then the list of nodes with long incoming lists (at most in_count / 512 of them) and its counter
+        if ((rc = ensure_scratch(ctx, 0, (in_count + 1) * sizeof(double) + (in_count / 512 + 8) * sizeof(uint32_t), &scratch)) != GZK_OK) return rc;
         alpha_in = static_cast<double*>(scratch);
         LaunchScope scope(ctx, "forward_softmax_stats");
         softmax_stats_warp_kernel<<<grid_for(nodes * 32), kThreads, 0, ctx->stream>>>(f64_ptr(out->E_src), f64_ptr(out->E_dst), in_ptr, in_src, nodes,
@@ -365,11 +471,25 @@ extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, cons
     GZK_CUDA_TRY(ctx, cudaGetLastError());
     if (by_warp && (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr))
     {
+        // the list of nodes with long incoming lists sits behind alpha_in in the same scratch area
+        uint32_t* heavy_count = reinterpret_cast<uint32_t*>(alpha_in + in_count + 1);
+        uint32_t* heavy = heavy_count + 2;
+        static bool opted_in[64] = {};
+        if (ctx->device >= 0 && ctx->device < 64 && !opted_in[ctx->device])
+        {
+            GZK_CUDA_TRY(ctx, cudaFuncSetAttribute(aggregate_heavy_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kAggSmemBytes)));
+            opted_in[ctx->device] = true;
+        }
+        const uint32_t bias_count = head->output_bias != nullptr ? static_cast<uint32_t>(head->output_bias_count) : 0u;
+        GZK_CUDA_TRY(ctx, cudaMemsetAsync(heavy_count, 0, 2 * sizeof(uint32_t), ctx->stream));
         LaunchScope scope(ctx, "forward_aggregate");
+        list_heavy_nodes_kernel<<<grid_for(nodes), kThreads, 0, ctx->stream>>>(in_ptr, nodes, heavy, heavy_count);
         aggregate_alpha_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(
-            f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, nodes, width, f64_ptr(head->output_bias),
-            head->output_bias != nullptr ? static_cast<uint32_t>(head->output_bias_count) : 0u, head->apply_activation, f64_ptr(out->H_agg_pre_bias),
-            f64_ptr(out->H_agg));
+            f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, nodes, width, f64_ptr(head->output_bias), bias_count, head->apply_activation,
+            f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg), kHeavyDegree);
+        aggregate_heavy_kernel<<<ctx->sm_count, kThreads, kAggSmemBytes, ctx->stream>>>(
+            f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, heavy, heavy_count, width, f64_ptr(head->output_bias), bias_count, head->apply_activation,
+            f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg));
     }
     else if (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr)
     {

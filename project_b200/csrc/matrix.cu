@@ -100,6 +100,49 @@ namespace gzk
                     acc.mac<2>(signed_w.l, f);
             }
         };
+        // acc += w * (v + 2^31) for a signed 64-bit entry: the biased value is non-negative, so the sign needs no
+        // negated weight; the caller subtracts 2^31 * (sum of the weights) once per sum.  v + 2^31 = u + 2^32 k with
+        // u = low word of v with its top bit flipped and k = (v >> 32) + (bit 31 of v): k is 0 for |v| < 2^31, i.e.
+        // for every witness value in practice, and the product is then eight limb products.
+        __device__ __forceinline__ void mac_biased_i64(WideAcc& acc, const Fr& w, long long v)
+        {
+            const uint32_t low = static_cast<uint32_t>(static_cast<unsigned long long>(v));
+            const uint32_t u = low ^ 0x80000000u;
+            const long long k = (v >> 32) + static_cast<long long>(low >> 31);
+            acc.mac<1>(w.l, &u);
+            if (k != 0)
+            {
+                const unsigned long long mag = k < 0 ? 0ULL - static_cast<unsigned long long>(k) : static_cast<unsigned long long>(k);
+                const Fr signed_w = k < 0 ? sub(Fr::zero(), w) : w;
+                acc.row<1>(signed_w.l, static_cast<uint32_t>(mag));
+                if ((mag >> 32) != 0) acc.row<2>(signed_w.l, static_cast<uint32_t>(mag >> 32));
+            }
+        }
+
+        // out = scale * (v[0] + ... + v[count-1]), everything in Montgomery form; one CTA.
+        __global__ void __launch_bounds__(kThreads) scaled_sum_kernel(const Fr* v, uint32_t count, Fr scale, Fr* out)
+        {
+            __shared__ Fr warp_sum[kThreads / 32];
+            Fr acc = Fr::zero();
+            for (uint32_t i = threadIdx.x; i < count; i += kThreads) acc = add(acc, load_fr(v + i));
+            const int lane = threadIdx.x & 31;
+#pragma unroll
+            for (int offset = 16; offset > 0; offset >>= 1)
+            {
+                const Fr other = shfl_fr_idx(acc, (lane + offset) & 31);
+                if (lane < offset) acc = add(acc, other);
+            }
+            if (lane == 0) warp_sum[threadIdx.x >> 5] = acc;
+            __syncthreads();
+            if (threadIdx.x == 0)
+            {
+                Fr sum = warp_sum[0];
+#pragma unroll
+                for (int w = 1; w < kThreads / 32; ++w) sum = add(sum, warp_sum[w]);
+                store_fr(out, mul(sum, scale));
+            }
+        }
+
         // FR and FR_MONT share the field-element code
         constexpr int entry_kind(int kind) { return kind == GZK_KIND_U32 || kind == GZK_KIND_I64 ? kind : GZK_KIND_FR; }
 
@@ -109,8 +152,10 @@ namespace gzk
         // (one warp per block, each lane keeps its eight powers in registers), and leave Horner to the
         // 256 times shorter polynomial sum_b r_b (x^256)^b.  out[b] is the Montgomery form of r_b.
         constexpr int kDotBlock = 256;
+        // `bias` (I64 only): 2^31 * (sum of the 256 powers), Montgomery form; the entries then enter biased.
         template <int KIND>
-        __global__ void __launch_bounds__(kThreads) block_dot_kernel(const void* coeffs, uint64_t total, const Fr* powers, uint64_t blocks, Fr* out)
+        __global__ void __launch_bounds__(kThreads) block_dot_kernel(const void* coeffs, uint64_t total, const Fr* powers, uint64_t blocks, Fr* out,
+                                                                     const Fr* bias)
         {
             const uint32_t lane = threadIdx.x & 31;
             const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
@@ -130,7 +175,13 @@ namespace gzk
                     raw[k] = i < total ? Entry<KIND>::load(coeffs, i) : Entry<KIND>::zero();
                 }
 #pragma unroll
-                for (int k = 0; k < kDotBlock / 32; ++k) Entry<KIND>::mac(acc, p[k], raw[k]);
+                for (int k = 0; k < kDotBlock / 32; ++k)
+                {
+                    if constexpr (KIND == GZK_KIND_I64)
+                        mac_biased_i64(acc, p[k], raw[k]);
+                    else
+                        Entry<KIND>::mac(acc, p[k], raw[k]);
+                }
                 uint32_t sum[kAccLimbs];
                 acc.fold(sum);
 #pragma unroll
@@ -141,7 +192,12 @@ namespace gzk
                     for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, sum[i], offset);
                     acc_add<kAccLimbs, kAccLimbs>(sum, other);
                 }
-                if (lane == 0) store_fr(out + b, mul(redc_wide<FrCfg, 9>(sum), fr_const_2_544()));
+                if (lane == 0)
+                {
+                    Fr value = mul(redc_wide<FrCfg, 9>(sum), fr_const_2_544());
+                    if constexpr (KIND == GZK_KIND_I64) value = sub(value, load_fr(bias));
+                    store_fr(out + b, value);
+                }
             }
         }
 
@@ -213,7 +269,7 @@ namespace gzk
         // One warp per row: lanes stride over the columns, exact warp sum, one reduction.
         template <int KIND>
         __global__ void __launch_bounds__(kThreads) linear_form_kernel(const void* matrix, int montgomery_entries, const Fr* powers, uint64_t rows,
-                                                                       uint32_t cols, Fr* out)
+                                                                       uint32_t cols, Fr* out, const Fr* bias)
         {
             const uint32_t lane = threadIdx.x & 31;
             const uint64_t row = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
@@ -227,9 +283,21 @@ namespace gzk
 #pragma unroll
                 for (int u = 0; u < 4; ++u) raw[u] = Entry<KIND>::load(matrix, row * cols + j + 32 * u);
 #pragma unroll
-                for (int u = 0; u < 4; ++u) Entry<KIND>::mac(acc, load_fr(powers + j + 32 * u), raw[u]);
+                for (int u = 0; u < 4; ++u)
+                {
+                    if constexpr (KIND == GZK_KIND_I64)
+                        mac_biased_i64(acc, load_fr(powers + j + 32 * u), raw[u]);
+                    else
+                        Entry<KIND>::mac(acc, load_fr(powers + j + 32 * u), raw[u]);
+                }
             }
-            for (; j < cols; j += 32) Entry<KIND>::mac(acc, load_fr(powers + j), Entry<KIND>::load(matrix, row * cols + j));
+            for (; j < cols; j += 32)
+            {
+                if constexpr (KIND == GZK_KIND_I64)
+                    mac_biased_i64(acc, load_fr(powers + j), Entry<KIND>::load(matrix, row * cols + j));
+                else
+                    Entry<KIND>::mac(acc, load_fr(powers + j), Entry<KIND>::load(matrix, row * cols + j));
+            }
             uint32_t sum[kAccLimbs];
             acc.fold(sum);
 #pragma unroll
@@ -255,7 +323,9 @@ namespace gzk
 #pragma unroll
                     for (int i = 0; i < 8; ++i) fix.l[i] = c288[i];
                 }
-                store_fr(out + row, mul(reduced, fix));
+                Fr value = mul(reduced, fix);
+                if constexpr (KIND == GZK_KIND_I64) value = sub(value, load_fr(bias));  // every entry entered as v + 2^31
+                store_fr(out + row, value);
             }
         }
 
@@ -263,6 +333,14 @@ namespace gzk
         {
             const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
             if (i < count) store_fr(out + i, pow_u64(c, i));
+        }
+
+        // 2^31 in Montgomery form
+        Fr mont_two_31()
+        {
+            Fr v = Fr::one();
+            for (int d = 0; d < 31; ++d) v = add(v, v);
+            return v;
         }
 
         int scalar_mont(gzk_ctx* ctx, const uint8_t* bytes, Fr* out)
@@ -295,7 +373,7 @@ extern "C"
         span = (span + kThreads - 1) / kThreads * kThreads;
         ctas = (horner_total + span - 1) / span;
         void* scratch = nullptr;
-        int rc = ensure_scratch(ctx, 2, (ctas + 1 + (blocked ? kDotBlock + dot_blocks : 0)) * sizeof(Fr), &scratch);
+        int rc = ensure_scratch(ctx, 2, (ctas + 1 + (blocked ? kDotBlock + 1 + dot_blocks : 0)) * sizeof(Fr), &scratch);
         if (rc != GZK_OK) return rc;
         Fr* partial = static_cast<Fr*>(scratch);
         ColRef m;
@@ -305,10 +383,12 @@ extern "C"
         if (blocked)
         {
             Fr* powers = partial + ctas + 1;
-            Fr* block_values = powers + kDotBlock;
+            Fr* bias = powers + kDotBlock;
+            Fr* block_values = bias + 1;
             {
                 LaunchScope scope(ctx, "powers");
                 powers_kernel<<<1, kDotBlock, 0, ctx->stream>>>(x, kDotBlock, powers);
+                if (matrix->kind == GZK_KIND_I64) scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, kDotBlock, mont_two_31(), bias);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
             const uint64_t warps_wanted = dot_blocks < static_cast<uint64_t>(ctx->sm_count) * 64 ? dot_blocks : static_cast<uint64_t>(ctx->sm_count) * 64;
@@ -316,9 +396,9 @@ extern "C"
                 LaunchScope scope(ctx, "horner_block_dot");
                 const unsigned grid = static_cast<unsigned>((warps_wanted * 32 + kThreads - 1) / kThreads);
                 if (matrix->kind == GZK_KIND_I64)
-                    block_dot_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values);
+                    block_dot_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values, bias);
                 else
-                    block_dot_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values);
+                    block_dot_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values, nullptr);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
             m.ptr = block_values;
@@ -461,6 +541,12 @@ extern "C"
         m.kind = matrix->kind;
         const uint64_t warps_per_cta = kThreads / 32;
         const uint64_t ctas = (rows + warps_per_cta - 1) / warps_per_cta;
+        void* bias_scratch = nullptr;
+        {
+            const int rc_scratch = ensure_scratch(ctx, 2, 2 * sizeof(Fr), &bias_scratch);
+            if (rc_scratch != GZK_OK) return rc_scratch;
+        }
+        Fr* bias = static_cast<Fr*>(bias_scratch);
         {
             LaunchScope scope(ctx, "linear_form");
             const unsigned grid = static_cast<unsigned>(ctas);
@@ -469,9 +555,17 @@ extern "C"
             Fr* dst = static_cast<Fr*>(out->dptr);
             switch (entry_kind(matrix->kind))
             {
-            case GZK_KIND_I64: linear_form_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst); break;
-            case GZK_KIND_U32: linear_form_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst); break;
-            default: linear_form_kernel<GZK_KIND_FR><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst); break;
+            case GZK_KIND_I64:
+                // entries enter as v + 2^31: 2^31 * (sum of the powers) is taken off every row
+                scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, static_cast<uint32_t>(cols), mont_two_31(), bias);
+                linear_form_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, bias);
+                break;
+            case GZK_KIND_U32:
+                linear_form_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, nullptr);
+                break;
+            default:
+                linear_form_kernel<GZK_KIND_FR><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, nullptr);
+                break;
             }
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());

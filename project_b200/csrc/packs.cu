@@ -317,8 +317,10 @@ extern "C"
                                                        static_cast<int>(kSharedTableLimit * sizeof(uint32_t))));
                 opted_in[ctx->device] = true;
             }
+            // as many CTAs per SM as their histograms fit in its shared memory (two for the 24 579-row table)
             uint64_t ctas = (count + kHistThreads - 1) / kHistThreads;
-            if (ctas > static_cast<uint64_t>(ctx->sm_count)) ctas = ctx->sm_count;
+            const uint64_t per_sm = table_size * sizeof(uint32_t) <= 100 * 1024 ? 2 : 1;
+            if (ctas > static_cast<uint64_t>(ctx->sm_count) * per_sm) ctas = static_cast<uint64_t>(ctx->sm_count) * per_sm;
             LaunchScope scope(ctx, "lookup_multiplicity");
             banded_multiplicity_shared_kernel<<<static_cast<unsigned>(ctas), kHistThreads, table_size * sizeof(uint32_t), ctx->stream>>>(
                 ref(x), has_y ? ref(y) : ref(x), has_y ? 1 : 0, count, static_cast<long long>(x_min), static_cast<uint32_t>(band),
@@ -354,7 +356,8 @@ extern "C"
         if (src->kind != dst->kind)
             return fail(ctx, GZK_E_INVALID, "copy_block: source and destination must hold the same kind of element");
         if (src->kind == GZK_KIND_G1) return fail(ctx, GZK_E_INVALID, "copy_block: point buffers are not supported");
-        if (width > src_stride || width > dst_stride || src_offset + (rows - 1) * src_stride + width > src->count ||
+        // src_stride 0 repeats one source row (a bias vector under every row of a matrix)
+        if ((src_stride != 0 && width > src_stride) || width > dst_stride || src_offset + (rows - 1) * src_stride + width > src->count ||
             dst_offset + (rows - 1) * dst_stride + width > dst->count)
             return fail(ctx, GZK_E_INVALID, "copy_block: block exceeds a buffer");
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));

@@ -38,6 +38,7 @@ namespace gzk
             kProduct = 3,    // term = a*b
             kSegmented = 4,  // term = value, running sum restarts where q_new = 1
             kLogupIndexed = 5,  // the LogUp term with every inverse fetched from a table of 1/(T_t+beta), see scan_main_body
+            kRouteEdgeIndexed = 6,  // term = inv_table[index[e]]: the edge side of a route whose queries are gathered table rows
         };
 
         struct ScanArgs
@@ -301,6 +302,22 @@ namespace gzk
                     else if (OP == kProduct)
                     {
                         term[j] = fix_scale(mul(col_load_stored(a.c0, e), col_load_stored(a.c1, e)), deficit(a.c0) + deficit(a.c1));
+                    }
+                    else if (OP == kRouteEdgeIndexed)
+                    {
+                        // the query of edge e is the table row of the node the edge points at, so 1/(Q_e + beta)
+                        // is that node's entry of the inverted table
+                        const uint64_t node = a.c0.kind == GZK_KIND_U32 ? static_cast<uint64_t>(__ldg(static_cast<const uint32_t*>(a.c0.ptr) + e))
+                                                                        : static_cast<uint64_t>(__ldg(static_cast<const long long*>(a.c0.ptr) + e));
+                        if (node < a.table_size)
+                        {
+                            term[j] = load_fr(a.inv_table + node);
+                        }
+                        else
+                        {
+                            raise_status(a.status, GZK_E_INVALID, 1406);
+                            term[j] = Fr::zero();
+                        }
                     }
                     else if (OP == kLogupIndexed)
                     {
@@ -659,7 +676,7 @@ namespace gzk
                 if ((rc = launch_batch_invert_single_cta(ctx, args.cta_products, tmp, ctas)) != GZK_OK) return rc;
             }
             {
-                LaunchScope scope(ctx, OP == kLogup ? "scan_main_logup" : OP == kLogupIndexed ? "scan_main_logup_indexed" : OP == kRouteNode ? "scan_main_route_node" : OP == kRouteEdge ? "scan_main_route_edge"
+                LaunchScope scope(ctx, OP == kLogup ? "scan_main_logup" : OP == kLogupIndexed ? "scan_main_logup_indexed" : OP == kRouteEdgeIndexed ? "scan_main_route_edge_indexed" : OP == kRouteNode ? "scan_main_route_node" : OP == kRouteEdge ? "scan_main_route_edge"
                                        : OP == kProduct ? "scan_main_product" : "scan_main_segmented");
                 if (local_inverse)
                     scan_main_kernel<OP, true><<<ctas, kThreads, 0, ctx->stream>>>(args);
@@ -773,6 +790,40 @@ extern "C"
         args.x_min = static_cast<long long>(x_min);
         args.band = static_cast<uint32_t>(band);
         return run_scan<kLogupIndexed>(ctx, args, false, nullptr, true);
+    }
+
+    int gzk_route_edge_accumulator_indexed(gzk_ctx* ctx, const gzk_buf* table, size_t node_count, const gzk_buf* index, size_t valid_length,
+                                           size_t domain_size, const uint8_t beta[32], gzk_buf* out)
+    {
+        if (ctx == nullptr) return GZK_E_INVALID;
+        if (beta == nullptr || !out_ok(out, domain_size)) return fail(ctx, GZK_E_INVALID, "route: output must be a Montgomery buffer of the domain size");
+        if (domain_size == 0) return GZK_OK;
+        if (valid_length > domain_size - 1) valid_length = domain_size - 1;
+        if (node_count == 0 || !col_ok(table, node_count) || index == nullptr || (index->kind != GZK_KIND_I64 && index->kind != GZK_KIND_U32) ||
+            index->count < valid_length)
+            return fail(ctx, GZK_E_INVALID, "route accumulator input size mismatch");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        ScanArgs args{};
+        int rc = load_scalar(ctx, beta, &args.beta, &args.beta_canon);
+        if (rc != GZK_OK) return rc;
+        void* scratch = nullptr;
+        if ((rc = ensure_scratch(ctx, 1, node_count * sizeof(Fr), &scratch)) != GZK_OK) return rc;
+        args.c0 = ref(table);
+        args.count = node_count;
+        args.status = ctx->d_status;
+        if ((rc = begin_call(ctx)) != GZK_OK) return rc;
+        {
+            LaunchScope scope(ctx, "route_table_inverses");
+            shifted_inverse_kernel<<<static_cast<unsigned>((node_count + kChunk - 1) / kChunk), kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(scratch));
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        args.c0 = ref(index);
+        args.count = valid_length;
+        args.n = domain_size;
+        args.out = static_cast<Fr*>(out->dptr);
+        args.inv_table = static_cast<const Fr*>(scratch);
+        args.table_size = node_count;
+        return run_scan<kRouteEdgeIndexed>(ctx, args, false, nullptr, true);
     }
 
     int gzk_logup_accumulator(gzk_ctx* ctx, const gzk_buf* table, const gzk_buf* query, const gzk_buf* multiplicity,

@@ -216,6 +216,12 @@ namespace
                                                         it->beta.data(), raw(it->out)));
                     it = long_jobs.erase(it);
                 }
+                else if (it->op == ScanJob::kRouteEdge && it->key_x != nullptr && it->table_y != nullptr && it->table_size != 0)
+                {
+                    check(gzk_route_edge_accumulator_indexed(ctx_, raw(it->table_y), it->table_size, raw(it->key_x), it->count, it->domain_size,
+                                                             it->beta.data(), raw(it->out)));
+                    it = long_jobs.erase(it);
+                }
                 else
                 {
                     ++it;

@@ -1212,6 +1212,14 @@ namespace gatzk_flow
         queue_scan(ScanJob::kRouteNode, out.table, multiplicity, nullptr, nullptr, nullptr, n_nodes_, n.size, beta, out.node_acc);
         out.edge_acc = be_.alloc(kFrMont, es_);
         queue_scan(ScanJob::kRouteEdge, out.query, nullptr, nullptr, nullptr, nullptr, n_edges_, es_, beta, out.edge_acc);
+        {
+            // the edge columns are the node columns gathered by the first edge column (the endpoint ids), so a
+            // backend may fetch 1/(query + beta) from the inverted node table instead of inverting per edge
+            ScanJob& job = scan_queue_.back();
+            job.key_x = edge_cols.front();
+            job.table_y = out.table;
+            job.table_size = n_nodes_;
+        }
         return out;
     }
 

@@ -55,11 +55,13 @@ namespace gatzk_flow
         const auto& bias = in_.output_layer.heads[head_index].output_bias;
         if (!bias.empty())
         {
-            std::vector<std::int64_t> rep(n_nodes_ * c, 0);
-            for (std::size_t r = 0; r < n_nodes_; ++r)
-                for (std::size_t j = 0; j < c && j < bias.size(); ++j) rep[r * c + j] = quantize_value(bias[j]);
+            // the quantised bias under every row: one row uploaded, repeated on the backend
+            std::vector<std::int64_t> row(c, 0);
+            for (std::size_t j = 0; j < c && j < bias.size(); ++j) row[j] = quantize_value(bias[j]);
+            const ColP rep = be_.alloc(kI64, n_nodes_ * c);
+            be_.copy_block(upload_i64(row), 0, 0, rep, 0, c, n_nodes_, c);
             y = be_.alloc(kFrMont, n_nodes_ * c);
-            be_.linear_combination({y_lin, upload_i64(rep)}, {fe_u64(1), fe_u64(1)}, n_nodes_ * c, n_nodes_ * c, y);
+            be_.linear_combination({y_lin, rep}, {fe_u64(1), fe_u64(1)}, n_nodes_ * c, n_nodes_ * c, y);
         }
         y_lin_all->push_back(y_lin);
         y_all->push_back(y);

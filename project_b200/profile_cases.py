@@ -6,7 +6,7 @@ import numpy as np
 
 from . import KIND_F64, KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, Backend
 
-CASES = ("eval", "eval_int", "logup_indexed", "bary", "matrix", "combine", "multiplicity", "project", "ntt")
+CASES = ("eval", "eval_int", "logup_indexed", "bary", "matrix", "combine", "multiplicity", "project", "ntt", "msm")
 
 
 def _challenge(seed):
@@ -93,6 +93,18 @@ def run_case(name, device=0, repeats=2):
     elif name == "ntt":
         v = field_column(1 << 22)
         run = lambda: be.ntt(v, 22)
+    elif name == "msm":
+        # 2^20 points (the Lagrange SRS of a 2^20 domain) against uniform-looking scalars: plain Pippenger
+        import os
+        import sys
+
+        sys.path.insert(0, os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "tests"))
+        import pyref
+
+        G = np.frombuffer(pyref.g1_bytes((pyref.GX, pyref.GY)), dtype=np.uint8).copy()
+        srs = be.srs_lagrange(20, G, x)
+        scalars = field_column(1 << 20)
+        run = lambda: be.msm(scalars, srs, 1 << 20)
     else:
         raise SystemExit(f"unknown profile case {name}; one of {CASES}")
     run()
