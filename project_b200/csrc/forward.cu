@@ -236,7 +236,8 @@ namespace gzk
         // column, so no barrier is needed - only cp.async.wait_group.
         constexpr uint32_t kHeavyDegree = 512;
         constexpr int kAggStages = 4, kAggChunk = 16;
-        constexpr size_t kAggSmemBytes = static_cast<size_t>(kAggStages) * kAggChunk * kThreads * sizeof(double);  // 128 KiB
+        // 128 KiB of gathered values + 4 KiB of attention weights (a private copy per warp)
+        constexpr size_t kAggSmemBytes = static_cast<size_t>(kAggStages) * kAggChunk * (kThreads + kThreads / 32) * sizeof(double);
 
         __global__ void list_heavy_nodes_kernel(const uint32_t* in_ptr, uint64_t nodes, uint32_t* heavy, uint32_t* heavy_count)
         {
@@ -258,7 +259,9 @@ namespace gzk
                                                                            uint32_t width, const double* out_bias, uint32_t bias_count,
                                                                            int apply_activation, double* pre_out, double* agg_out)
         {
-            extern __shared__ double agg_stage[];  // [stage][entry][thread]
+            extern __shared__ double agg_stage[];  // [stage][entry][thread], then per warp [stage][entry] attention weights
+            double* alpha_stage = agg_stage + static_cast<size_t>(kAggStages) * kAggChunk * kThreads + (threadIdx.x >> 5) * (kAggStages * kAggChunk);
+            const uint32_t lane = threadIdx.x & 31;
             const uint32_t count = *heavy_count;
             for (uint32_t item = blockIdx.x; item < count; item += gridDim.x)
             {
@@ -269,40 +272,58 @@ namespace gzk
                 {
                     const uint32_t c = c0 + threadIdx.x;
                     const bool active = c < width;
-                    auto issue = [&](uint32_t ch) {
-                        if (active)
-                        {
-                            const uint32_t base = begin + ch * kAggChunk;
-                            double* slot = agg_stage + static_cast<size_t>(ch % kAggStages) * kAggChunk * kThreads + threadIdx.x;
+                    // The source ids of a chunk are fetched by sixteen lanes (one load per warp instead of sixteen
+                    // broadcast loads in a row) one chunk ahead of their use; the attention weights travel with the
+                    // gathers as asynchronous copies of their own.
+                    auto fetch_sources = [&](uint32_t ch) -> uint32_t {
+                        const uint32_t p = begin + ch * kAggChunk + lane;
+                        return (ch < chunks && lane < kAggChunk && p < end) ? in_src[p] : 0u;
+                    };
+                    auto issue = [&](uint32_t ch, uint32_t my_source) {
+                        const uint32_t base = begin + ch * kAggChunk;
+                        const uint32_t st = ch % kAggStages;
+                        double* slot = agg_stage + static_cast<size_t>(st) * kAggChunk * kThreads + threadIdx.x;
+                        if (lane < kAggChunk && base + lane < end) cp_async_f64(alpha_stage + st * kAggChunk + lane, alpha_in + base + lane);
 #pragma unroll
-                            for (int e = 0; e < kAggChunk; ++e)
-                                if (base + e < end) cp_async_f64(slot + e * kThreads, h + static_cast<uint64_t>(in_src[base + e]) * width + c);
+                        for (int e = 0; e < kAggChunk; ++e)
+                        {
+                            const uint32_t source = __shfl_sync(0xffffffffu, my_source, e);
+                            if (active && base + e < end) cp_async_f64(slot + e * kThreads, h + static_cast<uint64_t>(source) * width + c);
                         }
                         cp_async_commit();  // one group per step, empty or not, so that the wait below counts steps
                     };
+                    uint32_t next_sources = fetch_sources(0);
                     for (uint32_t ch = 0; ch < kAggStages - 1; ++ch)
                     {
+                        const uint32_t mine = next_sources;
+                        next_sources = fetch_sources(ch + 1);
                         if (ch < chunks)
-                            issue(ch);
+                            issue(ch, mine);
                         else
                             cp_async_commit();
                     }
                     double acc = 0.0;
                     for (uint32_t ch = 0; ch < chunks; ++ch)
                     {
-                        if (ch + kAggStages - 1 < chunks)
-                            issue(ch + kAggStages - 1);
+                        const uint32_t ahead = ch + kAggStages - 1;
+                        const uint32_t mine = next_sources;
+                        next_sources = fetch_sources(ahead + 1);
+                        if (ahead < chunks)
+                            issue(ahead, mine);
                         else
                             cp_async_commit();
                         cp_async_wait<kAggStages - 1>();  // everything but the newest three groups has landed: chunk ch is in
+                        __syncwarp();                       // the weights of the chunk were copied by other lanes of this warp
+                        const uint32_t base = begin + ch * kAggChunk;
+                        const uint32_t st = ch % kAggStages;
+                        const double* slot = agg_stage + static_cast<size_t>(st) * kAggChunk * kThreads + threadIdx.x;
                         if (active)
                         {
-                            const uint32_t base = begin + ch * kAggChunk;
-                            const double* slot = agg_stage + static_cast<size_t>(ch % kAggStages) * kAggChunk * kThreads + threadIdx.x;
 #pragma unroll
                             for (int e = 0; e < kAggChunk; ++e)
-                                if (base + e < end) acc = __dadd_rn(acc, __dmul_rn(alpha_in[base + e], slot[e * kThreads]));
+                                if (base + e < end) acc = __dadd_rn(acc, __dmul_rn(alpha_stage[st * kAggChunk + e], slot[e * kThreads]));
                         }
+                        __syncwarp();  // the stage is refilled by the copies issued in the next step
                     }
                     cp_async_wait<0>();
                     if (active)
@@ -482,14 +503,20 @@ extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, cons
         }
         const uint32_t bias_count = head->output_bias != nullptr ? static_cast<uint32_t>(head->output_bias_count) : 0u;
         GZK_CUDA_TRY(ctx, cudaMemsetAsync(heavy_count, 0, 2 * sizeof(uint32_t), ctx->stream));
-        LaunchScope scope(ctx, "forward_aggregate");
-        list_heavy_nodes_kernel<<<grid_for(nodes), kThreads, 0, ctx->stream>>>(in_ptr, nodes, heavy, heavy_count);
-        aggregate_alpha_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(
-            f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, nodes, width, f64_ptr(head->output_bias), bias_count, head->apply_activation,
-            f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg), kHeavyDegree);
-        aggregate_heavy_kernel<<<ctx->sm_count, kThreads, kAggSmemBytes, ctx->stream>>>(
-            f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, heavy, heavy_count, width, f64_ptr(head->output_bias), bias_count, head->apply_activation,
-            f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg));
+        {
+            LaunchScope scope(ctx, "forward_aggregate");
+            list_heavy_nodes_kernel<<<grid_for(nodes), kThreads, 0, ctx->stream>>>(in_ptr, nodes, heavy, heavy_count);
+            aggregate_alpha_kernel<<<grid_for(nodes * width), kThreads, 0, ctx->stream>>>(
+                f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, nodes, width, f64_ptr(head->output_bias), bias_count, head->apply_activation,
+                f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg), kHeavyDegree);
+        }
+        GZK_CUDA_TRY(ctx, cudaGetLastError());
+        {
+            LaunchScope scope(ctx, "forward_aggregate_heavy");
+            aggregate_heavy_kernel<<<ctx->sm_count, kThreads, kAggSmemBytes, ctx->stream>>>(
+                f64_ptr(out->H_prime), alpha_in, in_ptr, in_src, heavy, heavy_count, width, f64_ptr(head->output_bias), bias_count,
+                head->apply_activation, f64_ptr(out->H_agg_pre_bias), f64_ptr(out->H_agg));
+        }
     }
     else if (out->H_agg_pre_bias != nullptr || out->H_agg != nullptr)
     {

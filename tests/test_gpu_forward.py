@@ -39,7 +39,7 @@ def random_graph(rng, nodes, edges, self_loops):
     return src, dst
 
 
-def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, shuffle=False):
+def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, shuffle=False, hubs=()):
     from project_b200 import KIND_F64, KIND_U32, incoming_lists
 
     x = rng.normal(size=(nodes, inner)) * (rng.random((nodes, inner)) < 0.3)
@@ -48,6 +48,12 @@ def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, 
     b_src, b_dst = float(rng.uniform(-0.1, 0.1)), float(rng.uniform(-0.1, 0.1))
     out_bias = rng.uniform(-0.2, 0.2, size=width) if bias else None
     src, dst = random_graph(rng, nodes, edges, self_loops)
+    for node, degree in hubs:  # nodes with long incoming lists (the hubs of a power-law graph)
+        src = np.concatenate([src, rng.integers(0, nodes, size=degree, dtype=np.uint32)])
+        dst = np.concatenate([dst, np.full(degree, node, dtype=np.uint32)])
+    if hubs:
+        order = np.argsort(dst, kind="stable")
+        src, dst = src[order], dst[order]
     if shuffle:  # the reference accepts any edge order; the incoming lists then follow that order
         perm = rng.permutation(src.size)
         src, dst = src[perm], dst[perm]
@@ -95,6 +101,13 @@ def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, 
 ])
 def test_head_forward_matches_oracle(be, nodes, inner, width, edges, self_loops, bias, activation):
     run_case(be, np.random.default_rng(nodes * 7 + width), nodes, inner, width, edges, self_loops, bias, activation)
+
+
+def test_head_forward_with_hub_nodes(be):
+    """Incoming lists of 1500 and 700 entries take the kernels for long lists (one warp per node for the softmax
+    statistics, a CTA per node with asynchronous gathers for the aggregation); 300 output columns need two column
+    passes there and a ragged last tile in the projection."""
+    run_case(be, np.random.default_rng(4242), 600, 20, 300, 5000, True, True, True, hubs=((3, 1500), (5, 700), (599, 513)))
 
 
 def test_head_forward_unsorted_edges(be):
