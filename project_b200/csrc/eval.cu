@@ -331,8 +331,10 @@ namespace gzk
                 eval_partial_kernel<1><<<blocks, kThreads, smem_bytes(1), stream>>>(args);
         }
 
-        // One warp per (rotation, column) pair: the lanes sum the per-tile partials, the
-        // warp adds them up exactly, lane 0 reduces once and writes the result.
+        // One CTA of 256 threads per (rotation, column) pair: the threads sum the per-tile partials
+        // (up to 4096 of them: a single warp walking them was a 40 us chain of dependent loads), the
+        // warps and then the CTA add them up exactly, thread 0 reduces once and writes the result.
+        constexpr int kFinishThreads = 256;
         // `poison_status`: when given and raised (a bounded wait of the partial kernel gave up, so some
         // partial sums were never written), every output becomes 32 bytes of 0xFF - not a canonical
         // field element - instead of a sum over stale partials.
@@ -340,12 +342,13 @@ namespace gzk
                                            uint32_t k_count, Fr* out_canonical, int uniform_kind = -1, int out_montgomery = 0,
                                            const int* poison_status = nullptr)
         {
+            __shared__ uint32_t warp_acc[kFinishThreads / 32][kAccLimbs];
             const uint32_t lane = threadIdx.x & 31;
-            const uint32_t idx = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+            const uint32_t idx = blockIdx.x;
             if (idx >= p_count * k_count) return;
             if (poison_status != nullptr && *poison_status != 0)
             {
-                if (lane == 0)
+                if (threadIdx.x == 0)
                 {
                     Fr bad;
 #pragma unroll
@@ -359,7 +362,7 @@ namespace gzk
             uint32_t acc[kAccLimbs];
 #pragma unroll
             for (int i = 0; i < kAccLimbs; ++i) acc[i] = 0;
-            for (uint32_t tile = lane; tile < tiles; tile += 32)
+            for (uint32_t tile = threadIdx.x; tile < tiles; tile += kFinishThreads)
             {
                 const uint32_t* src = partial + ((static_cast<uint64_t>(tile) * p_count + p) * k_count + k) * kAccLimbs;
                 uint32_t t[kAccLimbs];
@@ -375,7 +378,15 @@ namespace gzk
                 for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, acc[i], offset);
                 acc_add<kAccLimbs, kAccLimbs>(acc, other);
             }
-            if (lane != 0) return;
+            if (lane == 0)
+            {
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) warp_acc[threadIdx.x >> 5][i] = acc[i];
+            }
+            __syncthreads();
+            if (threadIdx.x != 0) return;
+#pragma unroll 1
+            for (int w = 1; w < kFinishThreads / 32; ++w) acc_add<kAccLimbs, kAccLimbs>(acc, warp_acc[w]);
             // acc = 2^256 * S (canonical columns) or 2^512 * S (Montgomery columns), S the
             // true sum; 9 reduction rows divide by 2^288.
             const Fr reduced = redc_wide<FrCfg, 9>(acc);
@@ -407,7 +418,7 @@ namespace gzk
                            Fr* out, bool out_montgomery)
     {
         LaunchScope scope(ctx, "eval_finish");
-        eval_finish_kernel<<<(k_count + 3) / 4, 128, 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
+        eval_finish_kernel<<<k_count, kFinishThreads, 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
                                                                           out_montgomery ? 1 : 0);
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return GZK_OK;
@@ -558,7 +569,7 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
         const uint32_t outs = p_now * static_cast<uint32_t>(k_count);
         {
             LaunchScope scope(ctx, "eval_finish");
-            eval_finish_kernel<<<(outs + 3) / 4, 128, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
+            eval_finish_kernel<<<outs, kFinishThreads, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
                                                                            static_cast<uint32_t>(k_count), d_out + p0 * k_count, -1,
                                                                            dest != nullptr && dest_montgomery ? 1 : 0);
         }
@@ -743,7 +754,7 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     launch_eval_partial(s, args, static_cast<int>(p_count), static_cast<unsigned>(blocks));
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
-    eval_finish_kernel<<<(outs + 3) / 4, 128, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
+    eval_finish_kernel<<<outs, kFinishThreads, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
                                                          static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device), -1, 0, args.status);
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     return GZK_OK;
