@@ -287,7 +287,11 @@ extern "C"
             cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaEventCreateWithFlags(&ctx->copy_event, cudaEventDisableTiming) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 64) != cudaSuccess ||
-            cudaMemset(ctx->d_status, 0, 64) != cudaSuccess)
+            // cleared ON THE CONTEXT'S STREAM and waited for: a cudaMemset would run on the legacy default stream, which
+            // is not ordered with this non-blocking stream, so the first status read (gzk_ctx_set_deferred,
+            // microseconds later) could overtake it and see whatever the memory held before - e.g. the
+            // Montgomery 1 at the head of a domain table a context destroyed just before had freed
+            cudaMemsetAsync(ctx->d_status, 0, 64, ctx->stream) != cudaSuccess || cudaStreamSynchronize(ctx->stream) != cudaSuccess)
         {
             delete ctx;
             return GZK_E_CUDA;

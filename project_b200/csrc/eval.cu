@@ -245,7 +245,38 @@ namespace gzk
                     // I64, FieldElement::from_signed: v < 0 stands for r - |v|.  w * (r - |v|)
                     // is congruent to (r - w) * |v|, which keeps the product 8 x 2 limbs.
                     const long long* values = static_cast<const long long*>(col);
-                    for (uint64_t c = c_begin + lane; c < c_end; c += 32)
+                    uint64_t c = c_begin + lane;
+                    // A few rows per lane at a time: their values and weights are all requested before the first
+                    // product, so the loop waits for memory once per group instead of once per row (with one row in
+                    // flight per lane this path ran at a sixth of its instruction rate).
+                    constexpr int kGroup = P == 1 ? 4 : 2;
+                    for (; c + 32ull * (kGroup - 1) < c_end; c += 32ull * kGroup)
+                    {
+                        long long v[kGroup];
+                        Fr w[kGroup][P];
+#pragma unroll
+                        for (int u = 0; u < kGroup; ++u) v[u] = __ldcs(values + c + 32ull * u);
+#pragma unroll
+                        for (int u = 0; u < kGroup; ++u)
+#pragma unroll
+                            for (int p = 0; p < P; ++p) w[u][p] = load_fr(a.weights + ((c + 32ull * u - a.rot[p]) & a.mask));
+#pragma unroll
+                        for (int u = 0; u < kGroup; ++u)
+                        {
+                            const unsigned long long mag = v[u] < 0 ? 0ULL - static_cast<unsigned long long>(v[u]) : static_cast<unsigned long long>(v[u]);
+                            const uint32_t f[2] = {static_cast<uint32_t>(mag), static_cast<uint32_t>(mag >> 32)};
+#pragma unroll
+                            for (int p = 0; p < P; ++p)
+                            {
+                                const Fr signed_w = v[u] < 0 ? sub(Fr::zero(), w[u][p]) : w[u][p];
+                                if (f[1] == 0)
+                                    acc[p].template mac<1>(signed_w.l, f);
+                                else
+                                    acc[p].template mac<2>(signed_w.l, f);
+                            }
+                        }
+                    }
+                    for (; c < c_end; c += 32)
                     {
                         const long long v = __ldcs(values + c);
                         const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
