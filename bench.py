@@ -373,10 +373,10 @@ def main():
         "bound": "integer_pipe",
         "kernel": "eval_partial_kernel (packed evaluation: commit tau-evaluations, quotient and opening evaluations; all launches of one proof, each timed by itself)",
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None,
-        "traffic": (560.1e6 + 5.4e6) / 545.3e6 * work[0] / max(1, eval_launches),
-        "traffic_note": "average launch of this run: its algorithmic bytes times the ratio ncu measured on a 2^18 x 64-column 2-rotation launch "
-                        "(dram read+write 565.5e6 against 545.3e6 algorithmic; traffic grows in proportion to columns x rows); "
-                        "profiles/eval_partial_kernel_edge2p18x64.md",
+        "traffic": (537.3e6 + 4.2e6) / 536.9e6 * work[0] / max(1, eval_launches),
+        "traffic_note": "average launch of this run: its algorithmic bytes times the ratio ncu measured on a 2^22-row, 3-column launch "
+                        "(dram read+write 541.5e6 against 536.9e6 algorithmic; traffic grows in proportion to columns x rows); "
+                        "profiles/eval_partial_kernel_2p22_rows.md",
         "peak_source": peak_src, "launches": eval_launches, "avg_launch_ms": eval_ms / max(1, eval_launches), "bytes_per_step": int(work[0]),
         "integer_pipe": {"achieved_limb_products_per_s": limb_rate, "measured_peak_limb_products_per_s": mac_peak * 64,
                          "frac": limb_rate / (mac_peak * 64) if mac_peak else None,

@@ -138,6 +138,10 @@ int gzk_fr_op(int op, const uint8_t a[32], const uint8_t b[32], uint8_t out[32])
  * direct-index branch of build_domain_evaluation_weights,
  * include/gatzk/algebra/domain_evaluation.hpp:40-71, which the caller handles). */
 int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf* out);
+/* The same vector when only w[0 .. keep) and w[n-1] will be read (every column of the domain is stored as a
+ * prefix of at most `keep` rows; w[n-1] is what row 0 meets at rotation 1): the other entries of `out` are
+ * not written, which saves their share of the arithmetic. */
+int gzk_bary_weights_prefix(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], uint64_t keep, gzk_buf* out);
 
 /* ---- a3 / a4: packed evaluation and commit inner products ------------------------
  * out[p][k] = sum_{c < len} col_k[c] * w[(c - rot_p) mod n]

@@ -37,6 +37,7 @@ namespace gzk
             Fr scale;   // (x^n - 1)/n, Montgomery
             Fr x2, x4;  // x^2, x^4 (whole-domain kernels)
             Fr root4;   // I = omega^(n/4)
+            uint64_t keep;  // whole-domain kernels: weights with index >= keep are not needed (except the last one, which a rotated evaluation reads for row 0)
         };
 
         __device__ __forceinline__ Fr shfl_fr(const Fr& v, int src_lane)
@@ -410,10 +411,12 @@ namespace gzk
                 const Fr ip1 = mul(a.root4, p1);
                 const Fr plus = add(a.x2, p2), minus = sub(a.x2, p2);
                 const Fr ea = mul(scaled_inverse, p1), eia = mul(scaled_inverse, ip1);
-                store_fr(out + e, mul(ea, mul(add(a.x, p1), plus)));                          // point  a
-                store_fr(out + e + 2 * a.n, neg(mul(ea, mul(sub(a.x, p1), plus))));           // point -a
-                store_fr(out + e + a.n, mul(eia, mul(add(a.x, ip1), minus)));                 // point  Ia
-                store_fr(out + e + 3 * a.n, neg(mul(eia, mul(sub(a.x, ip1), minus))));        // point -Ia
+                const uint64_t last = 4 * a.n - 1;
+                auto wanted = [&](uint64_t index) { return index < a.keep || index == last; };
+                if (wanted(e)) store_fr(out + e, mul(ea, mul(add(a.x, p1), plus)));                                   // point  a
+                if (wanted(e + 2 * a.n)) store_fr(out + e + 2 * a.n, neg(mul(ea, mul(sub(a.x, p1), plus))));          // point -a
+                if (wanted(e + a.n)) store_fr(out + e + a.n, mul(eia, mul(add(a.x, ip1), minus)));                    // point  Ia
+                if (wanted(e + 3 * a.n)) store_fr(out + e + 3 * a.n, neg(mul(eia, mul(sub(a.x, ip1), minus))));       // point -Ia
             }
         }
     }
@@ -432,7 +435,7 @@ namespace gzk
 
 using namespace gzk;
 
-static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], uint64_t first, uint64_t count, gzk_buf* out)
+static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], uint64_t first, uint64_t count, gzk_buf* out, uint64_t keep = ~0ULL)
 {
     if (ctx == nullptr) return GZK_E_INVALID;
     if (x_bytes == nullptr || out == nullptr) return fail(ctx, GZK_E_INVALID, "bary_weights: null argument");
@@ -456,6 +459,7 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     args.n = count;
     args.first = first;
     args.mask = n - 1;
+    args.keep = keep;
     args.x = to_mont(x_plain);
     Fr xn = args.x;
     for (unsigned s = 0; s < log2n; ++s) xn = sqr(xn);
@@ -508,6 +512,13 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     rc = finish_call(ctx, "bary_weights: invalid input");
     if (rc == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
     return rc;
+}
+
+// The whole-domain weights of which only w[0 .. keep) and w[n-1] will be read (columns stored as prefixes shorter
+// than the domain; the last weight meets row 0 at rotation 1): the other entries of `out` are left as they were.
+extern "C" int gzk_bary_weights_prefix(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], uint64_t keep, gzk_buf* out)
+{
+    return bary_impl(ctx, log2n, x_bytes, 0, log2n <= 30 ? (1ULL << log2n) : 0, out, keep);
 }
 
 extern "C" int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], gzk_buf* out)

@@ -248,6 +248,10 @@ namespace
             check(gzk_running_sums_batch(ctx_, raw_jobs.data(), raw_jobs.size()));
         }
         void bary_weights(unsigned log2n, const Fe& x, const ColP& out) override { check(gzk_bary_weights(ctx_, log2n, x.data(), raw(out))); }
+        void bary_weights_prefix(unsigned log2n, const Fe& x, std::size_t keep, const ColP& out) override
+        {
+            check(gzk_bary_weights_prefix(ctx_, log2n, x.data(), keep, raw(out)));
+        }
         void fold_rows(const ColP& m, std::size_t rows, std::size_t cols, const ColP& weights, std::size_t row_count, const ColP& out) override
         {
             check(gzk_fold_rows(ctx_, raw(m), rows, cols, raw(weights), row_count, raw(out)));

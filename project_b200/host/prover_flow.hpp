@@ -154,6 +154,13 @@ namespace gatzk_flow
         }
         // a2 / a9: weights and row folds
         virtual void bary_weights(unsigned log2n, const Fe& x, const ColP& out) = 0;
+        // the same when only the first `keep` weights and the last one will be read (every column of the domain is a
+        // prefix of at most `keep` rows); a backend may leave the other entries unwritten
+        virtual void bary_weights_prefix(unsigned log2n, const Fe& x, std::size_t keep, const ColP& out)
+        {
+            (void)keep;
+            bary_weights(log2n, x, out);
+        }
         virtual void fold_rows(const ColP& matrix, std::size_t rows, std::size_t cols, const ColP& weights, std::size_t row_count, const ColP& out) = 0;
         // a3 / a4 / a5 / a6 / a11: evaluation and commitment; results stay in backend buffers
         virtual void eval_device(const std::vector<ColP>& cols, std::size_t len, unsigned log2n, const ColP& weights,
@@ -827,6 +834,9 @@ namespace gatzk_flow
         dst_multiplicity_ = upload_u32(dst_mult);
 
         // static tables: prover.cpp:460-535
+        // A selector is zero beyond its last 1, so only that prefix has to be evaluated (prefix-stored runs; the
+        // whole-domain run keeps the reference's full-length evaluation).
+        auto sel_len = [&](std::size_t valid) { return compact_ ? std::min(edge_size, valid) : edge_size; };
         auto selector = [&](std::size_t valid) {
             std::vector<std::uint32_t> s(edge_size, 0);
             for (std::size_t i = 0; i < valid && i < edge_size; ++i) s[i] = 1;
@@ -877,9 +887,9 @@ namespace gatzk_flow
         commit_static("P_I", ids_i64_, "N", n_nodes_);
         commit_static("P_src", src_i64_, "edge", n_edges_);
         commit_static("P_dst", dst_i64_, "edge", n_edges_);
-        commit_static("P_Q_new_edge", q_new_, "edge", edge_size);
-        commit_static("P_Q_end_edge", upload_u32(q_end), "edge", edge_size);
-        commit_static("P_Q_edge_valid", q_edge_valid_, "edge", edge_size);
+        commit_static("P_Q_new_edge", q_new_, "edge", sel_len(n_edges_));
+        commit_static("P_Q_end_edge", upload_u32(q_end), "edge", sel_len(n_edges_));
+        commit_static("P_Q_edge_valid", q_edge_valid_, "edge", sel_len(n_edges_));
         {
             auto valid_selector = [&](const std::string& domain, std::size_t valid) {
                 std::vector<std::uint32_t> s(dom_.at(domain).size, 0);
@@ -899,14 +909,14 @@ namespace gatzk_flow
         commit_static("V_T_exp_y", t_exp_y_, "edge", exp_table_size);
         commit_static("V_T_ELU_x", t_elu_x_, "edge", elu_table_size);
         commit_static("V_T_ELU_y", t_elu_y_, "edge", elu_table_size);
-        commit_static("P_Q_tbl_L", q_tbl_l_, "edge", edge_size);
-        commit_static("P_Q_qry_L", q_qry_l_, "edge", edge_size);
-        commit_static("P_Q_tbl_R", q_tbl_r_, "edge", edge_size);
-        commit_static("P_Q_qry_R", q_qry_r_, "edge", edge_size);
-        commit_static("P_Q_tbl_exp", q_tbl_exp_, "edge", edge_size);
-        commit_static("P_Q_qry_exp", q_qry_exp_, "edge", edge_size);
-        commit_static("P_Q_tbl_ELU", q_tbl_elu_, "edge", edge_size);
-        commit_static("P_Q_qry_ELU", q_qry_elu_, "edge", edge_size);
+        commit_static("P_Q_tbl_L", q_tbl_l_, "edge", sel_len(lrelu_table_size));
+        commit_static("P_Q_qry_L", q_qry_l_, "edge", sel_len(n_edges_));
+        commit_static("P_Q_tbl_R", q_tbl_r_, "edge", sel_len(range_size_));
+        commit_static("P_Q_qry_R", q_qry_r_, "edge", sel_len(n_edges_));
+        commit_static("P_Q_tbl_exp", q_tbl_exp_, "edge", sel_len(exp_table_size));
+        commit_static("P_Q_qry_exp", q_qry_exp_, "edge", sel_len(n_edges_));
+        commit_static("P_Q_tbl_ELU", q_tbl_elu_, "edge", sel_len(elu_table_size));
+        commit_static("P_Q_qry_ELU", q_qry_elu_, "edge", sel_len(n_nodes_ * d_h));
 
         // model parameters, quantised as cached_quantized_*_head_parameters do (trace.cpp:1027-1139)
         auto quantise_vector = [&](const std::vector<double>& v) {

@@ -653,7 +653,19 @@ namespace gatzk_flow
             const Domain& d = dom_.at(kDomains[di]);
             const Fe z0 = z.at(kDomains[di]), z1 = mul(z0, d.omega);
             const ColP w_z = be_.alloc(kFrMont, d.size);
-            be_.bary_weights(d.log2n, z0, w_z);
+            {
+                // the longest stored column of the domain bounds the weights that will be read
+                std::size_t keep = std::string(kDomains[di]) == "FH" ? n_nodes_ * in_.feature_count : 0;
+                const auto opened = opened_.find(kDomains[di]);
+                if (opened != opened_.end())
+                    for (const auto& label : opened->second) keep = std::max(keep, columns_.at(label).length);
+                for (const auto& item : static_columns_)
+                    if (item.second.domain == kDomains[di]) keep = std::max(keep, item.second.length);
+                if (compact_ && keep < d.size)
+                    be_.bary_weights_prefix(d.log2n, z0, keep, w_z);
+                else
+                    be_.bary_weights(d.log2n, z0, w_z);
+            }
             std::map<std::string, std::array<Fe, 2>> values;
             evaluate_domain(kDomains[di], w_z, false, values);
             std::vector<std::string> labels = domain_labels(kDomains[di]);
