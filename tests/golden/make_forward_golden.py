@@ -53,4 +53,6 @@ def main(reference_root):
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python make_forward_golden.py <checkout of the reference repository>")
+    main(sys.argv[1])
