@@ -63,23 +63,25 @@ WORKLOAD_NAMES = {
 }
 
 
-def cpu_sample_inputs(workload):
-    """Inputs of the CPU arm and the factor its time is multiplied by."""
+def cpu_sample_inputs(workload, proofs=1):
+    """Inputs of the CPU arm and the factor its time is multiplied by.  The b4 sample shrinks further when many proofs are
+    asked for, so that the whole run stays within a few minutes (a 1/16 graph takes about 26 s per proof on 16 cores)."""
     from project_b200 import synthetic
 
     shape = dict(WORKLOADS[workload])
     if workload != "b4":
         return synthetic.make_inputs(**shape), 1
-    shape["nodes"] //= CPU_SAMPLE_DIVISOR
-    shape["directed_edges"] //= CPU_SAMPLE_DIVISOR
-    return synthetic.make_inputs(**shape), CPU_SAMPLE_DIVISOR
+    divisor = CPU_SAMPLE_DIVISOR if proofs <= 8 else 2 * CPU_SAMPLE_DIVISOR if proofs <= 16 else 4 * CPU_SAMPLE_DIVISOR
+    shape["nodes"] //= divisor
+    shape["directed_edges"] //= divisor
+    return synthetic.make_inputs(**shape), divisor
 
 
-def cpu_sample_text(workload, stats, threads):
+def cpu_sample_text(workload, stats, threads, divisor=CPU_SAMPLE_DIVISOR):
     if workload == "b4":
         return (f"the whole commit+prove flow ({stats['dynamic_commitments']} commitments, {stats['commit_barriers']} barriers) of the same model on a "
-                f"graph of 1/{CPU_SAMPLE_DIVISOR} of the nodes and edges ({WORKLOADS['b4']['nodes'] // CPU_SAMPLE_DIVISOR} nodes), over the CPU "
-                f"restatement, {threads} host threads; time multiplied by {CPU_SAMPLE_DIVISOR} (cost linear in nodes and edges: 26.3 s at 1/16, "
+                f"graph of 1/{divisor} of the nodes and edges ({WORKLOADS['b4']['nodes'] // divisor} nodes), over the CPU "
+                f"restatement, {threads} host threads; time multiplied by {divisor} (cost linear in nodes and edges: 26.3 s at 1/16, "
                 f"103.7 s at 1/4 measured on 16 cores; the full size needs about 150 GB of host memory and seven minutes per proof)")
     return (f"full workload every step: the whole commit+prove flow ({stats['dynamic_commitments']} commitments, {stats['commit_barriers']} barriers) "
             f"over the CPU restatement of the reference's leaves, {threads} host threads where the reference fans out, builders serial per column")
@@ -192,11 +194,11 @@ def run_reference(args):
     if rank != 0:
         return 0
     threads = cpu_count()
-    inputs, factor = cpu_sample_inputs(args.workload)
-    warmup = args.warmup if factor == 1 else min(args.warmup, 1)  # the CPU flow has no warm-up effect worth 26 s a step
+    warmup = args.warmup if args.workload != "b4" else min(args.warmup, 1)  # the CPU flow has no warm-up effect worth 26 s a step
+    inputs, factor = cpu_sample_inputs(args.workload, proofs=args.steps + warmup)
     value, times, stats = cpu_flow_run(inputs, args.steps, warmup, threads, compact=args.workload in COMPACT)
     value *= factor
-    sample = cpu_sample_text(args.workload, stats, threads)
+    sample = cpu_sample_text(args.workload, stats, threads, factor)
     emit({
         "impl": "reference", "metric": METRIC, "value": value, "unit": "ms", "n_gpus": args.gpus, "steps": args.steps, "warmup": warmup,
         "ms_per_step": value, "higher_is_better": False, "scaling": "weak", "vs_baseline": None,
@@ -452,7 +454,7 @@ def main():
         threads = cpu_count()
         cpu_inputs, factor = cpu_sample_inputs(args.workload)
         v, _, cstats = cpu_flow_run(cpu_inputs, 1, 0, threads, compact=compact)
-        cpu_baseline = {"value": v * factor, "unit": "ms", "cores": threads, "kind": "port", "sample": "one proof: " + cpu_sample_text(args.workload, cstats, threads)}
+        cpu_baseline = {"value": v * factor, "unit": "ms", "cores": threads, "kind": "port", "sample": "one proof: " + cpu_sample_text(args.workload, cstats, threads, factor)}
 
     if rank == 0:
         emit({

@@ -6,7 +6,7 @@ import numpy as np
 
 from . import KIND_F64, KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, Backend
 
-CASES = ("eval", "eval_int", "logup_indexed", "bary", "matrix", "combine", "multiplicity", "project", "ntt", "msm")
+CASES = ("eval", "eval_int", "logup_indexed", "bary", "matrix", "combine", "multiplicity", "project", "ntt", "msm", "scan_batch")
 
 
 def _challenge(seed):
@@ -49,7 +49,9 @@ def run_case(name, device=0, repeats=2):
         mult = be.banded_lookup_multiplicity(bx, by, valid, -4096, band, bty, xs * band, n)
         table = be.linear_combination([btx, bty], np.concatenate([one, x]), xs * band, n)
         out = be.alloc(KIND_FR_MONT, n)
-        run = lambda: be.logup_accumulator_indexed(table, mult, bx, by, valid, -4096, band, bty, xs * band, n, _challenge(2), out=out)
+        beta = np.zeros(32, dtype=np.uint8)
+        beta[:16] = rng.integers(0, 256, size=16, dtype=np.uint8)
+        run = lambda: be.logup_accumulator_indexed(table, mult, bx, by, valid, -4096, band, bty, xs * band, n, beta, out=out)
     elif name == "bary":
         out = be.alloc(KIND_FR_MONT, 1 << 22)
         run = lambda: be.bary_weights(22, x, out=out)
@@ -93,6 +95,32 @@ def run_case(name, device=0, repeats=2):
     elif name == "ntt":
         v = field_column(1 << 22)
         run = lambda: be.ntt(v, 22)
+    elif name == "scan_batch":
+        # the independent running sums between two Fiat-Shamir points of one head of the mid-size configuration: four
+        # LogUp accumulators, three route accumulators and two segmented states over 2^18 rows, one batched call
+        from .lib import SCAN_GROUP_PREFIX, SCAN_LOGUP, SCAN_ROUTE_EDGE, SCAN_ROUTE_NODE
+
+        n, valid = 1 << 18, (1 << 18) - 37
+        sel = np.zeros(n, dtype=np.uint32)
+        sel[:valid] = 1
+        starts = (rng.random(n) < 0.1).astype(np.uint32)
+        starts[0] = 1
+        bsel, bstarts = be.upload(sel, KIND_U32), be.upload(starts, KIND_U32)
+        mult = be.upload(rng.integers(0, 4, size=n, dtype=np.uint32), KIND_U32)
+        fields = [field_column(n) for _ in range(8)]
+        outs = [be.alloc(KIND_FR_MONT, n) for _ in range(9)]
+        beta = np.zeros(32, dtype=np.uint8)  # unrelated to the multiplier inside the field columns
+        beta[:16] = rng.integers(0, 256, size=16, dtype=np.uint8)
+        jobs = [(SCAN_LOGUP, [fields[0], fields[1], mult, bsel, bsel], valid, n, beta, outs[0]),
+                (SCAN_LOGUP, [fields[2], fields[3], mult, bsel, bsel], valid, n, beta, outs[1]),
+                (SCAN_LOGUP, [fields[4], fields[5], mult, bsel, bsel], valid, n, beta, outs[2]),
+                (SCAN_LOGUP, [fields[6], fields[7], mult, bsel, bsel], valid, n, beta, outs[3]),
+                (SCAN_ROUTE_NODE, [fields[0], mult], valid, n, beta, outs[4]),
+                (SCAN_ROUTE_EDGE, [fields[1]], valid, n, beta, outs[5]),
+                (SCAN_ROUTE_EDGE, [fields[3]], valid, n, beta, outs[6]),
+                (SCAN_GROUP_PREFIX, [fields[5], bstarts], n, n, None, outs[7]),
+                (SCAN_GROUP_PREFIX, [mult, bstarts], n, n, None, outs[8])]
+        run = lambda: be.running_sums_batch(jobs)
     elif name == "msm":
         # 2^20 points (the Lagrange SRS of a 2^20 domain) against uniform-looking scalars: plain Pippenger
         import os
