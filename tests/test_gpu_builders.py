@@ -461,3 +461,53 @@ def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y):
     with pytest.raises(GzkError) as e:
         be.logup_accumulator_indexed(table, mult, be.upload(bad, KIND_I64), by, valid, x_min, band, bty, table_size, n, beta)
     assert e.value.code == 1
+
+
+@pytest.mark.parametrize("kind_name", ["i64", "u32"])
+def test_small_integer_matrix_kernels_with_values_of_every_width(be, kind_name):
+    """fold_rows, linear_form_rows, matrix_horner (blocked path: 300 x 256 = 76 800 entries), packed evaluation and
+    linear_combination on small-integer buffers whose values range from a few bits to the whole 64-bit range: the
+    one-limb fast paths, the biased entries (v + 2^31 spilling into further limbs) and the two-limb paths must all agree
+    with the field arithmetic of the oracle."""
+    from project_b200 import KIND_FR_MONT, KIND_I64, KIND_U32
+
+    rng = np.random.default_rng(909)
+    rows, cols = 300, 256
+    if kind_name == "i64":
+        vals = rng.integers(-1000, 1000, size=rows * cols, dtype=np.int64)
+        wide = rng.integers(0, rows * cols, size=6000)
+        vals[wide[:2000]] = rng.integers(-(1 << 40), 1 << 40, size=2000, dtype=np.int64)
+        vals[wide[2000:4000]] = rng.integers(-(1 << 62), 1 << 62, size=2000, dtype=np.int64)
+        edge = np.array([np.iinfo(np.int64).max, np.iinfo(np.int64).min, -(1 << 31), (1 << 31) - 1, 1 << 31, -(1 << 31) - 1, (1 << 32) - 1, -(1 << 32)],
+                        dtype=np.int64)
+        vals[wide[4000:4008]] = edge
+        kind = KIND_I64
+        as_field = ora.fr_from_i64(vals)
+    else:
+        vals = rng.integers(0, 1 << 32, size=rows * cols, dtype=np.uint32)
+        vals[:100] = 0xFFFFFFFF
+        kind = KIND_U32
+        as_field = ora.fr_from_i64(vals.astype(np.int64))
+    m = as_field.reshape(rows, cols, 32)
+    buf = be.upload(vals, kind)
+    w = rand_fr(rng, rows)
+    got = be.fold_rows(buf, rows, cols, be.upload(w, KIND_FR_MONT), rows).download()
+    assert np.array_equal(got, ora.weighted_column_sum(m, w, rows))
+    c = fr_array([int(rng.integers(2, 1 << 62))])
+    got = be.linear_form_rows(buf, rows, cols, be.powers(c, cols)).download()
+    assert np.array_equal(got, ora.linear_form_by_powers(m, ora.powers(c, cols)))
+    assert np.array_equal(be.matrix_horner(buf, rows, cols, c), ora.matrix_row_major_eval(m, c))
+    # packed evaluation of the same values read as one long column, and a linear combination with a field column
+    n = 1 << 17
+    weights = be.bary_weights(17, c)
+    got = be.eval_batch([buf], rows * cols, 17, weights, (0, 1))
+    padded = np.zeros((1, n, 32), dtype=np.uint8)
+    padded[0, :rows * cols] = as_field
+    assert np.array_equal(got, ora.eval_rotations(padded, weights.download(), (0, 1)))
+    other = rand_fr(rng, rows * cols)
+    coeff = np.concatenate([fr_array([1]), c])
+    got = be.linear_combination([buf, be.upload(other, KIND_FR_MONT)], coeff, rows * cols, rows * cols).download()
+    assert np.array_equal(got, ora.weighted_sum(as_field, c, other, rows * cols))
+    got2 = be.linear_combination([buf, buf], coeff, rows * cols, rows * cols).download()  # every term a small integer: the three-row reduction
+    one_plus_c = fr_array([(1 + int.from_bytes(bytes(c.reshape(-1)), "little")) % R])
+    assert np.array_equal(got2, be.linear_combination([buf], one_plus_c, rows * cols, rows * cols).download())
