@@ -142,6 +142,10 @@ int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf*
  * prefix of at most `keep` rows; w[n-1] is what row 0 meets at rotation 1): the other entries of `out` are
  * not written, which saves their share of the arithmetic. */
 int gzk_bary_weights_prefix(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], uint64_t keep, gzk_buf* out);
+/* Weight vectors of one domain at `count` points (points: count x 32 bytes) into outs[0 .. count): for a domain of at
+ * most 2^18 points and up to four points one launch (the binding points a head draws at the same transcript stage,
+ * src/protocol/trace.cpp:2461-2530, are independent dependent-chains); otherwise one gzk_bary_weights per point. */
+int gzk_bary_weights_multi(gzk_ctx* ctx, unsigned log2n, const uint8_t* points, size_t count, gzk_buf* const* outs);
 
 /* ---- a3 / a4: packed evaluation and commit inner products ------------------------
  * out[p][k] = sum_{c < len} col_k[c] * w[(c - rot_p) mod n]

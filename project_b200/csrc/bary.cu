@@ -339,13 +339,21 @@ namespace gzk
         // node-domain weights every binding of the flow asks for) is one dependent chain, so it takes one
         // quartet per thread and spreads over as many SMs as it has 256-quartet groups; a large domain
         // takes four and amortises the serial inversion over 1024 quartets.
-        template <int ELEMS>
-        __global__ void __launch_bounds__(kThreads, 2) bary4_fused_kernel(BaryArgs a, Fr* out, int* status)
+        struct FusedShared
         {
-            __shared__ Fr warp_incl[kThreads / 32];
-            __shared__ Fr warp_pre[kThreads / 32];
-            __shared__ Fr warp_suf[kThreads / 32];
-            __shared__ Fr cta_inverse;
+            Fr warp_incl[kThreads / 32];
+            Fr warp_pre[kThreads / 32];
+            Fr warp_suf[kThreads / 32];
+            Fr cta_inverse;
+        };
+
+        template <int ELEMS>
+        __device__ __forceinline__ void bary4_fused_body(const BaryArgs& a, Fr* out, int* status, FusedShared& sh)
+        {
+            Fr* warp_incl = sh.warp_incl;
+            Fr* warp_pre = sh.warp_pre;
+            Fr* warp_suf = sh.warp_suf;
+            Fr& cta_inverse = sh.cta_inverse;
             const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kThreads * ELEMS);
             const int lane = threadIdx.x & 31;
             const int warp = threadIdx.x >> 5;
@@ -418,6 +426,27 @@ namespace gzk
                 if (wanted(e + a.n)) store_fr(out + e + a.n, mul(eia, mul(add(a.x, ip1), minus)));                    // point  Ia
                 if (wanted(e + 3 * a.n)) store_fr(out + e + 3 * a.n, neg(mul(eia, mul(sub(a.x, ip1), minus))));       // point -Ia
             }
+        }
+
+        template <int ELEMS>
+        __global__ void __launch_bounds__(kThreads, 2) bary4_fused_kernel(BaryArgs a, Fr* out, int* status)
+        {
+            __shared__ FusedShared sh;
+            bary4_fused_body<ELEMS>(a, out, status, sh);
+        }
+
+        // Several points of one small domain in one launch (blockIdx.y picks the point): the weight vectors a head
+        // needs at the same Fiat-Shamir stage are independent dependent-chains, so side by side they cost one chain.
+        constexpr int kMaxPoints = 4;
+        struct BaryMultiArgs
+        {
+            BaryArgs point[kMaxPoints];
+            Fr* out[kMaxPoints];
+        };
+        __global__ void __launch_bounds__(kThreads, 2) bary4_fused_multi_kernel(BaryMultiArgs m, int* status)
+        {
+            __shared__ FusedShared sh;
+            bary4_fused_body<1>(m.point[blockIdx.y], m.out[blockIdx.y], status, sh);
         }
     }
 
@@ -507,6 +536,66 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     {
         LaunchScope scope(ctx, "bary_finish");
         bary_finish_kernel<<<blocks, kThreads, 0, ctx->stream>>>(args, products, static_cast<Fr*>(out->dptr));
+    }
+    GZK_CUDA_TRY(ctx, cudaGetLastError());
+    rc = finish_call(ctx, "bary_weights: invalid input");
+    if (rc == GZK_E_DOMAIN) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
+    return rc;
+}
+
+// Weights of the same small domain at several points in one launch (gzk_bary_weights for each otherwise).
+extern "C" int gzk_bary_weights_multi(gzk_ctx* ctx, unsigned log2n, const uint8_t* points, size_t count, gzk_buf* const* outs)
+{
+    if (ctx == nullptr) return GZK_E_INVALID;
+    if (count == 0) return GZK_OK;
+    if (points == nullptr || outs == nullptr) return fail(ctx, GZK_E_INVALID, "bary_weights_multi: null argument");
+    const uint64_t n = log2n <= 30 ? (1ULL << log2n) : 0;
+    const bool one_launch = count <= static_cast<size_t>(kMaxPoints) && n >= 4 && n / 4 <= (1u << 16);
+    if (!one_launch)
+    {
+        for (size_t j = 0; j < count; ++j)
+        {
+            const int rc = bary_impl(ctx, log2n, points + 32 * j, 0, n, outs[j]);
+            if (rc != GZK_OK) return rc;
+        }
+        return GZK_OK;
+    }
+    GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+    const DomainTables* dom = nullptr;
+    int rc = get_domain(ctx, log2n, &dom);
+    if (rc != GZK_OK) return rc;
+    BaryMultiArgs m{};
+    for (size_t j = 0; j < count; ++j)
+    {
+        if (outs[j] == nullptr || outs[j]->kind != GZK_KIND_FR_MONT || outs[j]->count < n)
+            return fail(ctx, GZK_E_INVALID, "bary_weights: output must be a Montgomery buffer of the requested size");
+        bool canonical = false;
+        const Fr x_plain = host_fr_from_bytes(points + 32 * j, &canonical);
+        if (!canonical) return fail(ctx, GZK_E_INVALID, "bary_weights: x is not a canonical field element");
+        BaryArgs& a = m.point[j];
+        a.lo = dom->lo;
+        a.hi = dom->hi;
+        a.lo_bits = dom->lo_bits;
+        a.n = n / 4;
+        a.first = 0;
+        a.mask = n - 1;
+        a.keep = ~0ULL;
+        a.x = to_mont(x_plain);
+        Fr xn = a.x;
+        for (unsigned s = 0; s < log2n; ++s) xn = sqr(xn);
+        const Fr zero_eval = sub(xn, Fr::one());
+        if (zero_eval.is_zero()) return fail(ctx, GZK_E_DOMAIN, "bary_weights: x is a point of the domain");
+        a.scale = mul(zero_eval, dom->inv_size);
+        a.x2 = sqr(a.x);
+        a.x4 = sqr(a.x2);
+        a.root4 = host_root_of_unity(2);
+        m.out[j] = static_cast<Fr*>(outs[j]->dptr);
+    }
+    if ((rc = begin_call(ctx)) != GZK_OK) return rc;
+    {
+        LaunchScope scope(ctx, "bary_fused");
+        const dim3 grid(static_cast<unsigned>((n / 4 + kThreads - 1) / kThreads), static_cast<unsigned>(count));
+        bary4_fused_multi_kernel<<<grid, kThreads, 0, ctx->stream>>>(m, ctx->d_status);
     }
     GZK_CUDA_TRY(ctx, cudaGetLastError());
     rc = finish_call(ctx, "bary_weights: invalid input");

@@ -248,6 +248,17 @@ namespace
             check(gzk_running_sums_batch(ctx_, raw_jobs.data(), raw_jobs.size()));
         }
         void bary_weights(unsigned log2n, const Fe& x, const ColP& out) override { check(gzk_bary_weights(ctx_, log2n, x.data(), raw(out))); }
+        void bary_weights_multi(unsigned log2n, const std::vector<Fe>& xs, const std::vector<ColP>& outs) override
+        {
+            std::vector<std::uint8_t> points(32 * xs.size());
+            std::vector<gzk_buf*> bufs;
+            for (std::size_t i = 0; i < xs.size(); ++i)
+            {
+                std::memcpy(points.data() + 32 * i, xs[i].data(), 32);
+                bufs.push_back(raw(outs[i]));
+            }
+            check(gzk_bary_weights_multi(ctx_, log2n, points.data(), xs.size(), bufs.data()));
+        }
         void bary_weights_prefix(unsigned log2n, const Fe& x, std::size_t keep, const ColP& out) override
         {
             check(gzk_bary_weights_prefix(ctx_, log2n, x.data(), keep, raw(out)));

@@ -154,6 +154,11 @@ namespace gatzk_flow
         }
         // a2 / a9: weights and row folds
         virtual void bary_weights(unsigned log2n, const Fe& x, const ColP& out) = 0;
+        // weights of one domain at several points; a backend may compute them side by side
+        virtual void bary_weights_multi(unsigned log2n, const std::vector<Fe>& xs, const std::vector<ColP>& outs)
+        {
+            for (std::size_t i = 0; i < xs.size(); ++i) bary_weights(log2n, xs[i], outs[i]);
+        }
         // the same when only the first `keep` weights and the last one will be read (every column of the domain is a
         // prefix of at most `keep` rows); a backend may leave the other entries unwritten
         virtual void bary_weights_prefix(unsigned log2n, const Fe& x, std::size_t keep, const ColP& out)
@@ -568,7 +573,16 @@ namespace gatzk_flow
             ColP a, b, acc;
         };
         Binding build_binding(const ColP& matrix, std::size_t rows, std::size_t cols, const Fe& point, const ColP& parameter_values,
-                              const std::string& dim_domain, ColP* weights_out = nullptr);
+                              const std::string& dim_domain, ColP* weights_out = nullptr, const ColP& ready_weights = nullptr);
+        // node-domain weights at the binding points drawn at one transcript stage, side by side
+        std::vector<ColP> node_weights_at(const std::vector<Fe>& points)
+        {
+            const Domain& n = dom_.at("N");
+            std::vector<ColP> outs;
+            for (std::size_t i = 0; i < points.size(); ++i) outs.push_back(be_.alloc(kFrMont, n.size));
+            be_.bary_weights_multi(n.log2n, points, outs);
+            return outs;
+        }
         struct Lookup
         {
             ColP table, query, multiplicity, acc;
@@ -1142,12 +1156,17 @@ namespace gatzk_flow
 
     // build_binding_trace, src/protocol/trace.cpp:1595-1621
     inline ProverFlow::Binding ProverFlow::build_binding(const ColP& matrix, std::size_t rows, std::size_t cols, const Fe& point,
-                                                         const ColP& parameter_values, const std::string& dim_domain, ColP* weights_out)
+                                                         const ColP& parameter_values, const std::string& dim_domain, ColP* weights_out,
+                                                         const ColP& ready_weights)
     {
         const Domain& n = dom_.at("N");
         const Domain& dd = dom_.at(dim_domain);
-        const ColP weights = be_.alloc(kFrMont, n.size);
-        be_.bary_weights(n.log2n, point, weights);
+        ColP weights = ready_weights;
+        if (weights == nullptr)
+        {
+            weights = be_.alloc(kFrMont, n.size);
+            be_.bary_weights(n.log2n, point, weights);
+        }
         Binding out;
         out.a = be_.alloc(kFr, dd.size);
         be_.zero(out.a);
@@ -1402,11 +1421,12 @@ namespace gatzk_flow
         be_.linear_form_rows(param_matrices_.at(w_label), layer.input_dim, d, y_proj_powers, proj_b_mont);
         const ColP input_q = layer_index == 0 ? features_q_ : layer_inputs_q_.at(layer_index);
         ColP w_src, w_dst, w_star;
-        const Binding proj = build_binding(input_q, n_nodes_, layer.input_dim, y_proj, proj_b_mont, "in");
+        const std::vector<ColP> stage_weights = node_weights_at({y_proj, y_src, y_dst});
+        const Binding proj = build_binding(input_q, n_nodes_, layer.input_dim, y_proj, proj_b_mont, "in", nullptr, stage_weights[0]);
         const ColP a_src_col = upload_fe(param_vectors_.at("V_h" + h + "_a_src"), dom_.at("d").size);
         const ColP a_dst_col = upload_fe(param_vectors_.at("V_h" + h + "_a_dst"), dom_.at("d").size);
-        const Binding src_b = build_binding(w.h_prime, n_nodes_, d, y_src, a_src_col, "d", &w_src);
-        const Binding dst_b = build_binding(w.h_prime, n_nodes_, d, y_dst, a_dst_col, "d", &w_dst);
+        const Binding src_b = build_binding(w.h_prime, n_nodes_, d, y_src, a_src_col, "d", &w_src, stage_weights[1]);
+        const Binding dst_b = build_binding(w.h_prime, n_nodes_, d, y_dst, a_dst_col, "d", &w_dst, stage_weights[2]);
         absorb_dyn(t, prefix + "H_star");
         const Fe y_star = challenge(t, "y_star_h" + h);
         const ColP xi_powers_padded = be_.alloc(kFrMont, dom_.at("d").size);
@@ -1506,8 +1526,9 @@ namespace gatzk_flow
         const Fe beta_dst = challenge(t, "beta_dst_h" + h);
 
         ColP w_agg_pre, w_agg;
-        const Binding agg_pre_b = build_binding(w.h_agg_pre, n_nodes_, d, y_agg_pre, xi_powers_padded, "d", &w_agg_pre);
-        const Binding agg_b = build_binding(w.h_agg, n_nodes_, d, y_agg, xi_powers_padded, "d", &w_agg);
+        const std::vector<ColP> agg_weights = node_weights_at({y_agg_pre, y_agg});
+        const Binding agg_pre_b = build_binding(w.h_agg_pre, n_nodes_, d, y_agg_pre, xi_powers_padded, "d", &w_agg_pre, agg_weights[0]);
+        const Binding agg_b = build_binding(w.h_agg, n_nodes_, d, y_agg, xi_powers_padded, "d", &w_agg, agg_weights[1]);
         // ELU lookup over the flattened node_count x d matrices (trace.cpp:2920-2971): the row-major
         // matrix buffers ARE the flat columns
         const std::size_t flat = n_nodes_ * d;

@@ -180,10 +180,13 @@ namespace gatzk_flow
         be_.zero(proj_b);
         be_.linear_form_rows(param_matrices_.at(v_base + "_W"), cat_width, c, y_proj_powers, proj_b);
         ColP w_src, w_dst, w_star;
-        const Binding proj = build_binding(h_cat_q, n_nodes_, cat_width, y_proj, proj_b, "cat");
-        const Binding src_b = build_binding(y_prime, n_nodes_, c, y_src, upload_fe(param_vectors_.at(v_base + "_a_src"), cd.size), "C", &w_src);
-        const Binding dst_b = build_binding(y_prime, n_nodes_, c, y_dst, upload_fe(param_vectors_.at(v_base + "_a_dst"), cd.size), "C", &w_dst);
-        const Binding y_b = build_binding(y_lin, n_nodes_, c, y_out_star, xi_powers, "C", &w_star);
+        const std::vector<ColP> stage_weights = node_weights_at({y_proj, y_src, y_dst, y_out_star});
+        const Binding proj = build_binding(h_cat_q, n_nodes_, cat_width, y_proj, proj_b, "cat", nullptr, stage_weights[0]);
+        const Binding src_b =
+            build_binding(y_prime, n_nodes_, c, y_src, upload_fe(param_vectors_.at(v_base + "_a_src"), cd.size), "C", &w_src, stage_weights[1]);
+        const Binding dst_b =
+            build_binding(y_prime, n_nodes_, c, y_dst, upload_fe(param_vectors_.at(v_base + "_a_dst"), cd.size), "C", &w_dst, stage_weights[2]);
+        const Binding y_b = build_binding(y_lin, n_nodes_, c, y_out_star, xi_powers, "C", &w_star, stage_weights[3]);
         const Fe eta_dst = challenge(t, cname("eta_dst_out"));
         const Fe beta_dst = challenge(t, cname("beta_dst_out"));
         const Route dst_route = build_route({ids_i64_, w.e_dst, w.m, w.sum, w.inv, y_star},
