@@ -105,6 +105,10 @@ int gzk_buf_wrap(gzk_ctx* ctx, int kind, size_t count, void* device_ptr, gzk_buf
  * buffer holds from now on, for work areas that are refilled by copies (gzk_transpose,
  * gzk_swap_outer, an exchange between GPUs); nothing is converted. */
 int gzk_buf_retag(gzk_buf* buf, int kind);
+/* Copies `count` elements from host memory (canonical form; an FR_MONT or G1 buffer converts on the
+ * device).  The host memory may be reused as soon as the call returns.  The call waits for the copy,
+ * except in deferred mode for uploads of at most 256 KiB, which are staged and ordered on the
+ * context's stream like a kernel (another context sees them after gzk_ctx_synchronize). */
 int gzk_buf_upload(gzk_ctx* ctx, gzk_buf* buf, size_t offset, const void* host, size_t count);
 /* gzk_buf_upload_async queues the copy on a second stream so that it overlaps with kernels
  * in flight (host memory should be pinned and must stay valid); gzk_copy_fence makes all

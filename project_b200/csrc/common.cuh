@@ -89,6 +89,14 @@ struct gzk_ctx
     void* pinned = nullptr;  // small pinned staging area for results
     size_t pinned_bytes = 0;
     int* d_status = nullptr;  // device-side status word (zero-denominator flags etc.)
+    // pinned ring for the small uploads of deferred mode: the data is copied into a slot and the
+    // call returns without waiting; a slot is reused once the copy that read it has completed
+    static constexpr int kUploadSlots = 16;
+    static constexpr size_t kUploadSlotBytes = 256u << 10;
+    char* upload_ring = nullptr;
+    cudaEvent_t upload_done[kUploadSlots] = {};
+    bool upload_busy[kUploadSlots] = {};
+    int upload_next = 0;
     bool timing = false;
     bool deferred = false;  // builder calls return without synchronising; errors surface at gzk_ctx_synchronize
     std::vector<gzk::FamilyStat> families;

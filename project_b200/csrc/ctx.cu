@@ -167,38 +167,58 @@ namespace gzk
 
     void host_fr_to_bytes(const Fr& canonical, uint8_t* bytes) { std::memcpy(bytes, canonical.l, 32); }
 
-    Fr host_root_of_unity(unsigned log2n)
+    namespace
     {
-        // exponent = (r - 1) >> log2n, as FieldElement::root_of_unity divides (r-1) by n
-        uint32_t e[8];
-        for (int i = 0; i < 8; ++i) e[i] = FrCfg::mod(i);
-        e[0] -= 1;
-        for (unsigned s = 0; s < log2n; ++s)
+        // 5^((r - 1) >> log2n), as FieldElement::root_of_unity divides (r-1) by n
+        Fr root_of_unity_by_power(unsigned log2n)
         {
-            for (int i = 0; i < 8; ++i)
+            uint32_t e[8];
+            for (int i = 0; i < 8; ++i) e[i] = FrCfg::mod(i);
+            e[0] -= 1;
+            for (unsigned s = 0; s < log2n; ++s)
             {
-                e[i] >>= 1;
-                if (i + 1 < 8) e[i] |= e[i + 1] << 31;
-            }
-        }
-        Fr five = Fr::zero();
-        five.l[0] = 5;
-        const Fr base = to_mont(five);
-        Fr out = Fr::one();
-        bool started = false;
-        for (int limb = 7; limb >= 0; --limb)
-        {
-            for (int bit = 31; bit >= 0; --bit)
-            {
-                if (started) out = sqr(out);
-                if ((e[limb] >> bit) & 1U)
+                for (int i = 0; i < 8; ++i)
                 {
-                    out = started ? mul(out, base) : base;
-                    started = true;
+                    e[i] >>= 1;
+                    if (i + 1 < 8) e[i] |= e[i + 1] << 31;
                 }
             }
+            Fr five = Fr::zero();
+            five.l[0] = 5;
+            const Fr base = to_mont(five);
+            Fr out = Fr::one();
+            bool started = false;
+            for (int limb = 7; limb >= 0; --limb)
+            {
+                for (int bit = 31; bit >= 0; --bit)
+                {
+                    if (started) out = sqr(out);
+                    if ((e[limb] >> bit) & 1U)
+                    {
+                        out = started ? mul(out, base) : base;
+                        started = true;
+                    }
+                }
+            }
+            return out;
         }
-        return out;
+        struct RootTable
+        {
+            Fr root[33];
+            // the 2^32-th root by one exponentiation, every smaller one by squaring it
+            RootTable()
+            {
+                root[32] = root_of_unity_by_power(32);
+                for (int k = 31; k >= 0; --k) root[k] = sqr(root[k + 1]);
+            }
+        };
+    }
+
+    // Every weight vector and every domain asks for a root; the table is built on first use.
+    Fr host_root_of_unity(unsigned log2n)
+    {
+        static const RootTable table;
+        return table.root[log2n <= 32 ? log2n : 32];
     }
 
     int get_domain(gzk_ctx* ctx, unsigned log2n, const DomainTables** out)
@@ -318,6 +338,11 @@ extern "C"
             if (t != nullptr) cudaFree(t);
         for (auto& t : ctx->ntt_twists) cudaFree(t.table);
         if (ctx->pinned != nullptr) cudaFreeHost(ctx->pinned);
+        if (ctx->upload_ring != nullptr)
+        {
+            cudaFreeHost(ctx->upload_ring);
+            for (auto e : ctx->upload_done) cudaEventDestroy(e);
+        }
         if (ctx->d_status != nullptr) cudaFree(ctx->d_status);
         timing_collect(ctx);
         g1_release_tables(ctx);
@@ -483,7 +508,32 @@ extern "C"
         if (offset + count > buf->count) return fail(ctx, GZK_E_INVALID, "upload exceeds the buffer");
         if (count == 0) return GZK_OK;
         char* dst = static_cast<char*>(buf->dptr) + offset * buf->elem_bytes;
-        GZK_CUDA_TRY(ctx, cudaMemcpyAsync(dst, host, count * buf->elem_bytes, cudaMemcpyHostToDevice, ctx->stream));
+        const size_t bytes = count * buf->elem_bytes;
+        // Deferred mode, small upload: stage it in a pinned slot and return without waiting, so that the
+        // caller keeps queueing work behind the kernels still running (a synchronous upload in the
+        // middle of a stage drains the stream and leaves the device idle while the host catches up).
+        const bool staged = ctx->deferred && bytes <= gzk_ctx::kUploadSlotBytes;
+        if (staged)
+        {
+            GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+            if (ctx->upload_ring == nullptr)
+            {
+                GZK_CUDA_TRY(ctx, cudaHostAlloc(reinterpret_cast<void**>(&ctx->upload_ring), gzk_ctx::kUploadSlots * gzk_ctx::kUploadSlotBytes, cudaHostAllocDefault));
+                for (auto& e : ctx->upload_done) GZK_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            }
+            const int slot = ctx->upload_next;
+            ctx->upload_next = (slot + 1) % gzk_ctx::kUploadSlots;
+            if (ctx->upload_busy[slot]) GZK_CUDA_TRY(ctx, cudaEventSynchronize(ctx->upload_done[slot]));
+            char* stage = ctx->upload_ring + static_cast<size_t>(slot) * gzk_ctx::kUploadSlotBytes;
+            std::memcpy(stage, host, bytes);
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(dst, stage, bytes, cudaMemcpyHostToDevice, ctx->stream));
+            GZK_CUDA_TRY(ctx, cudaEventRecord(ctx->upload_done[slot], ctx->stream));
+            ctx->upload_busy[slot] = true;
+        }
+        else
+        {
+            GZK_CUDA_TRY(ctx, cudaMemcpyAsync(dst, host, bytes, cudaMemcpyHostToDevice, ctx->stream));
+        }
         if (buf->kind == GZK_KIND_FR_MONT)
         {
             Fr* p = reinterpret_cast<Fr*>(dst);
@@ -497,7 +547,7 @@ extern "C"
             const int rc = launch_convert_fp(ctx, dst, dst, count * 2, true);
             if (rc != GZK_OK) return rc;
         }
-        GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        if (!staged) GZK_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
         return GZK_OK;
     }
 
@@ -611,6 +661,82 @@ extern "C"
         return GZK_OK;
     }
 
+    namespace
+    {
+        // Montgomery product on four 64-bit limbs (coarsely integrated operand scanning): the host's
+        // 64x64->128 multiplier does in 32 products what the kernels' 32-bit limb code does in 128.
+        struct HostFr64
+        {
+            uint64_t modulus[4], r2[4], n0;  // n0 = -modulus^-1 mod 2^64
+            HostFr64()
+            {
+                const Fr rr = Fr::r2();
+                for (int i = 0; i < 4; ++i)
+                {
+                    modulus[i] = static_cast<uint64_t>(FrCfg::mod(2 * i)) | (static_cast<uint64_t>(FrCfg::mod(2 * i + 1)) << 32);
+                    r2[i] = static_cast<uint64_t>(rr.l[2 * i]) | (static_cast<uint64_t>(rr.l[2 * i + 1]) << 32);
+                }
+                uint64_t x = 1;  // Newton: x <- x (2 - m x) doubles the correct low bits
+                for (int i = 0; i < 6; ++i) x *= 2 - modulus[0] * x;
+                n0 = ~x + 1;
+            }
+            void mul(const uint64_t a[4], const uint64_t b[4], uint64_t out[4]) const
+            {
+                using u128 = unsigned __int128;
+                uint64_t t[6] = {0, 0, 0, 0, 0, 0};
+                for (int i = 0; i < 4; ++i)
+                {
+                    uint64_t carry = 0;
+                    for (int j = 0; j < 4; ++j)
+                    {
+                        const u128 w = static_cast<u128>(a[j]) * b[i] + t[j] + carry;
+                        t[j] = static_cast<uint64_t>(w);
+                        carry = static_cast<uint64_t>(w >> 64);
+                    }
+                    u128 top = static_cast<u128>(t[4]) + carry;
+                    t[4] = static_cast<uint64_t>(top);
+                    t[5] = static_cast<uint64_t>(top >> 64);
+                    const uint64_t q = t[0] * n0;
+                    u128 w = static_cast<u128>(q) * modulus[0] + t[0];
+                    carry = static_cast<uint64_t>(w >> 64);
+                    for (int j = 1; j < 4; ++j)
+                    {
+                        w = static_cast<u128>(q) * modulus[j] + t[j] + carry;
+                        t[j - 1] = static_cast<uint64_t>(w);
+                        carry = static_cast<uint64_t>(w >> 64);
+                    }
+                    top = static_cast<u128>(t[4]) + carry;
+                    t[3] = static_cast<uint64_t>(top);
+                    t[4] = t[5] + static_cast<uint64_t>(top >> 64);
+                }
+                // t < 2 * modulus: one conditional subtraction
+                uint64_t d[4];
+                unsigned __int128 borrow = 0;
+                for (int j = 0; j < 4; ++j)
+                {
+                    const u128 w = static_cast<u128>(t[j]) - modulus[j] - static_cast<uint64_t>(borrow);
+                    d[j] = static_cast<uint64_t>(w);
+                    borrow = (w >> 64) & 1;
+                }
+                const bool keep = t[4] == 0 && borrow != 0;
+                for (int j = 0; j < 4; ++j) out[j] = keep ? t[j] : d[j];
+            }
+        };
+        // product of two canonical elements, canonical: (a R^2 / R) b / R
+        Fr host_mul_canonical(const Fr& a, const Fr& b)
+        {
+            static const HostFr64 f;
+            uint64_t x[4], y[4], ar[4], out[4];
+            std::memcpy(x, a.l, 32);
+            std::memcpy(y, b.l, 32);
+            f.mul(x, f.r2, ar);
+            f.mul(ar, y, out);
+            Fr r;
+            std::memcpy(r.l, out, 32);
+            return r;
+        }
+    }
+
     // Host-side scalar arithmetic for the O(#columns) glue of a caller (same limb code as the
     // kernels, run on the CPU): op 0 add, 1 sub, 2 mul, 3 inverse of a (b ignored).
     int gzk_fr_op(int op, const uint8_t a[32], const uint8_t b[32], uint8_t out[32])
@@ -626,7 +752,7 @@ extern "C"
         {
         case 0: r = add(x, y); break;
         case 1: r = sub(x, y); break;
-        case 2: r = from_mont(mul(to_mont(x), to_mont(y))); break;
+        case 2: r = host_mul_canonical(x, y); break;
         case 3:
             if (x.is_zero()) return GZK_E_DOMAIN;  // FieldElement::inv throws on zero
             r = from_mont(inv(to_mont(x)));

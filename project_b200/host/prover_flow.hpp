@@ -244,37 +244,43 @@ namespace gatzk_flow
     class Transcript
     {
     public:
-        explicit Transcript(std::string label) : state_(std::move(label)) {}
+        explicit Transcript(const std::string& label) { append(label); }
         void absorb_scalar(const std::string& label, const Fe& value)
         {
-            state_.append("|");
-            state_.append(label);
-            state_.append("=");
-            state_.append(fe_to_decimal(value));
+            append("|");
+            append(label);
+            append("=");
+            append(fe_to_decimal(value));
         }
         void absorb_commitment(const std::string& label, const G1& point)
         {
-            state_.append("|");
-            state_.append(label);
-            state_.append("=");
+            append("|");
+            append(label);
+            append("=");
             static const char kHex[] = "0123456789abcdef";
+            char hex[2 * sizeof(G1)];
+            std::size_t n = 0;
             for (const auto byte : point_bytes(point))
             {
-                state_.push_back(kHex[(byte >> 4U) & 0x0FU]);
-                state_.push_back(kHex[byte & 0x0FU]);
+                hex[n++] = kHex[(byte >> 4U) & 0x0FU];
+                hex[n++] = kHex[byte & 0x0FU];
             }
+            append(std::string(hex, n));
         }
+        // FNV-1a of everything absorbed so far followed by "|label|count".  The hash is a byte-serial
+        // recurrence, so the digest of the absorbed text is carried along instead of the text: a
+        // challenge costs its own few bytes, not a pass over the whole history.
         Fe challenge(const std::string& label)
         {
-            const auto hash = fnv1a(state_ + "|" + label + "|" + std::to_string(issued_));
+            const auto hash = fnv1a("|" + label + "|" + std::to_string(issued_), digest_);
             ++issued_;
             const Fe value = fe_u64(hash);
             absorb_scalar(label, value);
             return value;
         }
-        static std::uint64_t fnv1a(const std::string& data)
+        static constexpr std::uint64_t kFnvOffset = 1469598103934665603ULL;
+        static std::uint64_t fnv1a(const std::string& data, std::uint64_t hash = kFnvOffset)
         {
-            std::uint64_t hash = 1469598103934665603ULL;
             for (const unsigned char ch : data)
             {
                 hash ^= ch;
@@ -284,7 +290,8 @@ namespace gatzk_flow
         }
 
     private:
-        std::string state_;
+        void append(const std::string& text) { digest_ = fnv1a(text, digest_); }
+        std::uint64_t digest_ = kFnvOffset;
         std::size_t issued_ = 0;
     };
 
@@ -735,7 +742,7 @@ namespace gatzk_flow
         be_.g1_fixed_base(in_.generator, scalar, 1, point);
         be_.download(point, 0, 1, c.point.data());
         static_commitments_[label] = c;
-        static_columns_[label] = ColumnEntry{col, domain, length};
+        static_columns_[label] = ColumnEntry{col, domain, length, false, Fe{}, {}};
         return c;
     }
 

@@ -73,6 +73,35 @@ def test_msm_window_choice_is_host_arithmetic():
     assert lib.gzk_msm_table_points(ctypes.c_size_t(1), ctypes.c_uint(20)) == 13
 
 
+def test_host_scalar_arithmetic_matches_integers():
+    """gzk_fr_op (the 64-bit-limb host product, sum, difference, inverse) against Python integers."""
+    import random
+
+    from project_b200 import load_library
+
+    lib = load_library()
+    r = 0x73EDA753299D7D483339D80809A1D80553BDA402FFFE5BFEFFFFFFFF00000001
+    word = ctypes.c_uint8 * 32
+
+    def op(code, a, b=0):
+        out = word()
+        rc = lib.gzk_fr_op(code, word.from_buffer_copy(a.to_bytes(32, "little")), word.from_buffer_copy(b.to_bytes(32, "little")), out)
+        return rc, int.from_bytes(bytes(out), "little")
+
+    rng = random.Random(7)
+    edge = [0, 1, 2, r - 1, r - 2, (1 << 64) - 1, 1 << 64, (1 << 128) - 1, (1 << 192) + 1, (1 << 255) % r, r >> 1]
+    cases = [(a, b) for a in edge for b in edge] + [(rng.randrange(r), rng.randrange(r)) for _ in range(3000)]
+    for a, b in cases:
+        assert op(0, a, b) == (0, (a + b) % r)
+        assert op(1, a, b) == (0, (a - b) % r)
+        assert op(2, a, b) == (0, a * b % r)
+    for a, _ in cases[-200:] + [(1, 0), (r - 1, 0)]:
+        rc, inv = op(3, a)
+        assert rc == 0 and inv * a % r == 1
+    assert op(3, 0)[0] != 0          # FieldElement::inv throws on zero
+    assert op(2, r, 1)[0] != 0       # not canonical
+
+
 def test_header_is_plain_c(tmp_path):
     """The boundary is a C ABI: the header must compile as C99 (and as C++) with nothing but its own declarations."""
     import os
