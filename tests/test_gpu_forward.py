@@ -98,6 +98,9 @@ def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, 
     (300, 50, 8, 2000, True, False, True),
     (300, 64, 7, 1500, False, True, False),
     (2000, 33, 64, 15000, True, True, True),
+    # width a multiple of 64 and inner a multiple of 8: the 128 x 64 projection tiles (ragged last row tile; one slice; many)
+    (333, 8, 64, 2500, True, True, True),
+    (1100, 72, 128, 9000, True, True, True),
 ])
 def test_head_forward_matches_oracle(be, nodes, inner, width, edges, self_loops, bias, activation):
     run_case(be, np.random.default_rng(nodes * 7 + width), nodes, inner, width, edges, self_loops, bias, activation)
