@@ -38,6 +38,9 @@ namespace gzk
             Fr x2, x4;  // x^2, x^4 (whole-domain kernels)
             Fr root4;   // I = omega^(n/4)
             uint64_t keep;  // whole-domain kernels: weights with index >= keep are not needed (except the last one, which a rotated evaluation reads for row 0)
+            // fused whole-domain kernel: CTA b works on chunk b of the quartets while b < kept_blocks and on chunk
+            // last_chunk otherwise (a short prefix is kept: only its chunks and the one holding the last weight run)
+            uint32_t kept_blocks, last_chunk;
         };
 
         __device__ __forceinline__ Fr shfl_fr(const Fr& v, int src_lane)
@@ -354,7 +357,8 @@ namespace gzk
             Fr* warp_pre = sh.warp_pre;
             Fr* warp_suf = sh.warp_suf;
             Fr& cta_inverse = sh.cta_inverse;
-            const uint64_t base = static_cast<uint64_t>(blockIdx.x) * (kThreads * ELEMS);
+            const uint32_t chunk = blockIdx.x < a.kept_blocks ? blockIdx.x : a.last_chunk;
+            const uint64_t base = static_cast<uint64_t>(chunk) * (kThreads * ELEMS);
             const int lane = threadIdx.x & 31;
             const int warp = threadIdx.x >> 5;
 
@@ -489,6 +493,8 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     args.first = first;
     args.mask = n - 1;
     args.keep = keep;
+    args.kept_blocks = ~0u;
+    args.last_chunk = 0;
     args.x = to_mont(x_plain);
     Fr xn = args.x;
     for (unsigned s = 0; s < log2n; ++s) xn = sqr(xn);
@@ -515,12 +521,28 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     if ((rc = begin_call(ctx)) != GZK_OK) return rc;
     if (quartets)
     {
+        // Quartet e yields the weights e, e + n/4, e + n/2 and e + 3n/4.  When only a prefix shorter than n/4 is kept,
+        // the quartets below `keep` and the last one (weight n - 1) are all that is needed: the work shrinks with
+        // the prefix instead of staying that of the whole domain.
+        args.kept_blocks = blocks;
+        args.last_chunk = blocks - 1;
+        uint32_t launch_blocks = blocks;
+        if (keep < args.n)
+        {
+            const uint64_t per_block = short_chain ? kThreads : kChunk;
+            const uint64_t kept = (keep + per_block - 1) / per_block;
+            if (kept + 1 < blocks)
+            {
+                args.kept_blocks = static_cast<uint32_t>(kept);
+                launch_blocks = static_cast<uint32_t>(kept) + 1;
+            }
+        }
         {
             LaunchScope scope(ctx, "bary_fused");
             if (short_chain)
-                bary4_fused_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
+                bary4_fused_kernel<1><<<launch_blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
             else
-                bary4_fused_kernel<kElems><<<blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
+                bary4_fused_kernel<kElems><<<launch_blocks, kThreads, 0, ctx->stream>>>(args, static_cast<Fr*>(out->dptr), ctx->d_status);
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         rc = finish_call(ctx, "bary_weights: invalid input");
@@ -580,6 +602,8 @@ extern "C" int gzk_bary_weights_multi(gzk_ctx* ctx, unsigned log2n, const uint8_
         a.first = 0;
         a.mask = n - 1;
         a.keep = ~0ULL;
+        a.kept_blocks = ~0u;  // every CTA works on its own chunk
+        a.last_chunk = 0;
         a.x = to_mont(x_plain);
         Fr xn = a.x;
         for (unsigned s = 0; s < log2n; ++s) xn = sqr(xn);

@@ -215,6 +215,20 @@ class Backend:
         self._check(self.lib.gzk_bary_weights(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), out.handle))
         return out
 
+    def bary_weights_prefix(self, log2n, x, keep, out=None):
+        """Whole-domain weights of which only the first `keep` and the last one are written."""
+        out = out or self.alloc(KIND_FR_MONT, 1 << log2n)
+        self._check(self.lib.gzk_bary_weights_prefix(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), ctypes.c_uint64(keep), out.handle))
+        return out
+
+    def bary_weights_multi(self, log2n, xs, outs=None):
+        """Weights of one domain at several points (one launch for up to four points of a small domain)."""
+        outs = outs or [self.alloc(KIND_FR_MONT, 1 << log2n) for _ in xs]
+        points = np.ascontiguousarray(np.stack([_fr(x) for x in xs]))
+        handles = (ctypes.c_void_p * len(outs))(*[o.handle for o in outs])
+        self._check(self.lib.gzk_bary_weights_multi(self.ctx, ctypes.c_uint(log2n), _ptr(points), _sz(len(outs)), handles))
+        return outs
+
     def logup_accumulator(self, table, query, mult, q_table, q_query, n, beta, active_count, out=None):
         out = out or self.alloc(KIND_FR_MONT, n)
         self._check(self.lib.gzk_logup_accumulator(self.ctx, table.handle, query.handle, mult.handle, q_table.handle, q_query.handle,

@@ -63,6 +63,36 @@ def test_bary_weights(be, log2n):
     w.free()
 
 
+@pytest.mark.parametrize("log2n,keeps", [(12, (0, 1, 255, 256, 257, 1023, 1024, 3000, 4096)),
+                                         (20, (0, 1, 1000, 1024, 1025, 70000, (1 << 18) - 1024, (1 << 18) - 1, 1 << 18, 600000, 1 << 20))])
+def test_bary_weights_prefix(be, log2n, keeps):
+    """Only the quartets below the kept prefix and the one holding the last weight run: the first `keep` weights and
+    the last one are the whole vector's; nothing else of the output is relied on."""
+    from project_b200 import KIND_FR, KIND_FR_MONT
+
+    rng = random.Random(300 + log2n)
+    x = fr_array([rng.randrange(1 << 64)])
+    n = 1 << log2n
+    want = ora.bary_weights(x, n)
+    for keep in keeps:
+        out = be.upload(np.full((n, 32), 0x11, dtype=np.uint8), KIND_FR)
+        out.retag(KIND_FR_MONT)
+        got = be.bary_weights_prefix(log2n, x, keep, out).download()
+        assert np.array_equal(got[:keep], want[:keep]), keep
+        assert np.array_equal(got[n - 1], want[n - 1]), keep
+        out.free()
+
+
+def test_bary_weights_multi(be):
+    rng = random.Random(77)
+    for log2n, count in ((10, 3), (15, 4), (18, 2), (12, 6), (19, 2)):
+        xs = [fr_array([rng.randrange(1 << 64)]) for _ in range(count)]
+        outs = be.bary_weights_multi(log2n, xs)
+        for x, w in zip(xs, outs):
+            assert np.array_equal(w.download(), ora.bary_weights(x, 1 << log2n)), (log2n, count)
+            w.free()
+
+
 def test_bary_weights_point_on_domain(be):
     from project_b200 import GzkError
 
