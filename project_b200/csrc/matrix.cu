@@ -146,41 +146,67 @@ namespace gzk
         // FR and FR_MONT share the field-element code
         constexpr int entry_kind(int kind) { return kind == GZK_KIND_U32 || kind == GZK_KIND_I64 ? kind : GZK_KIND_FR; }
 
+        // A table of field elements in shared memory as two arrays of 16-byte halves: lanes that read consecutive
+        // elements then touch consecutive 16-byte words (no bank conflict), and a whole warp reading one element
+        // is a broadcast.
+        __device__ __forceinline__ void store_fr_split(uint4* lo, uint4* hi, uint32_t i, const Fr& v)
+        {
+            lo[i] = make_uint4(v.l[0], v.l[1], v.l[2], v.l[3]);
+            hi[i] = make_uint4(v.l[4], v.l[5], v.l[6], v.l[7]);
+        }
+        __device__ __forceinline__ Fr load_fr_split(const uint4* lo, const uint4* hi, uint32_t i)
+        {
+            const uint4 a = lo[i], b = hi[i];
+            Fr o;
+            o.l[0] = a.x; o.l[1] = a.y; o.l[2] = a.z; o.l[3] = a.w;
+            o.l[4] = b.x; o.l[5] = b.y; o.l[6] = b.z; o.l[7] = b.w;
+            return o;
+        }
+
         // Small-integer coefficients: Horner costs a full field multiplication per coefficient although the
-        // coefficient itself is one or two limbs.  Cut the polynomial into blocks of 256 coefficients,
-        // r_b = sum_j c[256 b + j] x^j as an exact 8 x 2 limb inner product against the 256 powers of x
-        // (one warp per block, each lane keeps its eight powers in registers), and leave Horner to the
-        // 256 times shorter polynomial sum_b r_b (x^256)^b.  out[b] is the Montgomery form of r_b.
-        constexpr int kDotBlock = 256;
-        // `bias` (I64 only): 2^31 * (sum of the 256 powers), Montgomery form; the entries then enter biased.
+        // coefficient itself is one or two limbs.  Cut the polynomial into blocks of 1024 coefficients,
+        // r_b = sum_j c[1024 b + j] x^j as an exact 8 x 2 limb inner product against the 1024 powers of x
+        // (one warp per block, 32 coefficients per lane, the powers in shared memory), and leave Horner to the
+        // 1024 times shorter polynomial sum_b r_b (x^1024)^b.  out[b] is the Montgomery form of r_b.
+        // The block is long because every block ends in a warp-wide exact sum, one reduction and one field
+        // multiplication (some 500 instructions per lane): with 256-coefficient blocks that tail was twice the
+        // cost of the products themselves.
+        constexpr int kDotBlock = 1024;
+        // `bias` (I64 only): 2^31 * (sum of the powers), Montgomery form; the entries then enter biased.
         template <int KIND>
         __global__ void __launch_bounds__(kThreads) block_dot_kernel(const void* coeffs, uint64_t total, const Fr* powers, uint64_t blocks, Fr* out,
                                                                      const Fr* bias)
         {
+            __shared__ uint4 pw_lo[kDotBlock], pw_hi[kDotBlock];
+            for (uint32_t i = threadIdx.x; i < kDotBlock; i += kThreads) store_fr_split(pw_lo, pw_hi, i, load_fr(powers + i));
+            __syncthreads();
             const uint32_t lane = threadIdx.x & 31;
             const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
             const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
-            Fr p[kDotBlock / 32];
-#pragma unroll
-            for (int k = 0; k < kDotBlock / 32; ++k) p[k] = load_fr(powers + lane + 32 * k);
             for (uint64_t b = warp; b < blocks; b += warps)
             {
                 WideAcc acc;
                 acc.clear();
-                typename Entry<KIND>::Raw raw[kDotBlock / 32];
-#pragma unroll
-                for (int k = 0; k < kDotBlock / 32; ++k)
+                const uint64_t base = b * kDotBlock + lane;
+#pragma unroll 1
+                for (int k = 0; k < kDotBlock / 32; k += 4)
                 {
-                    const uint64_t i = b * kDotBlock + lane + 32 * k;
-                    raw[k] = i < total ? Entry<KIND>::load(coeffs, i) : Entry<KIND>::zero();
-                }
+                    typename Entry<KIND>::Raw raw[4];
 #pragma unroll
-                for (int k = 0; k < kDotBlock / 32; ++k)
-                {
-                    if constexpr (KIND == GZK_KIND_I64)
-                        mac_biased_i64(acc, p[k], raw[k]);
-                    else
-                        Entry<KIND>::mac(acc, p[k], raw[k]);
+                    for (int u = 0; u < 4; ++u)
+                    {
+                        const uint64_t i = base + 32ull * (k + u);
+                        raw[u] = i < total ? Entry<KIND>::load(coeffs, i) : Entry<KIND>::zero();
+                    }
+#pragma unroll
+                    for (int u = 0; u < 4; ++u)
+                    {
+                        const Fr w = load_fr_split(pw_lo, pw_hi, lane + 32u * (k + u));
+                        if constexpr (KIND == GZK_KIND_I64)
+                            mac_biased_i64(acc, w, raw[u]);
+                        else
+                            Entry<KIND>::mac(acc, w, raw[u]);
+                    }
                 }
                 uint32_t sum[kAccLimbs];
                 acc.fold(sum);
@@ -329,6 +355,56 @@ namespace gzk
             }
         }
 
+        // Small-integer matrices with many rows: one THREAD per row.  A CTA stages 128 rows x 32 columns at a time in
+        // shared memory (read row-wise by the warps, so the global loads stay contiguous; rows padded by one entry
+        // so that the threads' walks along their rows fall on different banks) together with the 32 powers, which
+        // every thread then reads as a broadcast.  No sum crosses lanes: each thread folds and reduces its own row
+        // once, which costs a few instructions per entry instead of the warp-wide exact sum per 256-entry row of
+        // the warp-per-row kernel (two thirds of that kernel's instructions).
+        constexpr int kRowThreads = 128, kRowChunk = 32;
+        template <int KIND>
+        __global__ void __launch_bounds__(kRowThreads) linear_form_by_thread_kernel(const void* matrix, const Fr* powers, uint64_t rows, uint32_t cols,
+                                                                                    Fr* out, const Fr* bias)
+        {
+            using Raw = typename Entry<KIND>::Raw;
+            __shared__ Raw tile[kRowThreads][kRowChunk + 1];
+            __shared__ uint4 pw_lo[kRowChunk], pw_hi[kRowChunk];
+            const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+            const uint64_t row0 = static_cast<uint64_t>(blockIdx.x) * kRowThreads;
+            WideAcc acc;
+            acc.clear();
+            for (uint32_t c0 = 0; c0 < cols; c0 += kRowChunk)
+            {
+                const uint32_t col = c0 + lane;
+#pragma unroll 8
+                for (uint32_t r = warp; r < kRowThreads; r += kRowThreads / 32)
+                {
+                    const uint64_t row = row0 + r;
+                    tile[r][lane] = (row < rows && col < cols) ? Entry<KIND>::load(matrix, row * cols + col) : Entry<KIND>::zero();
+                }
+                if (threadIdx.x < kRowChunk) store_fr_split(pw_lo, pw_hi, threadIdx.x, c0 + threadIdx.x < cols ? load_fr(powers + c0 + threadIdx.x) : Fr::zero());
+                __syncthreads();
+                const uint32_t n = cols - c0 < kRowChunk ? cols - c0 : kRowChunk;
+#pragma unroll 4
+                for (uint32_t j = 0; j < n; ++j)
+                {
+                    const Fr w = load_fr_split(pw_lo, pw_hi, j);
+                    if constexpr (KIND == GZK_KIND_I64)
+                        mac_biased_i64(acc, w, tile[threadIdx.x][j]);
+                    else
+                        Entry<KIND>::mac(acc, w, tile[threadIdx.x][j]);
+                }
+                __syncthreads();
+            }
+            const uint64_t row = row0 + threadIdx.x;
+            if (row >= rows) return;
+            uint32_t sum[kAccLimbs];
+            acc.fold(sum);
+            Fr value = mul(redc_wide<FrCfg, 9>(sum), fr_const_2_544());  // small-integer entries: one factor of R less in the sum
+            if constexpr (KIND == GZK_KIND_I64) value = sub(value, load_fr(bias));  // every entry entered as v + 2^31
+            store_fr(out + row, value);
+        }
+
         __global__ void powers_kernel(Fr c, uint64_t count, Fr* out)
         {
             const uint64_t i = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -387,7 +463,7 @@ extern "C"
             Fr* block_values = bias + 1;
             {
                 LaunchScope scope(ctx, "powers");
-                powers_kernel<<<1, kDotBlock, 0, ctx->stream>>>(x, kDotBlock, powers);
+                powers_kernel<<<kDotBlock / kThreads, kThreads, 0, ctx->stream>>>(x, kDotBlock, powers);
                 if (matrix->kind == GZK_KIND_I64) scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, kDotBlock, mont_two_31(), bias);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
@@ -553,15 +629,24 @@ extern "C"
             const Fr* powers = static_cast<const Fr*>(column_powers->dptr);
             const int mont = matrix->kind == GZK_KIND_FR_MONT ? 1 : 0;
             Fr* dst = static_cast<Fr*>(out->dptr);
+            // a thread per row once the rows fill the machine that way (a warp per row below that)
+            const bool by_thread = rows >= static_cast<uint64_t>(ctx->sm_count) * kRowThreads * 2;
+            const unsigned row_ctas = static_cast<unsigned>((rows + kRowThreads - 1) / kRowThreads);
             switch (entry_kind(matrix->kind))
             {
             case GZK_KIND_I64:
                 // entries enter as v + 2^31: 2^31 * (sum of the powers) is taken off every row
                 scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, static_cast<uint32_t>(cols), mont_two_31(), bias);
-                linear_form_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, bias);
+                if (by_thread)
+                    linear_form_by_thread_kernel<GZK_KIND_I64><<<row_ctas, kRowThreads, 0, ctx->stream>>>(m.ptr, powers, rows, static_cast<uint32_t>(cols), dst, bias);
+                else
+                    linear_form_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, bias);
                 break;
             case GZK_KIND_U32:
-                linear_form_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, nullptr);
+                if (by_thread)
+                    linear_form_by_thread_kernel<GZK_KIND_U32><<<row_ctas, kRowThreads, 0, ctx->stream>>>(m.ptr, powers, rows, static_cast<uint32_t>(cols), dst, nullptr);
+                else
+                    linear_form_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, nullptr);
                 break;
             default:
                 linear_form_kernel<GZK_KIND_FR><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, mont, powers, rows, static_cast<uint32_t>(cols), dst, nullptr);

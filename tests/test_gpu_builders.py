@@ -463,16 +463,40 @@ def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y):
     assert e.value.code == 1
 
 
+@pytest.mark.parametrize("kind_name,rows,cols", [("i64", 40000, 40), ("i64", 38000, 7), ("u32", 39000, 33), ("i64", 37999, 64)])
+def test_linear_form_of_a_tall_small_integer_matrix(be, kind_name, rows, cols):
+    """Tall matrices take the thread-per-row kernel (shared-memory tiles of 128 rows x 32 columns): ragged last
+    column chunk, ragged last row tile, values of every width."""
+    from project_b200 import KIND_I64, KIND_U32
+
+    rng = np.random.default_rng(rows + cols)
+    if kind_name == "i64":
+        vals = rng.integers(-5000, 5000, size=rows * cols, dtype=np.int64)
+        wide = rng.integers(0, rows * cols, size=3000)
+        vals[wide[:1500]] = rng.integers(-(1 << 62), 1 << 62, size=1500, dtype=np.int64)
+        vals[wide[1500:1508]] = np.array([np.iinfo(np.int64).max, np.iinfo(np.int64).min, -(1 << 31), (1 << 31) - 1, 1 << 31, -(1 << 31) - 1,
+                                          (1 << 32) - 1, -(1 << 32)], dtype=np.int64)
+        buf = be.upload(vals, KIND_I64)
+        as_field = ora.fr_from_i64(vals)
+    else:
+        vals = rng.integers(0, 1 << 32, size=rows * cols, dtype=np.uint32)
+        buf = be.upload(vals, KIND_U32)
+        as_field = ora.fr_from_i64(vals.astype(np.int64))
+    c = fr_array([int(rng.integers(2, 1 << 62))])
+    got = be.linear_form_rows(buf, rows, cols, be.powers(c, cols)).download()
+    assert np.array_equal(got, ora.linear_form_by_powers(as_field.reshape(rows, cols, 32), ora.powers(c, cols)))
+
+
 @pytest.mark.parametrize("kind_name", ["i64", "u32"])
 def test_small_integer_matrix_kernels_with_values_of_every_width(be, kind_name):
-    """fold_rows, linear_form_rows, matrix_horner (blocked path: 300 x 256 = 76 800 entries), packed evaluation and
+    """fold_rows, linear_form_rows, matrix_horner (blocked path: 301 x 256 entries, a ragged last block), packed evaluation and
     linear_combination on small-integer buffers whose values range from a few bits to the whole 64-bit range: the
     one-limb fast paths, the biased entries (v + 2^31 spilling into further limbs) and the two-limb paths must all agree
     with the field arithmetic of the oracle."""
     from project_b200 import KIND_FR_MONT, KIND_I64, KIND_U32
 
     rng = np.random.default_rng(909)
-    rows, cols = 300, 256
+    rows, cols = 301, 256
     if kind_name == "i64":
         vals = rng.integers(-1000, 1000, size=rows * cols, dtype=np.int64)
         wide = rng.integers(0, rows * cols, size=6000)
