@@ -242,11 +242,16 @@ namespace gzk
         // CTA (tile, column chunk): threads are laid out as (row lane, column); each
         // thread accumulates w[row] * M[row][c] unreduced over the rows of the tile that
         // fall on its row lane; row lanes are then summed through shared memory.
+        // Signed 64-bit entries enter biased, as v + 2^31 >= 0 (no negated weight per negative entry); the surplus
+        // 2^31 * (sum of the tile's weights) is the same for every column of the tile, so the CTA adds up its
+        // weights once and every column's partial sum receives 2^31 * (r - that sum), which cancels it modulo r.
         template <int KIND>
         __global__ void __launch_bounds__(kThreads) fold_rows_kernel(const void* matrix, const Fr* weights, uint64_t row_count, uint32_t cols,
                                                                      uint64_t tile_rows, uint32_t col_chunks, uint32_t* partial)
         {
             extern __shared__ uint32_t lanes_sum[];  // [kThreads][17]
+            __shared__ Fr warp_weights[kThreads / 32];
+            __shared__ uint32_t correction[9];
             const uint32_t tile = blockIdx.x / col_chunks;
             const uint32_t chunk = blockIdx.x - tile * col_chunks;
             const uint32_t width = cols < kThreads ? cols : kThreads;   // columns handled by this CTA
@@ -256,20 +261,49 @@ namespace gzk
             const uint32_t c = chunk * kThreads + c_local;
             const uint64_t r_begin = static_cast<uint64_t>(tile) * tile_rows;
             const uint64_t r_end = r_begin + tile_rows < row_count ? r_begin + tile_rows : row_count;
+            if constexpr (KIND == GZK_KIND_I64)
+            {
+                Fr mine = Fr::zero();
+                for (uint64_t row = r_begin + threadIdx.x; row < r_end; row += kThreads) mine = add(mine, load_fr(weights + row));
+                const int lane = threadIdx.x & 31;
+#pragma unroll
+                for (int offset = 16; offset > 0; offset >>= 1) mine = add(mine, shfl_fr_idx(mine, (lane + offset) & 31));  // lane 0 ends with the warp's sum
+                if (lane == 0) warp_weights[threadIdx.x >> 5] = mine;
+                __syncthreads();
+                if (threadIdx.x == 0)
+                {
+                    Fr total = warp_weights[0];
+#pragma unroll
+                    for (int w = 1; w < kThreads / 32; ++w) total = add(total, warp_weights[w]);
+                    const Fr rest = sub(Fr::zero(), total);  // r - total (0 when total is 0)
+                    correction[0] = rest.l[0] << 31;
+#pragma unroll
+                    for (int i = 1; i < 8; ++i) correction[i] = (rest.l[i] << 31) | (rest.l[i - 1] >> 1);
+                    correction[8] = rest.l[7] >> 1;
+                }
+                __syncthreads();
+            }
             WideAcc acc;
             acc.clear();
             if (row_lane < row_lanes && c < cols)
             {
+                auto mac = [&](const Fr& w, const typename Entry<KIND>::Raw& v) {
+                    if constexpr (KIND == GZK_KIND_I64)
+                        mac_biased_i64(acc, w, v);
+                    else
+                        Entry<KIND>::mac(acc, w, v);
+                };
+                constexpr int kAhead = KIND == GZK_KIND_FR ? 4 : 8;  // entries requested before the first product
                 uint64_t row = r_begin + row_lane;
-                for (; row + 3ull * row_lanes < r_end; row += 4ull * row_lanes)
+                for (; row + static_cast<uint64_t>(kAhead - 1) * row_lanes < r_end; row += static_cast<uint64_t>(kAhead) * row_lanes)
                 {
-                    typename Entry<KIND>::Raw raw[4];
+                    typename Entry<KIND>::Raw raw[kAhead];
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) raw[u] = Entry<KIND>::load(matrix, (row + static_cast<uint64_t>(u) * row_lanes) * cols + c);
+                    for (int u = 0; u < kAhead; ++u) raw[u] = Entry<KIND>::load(matrix, (row + static_cast<uint64_t>(u) * row_lanes) * cols + c);
 #pragma unroll
-                    for (int u = 0; u < 4; ++u) Entry<KIND>::mac(acc, load_fr(weights + row + static_cast<uint64_t>(u) * row_lanes), raw[u]);
+                    for (int u = 0; u < kAhead; ++u) mac(load_fr(weights + row + static_cast<uint64_t>(u) * row_lanes), raw[u]);
                 }
-                for (; row < r_end; row += row_lanes) Entry<KIND>::mac(acc, load_fr(weights + row), Entry<KIND>::load(matrix, row * cols + c));
+                for (; row < r_end; row += row_lanes) mac(load_fr(weights + row), Entry<KIND>::load(matrix, row * cols + c));
             }
             uint32_t sum[kAccLimbs];
             acc.fold(sum);
@@ -284,6 +318,13 @@ namespace gzk
 #pragma unroll
                     for (int i = 0; i < kAccLimbs; ++i) other[i] = lanes_sum[(rl * width + c_local) * kAccLimbs + i];
                     acc_add<kAccLimbs, kAccLimbs>(sum, other);
+                }
+                if constexpr (KIND == GZK_KIND_I64)
+                {
+                    uint32_t fix[9];
+#pragma unroll
+                    for (int i = 0; i < 9; ++i) fix[i] = correction[i];
+                    acc_add<kAccLimbs, 9>(sum, fix);
                 }
                 uint32_t* dst = partial + (static_cast<uint64_t>(tile) * cols + c) * kAccLimbs;
 #pragma unroll
