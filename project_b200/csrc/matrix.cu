@@ -72,6 +72,7 @@ namespace gzk
             using Raw = Fr;
             static __device__ __forceinline__ Raw zero() { return Fr::zero(); }
             static __device__ __forceinline__ Raw load(const void* ptr, uint64_t i) { return load_fr(static_cast<const Fr*>(ptr) + i); }
+            static __device__ __forceinline__ Raw at(const Raw* p) { return load_fr(p); }
             static __device__ __forceinline__ void mac(WideAcc& acc, const Fr& w, const Raw& v) { acc.mac<8>(w.l, v.l); }
         };
         template <>
@@ -80,6 +81,7 @@ namespace gzk
             using Raw = uint32_t;
             static __device__ __forceinline__ Raw zero() { return 0u; }
             static __device__ __forceinline__ Raw load(const void* ptr, uint64_t i) { return __ldg(static_cast<const uint32_t*>(ptr) + i); }
+            static __device__ __forceinline__ Raw at(const Raw* p) { return __ldg(p); }
             static __device__ __forceinline__ void mac(WideAcc& acc, const Fr& w, const Raw& v) { acc.mac<1>(w.l, &v); }
         };
         template <>
@@ -88,6 +90,7 @@ namespace gzk
             using Raw = long long;
             static __device__ __forceinline__ Raw zero() { return 0; }
             static __device__ __forceinline__ Raw load(const void* ptr, uint64_t i) { return __ldg(static_cast<const long long*>(ptr) + i); }
+            static __device__ __forceinline__ Raw at(const Raw* p) { return __ldg(p); }
             static __device__ __forceinline__ void mac(WideAcc& acc, const Fr& w, const Raw& v)
             {
                 const unsigned long long mag = v < 0 ? 0ULL - static_cast<unsigned long long>(v) : static_cast<unsigned long long>(v);
@@ -245,6 +248,7 @@ namespace gzk
         // Signed 64-bit entries enter biased, as v + 2^31 >= 0 (no negated weight per negative entry); the surplus
         // 2^31 * (sum of the tile's weights) is the same for every column of the tile, so the CTA adds up its
         // weights once and every column's partial sum receives 2^31 * (r - that sum), which cancels it modulo r.
+        constexpr uint32_t kFoldStage = 512;
         template <int KIND>
         __global__ void __launch_bounds__(kThreads) fold_rows_kernel(const void* matrix, const Fr* weights, uint64_t row_count, uint32_t cols,
                                                                      uint64_t tile_rows, uint32_t col_chunks, uint32_t* partial)
@@ -252,6 +256,7 @@ namespace gzk
             extern __shared__ uint32_t lanes_sum[];  // [kThreads][17]
             __shared__ Fr warp_weights[kThreads / 32];
             __shared__ uint32_t correction[9];
+            __shared__ uint4 stage_lo[kFoldStage], stage_hi[kFoldStage];
             const uint32_t tile = blockIdx.x / col_chunks;
             const uint32_t chunk = blockIdx.x - tile * col_chunks;
             const uint32_t width = cols < kThreads ? cols : kThreads;   // columns handled by this CTA
@@ -285,25 +290,43 @@ namespace gzk
             }
             WideAcc acc;
             acc.clear();
-            if (row_lane < row_lanes && c < cols)
+            auto mac = [&](const Fr& w, const typename Entry<KIND>::Raw& v) {
+                if constexpr (KIND == GZK_KIND_I64)
+                    mac_biased_i64(acc, w, v);
+                else
+                    Entry<KIND>::mac(acc, w, v);
+            };
+            // The weights of kFoldStage rows at a time pass through shared memory (every thread of the CTA needs the
+            // same ones: a broadcast read each), and the entries are walked with a running pointer.
+            using Raw = typename Entry<KIND>::Raw;
+            constexpr int kAhead = KIND == GZK_KIND_FR ? 4 : 8;  // entries requested before the first product
+            const bool active = row_lane < row_lanes && c < cols;
+            const uint64_t stride = static_cast<uint64_t>(row_lanes) * cols;
+            for (uint64_t s0 = r_begin; s0 < r_end; s0 += kFoldStage)
             {
-                auto mac = [&](const Fr& w, const typename Entry<KIND>::Raw& v) {
-                    if constexpr (KIND == GZK_KIND_I64)
-                        mac_biased_i64(acc, w, v);
-                    else
-                        Entry<KIND>::mac(acc, w, v);
-                };
-                constexpr int kAhead = KIND == GZK_KIND_FR ? 4 : 8;  // entries requested before the first product
-                uint64_t row = r_begin + row_lane;
-                for (; row + static_cast<uint64_t>(kAhead - 1) * row_lanes < r_end; row += static_cast<uint64_t>(kAhead) * row_lanes)
+                const uint32_t n = static_cast<uint32_t>(r_end - s0 < kFoldStage ? r_end - s0 : kFoldStage);
+                for (uint32_t i = threadIdx.x; i < n; i += kThreads) store_fr_split(stage_lo, stage_hi, i, load_fr(weights + s0 + i));
+                __syncthreads();
+                if (active)
                 {
-                    typename Entry<KIND>::Raw raw[kAhead];
+                    const Raw* p = static_cast<const Raw*>(matrix) + (s0 + row_lane) * cols + c;
+                    uint32_t j = row_lane;
+                    for (; j + (kAhead - 1) * row_lanes < n; j += kAhead * row_lanes)
+                    {
+                        Raw raw[kAhead];
 #pragma unroll
-                    for (int u = 0; u < kAhead; ++u) raw[u] = Entry<KIND>::load(matrix, (row + static_cast<uint64_t>(u) * row_lanes) * cols + c);
+                        for (int u = 0; u < kAhead; ++u) raw[u] = Entry<KIND>::at(p + u * stride);
 #pragma unroll
-                    for (int u = 0; u < kAhead; ++u) mac(load_fr(weights + row + static_cast<uint64_t>(u) * row_lanes), raw[u]);
+                        for (int u = 0; u < kAhead; ++u) mac(load_fr_split(stage_lo, stage_hi, j + u * row_lanes), raw[u]);
+                        p += kAhead * stride;
+                    }
+                    for (; j < n; j += row_lanes)
+                    {
+                        mac(load_fr_split(stage_lo, stage_hi, j), Entry<KIND>::at(p));
+                        p += stride;
+                    }
                 }
-                for (; row < r_end; row += row_lanes) mac(load_fr(weights + row), Entry<KIND>::load(matrix, row * cols + c));
+                __syncthreads();
             }
             uint32_t sum[kAccLimbs];
             acc.fold(sum);
