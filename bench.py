@@ -330,15 +330,22 @@ def main():
             ms = float(t.item())
         return ms, clocks.summary()
 
+    def contexts():
+        return [ctx] + flow.side_contexts()  # the side contexts (streams) appear with the first proof
+
     def timing_report():
         out = {}
-        for i in range(lib.gzk_timing_family_count(ctx)):
-            name, launches, ms = ctypes.c_char_p(), ctypes.c_uint64(), ctypes.c_double()
-            lib.gzk_timing_get(ctx, i, ctypes.byref(name), ctypes.byref(launches), ctypes.byref(ms))
-            out[name.value.decode()] = (int(launches.value), float(ms.value))
+        for c in contexts():
+            for i in range(lib.gzk_timing_family_count(c)):
+                name, launches, ms = ctypes.c_char_p(), ctypes.c_uint64(), ctypes.c_double()
+                lib.gzk_timing_get(c, i, ctypes.byref(name), ctypes.byref(launches), ctypes.byref(ms))
+                seen = out.get(name.value.decode(), (0, 0.0))
+                out[name.value.decode()] = (seen[0] + int(launches.value), seen[1] + float(ms.value))
         return out
 
-    lib.gzk_timing_reset(ctx)
+    flow.prove(inputs_resident=True)  # untimed: buffers, work areas and side contexts come into being
+    for c in contexts():
+        lib.gzk_timing_reset(c)
     ms_total, clocks = timed(lambda: flow.prove(inputs_resident=True), args.steps, args.warmup)
     ms_per_step = ms_total / args.steps / world  # `world` independent proofs run side by side
     launches_per_step = sum(v[0] for v in timing_report().values()) // (args.steps + args.warmup)
@@ -347,13 +354,15 @@ def main():
     resident_gb = (total_bytes - free_bytes) / 1e9  # columns of one proof, tables, weights, pooled buffers
 
     # per-kernel durations: one more proof with every launch bracketed by CUDA events
-    lib.gzk_timing_reset(ctx)
-    lib.gzk_timing_enable(ctx, 1)
+    for c in contexts():
+        lib.gzk_timing_reset(c)
+        lib.gzk_timing_enable(c, 1)
     flow.prove(inputs_resident=True)
     report = timing_report()
     work = (ctypes.c_uint64 * 3)()
     lib.gzk_eval_work_counters(ctx, work)
-    lib.gzk_timing_enable(ctx, 0)
+    for c in contexts():
+        lib.gzk_timing_enable(c, 0)
     kernel_ms = {k: round(v[1], 3) for k, v in sorted(report.items(), key=lambda kv: -kv[1][1]) if v[0]}
 
     # ---- roofline of the dominant kernel family (packed evaluation) --------------------------------

@@ -64,6 +64,11 @@ int gzk_ctx_synchronize(gzk_ctx* ctx);
 int gzk_ctx_set_deferred(gzk_ctx* ctx, int on);
 /* the CUDA stream (cudaStream_t) all work of this context is issued on */
 void* gzk_ctx_stream(gzk_ctx* ctx);
+/* Orders two contexts of one GPU on the device: what is queued on `ctx` after this call runs after what
+ * was queued on `other` before it.  Nothing waits on the host.  For a host thread that deals independent
+ * chains of short calls over several contexts (each context is one stream) and joins them again; the
+ * reference runs such chains as concurrent std::async tasks (src/protocol/trace.cpp:2737-2772). */
+int gzk_ctx_wait_for(gzk_ctx* ctx, gzk_ctx* other);
 
 /* ---- measurement ---------------------------------------------------------------
  * Per kernel family: number of launches since the last reset and, while timing is

@@ -87,6 +87,10 @@ int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* leng
 size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap);
 /* the gzk_ctx the flow issues its work on (for gzk_timing_* and stream queries) */
 void* gzk_flow_context(gzk_flow* flow);
+/* The further contexts of the same GPU the flow deals independent chains of short calls over (the
+ * indexed accumulators of one commit barrier): index 0, 1, ...; NULL past the last one.  Their kernel
+ * families and launch counts are kept per context like those of the main one. */
+void* gzk_flow_side_context(gzk_flow* flow, size_t index);
 /* Test hook (no counterpart in the reference): while on, every device buffer the flow allocates is
  * filled with a byte pattern first, so a builder that reads a row nobody wrote gives a wrong proof
  * deterministically instead of depending on what the memory held before. */

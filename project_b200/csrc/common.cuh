@@ -81,6 +81,7 @@ struct gzk_ctx
     cudaStream_t stream = nullptr;
     cudaStream_t copy_stream = nullptr;  // host-to-device uploads that overlap with kernels
     cudaEvent_t copy_event = nullptr;
+    cudaEvent_t order_event = nullptr;   // recorded on this stream for another context to wait on (gzk_ctx_wait_for)
     std::string last_error;
     std::unordered_map<unsigned, gzk::DomainTables> domains;
     gzk::Fr* ntt_small[2] = {nullptr, nullptr};  // omega_1024^m and omega_1024^-m, m < 512

@@ -306,6 +306,7 @@ extern "C"
         if (cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaStreamCreateWithFlags(&ctx->copy_stream, cudaStreamNonBlocking) != cudaSuccess ||
             cudaEventCreateWithFlags(&ctx->copy_event, cudaEventDisableTiming) != cudaSuccess ||
+            cudaEventCreateWithFlags(&ctx->order_event, cudaEventDisableTiming) != cudaSuccess ||
             cudaMalloc(reinterpret_cast<void**>(&ctx->d_status), 64) != cudaSuccess ||
             // cleared ON THE CONTEXT'S STREAM and waited for: a cudaMemset would run on the legacy default stream, which
             // is not ordered with this non-blocking stream, so the first status read (gzk_ctx_set_deferred,
@@ -349,6 +350,7 @@ extern "C"
         for (auto e : ctx->event_pool) cudaEventDestroy(e);
         cudaStreamSynchronize(ctx->copy_stream);
         cudaEventDestroy(ctx->copy_event);
+        cudaEventDestroy(ctx->order_event);
         cudaStreamDestroy(ctx->copy_stream);
         cudaStreamDestroy(ctx->stream);
         delete ctx;
@@ -374,6 +376,19 @@ extern "C"
     }
 
     void* gzk_ctx_stream(gzk_ctx* ctx) { return ctx == nullptr ? nullptr : ctx->stream; }
+
+    // Everything queued on `ctx` from now on runs after everything queued on `other` so far (an event on the
+    // one stream, a wait on the other: nothing blocks on the host).  Both contexts must be on the same GPU.
+    int gzk_ctx_wait_for(gzk_ctx* ctx, gzk_ctx* other)
+    {
+        if (ctx == nullptr || other == nullptr) return GZK_E_INVALID;
+        if (ctx == other) return GZK_OK;
+        if (ctx->device != other->device) return fail(ctx, GZK_E_INVALID, "ctx_wait_for: contexts of different GPUs");
+        GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        GZK_CUDA_TRY(ctx, cudaEventRecord(other->order_event, other->stream));
+        GZK_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, other->order_event, 0));
+        return GZK_OK;
+    }
 
     int gzk_timing_enable(gzk_ctx* ctx, int on)
     {

@@ -110,6 +110,18 @@ class Flow:
         self.lib.gzk_flow_context.restype = ctypes.c_void_p
         return ctypes.c_void_p(self.lib.gzk_flow_context(self.handle))
 
+    def side_contexts(self):
+        """The further gzk_ctx handles a GPU flow deals independent call chains over (they exist once a proof has run)."""
+        if self.prefix != "gzk_flow_":
+            return []
+        self.lib.gzk_flow_side_context.restype = ctypes.c_void_p
+        out = []
+        while True:
+            side = self.lib.gzk_flow_side_context(self.handle, ctypes.c_size_t(len(out)))
+            if not side:
+                return out
+            out.append(ctypes.c_void_p(side))
+
     def close(self):
         if self.handle:
             fn = self._fn("destroy")

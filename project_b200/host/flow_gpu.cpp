@@ -2,6 +2,7 @@
 // Every Backend method is one gzk_* call; columns are gzk_buf handles that live on the GPU from
 // the forward pass to the last opening.  The context runs in deferred mode: builder calls only
 // queue kernels, the host reads values back once per commit barrier.
+#include <algorithm>
 #include <atomic>
 #include <cstring>
 
@@ -27,18 +28,21 @@ namespace
     class GpuBackend : public Backend
     {
     public:
-        explicit GpuBackend(int device)
+        explicit GpuBackend(int device) : device_(device)
         {
             if (gzk_ctx_create(device, &ctx_) != GZK_OK) throw std::runtime_error("b200 backend: no usable sm_100 GPU (there is no CPU fallback)");
             check(gzk_ctx_set_deferred(ctx_, 1));
         }
         ~GpuBackend() override
         {
+            for (gzk_ctx* side : side_) gzk_ctx_synchronize(side);
             for (auto& slot : pool_)
                 for (gzk_buf* b : slot.second) gzk_buf_free(ctx_, b);
+            for (gzk_ctx* side : side_) gzk_ctx_destroy(side);
             gzk_ctx_destroy(ctx_);
         }
         gzk_ctx* context() const { return ctx_; }
+        gzk_ctx* side_context(std::size_t i) const { return i < side_.size() ? side_[i] : nullptr; }
         // Buffers go back to a free list keyed by (kind, count) instead of to cudaFree: every proof
         // allocates the same set of columns, so from the second proof on nothing is allocated, and a
         // recycled buffer is safe to reuse at once because all work is ordered on the one stream.
@@ -206,26 +210,51 @@ namespace
             std::vector<ScanJob> small_jobs, long_jobs;
             for (const ScanJob& j : jobs)
                 ((j.op == ScanJob::kGroupPrefix ? j.domain_size : j.count) > kBatchRows ? long_jobs : small_jobs).push_back(j);
-            for (auto it = long_jobs.begin(); it != long_jobs.end();)
+            // The indexed accumulators are chains of a few kernels each, two of them short and serial (the inversion
+            // of the table, the scan of the block sums).  The jobs of one barrier are independent, so they are dealt
+            // over this context and two side contexts (one stream each): the short kernels of one job then run beside
+            // the long ones of another.  The side streams start after everything queued here so far and this stream
+            // resumes after them.
+            std::vector<const ScanJob*> indexed;
+            for (auto it = long_jobs.begin(); it != long_jobs.end(); ++it)
             {
+                const bool logup = it->op == ScanJob::kLogup && it->key_x != nullptr && it->table_size != 0 && it->table_size <= it->count;
+                const bool route = it->op == ScanJob::kRouteEdge && it->key_x != nullptr && it->table_y != nullptr && it->table_size != 0;
+                if (logup || route) indexed.push_back(&*it);
+            }
+            if (indexed.size() > 1 && side_.empty())
+            {
+                for (int i = 0; i < 2; ++i)
+                {
+                    gzk_ctx* side = nullptr;
+                    if (gzk_ctx_create(device_, &side) != GZK_OK) throw std::runtime_error("b200 backend: cannot create a side context");
+                    side_.push_back(side);
+                    check_on(side, gzk_ctx_set_deferred(side, 1));
+                }
+            }
+            const bool spread = indexed.size() > 1;
+            if (spread)
+                for (gzk_ctx* side : side_) check_on(side, gzk_ctx_wait_for(side, ctx_));
+            for (std::size_t i = 0; i < indexed.size(); ++i)
+            {
+                const ScanJob* it = indexed[i];
+                gzk_ctx* on = spread && i % (side_.size() + 1) != 0 ? side_[i % (side_.size() + 1) - 1] : ctx_;
                 // a long lookup accumulator: inverses fetched from the table (one inversion per table row, not per query)
-                if (it->op == ScanJob::kLogup && it->key_x != nullptr && it->table_size != 0 && it->table_size <= it->count)
-                {
-                    check(gzk_logup_accumulator_indexed(ctx_, raw(it->c0), raw(it->c2), raw(it->key_x), it->key_y ? raw(it->key_y) : nullptr, it->count,
-                                                        it->x_min, it->band, it->table_y ? raw(it->table_y) : nullptr, it->table_size, it->domain_size,
-                                                        it->beta.data(), raw(it->out)));
-                    it = long_jobs.erase(it);
-                }
-                else if (it->op == ScanJob::kRouteEdge && it->key_x != nullptr && it->table_y != nullptr && it->table_size != 0)
-                {
-                    check(gzk_route_edge_accumulator_indexed(ctx_, raw(it->table_y), it->table_size, raw(it->key_x), it->count, it->domain_size,
-                                                             it->beta.data(), raw(it->out)));
-                    it = long_jobs.erase(it);
-                }
+                if (it->op == ScanJob::kLogup)
+                    check_on(on, gzk_logup_accumulator_indexed(on, raw(it->c0), raw(it->c2), raw(it->key_x), it->key_y ? raw(it->key_y) : nullptr, it->count,
+                                                               it->x_min, it->band, it->table_y ? raw(it->table_y) : nullptr, it->table_size,
+                                                               it->domain_size, it->beta.data(), raw(it->out)));
                 else
-                {
-                    ++it;
-                }
+                    check_on(on, gzk_route_edge_accumulator_indexed(on, raw(it->table_y), it->table_size, raw(it->key_x), it->count, it->domain_size,
+                                                                    it->beta.data(), raw(it->out)));
+            }
+            if (spread)
+                for (gzk_ctx* side : side_) check(gzk_ctx_wait_for(ctx_, side));
+            {
+                std::vector<ScanJob> rest;
+                for (const ScanJob& j : long_jobs)
+                    if (std::find(indexed.begin(), indexed.end(), &j) == indexed.end()) rest.push_back(j);
+                long_jobs.swap(rest);
             }
             if (!long_jobs.empty()) Backend::running_sums_batch(long_jobs);
             if (small_jobs.empty()) return;
@@ -289,7 +318,11 @@ namespace
             check(gzk_fh_public_eval_rotated(ctx_, raw(features), rows, fc, abs_ids ? raw(abs_ids) : nullptr, raw(weights), log2n, rotation, bytes));
             for (int i = 0; i < 5; ++i) std::memcpy(out[i].data(), bytes + 32 * i, 32);
         }
-        void synchronize() override { check(gzk_ctx_synchronize(ctx_)); }
+        void synchronize() override
+        {
+            check(gzk_ctx_synchronize(ctx_));
+            for (gzk_ctx* side : side_) check_on(side, gzk_ctx_synchronize(side));  // their deferred errors
+        }
         bool supports_msm() const override { return true; }
         bool supports_indexed_logup() const override { return true; }
         ColP srs_lagrange(unsigned log2n, const G1& base, const Fe& tau) override
@@ -323,7 +356,13 @@ namespace
         {
             if (rc != GZK_OK) throw std::runtime_error(gzk_last_error(ctx_));
         }
+        void check_on(gzk_ctx* ctx, int rc) const
+        {
+            if (rc != GZK_OK) throw std::runtime_error(gzk_last_error(ctx));
+        }
+        int device_ = 0;
         gzk_ctx* ctx_ = nullptr;
+        std::vector<gzk_ctx*> side_;  // further contexts (streams) of the same GPU for independent chains of short calls
         std::map<std::pair<int, std::size_t>, std::vector<gzk_buf*>> pool_;
     };
 
@@ -388,4 +427,8 @@ extern "C"
     }
     void gzk_flow_debug_poison_allocations(int on) { g_poison_allocations.store(on); }
     void* gzk_flow_context(gzk_flow* flow) { return flow == nullptr ? nullptr : static_cast<GpuBackend*>(flow->backend.get())->context(); }
+    void* gzk_flow_side_context(gzk_flow* flow, size_t index)
+    {
+        return flow == nullptr ? nullptr : static_cast<GpuBackend*>(flow->backend.get())->side_context(index);
+    }
 }
