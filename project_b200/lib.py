@@ -173,6 +173,10 @@ class Backend:
     def synchronize(self):
         self._check(self.lib.gzk_ctx_synchronize(self.ctx))
 
+    def wait_for(self, other):
+        """Everything queued on this context from now on runs after what `other` (same GPU) has queued so far."""
+        self._check(self.lib.gzk_ctx_wait_for(self.ctx, other.ctx))
+
     def timing_enable(self, on=True):
         self._check(self.lib.gzk_timing_enable(self.ctx, int(bool(on))))
 

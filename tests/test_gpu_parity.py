@@ -240,3 +240,72 @@ def test_bounded_wait_that_runs_out_returns_timeout():
     got = be.eval_batch(bufs, n, log2n, w, (0, 1))
     assert np.array_equal(got, ora.eval_rotations(cols, w.download(), (0, 1)))
     be.close()
+
+
+def test_small_deferred_uploads_are_staged_in_order(be):
+    """Deferred mode queues uploads of at most 256 KiB through a ring of 16 pinned slots without waiting: forty
+    uploads from one reused host array (more than the ring holds) must each arrive with the data they were given,
+    a larger one (the waiting path) in between included."""
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_I64
+
+    rng = np.random.default_rng(5)
+    be.set_deferred(True)
+    try:
+        host = np.zeros(3000, dtype=np.int64)
+        bufs, want = [], []
+        for i in range(40):
+            host[:] = rng.integers(-(1 << 40), 1 << 40, size=host.size)
+            want.append(host.copy())
+            bufs.append(be.upload(host, KIND_I64))
+            if i == 20:
+                big = rng.integers(0, 1 << 62, size=70000, dtype=np.int64)  # 560 KB: not staged
+                big_buf = be.upload(big, KIND_I64)
+        mont = rand_fr_local(rng, 500)
+        mont_buf = be.upload(mont, KIND_FR_MONT)  # converted on the device behind the staged copy
+        be.synchronize()
+        for b, w in zip(bufs, want):
+            assert np.array_equal(b.download(), w)
+            b.free()
+        assert np.array_equal(big_buf.download(), big)
+        assert np.array_equal(mont_buf.download(), mont)
+    finally:
+        be.set_deferred(False)
+
+
+def rand_fr_local(rng, n):
+    a = rng.integers(0, 256, size=(n, 32), dtype=np.uint8)
+    a[:, 31] &= 0x3F
+    return a
+
+
+def test_contexts_ordered_on_the_device(be):
+    """gzk_ctx_wait_for: a second context (its own stream) consumes what the first one has only queued, and the first
+    one then consumes the second one's result, with no host synchronisation in between."""
+    from project_b200 import KIND_FR, KIND_I64, Backend
+
+    rng = np.random.default_rng(11)
+    side = Backend(0)
+    n, log2n = 1 << 18, 18
+    x = fr_array([int(rng.integers(2, 1 << 62))])
+    one = np.frombuffer((1).to_bytes(32, "little"), dtype=np.uint8)
+    a, b = rng.integers(-1000, 1000, size=n, dtype=np.int64), rng.integers(-1000, 1000, size=n, dtype=np.int64)
+    be.set_deferred(True)
+    side.set_deferred(True)
+    try:
+        ba, bb = be.upload(a, KIND_I64), be.upload(b, KIND_I64)
+        w = be.bary_weights(log2n, x)                                        # queued on the main context
+        col = be.linear_combination([ba, bb], np.concatenate([one, x.reshape(32)]), n, n)  # a + x b, queued behind it
+        side.wait_for(be)
+        out = side.alloc(KIND_FR, 2)
+        side.eval_batch_range_device([col], n, 0, log2n, w, 0, (0, 1), out)  # reads both on the side stream
+        be.wait_for(side)
+        got = out.download()                                                  # a read through the main context
+        side.synchronize()
+    finally:
+        be.set_deferred(False)
+        side.set_deferred(False)
+    xi = fr_ints(x)[0]
+    col_host = fr_array([(int(u) + xi * int(v)) % R for u, v in zip(a, b)])
+    want = ora.eval_rotations(col_host[None, :, :], ora.bary_weights(x, n), (0, 1))
+    assert np.array_equal(got.reshape(2, 32), want.reshape(2, 32))
+    side.close()
