@@ -274,6 +274,13 @@ class Backend:
         self._check(self.lib.gzk_route_edge_accumulator(self.ctx, query.handle, _sz(valid_length), _sz(domain_size), _ptr(_fr(beta)), out.handle))
         return out
 
+    def route_edge_accumulator_indexed(self, table, node_count, index, valid_length, domain_size, beta, out=None):
+        """Edge side of a route whose query of edge e is table[index[e]]: the node-table inverses are fetched per edge."""
+        out = out or self.alloc(KIND_FR_MONT, domain_size)
+        self._check(self.lib.gzk_route_edge_accumulator_indexed(self.ctx, table.handle, _sz(node_count), index.handle, _sz(valid_length),
+                                                                _sz(domain_size), _ptr(_fr(beta)), out.handle))
+        return out
+
     def running_sums_batch(self, jobs):
         """jobs: list of (op, [input Buffers], count, domain_size, beta or None, out Buffer): gzk_running_sums_batch."""
         raw = (_ScanJob * len(jobs))()

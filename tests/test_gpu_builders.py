@@ -415,19 +415,20 @@ def test_running_sums_batch_reports_a_zero_denominator(be):
         be.running_sums_batch([(SCAN_ROUTE_EDGE, [be.upload(q, KIND_FR)], 10, n, beta, be.alloc(KIND_FR_MONT, n))])
 
 
-@pytest.mark.parametrize("has_y", [True, False])
-def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y):
+@pytest.mark.parametrize("has_y,n,valid", [(True, 70000, 66001), (False, 70000, 66001),
+                                           # more than 2048 chunks of 512 rows: the offsets of the chunks come from a pass of their own;
+                                           # with rows behind the last query that repeat the total
+                                           (True, 1400000, 1200003), (False, 1300000, 1299999)])
+def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y, n, valid):
     """A lookup into a banded static table: the accumulator with the inverses fetched from the table's own
     1/(T_t + beta) must equal, element for element, the one that inverts every row (and the oracle's)."""
     from project_b200 import KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32, GzkError
 
-    rng = np.random.default_rng(77 + has_y)
+    rng = np.random.default_rng(77 + has_y + n)
     band = 3 if has_y else 1
     xs = 700
     x_min = -350
     table_size = xs * band
-    n = 70000
-    valid = 66001
     table_x = np.repeat(np.arange(x_min, x_min + xs, dtype=np.int64), band)
     table_y = (table_x * 7 + np.tile(np.arange(band, dtype=np.int64), xs) - 1) if has_y else None
     pick = rng.integers(0, table_size, size=valid)
@@ -460,6 +461,33 @@ def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y):
     bad[3] = x_min + xs + 5
     with pytest.raises(GzkError) as e:
         be.logup_accumulator_indexed(table, mult, be.upload(bad, KIND_I64), by, valid, x_min, band, bty, table_size, n, beta)
+    assert e.value.code == 1
+
+
+@pytest.mark.parametrize("nodes,edges,n", [(500, 3000, 4096), (9000, 1200000, 1200001), (20000, 1100000, 1 << 21)])
+def test_route_edge_indexed_equals_the_accumulator_over_the_gathered_query(be, nodes, edges, n):
+    """The edge side of a route whose query is the node table gathered by an endpoint list: fetching the node
+    table's inverses per edge must give the accumulator of the gathered query column element for element (short
+    form, and more than 2048 chunks with and without rows behind the last edge)."""
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_U32, GzkError
+
+    rng = np.random.default_rng(nodes + edges)
+    table = rand_fr(rng, nodes)
+    index = rng.integers(0, nodes, size=edges, dtype=np.uint32)
+    index[: edges // 10] = 7  # a hub
+    beta = fr_array([int(rng.integers(1, 1 << 62))])
+    pad_idx = np.concatenate([index, np.zeros(n - edges, dtype=np.uint32)])
+    query = np.zeros((n, 32), dtype=np.uint8)
+    query[:edges] = table[index]
+    bt = be.upload(np.concatenate([table, np.zeros((max(n - nodes, 0), 32), dtype=np.uint8)]), KIND_FR)
+    got = be.route_edge_accumulator_indexed(bt, nodes, be.upload(pad_idx, KIND_U32), edges, n, beta).download()
+    plain = be.route_edge_accumulator(be.upload(query, KIND_FR), edges, n, beta).download()
+    assert np.array_equal(got, plain)
+    assert np.array_equal(got, ora.route_edge_accumulator(query, edges, beta))
+    bad = pad_idx.copy()
+    bad[5] = nodes
+    with pytest.raises(GzkError) as e:
+        be.route_edge_accumulator_indexed(bt, nodes, be.upload(bad, KIND_U32), edges, n, beta)
     assert e.value.code == 1
 
 
