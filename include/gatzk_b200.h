@@ -147,9 +147,9 @@ int gzk_fr_op(int op, const uint8_t a[32], const uint8_t b[32], uint8_t out[32])
  * direct-index branch of build_domain_evaluation_weights,
  * include/gatzk/algebra/domain_evaluation.hpp:40-71, which the caller handles). */
 int gzk_bary_weights(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], gzk_buf* out);
-/* The same vector when only w[0 .. keep) and w[n-1] will be read (every column of the domain is stored as a
- * prefix of at most `keep` rows; w[n-1] is what row 0 meets at rotation 1): the other entries of `out` are
- * not written, which saves their share of the arithmetic. */
+/* The same vector when only w[0 .. keep), w[n-2] and w[n-1] will be read (every column of the domain is stored
+ * as a prefix of at most `keep` rows; the last two are what rows 0 and 1 meet at rotations 1 and 2): the other
+ * entries of `out` are not written, which saves their share of the arithmetic. */
 int gzk_bary_weights_prefix(gzk_ctx* ctx, unsigned log2n, const uint8_t x[32], uint64_t keep, gzk_buf* out);
 /* Weight vectors of one domain at `count` points (points: count x 32 bytes) into outs[0 .. count): for a domain of at
  * most 2^18 points and up to four points one launch (the binding points a head draws at the same transcript stage,

@@ -83,6 +83,16 @@ int gzk_flow_stats(gzk_flow* flow, uint64_t out[14]);
  * when out is not NULL, its first min(length, cap_elements) elements in the wire format of
  * gzk_buf_download. */
 int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* length, void* out, size_t cap_elements);
+/* Row check of the quotient numerators of the last proof run (src/protocol/quotients.cpp:311-1303 as restated
+ * in the flow): a constraint must vanish on every row of its domain when it reads the committed columns
+ * themselves (rows i and i+1; L_0 and L_{n-1} become the indicators of the first and the last row).  Checked are
+ * the constraints that the witness of the reference's own builders satisfies (not those that tie quantised values
+ * to exact arithmetic, the LogUp steps of accumulators the builders cut short, the source route; a running sum's
+ * step is not checked across the wrap-around).  out[d] = rows of domain d (FH, edge, in, d, cat, C, N) on which a
+ * checked constraint does not vanish; failures (optional) receives up to cap
+ * triples (domain index, index of the constraint in the order the reference adds them, rows it failed on), count
+ * their number.  Reads every column back: a diagnostic for small models. */
+int gzk_flow_constraint_violations(gzk_flow* flow, uint64_t out[7], uint64_t* failures, size_t cap, size_t* count);
 /* newline-separated labels of the opened columns of a domain ("FH", "edge", "in", "d", "cat", "C", "N") */
 size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap);
 /* the gzk_ctx the flow issues its work on (for gzk_timing_* and stream queries) */

@@ -598,6 +598,10 @@ extern "C"
     {
         return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);
     }
+    int ora_flow_constraint_violations(ora_flow* flow, uint64_t out[7], uint64_t* failures, size_t cap, size_t* count)
+    {
+        return gatzk_flow::flow_constraint_violations_impl(flow, out, failures, cap, count);
+    }
     size_t ora_flow_domain_labels(ora_flow* flow, const char* domain, char* out, size_t cap)
     {
         return gatzk_flow::flow_domain_labels_impl(flow, domain, out, cap);

@@ -64,7 +64,7 @@ def build(verbose=False, force=False):
         subprocess.run([nvcc, *NVCC_FLAGS[:-2], "-shared", tuning_src, "-o", TUNING_LIB_PATH], check=True)
     # the commit + prove flow: plain C++ host code over the C ABI of the library above
     host = os.path.join(HERE, "host")
-    flow_deps = [os.path.join(host, f) for f in ("flow_gpu.cpp", "prover_flow.hpp", "prover_flow_tail.hpp", "flow_c_impl.hpp", "proof_codec.hpp", "host_forward.hpp")]
+    flow_deps = [os.path.join(host, f) for f in ("flow_gpu.cpp", "prover_flow.hpp", "prover_flow_tail.hpp", "prover_flow_quotients.hpp", "flow_c_impl.hpp", "proof_codec.hpp", "host_forward.hpp")]
     flow_deps += [os.path.join(os.path.dirname(HERE), "include", f) for f in ("gatzk_b200.h", "gatzk_b200_flow.h")]
     if force or _stale(FLOW_LIB_PATH, flow_deps + [LIB_PATH]):
         subprocess.run([os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-Wextra", flow_deps[0], "-o", FLOW_LIB_PATH,

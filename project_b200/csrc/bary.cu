@@ -37,9 +37,9 @@ namespace gzk
             Fr scale;   // (x^n - 1)/n, Montgomery
             Fr x2, x4;  // x^2, x^4 (whole-domain kernels)
             Fr root4;   // I = omega^(n/4)
-            uint64_t keep;  // whole-domain kernels: weights with index >= keep are not needed (except the last one, which a rotated evaluation reads for row 0)
+            uint64_t keep;  // whole-domain kernels: weights with index >= keep are not needed (except the last two, which evaluations rotated by one and by two read for rows 0 and 1)
             // fused whole-domain kernel: CTA b works on chunk b of the quartets while b < kept_blocks and on chunk
-            // last_chunk otherwise (a short prefix is kept: only its chunks and the one holding the last weight run)
+            // last_chunk otherwise (a short prefix is kept: only its chunks and the one holding the last two weights run)
             uint32_t kept_blocks, last_chunk;
         };
 
@@ -424,7 +424,7 @@ namespace gzk
                 const Fr plus = add(a.x2, p2), minus = sub(a.x2, p2);
                 const Fr ea = mul(scaled_inverse, p1), eia = mul(scaled_inverse, ip1);
                 const uint64_t last = 4 * a.n - 1;
-                auto wanted = [&](uint64_t index) { return index < a.keep || index == last; };
+                auto wanted = [&](uint64_t index) { return index < a.keep || index + 1 >= last; };  // the prefix and the last two
                 if (wanted(e)) store_fr(out + e, mul(ea, mul(add(a.x, p1), plus)));                                   // point  a
                 if (wanted(e + 2 * a.n)) store_fr(out + e + 2 * a.n, neg(mul(ea, mul(sub(a.x, p1), plus))));          // point -a
                 if (wanted(e + a.n)) store_fr(out + e + a.n, mul(eia, mul(add(a.x, ip1), minus)));                    // point  Ia
@@ -522,7 +522,7 @@ static int bary_impl(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], ui
     if (quartets)
     {
         // Quartet e yields the weights e, e + n/4, e + n/2 and e + 3n/4.  When only a prefix shorter than n/4 is kept,
-        // the quartets below `keep` and the last one (weight n - 1) are all that is needed: the work shrinks with
+        // the quartets below `keep` and the last two (weights n - 1 and n - 2, both in the last chunk) are all that is needed: the work shrinks with
         // the prefix instead of staying that of the whole domain.
         args.kept_blocks = blocks;
         args.last_chunk = blocks - 1;
@@ -627,8 +627,9 @@ extern "C" int gzk_bary_weights_multi(gzk_ctx* ctx, unsigned log2n, const uint8_
     return rc;
 }
 
-// The whole-domain weights of which only w[0 .. keep) and w[n-1] will be read (columns stored as prefixes shorter
-// than the domain; the last weight meets row 0 at rotation 1): the other entries of `out` are left as they were.
+// The whole-domain weights of which only w[0 .. keep), w[n-2] and w[n-1] will be read (columns stored as prefixes
+// shorter than the domain; the last weights meet rows 0 and 1 at rotations 1 and 2): the other entries of `out` are
+// left as they were.
 extern "C" int gzk_bary_weights_prefix(gzk_ctx* ctx, unsigned log2n, const uint8_t x_bytes[32], uint64_t keep, gzk_buf* out)
 {
     return bary_impl(ctx, log2n, x_bytes, 0, log2n <= 30 ? (1ULL << log2n) : 0, out, keep);

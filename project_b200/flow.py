@@ -84,6 +84,16 @@ class Flow:
         return {"commit_barriers": v[0], "challenges": v[1], "dynamic_commitments": v[2], "opened_columns": v[3],
                 "domains": dict(zip(DOMAINS, v[4:11])), "h2d_bytes": v[11], "d2h_bytes": v[12], "guard_flags": v[13]}
 
+    def constraint_violations(self):
+        """(rows with a non-zero quotient numerator per domain, [(domain index, constraint index, rows it failed on), ...])."""
+        out = (ctypes.c_uint64 * 7)()
+        cap = 4096
+        failures = (ctypes.c_uint64 * (3 * cap))()
+        count = ctypes.c_size_t(0)
+        self._check(self._fn("constraint_violations")(self.handle, out, failures, ctypes.c_size_t(cap), ctypes.byref(count)))
+        n = min(int(count.value), cap)
+        return list(out), [(int(failures[3 * i]), int(failures[3 * i + 1]), int(failures[3 * i + 2])) for i in range(n)]
+
     def domain_labels(self, domain):
         fn = self._fn("domain_labels")
         size = fn(self.handle, domain.encode(), None, ctypes.c_size_t(0))

@@ -125,6 +125,19 @@ namespace gatzk_flow
         out[13] = s.guard_flags;
         return 0;
     }
+    // out[0..6]: rows of each domain on which a quotient numerator does not vanish; failures (optional, up to cap
+    // triples of domain index, constraint index, rows it failed on)
+    inline int flow_constraint_violations_impl(FlowHandle* h, std::uint64_t out[7], std::uint64_t* failures, std::size_t cap, std::size_t* count)
+    {
+        return flow_guard([&] {
+            std::vector<std::array<std::uint64_t, 3>> first;
+            const auto bad = h->flow->constraint_violations(&first);
+            for (int i = 0; i < 7; ++i) out[i] = bad[i];
+            if (count != nullptr) *count = first.size();
+            for (std::size_t i = 0; i < first.size() && i < cap && failures != nullptr; ++i)
+                for (int j = 0; j < 3; ++j) failures[3 * i + j] = first[i][j];
+        });
+    }
     inline int flow_column_impl(FlowHandle* h, const char* label, int* kind, std::uint64_t* length, void* out, std::size_t cap_elements)
     {
         return flow_guard([&] {

@@ -421,6 +421,10 @@ extern "C"
     {
         return gatzk_flow::flow_column_impl(flow, label, kind, length, out, cap_elements);
     }
+    int gzk_flow_constraint_violations(gzk_flow* flow, uint64_t out[7], uint64_t* failures, size_t cap, size_t* count)
+    {
+        return gatzk_flow::flow_constraint_violations_impl(flow, out, failures, cap, count);
+    }
     size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap)
     {
         return gatzk_flow::flow_domain_labels_impl(flow, domain, out, cap);

@@ -31,8 +31,10 @@
 #include <cmath>
 #include <cstdint>
 #include <cstring>
+#include <functional>
 #include <map>
 #include <memory>
+#include <set>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -159,7 +161,7 @@ namespace gatzk_flow
         {
             for (std::size_t i = 0; i < xs.size(); ++i) bary_weights(log2n, xs[i], outs[i]);
         }
-        // the same when only the first `keep` weights and the last one will be read (every column of the domain is a
+        // the same when only the first `keep` weights and the last two will be read (every column of the domain is a
         // prefix of at most `keep` rows); a backend may leave the other entries unwritten
         virtual void bary_weights_prefix(unsigned log2n, const Fe& x, std::size_t keep, const ColP& out)
         {
@@ -392,6 +394,7 @@ namespace gatzk_flow
         std::size_t msm_mismatches() const { return msm_mismatches_; }
         std::size_t domain_size(const std::string& name) const { return dom_.at(name).size; }
         // a column of the last proof by label (tests compare a few against the CPU restatement)
+        std::vector<std::uint64_t> constraint_violations(std::vector<std::array<std::uint64_t, 3>>* first_failures = nullptr);
         ColP column(const std::string& label, std::size_t* length = nullptr) const
         {
             const auto it = columns_.find(label);
@@ -702,6 +705,19 @@ namespace gatzk_flow
         std::vector<std::pair<std::string, Fe>> external_evaluations_, witness_scalars_;
         std::vector<std::pair<std::string, Fe>> external_sources_;  // per external evaluation: committed label, evaluation point
         std::map<std::size_t, ColP> layer_inputs_q_;                 // quantised input matrix of hidden layer i >= 1
+        // constraint numerators of the quotients (prover_flow_quotients.hpp)
+        using PointValues = std::function<Fe(const std::string&, int)>;
+        std::vector<std::string> rotated_labels(const std::string& domain) const;
+        Fe quotient_numerator(const std::string& domain, const PointValues& at, const Fe& first, const Fe& last);
+        std::map<std::string, Fe> quotient_scalars_, quotient_externals_;  // witness scalars and external evaluations by name
+        std::vector<std::size_t>* nonzero_terms_ = nullptr;                // row check: indices of the constraints that did not vanish
+        // L_0(x) and L_{n-1}(x) of a domain (RootOfUnityDomain::lagrange_basis_eval, src/algebra/polynomial.cpp:122-127)
+        std::array<Fe, 2> boundary_basis(const Domain& d, const Fe& x)
+        {
+            const Fe zero_eval = sub(pow(x, d.size), fe_u64(1)), scale = mul(zero_eval, inv(fe_u64(d.size)));
+            const Fe last_point = inv(d.omega);
+            return {mul(scale, inv(sub(x, fe_u64(1)))), mul(mul(scale, last_point), inv(sub(x, last_point)))};
+        }
         void add_external(const std::string& name, const Fe& value, const std::string& label, const Fe& point)
         {
             external_evaluations_.push_back({name, value});
@@ -1584,3 +1600,4 @@ namespace gatzk_flow
 }  // namespace gatzk_flow
 
 #include "prover_flow_tail.hpp"
+#include "prover_flow_quotients.hpp"

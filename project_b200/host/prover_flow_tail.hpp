@@ -480,14 +480,36 @@ namespace gatzk_flow
         // by stored length, one result buffer.  With at_tau the point is tau itself: the first value of every
         // column is the evaluation its commitment was made from, and the key-dependent columns' values at
         // omega*tau are computed once per context, so only rotation 1 of the witness columns is evaluated.
-        auto evaluate_domain = [&](const std::string& domain, const ColP& weights, bool at_tau, std::map<std::string, std::array<Fe, 2>>& out) {
+        // `rotations` lists the points as powers of omega times the point of `weights` (one or two of them).
+        // `only_rotated`: just the columns a quotient numerator reads at omega*x (rotated_labels) are evaluated;
+        // at tau the others still get their first value, the evaluation their commitment was made from.
+        auto evaluate_domain = [&](const std::string& domain, const ColP& weights, bool at_tau, const std::vector<std::uint64_t>& rotations, bool only_rotated,
+                                   std::map<std::string, std::array<Fe, 2>>& out) {
             const auto it = opened_.find(domain);
             std::vector<std::string> labels = it == opened_.end() ? std::vector<std::string>{} : it->second;
+            std::vector<std::string> wanted_list = only_rotated ? rotated_labels(domain) : std::vector<std::string>{};
+            const std::set<std::string> wanted(wanted_list.begin(), wanted_list.end());
+            if (only_rotated)
+            {
+                std::vector<std::string> kept;
+                for (const auto& label : labels)
+                {
+                    if (wanted.count(label) != 0)
+                        kept.push_back(label);
+                    else if (at_tau)
+                        out[label] = {commitments_.at(label).tau_evaluation, fe_u64(0)};
+                }
+                labels.swap(kept);
+            }
             for (const auto& item : static_columns_)
             {
                 if (item.second.domain != domain) continue;
                 const auto cached = static_omega_tau_.find(item.first);
-                if (at_tau && cached != static_omega_tau_.end())
+                if (only_rotated && wanted.count(item.first) == 0)
+                {
+                    if (at_tau) out[item.first] = {static_commitments_.at(item.first).tau_evaluation, fe_u64(0)};
+                }
+                else if (at_tau && cached != static_omega_tau_.end())
                     out[item.first] = {static_commitments_.at(item.first).tau_evaluation, cached->second};
                 else
                     labels.push_back(item.first);
@@ -518,7 +540,6 @@ namespace gatzk_flow
                 return;
             }
             const Domain& d = dom_.at(domain);
-            const std::vector<std::uint64_t> rotations = at_tau ? std::vector<std::uint64_t>{1} : std::vector<std::uint64_t>{0, 1};
             const std::size_t points = rotations.size();
             std::map<std::size_t, std::vector<std::string>> by_length;
             for (const auto& label : labels)
@@ -590,7 +611,7 @@ namespace gatzk_flow
                     }
                     if (!at_tau)
                     {
-                        out[label] = {value[0], value[1]};
+                        out[label] = {value[0], points > 1 ? value[1] : fe_u64(0)};
                     }
                     else if (c != columns_.end())
                     {
@@ -606,29 +627,42 @@ namespace gatzk_flow
             finish_derived();
         };
 
-        // ---- quotient scalars at tau ------------------------------------------------------------------
+        // Names the numerators use for columns this flow keeps under another label: the static tables are committed
+        // as V_T_*; the feature domain has one selector for table and query rows and one column-index column.
+        auto column_name = [](const std::string& label) -> std::string {
+            if (label.rfind("P_T_", 0) == 0 && label != "P_T_H") return "V_T_" + label.substr(4);
+            if (label == "P_Q_qry_feat") return "P_Q_tbl_feat";
+            if (label == "P_Col_feat_qry") return "P_Col_feat_tbl";
+            return label;
+        };
+        auto value_of = [&](const std::map<std::string, std::array<Fe, 2>>& values, const std::string& label, int r) -> Fe {
+            const auto found = values.find(column_name(label));
+            if (found == values.end()) throw std::runtime_error("flow: the quotient numerator reads " + label + ", which has no evaluation here");
+            return found->second[r];
+        };
+        // ---- quotient scalars at tau (prover.cpp:3076-3160 with evaluate_t_* of quotients.cpp) --------------
+        // Values at omega*tau are needed of the running columns only (rotated_labels); the reference precomputes
+        // them for every dependency label, which changes no output.
         std::vector<Fe> quotient_values(7);
         for (int di = 0; di < 7; ++di)
         {
             const Domain& d = dom_.at(kDomains[di]);
             std::map<std::string, std::array<Fe, 2>> values;
-            evaluate_domain(kDomains[di], d.w_tau, true, values);
+            evaluate_domain(kDomains[di], d.w_tau, true, {1}, true, values);
             if (std::string(kDomains[di]) == "FH")
             {
                 // generated public columns at tau and omega*tau (prepared with the key) and P_H
                 const char* names[5] = {"P_Q_tbl_feat", "P_Row_feat_tbl", "P_Col_feat_tbl", "P_I_feat_qry", "P_T_H"};
                 for (int i = 0; i < 5; ++i) values[names[i]] = {fh_public_tau_[i], fh_public_omega_tau_[i]};
+                // the lazy lookup columns: the evaluations their commitments were made from (P_R_feat is identically zero)
+                for (const char* label : {"P_H", "P_Table_feat", "P_Query_feat", "P_m_feat", "P_R_feat"})
+                    values[label] = {commitments_.at(label).tau_evaluation, fe_u64(0)};
             }
-            // stand-in for the constraint numerators of quotients.cpp: every evaluation enters once
-            Fe acc = fe_u64(0), power = fe_u64(1);
-            for (const auto& item : values)
-                for (int p = 0; p < 2; ++p)
-                {
-                    acc = add(acc, mul(power, item.second[p]));
-                    power = mul(power, alpha_quot);
-                }
+            const auto basis = boundary_basis(d, tau_);
+            const Fe numerator = quotient_numerator(
+                kDomains[di], [&](const std::string& label, int r) { return value_of(values, label, r); }, basis[0], basis[1]);
             const Fe zero_eval = sub(pow(tau_, d.size), fe_u64(1));  // Z_D(tau) = tau^n - 1
-            quotient_values[di] = mul(acc, inv(zero_eval));
+            quotient_values[di] = mul(numerator, inv(zero_eval));
             quotient_log_.push_back({std::string("t_") + kBundles[di], quotient_values[di]});
             stats_.opened_columns += values.size();
         }
@@ -669,8 +703,11 @@ namespace gatzk_flow
                 else
                     be_.bary_weights(d.log2n, z0, w_z);
             }
-            std::map<std::string, std::array<Fe, 2>> values;
-            evaluate_domain(kDomains[di], w_z, false, values);
+            std::map<std::string, std::array<Fe, 2>> values, twice_rotated;
+            evaluate_domain(kDomains[di], w_z, false, {0, 1}, false, values);
+            // t_D is opened at omega*z too, and its numerator there reads the running columns at omega^2 z
+            // (fh_dependency_points, prover.cpp:2294-2306)
+            if (std::string(kDomains[di]) != "FH") evaluate_domain(kDomains[di], w_z, false, {2}, true, twice_rotated);
             std::vector<std::string> labels = domain_labels(kDomains[di]);
             if (std::string(kDomains[di]) == "FH")
             {
@@ -692,18 +729,22 @@ namespace gatzk_flow
                 const auto a = combos(at_z), b = combos(at_wz);
                 labels = {"P_H", "P_Table_feat", "P_Query_feat", "P_m_feat", "P_R_feat"};
                 for (int i = 0; i < 5; ++i) values[labels[i]] = {a[i], b[i]};
+                const char* names[5] = {"P_Q_tbl_feat", "P_Row_feat_tbl", "P_Col_feat_tbl", "P_I_feat_qry", "P_T_H"};
+                for (int i = 0; i < 5; ++i) values[names[i]] = {at_z[i], at_wz[i]};
+                twice_rotated["P_R_feat"] = {fe_u64(0), fe_u64(0)};  // the accumulator of the feature lookup is identically zero
             }
-            // the quotient's own value at the two points (make_bundle adds the t_D label, prover.cpp:3273-3274)
+            // the quotient's own value at the two points (make_bundle adds the t_D label, prover.cpp:3273-3274):
+            // the same numerator over the opened values; Z_D(omega z) = Z_D(z)
             {
-                Fe acc0 = fe_u64(0), acc1 = fe_u64(0), power = fe_u64(1);
-                for (const auto& item : values)
-                {
-                    acc0 = add(acc0, mul(power, item.second[0]));
-                    acc1 = add(acc1, mul(power, item.second[1]));
-                    power = mul(power, alpha_quot);
-                }
-                const Fe t0 = mul(acc0, inv(sub(pow(z0, d.size), fe_u64(1)))), t1 = mul(acc1, inv(sub(pow(z1, d.size), fe_u64(1))));
-                values[std::string("t_") + kBundles[di]] = {t0, t1};
+                const Fe inv_zero_eval = inv(sub(pow(z0, d.size), fe_u64(1)));
+                const auto basis0 = boundary_basis(d, z0), basis1 = boundary_basis(d, z1);
+                const Fe n0 = quotient_numerator(
+                    kDomains[di], [&](const std::string& label, int r) { return value_of(values, label, r); }, basis0[0], basis0[1]);
+                const Fe n1 = quotient_numerator(
+                    kDomains[di],
+                    [&](const std::string& label, int r) { return r == 0 ? value_of(values, label, 1) : value_of(twice_rotated, label, 0); },
+                    basis1[0], basis1[1]);
+                values[std::string("t_") + kBundles[di]] = {mul(n0, inv_zero_eval), mul(n1, inv_zero_eval)};
                 labels.push_back(std::string("t_") + kBundles[di]);
             }
             gatzk_b200::protocol::DomainOpeningBundle bundle;

@@ -220,7 +220,7 @@ class Backend:
         return out
 
     def bary_weights_prefix(self, log2n, x, keep, out=None):
-        """Whole-domain weights of which only the first `keep` and the last one are written."""
+        """Whole-domain weights of which only the first `keep` and the last two are written."""
         out = out or self.alloc(KIND_FR_MONT, 1 << log2n)
         self._check(self.lib.gzk_bary_weights_prefix(self.ctx, ctypes.c_uint(log2n), _ptr(_fr(x)), ctypes.c_uint64(keep), out.handle))
         return out

@@ -1,5 +1,6 @@
 """The prover flow over the CPU restatement: structure of the proof it produces.  (The comparison
 with the GPU backend is tests/test_gpu_proof_parity.py.)"""
+import pytest
 import numpy as np
 
 import oracle_lib as ora
@@ -76,3 +77,18 @@ def test_prefix_stored_columns_give_the_same_proof():
         assert np.array_equal(full.proof_bytes(), compact.proof_bytes())
         full.close()
         compact.close()
+
+
+@pytest.mark.parametrize("output_heads,compact", [(1, False), (2, False), (1, True)])
+def test_quotient_constraints_vanish_on_the_rows(output_heads, compact):
+    """The constraint numerators of the seven quotients, restated from src/protocol/quotients.cpp, read at the points
+    of a domain: every constraint that the witness of the reference's own builders satisfies must vanish on every row
+    (the running-sum steps on every row but the last).  Which constraints are left out, and why, is stated where the
+    numerators are written (ProverFlow::quotient_numerator)."""
+    inputs = synthetic.make_inputs(seed=3, nodes=24, directed_edges=60, feature_count=6, hidden=[(2, 4)], output_heads=output_heads, class_count=3)
+    flow = Flow(ora.lib(), "ora_flow_", 2, inputs, G, compact_columns=compact)
+    flow.prove()
+    bad, failures = flow.constraint_violations()
+    flow.close()
+    assert bad == [0] * 7, failures
+    assert failures == []

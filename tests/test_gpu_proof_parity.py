@@ -139,3 +139,16 @@ def test_no_builder_reads_a_row_nobody_wrote():
         assert first_difference(gpu.dump(), cpu.dump()) is None
         cpu.close()
         gpu.close()
+
+
+@pytest.mark.parametrize("compact", [False, True])
+def test_quotient_constraints_vanish_on_the_rows_of_the_gpu_columns(compact):
+    """The row check of the restated quotient numerators (every constraint the reference's own witness satisfies
+    vanishes on every row; ProverFlow::constraint_violations) over the columns the GPU backend built, two hidden
+    layers and two output heads."""
+    inputs = synthetic.make_inputs(seed=5, nodes=30, directed_edges=90, feature_count=7, hidden=[(2, 3), (1, 4)], output_heads=2, class_count=3)
+    gpu = gpu_flow(0, inputs, G, compact_columns=compact)
+    gpu.prove()
+    bad, failures = gpu.constraint_violations()
+    gpu.close()
+    assert bad == [0] * 7, failures
