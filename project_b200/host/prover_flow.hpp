@@ -7,8 +7,9 @@
 // proof, heads in transcript order, per hidden head the barrier groups of trace.cpp:2392-2414
 // (16 columns), :2454-2459 (H_star), :2774-2823 (43 columns), :3023-3046 (17) and :3047-3058 (5),
 // the layer concatenation of :3076-3133, the output heads of :3185-3650 and the final challenges
-// of :4241-4257; then the evaluation of every opened column at {tau, omega*tau} and, after the
-// quotient commitments, at {z, omega*z} per domain.  Labels and challenge names are those of
+// of :4241-4257; then the quotient scalars from the evaluations at {tau, omega*tau}
+// (src/protocol/quotients.cpp:311-1303) and, after the quotient commitments, the evaluation of every
+// opened column at {z, omega*z} per domain with the quotients' own values there.  Labels and challenge names are those of
 // src/protocol/challenges.cpp:138-309, 396-507 and src/protocol/schema.cpp.
 //
 // All O(domain) work goes through `Backend`; this file only does O(#columns) scalar glue.  The
@@ -18,10 +19,9 @@
 // Deliberate differences from the reference, all in host glue outside the hot path:
 //  - the G1 generator is an input and points are serialised by a local 48-byte encoding (the
 //    reference takes both from the mcl library: src/crypto/kzg.cpp:383, src/crypto/curve.cpp:63-73);
-//  - the constraint numerators of src/protocol/quotients.cpp:311-1303 are not restated: the
-//    quotient scalar t_D(tau) of a domain is formed here as the alpha_quot-weighted sum of ALL
-//    evaluations of the domain's columns at tau and omega*tau, divided by Z_D(tau).  It has the
-//    same inputs and the same place in the transcript as the reference's scalar, not its value;
+//  - a quotient numerator reads only the running columns at a rotated point, so only those are
+//    evaluated at omega*tau and at omega^2*z (prover_flow_quotients.hpp); the reference evaluates every
+//    dependency label at every point, which changes no value of the proof;
 //  - public and static columns are limited to those the transcript absorbs and the builders read
 //    (ids, endpoints, selectors, tables, model parameters).
 #pragma once
