@@ -106,8 +106,10 @@ namespace gzk
             }
         }
 
-        // The same sums again for the shapes of the large models (inner a multiple of 8, width a multiple
-        // of 64): a CTA owns 128 rows x 64 columns and a thread 8 x 4 of them, so an operand read from shared
+        // The same sums again for the shapes of the large models (inner a multiple of 8, width even):
+        // a CTA owns 128 rows x 64 columns and a thread 8 x 4 of them (columns 2t, 2t+1, 32+2t, 32+2t+1 of the
+        // tile, so that the threads of a warp read consecutive 16-byte pieces of a W row: no bank conflict; the
+        // columns beyond a ragged width are computed on zeros and not stored), so an operand read from shared
         // memory feeds 5.3 multiply-adds instead of 4; the 8-deep slices are double-buffered (the next one is
         // requested from global memory before the current one is consumed) and the slice loop is unrolled.
         // Two CTAs per SM (128 registers).  Runs at about four fifths of the rate at which the fp64 pipe
@@ -130,6 +132,7 @@ namespace gzk
             constexpr int kXLoads = kWideM * kWideK / 2 / kThreads;  // pairs of doubles per thread and slice
             constexpr int kWLoads = kWideK * kWideN / 2 / kThreads;
             static_assert(kXLoads * kThreads * 2 == kWideM * kWideK && kWLoads * kThreads * 2 == kWideK * kWideN, "slices must divide among the threads");
+            static_assert(kWideCols == 4, "a thread owns two pairs of columns, half a tile apart");
             double2 xr[kXLoads], wr[kWLoads];
             auto request = [&](uint32_t k0) {
 #pragma unroll
@@ -145,7 +148,7 @@ namespace gzk
                 {
                     const uint32_t id = threadIdx.x + p * kThreads;
                     const uint32_t kr = id / (kWideN / 2), jq = (id % (kWideN / 2)) * 2;
-                    wr[p] = __ldg(reinterpret_cast<const double2*>(w + static_cast<uint64_t>(k0 + kr) * width + j0 + jq));
+                    wr[p] = j0 + jq < width ? __ldg(reinterpret_cast<const double2*>(w + static_cast<uint64_t>(k0 + kr) * width + j0 + jq)) : make_double2(0.0, 0.0);
                 }
             };
             auto stash = [&](int buf) {
@@ -187,7 +190,7 @@ namespace gzk
 #pragma unroll
                     for (int c = 0; c < kWideCols; c += 2)
                     {
-                        const double2 v = *reinterpret_cast<const double2*>(&ws[buf][kk][tx * kWideCols + c]);
+                        const double2 v = *reinterpret_cast<const double2*>(&ws[buf][kk][(c / 2) * (kWideN / 2) + tx * 2]);
                         b[c] = v.x;
                         b[c + 1] = v.y;
                     }
@@ -207,7 +210,10 @@ namespace gzk
                 if (row >= rows) continue;
 #pragma unroll
                 for (int c = 0; c < kWideCols; c += 2)
-                    *reinterpret_cast<double2*>(out + row * width + j0 + tx * kWideCols + c) = make_double2(acc[r][c], acc[r][c + 1]);
+                {
+                    const uint32_t j = j0 + (c / 2) * (kWideN / 2) + tx * 2;
+                    if (j < width) *reinterpret_cast<double2*>(out + row * width + j) = make_double2(acc[r][c], acc[r][c + 1]);
+                }
             }
         }
 
@@ -553,10 +559,10 @@ extern "C" int gzk_gat_head_forward(gzk_ctx* ctx, const gzk_gat_head* head, cons
             return fail(ctx, GZK_E_INVALID, "edge out of bounds while running attention head forward");
         }
     }
-    if (width % kWideN == 0 && inner % kWideK == 0 && inner != 0)
+    if (width % 2 == 0 && width >= 32 && inner % kWideK == 0 && inner != 0)
     {
         LaunchScope scope(ctx, "forward_project");
-        const dim3 grid(width / kWideN, static_cast<unsigned>((nodes + kWideM - 1) / kWideM));
+        const dim3 grid((width + kWideN - 1) / kWideN, static_cast<unsigned>((nodes + kWideM - 1) / kWideM));
         project_wide_kernel<<<grid, kThreads, 0, ctx->stream>>>(f64_ptr(head->features), f64_ptr(head->seq_kernel), nodes, inner, width,
                                                                 f64_ptr(out->H_prime));
     }

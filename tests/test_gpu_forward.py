@@ -101,6 +101,9 @@ def run_case(be, rng, nodes, inner, width, edges, self_loops, bias, activation, 
     # width a multiple of 64 and inner a multiple of 8: the 128 x 64 projection tiles (ragged last row tile; one slice; many)
     (333, 8, 64, 2500, True, True, True),
     (1100, 72, 128, 9000, True, True, True),
+    # an even width that is not a multiple of 64 (the 40 classes of the large model's output layer): ragged column tile
+    (700, 48, 40, 5000, True, True, True),
+    (260, 16, 98, 1500, True, True, True),
 ])
 def test_head_forward_matches_oracle(be, nodes, inner, width, edges, self_loops, bias, activation):
     run_case(be, np.random.default_rng(nodes * 7 + width), nodes, inner, width, edges, self_loops, bias, activation)
