@@ -460,6 +460,65 @@ namespace gzk
             if (threadIdx.x == 0) store_fr(total_out, total.v);
         }
 
+        // The same scan in two levels for long columns (a single CTA walks 2^17 aggregates in two dependent passes of
+        // 128 loads per thread: 55 us of one SM while the others wait): every group of 1024 aggregates is scanned
+        // by a CTA of its own, the group totals by the kernel above, and a third kernel adds the group offsets.
+        __global__ void __launch_bounds__(kOffsetThreads) scan_group_offsets_kernel(Fr* agg_value, uint32_t* agg_flag, uint32_t ctas, Fr* group_value,
+                                                                                   uint32_t* group_flag)
+        {
+            __shared__ SegVal seg_slots[kOffsetThreads / 32];
+            const uint32_t i = blockIdx.x * kOffsetThreads + threadIdx.x;
+            SegVal mine;
+            mine.v = Fr::zero();
+            mine.flag = 0;
+            if (i < ctas)
+            {
+                mine.v = load_fr_plain(agg_value + i);
+                mine.flag = agg_flag[i];
+            }
+            SegVal total;
+            const SegVal prefix = block_seg_exclusive_scan<kOffsetThreads>(mine, seg_slots, &total);
+            if (i < ctas)
+            {
+                store_fr(agg_value + i, prefix.v);
+                agg_flag[i] = prefix.flag;
+            }
+            if (threadIdx.x == 0)
+            {
+                store_fr(group_value + blockIdx.x, total.v);
+                group_flag[blockIdx.x] = total.flag;
+            }
+        }
+        __global__ void __launch_bounds__(kOffsetThreads) scan_apply_group_offsets_kernel(Fr* agg_value, uint32_t* agg_flag, uint32_t ctas, const Fr* group_value,
+                                                                                         const uint32_t* group_flag)
+        {
+            const uint32_t i = blockIdx.x * kOffsetThreads + threadIdx.x;
+            if (i >= ctas || blockIdx.x == 0) return;
+            SegVal before, mine;
+            before.v = load_fr_plain(group_value + blockIdx.x);
+            before.flag = group_flag[blockIdx.x];
+            mine.v = load_fr_plain(agg_value + i);
+            mine.flag = agg_flag[i];
+            const SegVal both = seg_combine(before, mine);
+            store_fr(agg_value + i, both.v);
+            agg_flag[i] = both.flag;
+        }
+        // the offsets pass of a column with `ctas` chunks; `groups` holds 2 * (groups + 1) spare field elements
+        void launch_scan_offsets(gzk_ctx* ctx, Fr* agg_value, uint32_t* agg_flag, uint32_t ctas, Fr* total, Fr* groups)
+        {
+            LaunchScope scope(ctx, "scan_offsets");
+            if (ctas <= 8 * kOffsetThreads)
+            {
+                scan_offsets_kernel<<<1, kOffsetThreads, 0, ctx->stream>>>(agg_value, agg_flag, ctas, total);
+                return;
+            }
+            const uint32_t group_count = (ctas + kOffsetThreads - 1) / kOffsetThreads;
+            uint32_t* group_flag = reinterpret_cast<uint32_t*>(groups + group_count + 1);
+            scan_group_offsets_kernel<<<group_count, kOffsetThreads, 0, ctx->stream>>>(agg_value, agg_flag, ctas, groups, group_flag);
+            scan_offsets_kernel<<<1, kOffsetThreads, 0, ctx->stream>>>(groups, group_flag, group_count, total);
+            scan_apply_group_offsets_kernel<<<group_count, kOffsetThreads, 0, ctx->stream>>>(agg_value, agg_flag, ctas, groups, group_flag);
+        }
+
         template <int OP>
         __global__ void __launch_bounds__(kThreads) scan_fixup_kernel(ScanArgs a)
         {
@@ -653,7 +712,8 @@ namespace gzk
             const uint64_t span = OP == kSegmented ? args.n : args.count;
             const uint32_t ctas = static_cast<uint32_t>((span + kChunk - 1) / kChunk > 0 ? (span + kChunk - 1) / kChunk : 1);
             void* scratch = nullptr;
-            const size_t bytes = static_cast<size_t>(ctas) * (3 * sizeof(Fr) + 2 * sizeof(uint32_t)) + 2 * sizeof(Fr);
+            const size_t group_count = (static_cast<size_t>(ctas) + kOffsetThreads - 1) / kOffsetThreads;
+            const size_t bytes = static_cast<size_t>(ctas) * (3 * sizeof(Fr) + 2 * sizeof(uint32_t)) + 2 * sizeof(Fr) + 2 * (group_count + 1) * sizeof(Fr);
             int rc = ensure_scratch(ctx, 2, bytes, &scratch);
             if (rc != GZK_OK) return rc;
             Fr* base = static_cast<Fr*>(scratch);
@@ -663,6 +723,7 @@ namespace gzk
             args.total = base + 3 * static_cast<size_t>(ctas);
             args.agg_flag = reinterpret_cast<uint32_t*>(base + 3 * static_cast<size_t>(ctas) + 2);
             args.agg_first = args.agg_flag + ctas;
+            Fr* group_area = reinterpret_cast<Fr*>(reinterpret_cast<char*>(scratch) + ((static_cast<size_t>(ctas) * (3 * sizeof(Fr) + 2 * sizeof(uint32_t)) + 2 * sizeof(Fr) + 31) & ~static_cast<size_t>(31)));
             args.status = ctx->d_status;
             if (!call_begun && (rc = begin_call(ctx)) != GZK_OK) return rc;
             const bool local_inverse = inverting && ctas <= static_cast<uint32_t>(ctx->sm_count) * 4;
@@ -695,10 +756,7 @@ namespace gzk
             }
             else
             {
-                {
-                    LaunchScope scope(ctx, "scan_offsets");
-                    scan_offsets_kernel<<<1, kOffsetThreads, 0, ctx->stream>>>(args.agg_value, args.agg_flag, ctas, args.total);
-                }
+                launch_scan_offsets(ctx, args.agg_value, args.agg_flag, ctas, args.total, group_area);
                 GZK_CUDA_TRY(ctx, cudaGetLastError());
                 if (args.n > 0)
                 {

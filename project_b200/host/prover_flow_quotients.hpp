@@ -495,7 +495,7 @@ namespace gatzk_flow
             {
                 std::vector<std::size_t> failed;
                 nonzero_terms_ = &failed;
-                const Fe numerator = quotient_numerator(
+                quotient_numerator(
                     domain,
                     [&](const std::string& label, int r) {
                         auto found = by_request.find(label);

@@ -473,7 +473,7 @@ namespace gatzk_flow
     // and the folded external opening (kzg.cpp:619-633).
     inline void ProverFlow::prove_openings(Transcript& t)
     {
-        const Fe alpha_quot = challenge(t, "alpha_quot");
+        challenge(t, "alpha_quot");  // read back by name where the numerators are formed
         static const char* kDomains[7] = {"FH", "edge", "in", "d", "cat", "C", "N"};
         static const char* kBundles[7] = {"FH", "edge", "in", "d_h", "cat", "C", "N"};
         // All columns of a domain evaluated at two points (the point of `weights` and omega times it): grouped
