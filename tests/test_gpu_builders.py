@@ -464,7 +464,9 @@ def test_logup_indexed_equals_the_row_by_row_accumulator(be, has_y, n, valid):
     assert e.value.code == 1
 
 
-@pytest.mark.parametrize("nodes,edges,n", [(500, 3000, 4096), (9000, 1200000, 1200001), (20000, 1100000, 1 << 21)])
+@pytest.mark.parametrize("nodes,edges,n", [(500, 3000, 4096), (9000, 1200000, 1200001), (20000, 1100000, 1 << 21),
+                                           # more than 8192 chunks: the chunk offsets are scanned in two levels
+                                           (30000, 4300000, 4300001)])
 def test_route_edge_indexed_equals_the_accumulator_over_the_gathered_query(be, nodes, edges, n):
     """The edge side of a route whose query is the node table gathered by an endpoint list: fetching the node
     table's inverses per edge must give the accumulator of the gathered query column element for element (short
