@@ -625,8 +625,18 @@ extern "C"
         const uint32_t col_chunks = static_cast<uint32_t>((cols + kThreads - 1) / kThreads);
         const uint32_t width = cols < kThreads ? static_cast<uint32_t>(cols) : kThreads;
         const uint32_t row_lanes = kThreads / width;
-        // enough tiles to fill the machine, each tile at least 8 rows per row lane
-        uint64_t tiles = static_cast<uint64_t>(ctx->sm_count) * 4 / col_chunks;
+        // Enough tiles to fill the machine, each tile at least 8 rows per row lane: a whole number of rounds of the
+        // CTAs that are resident at once (two rounds), so that the last round is not a partly filled one.
+        const size_t smem = static_cast<size_t>(kThreads) * kAccLimbs * sizeof(uint32_t);
+        int resident = 0;
+        switch (entry_kind(matrix->kind))
+        {
+        case GZK_KIND_I64: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fold_rows_kernel<GZK_KIND_I64>, kThreads, smem); break;
+        case GZK_KIND_U32: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fold_rows_kernel<GZK_KIND_U32>, kThreads, smem); break;
+        default: cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fold_rows_kernel<GZK_KIND_FR>, kThreads, smem); break;
+        }
+        if (resident < 1) resident = 2;
+        uint64_t tiles = static_cast<uint64_t>(ctx->sm_count) * static_cast<uint64_t>(resident) * 2 / col_chunks;
         const uint64_t max_tiles = (row_count + 8ull * row_lanes - 1) / (8ull * row_lanes);
         if (tiles > max_tiles) tiles = max_tiles;
         if (tiles > 1024) tiles = 1024;
@@ -639,7 +649,6 @@ extern "C"
         ColRef m;
         m.ptr = matrix->dptr;
         m.kind = matrix->kind;
-        const size_t smem = static_cast<size_t>(kThreads) * kAccLimbs * sizeof(uint32_t);
         {
             LaunchScope scope(ctx, "fold_rows");
             const unsigned grid = static_cast<unsigned>(tiles * col_chunks);
