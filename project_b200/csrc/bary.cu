@@ -422,13 +422,21 @@ namespace gzk
                 const Fr p2 = sqr(p1);
                 const Fr ip1 = mul(a.root4, p1);
                 const Fr plus = add(a.x2, p2), minus = sub(a.x2, p2);
-                const Fr ea = mul(scaled_inverse, p1), eia = mul(scaled_inverse, ip1);
                 const uint64_t last = 4 * a.n - 1;
                 auto wanted = [&](uint64_t index) { return index < a.keep || index + 1 >= last; };  // the prefix and the last two
-                if (wanted(e)) store_fr(out + e, mul(ea, mul(add(a.x, p1), plus)));                                   // point  a
-                if (wanted(e + 2 * a.n)) store_fr(out + e + 2 * a.n, neg(mul(ea, mul(sub(a.x, p1), plus))));          // point -a
-                if (wanted(e + a.n)) store_fr(out + e + a.n, mul(eia, mul(add(a.x, ip1), minus)));                    // point  Ia
-                if (wanted(e + 3 * a.n)) store_fr(out + e + 3 * a.n, neg(mul(eia, mul(sub(a.x, ip1), minus))));       // point -Ia
+                // the factor the two points of a pair share is formed once: three multiplications per pair, not four
+                if (wanted(e) || wanted(e + 2 * a.n))
+                {
+                    const Fr shared = mul(mul(scaled_inverse, p1), plus);
+                    if (wanted(e)) store_fr(out + e, mul(shared, add(a.x, p1)));                        // point  a
+                    if (wanted(e + 2 * a.n)) store_fr(out + e + 2 * a.n, neg(mul(shared, sub(a.x, p1))));  // point -a
+                }
+                if (wanted(e + a.n) || wanted(e + 3 * a.n))
+                {
+                    const Fr shared = mul(mul(scaled_inverse, ip1), minus);
+                    if (wanted(e + a.n)) store_fr(out + e + a.n, mul(shared, add(a.x, ip1)));                 // point  Ia
+                    if (wanted(e + 3 * a.n)) store_fr(out + e + 3 * a.n, neg(mul(shared, sub(a.x, ip1))));   // point -Ia
+                }
             }
         }
 
