@@ -93,6 +93,16 @@ int gzk_flow_column(gzk_flow* flow, const char* label, int* kind, uint64_t* leng
  * triples (domain index, index of the constraint in the order the reference adds them, rows it failed on), count
  * their number.  Reads every column back: a diagnostic for small models. */
 int gzk_flow_constraint_violations(gzk_flow* flow, uint64_t out[7], uint64_t* failures, size_t cap, size_t* count);
+/* Honest quotient of one domain of the last proof run (a diagnostic: the reference commits t_D = N(tau)/Z(tau) by
+ * the trapdoor and never divides a polynomial, src/protocol/prover.cpp:3076-3160).  Every column the domain's
+ * numerator reads is interpolated (gzk_ntt, inverse) and evaluated on the domain of n << log2_blowup points
+ * (gzk_ntt, forward); the numerator of the constraint classes in `classes` (bit 0: constraints that vanish on every
+ * row, bit 1: those that vanish except across the wrap-around, bit 2: those the reference's own witness does not
+ * satisfy) is formed pointwise, transformed to coefficients and divided by X^n - 1: N = t (X^n - 1) + R.
+ * out: n, points, degree of N, rows on which R does not vanish, 1 when t(x)(x^n - 1) + R(x) equals the numerator
+ * formed directly at a point x outside the domains (0: the blow-up is too small for the degree), degree of t.
+ * log2_blowup 1..4, at most 2^22 points; the pointwise part runs on the host: for small models. */
+int gzk_flow_honest_quotient(gzk_flow* flow, const char* domain, unsigned log2_blowup, unsigned classes, uint64_t out[6]);
 /* newline-separated labels of the opened columns of a domain ("FH", "edge", "in", "d", "cat", "C", "N") */
 size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap);
 /* the gzk_ctx the flow issues its work on (for gzk_timing_* and stream queries) */

@@ -28,6 +28,7 @@ extern "C" int ora_gat_head_forward(const double* features, std::size_t nodes, s
                                     double* Z, double* M, double* Delta, double* U, double* Sum, double* inv, double* alpha, double* H_agg_pre,
                                     double* H_agg);
 extern "C" const char* ora_last_error();
+extern "C" int ora_ntt(std::uint8_t* data, std::uint64_t size, int inverse, const std::uint8_t* coset_shift);
 
 namespace
 {
@@ -525,6 +526,27 @@ namespace
             }
         }
         void synchronize() override {}
+        // the radix-2 transform of oracle.cpp over the same bytes
+        void transform(std::vector<Fe>& data, bool inverse) override
+        {
+            if (ora_ntt(reinterpret_cast<std::uint8_t*>(data.data()), data.size(), inverse ? 1 : 0, nullptr) != 0)
+                throw std::runtime_error("transform: the length must be a power of two");
+        }
+        // independent vectors on the host's threads
+        void transform_many(std::vector<std::vector<Fe>>& vectors, bool inverse) override
+        {
+            const std::size_t workers = std::max<std::size_t>(1, std::min<std::size_t>({std::thread::hardware_concurrency(), 32, vectors.size()}));
+            std::vector<std::thread> pool;
+            std::vector<int> failed(workers, 0);
+            for (std::size_t w = 0; w < workers; ++w)
+                pool.emplace_back([&, w] {
+                    for (std::size_t i = w; i < vectors.size(); i += workers)
+                        if (ora_ntt(reinterpret_cast<std::uint8_t*>(vectors[i].data()), vectors[i].size(), inverse ? 1 : 0, nullptr) != 0) failed[w] = 1;
+                });
+            for (auto& t : pool) t.join();
+            for (int f : failed)
+                if (f) throw std::runtime_error("transform: the length must be a power of two");
+        }
 
     private:
         static CpuCol& cpu(const ColP& c)
@@ -601,6 +623,10 @@ extern "C"
     int ora_flow_constraint_violations(ora_flow* flow, uint64_t out[7], uint64_t* failures, size_t cap, size_t* count)
     {
         return gatzk_flow::flow_constraint_violations_impl(flow, out, failures, cap, count);
+    }
+    int ora_flow_honest_quotient(ora_flow* flow, const char* domain, unsigned log2_blowup, unsigned classes, uint64_t out[6])
+    {
+        return gatzk_flow::flow_honest_quotient_impl(flow, domain, log2_blowup, classes, out);
     }
     size_t ora_flow_domain_labels(ora_flow* flow, const char* domain, char* out, size_t cap)
     {

@@ -94,6 +94,14 @@ class Flow:
         n = min(int(count.value), cap)
         return list(out), [(int(failures[3 * i]), int(failures[3 * i + 1]), int(failures[3 * i + 2])) for i in range(n)]
 
+    def honest_quotient(self, domain, log2_blowup=2, classes=1):
+        """N = t (X^n - 1) + R of one domain's quotient numerator, restricted to the constraint classes in `classes`
+        (bit 0 exact, bit 1 wrapping, bit 2 loose), through the backend's transforms."""
+        out = (ctypes.c_uint64 * 6)()
+        self._check(self._fn("honest_quotient")(self.handle, domain.encode(), ctypes.c_uint(log2_blowup), ctypes.c_uint(classes), out))
+        keys = ("n", "points", "numerator_degree", "remainder_rows", "identity_holds", "quotient_degree")
+        return dict(zip(keys, (int(v) for v in out)))
+
     def domain_labels(self, domain):
         fn = self._fn("domain_labels")
         size = fn(self.handle, domain.encode(), None, ctypes.c_size_t(0))

@@ -138,6 +138,14 @@ namespace gatzk_flow
                 for (int j = 0; j < 3; ++j) failures[3 * i + j] = first[i][j];
         });
     }
+    // the honest quotient of one domain ("FH", "edge", "in", "d", "cat", "C", "N"): see ProverFlow::honest_quotient
+    inline int flow_honest_quotient_impl(FlowHandle* h, const char* domain, unsigned log2_blowup, unsigned classes, std::uint64_t out[6])
+    {
+        return flow_guard([&] {
+            const auto report = h->flow->honest_quotient(domain, log2_blowup, classes);
+            for (int i = 0; i < 6; ++i) out[i] = report[i];
+        });
+    }
     inline int flow_column_impl(FlowHandle* h, const char* label, int* kind, std::uint64_t* length, void* out, std::size_t cap_elements)
     {
         return flow_guard([&] {

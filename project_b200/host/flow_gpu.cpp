@@ -323,6 +323,16 @@ namespace
             check(gzk_ctx_synchronize(ctx_));
             for (gzk_ctx* side : side_) check_on(side, gzk_ctx_synchronize(side));  // their deferred errors
         }
+        void transform(std::vector<Fe>& data, bool inverse) override
+        {
+            unsigned log2n = 0;
+            while ((std::size_t{1} << log2n) < data.size()) ++log2n;
+            if (data.empty() || (std::size_t{1} << log2n) != data.size()) throw std::runtime_error("transform: the length must be a power of two");
+            const ColP in = alloc(kFr, data.size()), out = alloc(kFrMont, data.size());
+            upload(in, data.data(), data.size());
+            check(gzk_ntt(ctx_, raw(in), raw(out), log2n, 1, inverse ? 1 : 0, nullptr));
+            download(out, 0, data.size(), data.data());
+        }
         bool supports_msm() const override { return true; }
         bool supports_indexed_logup() const override { return true; }
         ColP srs_lagrange(unsigned log2n, const G1& base, const Fe& tau) override
@@ -424,6 +434,10 @@ extern "C"
     int gzk_flow_constraint_violations(gzk_flow* flow, uint64_t out[7], uint64_t* failures, size_t cap, size_t* count)
     {
         return gatzk_flow::flow_constraint_violations_impl(flow, out, failures, cap, count);
+    }
+    int gzk_flow_honest_quotient(gzk_flow* flow, const char* domain, unsigned log2_blowup, unsigned classes, uint64_t out[6])
+    {
+        return gatzk_flow::flow_honest_quotient_impl(flow, domain, log2_blowup, classes, out);
     }
     size_t gzk_flow_domain_labels(gzk_flow* flow, const char* domain, char* out, size_t cap)
     {

@@ -37,6 +37,7 @@
 #include <set>
 #include <stdexcept>
 #include <string>
+#include <thread>
 #include <utility>
 #include <vector>
 
@@ -178,6 +179,14 @@ namespace gatzk_flow
         virtual void fh_public_eval(const ColP& features, std::size_t rows, std::size_t feature_count, const ColP& abs_ids, const ColP& weights,
                                     unsigned log2n, std::uint64_t rotation, Fe out[5]) = 0;
         virtual void synchronize() = 0;
+        // Number-theoretic transform of a host vector in place (length a power of two; natural order; forward:
+        // out[j] = sum_i in[i] omega^(ij) with omega = root_of_unity(length); inverse undoes it).  Only the
+        // honest-quotient diagnostic calls it.
+        virtual void transform(std::vector<Fe>& data, bool inverse) = 0;
+        virtual void transform_many(std::vector<std::vector<Fe>>& vectors, bool inverse)
+        {
+            for (auto& v : vectors) transform(v, inverse);
+        }
         // Honest-prover commitment by multi-scalar multiplication (optional): structured reference strings
         // [L_i(tau)] G of a domain / [tau^i] G, the resident table of shifted bases of such a point set,
         // and sum_i scalars[i] * P_i against it.  `scalars` is a field-element column (kFr / kFrMont).
@@ -395,6 +404,7 @@ namespace gatzk_flow
         std::size_t domain_size(const std::string& name) const { return dom_.at(name).size; }
         // a column of the last proof by label (tests compare a few against the CPU restatement)
         std::vector<std::uint64_t> constraint_violations(std::vector<std::array<std::uint64_t, 3>>* first_failures = nullptr);
+        std::array<std::uint64_t, 6> honest_quotient(const std::string& domain, unsigned log2_blowup, unsigned classes);
         ColP column(const std::string& label, std::size_t* length = nullptr) const
         {
             const auto it = columns_.find(label);
@@ -709,6 +719,9 @@ namespace gatzk_flow
         using PointValues = std::function<Fe(const std::string&, int)>;
         std::vector<std::string> rotated_labels(const std::string& domain) const;
         Fe quotient_numerator(const std::string& domain, const PointValues& at, const Fe& first, const Fe& last);
+        std::map<std::string, std::vector<Fe>> domain_cells(const std::string& domain);
+        static std::string numerator_column(const std::string& label);
+        unsigned term_classes_ = 7u;  // classes of constraints that enter the numerator (bit c = class c); all, except inside the honest-quotient diagnostic
         std::map<std::string, Fe> quotient_scalars_, quotient_externals_;  // witness scalars and external evaluations by name
         std::vector<std::size_t>* nonzero_terms_ = nullptr;                // row check: indices of the constraints that did not vanish
         // L_0(x) and L_{n-1}(x) of a domain (RootOfUnityDomain::lagrange_basis_eval, src/algebra/polynomial.cpp:122-127)

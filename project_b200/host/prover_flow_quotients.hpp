@@ -86,7 +86,7 @@ namespace gatzk_flow
         auto push = [&](const Fe& term, int cls = kExact) {
             if (nonzero_terms_ != nullptr && term != fe_u64(0)) nonzero_terms_->push_back(index * 4 + static_cast<std::size_t>(cls));
             ++index;
-            sum = add(sum, mul(power, term));
+            if ((term_classes_ >> cls) & 1u) sum = add(sum, mul(power, term));
             power = mul(power, alpha);
         };
         auto ch = [&](const std::string& name) {
@@ -396,6 +396,96 @@ namespace gatzk_flow
         throw std::runtime_error("flow: unknown quotient domain " + domain);
     }
 
+    // Every column a domain's numerator reads, as n field elements on the host: committed columns (prefix-stored ones
+    // filled out with their tail), derived columns summed from their sources, static columns, and for the feature
+    // domain the columns the flow never stores.
+    inline std::map<std::string, std::vector<Fe>> ProverFlow::domain_cells(const std::string& domain)
+    {
+        const Domain& d = dom_.at(domain);
+        const std::size_t n = d.size;
+        const Fe zero = fe_u64(0), one = fe_u64(1);
+        std::map<std::string, std::vector<Fe>> cells;
+        auto read_column = [&](const ColP& col, std::size_t length, bool const_tail, const Fe& tail) {
+            std::vector<Fe> out(n, const_tail ? tail : zero);
+            length = std::min(length, n);
+            if (col->kind == kI64)
+            {
+                std::vector<std::int64_t> raw(length);
+                be_.download(col, 0, length, raw.data());
+                for (std::size_t i = 0; i < length; ++i) out[i] = from_signed(raw[i]);
+            }
+            else if (col->kind == kU32)
+            {
+                std::vector<std::uint32_t> raw(length);
+                be_.download(col, 0, length, raw.data());
+                for (std::size_t i = 0; i < length; ++i) out[i] = fe_u64(raw[i]);
+            }
+            else
+            {
+                be_.download(col, 0, length, out.data());
+            }
+            return out;
+        };
+        if (domain == "FH")
+        {
+            const std::size_t fc = in_.feature_count, valid = n_nodes_ * fc;
+            std::vector<std::int64_t> ids(n_nodes_), feats(valid);
+            be_.download(ids_i64_, 0, n_nodes_, ids.data());
+            be_.download(features_q_, 0, valid, feats.data());
+            const Fe eta = challenges_.at("eta_feat"), eta2 = mul(eta, eta);
+            for (const char* label : {"P_Q_tbl_feat", "P_Row_feat_tbl", "P_Col_feat_tbl", "P_I_feat_qry", "P_T_H", "P_H", "P_Table_feat", "P_Query_feat", "P_m_feat", "P_R_feat"})
+                cells[label] = std::vector<Fe>(n, zero);
+            for (std::size_t i = 0; i < valid && i < n; ++i)
+            {
+                const Fe row = fe_u64(i / fc), column = fe_u64(i % fc), id = from_signed(ids[i / fc]), value = from_signed(feats[i]);
+                cells["P_Q_tbl_feat"][i] = one;
+                cells["P_Row_feat_tbl"][i] = row;
+                cells["P_Col_feat_tbl"][i] = column;
+                cells["P_I_feat_qry"][i] = id;
+                cells["P_T_H"][i] = value;
+                cells["P_H"][i] = value;
+                cells["P_m_feat"][i] = one;
+                cells["P_Table_feat"][i] = add(add(row, mul(eta, column)), mul(eta2, value));
+                cells["P_Query_feat"][i] = add(add(id, mul(eta, column)), mul(eta2, value));
+            }
+        }
+        else
+        {
+            std::vector<std::string> derived;
+            const auto opened = opened_.find(domain);
+            if (opened != opened_.end())
+                for (const auto& label : opened->second)
+                {
+                    const ColumnEntry& c = columns_.at(label);
+                    if (!c.derived_from.empty())
+                        derived.push_back(label);
+                    else
+                        cells[label] = read_column(c.col, c.length, c.const_tail, c.tail);
+                }
+            for (const auto& item : static_columns_)
+                if (item.second.domain == domain) cells[item.first] = read_column(item.second.col, item.second.length, false, zero);
+            for (const auto& label : derived)
+            {
+                std::vector<Fe> out(n, zero);
+                for (const auto& term : columns_.at(label).derived_from)
+                {
+                    const auto& source = cells.at(term.first);
+                    for (std::size_t i = 0; i < n; ++i) out[i] = add(out[i], mul(term.second, source[i]));
+                }
+                cells[label] = out;
+            }
+        }
+        return cells;
+    }
+    // The numerator spells a few columns differently from the committed label.
+    inline std::string ProverFlow::numerator_column(const std::string& label)
+    {
+        if (label.rfind("P_T_", 0) == 0 && label != "P_T_H") return "V_T_" + label.substr(4);
+        if (label == "P_Q_qry_feat") return "P_Q_tbl_feat";
+        if (label == "P_Col_feat_qry") return "P_Col_feat_tbl";
+        return label;
+    }
+
     // Row check of the restated constraints (a diagnostic; no counterpart call in the reference, whose verifier
     // checks the same identities at the opening points): on a point omega^i of a domain the "evaluations" are the
     // column entries of rows i and i+1, L_0 and L_{n-1} are the indicators of the first and the last row, and
@@ -410,85 +500,9 @@ namespace gatzk_flow
         for (int di = 0; di < 7; ++di)
         {
             const std::string domain = kDomains[di];
-            const Domain& d = dom_.at(domain);
-            const std::size_t n = d.size;
-            std::map<std::string, std::vector<Fe>> cells;
-            auto read_column = [&](const ColP& col, std::size_t length, bool const_tail, const Fe& tail) {
-                std::vector<Fe> out(n, const_tail ? tail : zero);
-                length = std::min(length, n);
-                if (col->kind == kI64)
-                {
-                    std::vector<std::int64_t> raw(length);
-                    be_.download(col, 0, length, raw.data());
-                    for (std::size_t i = 0; i < length; ++i) out[i] = from_signed(raw[i]);
-                }
-                else if (col->kind == kU32)
-                {
-                    std::vector<std::uint32_t> raw(length);
-                    be_.download(col, 0, length, raw.data());
-                    for (std::size_t i = 0; i < length; ++i) out[i] = fe_u64(raw[i]);
-                }
-                else
-                {
-                    be_.download(col, 0, length, out.data());
-                }
-                return out;
-            };
-            if (domain == "FH")
-            {
-                const std::size_t fc = in_.feature_count, valid = n_nodes_ * fc;
-                std::vector<std::int64_t> ids(n_nodes_), feats(valid);
-                be_.download(ids_i64_, 0, n_nodes_, ids.data());
-                be_.download(features_q_, 0, valid, feats.data());
-                const Fe eta = challenges_.at("eta_feat"), eta2 = mul(eta, eta);
-                for (const char* label : {"P_Q_tbl_feat", "P_Row_feat_tbl", "P_Col_feat_tbl", "P_I_feat_qry", "P_T_H", "P_H", "P_Table_feat", "P_Query_feat", "P_m_feat", "P_R_feat"})
-                    cells[label] = std::vector<Fe>(n, zero);
-                for (std::size_t i = 0; i < valid && i < n; ++i)
-                {
-                    const Fe row = fe_u64(i / fc), column = fe_u64(i % fc), id = from_signed(ids[i / fc]), value = from_signed(feats[i]);
-                    cells["P_Q_tbl_feat"][i] = one;
-                    cells["P_Row_feat_tbl"][i] = row;
-                    cells["P_Col_feat_tbl"][i] = column;
-                    cells["P_I_feat_qry"][i] = id;
-                    cells["P_T_H"][i] = value;
-                    cells["P_H"][i] = value;
-                    cells["P_m_feat"][i] = one;
-                    cells["P_Table_feat"][i] = add(add(row, mul(eta, column)), mul(eta2, value));
-                    cells["P_Query_feat"][i] = add(add(id, mul(eta, column)), mul(eta2, value));
-                }
-            }
-            else
-            {
-                std::vector<std::string> derived;
-                const auto opened = opened_.find(domain);
-                if (opened != opened_.end())
-                    for (const auto& label : opened->second)
-                    {
-                        const ColumnEntry& c = columns_.at(label);
-                        if (!c.derived_from.empty())
-                            derived.push_back(label);
-                        else
-                            cells[label] = read_column(c.col, c.length, c.const_tail, c.tail);
-                    }
-                for (const auto& item : static_columns_)
-                    if (item.second.domain == domain) cells[item.first] = read_column(item.second.col, item.second.length, false, zero);
-                for (const auto& label : derived)
-                {
-                    std::vector<Fe> out(n, zero);
-                    for (const auto& term : columns_.at(label).derived_from)
-                    {
-                        const auto& source = cells.at(term.first);
-                        for (std::size_t i = 0; i < n; ++i) out[i] = add(out[i], mul(term.second, source[i]));
-                    }
-                    cells[label] = out;
-                }
-            }
-            auto name_of = [](const std::string& label) -> std::string {
-                if (label.rfind("P_T_", 0) == 0 && label != "P_T_H") return "V_T_" + label.substr(4);
-                if (label == "P_Q_qry_feat") return "P_Q_tbl_feat";
-                if (label == "P_Col_feat_qry") return "P_Col_feat_tbl";
-                return label;
-            };
+            const std::size_t n = dom_.at(domain).size;
+            const std::map<std::string, std::vector<Fe>> cells = domain_cells(domain);
+            auto name_of = [](const std::string& label) { return numerator_column(label); };
             std::map<std::string, const std::vector<Fe>*> by_request;  // the numerator's own spelling -> column
             std::map<std::size_t, std::uint64_t> rows_failed;           // constraint index -> rows
             for (std::size_t i = 0; i < n; ++i)
@@ -525,5 +539,166 @@ namespace gatzk_flow
                 for (const auto& item : rows_failed) failures->push_back({static_cast<std::uint64_t>(di), item.first, item.second});
         }
         return bad;
+    }
+    // Honest quotient of one domain (a diagnostic; the reference commits t_D by the trapdoor shortcut N(tau)/Z(tau) and
+    // never divides a polynomial, src/protocol/prover.cpp:3076-3160).  Every column the numerator reads goes through
+    // the backend's transforms: inverse transform of its n rows, zero padding, forward transform on the domain of
+    // n << log2_blowup points.  The numerator, restricted to the constraint classes in `classes` (bit c = class c of
+    // quotient_numerator), is formed point by point there - a rotation by omega is a step of 1 << log2_blowup points -
+    // and transformed back to coefficients, which are divided by X^n - 1:  N = t (X^n - 1) + R.
+    //   out[0] n   out[1] points   out[2] degree of N (highest non-zero coefficient; 0 for the zero polynomial)
+    //   out[3] rows omega^i on which R does not vanish (R(omega^i) = N(omega^i): what the row check counts)
+    //   out[4] 1 when t(x) (x^n - 1) + R(x) equals the numerator formed directly from the columns' values at x and
+    //          omega x (Horner on their coefficients), x a point outside the domains - this fails when the blow-up is
+    //          too small for the numerator's degree
+    //   out[5] degree of t
+    // Host work grows with points x constraints: meant for configurations of a few thousand rows per domain.
+    inline std::array<std::uint64_t, 6> ProverFlow::honest_quotient(const std::string& domain, unsigned log2_blowup, unsigned classes)
+    {
+        const Domain& d = dom_.at(domain);
+        const std::size_t n = d.size, blowup = std::size_t{1} << log2_blowup, points = n * blowup;
+        if (log2_blowup < 1 || log2_blowup > 4 || points > (std::size_t{1} << 22)) throw std::runtime_error("flow: the honest quotient takes a blow-up of 2..16 and at most 2^22 points");
+        const Fe zero = fe_u64(0), one = fe_u64(1);
+        std::map<std::string, std::vector<Fe>> cells = domain_cells(domain);
+        cells["(first row)"] = std::vector<Fe>(n, zero);
+        cells["(first row)"][0] = one;
+        cells["(last row)"] = std::vector<Fe>(n, zero);
+        cells["(last row)"][n - 1] = one;
+
+        struct Extended
+        {
+            std::vector<Fe> coefficients, values;
+        };
+        std::map<std::string, Extended> extended;  // by the numerator's own spelling
+        {
+            // which columns the numerator reads: one pass over it with every value zero
+            std::vector<std::string> labels = {"(first row)", "(last row)"};
+            quotient_numerator(
+                domain,
+                [&](const std::string& label, int) {
+                    if (std::find(labels.begin(), labels.end(), label) == labels.end()) labels.push_back(label);
+                    return zero;
+                },
+                zero, zero);
+            std::vector<std::vector<Fe>> work;
+            for (const auto& label : labels)
+            {
+                const auto column = cells.find(numerator_column(label));
+                if (column == cells.end()) throw std::runtime_error("flow: the honest quotient finds no column " + label);
+                work.push_back(column->second);
+            }
+            be_.transform_many(work, true);
+            for (std::size_t i = 0; i < labels.size(); ++i)
+            {
+                extended[labels[i]].coefficients = work[i];
+                work[i].resize(points, zero);
+            }
+            be_.transform_many(work, false);
+            for (std::size_t i = 0; i < labels.size(); ++i) extended[labels[i]].values = std::move(work[i]);
+        }
+        auto extend = [&](const std::string& label) -> const Extended& {
+            const auto found = extended.find(label);
+            if (found == extended.end()) throw std::runtime_error("flow: the numerator reads " + label + " on some points only");
+            return found->second;
+        };
+        const unsigned saved = term_classes_;
+        term_classes_ = classes;
+        std::vector<Fe> numerator(points);
+        try
+        {
+            const std::vector<Fe>&first = extend("(first row)").values, &last = extend("(last row)").values;
+            using Requested = std::map<std::string, const std::vector<Fe>*>;
+            auto at_point = [&](std::size_t j, Requested& by_request) {
+                return quotient_numerator(
+                    domain,
+                    [&](const std::string& label, int r) {
+                        auto found = by_request.find(label);
+                        if (found == by_request.end()) found = by_request.emplace(label, &extend(label).values).first;
+                        return (*found->second)[(j + static_cast<std::size_t>(r) * blowup) % points];
+                    },
+                    first[j], last[j]);
+            };
+            // pointwise on all host threads: the columns are only read
+            const std::size_t workers = std::max<std::size_t>(1, std::min<std::size_t>({std::thread::hardware_concurrency(), 32, points / 64 + 1}));
+            std::vector<std::thread> pool;
+            std::vector<std::string> errors(workers);
+            for (std::size_t w = 0; w < workers; ++w)
+                pool.emplace_back([&, w] {
+                    try
+                    {
+                        Requested mine;
+                        for (std::size_t j = w; j < points; j += workers) numerator[j] = at_point(j, mine);
+                    }
+                    catch (const std::exception& e)
+                    {
+                        errors[w] = e.what();
+                    }
+                });
+            for (auto& t : pool) t.join();
+            for (const auto& e : errors)
+                if (!e.empty()) throw std::runtime_error(e);
+        }
+        catch (...)
+        {
+            term_classes_ = saved;
+            throw;
+        }
+        be_.transform(numerator, true);  // coefficients of N
+        auto degree_of = [&](const std::vector<Fe>& c) {
+            for (std::size_t i = c.size(); i-- > 0;)
+                if (c[i] != zero) return static_cast<std::uint64_t>(i);
+            return std::uint64_t{0};
+        };
+        // t's block k-1 is the sum of N's blocks k and above; R = N's block 0 + t's block 0
+        std::vector<Fe> quotient(points - n, zero), remainder(n);
+        for (std::size_t i = 0; i < n; ++i)
+        {
+            Fe running = zero;
+            for (std::size_t k = blowup; k-- > 1;)
+            {
+                running = add(running, numerator[k * n + i]);
+                quotient[(k - 1) * n + i] = running;
+            }
+            remainder[i] = add(numerator[i], running);
+        }
+        auto horner = [&](const std::vector<Fe>& c, const Fe& x) {
+            Fe acc = zero;
+            for (std::size_t i = c.size(); i-- > 0;) acc = add(mul(acc, x), c[i]);
+            return acc;
+        };
+        // a point outside every domain, fixed by the transcript
+        const Fe x = add(challenges_.at("alpha_quot"), fe_u64(0x9e3779b97f4a7c15ULL));
+        Fe direct = zero;
+        std::map<std::pair<std::string, int>, Fe> at_x;  // a column's value at x (rotation 0) or omega x (rotation 1), formed once
+        try
+        {
+            const auto basis = boundary_basis(d, x);
+            direct = quotient_numerator(
+                domain,
+                [&](const std::string& label, int r) {
+                    const auto key = std::make_pair(label, r);
+                    auto found = at_x.find(key);
+                    if (found == at_x.end()) found = at_x.emplace(key, horner(extend(label).coefficients, r == 0 ? x : mul(x, pow(d.omega, static_cast<std::uint64_t>(r))))).first;
+                    return found->second;
+                },
+                basis[0], basis[1]);
+        }
+        catch (...)
+        {
+            term_classes_ = saved;
+            throw;
+        }
+        term_classes_ = saved;
+        const Fe divided = add(mul(horner(quotient, x), sub(pow(x, n), one)), horner(remainder, x));
+        std::array<std::uint64_t, 6> out{};
+        out[0] = n;
+        out[1] = points;
+        out[2] = degree_of(numerator);
+        out[5] = degree_of(quotient);
+        out[4] = divided == direct ? 1 : 0;
+        be_.transform(remainder, false);
+        for (const Fe& value : remainder)
+            if (value != zero) ++out[3];
+        return out;
     }
 }

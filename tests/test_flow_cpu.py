@@ -92,3 +92,35 @@ def test_quotient_constraints_vanish_on_the_rows(output_heads, compact):
     flow.close()
     assert bad == [0] * 7, failures
     assert failures == []
+
+
+def test_honest_quotients_divide():
+    """The honest quotient of every domain (no counterpart in the reference, which commits t_D = N(tau)/Z(tau) by the
+    trapdoor, src/protocol/prover.cpp:3076-3160): the numerator of the constraints that vanish on every row, extended
+    through the transforms to four times the domain, divides by X^n - 1 without remainder; with the wrapping
+    running-sum steps the remainder lives on the last row alone; the division identity N = t (X^n - 1) + R holds at a
+    point outside the domains for every class of constraints; a blow-up too small for the numerator's degree is
+    reported."""
+    inputs = synthetic.make_inputs(seed=3, nodes=24, directed_edges=60, feature_count=6, hidden=[(2, 4)], output_heads=1, class_count=3)
+    flow = Flow(ora.lib(), "ora_flow_", 2, inputs, G)
+    flow.prove()
+    bad, _ = flow.constraint_violations()
+    assert bad == [0] * 7
+    for domain in ("FH", "in", "d", "cat", "C", "N", "edge"):
+        exact = flow.honest_quotient(domain, 2, 1)
+        assert exact["remainder_rows"] == 0 and exact["identity_holds"] == 1, (domain, exact)
+        assert exact["points"] == 4 * exact["n"]
+        if exact["numerator_degree"] > 0:
+            assert exact["quotient_degree"] == exact["numerator_degree"] - exact["n"], (domain, exact)
+        if domain == "edge":
+            continue  # 131072 points: the other classes of this domain are covered on the GPU
+        wrapping = flow.honest_quotient(domain, 2, 3)
+        assert wrapping["remainder_rows"] <= 1 and wrapping["identity_holds"] == 1, (domain, wrapping)
+        everything = flow.honest_quotient(domain, 2, 7)
+        assert everything["identity_holds"] == 1 and everything["remainder_rows"] >= wrapping["remainder_rows"], (domain, everything)
+    # degree 3n - 3 (n = 8) does not fit 2n points
+    assert flow.honest_quotient("in", 1, 1)["identity_holds"] == 0
+    assert flow.honest_quotient("N", 3, 1) == dict(flow.honest_quotient("N", 2, 1), points=8 * 32)
+    with pytest.raises(Exception):
+        flow.honest_quotient("N", 0, 1)
+    flow.close()

@@ -152,3 +152,26 @@ def test_quotient_constraints_vanish_on_the_rows_of_the_gpu_columns(compact):
     bad, failures = gpu.constraint_violations()
     gpu.close()
     assert bad == [0] * 7, failures
+
+
+def test_honest_quotients_through_the_gpu_transforms():
+    """The honest quotient of every domain with the columns built, interpolated and extended on the GPU (gzk_ntt on
+    the trace columns of a proof): the same report as over the CPU backend for every class of constraints, no
+    remainder for the constraints that vanish on every row, and the division identity at a point outside the
+    domains."""
+    inputs = synthetic.make_inputs(seed=3, nodes=24, directed_edges=60, feature_count=6, hidden=[(2, 4)], output_heads=1, class_count=3)
+    cpu = Flow(ora.lib(), "ora_flow_", 2, inputs, G)
+    gpu = gpu_flow(0, inputs, G)
+    cpu.prove()
+    gpu.prove()
+    for domain in ("FH", "in", "d", "cat", "C", "N", "edge"):
+        for classes in (1, 3, 7):
+            report = gpu.honest_quotient(domain, 2, classes)
+            assert report["identity_holds"] == 1, (domain, classes, report)
+            if classes == 1:
+                assert report["remainder_rows"] == 0, (domain, report)
+            if domain != "edge" or classes == 1:
+                assert report == cpu.honest_quotient(domain, 2, classes), (domain, classes)
+    assert gpu.honest_quotient("in", 1, 1)["identity_holds"] == 0
+    cpu.close()
+    gpu.close()
