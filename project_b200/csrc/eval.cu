@@ -362,19 +362,24 @@ namespace gzk
                 eval_partial_kernel<1><<<blocks, kThreads, smem_bytes(1), stream>>>(args);
         }
 
-        // One CTA of 256 threads per (rotation, column) pair: the threads sum the per-tile partials
-        // (up to 4096 of them: a single warp walking them was a 40 us chain of dependent loads), the
-        // warps and then the CTA add them up exactly, thread 0 reduces once and writes the result.
-        constexpr int kFinishThreads = 256;
+        // One CTA per (rotation, column) pair: the threads sum the per-tile partials (up to 4096 of them: a
+        // single warp walking them was a 40 us chain of dependent loads), four tiles requested at a time so that
+        // a thread waits for memory once or twice, not once per tile; the warps and then the first warp add
+        // them up exactly, thread 0 reduces once and writes the result.
+        constexpr int kFinishThreads = 256;      // up to 1024 tiles
+        constexpr int kFinishThreadsWide = 512;  // more
+        constexpr int kFinishGroup = 4;
+        inline unsigned finish_threads(uint32_t tiles) { return tiles > 1024 ? kFinishThreadsWide : kFinishThreads; }
         // `poison_status`: when given and raised (a bounded wait of the partial kernel gave up, so some
         // partial sums were never written), every output becomes 32 bytes of 0xFF - not a canonical
         // field element - instead of a sum over stale partials.
-        __global__ void eval_finish_kernel(const uint32_t* partial, const int* kinds, uint32_t tiles, uint32_t p_count,
-                                           uint32_t k_count, Fr* out_canonical, int uniform_kind = -1, int out_montgomery = 0,
-                                           const int* poison_status = nullptr)
+        __global__ void __launch_bounds__(kFinishThreadsWide)
+            eval_finish_kernel(const uint32_t* partial, const int* kinds, uint32_t tiles, uint32_t p_count, uint32_t k_count, Fr* out_canonical,
+                               int uniform_kind = -1, int out_montgomery = 0, const int* poison_status = nullptr)
         {
-            __shared__ uint32_t warp_acc[kFinishThreads / 32][kAccLimbs];
+            __shared__ uint32_t warp_acc[kFinishThreadsWide / 32][kAccLimbs];
             const uint32_t lane = threadIdx.x & 31;
+            const uint32_t threads = blockDim.x;
             const uint32_t idx = blockIdx.x;
             if (idx >= p_count * k_count) return;
             if (poison_status != nullptr && *poison_status != 0)
@@ -393,31 +398,53 @@ namespace gzk
             uint32_t acc[kAccLimbs];
 #pragma unroll
             for (int i = 0; i < kAccLimbs; ++i) acc[i] = 0;
-            for (uint32_t tile = threadIdx.x; tile < tiles; tile += kFinishThreads)
+            const uint64_t tile_stride = static_cast<uint64_t>(p_count) * k_count * kAccLimbs;
+            const uint32_t* mine = partial + (static_cast<uint64_t>(p) * k_count + k) * kAccLimbs;
+            uint32_t tile = threadIdx.x;
+            for (; tile + (kFinishGroup - 1) * threads < tiles; tile += kFinishGroup * threads)
             {
-                const uint32_t* src = partial + ((static_cast<uint64_t>(tile) * p_count + p) * k_count + k) * kAccLimbs;
+                uint32_t t[kFinishGroup][kAccLimbs];
+#pragma unroll
+                for (int g = 0; g < kFinishGroup; ++g)
+                {
+                    const uint32_t* src = mine + (tile + g * threads) * tile_stride;
+#pragma unroll
+                    for (int i = 0; i < kAccLimbs; ++i) t[g][i] = src[i];
+                }
+#pragma unroll
+                for (int g = 0; g < kFinishGroup; ++g) acc_add<kAccLimbs, kAccLimbs>(acc, t[g]);
+            }
+            for (; tile < tiles; tile += threads)
+            {
+                const uint32_t* src = mine + tile * tile_stride;
                 uint32_t t[kAccLimbs];
 #pragma unroll
                 for (int i = 0; i < kAccLimbs; ++i) t[i] = src[i];
                 acc_add<kAccLimbs, kAccLimbs>(acc, t);
             }
+            auto warp_sum = [&]() {
 #pragma unroll
-            for (int offset = 16; offset > 0; offset >>= 1)
-            {
-                uint32_t other[kAccLimbs];
+                for (int offset = 16; offset > 0; offset >>= 1)
+                {
+                    uint32_t other[kAccLimbs];
 #pragma unroll
-                for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, acc[i], offset);
-                acc_add<kAccLimbs, kAccLimbs>(acc, other);
-            }
+                    for (int i = 0; i < kAccLimbs; ++i) other[i] = __shfl_down_sync(0xffffffffu, acc[i], offset);
+                    acc_add<kAccLimbs, kAccLimbs>(acc, other);
+                }
+            };
+            warp_sum();
             if (lane == 0)
             {
 #pragma unroll
                 for (int i = 0; i < kAccLimbs; ++i) warp_acc[threadIdx.x >> 5][i] = acc[i];
             }
             __syncthreads();
-            if (threadIdx.x != 0) return;
-#pragma unroll 1
-            for (int w = 1; w < kFinishThreads / 32; ++w) acc_add<kAccLimbs, kAccLimbs>(acc, warp_acc[w]);
+            if (threadIdx.x >= 32) return;
+            // the first warp: lane w takes the sum of warp w
+#pragma unroll
+            for (int i = 0; i < kAccLimbs; ++i) acc[i] = lane < (threads >> 5) ? warp_acc[lane][i] : 0u;
+            warp_sum();
+            if (lane != 0) return;
             // acc = 2^256 * S (canonical columns) or 2^512 * S (Montgomery columns), S the
             // true sum; 9 reduction rows divide by 2^288.
             const Fr reduced = redc_wide<FrCfg, 9>(acc);
@@ -449,7 +476,7 @@ namespace gzk
                            Fr* out, bool out_montgomery)
     {
         LaunchScope scope(ctx, "eval_finish");
-        eval_finish_kernel<<<k_count, kFinishThreads, 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
+        eval_finish_kernel<<<k_count, finish_threads(tiles), 0, ctx->stream>>>(partial, nullptr, tiles, 1, k_count, out, uniform_kind,
                                                                           out_montgomery ? 1 : 0);
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         return GZK_OK;
@@ -600,7 +627,7 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
         const uint32_t outs = p_now * static_cast<uint32_t>(k_count);
         {
             LaunchScope scope(ctx, "eval_finish");
-            eval_finish_kernel<<<outs, kFinishThreads, 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
+            eval_finish_kernel<<<outs, finish_threads(tiles), 0, ctx->stream>>>(static_cast<const uint32_t*>(d_partial), d_kinds, tiles, p_now,
                                                                            static_cast<uint32_t>(k_count), d_out + p0 * k_count, -1,
                                                                            dest != nullptr && dest_montgomery ? 1 : 0);
         }
@@ -785,7 +812,7 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     launch_eval_partial(s, args, static_cast<int>(p_count), static_cast<unsigned>(blocks));
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
-    eval_finish_kernel<<<outs, kFinishThreads, 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
+    eval_finish_kernel<<<outs, finish_threads(tiles), 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
                                                          static_cast<uint32_t>(k_count), static_cast<Fr*>(out_device), -1, 0, args.status);
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     return GZK_OK;
