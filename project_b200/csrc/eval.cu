@@ -99,15 +99,101 @@ namespace gzk
                 if (mbar_try_wait(bar, parity)) return true;
             return false;
         }
-        __device__ __forceinline__ Fr load_fr_shared(const unsigned char* p)
+        // ---- field-element columns on the tensor cores -----------------------------------
+        // sum_i w_i * f_i over the rows of a unit, both factors 32 bytes: with W[i][a] and F[i][b] their bytes,
+        // C[a][b] = sum_i W[i][a] * F[i][b] is a 32 x 32 matrix product with the ROWS as the contraction
+        // index, and the exact integer sum is sum_ab C[a][b] * 2^(8(a+b)).  One warp-wide
+        // mma.sync m16n8k32 (u8 x u8 -> s32) contracts 32 rows for a 16 x 8 block of C; eight of them cover
+        // C for 32 rows - 32768 byte products where the integer pipe would issue 2048 limb products.
+        // A fragment register holds ONE byte index and FOUR rows, memory holds four byte indices of one row
+        // per word: every lane loads a 4 x 4 byte block (its word of four rows) and transposes it with eight
+        // byte permutes.  Which rows and which bytes a lane takes is free (any permutation of the rows, the
+        // same for both factors, and any numbering of the bytes): lane (g, t) = (lane / 4, lane % 4) takes word
+        // g of rows t, t+4, t+8, t+12 (+16 for the second half of the contraction) - conflict-free in shared
+        // memory - so that byte 4g + j of the weights is row 8*(j&1) + g of block j/2 of C, and byte
+        // 4g + j of the column values is column g of block j.
+        // s32 entries hold 255^2 * 32768 rows; the warp folds C into a 17-limb total before that many.
+        constexpr uint32_t kStepsPerFold = 1024;  // x 32 rows
+
+        __device__ __forceinline__ void load_rows_transposed(const unsigned char* step_base, uint32_t g, uint32_t t, uint32_t out[2][4])
         {
-            const uint4* q = reinterpret_cast<const uint4*>(p);
-            const uint4 a = q[0];
-            const uint4 b = q[1];
-            Fr o;
-            o.l[0] = a.x; o.l[1] = a.y; o.l[2] = a.z; o.l[3] = a.w;
-            o.l[4] = b.x; o.l[5] = b.y; o.l[6] = b.z; o.l[7] = b.w;
-            return o;
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+            {
+                const uint32_t* word = reinterpret_cast<const uint32_t*>(step_base + (16 * h + t) * 32) + g;
+                const uint32_t x0 = word[0], x1 = word[32], x2 = word[64], x3 = word[96];  // rows t, t+4, t+8, t+12
+                const uint32_t t0 = __byte_perm(x0, x1, 0x5140), t1 = __byte_perm(x2, x3, 0x5140);
+                const uint32_t t2 = __byte_perm(x0, x1, 0x7362), t3 = __byte_perm(x2, x3, 0x7362);
+                out[h][0] = __byte_perm(t0, t1, 0x5410);
+                out[h][1] = __byte_perm(t0, t1, 0x7632);
+                out[h][2] = __byte_perm(t2, t3, 0x5410);
+                out[h][3] = __byte_perm(t2, t3, 0x7632);
+            }
+        }
+        __device__ __forceinline__ void mma_u8(int32_t c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1)
+        {
+            asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                         : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+        }
+        // Adds sum_ab C[a][b] 2^(8(a+b)) to `total` (every lane ends with the same 17 limbs) and clears C.
+        // `scratch`: 4 KiB of this warp's shared memory that nothing else uses meanwhile.
+        __device__ __forceinline__ void fold_byte_products(int32_t c[2][4][4], unsigned char* scratch, uint32_t lane, uint32_t* total)
+        {
+            const uint32_t g = lane >> 2, t = lane & 3;
+            int32_t* matrix = reinterpret_cast<int32_t*>(scratch);
+            __syncwarp();
+#pragma unroll
+            for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                    {
+                        const uint32_t a = 4 * g + 2 * mt + (i >> 1);
+                        const uint32_t b = 8 * t + 4 * (i & 1) + nt;
+                        matrix[a * 32 + b] = c[mt][nt][i];
+                        c[mt][nt][i] = 0;
+                    }
+            __syncwarp();
+            // the two anti-diagonals a + b = lane and a + b = lane + 32
+            unsigned long long low = 0, high = 0;
+#pragma unroll 8
+            for (uint32_t a = 0; a < 32; ++a)
+            {
+                const uint32_t value = static_cast<uint32_t>(matrix[31 * a + lane + (a > lane ? 32 : 0)]);
+                if (a > lane)
+                    high += value;
+                else
+                    low += value;
+            }
+            __syncwarp();
+            unsigned long long* diagonal = reinterpret_cast<unsigned long long*>(scratch);
+            diagonal[lane] = low;
+            diagonal[lane + 32] = high;  // diagonal 63 does not exist: lane 31 writes 0
+            __syncwarp();
+            // limb j collects the diagonals 4j .. 4j+3 (each below 2^37, so the sum stays below 2^62)
+            unsigned long long* limb = reinterpret_cast<unsigned long long*>(scratch + 512);  // behind the 64 diagonals
+            if (lane < 16)
+                limb[lane] = diagonal[4 * lane] + (diagonal[4 * lane + 1] << 8) + (diagonal[4 * lane + 2] << 16) + (diagonal[4 * lane + 3] << 24);
+            __syncwarp();
+            uint32_t even[kAccLimbs], odd[kAccLimbs];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+            {
+                const unsigned long long e = limb[2 * k], o = limb[2 * k + 1];
+                even[2 * k] = static_cast<uint32_t>(e);
+                even[2 * k + 1] = static_cast<uint32_t>(e >> 32);
+                odd[2 * k + 1] = static_cast<uint32_t>(o);
+                odd[2 * k + 2] = static_cast<uint32_t>(o >> 32);
+            }
+            even[16] = 0;
+            odd[0] = 0;
+            acc_add<kAccLimbs, kAccLimbs>(total, even);
+            acc_add<kAccLimbs, kAccLimbs>(total, odd);
+            // the scratch is ring memory: order these accesses before the bulk copy that refills it
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            __syncwarp();
         }
 
         template <int P>
@@ -146,10 +232,6 @@ namespace gzk
                 const uint64_t c_begin = static_cast<uint64_t>(tile) * a.tile_rows;
                 const uint64_t c_end = c_begin + a.tile_rows < a.len ? c_begin + a.tile_rows : a.len;
 
-                WideAcc64 acc[P];
-#pragma unroll
-                for (int p = 0; p < P; ++p) acc[p].clear();
-
                 if (kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT)
                 {
                     const unsigned char* base = static_cast<const unsigned char*>(col) + c_begin * 32;
@@ -184,6 +266,18 @@ namespace gzk
                         for (; issued < kStages - 1 && issued < chunks; ++issued) issue(issued);
                     issued = __shfl_sync(0xffffffffu, issued, 0);
                     bool ok = true;
+                    const uint32_t g = lane >> 2, t = lane & 3;
+                    int32_t c[P][2][4][4];
+                    uint32_t total[P][kAccLimbs];
+#pragma unroll
+                    for (int p = 0; p < P; ++p)
+                    {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) (&c[p][0][0][0])[i] = 0;
+#pragma unroll
+                        for (int i = 0; i < kAccLimbs; ++i) total[p][i] = 0;
+                    }
+                    uint32_t steps_unfolded = 0;
                     for (uint32_t ch = 0; ch < chunks; ++ch)
                     {
                         if (issued < chunks)
@@ -199,19 +293,48 @@ namespace gzk
                             ok = false;
                             break;
                         }
-                        const unsigned char* stage = ring + static_cast<size_t>(slot) * slot_bytes(P);
+                        unsigned char* stage = ring + static_cast<size_t>(slot) * slot_bytes(P);
                         const uint64_t row0 = static_cast<uint64_t>(ch) * kChunkRows;
                         const uint32_t rows_here = static_cast<uint32_t>(rows - row0 < kChunkRows ? rows - row0 : kChunkRows);
-#pragma unroll 1
-                        for (uint32_t r = lane; r < rows_here; r += 32)
+#pragma unroll
+                        for (uint32_t step = 0; step < kChunkRows / 32; ++step)
                         {
-                            const Fr f = load_fr_shared(stage + r * 32);
+                            if (step * 32 >= rows_here) break;
+                            uint32_t fb[2][4];
+                            load_rows_transposed(stage + step * 1024, g, t, fb);
+                            if (rows_here < (step + 1) * 32)
+                            {
+                                // a ragged last chunk: the rows behind it hold older data, their bytes count as zero
+#pragma unroll
+                                for (int h = 0; h < 2; ++h)
+                                {
+                                    uint32_t keep = 0;
+#pragma unroll
+                                    for (int q = 0; q < 4; ++q)
+                                        if (step * 32 + 16 * h + t + 4 * q < rows_here) keep |= 0xffu << (8 * q);
+#pragma unroll
+                                    for (int j = 0; j < 4; ++j) fb[h][j] &= keep;
+                                }
+                            }
 #pragma unroll
                             for (int p = 0; p < P; ++p)
                             {
-                                const Fr w = load_fr_shared(stage + static_cast<size_t>(1 + p) * kChunkBytes + r * 32);
-                                acc[p].template mac<8>(w.l, f.l);
+                                uint32_t wa[2][4];
+                                load_rows_transposed(stage + static_cast<size_t>(1 + p) * kChunkBytes + step * 1024, g, t, wa);
+#pragma unroll
+                                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                                    for (int nt = 0; nt < 4; ++nt)
+                                        mma_u8(c[p][mt][nt], wa[0][2 * mt], wa[0][2 * mt + 1], wa[1][2 * mt], wa[1][2 * mt + 1], fb[0][nt], fb[1][nt]);
                             }
+                            ++steps_unfolded;
+                        }
+                        if (steps_unfolded + kChunkRows / 32 > kStepsPerFold || ch + 1 == chunks)
+                        {
+                            // the slot just read is this warp's until the next chunk is requested into it
+#pragma unroll
+                            for (int p = 0; p < P; ++p) fold_byte_products(c[p], stage, lane, total[p]);
+                            steps_unfolded = 0;
                         }
                         __syncwarp();  // the slot may be refilled from the next iteration on
                     }
@@ -225,8 +348,22 @@ namespace gzk
                         return;
                     }
                     ring_pos += chunks;
+                    if (lane == 0)
+                    {
+#pragma unroll
+                        for (int p = 0; p < P; ++p)
+                        {
+                            uint32_t* dst = a.partial + ((static_cast<uint64_t>(tile) * P + p) * a.k_count + k) * kAccLimbs;
+#pragma unroll
+                            for (int i = 0; i < kAccLimbs; ++i) dst[i] = total[p][i];
+                        }
+                    }
+                    continue;
                 }
-                else if (kind == GZK_KIND_U32)
+                WideAcc64 acc[P];
+#pragma unroll
+                for (int p = 0; p < P; ++p) acc[p].clear();
+                if (kind == GZK_KIND_U32)
                 {
                     const uint32_t* values = static_cast<const uint32_t*>(col);
                     for (uint64_t c = c_begin + lane; c < c_end; c += 32)
