@@ -57,11 +57,15 @@ namespace gzk
         // Every wait is bounded; a wait that gives up raises the status word and the
         // kernel returns.
         constexpr int kStages = 2;
-        constexpr int kChunkRows = 64;
-        constexpr int kChunkBytes = kChunkRows * 32;
+        // Rows per chunk: 128 at one evaluation point (the per-chunk bookkeeping - the wait, the next request -
+        // is a sixth of the instructions at 64), 64 at two, where 128 would leave room for two CTAs per SM only and
+        // the small-integer columns of the same launch need the warps.  Tiles are whole chunks of either size.
+        constexpr int kChunkRows = 128;
+        __host__ __device__ constexpr int chunk_rows(int p) { return p == 1 ? kChunkRows : kChunkRows / 2; }
+        __host__ __device__ constexpr int chunk_bytes(int p) { return chunk_rows(p) * 32; }
         constexpr int kWarps = kThreads / 32;
         // a ring slot holds the column chunk and, behind it, one weight chunk per rotation
-        __host__ __device__ constexpr size_t slot_bytes(int p) { return static_cast<size_t>(1 + p) * kChunkBytes; }
+        __host__ __device__ constexpr size_t slot_bytes(int p) { return static_cast<size_t>(1 + p) * chunk_bytes(p); }
         __host__ __device__ constexpr size_t ring_bytes(int p) { return static_cast<size_t>(kWarps) * kStages * slot_bytes(p); }
         __host__ __device__ constexpr size_t smem_bytes(int p) { return ring_bytes(p) + static_cast<size_t>(kWarps) * kStages * sizeof(uint64_t); }
         constexpr uint32_t kWaitLimit = 1u << 22;
@@ -236,14 +240,15 @@ namespace gzk
                 {
                     const unsigned char* base = static_cast<const unsigned char*>(col) + c_begin * 32;
                     const uint64_t rows = c_end > c_begin ? c_end - c_begin : 0;
-                    const uint32_t chunks = static_cast<uint32_t>((rows + kChunkRows - 1) / kChunkRows);
+                    constexpr int kRows = chunk_rows(P);
+                    const uint32_t chunks = static_cast<uint32_t>((rows + kRows - 1) / kRows);
                     auto issue = [&](uint32_t j) {
                         // chunk j of this unit goes to ring slot (ring_pos + j) % kStages: the column
                         // rows, then for every rotation the weights those rows meet (the weight index
                         // wraps around the domain at most once inside a chunk)
                         const uint32_t slot = (ring_pos + j) % kStages;
-                        const uint64_t row0 = static_cast<uint64_t>(j) * kChunkRows;
-                        const uint32_t rows_j = static_cast<uint32_t>(rows - row0 < kChunkRows ? rows - row0 : kChunkRows);
+                        const uint64_t row0 = static_cast<uint64_t>(j) * kRows;
+                        const uint32_t rows_j = static_cast<uint32_t>(rows - row0 < kRows ? rows - row0 : kRows);
                         const uint32_t bytes = rows_j * 32;
                         const uint32_t bar = smem_u32(bars + slot);
                         unsigned char* dst = ring + static_cast<size_t>(slot) * slot_bytes(P);
@@ -256,7 +261,7 @@ namespace gzk
                             const uint64_t w0 = (c_begin + row0 - a.rot[p]) & a.mask;
                             const uint64_t until_wrap = a.mask + 1 - w0;
                             const uint32_t first = static_cast<uint32_t>(until_wrap < rows_j ? until_wrap : rows_j);
-                            unsigned char* wdst = dst + static_cast<size_t>(1 + p) * kChunkBytes;
+                            unsigned char* wdst = dst + static_cast<size_t>(1 + p) * chunk_bytes(P);
                             bulk_load(smem_u32(wdst), a.weights + w0, first * 32, bar);
                             if (first < rows_j) bulk_load(smem_u32(wdst + first * 32), a.weights, (rows_j - first) * 32, bar);
                         }
@@ -294,10 +299,10 @@ namespace gzk
                             break;
                         }
                         unsigned char* stage = ring + static_cast<size_t>(slot) * slot_bytes(P);
-                        const uint64_t row0 = static_cast<uint64_t>(ch) * kChunkRows;
-                        const uint32_t rows_here = static_cast<uint32_t>(rows - row0 < kChunkRows ? rows - row0 : kChunkRows);
+                        const uint64_t row0 = static_cast<uint64_t>(ch) * kRows;
+                        const uint32_t rows_here = static_cast<uint32_t>(rows - row0 < kRows ? rows - row0 : kRows);
 #pragma unroll
-                        for (uint32_t step = 0; step < kChunkRows / 32; ++step)
+                        for (uint32_t step = 0; step < kRows / 32; ++step)
                         {
                             if (step * 32 >= rows_here) break;
                             uint32_t fb[2][4];
@@ -320,7 +325,7 @@ namespace gzk
                             for (int p = 0; p < P; ++p)
                             {
                                 uint32_t wa[2][4];
-                                load_rows_transposed(stage + static_cast<size_t>(1 + p) * kChunkBytes + step * 1024, g, t, wa);
+                                load_rows_transposed(stage + static_cast<size_t>(1 + p) * chunk_bytes(P) + step * 1024, g, t, wa);
 #pragma unroll
                                 for (int mt = 0; mt < 2; ++mt)
 #pragma unroll
@@ -329,7 +334,7 @@ namespace gzk
                             }
                             ++steps_unfolded;
                         }
-                        if (steps_unfolded + kChunkRows / 32 > kStepsPerFold || ch + 1 == chunks)
+                        if (steps_unfolded + kRows / 32 > kStepsPerFold || ch + 1 == chunks)
                         {
                             // the slot just read is this warp's until the next chunk is requested into it
 #pragma unroll
