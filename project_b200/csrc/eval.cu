@@ -140,7 +140,7 @@ namespace gzk
                          : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
                          : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
         }
-        // Adds sum_ab C[a][b] 2^(8(a+b)) to `total` (every lane ends with the same 17 limbs) and clears C.
+        // Adds sum_ab C[a][b] 2^(8(a+b)) to `total` (17 limbs in shared memory, kept by lane 0) and clears C.
         // `scratch`: 4 KiB of this warp's shared memory that nothing else uses meanwhile.
         __device__ __forceinline__ void fold_byte_products(int32_t c[2][4][4], unsigned char* scratch, uint32_t lane, uint32_t* total)
         {
@@ -193,17 +193,26 @@ namespace gzk
             }
             even[16] = 0;
             odd[0] = 0;
-            acc_add<kAccLimbs, kAccLimbs>(total, even);
-            acc_add<kAccLimbs, kAccLimbs>(total, odd);
+            if (lane == 0)
+            {
+                acc_add<kAccLimbs, kAccLimbs>(even, odd);
+                uint32_t sum[kAccLimbs];
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) sum[i] = total[i];
+                acc_add<kAccLimbs, kAccLimbs>(sum, even);
+#pragma unroll
+                for (int i = 0; i < kAccLimbs; ++i) total[i] = sum[i];
+            }
             // the scratch is ring memory: order these accesses before the bulk copy that refills it
             asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             __syncwarp();
         }
 
         template <int P>
-        __global__ void __launch_bounds__(kThreads) eval_partial_kernel(EvalArgs a)
+        __global__ void __launch_bounds__(kThreads, P == 2 ? 4 : 3) eval_partial_kernel(EvalArgs a)
         {
             extern __shared__ __align__(128) unsigned char smem[];
+            __shared__ uint32_t totals[kWarps][P][kAccLimbs];  // running sum of a field-element unit, per warp (lane 0's)
             const uint32_t lane = threadIdx.x & 31;
             const uint32_t warp_in_cta = threadIdx.x >> 5;
             unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * kStages * slot_bytes(P);
@@ -273,14 +282,17 @@ namespace gzk
                     bool ok = true;
                     const uint32_t g = lane >> 2, t = lane & 3;
                     int32_t c[P][2][4][4];
-                    uint32_t total[P][kAccLimbs];
+                    uint32_t(*total)[kAccLimbs] = totals[warp_in_cta];
 #pragma unroll
                     for (int p = 0; p < P; ++p)
                     {
 #pragma unroll
                         for (int i = 0; i < 32; ++i) (&c[p][0][0][0])[i] = 0;
+                        if (lane == 0)
+                        {
 #pragma unroll
-                        for (int i = 0; i < kAccLimbs; ++i) total[p][i] = 0;
+                            for (int i = 0; i < kAccLimbs; ++i) total[p][i] = 0;
+                        }
                     }
                     uint32_t steps_unfolded = 0;
                     for (uint32_t ch = 0; ch < chunks; ++ch)
