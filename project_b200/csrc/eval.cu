@@ -44,7 +44,13 @@ namespace gzk
             int* status;              // raised when a bounded wait gives up
             uint32_t wait_limit;      // polls a wait on a chunk may take before it gives up
             uint32_t skip_copies;     // stall injection (gzk_debug_inject_eval_stall): announce the chunks but issue no copy
+            const uint32_t* k_map;    // the columns this launch takes (indices into cols), or null: all k_count of them
+            uint32_t k_mapped;        // entries of k_map (k_count without a map)
         };
+        // Which kinds of columns a launch takes.  Field-element columns run through the shared-memory ring and the
+        // tensor cores, small-integer columns through plain loads and the integer pipe; these want many resident warps
+        // and no shared memory, so a call with both kinds launches one kernel for each over the same partial buffer.
+        enum { kAllKinds = 0, kFieldKinds = 1, kIntegerKinds = 2 };
 
         // ---- per-warp TMA ring -------------------------------------------------------
         // Both operands of the inner product reach the arithmetic through shared memory:
@@ -208,16 +214,17 @@ namespace gzk
             __syncwarp();
         }
 
-        template <int P>
-        __global__ void __launch_bounds__(kThreads, P == 2 ? 4 : 3) eval_partial_kernel(EvalArgs a)
+        template <int P, int MODE>
+        __global__ void __launch_bounds__(kThreads, MODE == kIntegerKinds ? (P == 2 ? 4 : 5) : (P == 2 ? 4 : 3)) eval_partial_kernel(EvalArgs a)
         {
+            constexpr bool kHasField = MODE != kIntegerKinds;
             extern __shared__ __align__(128) unsigned char smem[];
-            __shared__ uint32_t totals[kWarps][P][kAccLimbs];  // running sum of a field-element unit, per warp (lane 0's)
+            __shared__ uint32_t totals[kHasField ? kWarps : 1][P][kAccLimbs];  // running sum of a field-element unit, per warp (lane 0's)
             const uint32_t lane = threadIdx.x & 31;
             const uint32_t warp_in_cta = threadIdx.x >> 5;
             unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * kStages * slot_bytes(P);
             uint64_t* bars = reinterpret_cast<uint64_t*>(smem + ring_bytes(P)) + warp_in_cta * kStages;
-            if (lane == 0)
+            if (kHasField && lane == 0)
             {
 #pragma unroll
                 for (int st = 0; st < kStages; ++st) mbar_init(smem_u32(bars + st), 1);
@@ -228,7 +235,7 @@ namespace gzk
 
             const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
             const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
-            const uint64_t units = static_cast<uint64_t>(a.tiles) * a.k_count;
+            const uint64_t units = static_cast<uint64_t>(a.tiles) * a.k_mapped;
             uint32_t ring_pos = 0;  // chunks this warp has pushed through the ring so far
 
             // Units are tile-major and dealt round-robin: at any moment the grid works on a window of
@@ -238,14 +245,15 @@ namespace gzk
             // vector, far larger than L2, would cycle through the cache once per column.)
             for (uint64_t u = warp; u < units; u += warps)
             {
-                const uint32_t tile = static_cast<uint32_t>(u / a.k_count);
-                const uint32_t k = static_cast<uint32_t>(u - static_cast<uint64_t>(tile) * a.k_count);
+                const uint32_t tile = static_cast<uint32_t>(u / a.k_mapped);
+                const uint32_t slot_of_k = static_cast<uint32_t>(u - static_cast<uint64_t>(tile) * a.k_mapped);
+                const uint32_t k = a.k_map != nullptr ? a.k_map[slot_of_k] : slot_of_k;
                 const void* col = a.cols[k];
                 const int kind = a.kinds[k];
                 const uint64_t c_begin = static_cast<uint64_t>(tile) * a.tile_rows;
                 const uint64_t c_end = c_begin + a.tile_rows < a.len ? c_begin + a.tile_rows : a.len;
 
-                if (kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT)
+                if (kHasField && (kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT))
                 {
                     const unsigned char* base = static_cast<const unsigned char*>(col) + c_begin * 32;
                     const uint64_t rows = c_end > c_begin ? c_end - c_begin : 0;
@@ -377,6 +385,9 @@ namespace gzk
                     }
                     continue;
                 }
+                if constexpr (MODE != kFieldKinds)
+                {
+                if (kind == GZK_KIND_FR || kind == GZK_KIND_FR_MONT) continue;  // not this launch's
                 WideAcc64 acc[P];
 #pragma unroll
                 for (int p = 0; p < P; ++p) acc[p].clear();
@@ -468,6 +479,7 @@ namespace gzk
                         for (int i = 0; i < kAccLimbs; ++i) dst[i] = sum[i];
                     }
                 }
+                }
             }
         }
 
@@ -475,45 +487,66 @@ namespace gzk
         // device; also opts the kernels into their dynamic shared-memory size, which is a
         // per-device attribute).  Allocates nothing.
         constexpr int kOptInDevices = 64;
-        int blocks_per_sm(int p)
+        template <int P, int MODE>
+        int occupancy_of()
         {
-            static std::atomic<int> per_device[kOptInDevices][3];  // zero-initialised; contexts on several host threads may race to fill a slot with the same value
+            const size_t dynamic = MODE == kIntegerKinds ? 0 : smem_bytes(P);
+            if (dynamic != 0) cudaFuncSetAttribute(eval_partial_kernel<P, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(dynamic));
+            int nb = 0;
+            const cudaError_t err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<P, MODE>, kThreads, dynamic);
+            return (err == cudaSuccess && nb > 0) ? nb : 1;
+        }
+        int blocks_per_sm(int p, int mode = kAllKinds)
+        {
+            static std::atomic<int> per_device[kOptInDevices][3][3];  // zero-initialised; contexts on several host threads may race to fill a slot with the same value
             int device = 0;
             cudaGetDevice(&device);
-            std::atomic<int>* cached = per_device[device >= 0 && device < kOptInDevices ? device : 0];
-            if (device < 0 || device >= kOptInDevices || cached[p].load(std::memory_order_relaxed) == 0)
+            const bool cacheable = device >= 0 && device < kOptInDevices;
+            std::atomic<int>& cached = per_device[cacheable ? device : 0][p][mode];
+            if (!cacheable || cached.load(std::memory_order_relaxed) == 0)
             {
-                int nb = 0;
-                cudaError_t err;
+                int nb = 1;
                 if (p == 2)
-                {
-                    cudaFuncSetAttribute(eval_partial_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes(2)));
-                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<2>, kThreads, smem_bytes(2));
-                }
+                    nb = mode == kFieldKinds ? occupancy_of<2, kFieldKinds>() : mode == kIntegerKinds ? occupancy_of<2, kIntegerKinds>() : occupancy_of<2, kAllKinds>();
                 else
-                {
-                    cudaFuncSetAttribute(eval_partial_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes(1)));
-                    err = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, eval_partial_kernel<1>, kThreads, smem_bytes(1));
-                }
-                cached[p].store((err == cudaSuccess && nb > 0) ? nb : 1, std::memory_order_relaxed);
+                    nb = mode == kFieldKinds ? occupancy_of<1, kFieldKinds>() : mode == kIntegerKinds ? occupancy_of<1, kIntegerKinds>() : occupancy_of<1, kAllKinds>();
+                cached.store(nb, std::memory_order_relaxed);
             }
-            return cached[p].load(std::memory_order_relaxed);
+            return cached.load(std::memory_order_relaxed);
         }
 
         // Stall injection for tests of the bounded waits (gzk_debug_inject_eval_stall).
         std::atomic<int> g_inject_stall{0};
         constexpr uint32_t kInjectedWaitLimit = 1u << 10;
 
-        void launch_eval_partial(cudaStream_t stream, EvalArgs args, int p, unsigned blocks)
+        template <int P>
+        void launch_mode(cudaStream_t stream, const EvalArgs& args, int mode, unsigned blocks)
         {
-            blocks_per_sm(p);  // makes sure the shared-memory opt-in has happened on this device
+            if (mode == kFieldKinds)
+                eval_partial_kernel<P, kFieldKinds><<<blocks, kThreads, smem_bytes(P), stream>>>(args);
+            else if (mode == kIntegerKinds)
+                eval_partial_kernel<P, kIntegerKinds><<<blocks, kThreads, 0, stream>>>(args);
+            else
+                eval_partial_kernel<P, kAllKinds><<<blocks, kThreads, smem_bytes(P), stream>>>(args);
+        }
+        // `mode` says which columns args.k_map lists (kAllKinds without a map).  Returns the CTAs launched.
+        unsigned launch_eval_partial(cudaStream_t stream, EvalArgs args, int p, int sm_count, int mode = kAllKinds, unsigned blocks_per_sm_cap = 0)
+        {
+            const int per_sm = blocks_per_sm(p, mode);  // also makes sure the shared-memory opt-in has happened on this device
             const bool inject = g_inject_stall.load(std::memory_order_relaxed) != 0;
             args.wait_limit = inject ? kInjectedWaitLimit : kWaitLimit;
             args.skip_copies = inject ? 1u : 0u;
+            if (args.k_map == nullptr) args.k_mapped = args.k_count;
+            const uint64_t units = static_cast<uint64_t>(args.tiles) * args.k_mapped;
+            uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
+            const uint64_t max_blocks = static_cast<uint64_t>(sm_count) * (blocks_per_sm_cap != 0 && blocks_per_sm_cap < static_cast<unsigned>(per_sm) ? blocks_per_sm_cap : static_cast<unsigned>(per_sm));
+            if (blocks > max_blocks) blocks = max_blocks;
+            if (blocks == 0) return 0;
             if (p == 2)
-                eval_partial_kernel<2><<<blocks, kThreads, smem_bytes(2), stream>>>(args);
+                launch_mode<2>(stream, args, mode, static_cast<unsigned>(blocks));
             else
-                eval_partial_kernel<1><<<blocks, kThreads, smem_bytes(1), stream>>>(args);
+                launch_mode<1>(stream, args, mode, static_cast<unsigned>(blocks));
+            return static_cast<unsigned>(blocks);
         }
 
         // One CTA per (rotation, column) pair: the threads sum the per-tile partials (up to 4096 of them: a
@@ -700,7 +733,8 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     const uint32_t tiles = len == 0 ? 1 : static_cast<uint32_t>((len + tile_rows - 1) / tile_rows);
 
     // device-side tables and scratch
-    const size_t table_bytes = k_count * (sizeof(void*) + sizeof(int));
+    // column pointers, kinds, and the column indices with the field-element columns first
+    const size_t table_bytes = k_count * (sizeof(void*) + sizeof(int) + sizeof(uint32_t));
     const size_t table_padded = (table_bytes + 31) & ~static_cast<size_t>(31);
     // Host copy of the column table.  A call that reads results back ends with a synchronisation, so
     // it can stage through the context's pinned area; a call that leaves its results on the device
@@ -722,14 +756,20 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
     if ((rc = ensure_scratch(ctx, 0, table_padded + p_count * k_count * 32, &d_table)) != GZK_OK) return rc;
     const void** h_ptrs = static_cast<const void**>(h_table);
     int* h_kinds = reinterpret_cast<int*>(h_ptrs + k_count);
+    uint32_t* h_map = reinterpret_cast<uint32_t*>(h_kinds + k_count);
+    uint32_t field_columns = 0;
     for (size_t k = 0; k < k_count; ++k)
     {
         h_ptrs[k] = cols[k]->dptr;
         h_kinds[k] = cols[k]->kind;
+        if (cols[k]->kind == GZK_KIND_FR || cols[k]->kind == GZK_KIND_FR_MONT) h_map[field_columns++] = static_cast<uint32_t>(k);
     }
+    for (size_t k = 0, next = field_columns; k < k_count; ++k)
+        if (cols[k]->kind != GZK_KIND_FR && cols[k]->kind != GZK_KIND_FR_MONT) h_map[next++] = static_cast<uint32_t>(k);
     GZK_CUDA_TRY(ctx, cudaMemcpyAsync(d_table, h_table, table_bytes, cudaMemcpyHostToDevice, ctx->stream));
     const void* const* d_ptrs = static_cast<const void* const*>(d_table);
     const int* d_kinds = reinterpret_cast<const int*>(static_cast<const char*>(d_table) + k_count * sizeof(void*));
+    const uint32_t* d_map = reinterpret_cast<const uint32_t*>(d_kinds + k_count);
     Fr* d_out = dest != nullptr ? dest : reinterpret_cast<Fr*>(static_cast<char*>(d_table) + table_padded);
     if (dest != nullptr && (rc = begin_call(ctx)) != GZK_OK) return rc;
 
@@ -769,13 +809,21 @@ static int eval_batch_impl(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, s
         args.rot[1] = p_now == 2 ? rotations[p0 + 1] : 0;
         args.partial = static_cast<uint32_t*>(d_partial);
         args.status = ctx->d_status;
-        const uint64_t units = static_cast<uint64_t>(tiles) * k_count;
-        uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
-        const uint64_t max_blocks = static_cast<uint64_t>(ctx->sm_count) * blocks_per_sm(p_now);
-        if (blocks > max_blocks) blocks = max_blocks;
         {
+            // one launch per kind of column present, over the same partial buffer
             LaunchScope scope(ctx, p_now == 2 ? "eval_partial_p2" : "eval_partial_p1");
-            launch_eval_partial(ctx->stream, args, static_cast<int>(p_now), static_cast<unsigned>(blocks));
+            if (field_columns != 0)
+            {
+                args.k_map = d_map;
+                args.k_mapped = field_columns;
+                launch_eval_partial(ctx->stream, args, static_cast<int>(p_now), ctx->sm_count, kFieldKinds);
+            }
+            if (field_columns != k_count)
+            {
+                args.k_map = d_map + field_columns;
+                args.k_mapped = static_cast<uint32_t>(k_count) - field_columns;
+                launch_eval_partial(ctx->stream, args, static_cast<int>(p_now), ctx->sm_count, kIntegerKinds);
+            }
         }
         GZK_CUDA_TRY(ctx, cudaGetLastError());
         const uint32_t outs = p_now * static_cast<uint32_t>(k_count);
@@ -959,11 +1007,8 @@ extern "C" int gzk_eval_batch_static(int device, void* stream, const void* const
     args.rot[1] = p_count == 2 ? rotations[1] : 0;
     args.partial = reinterpret_cast<uint32_t*>(scratch + kStaticPartialOffset);
     args.status = reinterpret_cast<int*>(scratch + kStaticStatusOffset);
-    const uint64_t units = static_cast<uint64_t>(tiles) * k_count;
-    uint64_t blocks = (units + (kThreads / 32) - 1) / (kThreads / 32);
-    const uint64_t max_blocks = static_cast<uint64_t>(g_static_sms[device]) * 2;
-    if (blocks > max_blocks) blocks = max_blocks;
-    launch_eval_partial(s, args, static_cast<int>(p_count), static_cast<unsigned>(blocks));
+    args.k_map = nullptr;  // at most two CTAs per SM
+    launch_eval_partial(s, args, static_cast<int>(p_count), g_static_sms[device], kAllKinds, 2);
     if (cudaGetLastError() != cudaSuccess) return static_fail(err, err_cap, GZK_E_CUDA, "eval_batch_static: kernel launch failed");
     const uint32_t outs = static_cast<uint32_t>(p_count * k_count);
     eval_finish_kernel<<<outs, finish_threads(tiles), 0, s>>>(args.partial, args.kinds, tiles, static_cast<uint32_t>(p_count),
