@@ -380,20 +380,26 @@ def main():
     achieved = work[0] / (eval_ms * 1e-3) / 1e9 if eval_ms > 0 else 0.0
     mac_peak = measure_mac_peak(local_rank, 2, 20000)  # 8x8-limb products per second
     limb_rate = work[1] / (eval_ms * 1e-3) if eval_ms > 0 else 0.0
+    field_terms = max(0, (work[1] - 8 * work[2]) // 56)  # terms of field-element columns (64 limb products each; 8 for the others)
     roofline = {
-        "bound": "integer_pipe",
-        "kernel": "eval_partial_kernel (packed evaluation: commit tau-evaluations, quotient and opening evaluations; all launches of one proof, each timed by itself)",
+        "bound": "hbm",
+        "kernel": "eval_partial_kernel / eval_integers_kernel (packed evaluation: commit tau-evaluations, quotient and opening evaluations; "
+                  "all launches of one proof, each timed by itself)",
         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak if peak else None,
-        "traffic": (537.3e6 + 4.2e6) / 536.9e6 * work[0] / max(1, eval_launches),
+        "traffic": (537.0e6 + 4.5e6) / 536.9e6 * work[0] / max(1, eval_launches),
         "traffic_note": "average launch of this run: its algorithmic bytes times the ratio ncu measured on a 2^22-row, 3-column launch "
                         "(dram read+write 541.5e6 against 536.9e6 algorithmic; traffic grows in proportion to columns x rows); "
                         "profiles/eval_partial_kernel_2p22_rows.md",
         "peak_source": peak_src, "launches": eval_launches, "avg_launch_ms": eval_ms / max(1, eval_launches), "bytes_per_step": int(work[0]),
-        "integer_pipe": {"achieved_limb_products_per_s": limb_rate, "measured_peak_limb_products_per_s": mac_peak * 64,
-                         "frac": limb_rate / (mac_peak * 64) if mac_peak else None,
-                         "note": "the binding roof: 64 32x32-bit products per term of a field-element column, 8 for a small-integer column (I64 values that fit one limb, U32); "
-                                 "at two evaluation points per element the integer pipe saturates at about a third of the HBM rate; "
-                                 "peak measured in this run on register operands"},
+        "tensor": {"u8_products_per_s": field_terms * 1024 / (eval_ms * 1e-3) if eval_ms > 0 else 0.0,
+                   "note": "field-element columns: the 32 x 32 byte products of a row, summed over the rows, are one matrix product "
+                           "(mma.sync m16n8k32 u8 -> s32); the tensor pipe is 28-33 % busy in the ncu capture, memory and the byte "
+                           "transposition bound the kernel"},
+        "integer_pipe": {"limb_products_per_s_if_on_the_integer_pipe": limb_rate, "measured_peak_limb_products_per_s": mac_peak * 64,
+                         "ratio": limb_rate / (mac_peak * 64) if mac_peak else None,
+                         "note": "what the same sums would need of the integer pipe (64 32x32-bit products per term of a field-element column, 8 for a "
+                                 "small-integer column) against its measured peak: that pipe bounded this kernel at 0.48 before the field-element "
+                                 "columns moved to the tensor cores; it still bounds the weight, scan and matrix kernels"},
     }
 
     # ---- end to end: the feature matrix and the parameters travel from the host every step ---------

@@ -4,11 +4,16 @@
 // evaluation of the prover.
 //
 // Arithmetic: weights are in Montgomery form, column values in canonical form.
-// Each lane accumulates the plain 512-bit integer products w~[c] * f[c] in a
-// 17-limb register accumulator without any modular reduction (2^32 terms fit), so
-// a term costs one 8x8-limb product (64 wide multiply-adds) instead of a full
-// Montgomery multiplication (128).  One reduction per (tile, column) pair follows
-// in a second, tiny kernel.
+// A unit accumulates the plain 512-bit integer products w~[c] * f[c] into a 17-limb
+// sum without any modular reduction (2^32 terms fit); one reduction per (tile, column)
+// pair follows in a second, tiny kernel.  Field-element columns form the products on
+// the tensor cores: with the 32 bytes of w~ and of f as the two factors, the byte
+// products summed over the rows are a 32 x 32 matrix product whose contraction index
+// is the row (mma.sync m16n8k32, u8 x u8 -> s32; eight per 32 rows), and the sum is
+// sum_ab C[a][b] 2^(8(a+b)) - the integer pipe needs 64 wide multiply-adds per row for
+// the same sum and was the bound of this kernel.  Small-integer columns take the same
+// route in groups of four at two evaluation points, and the integer pipe (8 products
+// per row) at one.
 //
 // Work decomposition: the row range is cut into tiles; a unit of work is one
 // (tile, column) pair, enumerated tile-major so that the warps of a CTA stream
@@ -55,12 +60,11 @@ namespace gzk
 
         // ---- per-warp TMA ring -------------------------------------------------------
         // Both operands of the inner product reach the arithmetic through shared memory:
-        // lane 0 of each warp streams 2 KiB chunks (64 rows) of the column, and the
-        // matching 64 weights for every rotation, into a private ring with
+        // lane 0 of each warp streams chunks (128 or 64 rows) of the column, and the
+        // matching weights for every rotation, into a private ring with
         // cp.async.bulk, one chunk ahead of the arithmetic; the warp waits on the chunk's
         // mbarrier.  Column values (read once) bypass L1 entirely, the weights come from
-        // L2, and the multiply-accumulate loop sees only short shared-memory latencies
-        // (a global load per term in the loop halves the throughput of this kernel).
+        // L2, and the arithmetic sees only short shared-memory latencies.
         // Every wait is bounded; a wait that gives up raises the status word and the
         // kernel returns.
         constexpr int kStages = 2;
