@@ -309,3 +309,67 @@ def test_contexts_ordered_on_the_device(be):
     want = ora.eval_rotations(col_host[None, :, :], ora.bary_weights(x, n), (0, 1))
     assert np.array_equal(got.reshape(2, 32), want.reshape(2, 32))
     side.close()
+
+
+@pytest.mark.parametrize("length", [512, 389])
+@pytest.mark.parametrize("rots", [(0, 1), (3, 500)])
+def test_eval_groups_of_integer_columns_on_the_tensor_path(be, length, rots):
+    """Seven and nine small-integer columns (I64 with negative and extreme values, U32 among them) beside two
+    field-element columns at two evaluation points: whole groups of four integer columns, a group of three, and a
+    column left over for the integer pipe, all against the oracle (eval_backend.cpp:191-444 semantics:
+    FieldElement::from_signed for negative entries)."""
+    from project_b200 import KIND_FR, KIND_FR_MONT, KIND_I64, KIND_U32
+
+    rng = np.random.default_rng(41)
+    log2n, n = 9, 512
+    w = be.bary_weights(log2n, fr_array([987654321]))
+    w_host = w.download()
+    for integer_columns in (7, 9):
+        cols, bufs = [], []
+        for i in range(integer_columns):
+            if i % 3 == 2:
+                u32 = rng.integers(0, 1 << 32, size=n, dtype=np.uint64).astype(np.uint32)
+                u32[:2] = [0, 0xFFFFFFFF]
+                bufs.append(be.upload(u32, KIND_U32))
+                cols.append(fr_array([int(v) for v in u32]))
+            else:
+                i64 = rng.integers(-(1 << 50), 1 << 50, size=n, dtype=np.int64)
+                i64[:5] = [0, -1, 1, np.iinfo(np.int64).min + 1, np.iinfo(np.int64).max]
+                bufs.append(be.upload(i64, KIND_I64))
+                cols.append(ora.fr_from_i64(i64))
+        for kind in (KIND_FR, KIND_FR_MONT):
+            fr = rand_fr_bytes(rng, n)
+            bufs.insert(1, be.upload(fr, kind))
+            cols.insert(1, fr)
+        got = be.eval_batch(bufs, length, log2n, w, rots)
+        padded = np.stack(cols).copy()
+        padded[:, length:] = 0  # the rows behind `length` are not part of the columns
+        want = ora.eval_rotations(padded, w_host, rots)
+        assert np.array_equal(got, want)
+        for b in bufs:
+            b.free()
+    w.free()
+
+
+def test_eval_long_units_fold_their_byte_products_in_time(be):
+    """With many columns in one call the tile count is capped and a (tile, column) unit grows past 32768 rows, the
+    most the s32 byte products of the tensor path can take before they are folded into the running sum.  600 aliases
+    of one column of 2^25 rows at two points must all evaluate to what a single-column call gives (short units, and
+    for the integer column the integer-pipe kernel): a size-independent check of the mid-unit fold of both tensor
+    kernels."""
+    from project_b200 import KIND_I64
+
+    log2n, n = 25, 1 << 25
+    w = be.bary_weights(log2n, fr_array([(1 << 200) + 12345]))
+    field_column = be.bary_weights(log2n, fr_array([(1 << 100) + 7]))  # any 2^25 field elements will do
+    rng = np.random.default_rng(3)
+    values = rng.integers(-(1 << 45), 1 << 45, size=n, dtype=np.int64)
+    integer_column = be.upload(values, KIND_I64)
+    for column in (field_column, integer_column):
+        single = be.eval_batch([column], n, log2n, w, (0, 1))
+        many = be.eval_batch([column] * 600, n, log2n, w, (0, 1))
+        assert many.shape == (2, 600, 32)
+        assert np.array_equal(many, np.broadcast_to(single, many.shape))
+    integer_column.free()
+    field_column.free()
+    w.free()
