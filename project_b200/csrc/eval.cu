@@ -776,6 +776,130 @@ namespace gzk
             }
         }
 
+        // ---- weighted column sums of a row-major small-integer matrix (gzk_fold_rows) -----------
+        // out[j] = sum_i w[i] * M[i][j] is the packed evaluation of the matrix' columns, and four adjacent I64 columns
+        // of a row are 32 contiguous bytes - the layout the group kernel wants of its four columns.  A unit is
+        // (tile of rows, eight adjacent columns): two groups share one transposition of the weights.
+        constexpr int kFoldGroups = 2;
+        __host__ __device__ constexpr size_t fold_stage_bytes() { return static_cast<size_t>(kFoldGroups + 1) * kIntChunkRows * 32; }
+        __host__ __device__ constexpr size_t fold_smem_bytes() { return static_cast<size_t>(kWarps) * 2 * fold_stage_bytes(); }
+
+        __global__ void __launch_bounds__(kThreads, 3)
+            fold_rows_groups_kernel(const unsigned char* matrix, const unsigned char* weights, uint64_t row_count, uint32_t cols, uint64_t tile_rows,
+                                    uint32_t tiles, uint32_t* partial)
+        {
+            extern __shared__ __align__(128) unsigned char smem[];
+            __shared__ IntegerScratch scratch_of[kWarps];
+            __shared__ uint32_t totals[kWarps][kFoldGroups][kGroupColumns][kAccLimbs];
+            const uint32_t lane = threadIdx.x & 31;
+            const uint32_t warp_in_cta = threadIdx.x >> 5;
+            const uint32_t g = lane >> 2, t = lane & 3;
+            IntegerScratch& scratch = scratch_of[warp_in_cta];
+            unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * 2 * fold_stage_bytes();
+            const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+            const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
+            const uint32_t octets = cols / (kFoldGroups * kGroupColumns);
+            const uint64_t units = static_cast<uint64_t>(tiles) * octets;
+            const uint64_t row_bytes = static_cast<uint64_t>(cols) * 8;
+            for (uint64_t u = warp; u < units; u += warps)
+            {
+                const uint32_t tile = static_cast<uint32_t>(u / octets);
+                const uint32_t octet = static_cast<uint32_t>(u - static_cast<uint64_t>(tile) * octets);
+                const uint64_t c_begin = static_cast<uint64_t>(tile) * tile_rows;
+                const uint64_t c_end = c_begin + tile_rows < row_count ? c_begin + tile_rows : row_count;
+                const uint64_t rows = c_end > c_begin ? c_end - c_begin : 0;
+                const uint32_t chunks = static_cast<uint32_t>((rows + kIntChunkRows - 1) / kIntChunkRows);
+                if (lane < kFoldGroups * kGroupColumns)
+                {
+#pragma unroll
+                    for (int i = 0; i < kAccLimbs; ++i) totals[warp_in_cta][lane / kGroupColumns][lane % kGroupColumns][i] = 0;
+                }
+                int32_t cv[kFoldGroups][2][4][4], cs[kFoldGroups][2][4];
+#pragma unroll
+                for (int gi = 0; gi < kFoldGroups; ++gi)
+                {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) (&cv[gi][0][0][0])[i] = 0;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) (&cs[gi][0][0])[i] = 0;
+                }
+                auto request = [&](uint32_t chunk) {
+                    unsigned char* stage = ring + static_cast<size_t>(chunk & 1) * fold_stage_bytes();
+                    const uint64_t row0 = c_begin + static_cast<uint64_t>(chunk) * kIntChunkRows;
+                    const uint64_t left = c_end - row0;
+                    // the eight columns of a row are 64 contiguous bytes: four pieces, two per group
+#pragma unroll
+                    for (int i = 0; i < kIntChunkRows * 4 / 32; ++i)
+                    {
+                        const uint32_t piece = lane + 32 * i, row = piece >> 2, part = piece & 3;
+                        const bool inside = row < left;
+                        const unsigned char* src = inside ? matrix + (row0 + row) * row_bytes + static_cast<uint64_t>(octet) * 64 + part * 16 : matrix;
+                        copy16(stage + (part >> 1) * (kIntChunkRows * 32) + row * 32 + (part & 1) * 16, src, inside ? 16u : 0u);
+                    }
+#pragma unroll
+                    for (int i = 0; i < kIntChunkRows * 2 / 32; ++i)
+                    {
+                        const uint32_t piece = lane + 32 * i, row = piece >> 1;
+                        const bool inside = row < left;
+                        const unsigned char* src = inside ? weights + (row0 + row) * 32 + (piece & 1) * 16 : weights;
+                        copy16(stage + kFoldGroups * (kIntChunkRows * 32) + piece * 16, src, inside ? 16u : 0u);
+                    }
+                };
+                if (chunks != 0) request(0);
+                asm volatile("cp.async.commit_group;" ::: "memory");
+                uint32_t steps_unfolded = 0;
+                for (uint32_t ch = 0; ch < chunks; ++ch)
+                {
+                    if (ch + 1 < chunks) request(ch + 1);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    __syncwarp();
+                    const unsigned char* stage = ring + static_cast<size_t>(ch & 1) * fold_stage_bytes();
+                    const uint64_t left = rows - static_cast<uint64_t>(ch) * kIntChunkRows;
+#pragma unroll
+                    for (uint32_t step = 0; step < kIntChunkRows / 32; ++step)
+                    {
+                        if (step * 32 >= left) break;
+                        uint32_t wa[2][4];
+                        load_rows_transposed(stage + kFoldGroups * (kIntChunkRows * 32) + step * 1024, g, t, wa);
+#pragma unroll
+                        for (int gi = 0; gi < kFoldGroups; ++gi)
+                        {
+                            uint32_t fb[2][4], sb[2];
+                            load_rows_transposed(stage + gi * (kIntChunkRows * 32) + step * 1024, g, t, fb);
+                            sb[0] = (g & 1) ? ((fb[0][3] >> 7) & 0x01010101u) : 0u;  // word 1 of a column ends in its sign
+                            sb[1] = (g & 1) ? ((fb[1][3] >> 7) & 0x01010101u) : 0u;
+#pragma unroll
+                            for (int mt = 0; mt < 2; ++mt)
+                            {
+#pragma unroll
+                                for (int nt = 0; nt < 4; ++nt)
+                                    mma_u8(cv[gi][mt][nt], wa[0][2 * mt], wa[0][2 * mt + 1], wa[1][2 * mt], wa[1][2 * mt + 1], fb[0][nt], fb[1][nt]);
+                                mma_u8(cs[gi][mt], wa[0][2 * mt], wa[0][2 * mt + 1], wa[1][2 * mt], wa[1][2 * mt + 1], sb[0], sb[1]);
+                            }
+                        }
+                        ++steps_unfolded;
+                    }
+                    if (steps_unfolded + kIntChunkRows / 32 > kStepsPerFold || ch + 1 == chunks)
+                    {
+#pragma unroll
+                        for (int gi = 0; gi < kFoldGroups; ++gi) fold_integer_group<1>(cv[gi], cs[gi], scratch, lane, totals[warp_in_cta][gi]);
+                        steps_unfolded = 0;
+                    }
+                    __syncwarp();
+                }
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
+                __syncwarp();
+                if (lane < kFoldGroups * kGroupColumns)
+                {
+                    uint32_t* dst = partial + (static_cast<uint64_t>(tile) * cols + octet * (kFoldGroups * kGroupColumns) + lane) * kAccLimbs;
+#pragma unroll
+                    for (int i = 0; i < kAccLimbs; ++i) dst[i] = totals[warp_in_cta][lane / kGroupColumns][lane % kGroupColumns][i];
+                }
+                __syncwarp();
+            }
+        }
+
         // Resident CTAs per SM of the two kernel variants on the CURRENT device (queried once per
         // device; also opts the kernels into their dynamic shared-memory size, which is a
         // per-device attribute).  Allocates nothing.
@@ -964,6 +1088,40 @@ namespace gzk
 
 namespace gzk
 {
+    // gzk_fold_rows of an I64 matrix whose column count is a multiple of eight, on the tensor cores: chooses the
+    // tiles (whole 64-row chunks; about one unit of eight columns per resident warp), returns them, and fills
+    // partial[tile][column][17] (at least tiles x cols entries; at most 1024 tiles).
+    uint32_t fold_rows_groups_tiles(gzk_ctx* ctx, size_t row_count, uint32_t cols, uint64_t* tile_rows_out)
+    {
+        int resident = 0;
+        cudaFuncSetAttribute(fold_rows_groups_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(fold_smem_bytes()));
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fold_rows_groups_kernel, kThreads, fold_smem_bytes()) != cudaSuccess || resident < 1) resident = 1;
+        const uint64_t warps = static_cast<uint64_t>(ctx->sm_count) * resident * kWarps;
+        const uint64_t octets = cols / (kFoldGroups * kGroupColumns);
+        uint64_t tiles = warps / octets;  // rounded down: one unit for (nearly) every resident warp, no second round for a few of them
+        const uint64_t max_tiles = (row_count + 4 * kIntChunkRows - 1) / (4 * kIntChunkRows);  // at least four chunks to a unit
+        if (tiles > max_tiles) tiles = max_tiles;
+        if (tiles > 1024) tiles = 1024;
+        if (tiles == 0) tiles = 1;
+        uint64_t tile_rows = (row_count + tiles - 1) / tiles;
+        tile_rows = (tile_rows + kIntChunkRows - 1) / kIntChunkRows * kIntChunkRows;
+        if (tile_rows == 0) tile_rows = kIntChunkRows;
+        *tile_rows_out = tile_rows;
+        return row_count == 0 ? 1u : static_cast<uint32_t>((row_count + tile_rows - 1) / tile_rows);
+    }
+    void launch_fold_rows_groups(gzk_ctx* ctx, const void* matrix, const Fr* weights, size_t row_count, uint32_t cols, uint64_t tile_rows, uint32_t tiles,
+                                 uint32_t* partial)
+    {
+        int resident = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, fold_rows_groups_kernel, kThreads, fold_smem_bytes()) != cudaSuccess || resident < 1) resident = 1;
+        const uint64_t units = static_cast<uint64_t>(tiles) * (cols / (kFoldGroups * kGroupColumns));
+        uint64_t blocks = (units + kWarps - 1) / kWarps;
+        const uint64_t max_blocks = static_cast<uint64_t>(ctx->sm_count) * resident;
+        if (blocks > max_blocks) blocks = max_blocks;
+        fold_rows_groups_kernel<<<static_cast<unsigned>(blocks), kThreads, fold_smem_bytes(), ctx->stream>>>(
+            static_cast<const unsigned char*>(matrix), reinterpret_cast<const unsigned char*>(weights), row_count, cols, tile_rows, tiles, partial);
+    }
+
     // For the other inner-product kernels of the library, which produce partial sums
     // in the same [tile][p][k][17] layout: sum over tiles, reduce once, write results.
     int launch_eval_finish(gzk_ctx* ctx, const uint32_t* partial, int uniform_kind, uint32_t tiles, uint32_t k_count,

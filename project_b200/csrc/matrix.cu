@@ -10,6 +10,9 @@
 
 namespace gzk
 {
+    uint32_t fold_rows_groups_tiles(gzk_ctx* ctx, size_t row_count, uint32_t cols, uint64_t* tile_rows_out);
+    void launch_fold_rows_groups(gzk_ctx* ctx, const void* matrix, const Fr* weights, size_t row_count, uint32_t cols, uint64_t tile_rows, uint32_t tiles,
+                                 uint32_t* partial);
     int launch_eval_finish(gzk_ctx* ctx, const uint32_t* partial, int uniform_kind, uint32_t tiles, uint32_t k_count,
                            Fr* out, bool out_montgomery);
 
@@ -622,6 +625,24 @@ extern "C"
         if (out->kind != GZK_KIND_FR || out->count < cols) return fail(ctx, GZK_E_INVALID, "fold_rows: output must be an FR buffer of cols elements");
         if (cols > (1u << 24)) return fail(ctx, GZK_E_INVALID, "fold_rows: too many columns");
         GZK_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        if (matrix->kind == GZK_KIND_I64 && cols % 8 == 0 && static_cast<uint64_t>(row_count) * cols >= 65536)
+        {
+            // small-integer entries, eight adjacent columns to a unit: the byte products on the tensor cores (eval.cu)
+            uint64_t unit_rows = 0;
+            const uint32_t unit_tiles = fold_rows_groups_tiles(ctx, row_count, static_cast<uint32_t>(cols), &unit_rows);
+            void* sums = nullptr;
+            int rc = ensure_scratch(ctx, 1, static_cast<size_t>(unit_tiles) * cols * kAccLimbs * sizeof(uint32_t), &sums);
+            if (rc != GZK_OK) return rc;
+            {
+                LaunchScope scope(ctx, "fold_rows");
+                launch_fold_rows_groups(ctx, matrix->dptr, static_cast<const Fr*>(row_weights->dptr), row_count, static_cast<uint32_t>(cols), unit_rows, unit_tiles,
+                                        static_cast<uint32_t*>(sums));
+            }
+            GZK_CUDA_TRY(ctx, cudaGetLastError());
+            if ((rc = launch_eval_finish(ctx, static_cast<const uint32_t*>(sums), GZK_KIND_FR, unit_tiles, static_cast<uint32_t>(cols), static_cast<Fr*>(out->dptr), false)) != GZK_OK)
+                return rc;
+            return finish_call(ctx, "invalid input");
+        }
         const uint32_t col_chunks = static_cast<uint32_t>((cols + kThreads - 1) / kThreads);
         const uint32_t width = cols < kThreads ? static_cast<uint32_t>(cols) : kThreads;
         const uint32_t row_lanes = kThreads / width;

@@ -565,3 +565,19 @@ def test_small_integer_matrix_kernels_with_values_of_every_width(be, kind_name):
     got2 = be.linear_combination([buf, buf], coeff, rows * cols, rows * cols).download()  # every term a small integer: the three-row reduction
     one_plus_c = fr_array([(1 + int.from_bytes(bytes(c.reshape(-1)), "little")) % R])
     assert np.array_equal(got2, be.linear_combination([buf], one_plus_c, rows * cols, rows * cols).download())
+
+
+@pytest.mark.parametrize("rows,cols,row_count", [(70001, 64, 69001), (40000, 8, 40000), (2100, 256, 2049)])
+def test_fold_rows_of_small_integers_on_the_tensor_path(be, rows, cols, row_count):
+    """weighted_column_sum_native (trace.cpp:203-271) of an I64 matrix whose column count is a multiple of eight: units of
+    eight adjacent columns, several tiles of rows, a ragged last chunk and rows behind row_count that must not enter;
+    negative and extreme entries among the values."""
+    from project_b200 import KIND_FR_MONT, KIND_I64
+
+    rng = np.random.default_rng(rows + 3 * cols)
+    vals = rng.integers(-(1 << 44), 1 << 44, size=rows * cols, dtype=np.int64)
+    vals[:6] = [0, -1, np.iinfo(np.int64).max, np.iinfo(np.int64).min, 1 << 32, -(1 << 32)]
+    m = ora.fr_from_i64(vals).reshape(rows, cols, 32)
+    w = rand_fr(rng, rows)
+    got = be.fold_rows(be.upload(vals, KIND_I64), rows, cols, be.upload(w, KIND_FR_MONT), row_count).download()
+    assert np.array_equal(got, ora.weighted_column_sum(m, w, row_count))
