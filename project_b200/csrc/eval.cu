@@ -900,6 +900,170 @@ namespace gzk
             }
         }
 
+        // ---- row-wise linear forms of a small-integer matrix (gzk_linear_form_rows) ----------------
+        // out[i] = sum_j M[i][j] p_j: here the contraction runs along the contiguous bytes of a matrix row, so the
+        // entries need no transposition at all - a 32-bit word of a row IS four consecutive contraction bytes of an
+        // A fragment.  The other factor is a table, made once per call: P(8j + b) = p_j 2^(8b) mod r as a 32-byte
+        // integer, stored in the order the B fragments want.  An entry enters as u = v + 2^63 (its top bit
+        // flipped), 2^63 sum p_j is taken off every row.  A warp takes 32 rows; the 32 byte sums of a row are
+        // spread over a quad of lanes, which adds them up and reduces one row per lane.
+        __global__ void linear_form_table_kernel(const Fr* powers, uint32_t cols, unsigned char* table)
+        {
+            const uint32_t kappa = blockIdx.x * blockDim.x + threadIdx.x;  // 8j + b
+            if (kappa >= cols * 8) return;
+            Fr value = load_fr(powers + (kappa >> 3));
+            for (uint32_t d = 0; d < 8 * (kappa & 7); ++d) value = add(value, value);
+            const uint32_t step = kappa >> 5, within = kappa & 31, h = within >> 4, t = (within & 15) >> 2, q = within & 3;
+#pragma unroll
+            for (uint32_t n = 0; n < 32; ++n)
+            {
+                const uint32_t word = ((step * 4 + (n >> 3)) * 2 + h) * 32 + (n & 7) * 4 + t;
+                table[word * 4 + q] = static_cast<unsigned char>(value.l[n >> 2] >> (8 * (n & 3)));
+            }
+        }
+
+        // The rows reach the fragments through a per-warp ring: 32 rows x 256 bytes (8 contraction steps) per stage,
+        // 16-byte cp.async copies (coalesced along the rows; a copy behind the last entry fills zeros), rows padded
+        // to 272 bytes so that the eight rows a load instruction touches sit in different banks.
+        constexpr int kFormStepsPerChunk = 8;
+        constexpr int kFormRowStride = kFormStepsPerChunk * 32 + 16;
+        __host__ __device__ constexpr size_t form_stage_bytes() { return static_cast<size_t>(32) * kFormRowStride; }
+        __host__ __device__ constexpr size_t form_smem_bytes() { return static_cast<size_t>(kWarps) * 2 * form_stage_bytes(); }
+
+        __global__ void __launch_bounds__(kThreads) linear_form_tensor_kernel(const unsigned char* matrix, uint64_t rows, uint32_t cols, uint64_t total_entries,
+                                                                              const uint32_t* table, const Fr* bias, Fr* out)
+        {
+            extern __shared__ __align__(128) unsigned char smem[];
+            const uint32_t lane = threadIdx.x & 31;
+            const uint32_t warp_in_cta = threadIdx.x >> 5;
+            const uint32_t g = lane >> 2, t = lane & 3;
+            unsigned char* ring = smem + static_cast<size_t>(warp_in_cta) * 2 * form_stage_bytes();
+            const uint64_t warp = (static_cast<uint64_t>(blockIdx.x) * kThreads + threadIdx.x) >> 5;
+            const uint64_t warps = (static_cast<uint64_t>(gridDim.x) * kThreads) >> 5;
+            const uint32_t steps = cols / 4;
+            const uint32_t chunks = (steps + kFormStepsPerChunk - 1) / kFormStepsPerChunk;
+            const uint64_t row_bytes = static_cast<uint64_t>(cols) * 8;
+            const uint64_t total_bytes = total_entries * 8;
+            const uint32_t flip = (t & 1) ? 0x80000000u : 0u;  // odd words are the upper halves of the entries
+            const Fr offset = load_fr(bias);
+            constexpr uint32_t c288[8] = {0xcaaf6b13u, 0x355094eau, 0x69a568efu, 0xf6b10cb3u, 0x40cc3869u, 0xe2c926a6u, 0xed269aadu, 0x736a6d3bu};  // 2^288 mod r
+            const uint64_t row_blocks = (rows + 31) / 32;
+            const uint64_t my_blocks = warp < row_blocks ? (row_blocks - warp + warps - 1) / warps : 0;
+            const uint64_t sequence = my_blocks * chunks;  // (row block, chunk) pairs of this warp, in order
+            auto request = [&](uint64_t index) {
+                const uint64_t block = warp + (index / chunks) * warps;
+                const uint32_t chunk = static_cast<uint32_t>(index % chunks);
+                unsigned char* stage = ring + static_cast<size_t>(index & 1) * form_stage_bytes();
+                const uint32_t chunk_bytes = (steps - chunk * kFormStepsPerChunk < kFormStepsPerChunk ? steps - chunk * kFormStepsPerChunk : kFormStepsPerChunk) * 32;
+#pragma unroll
+                for (int i = 0; i < 32 * kFormStepsPerChunk * 2 / 32; ++i)
+                {
+                    const uint32_t piece = lane + 32 * i, row = piece >> 4, part = piece & 15;
+                    if (part * 16 >= chunk_bytes) continue;
+                    const uint64_t r = block * 32 + row;
+                    const uint64_t at = r * row_bytes + static_cast<uint64_t>(chunk) * (kFormStepsPerChunk * 32) + part * 16;  // two entries
+                    const uint32_t bytes = (r < rows && at < total_bytes) ? static_cast<uint32_t>(total_bytes - at < 16 ? total_bytes - at : 16) : 0u;
+                    copy16(stage + row * kFormRowStride + part * 16, bytes != 0 ? matrix + at : matrix, bytes);
+                }
+            };
+            if (sequence != 0) request(0);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            for (uint64_t turn = 0; turn < my_blocks; ++turn)
+            {
+                const uint64_t block = warp + turn * warps;
+                int32_t c[2][4][4];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) (&c[0][0][0])[i] = 0;
+                for (uint32_t chunk = 0; chunk < chunks; ++chunk)
+                {
+                    const uint64_t index = turn * chunks + chunk;
+                    if (index + 1 < sequence) request(index + 1);
+                    asm volatile("cp.async.commit_group;" ::: "memory");
+                    asm volatile("cp.async.wait_group 1;" ::: "memory");
+                    __syncwarp();
+                    const unsigned char* stage = ring + static_cast<size_t>(index & 1) * form_stage_bytes();
+                    const uint32_t steps_here = steps - chunk * kFormStepsPerChunk < kFormStepsPerChunk ? steps - chunk * kFormStepsPerChunk : kFormStepsPerChunk;
+#pragma unroll 4
+                    for (uint32_t local = 0; local < steps_here; ++local)
+                    {
+                        const uint32_t s = chunk * kFormStepsPerChunk + local;
+                        uint32_t a[2][4], b[4][2];
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                            for (int half = 0; half < 2; ++half)
+#pragma unroll
+                                for (int k16 = 0; k16 < 2; ++k16)
+                                    a[mt][half + 2 * k16] =
+                                        *reinterpret_cast<const uint32_t*>(stage + (16 * mt + 8 * half + g) * kFormRowStride + 32 * local + 16 * k16 + 4 * t) ^ flip;
+                        const uint32_t* tb = table + static_cast<size_t>(s) * 256 + lane;
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt)
+                        {
+                            b[nt][0] = __ldg(tb + (nt * 2) * 32);
+                            b[nt][1] = __ldg(tb + (nt * 2 + 1) * 32);
+                        }
+#pragma unroll
+                        for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                            for (int nt = 0; nt < 4; ++nt) mma_u8(c[mt][nt], a[mt][0], a[mt][1], a[mt][2], a[mt][3], b[nt][0], b[nt][1]);
+                    }
+                    __syncwarp();  // the stage is requested into again two turns on
+                }
+                // row sums: byte column n = 8 nt + 2 t + e of row (mt, half) sits in c[mt][nt][2 half + e]
+                uint32_t mine[10];
+#pragma unroll
+                for (int i = 0; i < 10; ++i) mine[i] = 0;
+#pragma unroll
+                for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+                    for (int half = 0; half < 2; ++half)
+                    {
+                        uint32_t sum[10];
+#pragma unroll
+                        for (int i = 0; i < 10; ++i) sum[i] = 0;
+#pragma unroll
+                        for (int nt = 0; nt < 4; ++nt)
+                        {
+                            const unsigned long long v = static_cast<unsigned long long>(static_cast<uint32_t>(c[mt][nt][2 * half])) +
+                                                         (static_cast<unsigned long long>(static_cast<uint32_t>(c[mt][nt][2 * half + 1])) << 8);
+                            const unsigned long long low = v << (16 * t);
+                            const unsigned long long high = t == 0 ? 0ull : v >> (64 - 16 * t);
+                            uint32_t part[10];
+#pragma unroll
+                            for (int i = 0; i < 10; ++i) part[i] = 0;
+                            part[2 * nt] = static_cast<uint32_t>(low);
+                            part[2 * nt + 1] = static_cast<uint32_t>(low >> 32);
+                            part[2 * nt + 2] = static_cast<uint32_t>(high);
+                            acc_add<10, 10>(sum, part);
+                        }
+#pragma unroll
+                        for (int across = 1; across <= 2; across <<= 1)
+                        {
+                            uint32_t other[10];
+#pragma unroll
+                            for (int i = 0; i < 10; ++i) other[i] = __shfl_xor_sync(0xffffffffu, sum[i], across);
+                            acc_add<10, 10>(sum, other);
+                        }
+                        if (static_cast<int>(t) == 2 * mt + half)
+                        {
+#pragma unroll
+                            for (int i = 0; i < 10; ++i) mine[i] = sum[i];
+                        }
+                    }
+                // lane t of the quad finishes row (mt, half) = (t / 2, t % 2)
+                const uint64_t r = block * 32 + 16 * (t >> 1) + 8 * (t & 1) + g;
+                if (r < rows)
+                {
+                    const Fr shifted = redc_wide<FrCfg, 1>(mine);  // the sum * 2^-32 mod r
+                    Fr back;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) back.l[i] = c288[i];
+                    store_fr(out + r, sub(mul(shifted, back), offset));
+                }
+            }
+        }
+
         // Resident CTAs per SM of the two kernel variants on the CURRENT device (queried once per
         // device; also opts the kernels into their dynamic shared-memory size, which is a
         // per-device attribute).  Allocates nothing.
@@ -1120,6 +1284,22 @@ namespace gzk
         if (blocks > max_blocks) blocks = max_blocks;
         fold_rows_groups_kernel<<<static_cast<unsigned>(blocks), kThreads, fold_smem_bytes(), ctx->stream>>>(
             static_cast<const unsigned char*>(matrix), reinterpret_cast<const unsigned char*>(weights), row_count, cols, tile_rows, tiles, partial);
+    }
+
+    // gzk_linear_form_rows of an I64 matrix (cols a multiple of four) on the tensor cores.  `table` needs cols * 256
+    // bytes; `bias` holds 2^63 * sum of the powers (Montgomery form); out receives Montgomery values.  Entries at
+    // and behind total_entries count as zero.
+    void launch_linear_form_tensor(gzk_ctx* ctx, const void* matrix, uint64_t rows, uint32_t cols, uint64_t total_entries, const Fr* powers, void* table,
+                                   const Fr* bias, Fr* out)
+    {
+        linear_form_table_kernel<<<(cols * 8 + 255) / 256, 256, 0, ctx->stream>>>(powers, cols, static_cast<unsigned char*>(table));
+        const uint64_t row_blocks = (rows + 31) / 32;
+        uint64_t blocks = (row_blocks + kWarps - 1) / kWarps;
+        const uint64_t max_blocks = static_cast<uint64_t>(ctx->sm_count) * 3;  // what the ring's shared memory lets an SM hold
+        if (blocks > max_blocks) blocks = max_blocks;
+        cudaFuncSetAttribute(linear_form_tensor_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(form_smem_bytes()));
+        linear_form_tensor_kernel<<<static_cast<unsigned>(blocks), kThreads, form_smem_bytes(), ctx->stream>>>(static_cast<const unsigned char*>(matrix), rows, cols, total_entries,
+                                                                                             static_cast<const uint32_t*>(table), bias, out);
     }
 
     // For the other inner-product kernels of the library, which produce partial sums

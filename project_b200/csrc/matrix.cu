@@ -13,6 +13,8 @@ namespace gzk
     uint32_t fold_rows_groups_tiles(gzk_ctx* ctx, size_t row_count, uint32_t cols, uint64_t* tile_rows_out);
     void launch_fold_rows_groups(gzk_ctx* ctx, const void* matrix, const Fr* weights, size_t row_count, uint32_t cols, uint64_t tile_rows, uint32_t tiles,
                                  uint32_t* partial);
+    void launch_linear_form_tensor(gzk_ctx* ctx, const void* matrix, uint64_t rows, uint32_t cols, uint64_t total_entries, const Fr* powers, void* table,
+                                   const Fr* bias, Fr* out);
     int launch_eval_finish(gzk_ctx* ctx, const uint32_t* partial, int uniform_kind, uint32_t tiles, uint32_t k_count,
                            Fr* out, bool out_montgomery);
 
@@ -479,6 +481,12 @@ namespace gzk
         }
 
         // 2^31 in Montgomery form
+        Fr mont_two_63()
+        {
+            Fr v = Fr::one();
+            for (int d = 0; d < 63; ++d) v = add(v, v);
+            return v;
+        }
         Fr mont_two_31()
         {
             Fr v = Fr::one();
@@ -729,6 +737,16 @@ extern "C"
             switch (entry_kind(matrix->kind))
             {
             case GZK_KIND_I64:
+                if (by_thread && cols % 4 == 0 && cols <= 4096)
+                {
+                    // tall matrices: the byte products on the tensor cores (eval.cu); entries enter as v + 2^63
+                    void* table = nullptr;
+                    const int rc_table = ensure_scratch(ctx, 1, cols * 256, &table);
+                    if (rc_table != GZK_OK) return rc_table;
+                    scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, static_cast<uint32_t>(cols), mont_two_63(), bias);
+                    launch_linear_form_tensor(ctx, m.ptr, rows, static_cast<uint32_t>(cols), static_cast<uint64_t>(rows) * cols, powers, table, bias, dst);
+                    break;
+                }
                 // entries enter as v + 2^31: 2^31 * (sum of the powers) is taken off every row
                 scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, static_cast<uint32_t>(cols), mont_two_31(), bias);
                 if (by_thread)

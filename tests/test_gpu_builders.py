@@ -493,7 +493,7 @@ def test_route_edge_indexed_equals_the_accumulator_over_the_gathered_query(be, n
     assert e.value.code == 1
 
 
-@pytest.mark.parametrize("kind_name,rows,cols", [("i64", 40000, 40), ("i64", 38000, 7), ("u32", 39000, 33), ("i64", 37999, 64)])
+@pytest.mark.parametrize("kind_name,rows,cols", [("i64", 40000, 40), ("i64", 38000, 7), ("u32", 39000, 33), ("i64", 37999, 64), ("i64", 38017, 256)])
 def test_linear_form_of_a_tall_small_integer_matrix(be, kind_name, rows, cols):
     """Tall matrices take the thread-per-row kernel (shared-memory tiles of 128 rows x 32 columns): ragged last
     column chunk, ragged last row tile, values of every width."""
