@@ -531,6 +531,9 @@ extern "C"
         m.ptr = matrix->dptr;
         m.kind = matrix->kind;
         Fr x_horner = x;
+        const bool tensor_blocks = blocked && matrix->kind == GZK_KIND_I64 && dot_blocks >= static_cast<uint64_t>(ctx->sm_count) * 32;
+        void* block_table = nullptr;
+        if (tensor_blocks && (rc = ensure_scratch(ctx, 1, static_cast<size_t>(kDotBlock) * 256, &block_table)) != GZK_OK) return rc;
         if (blocked)
         {
             Fr* powers = partial + ctas + 1;
@@ -539,14 +542,19 @@ extern "C"
             {
                 LaunchScope scope(ctx, "powers");
                 powers_kernel<<<kDotBlock / kThreads, kThreads, 0, ctx->stream>>>(x, kDotBlock, powers);
-                if (matrix->kind == GZK_KIND_I64) scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, kDotBlock, mont_two_31(), bias);
+                // many blocks of I64 coefficients: the block sums are a row-wise linear form of a dot_blocks x 1024 matrix
+                // and run on the tensor cores (entries biased by 2^63 there, by 2^31 in block_dot_kernel)
+                if (matrix->kind == GZK_KIND_I64)
+                    scaled_sum_kernel<<<1, kThreads, 0, ctx->stream>>>(powers, kDotBlock, tensor_blocks ? mont_two_63() : mont_two_31(), bias);
             }
             GZK_CUDA_TRY(ctx, cudaGetLastError());
             const uint64_t warps_wanted = dot_blocks < static_cast<uint64_t>(ctx->sm_count) * 64 ? dot_blocks : static_cast<uint64_t>(ctx->sm_count) * 64;
             {
                 LaunchScope scope(ctx, "horner_block_dot");
                 const unsigned grid = static_cast<unsigned>((warps_wanted * 32 + kThreads - 1) / kThreads);
-                if (matrix->kind == GZK_KIND_I64)
+                if (tensor_blocks)
+                    launch_linear_form_tensor(ctx, m.ptr, dot_blocks, kDotBlock, total, powers, block_table, bias, block_values);
+                else if (matrix->kind == GZK_KIND_I64)
                     block_dot_kernel<GZK_KIND_I64><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values, bias);
                 else
                     block_dot_kernel<GZK_KIND_U32><<<grid, kThreads, 0, ctx->stream>>>(m.ptr, total, powers, dot_blocks, block_values, nullptr);

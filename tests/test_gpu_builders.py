@@ -581,3 +581,19 @@ def test_fold_rows_of_small_integers_on_the_tensor_path(be, rows, cols, row_coun
     w = rand_fr(rng, rows)
     got = be.fold_rows(be.upload(vals, KIND_I64), rows, cols, be.upload(w, KIND_FR_MONT), row_count).download()
     assert np.array_equal(got, ora.weighted_column_sum(m, w, row_count))
+
+
+def test_matrix_horner_block_sums_on_the_tensor_path(be):
+    """Polynomial::evaluate of a long small-integer coefficient vector (polynomial.cpp:415-508 semantics through
+    gzk_matrix_horner): enough 1024-coefficient blocks that their sums run as a row-wise linear form on the tensor
+    cores, a ragged last block, negative and extreme coefficients."""
+    from project_b200 import KIND_I64
+
+    rows, cols = 19001, 256  # 4750 blocks and a quarter
+    rng = np.random.default_rng(77)
+    vals = rng.integers(-(1 << 20), 1 << 20, size=rows * cols, dtype=np.int64)
+    vals[:6] = [np.iinfo(np.int64).min, np.iinfo(np.int64).max, -1, 0, 1 << 40, -(1 << 40)]
+    vals[-3:] = [-7, np.iinfo(np.int64).min, 5]
+    x = fr_array([int(rng.integers(2, 1 << 62))])
+    got = be.matrix_horner(be.upload(vals, KIND_I64), rows, cols, x)
+    assert np.array_equal(got, ora.matrix_row_major_eval(ora.fr_from_i64(vals).reshape(rows, cols, 32), x))
