@@ -165,7 +165,10 @@ int gzk_bary_weights_multi(gzk_ctx* ctx, unsigned log2n, const uint8_t* points, 
  * (src/crypto/kzg.cpp:161-282; valid prefix = len, one rotation 0) and
  * dot_product_native_weights (src/algebra/vector_ops.cpp:168-219).
  * cols: K buffers of kind FR / FR_MONT / I64 / U32 with count >= len;
- * weights: FR_MONT with count >= n; out_host: P*K*32 bytes, [p][k]. */
+ * weights: FR_MONT with count >= n; out_host: P*K*32 bytes, [p][k].
+ * The sums are exact integers reduced once: field-element columns form them from byte products on the tensor
+ * cores, small-integer columns on the integer pipe or, at two points, in groups of four on the tensor cores; a call
+ * launches one kernel per kind of column present.  The results do not depend on which kernel took a column. */
 int gzk_eval_batch(gzk_ctx* ctx, gzk_buf* const* cols, size_t k_count, size_t len, unsigned log2n,
                    const gzk_buf* weights, const uint64_t* rotations, size_t p_count, uint8_t* out_host);
 
