@@ -137,3 +137,54 @@ def test_groups_of_integer_columns():
         total = value + (R << 84) - negative
         want = sum(to_int(W[i]) * values[col][i] for i in range(rows))
         assert 0 <= total < 2**544 and total - want == R << 84
+
+
+def test_row_wise_linear_form():
+    """linear_form_tensor_kernel: the words of a matrix row are the A fragments as they lie in memory (upper halves of the
+    entries with their top bit flipped: u = v + 2^63), the powers enter as the byte table P(8j + b) = p_j 2^(8b) mod r in
+    B-fragment order, and a quad of lanes adds the 32 byte sums of a row."""
+    rng = np.random.default_rng(9)
+    cols, rows = 8, 32  # two contraction steps of 32 bytes
+    values = rng.integers(-(1 << 62), 1 << 62, size=(rows, cols), dtype=np.int64)
+    values[0, :3] = [np.iinfo(np.int64).min, np.iinfo(np.int64).max, -1]
+    powers = [int.from_bytes(rng.bytes(32), "little") % R for _ in range(cols)]
+    # the table, written the way linear_form_table_kernel writes it
+    table = bytearray(cols * 256)
+    for kappa in range(cols * 8):
+        entry = (powers[kappa >> 3] << (8 * (kappa & 7))) % R
+        step, within = kappa >> 5, kappa & 31
+        h, t, q = within >> 4, (within & 15) >> 2, within & 3
+        for n in range(32):
+            word = ((step * 4 + (n >> 3)) * 2 + h) * 32 + (n & 7) * 4 + t
+            table[word * 4 + q] = (entry >> (8 * n)) & 255
+    words = np.frombuffer(bytes(table), dtype="<u4")
+    row_bytes = [int(v) & (2**64 - 1) for v in values.reshape(-1)]
+
+    def row_word(r, byte_offset):
+        entry = row_bytes[r * cols + byte_offset // 8]
+        return (entry >> (8 * (byte_offset % 8))) & 0xFFFFFFFF
+
+    c = [[[[0] * 4 for _ in range(4)] for _ in range(2)] for _ in range(32)]
+    for s in range(cols // 4):
+        for mt in range(2):
+            a = []
+            for lane in range(32):
+                g, t = lane >> 2, lane & 3
+                flip = 0x80000000 if t & 1 else 0
+                a.append([row_word(16 * mt + 8 * half + g, 32 * s + 16 * k16 + 4 * t) ^ flip for k16 in range(2) for half in range(2)])
+            for nt in range(4):
+                b = [[int(words[s * 256 + (nt * 2 + h) * 32 + lane]) for h in range(2)] for lane in range(32)]
+                mma([c[l][mt][nt] for l in range(32)], a, b)
+    bias = ((1 << 63) * sum(powers)) % R
+    for mt in range(2):
+        for half in range(2):
+            for g in range(8):
+                total = 0
+                for t in range(4):  # the quad of lanes that shares the row
+                    lane = 4 * g + t
+                    for nt in range(4):
+                        v = c[lane][mt][nt][2 * half] + (c[lane][mt][nt][2 * half + 1] << 8)
+                        total += (v << (16 * t)) << (64 * nt)
+                r = 16 * mt + 8 * half + g
+                want = sum(int(values[r, j]) * powers[j] for j in range(cols)) % R
+                assert total < 2**274 and (total - bias) % R == want
